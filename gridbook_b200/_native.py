@@ -1,0 +1,155 @@
+"""ctypes loader for libgridbook_b200.so — the only route to the kernels.
+
+Replaces the reference's JIT loader (gridbook/cuda_ext.py:344-431,446-522): one
+prebuilt library, a strict required-symbol list, and the same fail-closed rule.
+A missing library or symbol raises :class:`NativeKernelUnavailableError`
+(gridbook/cuda_ext.py:107-113); there is no CPU or eager fallback anywhere.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+GB_ABI_VERSION = 1
+
+REQUIRED_SYMBOLS = (
+    "gb_abi_version", "gb_last_error", "gb_prepare", "gb_device_status",
+    "gb_fp8_act_qdq", "gb_fp4_act_qdq",
+    "gb_expand_fp8", "gb_expand_fp4_bf16", "gb_expand_fp4_nvfp4",
+    "gb_gemv_workspace_bytes", "gb_gemv",
+    "gb_moe_route", "gb_moe_gemv_workspace_bytes", "gb_moe_gemv", "gb_moe_combine",
+)
+
+GRID_FP4, GRID_FP8 = 0, 1
+MODE_PRODUCT, MODE_SIGNED, MODE_FULL = 0, 1, 2
+SCALE_NONE, SCALE_V1, SCALE_V2 = 0, 1, 2
+SCALE_RULE_RECIP, SCALE_RULE_DIV = 0, 1
+ACT_NONE, ACT_FP4_GROUP16, ACT_FP8_TOKEN = 0, 1, 2
+
+
+class NativeKernelUnavailableError(RuntimeError):
+    """The compiled sm_100a library (or one of its entry points) is missing."""
+
+
+class StaleExtensionError(NativeKernelUnavailableError):
+    """The library on disk does not match this package's ABI version."""
+
+
+class GbFormat(ctypes.Structure):
+    _fields_ = [("grid", ctypes.c_int32), ("mode", ctypes.c_int32),
+                ("k_bits", ctypes.c_int32), ("n_sub", ctypes.c_int32),
+                ("type_size", ctypes.c_int32), ("scale_coding", ctypes.c_int32)]
+
+
+class GbWeight(ctypes.Structure):
+    _fields_ = [("qw", ctypes.c_void_p), ("row_stride", ctypes.c_int64),
+                ("codebook", ctypes.c_void_p), ("cb_row_offset", ctypes.c_void_p),
+                ("compose", ctypes.c_void_p), ("weight_scale", ctypes.c_void_p),
+                ("global_scale", ctypes.c_float), ("rows", ctypes.c_int64),
+                ("K", ctypes.c_int64), ("fmt", GbFormat)]
+
+
+_LOCK = threading.Lock()
+_LIB = None
+_PREPARED: set[int] = set()
+
+
+def library_path() -> str:
+    override = os.environ.get("GRIDBOOK_B200_LIB")
+    if override:
+        return override
+    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "libgridbook_b200.so")
+
+
+def _declare(lib) -> None:
+    vp, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
+    wp = ctypes.POINTER(GbWeight)
+    lib.gb_abi_version.restype = i32
+    lib.gb_last_error.restype = ctypes.c_char_p
+    lib.gb_prepare.argtypes = [i32]
+    lib.gb_device_status.argtypes = [i32, ctypes.POINTER(ctypes.c_int)]
+    lib.gb_fp8_act_qdq.argtypes = [vp, vp, i64, i64, i32, vp]
+    lib.gb_fp4_act_qdq.argtypes = [vp, vp, i64, i64, i32, vp]
+    lib.gb_expand_fp8.argtypes = [wp, i64, i64, vp, vp]
+    lib.gb_expand_fp4_bf16.argtypes = [wp, i64, i64, vp, vp]
+    lib.gb_expand_fp4_nvfp4.argtypes = [wp, i64, i64, vp, vp, i32, vp]
+    lib.gb_gemv_workspace_bytes.argtypes = [i64, i64, i64]
+    lib.gb_gemv_workspace_bytes.restype = i64
+    lib.gb_gemv.argtypes = [vp, i64, wp, i32, i32, vp, vp, i64, vp]
+    lib.gb_moe_route.argtypes = [vp, i64, i64, i64, vp, vp, vp, vp]
+    lib.gb_moe_gemv_workspace_bytes.argtypes = [i64, i64]
+    lib.gb_moe_gemv_workspace_bytes.restype = i64
+    lib.gb_moe_gemv.argtypes = [vp, vp, wp, i64, i64, vp, vp, i64, i32, vp, vp, i64, vp]
+    lib.gb_moe_combine.argtypes = [vp, vp, i64, i64, i64, vp, vp]
+    for name in REQUIRED_SYMBOLS:
+        fn = getattr(lib, name)
+        if fn.restype is ctypes.c_int:
+            fn.restype = i32
+
+
+def load(what: str = "gridbook_b200 kernels"):
+    """Return the loaded library or raise NativeKernelUnavailableError."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    with _LOCK:
+        if _LIB is not None:
+            return _LIB
+        path = library_path()
+        if not os.path.exists(path):
+            raise NativeKernelUnavailableError(
+                f"[prismaquant-cb] {what}: {path} is missing. Build it with "
+                "`python -m gridbook_b200.build`; there is no fallback path.")
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as exc:
+            raise NativeKernelUnavailableError(
+                f"[prismaquant-cb] {what}: cannot load {path}: {exc}") from exc
+        missing = [s for s in REQUIRED_SYMBOLS if not hasattr(lib, s)]
+        if missing:
+            raise StaleExtensionError(
+                f"[prismaquant-cb] {what}: {path} lacks required symbols {missing}; rebuild it")
+        _declare(lib)
+        got = lib.gb_abi_version()
+        if got != GB_ABI_VERSION:
+            raise StaleExtensionError(
+                f"[prismaquant-cb] {what}: {path} has ABI version {got}, this package "
+                f"wants {GB_ABI_VERSION}; rebuild it")
+        _LIB = lib
+        return lib
+
+
+def check(rc: int, lib=None) -> None:
+    if rc != 0:
+        lib = lib or load()
+        raise RuntimeError(f"gridbook_b200: {lib.gb_last_error().decode()} (status {rc})")
+
+
+def prepare(device: int | torch.device | None = None) -> None:
+    """One-time per-device set-up; call at model load, never inside a capture."""
+    lib = load()
+    if device is None:
+        device = torch.cuda.current_device()
+    if isinstance(device, torch.device):
+        device = device.index if device.index is not None else torch.cuda.current_device()
+    if device in _PREPARED:
+        return
+    with _LOCK:
+        if device in _PREPARED:
+            return
+        check(lib.gb_prepare(int(device)), lib)
+        _PREPARED.add(device)
+
+
+def device_status(device: int = 0) -> int:
+    lib = load()
+    out = ctypes.c_int(0)
+    check(lib.gb_device_status(int(device), ctypes.byref(out)), lib)
+    return out.value
+
+
+def stream_ptr(device=None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream

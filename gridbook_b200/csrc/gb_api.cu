@@ -1,0 +1,143 @@
+// Host-side plumbing shared by every entry point: error text, per-device
+// set-up, argument validation.
+#include "gb_common.cuh"
+
+#include <mutex>
+#include <string.h>
+
+namespace {
+thread_local char g_error[512] = "";
+std::mutex g_mutex;
+constexpr int kMaxDevices = 64;
+int g_sm_count[kMaxDevices] = {0};
+int* g_status[kMaxDevices] = {nullptr};
+}  // namespace
+
+__device__ int g_gb_status_word = 0;
+
+void gb_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int gb_fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+static int current_device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
+}
+
+static int prepare_locked(int dev) {
+  if (g_sm_count[dev] > 0) return GB_OK;
+  int sms = 0;
+  GB_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  int major = 0;
+  GB_CUDA_OK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  if (major != 10)
+    return gb_fail(GB_EUNSUPPORTED, "device %d has compute capability %d.x; this library is built for sm_100a only", dev, major);
+  void* p = nullptr;
+  GB_CUDA_OK(cudaGetSymbolAddress(&p, g_gb_status_word));
+  g_status[dev] = (int*)p;
+  g_sm_count[dev] = sms;
+  return GB_OK;
+}
+
+int gb_sm_count() {
+  const int dev = current_device_slot();
+  if (dev < 0) return 0;
+  if (g_sm_count[dev] == 0) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (prepare_locked(dev) != GB_OK) return 0;
+  }
+  return g_sm_count[dev];
+}
+
+int* gb_status_word() {
+  const int dev = current_device_slot();
+  if (dev < 0 || gb_sm_count() == 0) return nullptr;
+  return g_status[dev];
+}
+
+int gb_check_format(const gb_format& f, int64_t K) {
+  GB_REQUIRE(K > 0 && K % 256 == 0, "K=%lld must be a positive multiple of 256", (long long)K);
+  GB_REQUIRE(f.grid == GB_GRID_FP4 || f.grid == GB_GRID_FP8, "unknown grid %d", f.grid);
+  GB_REQUIRE(f.mode >= GB_MODE_PRODUCT && f.mode <= GB_MODE_FULL, "unknown mode %d", f.mode);
+  if (f.mode == GB_MODE_PRODUCT) {
+    GB_REQUIRE(f.n_sub == 2 || f.n_sub == 4, "product mode wants n_sub 2 or 4, got %d", f.n_sub);
+    GB_REQUIRE(f.k_bits >= f.n_sub && f.k_bits <= 48, "k_bits %d out of range", f.k_bits);
+    GB_REQUIRE((f.k_bits + f.n_sub - 1) / f.n_sub <= 14, "sub-table of 2^%d rows is too large",
+               (f.k_bits + f.n_sub - 1) / f.n_sub);
+  } else if (f.mode == GB_MODE_SIGNED) {
+    GB_REQUIRE(f.k_bits >= 9 && f.k_bits <= 22, "signed mode wants 9 <= k_bits <= 22, got %d", f.k_bits);
+  } else {
+    GB_REQUIRE(f.k_bits >= 1 && f.k_bits <= 14, "full mode wants 1 <= k_bits <= 14, got %d", f.k_bits);
+  }
+  int scale_bytes = 0;
+  if (f.grid == GB_GRID_FP4) {
+    GB_REQUIRE(f.scale_coding == GB_SCALE_V1 || f.scale_coding == GB_SCALE_V2,
+               "fp4 grid wants scale coding v1 or v2, got %d", f.scale_coding);
+    scale_bytes = f.scale_coding == GB_SCALE_V1 ? 16 : 9;
+  } else {
+    GB_REQUIRE(f.scale_coding == GB_SCALE_NONE, "fp8 grid carries no scale plane");
+  }
+  GB_REQUIRE(f.type_size == 4 * f.k_bits + scale_bytes,
+             "type_size %d does not match 4*%d+%d for this grid/scale coding", f.type_size,
+             f.k_bits, scale_bytes);
+  return GB_OK;
+}
+
+int gb_check_weight(const gb_weight* w) {
+  GB_REQUIRE(w != nullptr, "null weight descriptor");
+  int rc = gb_check_format(w->fmt, w->K);
+  if (rc != GB_OK) return rc;
+  GB_REQUIRE(w->qw != nullptr && w->codebook != nullptr, "null packed weights or codebook");
+  GB_REQUIRE(w->rows > 0, "rows=%lld", (long long)w->rows);
+  GB_REQUIRE(w->row_stride >= (w->K / 256) * w->fmt.type_size,
+             "row stride %lld is shorter than the packed row (%lld bytes)",
+             (long long)w->row_stride, (long long)((w->K / 256) * w->fmt.type_size));
+  if (w->fmt.grid == GB_GRID_FP8)
+    GB_REQUIRE(w->weight_scale != nullptr, "fp8 grid needs the per-row weight_scale");
+  if (w->fmt.scale_coding == GB_SCALE_V2)
+    GB_REQUIRE(w->compose != nullptr, "two-tier scale coding needs the compose table");
+  return GB_OK;
+}
+
+extern "C" {
+
+int gb_abi_version(void) { return GB_ABI_VERSION; }
+
+const char* gb_last_error(void) { return g_error; }
+
+int gb_prepare(int device) {
+  GB_REQUIRE(device >= 0 && device < kMaxDevices, "device %d out of range", device);
+  int prev = 0;
+  GB_CUDA_OK(cudaGetDevice(&prev));
+  GB_CUDA_OK(cudaSetDevice(device));
+  int rc;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    rc = prepare_locked(device);
+  }
+  if (rc == GB_OK) rc = gb_prepare_kernels();
+  cudaSetDevice(prev);
+  return rc;
+}
+
+int gb_device_status(int device, int* status_out) {
+  GB_REQUIRE(status_out != nullptr, "null status_out");
+  GB_REQUIRE(device >= 0 && device < kMaxDevices && g_status[device] != nullptr,
+             "device %d was not prepared", device);
+  GB_CUDA_OK(cudaMemcpy(status_out, g_status[device], sizeof(int), cudaMemcpyDeviceToHost));
+  return GB_OK;
+}
+
+}  // extern "C"

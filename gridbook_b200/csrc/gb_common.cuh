@@ -1,0 +1,221 @@
+// Shared host/device helpers for the gridbook_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#include "../../include/gridbook_b200.h"
+
+#define GB_DEVINL __device__ __forceinline__
+
+// ---------------------------------------------------------------------------
+// host-side error plumbing
+// ---------------------------------------------------------------------------
+void gb_set_error(const char* fmt, ...);
+int gb_fail(int code, const char* fmt, ...);
+int gb_sm_count();                 // SMs of the current device (cached)
+int* gb_status_word();             // device int the kernels raise on a timed-out wait
+
+#define GB_REQUIRE(cond, ...)                           \
+  do {                                                  \
+    if (!(cond)) return gb_fail(GB_EINVAL, __VA_ARGS__); \
+  } while (0)
+
+#define GB_CUDA_OK(expr)                                                       \
+  do {                                                                         \
+    cudaError_t e_ = (expr);                                                   \
+    if (e_ != cudaSuccess)                                                     \
+      return gb_fail(GB_ECUDA, "%s: %s", #expr, cudaGetErrorString(e_));       \
+  } while (0)
+
+#define GB_LAUNCH_OK(name)                                                     \
+  do {                                                                         \
+    cudaError_t e_ = cudaGetLastError();                                       \
+    if (e_ != cudaSuccess)                                                     \
+      return gb_fail(GB_ECUDA, "launch of %s: %s", name, cudaGetErrorString(e_)); \
+  } while (0)
+
+int gb_check_format(const gb_format& f, int64_t K);
+int gb_check_weight(const gb_weight* w);
+int gb_prepare_kernels();          // per-device function attributes of the big kernels
+
+// ---------------------------------------------------------------------------
+// scalar formats
+// ---------------------------------------------------------------------------
+GB_DEVINL float gb_bf16_bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
+
+GB_DEVINL uint32_t gb_f32_to_bf16_bits(float v) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+// E4M3 byte -> fp32, exact (no NaN handling: 0x7F/0xFF decode as 480, never stored).
+GB_DEVINL float gb_e4m3_to_f32(uint32_t b) {
+  const uint32_t mag = b & 0x7Fu;
+  // place exponent+mantissa at the fp32 exponent, then rebias by 2^120; the
+  // multiply also renormalises the subnormal codes (exponent field 0).
+  float f = __uint_as_float(mag << 20) * 0x1p120f;
+  return (b & 0x80u) ? -f : f;
+}
+
+// fp32 -> E4M3 with ONE rounding to nearest even (the hardware cvt may round
+// twice through fp16).  |f| must be < 480; callers clamp to 448 first.
+GB_DEVINL uint32_t gb_f32_to_e4m3(float f) {
+  uint32_t u = __float_as_uint(f);
+  const uint32_t sign = (u >> 24) & 0x80u;
+  u &= 0x7FFFFFFFu;
+  uint32_t r;
+  if (u < (121u << 23)) {
+    // below 2^-6 the result is subnormal with quantum 2^-9: adding 2^14 makes
+    // the fp32 adder do the nearest-even rounding at exactly that quantum.
+    const float shifted = __uint_as_float(u) + 16384.0f;
+    r = __float_as_uint(shifted) - __float_as_uint(16384.0f);
+  } else {
+    const uint32_t odd = (u >> 20) & 1u;
+    u += 0x7FFFFu + odd;            // round at bit 20
+    r = (u >> 20) - (120u << 3);    // rebias exponent 127 -> 7
+  }
+  return (r & 0x7Fu) | sign;
+}
+
+// ---------------------------------------------------------------------------
+// bit-stream extraction (docs/SPEC.md:56-92): codeword c of a superblock
+// occupies stream bits [c*k, c*k+k), least significant bit first.
+// ---------------------------------------------------------------------------
+// p must point at a 4-byte aligned address at or before the first needed byte;
+// bit is the offset of the codeword's LSB from p (may exceed 31).
+template <typename Ptr>
+GB_DEVINL uint64_t gb_extract_bits(Ptr words, uint32_t bit, int k_bits) {
+  const uint32_t w = bit >> 5, s = bit & 31u;
+  const uint32_t a = words[w], b = words[w + 1];
+  uint64_t lo = __funnelshift_r(a, b, s);
+  if (k_bits > 32) {
+    const uint32_t c = words[w + 2];
+    lo |= (uint64_t)__funnelshift_r(b, c, s) << 32;
+  }
+  return k_bits >= 64 ? lo : (lo & ((1ull << k_bits) - 1ull));
+}
+
+// Generic byte-granular version for unaligned global rows (expand kernels).
+GB_DEVINL uint64_t gb_extract_bits_bytes(const uint8_t* p, int64_t nbytes_valid,
+                                         uint32_t bit, int k_bits) {
+  const uint32_t byte0 = bit >> 3, s = bit & 7u;
+  uint64_t win = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int64_t idx = (int64_t)byte0 + i;
+    const uint64_t v = idx < nbytes_valid ? (uint64_t)p[idx] : 0ull;
+    win |= v << (8 * i);
+  }
+  return (win >> s) & ((1ull << k_bits) - 1ull);
+}
+
+struct GbSplit {
+  int width[4];
+  int shift[4];
+  int base[4];   // element offset of sub-table i inside one codebook block
+  int sub_dim;
+  int n_sub;
+};
+
+__host__ __device__ inline GbSplit gb_make_split(int k_bits, int n_sub) {
+  GbSplit s;
+  s.n_sub = n_sub;
+  s.sub_dim = 8 / n_sub;
+  int off = 0, base = 0;
+  for (int i = 0; i < 4; ++i) {
+    if (i < n_sub) {
+      s.width[i] = k_bits / n_sub + (i < k_bits % n_sub ? 1 : 0);
+      s.shift[i] = off;
+      s.base[i] = base;
+      off += s.width[i];
+      base += (1 << s.width[i]) * s.sub_dim;
+    } else {
+      s.width[i] = 0; s.shift[i] = 0; s.base[i] = 0;
+    }
+  }
+  return s;
+}
+
+__host__ __device__ inline int64_t gb_codebook_elems(const gb_format& f) {
+  if (f.mode == GB_MODE_FULL) return (int64_t)8 << f.k_bits;
+  if (f.mode == GB_MODE_SIGNED) return (int64_t)8 << (f.k_bits - 8);
+  GbSplit s = gb_make_split(f.k_bits, f.n_sub);
+  return (int64_t)s.base[f.n_sub - 1] + ((int64_t)s.sub_dim << s.width[f.n_sub - 1]);
+}
+
+// ---------------------------------------------------------------------------
+// mbarrier / bulk-copy primitives (all waits are bounded)
+// ---------------------------------------------------------------------------
+GB_DEVINL uint32_t gb_smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+GB_DEVINL void gb_mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(gb_smem_u32(bar)), "r"(count));
+}
+
+GB_DEVINL void gb_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(gb_smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+
+GB_DEVINL void gb_mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gb_smem_u32(bar)) : "memory");
+}
+
+GB_DEVINL uint64_t gb_globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Returns false when the wait ran out of patience (two seconds of wall clock);
+// the caller raises the status word and leaves the kernel.
+GB_DEVINL bool gb_mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = gb_smem_u32(bar);
+  uint64_t t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((spin & 255u) == 255u) {
+      const uint64_t now = gb_globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 2000000000ull) return false;
+    }
+  }
+}
+
+// 1-D bulk copy global -> this CTA's shared memory, completion on an mbarrier.
+// Both addresses 16-byte aligned, bytes a multiple of 16.
+GB_DEVINL void gb_bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          gb_smem_u32(smem_dst)),
+      "l"(gmem_src), "r"(bytes), "r"(gb_smem_u32(bar))
+      : "memory");
+}
+
+GB_DEVINL void gb_fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+GB_DEVINL void gb_mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}

@@ -1,0 +1,310 @@
+// Activation buckets and decoded-tile expanders.
+//
+// The expanders are the bit-exact gate of the whole library: every other kernel's
+// decode reduces to "the tile it multiplies equals what these write".
+#include "gb_common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+// ---------------------------------------------------------------------------
+// Activation buckets (gridbook/codec.py:248-260, 428-437)
+// ---------------------------------------------------------------------------
+// Signed E2M1 grid, ascending; +0 and -0 are one rung.
+__device__ __constant__ float kE2M1Grid[15] = {-6.0f, -4.0f, -3.0f, -2.0f, -1.5f, -1.0f, -0.5f, 0.0f,
+                                               0.5f,  1.0f,  1.5f,  2.0f,  3.0f,  4.0f,  6.0f};
+
+// Round-to-nearest on the signed grid with the reference's tie rule: the upper
+// neighbour wins only when it is STRICTLY closer, so an exact midpoint goes to
+// the lower (more negative) rung.
+GB_DEVINL float e2m1_rtn(float v) {
+  int idx = 15;  // first rung >= v  (bucketize, right = false)
+#pragma unroll
+  for (int i = 14; i >= 0; --i)
+    if (kE2M1Grid[i] >= v) idx = i;
+  const float lo = kE2M1Grid[idx > 0 ? idx - 1 : 0];
+  const float hi = kE2M1Grid[idx < 15 ? idx : 14];
+  return fabsf(__fsub_rn(hi, v)) < fabsf(__fsub_rn(v, lo)) ? hi : lo;
+}
+
+// One thread per group of 16: two 16-byte loads, amax, scale, 16 roundings.
+__global__ void __launch_bounds__(kThreads)
+fp4_group16_qdq_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out,
+                       int64_t n_groups, int scale_rule) {
+  const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= n_groups) return;
+  const uint4* src = reinterpret_cast<const uint4*>(x + g * 16);
+  uint4 raw[2] = {src[0], src[1]};
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(raw);
+  float v[16];
+  float amax = 0.0f;
+  bool has_nan = false;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[2 * i] = gb_bf16_bits_to_f32(w[i] & 0xFFFFu);
+    v[2 * i + 1] = gb_bf16_bits_to_f32(w[i] >> 16);
+    amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+    has_nan |= isnan(v[2 * i]) || isnan(v[2 * i + 1]);
+  }
+  amax = fmaxf(amax, 1e-8f);
+  float scale = scale_rule == GB_SCALE_RULE_DIV ? __fdiv_rn(amax, 6.0f)
+                                                : __fmul_rn(amax, 1.0f / 6.0f);
+  if (has_nan) scale = __int_as_float(0x7FC00000);
+  uint32_t packed[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float q0 = __fmul_rn(e2m1_rtn(__fdiv_rn(v[2 * i], scale)), scale);
+    const float q1 = __fmul_rn(e2m1_rtn(__fdiv_rn(v[2 * i + 1], scale)), scale);
+    packed[i] = gb_f32_to_bf16_bits(q0) | (gb_f32_to_bf16_bits(q1) << 16);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(out + g * 16);
+  dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+}
+
+// One block per token row: block-wide amax, then every element is scaled,
+// rounded once to E4M3 and scaled back.
+__global__ void __launch_bounds__(kThreads)
+fp8_token_qdq_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, int64_t K,
+                     int scale_rule) {
+  const uint16_t* row = x + (int64_t)blockIdx.x * K;
+  uint16_t* orow = out + (int64_t)blockIdx.x * K;
+  __shared__ float red[kThreads / 32];
+  __shared__ float s_scale;
+  float amax = 0.0f;
+  for (int64_t i = threadIdx.x; i < K; i += blockDim.x)
+    amax = fmaxf(amax, fabsf(gb_bf16_bits_to_f32(row[i])));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = red[0];
+    for (int w = 1; w < kThreads / 32; ++w) a = fmaxf(a, red[w]);
+    const float s = scale_rule == GB_SCALE_RULE_DIV ? __fdiv_rn(a, 448.0f)
+                                                    : __fmul_rn(a, 1.0f / 448.0f);
+    s_scale = fmaxf(s, 1.0f / (448.0f * 512.0f));
+  }
+  __syncthreads();
+  const float scale = s_scale;
+  for (int64_t i = threadIdx.x; i < K; i += blockDim.x) {
+    const float v = gb_bf16_bits_to_f32(row[i]);
+    const float q = fminf(fmaxf(__fdiv_rn(v, scale), -448.0f), 448.0f);
+    const float dq = gb_e4m3_to_f32(gb_f32_to_e4m3(q));
+    orow[i] = (uint16_t)gb_f32_to_bf16_bits(__fmul_rn(dq, scale));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Expanders.  One warp per (row, superblock); lane v owns codeword v, i.e. the
+// eight weights [8v, 8v+8) of the superblock and half of group v/2.
+// ---------------------------------------------------------------------------
+struct ExpandArgs {
+  const uint8_t* qw;
+  int64_t row_stride;
+  int64_t valid_bytes;   // bytes that may be read from the first row's start
+  const void* codebook;
+  const int32_t* cb_row_offset;
+  const float* compose;
+  int64_t row0, nrows, K;
+  gb_format fmt;
+  GbSplit split;
+};
+
+// Codebook values of one codeword as fp32 (exact for both grids).
+template <bool kFp8>
+GB_DEVINL void gather_values(const ExpandArgs& a, int64_t cb_base, uint64_t code, float (&val)[8]) {
+  auto load = [&](int64_t idx) -> float {
+    if constexpr (kFp8)
+      return gb_e4m3_to_f32(reinterpret_cast<const uint8_t*>(a.codebook)[cb_base + idx]);
+    else
+      return gb_bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(a.codebook)[cb_base + idx]);
+  };
+  if (a.fmt.mode == GB_MODE_FULL) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) val[j] = load((int64_t)code * 8 + j);
+  } else if (a.fmt.mode == GB_MODE_SIGNED) {
+    const int64_t mag = (int64_t)(code >> 8);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float m = load(mag * 8 + j);
+      val[j] = ((code >> j) & 1ull) ? -m : m;
+    }
+  } else {
+    const int sd = a.split.sub_dim;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int s = j / sd;   // sd is 2 or 4, so s < n_sub
+      const int64_t idx = (int64_t)((code >> a.split.shift[s]) & ((1ull << a.split.width[s]) - 1ull));
+      val[j] = load(a.split.base[s] + idx * sd + (j - s * sd));
+    }
+  }
+}
+
+// Group scale of codeword v (group v/2) for the fp4 grid, as fp32 and as its E4M3 byte.
+GB_DEVINL float fp4_group_scale(const ExpandArgs& a, const uint8_t* sb, int v, uint32_t* byte_out) {
+  const int g = v >> 1;
+  const uint8_t* plane = sb + 4 * a.fmt.k_bits;
+  if (a.fmt.scale_coding == GB_SCALE_V1) {
+    const uint32_t b = plane[g];
+    *byte_out = b;
+    return gb_e4m3_to_f32(b);
+  }
+  const uint32_t e = plane[0];
+  const uint32_t nib = (plane[1 + (g >> 1)] >> ((g & 1) * 4)) & 0xFu;
+  const float s = a.compose[e * 16 + nib];
+  *byte_out = gb_f32_to_e4m3(fminf(s, 448.0f));   // exact for every legal (E, c) pair
+  return s;
+}
+
+enum { kOutFp8 = 0, kOutBf16 = 1, kOutNvfp4 = 2 };
+
+template <int kOut>
+__global__ void __launch_bounds__(kThreads)
+expand_kernel(ExpandArgs a, void* __restrict__ out0, uint8_t* __restrict__ out_sf, int sf_swizzled) {
+  const int lane = threadIdx.x & 31;
+  const int64_t n_sb = a.K / 256;
+  const int64_t unit = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  if (unit >= a.nrows * n_sb) return;
+  const int64_t r = unit / n_sb, s = unit - r * n_sb;
+  const int64_t row = a.row0 + r;
+  const int64_t sb_off = r * a.row_stride + s * a.fmt.type_size;
+  const uint8_t* sb = a.qw + sb_off;   // a.qw is the first byte of row0
+  const uint64_t code =
+      gb_extract_bits_bytes(sb, a.valid_bytes - sb_off, (uint32_t)(lane * a.fmt.k_bits), a.fmt.k_bits);
+  const int64_t cb_base = a.cb_row_offset ? (int64_t)a.cb_row_offset[row] : 0;
+  float val[8];
+  gather_values<kOut == kOutFp8>(a, cb_base, code, val);
+  const int64_t col = s * 256 + lane * 8;
+
+  if constexpr (kOut == kOutFp8) {
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      lo |= gb_f32_to_e4m3(val[j]) << (8 * j);
+      hi |= gb_f32_to_e4m3(val[4 + j]) << (8 * j);
+    }
+    *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(out0) + r * a.K + col) = make_uint2(lo, hi);
+  } else if constexpr (kOut == kOutBf16) {
+    uint32_t sbyte;
+    const float scale = fp4_group_scale(a, sb, lane, &sbyte);
+    uint32_t p[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      p[j] = gb_f32_to_bf16_bits(__fmul_rn(val[2 * j], scale)) |
+             (gb_f32_to_bf16_bits(__fmul_rn(val[2 * j + 1], scale)) << 16);
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out0) + r * a.K + col) =
+        make_uint4(p[0], p[1], p[2], p[3]);
+  } else {
+    uint32_t nib = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      // E2M1 code: magnitudes {0,.5,1,1.5,2,3,4,6} -> 0..7, bit 3 = sign
+      const float m = fabsf(val[j]);
+      const uint32_t c = m < 2.0f ? (uint32_t)(m * 2.0f) : (m < 4.0f ? (uint32_t)m + 2u : (m < 6.0f ? 6u : 7u));
+      nib |= (c | (val[j] < 0.0f ? 8u : 0u)) << (4 * j);
+    }
+    reinterpret_cast<uint32_t*>(out0)[(r * a.K + col) >> 3] = nib;
+    if ((lane & 1) == 0) {
+      uint32_t sbyte;
+      (void)fp4_group_scale(a, sb, lane, &sbyte);
+      const int64_t groups = a.K / 16;
+      const int64_t g = s * 16 + (lane >> 1);
+      int64_t off = r * groups + g;
+      if (sf_swizzled) {
+        const int64_t gpad = (groups + 3) / 4 * 4;
+        off = (r % 32) * 16 + ((r / 32) % 4) * 4 + (g % 4) + (g / 4) * 512 + (r / 128) * (512 * (gpad / 4));
+      }
+      out_sf[off] = (uint8_t)sbyte;
+    }
+  }
+}
+
+int make_expand_args(const gb_weight* w, int64_t row0, int64_t nrows, ExpandArgs* a) {
+  int rc = gb_check_weight(w);
+  if (rc != GB_OK) return rc;
+  GB_REQUIRE(row0 >= 0 && nrows > 0 && row0 + nrows <= w->rows, "rows [%lld, %lld) outside [0, %lld)",
+             (long long)row0, (long long)(row0 + nrows), (long long)w->rows);
+  a->qw = w->qw;
+  a->row_stride = w->row_stride;
+  a->codebook = w->codebook;
+  a->cb_row_offset = w->cb_row_offset;
+  a->compose = w->compose;
+  a->row0 = row0;
+  a->nrows = nrows;
+  a->K = w->K;
+  a->fmt = w->fmt;
+  a->split = gb_make_split(w->fmt.k_bits, w->fmt.mode == GB_MODE_PRODUCT ? w->fmt.n_sub : 1);
+  return GB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int gb_fp4_act_qdq(const void* x, void* out, int64_t M, int64_t K, int scale_rule, void* stream) {
+  GB_REQUIRE(x && out, "null activation pointer");
+  GB_REQUIRE(M >= 0 && K > 0 && K % 16 == 0, "fp4 activation bucket wants K %% 16 == 0, got K=%lld",
+             (long long)K);
+  if (M == 0) return GB_OK;
+  const int64_t groups = M * (K / 16);
+  const unsigned blocks = (unsigned)((groups + kThreads - 1) / kThreads);
+  fp4_group16_qdq_kernel<<<blocks, kThreads, 0, (cudaStream_t)stream>>>(
+      (const uint16_t*)x, (uint16_t*)out, groups, scale_rule);
+  GB_LAUNCH_OK("fp4_group16_qdq_kernel");
+  return GB_OK;
+}
+
+int gb_fp8_act_qdq(const void* x, void* out, int64_t M, int64_t K, int scale_rule, void* stream) {
+  GB_REQUIRE(x && out, "null activation pointer");
+  GB_REQUIRE(M >= 0 && K > 0, "bad shape M=%lld K=%lld", (long long)M, (long long)K);
+  if (M == 0) return GB_OK;
+  fp8_token_qdq_kernel<<<(unsigned)M, kThreads, 0, (cudaStream_t)stream>>>(
+      (const uint16_t*)x, (uint16_t*)out, K, scale_rule);
+  GB_LAUNCH_OK("fp8_token_qdq_kernel");
+  return GB_OK;
+}
+
+}  // extern "C"
+
+namespace {
+template <int kOut>
+int launch_expand(const gb_weight* w, int64_t row0, int64_t nrows, void* out0, void* out_sf,
+                  int sf_swizzled, void* stream) {
+  ExpandArgs a;
+  int rc = make_expand_args(w, row0, nrows, &a);
+  if (rc != GB_OK) return rc;
+  GB_REQUIRE(out0 != nullptr, "null output");
+  // The kernel addresses rows relative to row0 so that `valid_bytes` bounds every read.
+  a.qw = w->qw + row0 * w->row_stride;
+  a.valid_bytes = (nrows - 1) * w->row_stride + (w->K / 256) * w->fmt.type_size;
+  const int64_t units = nrows * (w->K / 256);
+  const unsigned blocks = (unsigned)((units + kThreads / 32 - 1) / (kThreads / 32));
+  expand_kernel<kOut><<<blocks, kThreads, 0, (cudaStream_t)stream>>>(a, out0, (uint8_t*)out_sf,
+                                                                    sf_swizzled);
+  GB_LAUNCH_OK("expand_kernel");
+  return GB_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int gb_expand_fp8(const gb_weight* w, int64_t row0, int64_t nrows, void* out, void* stream) {
+  GB_REQUIRE(w && w->fmt.grid == GB_GRID_FP8, "gb_expand_fp8 wants an fp8-grid weight");
+  return launch_expand<kOutFp8>(w, row0, nrows, out, nullptr, 0, stream);
+}
+
+int gb_expand_fp4_bf16(const gb_weight* w, int64_t row0, int64_t nrows, void* out, void* stream) {
+  GB_REQUIRE(w && w->fmt.grid == GB_GRID_FP4, "gb_expand_fp4_bf16 wants an fp4-grid weight");
+  return launch_expand<kOutBf16>(w, row0, nrows, out, nullptr, 0, stream);
+}
+
+int gb_expand_fp4_nvfp4(const gb_weight* w, int64_t row0, int64_t nrows, void* out_packed,
+                        void* out_sf, int sf_swizzled, void* stream) {
+  GB_REQUIRE(w && w->fmt.grid == GB_GRID_FP4, "gb_expand_fp4_nvfp4 wants an fp4-grid weight");
+  GB_REQUIRE(out_sf != nullptr, "null scale-factor output");
+  return launch_expand<kOutNvfp4>(w, row0, nrows, out_packed, out_sf, sf_swizzled, stream);
+}
+
+}  // extern "C"

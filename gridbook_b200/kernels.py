@@ -1,0 +1,224 @@
+"""Tensor-level wrappers over the C ABI: build a ``gb_weight`` from torch tensors,
+pass raw pointers and the current stream, turn a non-zero status into
+RuntimeError.  Every function here launches CUDA work or raises; none computes
+on the host."""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import _native as nat
+from .formats import CBFormat
+
+_ZERO = ctypes.c_void_p(0)
+
+
+def _ptr(t: torch.Tensor | None):
+    return _ZERO if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("gridbook_b200 kernels take CUDA tensors only (no CPU path exists)")
+
+
+@dataclass
+class PackedWeight:
+    """One packed matrix (or one expert's matrix of a stack) as the kernels see it."""
+    qw: torch.Tensor                      # uint8 [rows, >= row_bytes] (or [E, rows, bytes])
+    codebook: torch.Tensor                # bf16 flat (fp4) / uint8 E4M3 flat (fp8)
+    fmt: CBFormat
+    K: int
+    rows: int
+    row_stride: int
+    cb_row_offset: torch.Tensor | None = None   # int32 [rows]
+    compose: torch.Tensor | None = None         # fp32 [4096], v2 only
+    weight_scale: torch.Tensor | None = None    # fp32 [rows] (or [E, rows]), fp8 only
+    global_scale: float = 1.0
+    expert_stride: int = 0
+    experts: int = 1
+
+    def native(self) -> nat.GbWeight:
+        return nat.GbWeight(
+            qw=self.qw.data_ptr(), row_stride=self.row_stride,
+            codebook=self.codebook.data_ptr(),
+            cb_row_offset=None if self.cb_row_offset is None else self.cb_row_offset.data_ptr(),
+            compose=None if self.compose is None else self.compose.data_ptr(),
+            weight_scale=None if self.weight_scale is None else self.weight_scale.data_ptr(),
+            global_scale=float(self.global_scale), rows=self.rows, K=self.K,
+            fmt=self.fmt.to_native())
+
+    @property
+    def packed_bytes(self) -> int:
+        """Algorithmic weight-stream bytes of one pass over this matrix (all experts)."""
+        return self.experts * self.rows * self.fmt.row_bytes(self.K)
+
+
+def make_weight(qw, codebook, fmt: CBFormat, K: int, *, cb_row_offset=None, compose=None,
+                weight_scale=None, global_scale: float = 1.0) -> PackedWeight:
+    _need_cuda(qw, codebook, cb_row_offset, compose, weight_scale)
+    if qw.dtype is not torch.uint8 or qw.stride(-1) != 1:
+        raise RuntimeError("packed weights must be uint8 with a unit inner stride")
+    if fmt.is_fp4:
+        if codebook.dtype is not torch.bfloat16:
+            raise RuntimeError("fp4-grid codebooks are bf16 flat tables")
+        if fmt.scale_coding == "v2" and compose is None:
+            raise RuntimeError("two-tier scale coding needs the compose table")
+    else:
+        if codebook.dtype is not torch.uint8:
+            raise RuntimeError("fp8-grid codebooks are E4M3 bytes")
+        if weight_scale is None:
+            raise RuntimeError("fp8-grid weights need weight_scale")
+    if qw.dim() == 3:
+        experts, rows = qw.shape[0], qw.shape[1]
+        return PackedWeight(qw, codebook, fmt, K, rows, qw.stride(1), cb_row_offset, compose,
+                            weight_scale, global_scale, qw.stride(0), experts)
+    return PackedWeight(qw, codebook, fmt, K, qw.shape[0], qw.stride(0), cb_row_offset, compose,
+                        weight_scale, global_scale)
+
+
+def _rule(scale_rule: str) -> int:
+    return nat.SCALE_RULE_DIV if scale_rule == "div" else nat.SCALE_RULE_RECIP
+
+
+def fp4_act_qdq(x: torch.Tensor, scale_rule: str = "recip") -> torch.Tensor:
+    _need_cuda(x)
+    lib = nat.load("FP4 activation QDQ")
+    if x.dtype is not torch.bfloat16:
+        raise TypeError("native FP4 activation QDQ requires CUDA BF16")
+    if x.shape[-1] % 16:
+        raise RuntimeError("fp4_act_qdq needs a last dim that is a multiple of the fp4 group (16)")
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    K = x.shape[-1]
+    nat.check(lib.gb_fp4_act_qdq(_ptr(x), _ptr(out), x.numel() // K, K, _rule(scale_rule),
+                                 nat.stream_ptr(x.device)), lib)
+    return out
+
+
+def fp8_act_qdq(x: torch.Tensor, scale_rule: str = "recip") -> torch.Tensor:
+    _need_cuda(x)
+    lib = nat.load("FP8 activation QDQ")
+    if x.dtype is not torch.bfloat16:
+        raise TypeError("native FP8 activation QDQ requires CUDA BF16")
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    K = x.shape[-1]
+    nat.check(lib.gb_fp8_act_qdq(_ptr(x), _ptr(out), x.numel() // K, K, _rule(scale_rule),
+                                 nat.stream_ptr(x.device)), lib)
+    return out
+
+
+def expand_fp8(w: PackedWeight, row0: int = 0, nrows: int | None = None) -> torch.Tensor:
+    lib = nat.load("FP8-CB transient expansion")
+    nrows = w.rows - row0 if nrows is None else nrows
+    out = torch.empty((nrows, w.K), dtype=torch.float8_e4m3fn, device=w.qw.device)
+    nw = w.native()
+    nat.check(lib.gb_expand_fp8(ctypes.byref(nw), row0, nrows, _ptr(out),
+                                nat.stream_ptr(w.qw.device)), lib)
+    return out
+
+
+def expand_fp4_bf16(w: PackedWeight, row0: int = 0, nrows: int | None = None) -> torch.Tensor:
+    lib = nat.load("FP4-CB transient expansion")
+    nrows = w.rows - row0 if nrows is None else nrows
+    out = torch.empty((nrows, w.K), dtype=torch.bfloat16, device=w.qw.device)
+    nw = w.native()
+    nat.check(lib.gb_expand_fp4_bf16(ctypes.byref(nw), row0, nrows, _ptr(out),
+                                     nat.stream_ptr(w.qw.device)), lib)
+    return out
+
+
+def expand_fp4_nvfp4(w: PackedWeight, row0: int = 0, nrows: int | None = None,
+                     swizzled: bool = False):
+    """-> (packed E2M1 [nrows, K/2] uint8, E4M3 group scales: [nrows, K/16] or the flat
+    128x4-atom plane)."""
+    lib = nat.load("NVFP4 tile expansion")
+    nrows = w.rows - row0 if nrows is None else nrows
+    dev = w.qw.device
+    packed = torch.empty((nrows, w.K // 2), dtype=torch.uint8, device=dev)
+    groups = w.K // 16
+    if swizzled:
+        sf = torch.zeros(((nrows + 127) // 128 * 128) * ((groups + 3) // 4 * 4),
+                         dtype=torch.uint8, device=dev)
+    else:
+        sf = torch.empty((nrows, groups), dtype=torch.uint8, device=dev)
+    nw = w.native()
+    nat.check(lib.gb_expand_fp4_nvfp4(ctypes.byref(nw), row0, nrows, _ptr(packed), _ptr(sf),
+                                      1 if swizzled else 0, nat.stream_ptr(dev)), lib)
+    return packed, sf
+
+
+_ACT = {None: nat.ACT_NONE, "none": nat.ACT_NONE, "fp4": nat.ACT_FP4_GROUP16,
+        "fp8": nat.ACT_FP8_TOKEN}
+
+
+def gemv(x: torch.Tensor, w: PackedWeight, *, act: str | None = None, scale_rule: str = "recip",
+         out: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """y[..., N] = bucket(x)[..., K] . W^T for up to 16 activation rows."""
+    _need_cuda(x)
+    lib = nat.load("codebook decode GEMV")
+    if x.dtype is not torch.bfloat16:
+        raise TypeError("the decode GEMV takes bf16 activations")
+    x2 = x.reshape(-1, w.K).contiguous()
+    M = x2.shape[0]
+    if out is None:
+        out = torch.empty((M, w.rows), dtype=torch.bfloat16, device=x.device)
+    need = lib.gb_gemv_workspace_bytes(M, w.rows, w.K)
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    nw = w.native()
+    nat.check(lib.gb_gemv(_ptr(x2), M, ctypes.byref(nw), _ACT[act], _rule(scale_rule), _ptr(out),
+                          _ptr(workspace), workspace.numel(), nat.stream_ptr(x.device)), lib)
+    return out.reshape(*x.shape[:-1], w.rows)
+
+
+def moe_route(topk_ids: torch.Tensor, E: int):
+    """-> (counts [E], offsets [E+1], order [P]) int32, all on device, no host read."""
+    _need_cuda(topk_ids)
+    lib = nat.load("MoE routing")
+    ids = topk_ids.to(torch.int32).contiguous()
+    T, topk = ids.shape
+    dev = ids.device
+    counts = torch.empty(E, dtype=torch.int32, device=dev)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    order = torch.empty(max(T * topk, 1), dtype=torch.int32, device=dev)
+    nat.check(lib.gb_moe_route(_ptr(ids), T, topk, E, _ptr(counts), _ptr(offsets), _ptr(order),
+                               nat.stream_ptr(dev)), lib)
+    return counts, offsets, order[:T * topk]
+
+
+def moe_gemv(x: torch.Tensor, w: PackedWeight, offsets: torch.Tensor, order: torch.Tensor, *,
+             x_row: torch.Tensor | None = None, swiglu: bool = False,
+             out: torch.Tensor | None = None) -> torch.Tensor:
+    """Grouped GEMV over the routed pairs; y[p] for pair p (rows/2 wide with swiglu)."""
+    _need_cuda(x, offsets, order, x_row)
+    lib = nat.load("grouped codebook decode GEMV")
+    if x.dtype is not torch.bfloat16:
+        raise TypeError("the grouped decode GEMV takes bf16 activations")
+    x = x.contiguous()
+    P = order.numel()
+    width = w.rows // 2 if swiglu else w.rows
+    if out is None:
+        # pairs dropped by routing (padding sentinel) are never written: start from zero
+        out = torch.zeros((P, width), dtype=torch.bfloat16, device=x.device)
+    nw = w.native()
+    nat.check(lib.gb_moe_gemv(_ptr(x), _ptr(x_row), ctypes.byref(nw), w.expert_stride, w.experts,
+                              _ptr(offsets), _ptr(order), P, 1 if swiglu else 0, _ptr(out),
+                              _ZERO, 0, nat.stream_ptr(x.device)), lib)
+    return out
+
+
+def moe_combine(y: torch.Tensor, pair_w: torch.Tensor, T: int, topk: int) -> torch.Tensor:
+    _need_cuda(y, pair_w)
+    lib = nat.load("grouped CB router combine")
+    y = y.contiguous()
+    H = y.shape[-1]
+    out = torch.empty((T, H), dtype=torch.bfloat16, device=y.device)
+    pw = pair_w.to(torch.float32).contiguous()
+    nat.check(lib.gb_moe_combine(_ptr(y), _ptr(pw), T, topk, H, _ptr(out),
+                                 nat.stream_ptr(y.device)), lib)
+    return out

@@ -1,0 +1,146 @@
+/*
+ * gridbook_b200 -- C ABI of the sm_100a codebook-decode linear / routed-MoE kernels.
+ *
+ * One shared library (libgridbook_b200.so) replaces the reference's JIT-built
+ * pybind11 modules (gridbook/cuda_ext.py:344-354 `_EXT_SYMBOLS`, :446-451
+ * `_V2_SYMBOLS`, :1370-1377, :1087-1095, :2011-2033).  Conventions, all taken from the
+ * reference's bindings (gridbook/csrc/cb_gemv.cu:658-712):
+ *   - every pointer is a DEVICE pointer on the current device unless it says host;
+ *   - work is enqueued on the caller's stream, nothing synchronises, nothing allocates;
+ *   - outputs are caller-owned; scratch is passed in as `workspace`;
+ *   - the return value is 0 on success, otherwise a GB_E* code, and
+ *     gb_last_error() returns a thread-local description (the reference raises
+ *     RuntimeError from TORCH_CHECK);
+ *   - bf16 tensors are row-major and contiguous, index vectors are int32.
+ */
+#ifndef GRIDBOOK_B200_H_
+#define GRIDBOOK_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GB_ABI_VERSION 1
+#define GB_API __attribute__((visibility("default")))
+
+enum { GB_OK = 0, GB_EINVAL = 1, GB_ECUDA = 2, GB_EUNSUPPORTED = 3, GB_EWORKSPACE = 4 };
+
+enum { GB_GRID_FP4 = 0, GB_GRID_FP8 = 1 };
+/* index-encoding modes of docs/SPEC.md:94-128 */
+enum { GB_MODE_PRODUCT = 0, GB_MODE_SIGNED = 1, GB_MODE_FULL = 2 };
+/* docs/SPEC.md:130-177: none (fp8), v1 = 16 E4M3 bytes, v2 = super byte + 16 nibbles */
+enum { GB_SCALE_NONE = 0, GB_SCALE_V1 = 1, GB_SCALE_V2 = 2 };
+/* how `amax / c` is evaluated in the activation buckets: the fp32 reciprocal
+ * multiply of torch-on-CUDA that the reference kernels reproduce
+ * (gridbook/csrc/cb_gemv.cu:88-91,485-511), or a true division (torch-on-CPU) */
+enum { GB_SCALE_RULE_RECIP = 0, GB_SCALE_RULE_DIV = 1 };
+enum { GB_ACT_NONE = 0, GB_ACT_FP4_GROUP16 = 1, GB_ACT_FP8_TOKEN = 2 };
+
+/* One packed format (the `scheme` dict of gridbook/config.py:803-957). */
+typedef struct gb_format {
+  int32_t grid;         /* GB_GRID_*  */
+  int32_t mode;         /* GB_MODE_*  */
+  int32_t k_bits;       /* bits per 8-weight codeword */
+  int32_t n_sub;        /* product mode: sub-indices per codeword (2 or 4); else 1 */
+  int32_t type_size;    /* bytes per 256-weight superblock */
+  int32_t scale_coding; /* GB_SCALE_* */
+} gb_format;
+
+/* A packed weight matrix as the kernels see it.  Mirrors the tensors the
+ * reference's linear method keeps resident (gridbook/linear.py:374-680). */
+typedef struct gb_weight {
+  const uint8_t* qw;            /* [rows, row_stride] packed superblocks; readable up to
+                                   the next 16-byte boundary past the last row */
+  int64_t row_stride;           /* bytes between rows (>= K/256*type_size) */
+  const void* codebook;         /* flat codebook: bf16 (fp4 grid) or E4M3 bytes (fp8 grid),
+                                   gridbook/codec.py:146-167 */
+  const int32_t* cb_row_offset; /* [rows] element offset of each row's codebook block, or NULL = 0
+                                   (gridbook/linear.py:419-459) */
+  const float* compose;         /* [256*16] two-tier table, v2 only (gridbook/codec.py:170-183) */
+  const float* weight_scale;    /* [rows] fp8 grid per-row scale, else NULL */
+  float global_scale;           /* epilogue multiplier (1.0f = none); no reference counterpart */
+  int64_t rows;                 /* N */
+  int64_t K;
+  gb_format fmt;
+} gb_weight;
+
+GB_API int gb_abi_version(void);
+GB_API const char* gb_last_error(void);
+
+/* Per-device one-time set-up (function attributes, SM count).  Call at model load,
+ * before any stream capture; replaces the `*_prepare` entries of
+ * gridbook/csrc/cb_gemv_v2.cu:495-548. */
+GB_API int gb_prepare(int device);
+
+/* Device error word written by kernels whose bounded waits ran out; 0 when healthy. */
+GB_API int gb_device_status(int device, int* status_out);
+
+/* ---- activation buckets ---------------------------------------------------- */
+/* replaces fp8_act_qdq (gridbook/csrc/cb_gemv.cu:135-172, gridbook/ops.py:441-447) */
+GB_API int gb_fp8_act_qdq(const void* x_bf16, void* out_bf16, int64_t M, int64_t K,
+                   int scale_rule, void* stream);
+/* replaces fp4_act_qdq (gridbook/csrc/cb_gemv.cu:532-570, gridbook/ops.py:454-460) */
+GB_API int gb_fp4_act_qdq(const void* x_bf16, void* out_bf16, int64_t M, int64_t K,
+                   int scale_rule, void* stream);
+
+/* ---- decoded tiles (bit-exact gates) ---------------------------------------- */
+/* replaces cb_expand_fp8 (gridbook/csrc/cb_gemv.cu:2168-2280, gridbook/ops.py:96-116):
+ * rows [row0, row0+nrows) -> [nrows, K] E4M3 bytes */
+GB_API int gb_expand_fp8(const gb_weight* w, int64_t row0, int64_t nrows, void* out_e4m3,
+                  void* stream);
+/* replaces cb_expand_v2 (gridbook/csrc/cb_gemv_v2.cu:374-439,802-863, gridbook/ops.py:119-134)
+ * for every fp4 mode and scale coding: -> [nrows, K] bf16 = bf16(value * group scale) */
+GB_API int gb_expand_fp4_bf16(const gb_weight* w, int64_t row0, int64_t nrows, void* out_bf16,
+                       void* stream);
+/* native NVFP4 tile (docs/SPEC.md:30-39; the operand of the reference's block-scaled
+ * GEMM, gridbook/csrc/cb_fused_fp4_gemm.cu:25-60): packed E2M1 [nrows, K/2] (even element
+ * in the low nibble) and E4M3 group scales, either row-major [nrows, K/16]
+ * (sf_swizzled = 0) or in the 128x4 atom layout of gridbook/codec.py:353-374
+ * (sf_swizzled = 1, plane padded to 128 rows x 4 groups, caller zero-fills). */
+GB_API int gb_expand_fp4_nvfp4(const gb_weight* w, int64_t row0, int64_t nrows, void* out_packed,
+                        void* out_sf, int sf_swizzled, void* stream);
+
+/* ---- decode-batch linear (M <= 16) ------------------------------------------ */
+/* replaces cb_gemv_fp8 / cb_gemv_fp4_v2 (gridbook/csrc/cb_gemv.cu:658-712,1138-1198;
+ * gridbook/ops.py:52-93).  y[M,N] = bucket(x)[M,K] . W^T, fp32 accumulate, one bf16
+ * rounding.  `act` selects a fused activation bucket applied to x first (GB_ACT_NONE
+ * when x is already bucketed).  workspace: gb_gemv_workspace_bytes() bytes. */
+GB_API int64_t gb_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K);
+GB_API int gb_gemv(const void* x_bf16, int64_t M, const gb_weight* w, int act, int scale_rule,
+            void* y_bf16, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* ---- routed MoE -------------------------------------------------------------- */
+/* Device-side histogram + exclusive scan + stable expert-major permutation of the
+ * P = T*topk routed pairs; replaces the torch chain of gridbook/moe.py:1609-1625 and
+ * gridbook/moe_routing.py:99-207.  ids < 0 (vLLM's padding sentinel,
+ * gridbook/ops.py:764-784) are dropped from every expert.
+ *   counts [E], offsets [E+1] (exclusive scan, offsets[E] = routed pairs kept),
+ *   order [P]: sorted position -> flat pair index t*topk+slot (token-ascending per expert). */
+GB_API int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E,
+                 int32_t* counts, int32_t* offsets, int32_t* order, void* stream);
+
+/* Grouped GEMV over routed pairs; replaces cb_moe_gemv_fp8 / cb_moe_gemv_fp4_v2 /
+ * cb_moe_gemv_v2 (gridbook/csrc/cb_gemv.cu:1210-1681,1873-2138; gridbook/csrc/cb_gemv_v2.cu:233-366).
+ * `w` describes ONE expert's matrix; expert e starts at qw + e*expert_stride bytes and
+ * weight_scale + e*rows.  Pairs come grouped by expert through (offsets, order); pair p
+ * reads activation row x_row[p] (NULL = p) and writes y[p].  When `swiglu` is set the
+ * kernel's output is silu(gate)*up of rows [0,rows/2) and [rows/2,rows) -> y[P, rows/2]
+ * (replaces native_moe_activation, gridbook/native_cutlass.py:129-155). */
+GB_API int64_t gb_moe_gemv_workspace_bytes(int64_t P, int64_t rows);
+GB_API int gb_moe_gemv(const void* x_bf16, const int32_t* x_row, const gb_weight* w,
+                int64_t expert_stride, int64_t E, const int32_t* offsets,
+                const int32_t* order, int64_t P, int swiglu, void* y_bf16,
+                void* workspace, int64_t workspace_bytes, void* stream);
+
+/* out[t] = sum over the token's topk pairs of w[p] * y[p], fp32 accumulate, one bf16
+ * rounding; replaces cb_moe_combine (gridbook/csrc/cb_gemv.cu:1853-1871,2140-2158).
+ * pair p = t*topk + slot. */
+GB_API int gb_moe_combine(const void* y_bf16, const float* pair_w, int64_t T, int64_t topk,
+                   int64_t H, void* out_bf16, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRIDBOOK_B200_H_ */

@@ -1,0 +1,159 @@
+"""GPU parity, part 2: the decode-batch linear and the routed MoE path against the
+oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import cb_oracle as O
+from tests.helpers import assert_close_bf16, f32_of, oracle_linear
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from gridbook_b200 import _native
+    _native.prepare(0)
+    return torch.device("cuda:0")
+
+
+def _fmt(name):
+    from gridbook_b200.formats import CBFormat
+    return {
+        "lit": CBFormat("fp4", 8, mode="full", scale_coding="v1"),
+        "k16v2": CBFormat("fp4", 16, n_sub=2, scale_coding="v2"),
+        "k13v2": CBFormat("fp4", 13, n_sub=2, scale_coding="v2"),
+        "k20v1": CBFormat("fp4", 20, n_sub=2, scale_coding="v1"),
+        "s13": CBFormat("fp4", 13, mode="signed", scale_coding="v2"),
+        "f8k32": CBFormat("fp8", 32, n_sub=4),
+        "f8k30": CBFormat("fp8", 30, n_sub=4),
+        "f8k44": CBFormat("fp8", 44, n_sub=4),
+        "f8lit": CBFormat("fp8", 16, n_sub=2),
+    }[name]
+
+
+@pytest.mark.parametrize("name", ["lit", "k16v2", "k13v2", "k20v1", "s13", "f8k32", "f8k30", "f8k44", "f8lit"])
+@pytest.mark.parametrize("M", [1, 2, 4, 8, 16])
+def test_gemv_matches_oracle(dev, name, M):
+    from gridbook_b200 import kernels, synth
+    fmt = _fmt(name)
+    N, K = 203, 1024                     # ragged last tile
+    d = synth.make_linear(fmt, N, K, seed=5, global_scale=(1.0 / 448.0 if name == "lit" else None))
+    w = synth.to_device_weight(d, dev)
+    x = synth.make_activations(M, K, seed=M)
+    xq = O.act_bucket(x, fmt.grid, "recip")
+    y = kernels.gemv(synth.bf16_tensor(xq, dev), w)
+    assert_close_bf16(f32_of(y), oracle_linear(xq, d, bucket=False), f"{name} M={M}")
+    # fused activation bucket
+    y2 = kernels.gemv(synth.bf16_tensor(x, dev), w, act=fmt.grid)
+    assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("name", ["lit", "k16v2", "f8k32"])
+def test_gemv_padded_rows_and_role_codebooks(dev, name):
+    """Row stride wider than the packed row (the reference pads 16 bytes,
+    gridbook/codec.py:200-229) and per-row codebook offsets whose boundary cuts a tile."""
+    from gridbook_b200 import kernels, synth
+    fmt = _fmt(name)
+    N, K = 100, 512
+    d = synth.make_linear(fmt, N, K, seed=9, n_books=3)       # boundaries at rows 34 and 68
+    w = synth.to_device_weight(d, dev, pad_rows=True)
+    assert w.row_stride == fmt.row_bytes(K) + 16
+    x = synth.make_activations(3, K, seed=2)
+    xq = O.act_bucket(x, fmt.grid, "recip")
+    y = kernels.gemv(synth.bf16_tensor(xq, dev), w)
+    assert_close_bf16(f32_of(y), oracle_linear(xq, d, bucket=False), name)
+
+
+@pytest.mark.parametrize("name,M,K", [("lit", 16, 8192), ("k16v2", 16, 6144), ("f8k32", 9, 7168)])
+def test_gemv_k_sliced(dev, name, M, K):
+    """Activation rows too large for one shared-memory slice: K-sliced launch with fp32
+    partial sums in the workspace."""
+    from gridbook_b200 import kernels, synth
+    fmt = _fmt(name)
+    N = 264
+    d = synth.make_linear(fmt, N, K, seed=11)
+    w = synth.to_device_weight(d, dev)
+    x = synth.make_activations(M, K, seed=4)
+    xq = O.act_bucket(x, fmt.grid, "recip")
+    y = kernels.gemv(synth.bf16_tensor(xq, dev), w)
+    assert_close_bf16(f32_of(y), oracle_linear(xq, d, bucket=False), f"{name} sliced")
+
+
+def test_gemv_reference_fixture_k16(dev, golden):
+    """y of the reference's own cb_linear_reference on its fixture bytes."""
+    from gridbook_b200 import kernels
+    from gridbook_b200.formats import CBFormat
+    p = "fp4v2_k16_"
+    qw = torch.zeros(6 * golden[p + "qw"].shape[1] + 16, dtype=torch.uint8, device=dev)
+    qw[:-16] = torch.from_numpy(golden[p + "qw"]).reshape(-1).to(dev)
+    w = kernels.make_weight(qw[:-16].view(6, -1),
+                            torch.from_numpy(golden[p + "cb"].view(np.int16)).view(torch.bfloat16).to(dev),
+                            CBFormat("fp4", 16, n_sub=2, scale_coding="v2"), 512,
+                            cb_row_offset=torch.from_numpy(golden[p + "off"]).to(dev),
+                            compose=torch.from_numpy(golden["compose"]).to(dev))
+    xq = torch.from_numpy(golden[p + "xq"].view(np.int16)).view(torch.bfloat16).to(dev)
+    y = kernels.gemv(xq, w)
+    assert_close_bf16(f32_of(y), O.bf16_bits_to_f32(golden[p + "y"]), "reference fixture")
+
+
+def test_gemv_shape_errors(dev):
+    from gridbook_b200 import kernels, synth
+    d = synth.make_linear(_fmt("lit"), 16, 256, seed=1)
+    w = synth.to_device_weight(d, dev)
+    with pytest.raises(RuntimeError, match="1..16 rows"):
+        kernels.gemv(torch.zeros(17, 256, dtype=torch.bfloat16, device=dev), w)
+
+
+# ---- routed MoE -----------------------------------------------------------------
+def test_route_matches_oracle(dev):
+    from gridbook_b200 import kernels, synth
+    for T, E, topk in ((1, 128, 8), (16, 128, 8), (256, 128, 8), (37, 9, 3)):
+        ids, _ = synth.make_routing(T, E, topk, seed=T)
+        ids[0, 0] = -1 if T == 37 else ids[0, 0]            # padding sentinel is dropped
+        counts, offsets, order = kernels.moe_route(torch.from_numpy(ids).to(dev), E)
+        keep = ids.reshape(-1) >= 0
+        rc, ro, rorder = O.route_by_expert(np.where(keep, ids.reshape(-1), E).reshape(ids.shape), E + 1)
+        assert np.array_equal(counts.cpu().numpy(), rc[:E])
+        assert np.array_equal(offsets.cpu().numpy(), ro[:E + 1])
+        n = int(ro[E])
+        assert np.array_equal(order.cpu().numpy()[:n], rorder[:n])
+
+
+def _moe_case(dev, fmt13, fmt2, E, hidden, inter, T, topk, seed):
+    from gridbook_b200 import kernels, synth
+    w13d, w2d = synth.make_moe(fmt13, fmt2, E, hidden, inter, seed=seed)
+    ids, tw = synth.make_routing(T, E, topk, seed=seed)
+    x = synth.make_activations(T, hidden, seed=seed)
+    f13 = fmt13.oracle_kwargs()
+    f2 = fmt2.oracle_kwargs()
+    ref = O.moe_loop_chain(x, ids, tw, w13d, w2d, E=E, hidden=hidden, inter=inter, fmt13=f13, fmt2=f2,
+                           scale_rule="recip")
+    w13 = synth.to_device_weight(w13d, dev)
+    w2 = synth.to_device_weight(w2d, dev)
+    xd = synth.bf16_tensor(x, dev)
+    idd = torch.from_numpy(ids).to(dev)
+    _, offsets, order = kernels.moe_route(idd, E)
+    xq = (kernels.fp4_act_qdq if fmt13.is_fp4 else kernels.fp8_act_qdq)(xd)
+    x_row = (torch.arange(T * topk, device=dev, dtype=torch.int32) // topk).contiguous()
+    a = kernels.moe_gemv(xq, w13, offsets, order, x_row=x_row, swiglu=True)
+    aq = (kernels.fp4_act_qdq if fmt2.is_fp4 else kernels.fp8_act_qdq)(a)
+    yd = kernels.moe_gemv(aq, w2, offsets, order)
+    pw = torch.from_numpy(tw).to(dev).to(torch.bfloat16).float().reshape(-1)
+    out = kernels.moe_combine(yd, pw, T, topk)
+    return f32_of(out), ref
+
+
+@pytest.mark.parametrize("T", [1, 5, 16, 40])
+def test_moe_fp4_k16_matches_loop_chain(dev, T):
+    fmt = _fmt("k16v2")
+    got, ref = _moe_case(dev, fmt, fmt, E=16, hidden=512, inter=256, T=T, topk=4, seed=T)
+    rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+    assert rel <= 1e-2 and np.abs(got - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max()), rel
+
+
+def test_moe_literal_and_fp8_and_mixed(dev):
+    for f13, f2 in (("lit", "lit"), ("f8k32", "f8k32"), ("f8lit", "lit")):
+        got, ref = _moe_case(dev, _fmt(f13), _fmt(f2), E=8, hidden=512, inter=256, T=6, topk=2, seed=3)
+        rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+        assert rel <= 1e-2, (f13, f2, rel)
