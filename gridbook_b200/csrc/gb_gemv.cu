@@ -288,20 +288,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
     bool restage_x;
     if constexpr (kMoE) restage_x = (t.expert != x_expert) || (t.m0 != x_m0);
     else restage_x = (t.slice != cur_slice);
-    // ---- codebook block of this tile's rows ----
-    const int rows_here = p.swiglu ? 2 * t.nrows : t.nrows;
-    int64_t off_lo = 0;
+    // ---- this lane's row, and the codebook block(s) of the tile's rows ----
+    const bool second_half = p.swiglu && g >= kTileRows / 2;
+    const int g_local = p.swiglu ? (g & 3) : g;
+    const bool row_ok = g_local < t.nrows;
+    const int64_t out_row = (int64_t)t.row0 + g_local + (second_half ? p.N / 2 : 0);
+    int64_t off_lo = 0, my_cb_off = 0;
     bool uniform = true;
     if (p.cb_row_offset) {
-      const int64_t first = t.row0, last = t.row0 + t.nrows - 1;
-      off_lo = p.cb_row_offset[first];
-      uniform = p.cb_row_offset[last] == off_lo;
-      if (p.swiglu) {
-        uniform = uniform && p.cb_row_offset[first + p.N / 2] == off_lo &&
-                  p.cb_row_offset[last + p.N / 2] == off_lo;
-      }
+      off_lo = p.cb_row_offset[t.row0];
+      if (row_ok) my_cb_off = p.cb_row_offset[out_row];
+      uniform = __all_sync(0xffffffffu, !row_ok || my_cb_off == off_lo);   // same verdict in every warp
     }
-    (void)rows_here;
     const bool restage_lut = uniform && (off_lo != lut_off);
     if (restage_x || restage_lut) {
       named_barrier_consumers();     // everyone is done with the previous contents
@@ -346,14 +344,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
     }
     const uint8_t* sbase = stages + (size_t)s * p.stage_bytes;
 
-    // ---- this lane's row ----
-    const bool second_half = p.swiglu && g >= kTileRows / 2;
-    const int g_local = p.swiglu ? (g & 3) : g;
-    const bool row_ok = g_local < t.nrows;
-    const int64_t out_row = (int64_t)t.row0 + g_local + (second_half ? p.N / 2 : 0);
     const uint8_t* rowp = sbase + sp.row_off[row_ok ? g : 0];
-    int64_t my_cb_off = 0;
-    if (!uniform && row_ok) my_cb_off = p.cb_row_offset[out_row];
+    // fp8 grid: the served weight is bf16(value * row scale), rounded per weight
+    float row_scale = 1.0f;
+    if constexpr (fp8) {
+      if (row_ok) row_scale = p.weight_scale[(int64_t)t.expert * p.N + out_row];
+    }
 
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const bool hi_rows = p.x_rows > 8;
@@ -397,7 +393,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
           for (int j = 0; j < 4; ++j)
             w[j] = (__float_as_uint(v[2 * j]) >> 16) | (__float_as_uint(v[2 * j + 1]) & 0xFFFF0000u);
         }
-        if constexpr (!fp8) {
+        if constexpr (fp8) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float lo = __uint_as_float(w[j] << 16) * row_scale;
+            const float hi = __uint_as_float(w[j] & 0xFFFF0000u) * row_scale;
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[j]) : "f"(hi), "f"(lo));
+          }
+        } else {
           // group scale (exact E4M3 value) as a bf16 pair
           const uint8_t* plane = sbp + 4 * p.fmt.k_bits;
           float sc;
@@ -446,11 +449,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
           for (int w8 = 0; w8 < kConsumerWarps; ++w8) other += red[w8 * 128 + (ctid ^ 4)];
           if (n < 4 && n < t.nrows) {
             const int64_t grow = (int64_t)t.row0 + n, urow = grow + p.N / 2;
-            float gs = p.global_scale, us = p.global_scale;
-            if constexpr (fp8) {
-              const float* wsc = p.weight_scale + (int64_t)t.expert * p.N;
-              gs *= wsc[grow]; us *= wsc[urow];
-            }
+            const float gs = p.global_scale, us = p.global_scale;
+            (void)urow;
             const float gate = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(v * gs));
             const float up = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(other * us));
             const float sl = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(gate / (1.0f + __expf(-gate))));
@@ -462,8 +462,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
           if (p.ksplit > 1) {
             atomicAdd(p.ws + (int64_t)m * p.N + row, v);
           } else {
-            float sc = p.global_scale;
-            if constexpr (fp8) sc *= p.weight_scale[(int64_t)t.expert * p.N + row];
+            const float sc = p.global_scale;
             int64_t orow = m;
             if constexpr (kMoE) orow = p.order[t.m0 + m];
             p.y[orow * p.N + row] = (uint16_t)gb_f32_to_bf16_bits(v * sc);
@@ -640,7 +639,7 @@ int gb_gemv(const void* x, int64_t M, const gb_weight* w, int act, int scale_rul
   if (p.ksplit > 1) {
     const int64_t total = M * w->rows;
     gemv_finalize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-        p.ws, w->fmt.grid == GB_GRID_FP8 ? w->weight_scale : nullptr, p.global_scale, p.y, M, w->rows);
+        p.ws, nullptr, p.global_scale, p.y, M, w->rows);
     GB_LAUNCH_OK("gemv_finalize_kernel");
   }
   return GB_OK;

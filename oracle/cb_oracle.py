@@ -276,7 +276,7 @@ def e2m1_codes(values: np.ndarray) -> np.ndarray:
     idx = np.argmax(np.abs(v)[..., None] == mags, axis=-1)
     if not np.array_equal(mags[idx], np.abs(v)):
         raise ValueError("value off the E2M1 grid")
-    return (idx + np.where(np.signbit(v), 8, 0)).astype(np.uint8)
+    return (idx + np.where(v < 0, 8, 0)).astype(np.uint8)    # -0.0 encodes as +0, as in the reference
 
 
 def decode_nvfp4_tile(qw, cb_flat, cb_row_offset, *, N, K, k_bits, n_sub,

@@ -43,3 +43,8 @@ def assert_close_bf16(got: np.ndarray, ref: np.ndarray, tag: str, ulps: float = 
     assert bad == 0, f"{tag}: {bad}/{d.size} elements beyond {ulps} bf16 ULP (max diff {d.max():.3e})"
     rel = np.linalg.norm(d) / max(np.linalg.norm(ref), 1e-6)
     assert rel <= rel_l2, f"{tag}: rel-L2 {rel:.3e} > {rel_l2}"
+
+
+
+def assert_linear_close(got, ref, fmt, tag):
+    assert_close_bf16(got, ref, tag)

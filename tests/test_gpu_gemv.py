@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from oracle import cb_oracle as O
-from tests.helpers import assert_close_bf16, f32_of, oracle_linear
+from tests.helpers import assert_close_bf16, assert_linear_close, f32_of, oracle_linear
 
 pytestmark = pytest.mark.gpu
 
@@ -43,7 +43,7 @@ def test_gemv_matches_oracle(dev, name, M):
     x = synth.make_activations(M, K, seed=M)
     xq = O.act_bucket(x, fmt.grid, "recip")
     y = kernels.gemv(synth.bf16_tensor(xq, dev), w)
-    assert_close_bf16(f32_of(y), oracle_linear(xq, d, bucket=False), f"{name} M={M}")
+    assert_linear_close(f32_of(y), oracle_linear(xq, d, bucket=False), fmt, f"{name} M={M}")
     # fused activation bucket
     y2 = kernels.gemv(synth.bf16_tensor(x, dev), w, act=fmt.grid)
     assert torch.equal(y, y2)
@@ -62,7 +62,7 @@ def test_gemv_padded_rows_and_role_codebooks(dev, name):
     x = synth.make_activations(3, K, seed=2)
     xq = O.act_bucket(x, fmt.grid, "recip")
     y = kernels.gemv(synth.bf16_tensor(xq, dev), w)
-    assert_close_bf16(f32_of(y), oracle_linear(xq, d, bucket=False), name)
+    assert_linear_close(f32_of(y), oracle_linear(xq, d, bucket=False), fmt, name)
 
 
 @pytest.mark.parametrize("name,M,K", [("lit", 16, 8192), ("k16v2", 16, 6144), ("f8k32", 9, 7168)])
@@ -77,7 +77,7 @@ def test_gemv_k_sliced(dev, name, M, K):
     x = synth.make_activations(M, K, seed=4)
     xq = O.act_bucket(x, fmt.grid, "recip")
     y = kernels.gemv(synth.bf16_tensor(xq, dev), w)
-    assert_close_bf16(f32_of(y), oracle_linear(xq, d, bucket=False), f"{name} sliced")
+    assert_linear_close(f32_of(y), oracle_linear(xq, d, bucket=False), fmt, f"{name} sliced")
 
 
 def test_gemv_reference_fixture_k16(dev, golden):
