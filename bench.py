@@ -1,0 +1,414 @@
+#!/usr/bin/env python
+"""Benchmark of the codebook-decode linear hot path.
+
+One step = one pass over the dense decode stack of the benchmark configuration: 64
+layers of hidden 5120, each with q (6144x5120), fused kv (2048x5120), o (5120x6144),
+fused gate_up (34816x5120) and down (5120x17408) codebook linears, at M activation rows.
+The metric is the packed weight-stream bandwidth, bytes = sum N*(K/256)*type_size.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--m M] [--format literal|k16v2|fp8k32]
+    python bench.py --impl reference ...      # the CPU restatement on the host cores
+
+Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HIDDEN = 5120
+# name, out partition sizes (roles), K
+PROJECTIONS = (
+    ("q_proj", (6144,), 5120),
+    ("kv_proj", (1024, 1024), 5120),
+    ("o_proj", (5120,), 6144),
+    ("gate_up_proj", (17408, 17408), 5120),
+    ("down_proj", (5120,), 17408),
+)
+
+
+def get_format(name):
+    from gridbook_b200 import formats
+    return {"literal": (formats.NVFP4_LITERAL, 1.0 / 448.0), "k16v2": (formats.NVFP4_CB_K16, 1.0),
+            "fp8k32": (formats.FP8_CB_K32, 1.0), "fp8lit": (formats.FP8_LITERAL, 1.0)}[name]
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            return json.load(fh), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0.0, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def build_stack(fmt, gscale, layers, device, rank, world, seed=0):
+    """Random-init codebook stack; with world > 1 every projection keeps whole-role row
+    ranges [r*n/world, (r+1)*n/world) of each role (column-parallel sharding)."""
+    import torch
+    from gridbook_b200 import synth
+    from gridbook_b200.linear import CBLinear
+    stack = []
+    for li in range(layers):
+        row = []
+        for pi, (name, parts, K) in enumerate(PROJECTIONS):
+            local = [p // world for p in parts]
+            gen = torch.Generator(device=device).manual_seed(seed + 1000 * li + 10 * pi + rank)
+            tabs = synth.codebook_tables(fmt, seed + li)          # one codebook per layer
+            lin = CBLinear(fmt, K, local, [tabs], global_scale=gscale, prefix=f"layers.{li}.{name}")
+            qw = synth.make_packed_device(fmt, sum(local), K, gen, device)
+            ws = None
+            if not fmt.is_fp4:
+                ws = (torch.rand(sum(local), generator=gen, device=device) + 0.5) * 0.02
+            row.append(lin.load(qw, ws, device))
+        stack.append(row)
+    return stack
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from gridbook_b200 import _native, kernels
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path for the kernels")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    _native.prepare(local_rank)
+
+    fmt, gscale = get_format(args.format)
+    M = args.m
+    stack = build_stack(fmt, gscale, args.layers, device, rank, world)
+    gen = torch.Generator(device=device).manual_seed(1234)
+    inputs_dev = [torch.randn(M, K, generator=gen, device=device).to(torch.bfloat16) for _, _, K in PROJECTIONS]
+    inputs_host = [t.cpu().pin_memory() for t in inputs_dev]
+    n_local = [sum(p // world for p in parts) for _, parts, _ in PROJECTIONS]
+    bytes_per_step_local = sum(lin._cb_weight.packed_bytes for row in stack for lin in row)
+    gathered = [torch.empty(world * M, n, dtype=torch.bfloat16, device=device) for n in n_local]
+    launches_per_linear = 2          # activation bucket + decode GEMV
+    extra = 0
+    for row in stack[:1]:
+        for lin in row:
+            pass
+    outs_host = [torch.empty(M, n * world, dtype=torch.bfloat16).pin_memory() for n in n_local]
+
+    def step():
+        ys = None
+        for row in stack:
+            ys = []
+            for lin, x, g in zip(row, inputs_dev, gathered):
+                y = lin(x)
+                if world > 1:
+                    dist.all_gather_into_tensor(g, y)     # [world*M, n_local], rank-major
+                    y = g
+                ys.append(y)
+        return ys
+
+    # warm-up eagerly (also settles allocator and NCCL), then capture one step
+    for _ in range(2):
+        last = step()
+    torch.cuda.synchronize()
+    graph = None
+    if not args.no_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                last = step()
+        except Exception as exc:            # capture is an optimisation, not a requirement
+            if rank == 0:
+                print(f"[bench] CUDA graph capture failed ({type(exc).__name__}: {exc}); running eagerly",
+                      file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            step()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        run_step()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        ev0.record()
+        for _ in range(args.steps):
+            run_step()
+        ev1.record()
+        barrier()
+    ms_total = ev0.elapsed_time(ev1)
+
+    # ---- end to end: host buffers in, host buffers out, copies inside the timed region ----
+    def e2e_step():
+        for d, h in zip(inputs_dev, inputs_host):
+            d.copy_(h, non_blocking=True)
+        run_step()
+        for h, y in zip(outs_host, last):
+            src = y if world == 1 else y.view(world, M, -1).permute(1, 0, 2).reshape(M, -1)
+            h.copy_(src, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+
+    # ---- dominant kernel alone: decode GEMV launches only, activations already bucketed ----
+    xq = [(kernels.fp4_act_qdq if fmt.is_fp4 else kernels.fp8_act_qdq)(x) for x in inputs_dev]
+    outs = [[torch.empty(M, n, dtype=torch.bfloat16, device=device) for n in n_local] for _ in range(1)]
+
+    def kernel_step():
+        for row in stack:
+            for lin, x, o in zip(row, xq, outs[0]):
+                kernels.gemv(x, lin._cb_weight, out=o, workspace=lin._cb_workspace)
+
+    kernel_step()
+    torch.cuda.synchronize()
+    kgraph = None
+    try:
+        kgraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(kgraph):
+            kernel_step()
+    except Exception:
+        kgraph = None
+        torch.cuda.synchronize()
+    for _ in range(3):
+        kgraph.replay() if kgraph else kernel_step()
+    barrier()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for _ in range(args.steps):
+        kgraph.replay() if kgraph else kernel_step()
+    k1.record()
+    barrier()
+    ms_kernel = k0.elapsed_time(k1)
+    status = _native.device_status(local_rank)
+
+    times = torch.tensor([ms_total, ms_e2e, ms_kernel, float(bytes_per_step_local)], dtype=torch.float64,
+                         device=device)
+    if world > 1:
+        tmax = times.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = times.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        ms_total, ms_e2e, ms_kernel = (float(v) for v in tmax[:3])
+        total_bytes = float(tsum[3])
+    else:
+        total_bytes = float(bytes_per_step_local)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peaks, peak_kind = measured_peaks()
+    n_linear = args.layers * len(PROJECTIONS)
+    gbs = total_bytes * args.steps / (ms_total * 1e-3) / 1e9
+    gbs_e2e = total_bytes * args.steps / (ms_e2e * 1e-3) / 1e9
+    # per-GPU figure of the dominant kernel: bytes one launch streams / its average duration
+    launch_bytes = bytes_per_step_local / n_linear
+    launch_ms = ms_kernel / args.steps / n_linear
+    achieved = launch_bytes / (launch_ms * 1e-3) / 1e9
+    line = {
+        "metric": "CB GEMV weight GB/s (% HBM peak); grouped-MoE decode tok/s at 1/2/4/8 B200",
+        "value": round(gbs, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_total / args.steps, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x E2M1/E4M3 codebook, fp32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": f"dense decode stack: {args.layers} layers x (q 6144x5120, kv 2048x5120, "
+                               f"o 5120x6144, gate_up 34816x5120, down 5120x17408), M={M}",
+                   "format": f"{args.format}: {fmt.grid} grid, {fmt.mode} k={fmt.k}, type_size {fmt.type_size}",
+                   "weight_bytes_per_step": int(total_bytes), "parallelism": f"N-sharded x{world}" if world > 1 else "1 GPU",
+                   "l2": "inputs larger than L2: every step streams all distinct layer weights",
+                   "cuda_graph": graph is not None},
+        "pct_hbm_peak": round(100.0 * gbs / (peaks["hbm_gbs"] * world), 2),
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None, "peak_kind": peak_kind,
+                     "kernel": "gemv_kernel", "avg_launch_us": round(launch_ms * 1e3, 3),
+                     "bytes_per_launch": int(launch_bytes)},
+        "e2e": {"value": round(gbs_e2e, 2), "unit": "GB/s",
+                "h2d_bytes_per_step": int(sum(t.numel() * 2 for t in inputs_host)),
+                "d2h_bytes_per_step": int(sum(t.numel() * 2 for t in outs_host))},
+        "gpu_launches": int(args.steps * n_linear * launches_per_linear + extra),
+        "clocks": clocks.summary(),
+        "device_status": status,
+    }
+    if world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(args.format, M, seconds=20.0)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_layer_inputs(fmt, gscale, M, seed=0):
+    """One layer (5 projections) of host-side synthetic weights for the CPU checker."""
+    from gridbook_b200 import synth
+    layer = []
+    for pi, (name, parts, K) in enumerate(PROJECTIONS):
+        d = synth.make_linear(fmt, sum(parts), K, seed=seed + pi, global_scale=gscale)
+        layer.append((d, synth.make_activations(M, K, seed=pi)))
+    return layer
+
+
+def cpu_pass(layer):
+    from oracle import c_oracle as C
+    nbytes = 0
+    for d, x in layer:
+        fmt = d["fmt"]
+        xq = C.act_qdq(x, fmt.grid, "recip")
+        C.linear(xq, d["qw"], d["cb"], None, N=d["N"], K=d["K"], compose=d["compose"],
+                 weight_scale=d["weight_scale"], global_scale=d["global_scale"], **fmt.oracle_kwargs())
+        nbytes += d["N"] * fmt.row_bytes(d["K"])
+    return nbytes
+
+
+def cpu_baseline(fmt_name, M, seconds=20.0):
+    """The CPU restatement of the reference path (C + OpenMP, every host core) on a bounded
+    sample: whole layers of the same workload until about `seconds` have been spent."""
+    from oracle import c_oracle as C
+    fmt, gscale = get_format(fmt_name)
+    layer = cpu_layer_inputs(fmt, gscale, M)
+    cpu_pass(layer)                                   # warm-up
+    t0 = time.perf_counter()
+    n, nbytes = 0, 0
+    while n < 1 or (time.perf_counter() - t0 < seconds and n < 64):
+        nbytes += cpu_pass(layer)
+        n += 1
+    dt = time.perf_counter() - t0
+    return {"value": round(nbytes / dt / 1e9, 4), "unit": "GB/s", "cores": C.num_threads(), "kind": "port",
+            "sample": f"{n} pass(es) over one layer (5 projections, {nbytes // n} packed bytes) of the same "
+                      f"stack at M={M}, {dt:.1f} s"}
+
+
+def run_reference(args):
+    """Reference arm: the reference's path is Python/torch and cannot travel, so its CPU
+    restatement (oracle/cb_oracle.c, validated against reference-generated fixtures) is
+    timed with every host thread.  One step = one layer of the stack."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import c_oracle as C
+    fmt, gscale = get_format(args.format)
+    layer = cpu_layer_inputs(fmt, gscale, args.m)
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_pass(layer)
+    t0 = time.perf_counter()
+    nbytes = 0
+    for _ in range(args.steps):
+        nbytes += cpu_pass(layer)
+    dt = time.perf_counter() - t0
+    gbs = nbytes / dt / 1e9
+    sample = (f"each step = one layer (5 projections, {nbytes // args.steps} packed bytes) of the "
+              f"{args.layers}-layer stack, M={args.m}")
+    print(json.dumps({
+        "impl": "reference",
+        "metric": "CB GEMV weight GB/s (% HBM peak); grouped-MoE decode tok/s at 1/2/4/8 B200",
+        "value": round(gbs, 4), "unit": "GB/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 3),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 weights, fp32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": f"dense decode stack layer shapes, M={args.m}", "format": args.format,
+                   "sample": sample},
+        "cpu_baseline": {"value": round(gbs, 4), "unit": "GB/s", "cores": C.num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(gbs, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--format", default="literal", choices=["literal", "k16v2", "fp8k32", "fp8lit"])
+    ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,85 @@
+"""Load-time format preparation, host side (mirrors gridbook/codec.py): flat codebooks,
+the two-tier compose table, row padding and grid validation.  Runs once per layer at
+model load; nothing here is on the forward path and nothing here is a dense weight."""
+from __future__ import annotations
+
+import torch
+
+SUPERBLOCK = 256
+FP4_GROUP = 16
+PAD_BYTES = 16
+SCALE_CODING_TWO_TIER = "two_tier"
+TWO_TIER_SUPER_BIAS = 127
+TWO_TIER_SUB_TABLE = (1.0, 1.125, 1.25, 1.375, 1.5, 1.625, 1.75, 1.875,
+                      2.0, 2.25, 2.5, 2.75, 3.0, 3.25, 3.5, 3.75)
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def type_size(k: int, is_fp4: bool, two_tier: bool = False) -> int:
+    """Bytes per superblock (gridbook/codec.py:40-41, docs/SPEC.md:195-214)."""
+    return 4 * int(k) + ((9 if two_tier else 16) if is_fp4 else 0)
+
+
+def validate_codebook_grid(raw: torch.Tensor, grid: str, prefix: str = "codebook") -> None:
+    """Reject tables that are not exactly on their declared grid
+    (gridbook/codec.py:106-143): a lossy cast must be an error, never a rounding."""
+    v = raw.reshape(-1).to(torch.float64)
+    if not bool(torch.isfinite(v).all()):
+        raise ValueError(f"[prismaquant] {prefix}: non-finite codebook values; {grid} codebooks "
+                         "must be finite and grid-valued")
+    if grid == "fp8":
+        ok = v == v.to(torch.float8_e4m3fn).to(torch.float64)
+    elif grid == "fp4":
+        mags = torch.tensor(_E2M1, dtype=torch.float64, device=v.device)
+        ok = (v.abs().unsqueeze(-1) == mags).any(dim=-1)
+    else:
+        raise ValueError(f"[prismaquant] {prefix}: unknown codebook grid {grid!r}")
+    if not bool(ok.all()):
+        raise ValueError(f"[prismaquant] {prefix}: {int((~ok).sum())} of {v.numel()} codebook values "
+                         f"are off the grid declared by the {grid} format")
+
+
+def build_flat_codebook(sub_tables: list[torch.Tensor], prefix: str = "codebook",
+                        grid: str | None = None) -> torch.Tensor:
+    """Concatenate the (2^w, sub_dim) tables row-major into the flat bf16 layout the
+    kernels stage (gridbook/codec.py:146-159): entry (idx, j) of table s sits at
+    base_s + idx*sub_dim + j."""
+    raw = torch.cat([t.reshape(-1).to(torch.float64) for t in sub_tables])
+    if grid is not None:
+        validate_codebook_grid(raw, grid, prefix)
+    flat = raw.to(torch.bfloat16).contiguous()
+    if not torch.equal(flat.to(torch.float64), raw):
+        raise ValueError(f"[prismaquant] {prefix}: the bf16 flat codebook cast is lossy")
+    return flat
+
+
+def flat_codebook_fp8(flat: torch.Tensor, prefix: str = "codebook") -> torch.Tensor:
+    """Flat E4M3-grid codebook as raw bytes (gridbook/codec.py:162-167)."""
+    f8 = flat.to(torch.float8_e4m3fn).contiguous()
+    if not torch.equal(f8.to(torch.float64), flat.to(torch.float64)):
+        raise ValueError(f"[prismaquant] {prefix}: the e4m3 flat codebook cast is lossy")
+    return f8.view(torch.uint8)
+
+
+def build_compose_table(sub_table=TWO_TIER_SUB_TABLE) -> torch.Tensor:
+    """(4096,) fp32 table ``T[c] * 2^(E-127)`` indexed ``E*16 + c``
+    (gridbook/codec.py:170-183, docs/SPEC.md:144-177)."""
+    t = torch.tensor(list(sub_table), dtype=torch.float64)
+    e = torch.arange(256, dtype=torch.float64)
+    return (t[None, :] * torch.pow(2.0, e[:, None] - float(TWO_TIER_SUPER_BIAS))
+            ).to(torch.float32).reshape(-1).contiguous()
+
+
+def pad_qweight(qw: torch.Tensor) -> torch.Tensor:
+    """Right-pad each row by 16 zero bytes (gridbook/codec.py:200-229).  The kernels
+    here do not need the slack per row (they read 16-byte windows of the whole
+    buffer), but accept the reference's padded layout through the row stride."""
+    return torch.nn.functional.pad(qw.contiguous(), (0, PAD_BYTES), value=0).contiguous()
+
+
+def with_tail_slack(qw: torch.Tensor) -> torch.Tensor:
+    """Same bytes in a buffer that stays readable for 16 bytes past the last row, which
+    is what the kernels' aligned windows may touch."""
+    flat = torch.zeros(qw.numel() + PAD_BYTES, dtype=torch.uint8, device=qw.device)
+    flat[:qw.numel()] = qw.reshape(-1)
+    return flat[:qw.numel()].view(qw.shape)

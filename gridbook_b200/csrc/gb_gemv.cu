@@ -1,23 +1,28 @@
 // Decode-batch (M <= 16) codebook linear and grouped routed-MoE GEMV.
 //
-// One persistent CTA per SM walks tiles of eight output rows.  A producer warp
-// streams each tile's packed rows into a shared-memory ring with 1-D bulk copies
-// (16-byte aligned windows around rows of any stride, so odd type_size rows need
-// no repacking); eight consumer warps split the tile's K range, expand each
-// codeword through a shared-memory codebook into bf16 grid values times the
-// group scale (exact: <= 6 significant bits), and feed them to m16n8k16 bf16 MMAs
-// against the activation rows held in shared memory.  Partials are reduced across
-// warps in shared memory, scaled and rounded to bf16 once.
+// Persistent CTAs of eight warps walk tiles of 64 output rows (x one K slice).  Every
+// warp owns eight whole rows of the tile and streams them through a private
+// shared-memory ring with 1-D bulk copies (16-byte aligned windows around rows of any
+// stride, so odd type_size rows need no repacking; each row lands on a bank-skewed
+// pitch).  The ring is refilled by the warp itself as soon as a stage is consumed, so
+// in steady state there is no CTA-wide synchronisation at all.  Lane (g, t) expands
+// codewords t, 4+t, ... of every superblock of row g through a shared-memory codebook
+// into bf16 grid values times the group scale (exact: <= 6 significant bits) and feeds
+// them to m16n8k16 bf16 MMAs against the activation rows held in shared memory; the
+// accumulators are scaled and rounded to bf16 once.  K slices (only when the activation
+// rows or a warp's rows would not fit) add into an fp32 workspace instead.
 #include "gb_common.cuh"
 
 namespace {
 
-constexpr int kConsumerWarps = 8;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr int kTileRows = 8;
-constexpr int kMaxStages = 8;
-constexpr int kSmemBudget = 220 * 1024;
-constexpr int kXBudget = 96 * 1024;
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kTileRows = 8 * kWarps;     // 64 rows per tile, eight per warp
+constexpr int kMaxStages = 4;
+constexpr int kSmemBig = 216 * 1024;      // one CTA per SM
+constexpr int kXBudget = 64 * 1024;
+constexpr int kTaskBytes = 10 * 1024;     // a warp's eight row slices should stay below this
+constexpr uint32_t kExpBias120 = 120u << 7;   // bf16 exponent offset of 2^120
 
 enum Fmt { kFp4Prod2 = 0, kFp4Signed = 1, kFp4Full = 2, kFp8Prod4 = 3, kFp8Prod2 = 4, kNumFmt = 5 };
 
@@ -44,13 +49,13 @@ struct GemvParams {
   const int32_t* order;
   int E;
   int swiglu;             // tile = 4 gate rows + 4 up rows, output silu(g)*u
-  int m_chunk;            // tokens per tile pass (MoE), multiple of... <= 16
+  int m_chunk;            // tokens per tile pass (MoE), <= 16
   // tiling
   int ksplit, sb_per_slice, n_sb;
   int n_row_tiles;
-  int stages, stage_bytes, run_pitch, piece_pitch;
+  int stages, stage_bytes, row_pitch;
   int x_pitch;            // bytes between activation rows in shared memory
-  int x_rows;             // 8 or 16 rows staged
+  int x_rows;             // activation rows staged (1..16); MMA rows beyond them are zero
   int lut_bytes;
   // outputs
   uint16_t* y;
@@ -115,87 +120,47 @@ struct TileWalker {
   }
 };
 
-struct StagePlan {
-  int n_copies;
-  const uint8_t* src[kTileRows];
-  uint32_t dst[kTileRows];
-  uint32_t bytes[kTileRows];
-  uint32_t row_off[kTileRows];   // byte offset of row g's first superblock inside the stage
-  uint32_t total;
-};
-
-// Where each row of a tile lives in global memory and in its stage buffer.
-GB_DEVINL void plan_stage(const GemvParams& p, const Tile& t, StagePlan& s) {
-  const uint8_t* ebase = p.qw + (int64_t)t.expert * p.expert_stride;
-  const int sb0 = t.slice * p.sb_per_slice;
-  const int nsb = min(p.sb_per_slice, p.n_sb - sb0);
-  s.total = 0;
-  if (p.ksplit == 1) {
-    const int runs = p.swiglu ? 2 : 1;
-    s.n_copies = runs;
-    for (int r = 0; r < runs; ++r) {
-      const int64_t first = (int64_t)t.row0 + (r ? p.N / 2 : 0);
-      const uint8_t* a = ebase + first * p.row_stride;
-      const uint32_t head = (uint32_t)((uintptr_t)a & 15u);
-      const uint32_t bytes = (head + (uint32_t)t.nrows * (uint32_t)p.row_stride + 15u) & ~15u;
-      s.src[r] = a - head;
-      s.dst[r] = r * p.run_pitch;
-      s.bytes[r] = bytes;
-      s.total += bytes;
-      for (int g = 0; g < t.nrows; ++g)
-        s.row_off[r * (kTileRows / 2) + g] = r * p.run_pitch + head + g * (uint32_t)p.row_stride;
-    }
-  } else {
-    s.n_copies = t.nrows;
-    for (int g = 0; g < t.nrows; ++g) {
-      const uint8_t* a = ebase + ((int64_t)t.row0 + g) * p.row_stride + (int64_t)sb0 * p.fmt.type_size;
-      const uint32_t head = (uint32_t)((uintptr_t)a & 15u);
-      const uint32_t bytes = (head + (uint32_t)nsb * p.fmt.type_size + 15u) & ~15u;
-      s.src[g] = a - head;
-      s.dst[g] = g * p.piece_pitch;
-      s.bytes[g] = bytes;
-      s.total += bytes;
-      s.row_off[g] = g * p.piece_pitch + head;
-    }
+// Row g (0..7) of warp `warp`'s share of a tile: its first byte in global memory, or
+// nullptr past the edge.  With swiglu a warp takes four gate rows and the four matching
+// up rows, so a tile covers 32 gate rows + 32 up rows.
+GB_DEVINL const uint8_t* tile_row_ptr(const GemvParams& p, const Tile& t, int warp, int g, int64_t* out_row) {
+  int local = 8 * warp + g;
+  int64_t row = (int64_t)t.row0 + local;
+  if (p.swiglu) {
+    local = 4 * warp + (g & 3);
+    row = (int64_t)t.row0 + local + (g >= 4 ? p.N / 2 : 0);
   }
+  *out_row = row;
+  if (local >= t.nrows) return nullptr;
+  return p.qw + (int64_t)t.expert * p.expert_stride + row * p.row_stride +
+         (int64_t)t.slice * p.sb_per_slice * p.fmt.type_size;
 }
 
-GB_DEVINL void named_barrier_consumers() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+// shared-memory loads by 32-bit shared address
+GB_DEVINL uint32_t lds_u32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
 }
-
-GB_DEVINL uint32_t lds32(const uint8_t* base, uint32_t off) {
-  return *reinterpret_cast<const uint32_t*>(base + off);
+GB_DEVINL uint32_t lds_u8(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
 }
-
-// Expand one codeword into eight bf16 grid values (four packed registers).
-template <int kFmt>
-GB_DEVINL void decode_codeword(const GemvParams& p, const uint8_t* lut, uint64_t code,
-                               uint32_t (&w)[4]) {
-  if constexpr (kFmt == kFp4Full) {
-    const uint4 v = *reinterpret_cast<const uint4*>(lut + (uint32_t)code * 16u);
-    w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
-  } else if constexpr (kFmt == kFp4Signed) {
-    const uint4 v = *reinterpret_cast<const uint4*>(lut + (uint32_t)(code >> 8) * 16u);
-    const uint32_t s = (uint32_t)code & 0xFFu;
-    // sign bit j flips coordinate j: bit 15 of the low half, bit 31 of the high half
-    w[0] = v.x ^ (((s >> 0) & 1u) << 15) ^ (((s >> 1) & 1u) << 31);
-    w[1] = v.y ^ (((s >> 2) & 1u) << 15) ^ (((s >> 3) & 1u) << 31);
-    w[2] = v.z ^ (((s >> 4) & 1u) << 15) ^ (((s >> 5) & 1u) << 31);
-    w[3] = v.w ^ (((s >> 6) & 1u) << 15) ^ (((s >> 7) & 1u) << 31);
-  } else if constexpr (kFmt == kFp4Prod2 || kFmt == kFp8Prod2) {
-    const uint32_t i0 = (uint32_t)code & ((1u << p.split.width[0]) - 1u);
-    const uint32_t i1 = (uint32_t)(code >> p.split.width[0]);
-    const uint2 a = *reinterpret_cast<const uint2*>(lut + i0 * 8u);
-    const uint2 b = *reinterpret_cast<const uint2*>(lut + (uint32_t)p.split.base[1] * 2u + i1 * 8u);
-    w[0] = a.x; w[1] = a.y; w[2] = b.x; w[3] = b.y;
-  } else {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t idx = (uint32_t)(code >> p.split.shift[i]) & ((1u << p.split.width[i]) - 1u);
-      w[i] = lds32(lut, (uint32_t)p.split.base[i] * 2u + idx * 4u);
-    }
-  }
+GB_DEVINL uint32_t lds_u16(uint32_t a) {
+  uint32_t v;
+  asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1]; cvt.u32.u16 %0, t; }" : "=r"(v) : "r"(a));
+  return v;
+}
+GB_DEVINL uint2 lds_v2(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+GB_DEVINL uint4 lds_v4(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
 }
 
 GB_DEVINL uint32_t mul_bf16x2(uint32_t a, uint32_t s2) {
@@ -204,7 +169,146 @@ GB_DEVINL uint32_t mul_bf16x2(uint32_t a, uint32_t s2) {
   return d;
 }
 
-// Copy one codebook block into the shared-memory table (as bf16).
+// Per-thread constants of the decode, computed once.
+struct LaneDecode {
+  uint32_t bit0;               // stream bit of this lane's first codeword (codeword t of the superblock)
+  uint32_t kstep;              // stream bits between this lane's consecutive codewords (4 codewords)
+  uint32_t mask[4], shift[4], lbase[4];   // product split: index masks, shifts, table byte offsets
+  uint32_t scale_off;          // byte offset of the scale plane inside a superblock
+};
+
+// Codeword bits at stream bit `bit` of the superblock at shared address sbp (any alignment).
+template <bool kWide>
+GB_DEVINL void fetch_code(uint32_t sbp, uint32_t bit, uint32_t& lo, uint32_t& hi) {
+  const uint32_t a = sbp + (bit >> 3);
+  const uint32_t mis = a & 3u, a4 = a - mis, sh = mis * 8u + (bit & 7u);
+  const uint32_t w0 = lds_u32(a4), w1 = lds_u32(a4 + 4);
+  lo = __funnelshift_r(w0, w1, sh);
+  hi = 0;
+  if constexpr (kWide) {
+    const uint32_t w2 = lds_u32(a4 + 8);
+    hi = __funnelshift_r(w1, w2, sh);
+  }
+}
+
+// Expand one codeword through the shared-memory table into eight bf16 values.
+template <int kFmt, bool kWide>
+GB_DEVINL void expand_code(const LaneDecode& d, uint32_t lut, uint32_t lo, uint32_t hi, uint32_t (&w)[4]) {
+  if constexpr (kFmt == kFp4Full) {
+    const uint4 v = lds_v4(lut + ((lo & d.mask[0]) << 4));
+    w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+  } else if constexpr (kFmt == kFp4Signed) {
+    const uint32_t code = lo & d.mask[0];
+    const uint4 v = lds_v4(lut + ((code >> 8) << 4));
+    // sign bit j flips coordinate j: bit 15 of the low half, bit 31 of the high half
+    w[0] = v.x ^ ((code & 1u) << 15) ^ ((code & 2u) << 30);
+    w[1] = v.y ^ ((code & 4u) << 13) ^ ((code & 8u) << 28);
+    w[2] = v.z ^ ((code & 16u) << 11) ^ ((code & 32u) << 26);
+    w[3] = v.w ^ ((code & 64u) << 9) ^ ((code & 128u) << 24);
+  } else if constexpr (kFmt == kFp4Prod2 || kFmt == kFp8Prod2) {
+    const uint32_t i0 = lo & d.mask[0];
+    const uint32_t i1 = (lo >> d.shift[1]) & d.mask[1];
+    const uint2 va = lds_v2(lut + (i0 << 3));
+    const uint2 vb = lds_v2(lut + d.lbase[1] + (i1 << 3));
+    w[0] = va.x; w[1] = va.y; w[2] = vb.x; w[3] = vb.y;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t idx;
+      if constexpr (kWide) {
+        const uint64_t code = ((uint64_t)hi << 32) | lo;
+        idx = (uint32_t)(code >> d.shift[i]) & d.mask[i];
+      } else {
+        idx = (lo >> d.shift[i]) & d.mask[i];
+      }
+      w[i] = lds_u32(lut + d.lbase[i] + (idx << 2));
+    }
+  }
+}
+
+// Same job when the rows of one task use different codebook blocks: gather this row's
+// entries from global memory (rare: only tasks that straddle a role boundary).
+template <bool kFp8>
+GB_DEVINL void expand_code_global(const GemvParams& p, int64_t cb_off, uint32_t lo, uint32_t hi, uint32_t (&w)[4]) {
+  uint64_t code = (uint64_t)lo | ((uint64_t)hi << 32);
+  code &= (1ull << p.fmt.k_bits) - 1ull;
+  const int sd = p.split.sub_dim;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t half[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int c = 2 * j + h;
+      int64_t idx;
+      bool neg = false;
+      if (p.fmt.mode == GB_MODE_FULL) idx = (int64_t)code * 8 + c;
+      else if (p.fmt.mode == GB_MODE_SIGNED) { idx = (int64_t)(code >> 8) * 8 + c; neg = (code >> c) & 1ull; }
+      else {
+        const int si = c / sd;
+        idx = p.split.base[si] + (int64_t)((code >> p.split.shift[si]) & ((1ull << p.split.width[si]) - 1ull)) * sd + (c - si * sd);
+      }
+      uint32_t b;
+      if constexpr (kFp8) b = __float_as_uint(gb_e4m3_to_f32(reinterpret_cast<const uint8_t*>(p.codebook)[cb_off + idx])) >> 16;
+      else b = reinterpret_cast<const uint16_t*>(p.codebook)[cb_off + idx];
+      if (neg) b ^= 0x8000u;
+      if constexpr (!kFp8) {          // match the pre-scaled shared-memory table (values * 2^120)
+        if (p.fmt.scale_coding == GB_SCALE_V1 && (b & 0x7FFFu)) b += kExpBias120;
+      }
+      half[h] = b;
+    }
+    w[j] = half[0] | (half[1] << 16);
+  }
+}
+
+// A task whose eight rows use different codebook blocks (it straddles a role boundary of a
+// fused module): same arithmetic, entries gathered from global memory.  Kept out of line so
+// the common loop stays small.
+template <bool kFp8>
+__device__ __noinline__ void mixed_codebook_task(const GemvParams& p, const LaneDecode& d, uint32_t sbp, int nsb,
+                                                 int64_t cb_off, float row_scale, uint32_t xa_s, uint32_t xb_s,
+                                                 uint32_t xa_step, uint32_t xb_step, uint32_t sub_s, int t4,
+                                                 float (&acc0)[4], float (&acc1)[4]) {
+  const uint32_t ts = (uint32_t)p.fmt.type_size;
+  const bool v1 = p.fmt.scale_coding == GB_SCALE_V1;
+  for (int sb = 0; sb < nsb; ++sb, sbp += ts, xa_s += xa_step, xb_s += xb_step) {
+    for (int kb = 0; kb < 8; ++kb) {
+      const uint4 xa = lds_v4(xa_s + kb * 64);
+      const uint4 xb = lds_v4(xb_s + kb * 64);
+      uint32_t lo, hi, w[4];
+      fetch_code<true>(sbp, d.bit0 + kb * d.kstep, lo, hi);
+      expand_code_global<kFp8>(p, cb_off, lo, hi, w);
+      if constexpr (kFp8) {
+        for (int j = 0; j < 4; ++j) {
+          const float flo = __uint_as_float(w[j] << 16) * row_scale;
+          const float fhi = __uint_as_float(w[j] & 0xFFFF0000u) * row_scale;
+          asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[j]) : "f"(fhi), "f"(flo));
+        }
+      } else {
+        const uint32_t grp = 2u * kb + ((uint32_t)t4 >> 1);
+        uint32_t sbits;
+        if (v1) {
+          const uint32_t b = lds_u8(sbp + d.scale_off + grp);
+          sbits = ((b & 0x7Fu) << 4) | ((b & 0x80u) << 8);
+        } else {
+          const uint32_t e = lds_u8(sbp + d.scale_off);
+          const uint32_t nib = (lds_u8(sbp + d.scale_off + 1u + (grp >> 1)) >> ((grp & 1u) * 4u)) & 0xFu;
+          sbits = (lds_u16(sub_s + nib * 2u) + ((e - 127u) << 7)) & 0xFFFFu;
+        }
+        const uint32_t s2 = sbits * 0x10001u;
+        for (int j = 0; j < 4; ++j) w[j] = mul_bf16x2(w[j], s2);
+      }
+      const uint32_t a0[4] = {xa.x, xb.x, xa.y, xb.y};
+      const uint32_t a1[4] = {xa.z, xb.z, xa.w, xb.w};
+      gb_mma_bf16_16816(acc0, a0, w[0], w[1]);
+      gb_mma_bf16_16816(acc1, a1, w[2], w[3]);
+    }
+  }
+}
+
+// Copy one codebook block into the shared-memory table as bf16.  For the fp4 grid with
+// E4M3-direct scales the entries are stored times 2^120, so that the raw scale byte,
+// shifted into the bf16 exponent/mantissa field (= scale * 2^-120, subnormal codes
+// included), multiplies to the exact product with one packed bf16 multiply.
 template <int kFmt>
 GB_DEVINL void stage_lut(const GemvParams& p, uint8_t* lut, int64_t cb_off, int tid, int nthreads) {
   constexpr bool fp8 = (kFmt == kFp8Prod4 || kFmt == kFp8Prod2);
@@ -215,341 +319,370 @@ GB_DEVINL void stage_lut(const GemvParams& p, uint8_t* lut, int64_t cb_off, int 
       dst[i] = (uint16_t)(__float_as_uint(gb_e4m3_to_f32(src[i])) >> 16);   // exact: 4 significant bits
   } else {
     const uint16_t* src = reinterpret_cast<const uint16_t*>(p.codebook) + cb_off;
-    for (int i = tid; i < p.cb_elems; i += nthreads) dst[i] = src[i];
+    const uint32_t bias = p.fmt.scale_coding == GB_SCALE_V1 ? kExpBias120 : 0u;
+    for (int i = tid; i < p.cb_elems; i += nthreads) {
+      const uint32_t b = src[i];
+      dst[i] = (uint16_t)((b & 0x7FFFu) ? b + bias : b);
+    }
   }
 }
 
-template <int kFmt, bool kMoE>
-__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
+// Lanes 0..7 of a warp each copy one of the warp's eight rows of tile t into ring stage `dst`.
+GB_DEVINL void issue_task(const GemvParams& p, const Tile& t, int warp, int lane, uint8_t* dst, uint64_t* bar) {
+  const int nsb = min(p.sb_per_slice, p.n_sb - t.slice * p.sb_per_slice);
+  int64_t row;
+  const uint8_t* src = lane < 8 ? tile_row_ptr(p, t, warp, lane, &row) : nullptr;
+  uint32_t bytes = 0, head = 0;
+  if (src) {
+    head = (uint32_t)((uintptr_t)src & 15u);
+    bytes = (head + (uint32_t)nsb * (uint32_t)p.fmt.type_size + 15u) & ~15u;
+  }
+  uint32_t total = bytes;
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+  if (lane == 0) gb_mbar_expect_tx(bar, total);     // total == 0 completes the phase at once
+  __syncwarp();
+  if (src) gb_bulk_g2s(dst + lane * p.row_pitch, src - head, bytes, bar);
+}
+
+template <int kFmt, bool kMoE, bool kWide, bool kLit>
+__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant__ GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);
-  uint64_t* empty_bar = full_bar + kMaxStages;
-  float* red = reinterpret_cast<float*>(smem + 256);                 // [8 warps][16][8]
-  uint8_t* lut = smem + 256 + kConsumerWarps * 16 * 8 * 4;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);             // [warps][kMaxStages]
+  uint16_t* sub_tab = reinterpret_cast<uint16_t*>(smem + 512);        // 16 bf16 two-tier multipliers
+  uint8_t* zero_strip = smem + 640;                                   // 640 zero bytes for idle MMA rows
+  uint8_t* lut = smem + 1280;
   uint8_t* xs = lut + p.lut_bytes;
-  uint8_t* stages = xs + p.x_rows * p.x_pitch;
+  uint8_t* rings = xs + p.x_rows * p.x_pitch;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr bool fp8 = (kFmt == kFp8Prod4 || kFmt == kFp8Prod2);
 
   if (tid == 0) {
-    for (int s = 0; s < p.stages; ++s) {
-      gb_mbar_init(&full_bar[s], 1);
-      gb_mbar_init(&empty_bar[s], kConsumerWarps);
-    }
+    for (int s = 0; s < kWarps * kMaxStages; ++s) gb_mbar_init(&full_bar[s], 1);
     gb_fence_barrier_init();
   }
+  for (int i = tid; i < 160; i += kThreads) reinterpret_cast<uint32_t*>(zero_strip)[i] = 0u;
+  if (tid < 16 && p.fmt.scale_coding == GB_SCALE_V2)
+    sub_tab[tid] = (uint16_t)(__float_as_uint(p.compose[127 * 16 + tid]) >> 16);   // T[c], exact in bf16
   __syncthreads();
 
-  if (warp == kConsumerWarps) {
-    // ------------------------------ producer ------------------------------
-    if (lane == 0) {
-      TileWalker<kMoE> walk(p);
-      Tile t;
-      StagePlan sp;
-      for (int it = 0; walk.next(t); ++it) {
-        const int s = it % p.stages;
-        if (it >= p.stages && !gb_mbar_wait(&empty_bar[s], ((it / p.stages) - 1) & 1)) {
-          atomicExch(p.status, 1);
-          return;
-        }
-        plan_stage(p, t, sp);
-        gb_mbar_expect_tx(&full_bar[s], sp.total);
-        uint8_t* sbase = stages + (size_t)s * p.stage_bytes;
-        for (int c = 0; c < sp.n_copies; ++c) gb_bulk_g2s(sbase + sp.dst[c], sp.src[c], sp.bytes[c], &full_bar[s]);
-      }
+  const int g = lane >> 2, t4 = lane & 3;
+  LaneDecode d;
+  {
+    d.bit0 = (uint32_t)t4 * (uint32_t)p.fmt.k_bits;
+    d.kstep = 4u * (uint32_t)p.fmt.k_bits;
+    d.scale_off = 4u * p.fmt.k_bits;
+    const bool product = p.fmt.mode == GB_MODE_PRODUCT;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      d.mask[i] = product ? ((1u << p.split.width[i]) - 1u) : 0u;
+      d.shift[i] = product ? (uint32_t)p.split.shift[i] : 0u;
+      d.lbase[i] = product ? (uint32_t)p.split.base[i] * 2u : 0u;
     }
-    return;
+    if (!product) d.mask[0] = p.fmt.k_bits >= 32 ? 0xFFFFFFFFu : ((1u << p.fmt.k_bits) - 1u);
+  }
+  const uint32_t lut_s = gb_smem_u32(lut), xs_s = gb_smem_u32(xs), sub_s = gb_smem_u32(sub_tab);
+  const uint32_t zero_s = gb_smem_u32(zero_strip);
+  // literal layout: byte selectors (index byte t4; scale byte 2(kb&1) + (t4>>1), duplicated into both halves)
+  const uint32_t sel_idx = 0x4440u | (uint32_t)t4;
+  const uint32_t sel_sc_even = 0x4040u | ((uint32_t)t4 >> 1) | (((uint32_t)t4 >> 1) << 8);
+  const uint32_t sel_sc_odd = 0x4040u | (2u + ((uint32_t)t4 >> 1)) | ((2u + ((uint32_t)t4 >> 1)) << 8);
+  uint8_t* my_ring = rings + (size_t)warp * p.stages * p.stage_bytes;
+  const uint32_t ring_s = gb_smem_u32(my_ring);
+  uint64_t* my_bar = full_bar + warp * kMaxStages;
+  const uint32_t ts = (uint32_t)p.fmt.type_size;
+  const bool v1 = p.fmt.scale_coding == GB_SCALE_V1;
+
+  // ---- fill this warp's ring: the weight stream does not depend on the activations ----
+  TileWalker<kMoE> ahead(p);
+  Tile ta;
+  bool more = true;
+  for (int i = 0; i < p.stages; ++i) {
+    more = more && ahead.next(ta);
+    if (more) issue_task(p, ta, warp, lane, my_ring + (size_t)i * p.stage_bytes, &my_bar[i]);
   }
 
-  // -------------------------------- consumers --------------------------------
-  const int g = lane >> 2, t4 = lane & 3;
-  const int cw = 4 * warp + t4;                       // codeword of the superblock this lane expands
-  const uint32_t cw_bit = (uint32_t)cw * (uint32_t)p.fmt.k_bits;
-  const int grp = cw >> 1;
-  const int ctid = tid, cthreads = kConsumerWarps * 32;
-
-  // zero the activation rows that stay padding
-  for (int i = ctid; i < p.x_rows * p.x_pitch / 4; i += cthreads) reinterpret_cast<uint32_t*>(xs)[i] = 0u;
   int64_t lut_off = -1;
-  int x_expert = -1, x_m0 = -1;
-  int cur_slice = -1;
-  named_barrier_consumers();
-
+  int x_expert = -1, x_m0 = -1, cur_slice = -1;
   TileWalker<kMoE> walk(p);
   Tile t;
-  StagePlan sp;
   for (int it = 0; walk.next(t); ++it) {
     const int s = it % p.stages;
     const int sb0 = t.slice * p.sb_per_slice;
     const int nsb = min(p.sb_per_slice, p.n_sb - sb0);
 
-    // ---- (re)stage the activations this tile multiplies ----
-    bool restage_x;
-    if constexpr (kMoE) restage_x = (t.expert != x_expert) || (t.m0 != x_m0);
-    else restage_x = (t.slice != cur_slice);
-    // ---- this lane's row, and the codebook block(s) of the tile's rows ----
-    const bool second_half = p.swiglu && g >= kTileRows / 2;
-    const int g_local = p.swiglu ? (g & 3) : g;
-    const bool row_ok = g_local < t.nrows;
-    const int64_t out_row = (int64_t)t.row0 + g_local + (second_half ? p.N / 2 : 0);
+    // ---- this lane's row, and the codebook block(s) of the task's rows ----
+    int64_t out_row;
+    const uint8_t* my_src = tile_row_ptr(p, t, warp, g, &out_row);
+    const bool row_ok = my_src != nullptr;
     int64_t off_lo = 0, my_cb_off = 0;
-    bool uniform = true;
+    bool uniform = true;            // per warp: do my eight rows share the staged codebook block?
     if (p.cb_row_offset) {
       off_lo = p.cb_row_offset[t.row0];
       if (row_ok) my_cb_off = p.cb_row_offset[out_row];
-      uniform = __all_sync(0xffffffffu, !row_ok || my_cb_off == off_lo);   // same verdict in every warp
+      uniform = __all_sync(0xffffffffu, !row_ok || my_cb_off == off_lo);
     }
-    const bool restage_lut = uniform && (off_lo != lut_off);
+    bool restage_x;
+    if constexpr (kMoE) restage_x = (t.expert != x_expert) || (t.m0 != x_m0);
+    else restage_x = (t.slice != cur_slice);
+    const bool restage_lut = off_lo != lut_off;       // same verdict in every warp of the CTA
     if (restage_x || restage_lut) {
-      named_barrier_consumers();     // everyone is done with the previous contents
+      if (it > 0) __syncthreads();     // everyone is done with the previous contents
       if (restage_lut) {
-        stage_lut<kFmt>(p, lut, off_lo, ctid, cthreads);
+        stage_lut<kFmt>(p, lut, off_lo, tid, kThreads);
         lut_off = off_lo;
       }
       if (restage_x) {
-        const int kw = nsb * 256;           // weights of K in this slice
-        const int vec_per_row = kw / 8;     // 16-byte vectors
-        const int mrows = t.mcount;
-        for (int i = ctid; i < mrows * vec_per_row; i += cthreads) {
+        const int vec_per_row = nsb * 32;     // 16-byte vectors of this K slice
+        for (int i = tid; i < t.mcount * vec_per_row; i += kThreads) {
           const int m = i / vec_per_row, v = i - m * vec_per_row;
-          int64_t src_row;
+          int64_t src_row = m;
           if constexpr (kMoE) {
             const int pair = p.order[t.m0 + m];
             src_row = p.x_row ? p.x_row[pair] : pair;
-          } else {
-            src_row = m;
           }
           const uint4 val = *reinterpret_cast<const uint4*>(p.x + src_row * p.K + (int64_t)sb0 * 256 + v * 8);
           *reinterpret_cast<uint4*>(xs + m * p.x_pitch + v * 16) = val;
         }
-        if constexpr (kMoE) {
-          // rows beyond this pass must read as zero
-          for (int i = ctid; i < (p.x_rows - mrows) * vec_per_row; i += cthreads) {
-            const int m = mrows + i / vec_per_row, v = i % vec_per_row;
-            *reinterpret_cast<uint4*>(xs + m * p.x_pitch + v * 16) = make_uint4(0, 0, 0, 0);
-          }
-          x_expert = t.expert; x_m0 = t.m0;
-        } else {
-          cur_slice = t.slice;
-        }
+        if constexpr (kMoE) { x_expert = t.expert; x_m0 = t.m0; }
+        else cur_slice = t.slice;
       }
-      named_barrier_consumers();
+      __syncthreads();
     }
 
-    plan_stage(p, t, sp);
-    if (!gb_mbar_wait(&full_bar[s], (it / p.stages) & 1)) {
-      atomicExch(p.status, 2);
-      return;
-    }
-    const uint8_t* sbase = stages + (size_t)s * p.stage_bytes;
-
-    const uint8_t* rowp = sbase + sp.row_off[row_ok ? g : 0];
+    // A wait that runs out raises the status word and carries on (the output is then
+    // garbage, and flagged): leaving here would strand the other warps at a CTA barrier.
+    if (!gb_mbar_wait(&my_bar[s], (it / p.stages) & 1)) atomicExch(p.status, 2);
+    uint32_t sbp = ring_s + (uint32_t)s * (uint32_t)p.stage_bytes + (uint32_t)g * (uint32_t)p.row_pitch +
+                   (row_ok ? (uint32_t)((uintptr_t)my_src & 15u) : 0u);
+    const uint32_t warp_head = __shfl_sync(0xffffffffu, (uint32_t)((uintptr_t)my_src & 15u), 0);
     // fp8 grid: the served weight is bf16(value * row scale), rounded per weight
     float row_scale = 1.0f;
     if constexpr (fp8) {
       if (row_ok) row_scale = p.weight_scale[(int64_t)t.expert * p.N + out_row];
     }
 
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    const bool hi_rows = p.x_rows > 8;
-    for (int sb = 0; sb < nsb; ++sb) {
-      const uint8_t* sbp = rowp + sb * p.fmt.type_size;
-      // activations: x[m][sb*256 + warp*32 + 8*t4 .. +8)
-      const uint32_t xoff = (uint32_t)(sb * 256 + warp * 32 + t4 * 8) * 2u;
-      const uint4 xa = *reinterpret_cast<const uint4*>(xs + g * p.x_pitch + xoff);
-      uint4 xb = make_uint4(0, 0, 0, 0);
-      if (hi_rows) xb = *reinterpret_cast<const uint4*>(xs + (g + 8) * p.x_pitch + xoff);
+    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+    float accx[6][4] = {};     // more independent accumulation chains: the MMA result latency is long
+    // Lanes whose MMA row has no activation row this pass read a zeroed strip instead, and
+    // lanes whose weight row lies past the edge decode the task's first row (their results
+    // are never stored): the loop below is branch-free.
+    const bool lo_live = g < t.mcount, hi_live = g + 8 < t.mcount;
+    const uint32_t x_lane = (uint32_t)t4 * 16u;
+    uint32_t xa_s = (lo_live ? xs_s + (uint32_t)g * (uint32_t)p.x_pitch : zero_s) + x_lane;
+    uint32_t xb_s = (hi_live ? xs_s + (uint32_t)(g + 8) * (uint32_t)p.x_pitch : zero_s) + x_lane;
+    const uint32_t xa_step = lo_live ? 512u : 0u, xb_step = hi_live ? 512u : 0u;
+    if (!row_ok) sbp = ring_s + (uint32_t)s * (uint32_t)p.stage_bytes + warp_head;
 
-      uint32_t w[4] = {0u, 0u, 0u, 0u};
-      if (row_ok) {
-        // codeword bits: aligned 32-bit words around an arbitrary byte address
-        const uint32_t byte_addr = (uint32_t)(uintptr_t)(sbp) + (cw_bit >> 3);
-        const uint32_t mis = byte_addr & 3u;
-        const uint32_t* words = reinterpret_cast<const uint32_t*>(sbp + (cw_bit >> 3) - mis);
-        const uint64_t code = gb_extract_bits(words, mis * 8u + (cw_bit & 7u), p.fmt.k_bits);
-        if (uniform) {
-          decode_codeword<kFmt>(p, lut, code, w);
-        } else {
-          // rows of one tile use different codebooks: gather this row's from global memory
-          const int sd = p.split.sub_dim;
-          float v[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            int64_t idx;
-            bool neg = false;
-            if (p.fmt.mode == GB_MODE_FULL) idx = (int64_t)code * 8 + j;
-            else if (p.fmt.mode == GB_MODE_SIGNED) { idx = (int64_t)(code >> 8) * 8 + j; neg = (code >> j) & 1ull; }
-            else {
-              const int si = j / sd;
-              idx = p.split.base[si] + (int64_t)((code >> p.split.shift[si]) & ((1ull << p.split.width[si]) - 1ull)) * sd + (j - si * sd);
-            }
-            float f;
-            if constexpr (fp8) f = gb_e4m3_to_f32(reinterpret_cast<const uint8_t*>(p.codebook)[my_cb_off + idx]);
-            else f = gb_bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(p.codebook)[my_cb_off + idx]);
-            v[j] = neg ? -f : f;
-          }
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            w[j] = (__float_as_uint(v[2 * j]) >> 16) | (__float_as_uint(v[2 * j + 1]) & 0xFFFF0000u);
+    if (uniform) {
+#ifdef GB_EXP_NO_COMPUTE
+      for (int sb = 0; sb < 0; ++sb, sbp += ts, xa_s += xa_step, xb_s += xb_step) {
+#else
+      for (int sb = 0; sb < nsb; ++sb, sbp += ts, xa_s += xa_step, xb_s += xb_step) {
+#endif
+        uint4 iw0, iw1, sw;                       // literal layout: index bytes and scale bytes
+        uint32_t super_bits = 0;
+        if constexpr (kLit) {
+          iw0 = lds_v4(sbp); iw1 = lds_v4(sbp + 16); sw = lds_v4(sbp + 32);
+        } else if constexpr (!fp8) {
+          if (!v1) super_bits = (lds_u8(sbp + d.scale_off) - 127u) << 7;   // two-tier exponent, once
         }
-        if constexpr (fp8) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float lo = __uint_as_float(w[j] << 16) * row_scale;
-            const float hi = __uint_as_float(w[j] & 0xFFFF0000u) * row_scale;
-            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[j]) : "f"(hi), "f"(lo));
-          }
-        } else {
-          // group scale (exact E4M3 value) as a bf16 pair
-          const uint8_t* plane = sbp + 4 * p.fmt.k_bits;
-          float sc;
-          if (p.fmt.scale_coding == GB_SCALE_V1) {
-            sc = gb_e4m3_to_f32(plane[grp]);
+        for (int kb = 0; kb < 8; ++kb) {
+          // k-block kb = weights [32 kb, 32 kb + 32): this lane expands codeword 4 kb + t4
+          const uint4 xa = lds_v4(xa_s + kb * 64);
+          const uint4 xb = lds_v4(xb_s + kb * 64);
+          uint32_t w[4];
+          if constexpr (kLit) {
+            const uint32_t iw = kb == 0 ? iw0.x : kb == 1 ? iw0.y : kb == 2 ? iw0.z : kb == 3 ? iw0.w
+                              : kb == 4 ? iw1.x : kb == 5 ? iw1.y : kb == 6 ? iw1.z : iw1.w;
+            const uint32_t code = __byte_perm(iw, 0u, sel_idx);
+            const uint4 v = lds_v4(lut_s + (code << 4));
+            w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+            const uint32_t scw = (kb >> 1) == 0 ? sw.x : (kb >> 1) == 1 ? sw.y : (kb >> 1) == 2 ? sw.z : sw.w;
+            const uint32_t b2 = __byte_perm(scw, 0u, (kb & 1) ? sel_sc_odd : sel_sc_even);   // byte in both halves
+            const uint32_t s2 = ((b2 & 0x007F007Fu) << 4) | ((b2 & 0x00800080u) << 8);       // scale * 2^-120
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[j] = mul_bf16x2(w[j], s2);
           } else {
-            const uint32_t e = plane[0];
-            const uint32_t nib = (plane[1 + (grp >> 1)] >> ((grp & 1) * 4)) & 0xFu;
-            sc = __ldg(p.compose + e * 16 + nib);
-          }
-          const uint32_t sb16 = __float_as_uint(sc) >> 16;
-          const uint32_t s2 = sb16 | (sb16 << 16);
+            uint32_t lo, hi;
+            fetch_code<kWide>(sbp, d.bit0 + kb * d.kstep, lo, hi);
+            expand_code<kFmt, kWide>(d, lut_s, lo, hi, w);
+            if constexpr (fp8) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) w[j] = mul_bf16x2(w[j], s2);
+              for (int j = 0; j < 4; ++j) {
+                const float flo = __uint_as_float(w[j] << 16) * row_scale;
+                const float fhi = __uint_as_float(w[j] & 0xFFFF0000u) * row_scale;
+                asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[j]) : "f"(fhi), "f"(flo));
+              }
+            } else {
+              // group (4 kb + t4) / 2 = 2 kb + (t4 >> 1); its scale as a packed bf16 pair
+              const uint32_t grp = 2u * kb + ((uint32_t)t4 >> 1);
+              uint32_t sbits;
+              if (v1) {
+                const uint32_t b = lds_u8(sbp + d.scale_off + grp);
+                sbits = ((b & 0x7Fu) << 4) | ((b & 0x80u) << 8);                 // scale * 2^-120
+              } else {
+                const uint32_t nib = (lds_u8(sbp + d.scale_off + 1u + (grp >> 1)) >> ((grp & 1u) * 4u)) & 0xFu;
+                sbits = (lds_u16(sub_s + nib * 2u) + super_bits) & 0xFFFFu;      // T[c] * 2^(E-127)
+              }
+              const uint32_t s2 = sbits * 0x10001u;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) w[j] = mul_bf16x2(w[j], s2);
+            }
+          }
+          const uint32_t a0[4] = {xa.x, xb.x, xa.y, xb.y};
+          const uint32_t a1[4] = {xa.z, xb.z, xa.w, xb.w};
+          if ((kb & 3) == 0) {
+            gb_mma_bf16_16816(acc0, a0, w[0], w[1]);
+            gb_mma_bf16_16816(acc1, a1, w[2], w[3]);
+          } else {
+            gb_mma_bf16_16816(accx[2 * (kb & 3) - 2], a0, w[0], w[1]);
+            gb_mma_bf16_16816(accx[2 * (kb & 3) - 1], a1, w[2], w[3]);
+          }
         }
       }
-      {
-        const uint32_t a[4] = {xa.x, xb.x, xa.y, xb.y};
-        gb_mma_bf16_16816(acc, a, w[0], w[1]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc0[i] += accx[0][i] + accx[2][i] + accx[4][i];
+        acc1[i] += accx[1][i] + accx[3][i] + accx[5][i];
       }
-      {
-        const uint32_t a[4] = {xa.z, xb.z, xa.w, xb.w};
-        gb_mma_bf16_16816(acc, a, w[2], w[3]);
-      }
+    } else {
+      mixed_codebook_task<fp8>(p, d, sbp, nsb, my_cb_off, row_scale, xa_s, xb_s, xa_step, xb_step, sub_s, t4,
+                               acc0, acc1);
     }
+    // ---- the stage is free: refill it with the task kMaxStages ahead ----
     __syncwarp();
-    if (lane == 0) gb_mbar_arrive(&empty_bar[s]);
+    more = more && ahead.next(ta);
+    if (more) issue_task(p, ta, warp, lane, my_ring + (size_t)s * p.stage_bytes, &my_bar[s]);
 
-    // ---- cross-warp reduction: red[warp][m][n] ----
-    float* my = red + warp * 128;
-    my[g * 8 + 2 * t4] = acc[0];
-    my[g * 8 + 2 * t4 + 1] = acc[1];
-    my[(g + 8) * 8 + 2 * t4] = acc[2];
-    my[(g + 8) * 8 + 2 * t4 + 1] = acc[3];
-    named_barrier_consumers();
-    if (ctid < 128) {
-      const int m = ctid >> 3, n = ctid & 7;
-      float v = 0.f;
+    // ---- results: lane (g, t4) holds C[m = g (+8)][n = 2 t4 (+1)], n = row inside the task ----
+    float c[4];
 #pragma unroll
-      for (int w8 = 0; w8 < kConsumerWarps; ++w8) v += red[w8 * 128 + ctid];
-      if (m < t.mcount) {
-        if (p.swiglu) {
-          // rows 0..3 are gate, 4..7 the matching up rows
-          float other = 0.f;
+    for (int i = 0; i < 4; ++i) c[i] = (acc0[i] + acc1[i]) * p.global_scale;
+    if (p.swiglu) {
+      // rows 0..3 of the task are gate rows, 4..7 the matching up rows held two lanes on
+      float up[4];
 #pragma unroll
-          for (int w8 = 0; w8 < kConsumerWarps; ++w8) other += red[w8 * 128 + (ctid ^ 4)];
-          if (n < 4 && n < t.nrows) {
-            const int64_t grow = (int64_t)t.row0 + n, urow = grow + p.N / 2;
-            const float gs = p.global_scale, us = p.global_scale;
-            (void)urow;
-            const float gate = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(v * gs));
-            const float up = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(other * us));
+      for (int i = 0; i < 4; ++i) up[i] = __shfl_down_sync(0xffffffffu, c[i], 2);
+      if (t4 < 2) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int m = g + (i >> 1) * 8, n = 2 * t4 + (i & 1);
+          if (m < t.mcount && 4 * warp + n < t.nrows) {
+            const float gate = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(c[i]));
+            const float upv = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(up[i]));
             const float sl = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(gate / (1.0f + __expf(-gate))));
             const int pair = p.order[t.m0 + m];
-            p.y[(int64_t)pair * (p.N / 2) + grow] = (uint16_t)gb_f32_to_bf16_bits(sl * up);
+            p.y[(int64_t)pair * (p.N / 2) + t.row0 + 4 * warp + n] = (uint16_t)gb_f32_to_bf16_bits(sl * upv);
           }
-        } else if (n < t.nrows) {
-          const int64_t row = (int64_t)t.row0 + n;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int m = g + (i >> 1) * 8, n = 2 * t4 + (i & 1);
+        if (m < t.mcount && 8 * warp + n < t.nrows) {
+          const int64_t row = (int64_t)t.row0 + 8 * warp + n;
           if (p.ksplit > 1) {
-            atomicAdd(p.ws + (int64_t)m * p.N + row, v);
+            atomicAdd(p.ws + (int64_t)m * p.N + row, acc0[i] + acc1[i]);
           } else {
-            const float sc = p.global_scale;
             int64_t orow = m;
             if constexpr (kMoE) orow = p.order[t.m0 + m];
-            p.y[orow * p.N + row] = (uint16_t)gb_f32_to_bf16_bits(v * sc);
+            p.y[orow * p.N + row] = (uint16_t)gb_f32_to_bf16_bits(c[i]);
           }
         }
       }
     }
-    named_barrier_consumers();
   }
 }
 
-__global__ void gemv_finalize_kernel(const float* __restrict__ ws, const float* __restrict__ weight_scale,
-                                     float global_scale, uint16_t* __restrict__ y, int64_t M, int64_t N) {
+__global__ void gemv_finalize_kernel(const float* __restrict__ ws, float global_scale,
+                                     uint16_t* __restrict__ y, int64_t total) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= M * N) return;
-  float sc = global_scale;
-  if (weight_scale) sc *= weight_scale[i % N];
-  y[i] = (uint16_t)gb_f32_to_bf16_bits(ws[i] * sc);
+  if (i < total) y[i] = (uint16_t)gb_f32_to_bf16_bits(ws[i] * global_scale);
 }
 
 using KernelFn = void (*)(const GemvParams);
 
-KernelFn pick_kernel(int fmt, bool moe) {
-  static const KernelFn dense[kNumFmt] = {gemv_kernel<kFp4Prod2, false>, gemv_kernel<kFp4Signed, false>,
-                                         gemv_kernel<kFp4Full, false>, gemv_kernel<kFp8Prod4, false>,
-                                         gemv_kernel<kFp8Prod2, false>};
-  static const KernelFn routed[kNumFmt] = {gemv_kernel<kFp4Prod2, true>, gemv_kernel<kFp4Signed, true>,
-                                          gemv_kernel<kFp4Full, true>, gemv_kernel<kFp8Prod4, true>,
-                                          gemv_kernel<kFp8Prod2, true>};
-  return moe ? routed[fmt] : dense[fmt];
+template <bool kMoE>
+KernelFn kernel_of(int fmt, bool wide, bool lit) {
+  switch (fmt) {
+    case kFp4Prod2: return gemv_kernel<kFp4Prod2, kMoE, false, false>;
+    case kFp4Signed: return gemv_kernel<kFp4Signed, kMoE, false, false>;
+    case kFp4Full: return lit ? gemv_kernel<kFp4Full, kMoE, false, true> : gemv_kernel<kFp4Full, kMoE, false, false>;
+    case kFp8Prod4: return wide ? gemv_kernel<kFp8Prod4, kMoE, true, false> : gemv_kernel<kFp8Prod4, kMoE, false, false>;
+    default: return gemv_kernel<kFp8Prod2, kMoE, false, false>;
+  }
 }
 
-int classify(const gb_format& f, int* out) {
+KernelFn pick_kernel(int fmt, bool moe, bool wide, bool lit) {
+  return moe ? kernel_of<true>(fmt, wide, lit) : kernel_of<false>(fmt, wide, lit);
+}
+
+// The 48-byte literal superblock (full mode, k = 8, E4M3-direct scales) with every row slice
+// on a 16-byte boundary can be read with three vector loads per superblock.
+bool literal_aligned(const GemvParams& p) {
+  return p.fmt.grid == GB_GRID_FP4 && p.fmt.mode == GB_MODE_FULL && p.fmt.k_bits == 8 &&
+         p.fmt.scale_coding == GB_SCALE_V1 && ((uintptr_t)p.qw & 15u) == 0 && p.row_stride % 16 == 0 &&
+         p.expert_stride % 16 == 0;
+}
+
+int classify(const gb_format& f, int* out, bool* wide) {
+  *wide = f.k_bits > 32;
   if (f.grid == GB_GRID_FP4) {
+    if (f.k_bits > 32) return gb_fail(GB_EUNSUPPORTED, "fp4 grid codewords wider than 32 bits");
     if (f.mode == GB_MODE_PRODUCT && f.n_sub == 2) { *out = kFp4Prod2; return GB_OK; }
     if (f.mode == GB_MODE_SIGNED) { *out = kFp4Signed; return GB_OK; }
     if (f.mode == GB_MODE_FULL) { *out = kFp4Full; return GB_OK; }
   } else {
     if (f.mode == GB_MODE_PRODUCT && f.n_sub == 4) { *out = kFp8Prod4; return GB_OK; }
-    if (f.mode == GB_MODE_PRODUCT && f.n_sub == 2) { *out = kFp8Prod2; return GB_OK; }
+    if (f.mode == GB_MODE_PRODUCT && f.n_sub == 2 && f.k_bits <= 28) { *out = kFp8Prod2; return GB_OK; }
   }
-  return gb_fail(GB_EUNSUPPORTED, "no decode-batch kernel for grid %d mode %d n_sub %d", f.grid, f.mode,
-                 f.n_sub);
+  return gb_fail(GB_EUNSUPPORTED, "no decode-batch kernel for grid %d mode %d n_sub %d k %d", f.grid, f.mode,
+                 f.n_sub, f.k_bits);
 }
 
-// Fill the tiling fields.  m_rows = activation rows a tile multiplies at once.
-int plan(GemvParams& p, int m_rows, bool moe, size_t* smem_bytes) {
+// Fill the tiling fields.  m_rows = activation rows a tile multiplies at once; `sms` sizes
+// the K slicing of the dense case so that the tiles cover the machine.
+int plan(GemvParams& p, int m_rows, bool moe, int sms, size_t* smem_bytes) {
   p.n_sb = (int)(p.K / 256);
   p.split = gb_make_split(p.fmt.k_bits, p.fmt.mode == GB_MODE_PRODUCT ? p.fmt.n_sub : 1);
   p.cb_elems = (int)gb_codebook_elems(p.fmt);
   p.lut_bytes = (p.cb_elems * 2 + 127) & ~127;
   if (p.lut_bytes > 72 * 1024)
     return gb_fail(GB_EUNSUPPORTED, "codebook of %d entries does not fit the shared-memory table", p.cb_elems);
-  p.x_rows = m_rows > 8 ? 16 : 8;
-  // K slicing so the staged activations fit their budget
-  p.ksplit = 1;
-  p.sb_per_slice = p.n_sb;
-  if (!moe) {
-    while ((int64_t)p.x_rows * (p.sb_per_slice * 512 + 64) > kXBudget) {
-      ++p.ksplit;
-      p.sb_per_slice = (p.n_sb + p.ksplit - 1) / p.ksplit;
-    }
-    p.ksplit = (p.n_sb + p.sb_per_slice - 1) / p.sb_per_slice;
-  }
-  p.x_pitch = p.sb_per_slice * 512 + 64;
+  p.x_rows = m_rows;
   const int half = p.swiglu ? kTileRows / 2 : kTileRows;
   const int64_t rows_out = p.swiglu ? p.N / 2 : p.N;
   p.n_row_tiles = (int)((rows_out + half - 1) / half);
-  const int64_t slice_bytes = (int64_t)p.sb_per_slice * p.fmt.type_size;
-  if (p.ksplit == 1) {
-    p.run_pitch = (int)((half * p.row_stride + 15 + 15) & ~15) + 16;
-    p.piece_pitch = 0;
-    p.stage_bytes = (p.swiglu ? 2 : 1) * p.run_pitch + 16;
-  } else {
-    p.piece_pitch = (int)((slice_bytes + 15 + 15) & ~15) + 16;
-    p.run_pitch = 0;
-    p.stage_bytes = kTileRows * p.piece_pitch + 16;
+  // K slices: (a) the staged activation rows fit their budget, (b) a warp's eight row slices
+  // stay small enough for a multi-stage ring, (c) dense only: enough tiles to cover the SMs.
+  int want = 1;
+  while ((int64_t)p.x_rows * (((p.n_sb + want - 1) / want) * 512 + 64) > kXBudget) ++want;
+  while ((int64_t)8 * ((p.n_sb + want - 1) / want) * p.fmt.type_size > kTaskBytes && want < p.n_sb) ++want;
+  if (!moe) {
+    while (p.n_row_tiles * want < 2 * sms && want < p.n_sb && (p.n_sb + want) / (want + 1) >= 2) ++want;
+  } else if (want > 1) {
+    return gb_fail(GB_EUNSUPPORTED, "K=%lld is too wide for the routed decode kernel at %d rows per pass",
+                   (long long)p.K, m_rows);
   }
-  p.stage_bytes = (p.stage_bytes + 127) & ~127;
-  const int64_t fixed = 256 + kConsumerWarps * 16 * 8 * 4 + p.lut_bytes + (int64_t)p.x_rows * p.x_pitch;
-  int64_t room = kSmemBudget - fixed;
-  int stages = (int)(room / p.stage_bytes);
+  p.sb_per_slice = (p.n_sb + want - 1) / want;
+  p.ksplit = (p.n_sb + p.sb_per_slice - 1) / p.sb_per_slice;
+  p.x_pitch = p.sb_per_slice * 512 + 64;
+  // one row's slice, plus the alignment head and a tail the word-wise extraction may touch,
+  // on a pitch that is 16 mod 32 so the eight rows of a task start in different banks
+  const int64_t slice_bytes = (int64_t)p.sb_per_slice * p.fmt.type_size;
+  p.row_pitch = (int)(((slice_bytes + 15 + 16 + 31) & ~31ll) + 16);
+  p.stage_bytes = (8 * p.row_pitch + 127) & ~127;
+  const int64_t fixed = 1280 + p.lut_bytes + (int64_t)p.x_rows * p.x_pitch;
+  const int stages = (int)((kSmemBig - fixed) / ((int64_t)kWarps * p.stage_bytes));
   if (stages < 2)
-    return gb_fail(GB_EUNSUPPORTED, "tile of %d bytes leaves no room for a two-stage ring (fixed %lld bytes)",
+    return gb_fail(GB_EUNSUPPORTED, "task of %d bytes leaves no room for a two-stage ring (fixed %lld bytes)",
                    p.stage_bytes, (long long)fixed);
   p.stages = stages > kMaxStages ? kMaxStages : stages;
-  *smem_bytes = (size_t)(fixed + (int64_t)p.stages * p.stage_bytes);
+  *smem_bytes = (size_t)(fixed + (int64_t)kWarps * p.stages * p.stage_bytes);
   return GB_OK;
 }
 
@@ -571,8 +704,10 @@ void fill_weight(GemvParams& p, const gb_weight* w) {
 int gb_prepare_kernels() {
   for (int f = 0; f < kNumFmt; ++f)
     for (int moe = 0; moe < 2; ++moe)
-      GB_CUDA_OK(cudaFuncSetAttribute((const void*)pick_kernel(f, moe != 0),
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 4096));
+      for (int wide = 0; wide < 2; ++wide)
+        for (int lit = 0; lit < 2; ++lit)
+          GB_CUDA_OK(cudaFuncSetAttribute((const void*)pick_kernel(f, moe != 0, wide != 0, lit != 0),
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBig + 4096));
   return GB_OK;
 }
 
@@ -595,7 +730,8 @@ int gb_gemv(const void* x, int64_t M, const gb_weight* w, int act, int scale_rul
   const int sms = gb_sm_count();
   if (sms <= 0) return gb_fail(GB_ECUDA, "no usable CUDA device: %s", gb_last_error());
   int fmt;
-  rc = classify(w->fmt, &fmt);
+  bool wide;
+  rc = classify(w->fmt, &fmt, &wide);
   if (rc != GB_OK) return rc;
 
   GemvParams p = {};
@@ -605,7 +741,7 @@ int gb_gemv(const void* x, int64_t M, const gb_weight* w, int act, int scale_rul
   p.m_chunk = 16;
   p.status = gb_status_word();
   size_t smem = 0;
-  rc = plan(p, (int)M, false, &smem);
+  rc = plan(p, (int)M, false, sms, &smem);
   if (rc != GB_OK) return rc;
 
   const uint16_t* xin = (const uint16_t*)x;
@@ -634,12 +770,11 @@ int gb_gemv(const void* x, int64_t M, const gb_weight* w, int act, int scale_rul
   if (grid > tiles) grid = tiles;
   grid = (grid / p.ksplit) * p.ksplit;
   if (grid < p.ksplit) grid = p.ksplit;
-  pick_kernel(fmt, false)<<<grid, kThreads, smem, stream>>>(p);
+  pick_kernel(fmt, false, wide, literal_aligned(p))<<<grid, kThreads, smem, stream>>>(p);
   GB_LAUNCH_OK("gemv_kernel");
   if (p.ksplit > 1) {
     const int64_t total = M * w->rows;
-    gemv_finalize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-        p.ws, nullptr, p.global_scale, p.y, M, w->rows);
+    gemv_finalize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(p.ws, p.global_scale, p.y, total);
     GB_LAUNCH_OK("gemv_finalize_kernel");
   }
   return GB_OK;
@@ -664,7 +799,8 @@ int gb_moe_gemv(const void* x, const int32_t* x_row, const gb_weight* w, int64_t
   const int sms = gb_sm_count();
   if (sms <= 0) return gb_fail(GB_ECUDA, "no usable CUDA device: %s", gb_last_error());
   int fmt;
-  rc = classify(w->fmt, &fmt);
+  bool wide;
+  rc = classify(w->fmt, &fmt, &wide);
   if (rc != GB_OK) return rc;
 
   GemvParams p = {};
@@ -678,17 +814,18 @@ int gb_moe_gemv(const void* x, const int32_t* x_row, const gb_weight* w, int64_t
   p.swiglu = swiglu ? 1 : 0;
   p.y = (uint16_t*)y;
   p.status = gb_status_word();
-  // tokens per pass: sixteen when their rows fit the activation budget, else eight
+  // tokens per pass: as many (up to sixteen) as the activation budget holds
   const int64_t pitch = (w->K / 256) * 512 + 64;
-  int mc = 16;
-  if (16 * pitch > kXBudget) mc = 8;
-  if (8 * pitch > kXBudget + 32 * 1024)
+  int mc = (int)(kXBudget / pitch);
+  if (mc > 16) mc = 16;
+  if (P < mc) mc = (int)P;
+  if (mc < 1)
     return gb_fail(GB_EUNSUPPORTED, "K=%lld is too wide for the routed decode kernel", (long long)w->K);
   p.m_chunk = mc;
   size_t smem = 0;
-  rc = plan(p, mc, true, &smem);
+  rc = plan(p, mc, true, sms, &smem);
   if (rc != GB_OK) return rc;
-  pick_kernel(fmt, true)<<<sms, kThreads, smem, stream>>>(p);
+  pick_kernel(fmt, true, wide, literal_aligned(p))<<<sms, kThreads, smem, stream>>>(p);
   GB_LAUNCH_OK("gemv_kernel (routed)");
   return GB_OK;
 }

@@ -1,0 +1,183 @@
+"""Dense codebook Linear behind the plugin surface: ``create_weights`` /
+``process_weights_after_loading`` / ``apply`` (gridbook/linear.py:204-273,374-680,
+1025-1264), dispatching to the sm_100a kernels through the C ABI."""
+from __future__ import annotations
+
+import torch
+
+from . import _native, codec, kernels
+from ._native import NativeKernelUnavailableError
+from ._vllm_compat import (ChannelQuantScaleParameter, LinearMethodBase, ModelWeightParameter,
+                           register_weight_loader_v2_supported_method)
+from .formats import CBFormat
+
+DECODE_MAX_M = 16          # the decode-batch kernels take up to sixteen rows
+
+
+@register_weight_loader_v2_supported_method
+class PrismaQuantCBLinearMethod(LinearMethodBase):
+    """One CB target Linear (possibly a fused q/k/v or gate/up module whose roles carry
+    their own codebooks)."""
+
+    def __init__(self, quant_config, scheme: dict, prefix: str) -> None:
+        self.quant_config = quant_config
+        self.scheme = scheme
+        self.prefix = prefix
+        self.fmt = CBFormat.from_scheme(scheme)
+        self.is_fp4 = self.fmt.is_fp4
+        self.k = self.fmt.k
+        self.n_sub = self.fmt.n_sub
+        self.type_size = self.fmt.type_size
+        self.is_v2 = self.fmt.scale_coding == "v2"
+        sc = scheme.get("scale_coding")
+        self._sub_table = (sc.get("table") if isinstance(sc, dict) else None) or codec.TWO_TIER_SUB_TABLE
+        self.global_scale = float(scheme.get("weight_global_scale", 1.0))
+
+    # ------------------------------------------------------------------ parameters
+    def create_weights(self, layer, input_size_per_partition, output_partition_sizes, input_size,
+                       output_size, params_dtype, **extra_weight_attrs):
+        del input_size, output_size, params_dtype
+        weight_loader = extra_weight_attrs.get("weight_loader")
+        K = input_size_per_partition
+        if K % codec.SUPERBLOCK != 0:
+            raise ValueError(f"{self.prefix}: in_features {K} not a multiple of {codec.SUPERBLOCK}")
+        rows = sum(output_partition_sizes)
+        layer.logical_widths = list(output_partition_sizes)
+        layer._cb_input_size = K
+        layer.register_parameter("cb_qweight", ModelWeightParameter(
+            data=torch.empty(rows, self.fmt.row_bytes(K), dtype=torch.uint8),
+            input_dim=1, output_dim=0, weight_loader=weight_loader))
+        if not self.is_fp4:
+            layer.register_parameter("weight_scale", ChannelQuantScaleParameter(
+                data=torch.empty(rows, dtype=torch.float32), output_dim=0, weight_loader=weight_loader))
+
+    # ------------------------------------------------------------------ post-load prep
+    def _role_codebooks(self) -> list[list[torch.Tensor]]:
+        """Codebook tables of every role of this (possibly fused) module, in shard order."""
+        qc = self.quant_config
+        if qc is None:
+            raise NativeKernelUnavailableError(f"{self.prefix}: no quantization config to resolve codebooks")
+        return qc.codebooks_for_prefix(self.prefix, self.scheme)
+
+    def process_weights_after_loading(self, layer) -> None:
+        """Build what the kernels keep resident: flat codebook block(s), per-row codebook
+        offsets, the compose table, a packed buffer with tail slack, and the layer id.
+        Everything that can fail does so here, never at the first forward."""
+        _native.load(f"{self.prefix}: CB Linear")
+        qw = layer.cb_qweight.data
+        dev = qw.device
+        if not qw.is_cuda:
+            raise NativeKernelUnavailableError(
+                f"{self.prefix}: CB Linear weights must live on a CUDA device; there is no CPU path")
+        _native.prepare(dev)
+        N, K = qw.shape[0], layer._cb_input_size
+        roles = self._role_codebooks()
+        grid = self.fmt.grid
+        blocks = [codec.build_flat_codebook([t.to(torch.float32) for t in tabs],
+                                            prefix=self.prefix, grid=grid) for tabs in roles]
+        for b in blocks:
+            if b.numel() != self.fmt.codebook_elems():
+                raise ValueError(f"{self.prefix}: codebook has {b.numel()} entries, format "
+                                 f"{self.fmt} wants {self.fmt.codebook_elems()}")
+        widths = list(getattr(layer, "logical_widths", [N]))
+        cb_row_offset = None
+        if len(blocks) > 1:
+            if len(blocks) != len(widths) or sum(widths) != N:
+                raise ValueError(f"{self.prefix}: {len(blocks)} role codebooks for shard widths {widths}")
+            cb_row_offset = torch.repeat_interleave(
+                torch.arange(len(blocks), dtype=torch.int32) * self.fmt.codebook_elems(),
+                torch.tensor(widths)).to(torch.int32).to(dev)
+        flat = torch.cat(blocks)
+        cb_dev = (flat if self.is_fp4 else codec.flat_codebook_fp8(flat, self.prefix)).to(dev)
+        compose = codec.build_compose_table(self._sub_table).to(dev) if self.is_v2 else None
+        packed = codec.with_tail_slack(qw)
+        layer.cb_qweight.data = packed          # same bytes, slack-backed storage
+        ws = layer.weight_scale.data.float().contiguous() if not self.is_fp4 else None
+        layer._cb_weight = kernels.make_weight(packed, cb_dev, self.fmt, K, cb_row_offset=cb_row_offset,
+                                               compose=compose, weight_scale=ws,
+                                               global_scale=self.global_scale)
+        layer._cb_N, layer._cb_K = N, K
+        layer._cb_workspace = torch.empty(
+            _native.load().gb_gemv_workspace_bytes(DECODE_MAX_M, N, K), dtype=torch.uint8, device=dev)
+        from .ops import register_cb_layer
+        layer._cb_layer_id = register_cb_layer(self, layer)
+        layer._cb_route = {"kernel": "gemv_kernel", "format": str(self.fmt), "N": N, "K": K}
+
+    # ------------------------------------------------------------------ forward
+    def apply(self, layer, x, bias=None):
+        if bias is not None:
+            raise NativeKernelUnavailableError(f"{self.prefix}: biased CB Linear has no native operator")
+        lid = getattr(layer, "_cb_layer_id", None)
+        if lid is None:
+            raise NativeKernelUnavailableError(
+                f"{self.prefix}: CB Linear was not registered during process_weights_after_loading")
+        from .ops import cb_linear_forward
+        return cb_linear_forward(x, lid)
+
+    def _apply_inline(self, layer, x, bias=None):
+        from . import ops
+        w = layer._cb_weight
+        N, K = layer._cb_N, layer._cb_K
+        x2 = x.reshape(-1, K)
+        M = x2.shape[0]
+        if M == 0:
+            return x.new_empty((*x.shape[:-1], N))
+        if M <= DECODE_MAX_M:
+            return kernels.gemv(x2, w, act=self.fmt.grid, scale_rule=ops.ACT_SCALE_RULE,
+                                workspace=layer._cb_workspace).reshape(*x.shape[:-1], N)
+        return self._apply_prefill(layer, x2).reshape(*x.shape[:-1], N)
+
+    def _apply_prefill(self, layer, x2):
+        """M > 16: bucket the activations, expand the layer once into a transient tile and
+        run one dense GEMM over it (the reference's default route,
+        gridbook/linear.py:983-1023,1146-1152,1255-1264)."""
+        from . import ops
+        w = layer._cb_weight
+        if self.is_fp4:
+            xq = kernels.fp4_act_qdq(x2.contiguous(), ops.ACT_SCALE_RULE)
+            wt = kernels.expand_fp4_bf16(w)
+        else:
+            xq = kernels.fp8_act_qdq(x2.contiguous(), ops.ACT_SCALE_RULE)
+            wt = (kernels.expand_fp8(w).to(torch.float32) * w.weight_scale[:, None]).to(torch.bfloat16)
+        y = torch.matmul(xq, wt.t())
+        if w.global_scale != 1.0:
+            y = (y.float() * w.global_scale).to(torch.bfloat16)
+        return y
+
+
+class CBLinear(torch.nn.Module):
+    """Stand-alone module that drives PrismaQuantCBLinearMethod exactly as an engine does:
+    create_weights -> copy the checkpoint tensors in -> process_weights_after_loading ->
+    apply.  Used by the tests, the benchmark and anyone without an engine."""
+
+    def __init__(self, fmt: CBFormat, in_features: int, out_partition_sizes, codebooks, *,
+                 global_scale: float = 1.0, prefix: str = "cb_linear"):
+        super().__init__()
+        scheme = {"grid": fmt.grid, "mode": fmt.mode, "k": fmt.k, "n_sub": fmt.n_sub,
+                  "type_size": fmt.type_size, "weight_global_scale": global_scale}
+        if fmt.scale_coding == "v2":
+            scheme["scale_coding"] = {"kind": "two_tier", "table": list(codec.TWO_TIER_SUB_TABLE)}
+        self.method = PrismaQuantCBLinearMethod(_InlineCodebooks(codebooks), scheme, prefix)
+        sizes = list(out_partition_sizes)
+        self.method.create_weights(self, in_features, sizes, in_features, sum(sizes), torch.bfloat16)
+
+    def load(self, qw: torch.Tensor, weight_scale: torch.Tensor | None = None, device="cuda"):
+        self.cb_qweight.data = qw.to(device)
+        if weight_scale is not None:
+            self.weight_scale.data = weight_scale.to(device)
+        self.method.process_weights_after_loading(self)
+        return self
+
+    def forward(self, x):
+        return self.method.apply(self, x)
+
+
+class _InlineCodebooks:
+    """Minimal codebook provider: ``roles`` is a list (one entry per fused role) of lists of
+    tables.  Stands in for PrismaQuantConfig.codebooks_for_prefix."""
+
+    def __init__(self, roles):
+        self.roles = roles
+
+    def codebooks_for_prefix(self, prefix, scheme):
+        return self.roles

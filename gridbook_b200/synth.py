@@ -179,3 +179,35 @@ def to_device_weight(d: dict, device, pad_rows: bool = False):
 def bf16_tensor(x: np.ndarray, device):
     import torch
     return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).to(torch.bfloat16).to(device)
+
+
+# ---- device-side generation (large stacks) ------------------------------------------
+def make_packed_device(fmt: CBFormat, rows: int, K: int, gen, device, super_span: int = 4):
+    """Same distributions as make_packed, drawn on the device by a seeded torch generator
+    (GiB-sized stacks take seconds on the host RNG)."""
+    import torch
+    n_sb = K // 256
+    blk = torch.empty((rows, n_sb, fmt.type_size), dtype=torch.uint8, device=device)
+    blk[:, :, :4 * fmt.k] = torch.randint(0, 256, (rows, n_sb, 4 * fmt.k), generator=gen,
+                                          dtype=torch.uint8, device=device)
+    if fmt.is_fp4 and fmt.scale_coding == "v1":
+        u = torch.rand((rows, n_sb, 16), generator=gen, device=device) * 6.0 - 4.0
+        blk[:, :, 4 * fmt.k:] = torch.exp2(u).to(torch.float8_e4m3fn).view(torch.uint8)
+    elif fmt.is_fp4:
+        sup = torch.from_numpy(legal_supers(super_span)).to(device)
+        pick = torch.randint(0, sup.numel(), (rows, n_sb), generator=gen, device=device)
+        blk[:, :, 4 * fmt.k] = sup[pick].to(torch.uint8)
+        blk[:, :, 4 * fmt.k + 1:] = torch.randint(0, 256, (rows, n_sb, 8), generator=gen,
+                                                  dtype=torch.uint8, device=device)
+    return blk.reshape(rows, n_sb * fmt.type_size)
+
+
+def codebook_tables(fmt: CBFormat, seed: int):
+    """Codebook tables [(rows, dims) fp32 tensors] of one format, on the host."""
+    import torch
+    flat = make_codebook(fmt, np.random.default_rng(seed))
+    out, pos = [], 0
+    for r, d in fmt.table_shapes():
+        out.append(torch.from_numpy(flat[pos:pos + r * d].reshape(r, d).copy()))
+        pos += r * d
+    return out
