@@ -57,6 +57,8 @@ struct GemvParams {
   int x_pitch;            // bytes between activation rows in shared memory
   int x_rows;             // activation rows staged (1..16); MMA rows beyond them are zero
   int lut_bytes;
+  int lut_rep;            // copies of each 16-byte table entry (1 or 8): lane l reads copy l % 8, so the
+                          // eight lanes of a quarter-warp never collide on a bank
   // outputs
   uint16_t* y;
   float* ws;              // [M, N] fp32 partial sums when ksplit > 1
@@ -163,6 +165,17 @@ GB_DEVINL uint4 lds_v4(uint32_t a) {
   return v;
 }
 
+// 16-byte shared load that only lanes with `live` perform; the others get zeros and cost
+// no shared-memory bandwidth.
+GB_DEVINL uint4 lds_v4_if(uint32_t a, bool live) {
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  asm volatile(
+      "{ .reg .pred q; setp.ne.u32 q, %5, 0; @q ld.shared.v4.u32 {%0,%1,%2,%3}, [%4]; }"
+      : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+      : "r"(a), "r"((uint32_t)live));
+  return v;
+}
+
 GB_DEVINL uint32_t mul_bf16x2(uint32_t a, uint32_t s2) {
   uint32_t d;
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(s2));
@@ -175,6 +188,7 @@ struct LaneDecode {
   uint32_t kstep;              // stream bits between this lane's consecutive codewords (4 codewords)
   uint32_t mask[4], shift[4], lbase[4];   // product split: index masks, shifts, table byte offsets
   uint32_t scale_off;          // byte offset of the scale plane inside a superblock
+  uint32_t ent_shift, rep_off; // 16-byte-entry tables: log2 of the entry pitch, this lane's replica offset
 };
 
 // Codeword bits at stream bit `bit` of the superblock at shared address sbp (any alignment).
@@ -195,11 +209,11 @@ GB_DEVINL void fetch_code(uint32_t sbp, uint32_t bit, uint32_t& lo, uint32_t& hi
 template <int kFmt, bool kWide>
 GB_DEVINL void expand_code(const LaneDecode& d, uint32_t lut, uint32_t lo, uint32_t hi, uint32_t (&w)[4]) {
   if constexpr (kFmt == kFp4Full) {
-    const uint4 v = lds_v4(lut + ((lo & d.mask[0]) << 4));
+    const uint4 v = lds_v4(lut + ((lo & d.mask[0]) << d.ent_shift) + d.rep_off);
     w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
   } else if constexpr (kFmt == kFp4Signed) {
     const uint32_t code = lo & d.mask[0];
-    const uint4 v = lds_v4(lut + ((code >> 8) << 4));
+    const uint4 v = lds_v4(lut + ((code >> 8) << d.ent_shift) + d.rep_off);
     // sign bit j flips coordinate j: bit 15 of the low half, bit 31 of the high half
     w[0] = v.x ^ ((code & 1u) << 15) ^ ((code & 2u) << 30);
     w[1] = v.y ^ ((code & 4u) << 13) ^ ((code & 8u) << 28);
@@ -320,9 +334,18 @@ GB_DEVINL void stage_lut(const GemvParams& p, uint8_t* lut, int64_t cb_off, int 
   } else {
     const uint16_t* src = reinterpret_cast<const uint16_t*>(p.codebook) + cb_off;
     const uint32_t bias = p.fmt.scale_coding == GB_SCALE_V1 ? kExpBias120 : 0u;
-    for (int i = tid; i < p.cb_elems; i += nthreads) {
-      const uint32_t b = src[i];
-      dst[i] = (uint16_t)((b & 0x7FFFu) ? b + bias : b);
+    if (p.lut_rep > 1) {
+      // entry e (eight values) -> eight copies at (e * 8 + r) * 16 bytes
+      for (int i = tid; i < p.cb_elems * 8; i += nthreads) {
+        const int e = i >> 6, r = (i >> 3) & 7, j = i & 7;
+        const uint32_t b = src[e * 8 + j];
+        dst[(e * 8 + r) * 8 + j] = (uint16_t)((b & 0x7FFFu) ? b + bias : b);
+      }
+    } else {
+      for (int i = tid; i < p.cb_elems; i += nthreads) {
+        const uint32_t b = src[i];
+        dst[i] = (uint16_t)((b & 0x7FFFu) ? b + bias : b);
+      }
     }
   }
 }
@@ -373,6 +396,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     d.bit0 = (uint32_t)t4 * (uint32_t)p.fmt.k_bits;
     d.kstep = 4u * (uint32_t)p.fmt.k_bits;
     d.scale_off = 4u * p.fmt.k_bits;
+    d.ent_shift = p.lut_rep > 1 ? 7u : 4u;
+    d.rep_off = p.lut_rep > 1 ? ((uint32_t)lane & 7u) << 4 : 0u;
     const bool product = p.fmt.mode == GB_MODE_PRODUCT;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -453,7 +478,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
 
     // A wait that runs out raises the status word and carries on (the output is then
     // garbage, and flagged): leaving here would strand the other warps at a CTA barrier.
+#ifndef GB_EXP_NO_TMA
     if (!gb_mbar_wait(&my_bar[s], (it / p.stages) & 1)) atomicExch(p.status, 2);
+#endif
     uint32_t sbp = ring_s + (uint32_t)s * (uint32_t)p.stage_bytes + (uint32_t)g * (uint32_t)p.row_pitch +
                    (row_ok ? (uint32_t)((uintptr_t)my_src & 15u) : 0u);
     const uint32_t warp_head = __shfl_sync(0xffffffffu, (uint32_t)((uintptr_t)my_src & 15u), 0);
@@ -464,7 +491,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     }
 
     float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
-    float accx[6][4] = {};     // more independent accumulation chains: the MMA result latency is long
     // Lanes whose MMA row has no activation row this pass read a zeroed strip instead, and
     // lanes whose weight row lies past the edge decode the task's first row (their results
     // are never stored): the loop below is branch-free.
@@ -476,77 +502,99 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     if (!row_ok) sbp = ring_s + (uint32_t)s * (uint32_t)p.stage_bytes + warp_head;
 
     if (uniform) {
-#ifdef GB_EXP_NO_COMPUTE
-      for (int sb = 0; sb < 0; ++sb, sbp += ts, xa_s += xa_step, xb_s += xb_step) {
-#else
+      // Software-pipelined by superblock: all shared-memory reads of a superblock (codes,
+      // table entries, scales, activations) are issued together, so a warp pays one
+      // shared-memory round trip per 256 weights instead of one per 32.
+      const bool hi_any = t.mcount > 8;          // uniform: any activation row in MMA rows 8..15
       for (int sb = 0; sb < nsb; ++sb, sbp += ts, xa_s += xa_step, xb_s += xb_step) {
-#endif
-        uint4 iw0, iw1, sw;                       // literal layout: index bytes and scale bytes
-        uint32_t super_bits = 0;
+        uint32_t w[8][4], s2[8];
+        uint4 xa[8];
         if constexpr (kLit) {
-          iw0 = lds_v4(sbp); iw1 = lds_v4(sbp + 16); sw = lds_v4(sbp + 32);
-        } else if constexpr (!fp8) {
-          if (!v1) super_bits = (lds_u8(sbp + d.scale_off) - 127u) << 7;   // two-tier exponent, once
+          const uint4 iw0 = lds_v4(sbp), iw1 = lds_v4(sbp + 16), sw = lds_v4(sbp + 32);
+          const uint32_t iw[8] = {iw0.x, iw0.y, iw0.z, iw0.w, iw1.x, iw1.y, iw1.z, iw1.w};
+          const uint32_t scw[4] = {sw.x, sw.y, sw.z, sw.w};
+#pragma unroll
+          for (int kb = 0; kb < 8; ++kb) {
+#ifdef GB_EXP_NO_LUT
+            const uint32_t cc = __byte_perm(iw[kb], 0u, sel_idx);
+            const uint4 v = make_uint4(0x3F803F80u + cc, 0x3F803F80u, 0x3F803F80u ^ cc, 0x3F803F80u);
+#else
+            const uint4 v = lds_v4(lut_s + (__byte_perm(iw[kb], 0u, sel_idx) << d.ent_shift) + d.rep_off);
+#endif
+            w[kb][0] = v.x; w[kb][1] = v.y; w[kb][2] = v.z; w[kb][3] = v.w;
+          }
+#pragma unroll
+#ifdef GB_EXP_NO_X
+          for (int kb = 0; kb < 8; ++kb) xa[kb] = make_uint4(xa_s + kb, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
+#else
+          for (int kb = 0; kb < 8; ++kb) xa[kb] = lds_v4_if(xa_s + kb * 64, lo_live);
+#endif
+#pragma unroll
+          for (int kb = 0; kb < 8; ++kb) {
+            const uint32_t b2 = __byte_perm(scw[kb >> 1], 0u, (kb & 1) ? sel_sc_odd : sel_sc_even);
+            s2[kb] = ((b2 & 0x007F007Fu) << 4) | ((b2 & 0x00800080u) << 8);      // scale * 2^-120, both halves
+          }
+        } else {
+          uint32_t lo[8], hi[8], sraw[8];
+          uint32_t super_bits = 0;
+#pragma unroll
+          for (int kb = 0; kb < 8; ++kb) fetch_code<kWide>(sbp, d.bit0 + kb * d.kstep, lo[kb], hi[kb]);
+          if constexpr (!fp8) {
+            // group (4 kb + t4) / 2 = 2 kb + (t4 >> 1)
+            if (v1) {
+#pragma unroll
+              for (int kb = 0; kb < 8; ++kb) sraw[kb] = lds_u8(sbp + d.scale_off + 2u * kb + ((uint32_t)t4 >> 1));
+            } else {
+              super_bits = (lds_u8(sbp + d.scale_off) - 127u) << 7;               // two-tier exponent, once
+#pragma unroll
+              for (int kb = 0; kb < 8; ++kb) sraw[kb] = lds_u8(sbp + d.scale_off + 1u + kb);   // groups 2kb, 2kb+1
+            }
+          }
+#pragma unroll
+          for (int kb = 0; kb < 8; ++kb) expand_code<kFmt, kWide>(d, lut_s, lo[kb], hi[kb], w[kb]);
+#pragma unroll
+          for (int kb = 0; kb < 8; ++kb) xa[kb] = lds_v4_if(xa_s + kb * 64, lo_live);
+          if constexpr (!fp8) {
+            if (v1) {
+#pragma unroll
+              for (int kb = 0; kb < 8; ++kb)
+                s2[kb] = (((sraw[kb] & 0x7Fu) << 4) | ((sraw[kb] & 0x80u) << 8)) * 0x10001u;   // scale * 2^-120
+            } else {
+              uint32_t tb[8];
+#pragma unroll
+              for (int kb = 0; kb < 8; ++kb)
+                tb[kb] = lds_u16(sub_s + ((sraw[kb] >> (((uint32_t)t4 >> 1) * 4u)) & 0xFu) * 2u);
+#pragma unroll
+              for (int kb = 0; kb < 8; ++kb) s2[kb] = ((tb[kb] + super_bits) & 0xFFFFu) * 0x10001u;   // T[c] 2^(E-127)
+            }
+          }
         }
 #pragma unroll
         for (int kb = 0; kb < 8; ++kb) {
-          // k-block kb = weights [32 kb, 32 kb + 32): this lane expands codeword 4 kb + t4
-          const uint4 xa = lds_v4(xa_s + kb * 64);
-          const uint4 xb = lds_v4(xb_s + kb * 64);
-          uint32_t w[4];
-          if constexpr (kLit) {
-            const uint32_t iw = kb == 0 ? iw0.x : kb == 1 ? iw0.y : kb == 2 ? iw0.z : kb == 3 ? iw0.w
-                              : kb == 4 ? iw1.x : kb == 5 ? iw1.y : kb == 6 ? iw1.z : iw1.w;
-            const uint32_t code = __byte_perm(iw, 0u, sel_idx);
-            const uint4 v = lds_v4(lut_s + (code << 4));
-            w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
-            const uint32_t scw = (kb >> 1) == 0 ? sw.x : (kb >> 1) == 1 ? sw.y : (kb >> 1) == 2 ? sw.z : sw.w;
-            const uint32_t b2 = __byte_perm(scw, 0u, (kb & 1) ? sel_sc_odd : sel_sc_even);   // byte in both halves
-            const uint32_t s2 = ((b2 & 0x007F007Fu) << 4) | ((b2 & 0x00800080u) << 8);       // scale * 2^-120
+          // k-block kb = weights [32 kb, 32 kb + 32): this lane holds codeword 4 kb + t4
+          if constexpr (fp8) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) w[j] = mul_bf16x2(w[j], s2);
-          } else {
-            uint32_t lo, hi;
-            fetch_code<kWide>(sbp, d.bit0 + kb * d.kstep, lo, hi);
-            expand_code<kFmt, kWide>(d, lut_s, lo, hi, w);
-            if constexpr (fp8) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float flo = __uint_as_float(w[j] << 16) * row_scale;
-                const float fhi = __uint_as_float(w[j] & 0xFFFF0000u) * row_scale;
-                asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[j]) : "f"(fhi), "f"(flo));
-              }
-            } else {
-              // group (4 kb + t4) / 2 = 2 kb + (t4 >> 1); its scale as a packed bf16 pair
-              const uint32_t grp = 2u * kb + ((uint32_t)t4 >> 1);
-              uint32_t sbits;
-              if (v1) {
-                const uint32_t b = lds_u8(sbp + d.scale_off + grp);
-                sbits = ((b & 0x7Fu) << 4) | ((b & 0x80u) << 8);                 // scale * 2^-120
-              } else {
-                const uint32_t nib = (lds_u8(sbp + d.scale_off + 1u + (grp >> 1)) >> ((grp & 1u) * 4u)) & 0xFu;
-                sbits = (lds_u16(sub_s + nib * 2u) + super_bits) & 0xFFFFu;      // T[c] * 2^(E-127)
-              }
-              const uint32_t s2 = sbits * 0x10001u;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) w[j] = mul_bf16x2(w[j], s2);
+            for (int j = 0; j < 4; ++j) {
+              const float flo = __uint_as_float(w[kb][j] << 16) * row_scale;
+              const float fhi = __uint_as_float(w[kb][j] & 0xFFFF0000u) * row_scale;
+              asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[kb][j]) : "f"(fhi), "f"(flo));
             }
-          }
-          const uint32_t a0[4] = {xa.x, xb.x, xa.y, xb.y};
-          const uint32_t a1[4] = {xa.z, xb.z, xa.w, xb.w};
-          if ((kb & 3) == 0) {
-            gb_mma_bf16_16816(acc0, a0, w[0], w[1]);
-            gb_mma_bf16_16816(acc1, a1, w[2], w[3]);
           } else {
-            gb_mma_bf16_16816(accx[2 * (kb & 3) - 2], a0, w[0], w[1]);
-            gb_mma_bf16_16816(accx[2 * (kb & 3) - 1], a1, w[2], w[3]);
-          }
-        }
-      }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        acc0[i] += accx[0][i] + accx[2][i] + accx[4][i];
-        acc1[i] += accx[1][i] + accx[3][i] + accx[5][i];
+            for (int j = 0; j < 4; ++j) w[kb][j] = mul_bf16x2(w[kb][j], s2[kb]);
+          }
+          uint4 xb = make_uint4(0, 0, 0, 0);
+          if (hi_any) xb = lds_v4_if(xb_s + kb * 64, hi_live);
+          const uint32_t a0[4] = {xa[kb].x, xb.x, xa[kb].y, xb.y};
+          const uint32_t a1[4] = {xa[kb].z, xb.z, xa[kb].w, xb.w};
+#ifdef GB_EXP_NO_MMA
+          acc0[0] += __uint_as_float((a0[0] ^ a0[2] ^ w[kb][0] ^ w[kb][1]) & 0x3FFFFFFFu);
+          acc1[0] += __uint_as_float((a1[0] ^ a1[2] ^ w[kb][2] ^ w[kb][3]) & 0x3FFFFFFFu);
+#else
+          gb_mma_bf16_16816(acc0, a0, w[kb][0], w[kb][1]);
+          gb_mma_bf16_16816(acc1, a1, w[kb][2], w[kb][3]);
+#endif
+        }
       }
     } else {
       mixed_codebook_task<fp8>(p, d, sbp, nsb, my_cb_off, row_scale, xa_s, xb_s, xa_step, xb_step, sub_s, t4,
@@ -555,7 +603,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     // ---- the stage is free: refill it with the task kMaxStages ahead ----
     __syncwarp();
     more = more && ahead.next(ta);
+#ifndef GB_EXP_NO_TMA
     if (more) issue_task(p, ta, warp, lane, my_ring + (size_t)s * p.stage_bytes, &my_bar[s]);
+#endif
 
     // ---- results: lane (g, t4) holds C[m = g (+8)][n = 2 t4 (+1)], n = row inside the task ----
     float c[4];
@@ -650,7 +700,10 @@ int plan(GemvParams& p, int m_rows, bool moe, int sms, size_t* smem_bytes) {
   p.n_sb = (int)(p.K / 256);
   p.split = gb_make_split(p.fmt.k_bits, p.fmt.mode == GB_MODE_PRODUCT ? p.fmt.n_sub : 1);
   p.cb_elems = (int)gb_codebook_elems(p.fmt);
-  p.lut_bytes = (p.cb_elems * 2 + 127) & ~127;
+  // Replicating 16-byte entries eight times removes the table's bank conflicts but costs 32 KB of
+  // staging per CTA; measured a loss on every layer but the largest, so it stays off.
+  p.lut_rep = 1;
+  p.lut_bytes = (p.cb_elems * 2 * p.lut_rep + 127) & ~127;
   if (p.lut_bytes > 72 * 1024)
     return gb_fail(GB_EUNSUPPORTED, "codebook of %d entries does not fit the shared-memory table", p.cb_elems);
   p.x_rows = m_rows;
