@@ -19,7 +19,7 @@ REQUIRED_SYMBOLS = (
     "gb_abi_version", "gb_last_error", "gb_prepare", "gb_device_status",
     "gb_fp8_act_qdq", "gb_fp4_act_qdq",
     "gb_expand_fp8", "gb_expand_fp4_bf16", "gb_expand_fp4_nvfp4",
-    "gb_gemv_workspace_bytes", "gb_gemv",
+    "gb_gemv_workspace_bytes", "gb_gemv", "gb_gemv_static",
     "gb_moe_route", "gb_moe_gemv_workspace_bytes", "gb_moe_gemv", "gb_moe_combine",
 )
 
@@ -79,6 +79,7 @@ def _declare(lib) -> None:
     lib.gb_gemv_workspace_bytes.argtypes = [i64, i64, i64]
     lib.gb_gemv_workspace_bytes.restype = i64
     lib.gb_gemv.argtypes = [vp, i64, wp, i32, i32, vp, vp, i64, vp]
+    lib.gb_gemv_static.argtypes = [vp, i64, wp, i32, i32, vp, vp]
     lib.gb_moe_route.argtypes = [vp, i64, i64, i64, vp, vp, vp, vp]
     lib.gb_moe_gemv_workspace_bytes.argtypes = [i64, i64]
     lib.gb_moe_gemv_workspace_bytes.restype = i64

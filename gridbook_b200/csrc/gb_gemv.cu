@@ -13,6 +13,8 @@
 // rows or a warp's rows would not fit) add into an fp32 workspace instead.
 #include "gb_common.cuh"
 
+#include <mutex>
+
 namespace {
 
 constexpr int kWarps = 8;
@@ -884,3 +886,47 @@ int gb_moe_gemv(const void* x, const int32_t* x_row, const gb_weight* w, int64_t
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// gb_gemv_static: the decode-batch linear for callers that must not allocate.
+// ---------------------------------------------------------------------------
+// Its scratch (bucketed activations + fp32 partial sums of a K-sliced launch) lives in
+// this file-scope device array instead of a caller-provided workspace.  Every device that
+// loads the library carries the array until the process exits.
+__device__ __align__(256) static unsigned char g_gemv_static_scratch[GB_GEMV_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_mutex;
+void* g_static_ptr[64] = {nullptr};   // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" int gb_gemv_static(const void* x, int64_t M, const gb_weight* w, int act, int scale_rule,
+                              void* y, void* stream) {
+  GB_REQUIRE(w != nullptr, "null weight descriptor");
+  GB_REQUIRE(M >= 1 && M <= 16, "decode-batch kernel takes 1..16 rows, got M=%lld", (long long)M);
+  const int64_t need = gb_gemv_workspace_bytes(M, w->rows, w->K);
+  GB_REQUIRE(need <= (int64_t)GB_GEMV_STATIC_SCRATCH_BYTES,
+             "gb_gemv_static: M=%lld N=%lld K=%lld needs %lld bytes of scratch, the built-in array holds %lld; "
+             "use gb_gemv with a caller-owned workspace for this shape",
+             (long long)M, (long long)w->rows, (long long)w->K, (long long)need,
+             (long long)GB_GEMV_STATIC_SCRATCH_BYTES);
+  int dev = -1;
+  GB_CUDA_OK(cudaGetDevice(&dev));
+  GB_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
+  void* scratch = g_static_ptr[dev];
+  if (scratch == nullptr) {
+    // Once per device, with that device current.  In host code the array's name is only a
+    // handle: the address a kernel may use has to be asked for.
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      GB_CUDA_OK(cudaGetSymbolAddress(&p, g_gemv_static_scratch));
+      g_static_ptr[dev] = p;
+    }
+    scratch = g_static_ptr[dev];
+  }
+  // gb_gemv overwrites the activation part and clears the partial sums it uses (an async
+  // memset on the caller's stream, not an allocation) before the kernel adds into them.
+  return gb_gemv(x, M, w, act, scale_rule, y, scratch, (int64_t)GB_GEMV_STATIC_SCRATCH_BYTES, stream);
+}
+

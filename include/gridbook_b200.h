@@ -111,6 +111,25 @@ GB_API int64_t gb_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K);
 GB_API int gb_gemv(const void* x_bf16, int64_t M, const gb_weight* w, int act, int scale_rule,
             void* y_bf16, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Same computation as gb_gemv for callers that are not allowed to allocate device memory
+ * and have no workspace to hand over: a runtime that has already given every byte of the
+ * device to its own pools, a serving loop whose allocator is frozen once graphs are being
+ * recorded, or a host binding whose ABI simply has no place for a scratch buffer.  The
+ * scratch is a fixed array of GB_GEMV_STATIC_SCRATCH_BYTES inside the library, resident on
+ * every device that loads it for the life of the process.
+ *   - Shapes whose scratch (gb_gemv_workspace_bytes) exceeds the array are refused with
+ *     GB_EINVAL and a message naming both sizes; use gb_gemv for those.
+ *   - The first call on a device looks up the array's device address; make that call during
+ *     set-up, before any stream capture starts on that device.
+ *   - All calls share the one array, which keeps whatever the previous call left; the part
+ *     that must start from zero is cleared on the caller's stream every time.  Two calls that
+ *     may overlap on the GPU (different streams, no dependency) race on it: serialise them.
+ *   - No cudaMalloc, cudaFree or allocating library routine is called.
+ * This entry point has no counterpart in the reference. */
+#define GB_GEMV_STATIC_SCRATCH_BYTES (4u << 20)
+GB_API int gb_gemv_static(const void* x_bf16, int64_t M, const gb_weight* w, int act, int scale_rule,
+                          void* y_bf16, void* stream);
+
 /* ---- routed MoE -------------------------------------------------------------- */
 /* Device-side histogram + exclusive scan + stable expert-major permutation of the
  * P = T*topk routed pairs; replaces the torch chain of gridbook/moe.py:1609-1625 and
