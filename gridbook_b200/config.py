@@ -1,0 +1,204 @@
+"""``PrismaQuantConfig`` — the quantization config vLLM instantiates for
+``quant_method: gridbook`` (gridbook/config.py:484-531,803-957,1042-1106,1129-1204,
+1422-1571,1605-1641).  Core paths only: pointer/inline resolution, target -> scheme map,
+fused-shard roles, codebook sidecar, per-prefix method dispatch."""
+from __future__ import annotations
+
+import json
+import os
+
+import torch
+
+from ._native import NativeKernelUnavailableError
+from ._vllm_compat import HAVE_VLLM, QuantizationConfig
+
+# fused module -> the checkpoint's per-role Linears, in shard order
+DEFAULT_PACKED_MODULES = {
+    "qkv_proj": ["q_proj", "k_proj", "v_proj"],
+    "gate_up_proj": ["gate_proj", "up_proj"],
+}
+_MOE_SUFFIXES = (".experts", ".mlp.experts", ".ffn.experts")
+
+
+class PrismaQuantConfig(QuantizationConfig):
+    """Holds the raw ``quantization_config`` and resolves it lazily (the sidecar files are
+    read on first use, gridbook/config.py:803-957)."""
+
+    def __init__(self, raw: dict, model_dir: str | None = None) -> None:
+        super().__init__()
+        self.raw = dict(raw)
+        self.model_dir = model_dir or self.raw.get("_model_dir")
+        self.packed_modules_mapping = dict(DEFAULT_PACKED_MODULES)
+        self._resolved = False
+        self.target_scheme: dict[str, dict] = {}
+        self.ignore: list[str] = []
+        self._codebooks: dict[str, torch.Tensor] | None = None
+
+    # ---- vLLM QuantizationConfig surface (gridbook/config.py:1042-1074) -------------
+    @classmethod
+    def get_name(cls) -> str:
+        return "gridbook"
+
+    @classmethod
+    def get_supported_act_dtypes(cls):
+        return [torch.bfloat16]
+
+    @classmethod
+    def get_min_capability(cls) -> int:
+        return 100                      # sm_100a only (the reference says 80)
+
+    @classmethod
+    def get_config_filenames(cls):
+        return []
+
+    @classmethod
+    def from_config(cls, config: dict) -> "PrismaQuantConfig":
+        return cls(config)
+
+    @classmethod
+    def override_quantization_method(cls, hf_quant_cfg, user_quant):
+        method = (hf_quant_cfg or {}).get("quant_method")
+        return "gridbook" if method in ("gridbook", "prismaquant") else None
+
+    def apply_vllm_mapper(self, hf_to_vllm_mapper) -> None:
+        self._ensure_resolved()
+        if hasattr(hf_to_vllm_mapper, "apply_dict"):
+            self.target_scheme = hf_to_vllm_mapper.apply_dict(self.target_scheme)
+
+    # ---- resolution -------------------------------------------------------------------
+    def _ensure_resolved(self) -> None:
+        if self._resolved:
+            return
+        full = self.raw
+        if "config_groups" not in full:                          # pointer stub (docs/SPEC.md:388-399)
+            if self.model_dir is None:
+                raise ValueError("[prismaquant] pointer-style quantization_config needs the model directory")
+            path = os.path.join(self.model_dir, full.get("config_file", "quant_config.json"))
+            with open(path) as fh:
+                full = json.load(fh)
+        for gname, group in full.get("config_groups", {}).items():
+            scheme = dict(group["scheme"])
+            if "scale_coding" not in scheme and full.get("layout_version") == 2 and scheme.get("grid") == "fp4":
+                scheme["scale_coding"] = {"kind": "two_tier"}
+            scheme.setdefault("_group", gname)
+            for target in group.get("targets", []):
+                self.target_scheme[target] = scheme
+        self.ignore = list(full.get("ignore", []))
+        self.codebook_file = full.get("codebook_file", self.raw.get("codebook_file", "cb_codebooks.pqcb"))
+        self._resolved = True
+
+    def get_codebooks(self) -> dict[str, torch.Tensor]:
+        """The codebook sidecar (a safetensors file, docs/SPEC.md:303-378), loaded once."""
+        if self._codebooks is None:
+            self._ensure_resolved()
+            inline = self.raw.get("_codebooks")
+            if inline is not None:
+                self._codebooks = dict(inline)
+            else:
+                from safetensors.torch import load_file
+                self._codebooks = load_file(os.path.join(self.model_dir, self.codebook_file))
+        return self._codebooks
+
+    def _tables(self, scheme: dict) -> list[torch.Tensor]:
+        ref = scheme["codebook_ref"]
+        names = ref if isinstance(ref, (list, tuple)) else [ref]
+        books = self.get_codebooks()
+        missing = [n for n in names if n not in books]
+        if missing:
+            raise KeyError(f"[prismaquant] codebook tensors {missing} are not in the sidecar")
+        return [books[n] for n in names]
+
+    # ---- fused shards (gridbook/config.py:1129-1204) ----------------------------------
+    def shard_target_keys(self, prefix: str, unfused_fallback: bool = False) -> list[str]:
+        self._ensure_resolved()
+        head, _, leaf = prefix.rpartition(".")
+        roles = self.packed_modules_mapping.get(leaf)
+        if roles:
+            keys = [f"{head}.{r}" if head else r for r in roles]
+            found = [k for k in keys if self._lookup(k) is not None]
+            if found and len(found) != len(keys):
+                raise ValueError(f"[prismaquant] {prefix}: only {found} of {keys} are CB targets; mixed "
+                                 "fused modules are not served")
+            if found:
+                return keys
+        if self._lookup(prefix) is not None or unfused_fallback:
+            return [prefix]
+        return []
+
+    def _lookup(self, key: str) -> dict | None:
+        if key in self.target_scheme:
+            return self.target_scheme[key]
+        for stored, scheme in self.target_scheme.items():       # class wrappers: language_model.model.* etc.
+            if key.endswith("." + stored) or stored.endswith("." + key):
+                return scheme
+        return None
+
+    def _scheme_for_prefix(self, prefix: str) -> dict | None:
+        keys = self.shard_target_keys(prefix)
+        if not keys:
+            return None
+        schemes = [self._lookup(k) for k in keys]
+        first = schemes[0]
+        fields = ("grid", "mode", "k", "n_sub", "type_size")
+        for other in schemes[1:]:
+            if any(other.get(f) != first.get(f) for f in fields):
+                raise ValueError(f"[prismaquant] {prefix}: fused roles use different formats; one method "
+                                 "cannot serve them")
+        return first
+
+    def codebooks_for_prefix(self, prefix: str, scheme: dict) -> list[list[torch.Tensor]]:
+        """Tables of every role of ``prefix`` in shard order (one entry for a plain Linear or a
+        routed stack).  Roles that share one ``codebook_ref`` collapse to a single entry."""
+        base = prefix
+        for tail in (".w13", ".w2"):
+            if prefix.endswith(tail):
+                return [self._tables(scheme)]
+        keys = self.shard_target_keys(base, unfused_fallback=True)
+        schemes = [self._lookup(k) or scheme for k in keys]
+        refs = [json.dumps(s["codebook_ref"]) for s in schemes]
+        if len(set(refs)) == 1:
+            return [self._tables(schemes[0])]
+        return [self._tables(s) for s in schemes]
+
+    def _moe_scheme_for_prefix(self, prefix: str):
+        """(gate_up scheme, down scheme) of a routed stack, or None
+        (gridbook/config.py:1605-1641).  Unlike the reference, the two projections may differ."""
+        self._ensure_resolved()
+        up = self._lookup(f"{prefix}.gate_up_proj")
+        down = self._lookup(f"{prefix}.down_proj")
+        if up is None and down is None:
+            return None
+        if up is None or down is None:
+            raise ValueError(f"[prismaquant] {prefix}: only one of gate_up_proj / down_proj is a CB target")
+        return up, down
+
+    # ---- dispatch (gridbook/config.py:1422-1571) --------------------------------------
+    def get_quant_method(self, layer, prefix: str):
+        self._ensure_resolved()
+        if any(prefix == ig or prefix.startswith(ig + ".") for ig in self.ignore):
+            return _unquantized(layer)
+        kind = type(layer).__name__
+        if "MoE" in kind or "RoutedExperts" in kind or prefix.endswith(_MOE_SUFFIXES):
+            pair = self._moe_scheme_for_prefix(prefix)
+            if pair is None:
+                return _unquantized(layer)
+            from .moe import PrismaQuantCBMoEMethod
+            return PrismaQuantCBMoEMethod(self, getattr(layer, "moe_config", None), pair[0], prefix,
+                                          scheme_down=pair[1])
+        scheme = self._scheme_for_prefix(prefix)
+        if scheme is None:
+            return _unquantized(layer)
+        from .linear import PrismaQuantCBLinearMethod
+        return PrismaQuantCBLinearMethod(self, scheme, prefix)
+
+
+def _unquantized(layer):
+    """Non-CB modules keep vLLM's own unquantized method (None lets the engine choose)."""
+    if HAVE_VLLM:
+        try:
+            from vllm.model_executor.layers.linear import LinearBase, UnquantizedLinearMethod
+            if isinstance(layer, LinearBase):
+                return UnquantizedLinearMethod()
+        except Exception:            # pragma: no cover
+            pass
+    return None

@@ -139,10 +139,20 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         else:
             xq = kernels.fp8_act_qdq(x2.contiguous(), ops.ACT_SCALE_RULE)
             wt = (kernels.expand_fp8(w).to(torch.float32) * w.weight_scale[:, None]).to(torch.bfloat16)
-        y = torch.matmul(xq, wt.t())
-        if w.global_scale != 1.0:
-            y = (y.float() * w.global_scale).to(torch.bfloat16)
-        return y
+        if w.global_scale == 1.0:
+            return torch.matmul(xq, wt.t())
+        # keep the fp32 accumulator until the epilogue multiplier is in: one bf16 rounding
+        acc = torch.mm(xq, wt.t(), out_dtype=torch.float32)
+        return (acc * w.global_scale).to(torch.bfloat16)
+
+
+def _scheme_of(fmt: CBFormat, global_scale: float = 1.0) -> dict:
+    """The reference-style scheme dict of a format (docs/SPEC.md:408-440)."""
+    scheme = {"grid": fmt.grid, "mode": fmt.mode, "k": fmt.k, "n_sub": fmt.n_sub,
+              "type_size": fmt.type_size, "weight_global_scale": global_scale}
+    if fmt.scale_coding == "v2":
+        scheme["scale_coding"] = {"kind": "two_tier", "table": list(codec.TWO_TIER_SUB_TABLE)}
+    return scheme
 
 
 class CBLinear(torch.nn.Module):
@@ -153,10 +163,7 @@ class CBLinear(torch.nn.Module):
     def __init__(self, fmt: CBFormat, in_features: int, out_partition_sizes, codebooks, *,
                  global_scale: float = 1.0, prefix: str = "cb_linear"):
         super().__init__()
-        scheme = {"grid": fmt.grid, "mode": fmt.mode, "k": fmt.k, "n_sub": fmt.n_sub,
-                  "type_size": fmt.type_size, "weight_global_scale": global_scale}
-        if fmt.scale_coding == "v2":
-            scheme["scale_coding"] = {"kind": "two_tier", "table": list(codec.TWO_TIER_SUB_TABLE)}
+        scheme = _scheme_of(fmt, global_scale)
         self.method = PrismaQuantCBLinearMethod(_InlineCodebooks(codebooks), scheme, prefix)
         sizes = list(out_partition_sizes)
         self.method.create_weights(self, in_features, sizes, in_features, sum(sizes), torch.bfloat16)

@@ -1,0 +1,215 @@
+"""Routed-experts (FusedMoE) method behind the plugin surface
+(gridbook/moe.py:406-550,552-955,957-1055,2388-2504): stacked packed experts, device-side
+routing, grouped codebook GEMV with fused SwiGLU, top-k weighted combine."""
+from __future__ import annotations
+
+import torch
+
+from . import _native, codec, kernels
+from ._native import NativeKernelUnavailableError
+from ._vllm_compat import FusedMoEMethodBase
+from .formats import CBFormat
+
+
+def _row_bytes(in_features: int, type_size: int) -> int:
+    if in_features % codec.SUPERBLOCK:
+        raise ValueError(f"in_features {in_features} not a multiple of {codec.SUPERBLOCK}")
+    return (in_features // codec.SUPERBLOCK) * type_size
+
+
+class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
+    """CB decode for routed experts.  ``scheme`` is the gate_up format; ``scheme_down``
+    (optional, not expressible in the reference: gridbook/config.py:1631-1640) gives the
+    down projection its own format."""
+
+    def __init__(self, quant_config, moe, scheme: dict, prefix: str, scheme_down: dict | None = None) -> None:
+        super().__init__(moe)
+        self.quant_config = quant_config
+        self.scheme = scheme
+        self.scheme_down = scheme_down or scheme
+        self.prefix = prefix
+        self.fmt13 = CBFormat.from_scheme(self.scheme)
+        self.fmt2 = CBFormat.from_scheme(self.scheme_down)
+        self.is_fp4 = self.fmt13.is_fp4
+        self.k, self.n_sub, self.type_size = self.fmt13.k, self.fmt13.n_sub, self.fmt13.type_size
+
+    # ------------------------------------------------------------------ parameters
+    def create_weights(self, layer, num_experts: int, hidden_size: int,
+                       intermediate_size_per_partition: int, params_dtype, **extra_weight_attrs):
+        del params_dtype
+        E, inter = num_experts, intermediate_size_per_partition
+        layer._cb_hidden, layer._cb_inter = hidden_size, inter
+        attrs = dict(extra_weight_attrs)
+
+        def param(shape, dtype):
+            p = torch.nn.Parameter(torch.empty(*shape, dtype=dtype), requires_grad=False)
+            for key, val in attrs.items():
+                setattr(p, key, val)
+            return p
+
+        # w13 = gate_up: out = 2*inter, in = hidden.  w2 = down: out = hidden, in = inter.
+        layer.register_parameter("w13_cb_qweight", param(
+            (E, 2 * inter, _row_bytes(hidden_size, self.fmt13.type_size)), torch.uint8))
+        layer.register_parameter("w2_cb_qweight", param(
+            (E, hidden_size, _row_bytes(inter, self.fmt2.type_size)), torch.uint8))
+        if not self.fmt13.is_fp4:
+            layer.register_parameter("w13_weight_scale", param((E, 2 * inter), torch.float32))
+        if not self.fmt2.is_fp4:
+            layer.register_parameter("w2_weight_scale", param((E, hidden_size), torch.float32))
+        self._install_load_hook(layer)
+
+    def _install_load_hook(self, layer) -> None:
+        """Checkpoint tensors `<proj>.cb_qweight` / `<proj>.weight_scale` load straight into
+        the stacked parameters; everything else goes to the layer's own loader
+        (gridbook/moe.py:503-546)."""
+        orig_load = getattr(layer, "load_weights", None)
+        if orig_load is None or getattr(layer, "_cb_load_wrapped", False):
+            return
+        prefix = self.prefix
+        cb_map = {"gate_up_proj.cb_qweight": "w13_cb_qweight", "down_proj.cb_qweight": "w2_cb_qweight",
+                  "gate_up_proj.weight_scale": "w13_weight_scale", "down_proj.weight_scale": "w2_weight_scale"}
+
+        def _cb_load_weights(weights):
+            deferred = []
+            for name, w in weights:
+                pname = cb_map.get(name)
+                if pname is not None and hasattr(layer, pname):
+                    p = getattr(layer, pname)
+                    if tuple(p.shape) != tuple(w.shape):
+                        raise ValueError(f"{prefix}.{name}: checkpoint shape {tuple(w.shape)} != param "
+                                         f"{tuple(p.shape)} — stacked (E, out, bytes) contract violated")
+                    p.data.copy_(w.to(p.dtype))
+                    yield pname
+                else:
+                    deferred.append((name, w))
+            if deferred:
+                yield from orig_load(deferred)
+
+        layer.load_weights = _cb_load_weights
+        layer._cb_load_wrapped = True
+
+    def get_fused_moe_quant_config(self, layer):
+        return None
+
+    # ------------------------------------------------------------------ post-load prep
+    def _stack_weight(self, layer, qw_name: str, scale_name: str, fmt: CBFormat, k_in: int, role: str):
+        qc = self.quant_config
+        if qc is None:
+            raise NativeKernelUnavailableError(f"{self.prefix}: no quantization config to resolve codebooks")
+        scheme = self.scheme if role == "w13" else self.scheme_down
+        roles = qc.codebooks_for_prefix(f"{self.prefix}.{role}", scheme)
+        if len(roles) != 1:
+            raise NativeKernelUnavailableError(
+                f"{self.prefix}: a routed stack shares one codebook per projection; got {len(roles)}")
+        flat = codec.build_flat_codebook([t.to(torch.float32) for t in roles[0]], prefix=self.prefix, grid=fmt.grid)
+        if flat.numel() != fmt.codebook_elems():
+            raise ValueError(f"{self.prefix}: codebook has {flat.numel()} entries, {fmt} wants {fmt.codebook_elems()}")
+        p = getattr(layer, qw_name)
+        dev = p.device
+        packed = codec.with_tail_slack(p.data)
+        p.data = packed
+        cb_dev = (flat if fmt.is_fp4 else codec.flat_codebook_fp8(flat, self.prefix)).to(dev)
+        sc = scheme.get("scale_coding")
+        table = (sc.get("table") if isinstance(sc, dict) else None) or codec.TWO_TIER_SUB_TABLE
+        compose = codec.build_compose_table(table).to(dev) if fmt.scale_coding == "v2" else None
+        ws = getattr(layer, scale_name).data.float().contiguous() if not fmt.is_fp4 else None
+        return kernels.make_weight(packed, cb_dev, fmt, k_in, compose=compose, weight_scale=ws,
+                                   global_scale=float(scheme.get("weight_global_scale", 1.0)))
+
+    def process_weights_after_loading(self, layer) -> None:
+        _native.load(f"{self.prefix}: CB routed experts")
+        if not layer.w13_cb_qweight.is_cuda:
+            raise NativeKernelUnavailableError(
+                f"{self.prefix}: CB expert stacks must live on a CUDA device; there is no CPU path")
+        _native.prepare(layer.w13_cb_qweight.device)
+        layer._cb_w13 = self._stack_weight(layer, "w13_cb_qweight", "w13_weight_scale", self.fmt13,
+                                           layer._cb_hidden, "w13")
+        layer._cb_w2 = self._stack_weight(layer, "w2_cb_qweight", "w2_weight_scale", self.fmt2,
+                                          layer._cb_inter, "w2")
+        layer._cb_E = layer.w13_cb_qweight.shape[0]
+        layer._cb_xrow_cache = {}
+        from .ops import register_cb_layer
+        layer._cb_layer_id = register_cb_layer(self, layer)
+        print(f"[prismaquant-cb] {self.prefix}: decode=grouped-cuda (sm_100a) "
+              f"w13={self.fmt13.grid}/k{self.fmt13.k} w2={self.fmt2.grid}/k{self.fmt2.k}", flush=True)
+
+    # ------------------------------------------------------------------ forward
+    def apply(self, layer, x, topk_weights, topk_ids, shared_experts=None, shared_experts_input=None,
+              apply_router_weight_on_input: bool = False, **_ignored):
+        """Routed-only output; the shared expert is the engine's business
+        (gridbook/moe.py:957-989)."""
+        if apply_router_weight_on_input:
+            raise NativeKernelUnavailableError(
+                f"{self.prefix}: apply_router_weight_on_input has no native Gridbook operator")
+        lid = getattr(layer, "_cb_layer_id", None)
+        if lid is None:
+            raise NativeKernelUnavailableError(
+                f"{self.prefix}: CB experts were not registered during process_weights_after_loading")
+        from .ops import cb_moe_forward
+        return cb_moe_forward(x, topk_weights, topk_ids, lid)
+
+    def _x_row(self, layer, T: int, topk: int, device):
+        key = (T, topk)
+        cached = layer._cb_xrow_cache.get(key)
+        if cached is None:
+            cached = (torch.arange(T * topk, device=device, dtype=torch.int32) // topk).contiguous()
+            layer._cb_xrow_cache[key] = cached
+        return cached
+
+    def _apply_inline(self, layer, x, topk_weights, topk_ids):
+        """route -> bucket -> grouped gate/up GEMV with SwiGLU -> bucket -> grouped down GEMV ->
+        combine.  Six launches, no host read, any token count (an expert's tokens are taken
+        in passes of up to sixteen rows, its weights stream once per pass)."""
+        from . import ops
+        rule = ops.ACT_SCALE_RULE
+        T, topk = topk_ids.shape
+        if T == 0:
+            return torch.empty_like(x)
+        x2 = x.reshape(T, -1).to(torch.bfloat16).contiguous()
+        _, offsets, order = kernels.moe_route(topk_ids, layer._cb_E)
+        bucket13 = kernels.fp4_act_qdq if self.fmt13.is_fp4 else kernels.fp8_act_qdq
+        bucket2 = kernels.fp4_act_qdq if self.fmt2.is_fp4 else kernels.fp8_act_qdq
+        xq = bucket13(x2, rule)
+        a = kernels.moe_gemv(xq, layer._cb_w13, offsets, order, x_row=self._x_row(layer, T, topk, x.device),
+                             swiglu=True)
+        aq = bucket2(a, rule)
+        y = kernels.moe_gemv(aq, layer._cb_w2, offsets, order)
+        # the loop chain multiplies by the bf16-rounded router weight (gridbook/moe.py:2407-2408)
+        pair_w = topk_weights.reshape(-1).to(torch.bfloat16).to(torch.float32)
+        out = kernels.moe_combine(y, pair_w, T, topk)
+        return out.to(x.dtype).reshape(x.shape)
+
+
+class CBMoE(torch.nn.Module):
+    """Stand-alone driver of PrismaQuantCBMoEMethod (tests, benchmark): create_weights ->
+    copy stacks in -> process_weights_after_loading -> apply."""
+
+    def __init__(self, fmt13: CBFormat, fmt2: CBFormat, num_experts: int, hidden: int, inter: int,
+                 codebooks13, codebooks2, *, prefix: str = "cb_moe"):
+        super().__init__()
+        from .linear import _scheme_of
+        books = {f"{prefix}.w13": [codebooks13], f"{prefix}.w2": [codebooks2]}
+        self.method = PrismaQuantCBMoEMethod(_PrefixCodebooks(books), None, _scheme_of(fmt13), prefix,
+                                             scheme_down=_scheme_of(fmt2))
+        self.method.create_weights(self, num_experts, hidden, inter, torch.bfloat16)
+
+    def load(self, w13, w2, w13_scale=None, w2_scale=None, device="cuda"):
+        self.w13_cb_qweight.data = w13.to(device)
+        self.w2_cb_qweight.data = w2.to(device)
+        if w13_scale is not None:
+            self.w13_weight_scale.data = w13_scale.to(device)
+        if w2_scale is not None:
+            self.w2_weight_scale.data = w2_scale.to(device)
+        self.method.process_weights_after_loading(self)
+        return self
+
+    def forward(self, x, topk_weights, topk_ids):
+        return self.method.apply(self, x, topk_weights, topk_ids)
+
+
+class _PrefixCodebooks:
+    def __init__(self, books):
+        self.books = books
+
+    def codebooks_for_prefix(self, prefix, scheme):
+        return self.books[prefix]

@@ -1,0 +1,209 @@
+"""Host-side logic that needs no GPU: the C-ABI library loads and exports every symbol the
+header declares, the loader fails closed, config resolution, plugin registration with a
+stubbed registry, the layer registry and the padding sentinel."""
+import ctypes
+import ctypes.util
+import gc
+import json
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _header_symbols():
+    text = open(os.path.join(ROOT, "include", "gridbook_b200.h")).read()
+    return sorted(set(re.findall(r"GB_API\s+[\w\s\*]+?\b(gb_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from gridbook_b200 import _native, build
+    build.build()
+    lib = ctypes.CDLL(_native.library_path())
+    declared = _header_symbols()
+    assert len(declared) >= 16
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    assert set(_native.REQUIRED_SYMBOLS) <= set(declared)
+    assert _native.load().gb_abi_version() == _native.GB_ABI_VERSION
+
+
+def test_loader_fails_closed(monkeypatch, tmp_path):
+    from gridbook_b200 import _native
+    monkeypatch.setattr(_native, "_LIB", None)
+    monkeypatch.setenv("GRIDBOOK_B200_LIB", str(tmp_path / "missing.so"))
+    with pytest.raises(_native.NativeKernelUnavailableError, match="missing"):
+        _native.load("unit test")
+    # a library without the required symbols is a stale extension
+    monkeypatch.setenv("GRIDBOOK_B200_LIB", ctypes.util.find_library("m") and "/lib/x86_64-linux-gnu/libm.so.6")
+    with pytest.raises(_native.NativeKernelUnavailableError):
+        _native.load("unit test")
+    monkeypatch.delenv("GRIDBOOK_B200_LIB")
+    assert _native.load() is not None
+
+
+def test_argument_validation_without_a_device():
+    """Validation runs before any CUDA call, so bad descriptors are reported on a CPU box."""
+    from gridbook_b200 import _native as nat
+    lib = nat.load()
+    fmt = nat.GbFormat(grid=0, mode=0, k_bits=16, n_sub=2, type_size=70, scale_coding=2)
+    w = nat.GbWeight(qw=1, row_stride=73, codebook=1, cb_row_offset=None, compose=1, weight_scale=None,
+                     global_scale=1.0, rows=8, K=256, fmt=fmt)
+    rc = lib.gb_expand_fp4_bf16(ctypes.byref(w), 0, 8, ctypes.c_void_p(1), None)
+    assert rc == 1 and b"type_size" in lib.gb_last_error()
+    w.fmt.type_size = 73
+    w.K = 250
+    rc = lib.gb_expand_fp4_bf16(ctypes.byref(w), 0, 8, ctypes.c_void_p(1), None)
+    assert rc == 1 and b"multiple of 256" in lib.gb_last_error()
+    assert lib.gb_gemv_workspace_bytes(16, 1024, 512) == 16 * 512 * 2 + 16 * 1024 * 4
+
+
+def test_kernels_refuse_cpu_tensors():
+    from gridbook_b200 import kernels, ops
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        kernels.fp8_act_qdq(torch.zeros(2, 32, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError):
+        ops.fp4_act_qdq_or_codec(torch.zeros(2, 32, dtype=torch.bfloat16))
+
+
+def _quant_config():
+    two_tier = {"kind": "two_tier", "table": [1.0, 1.125, 1.25, 1.375, 1.5, 1.625, 1.75, 1.875,
+                                              2.0, 2.25, 2.5, 2.75, 3.0, 3.25, 3.5, 3.75]}
+    fp4 = {"grid": "fp4", "mode": "product", "k": 16, "n_sub": 2, "type_size": 73,
+           "codebook_ref": ["cb.K16.sub0", "cb.K16.sub1"], "scale_coding": two_tier}
+    fp4_b = dict(fp4, codebook_ref=["cb.K16b.sub0", "cb.K16b.sub1"])
+    fp8 = {"grid": "fp8", "mode": "product", "k": 32, "n_sub": 4, "type_size": 128,
+           "codebook_ref": [f"cb.F32.sub{i}" for i in range(4)]}
+    return {
+        "quant_method": "gridbook", "format": "nvfp4_cb", "layout_version": 2,
+        "config_groups": {
+            "g0": {"targets": ["model.layers.0.self_attn.q_proj", "model.layers.0.self_attn.k_proj",
+                               "model.layers.0.self_attn.v_proj", "model.layers.0.mlp.gate_proj"], "scheme": fp4},
+            "g1": {"targets": ["model.layers.0.mlp.up_proj"], "scheme": fp4_b},
+            "g2": {"targets": ["model.layers.0.self_attn.o_proj", "model.layers.1.mlp.experts.gate_up_proj"],
+                   "scheme": fp8},
+            "g3": {"targets": ["model.layers.1.mlp.experts.down_proj"], "scheme": fp4},
+        },
+        "ignore": ["lm_head"],
+    }
+
+
+def test_config_resolution_inline_and_pointer(tmp_path):
+    from gridbook_b200.config import PrismaQuantConfig
+    from gridbook_b200.linear import PrismaQuantCBLinearMethod
+    from gridbook_b200.moe import PrismaQuantCBMoEMethod
+    assert PrismaQuantConfig.override_quantization_method({"quant_method": "prismaquant"}, None) == "gridbook"
+    assert PrismaQuantConfig.override_quantization_method({"quant_method": "awq"}, None) is None
+    assert PrismaQuantConfig.get_name() == "gridbook"
+
+    full = _quant_config()
+    books = {n: torch.zeros(256, 4) for n in ("cb.K16.sub0", "cb.K16.sub1", "cb.K16b.sub0", "cb.K16b.sub1")}
+    books.update({f"cb.F32.sub{i}": torch.zeros(256, 2) for i in range(4)})
+    cfg = PrismaQuantConfig.from_config(dict(full, _codebooks=books))
+
+    class Linear(torch.nn.Module):
+        pass
+
+    class FusedMoE(torch.nn.Module):
+        pass
+
+    m = cfg.get_quant_method(Linear(), "model.layers.0.self_attn.qkv_proj")
+    assert isinstance(m, PrismaQuantCBLinearMethod) and m.fmt.type_size == 73
+    assert cfg.shard_target_keys("model.layers.0.self_attn.qkv_proj") == [
+        "model.layers.0.self_attn.q_proj", "model.layers.0.self_attn.k_proj", "model.layers.0.self_attn.v_proj"]
+    assert len(cfg.codebooks_for_prefix("model.layers.0.self_attn.qkv_proj", m.scheme)) == 1     # shared book
+    gu = cfg.get_quant_method(Linear(), "model.layers.0.mlp.gate_up_proj")
+    assert len(cfg.codebooks_for_prefix("model.layers.0.mlp.gate_up_proj", gu.scheme)) == 2      # per-role books
+    assert cfg.get_quant_method(Linear(), "model.layers.0.self_attn.o_proj").fmt.grid == "fp8"
+    assert cfg.get_quant_method(Linear(), "lm_head") is None
+    assert cfg.get_quant_method(Linear(), "model.layers.7.mlp.down_proj") is None
+    moe = cfg.get_quant_method(FusedMoE(), "model.layers.1.mlp.experts")
+    assert isinstance(moe, PrismaQuantCBMoEMethod) and moe.fmt13.grid == "fp8" and moe.fmt2.grid == "fp4"
+    # class-wrapper prefixes resolve to the stored keys
+    assert cfg.get_quant_method(Linear(), "language_model.model.layers.0.self_attn.o_proj") is not None
+
+    # pointer stub -> quant_config.json in the model directory
+    (tmp_path / "quant_config.json").write_text(json.dumps(full))
+    ptr = PrismaQuantConfig({"quant_method": "gridbook", "config_file": "quant_config.json"}, str(tmp_path))
+    assert ptr.get_quant_method(Linear(), "model.layers.0.self_attn.o_proj").type_size == 128
+    with pytest.raises(ValueError, match="model directory"):
+        PrismaQuantConfig({"quant_method": "gridbook"}).get_quant_method(Linear(), "x")
+
+
+def test_scheme_parsing_and_type_size_guard():
+    from gridbook_b200.formats import CBFormat
+    f = CBFormat.from_scheme({"grid": "fp4", "k": 13, "n_sub": 1, "type_size": 61,
+                              "scale_coding": "two_tier"})
+    assert f.mode == "signed" and f.scale_coding == "v2"
+    assert CBFormat.from_scheme({"grid": "fp4", "mode": "full", "k": 8, "n_sub": 1}).type_size == 48
+    assert CBFormat("fp8", 30, n_sub=4).widths() == [8, 8, 7, 7]
+    with pytest.raises(ValueError, match="type_size"):
+        CBFormat.from_scheme({"grid": "fp8", "k": 32, "n_sub": 4, "type_size": 120})
+
+
+def test_codec_rejects_off_grid_codebooks():
+    from gridbook_b200 import codec
+    with pytest.raises(ValueError, match="off the grid"):
+        codec.build_flat_codebook([torch.tensor([[0.53125, 1.0, 2.0, 6.0]])], grid="fp4")
+    with pytest.raises(ValueError, match="off the grid"):
+        codec.build_flat_codebook([torch.tensor([[0.3, 1.0]])], grid="fp8")
+    flat = codec.build_flat_codebook([torch.tensor([[0.5, -6.0, 3.0, 0.0]])], grid="fp4")
+    assert flat.dtype is torch.bfloat16 and flat.tolist() == [0.5, -6.0, 3.0, 0.0]
+    assert codec.pad_qweight(torch.zeros(3, 73, dtype=torch.uint8)).shape == (3, 89)
+    assert codec.build_compose_table()[127 * 16 + 9].item() == 2.25
+
+
+def test_plugin_registers_both_names():
+    from gridbook_b200 import plugin
+    from gridbook_b200.config import PrismaQuantConfig
+    seen = {}
+
+    def registry(name):
+        def deco(cls):
+            seen[name] = cls
+            return cls
+        return deco
+
+    plugin.register(registry)
+    assert seen == {"gridbook": PrismaQuantConfig, "prismaquant": PrismaQuantConfig}
+
+
+def test_layer_registry_is_weak_and_monotonic():
+    from gridbook_b200 import ops
+
+    class Obj:
+        pass
+
+    m, l = Obj(), Obj()
+    a = ops.register_cb_layer(m, l)
+    b = ops.register_cb_layer(m, l)
+    assert b > a and ops._lookup_cb_layer(a) == (m, l)
+    del l
+    gc.collect()
+    with pytest.raises(RuntimeError, match="stale or unknown"):
+        ops._lookup_cb_layer(a)
+
+
+def test_padding_sentinel_is_neutralised():
+    from gridbook_b200 import ops
+    w = torch.tensor([[0.5, 0.5], [float("nan"), 1.0]])
+    ids = torch.tensor([[3, -1], [-1, 2]])
+    w2, ids2 = ops._neutralize_moe_padding_sentinel(w, ids)
+    assert ids2.tolist() == [[3, 0], [0, 2]] and w2.tolist() == [[0.5, 0.0], [0.0, 1.0]]
+
+
+def test_methods_fail_closed_before_load():
+    from gridbook_b200._native import NativeKernelUnavailableError
+    from gridbook_b200.formats import NVFP4_CB_K16
+    from gridbook_b200.linear import CBLinear
+    lin = CBLinear(NVFP4_CB_K16, 512, [16], [[torch.zeros(256, 4), torch.zeros(256, 4)]])
+    assert lin.cb_qweight.shape == (16, 2 * 73)
+    with pytest.raises(NativeKernelUnavailableError, match="not registered"):
+        lin(torch.zeros(1, 512, dtype=torch.bfloat16))
+    with pytest.raises(NativeKernelUnavailableError, match="biased"):
+        lin.method.apply(lin, torch.zeros(1, 512), bias=torch.zeros(16))
+    with pytest.raises(NativeKernelUnavailableError, match="CUDA device"):
+        lin.method.process_weights_after_loading(lin)
