@@ -120,7 +120,13 @@ def build_stack(fmt, gscale, layers, device, rank, world, seed=0):
             ws = None
             if not fmt.is_fp4:
                 ws = (torch.rand(sum(local), generator=gen, device=device) + 0.5) * 0.02
-            row.append(lin.load(qw, ws, device))
+            lin.load(qw, ws, device)
+            if world > 1:
+                from gridbook_b200.parallel import ShardedCBLinear
+                sh = ShardedCBLinear(lin, parts)
+                sh._cb_weight, sh._cb_workspace = lin._cb_weight, lin._cb_workspace
+                lin = sh
+            row.append(lin)
         stack.append(row)
     return stack
 
@@ -149,7 +155,6 @@ def run_gpu(args):
     inputs_host = [t.cpu().pin_memory() for t in inputs_dev]
     n_local = [sum(p // world for p in parts) for _, parts, _ in PROJECTIONS]
     bytes_per_step_local = sum(lin._cb_weight.packed_bytes for row in stack for lin in row)
-    gathered = [torch.empty(world * M, n, dtype=torch.bfloat16, device=device) for n in n_local]
     launches_per_linear = 2          # activation bucket + decode GEMV
     extra = 0
     for row in stack[:1]:
@@ -161,12 +166,8 @@ def run_gpu(args):
         ys = None
         for row in stack:
             ys = []
-            for lin, x, g in zip(row, inputs_dev, gathered):
-                y = lin(x)
-                if world > 1:
-                    dist.all_gather_into_tensor(g, y)     # [world*M, n_local], rank-major
-                    y = g
-                ys.append(y)
+            for lin, x in zip(row, inputs_dev):
+                ys.append(lin(x))          # N > 1: local shard + NCCL all-gather inside
         return ys
 
     # warm-up eagerly (also settles allocator and NCCL), then capture one step
@@ -215,8 +216,7 @@ def run_gpu(args):
             d.copy_(h, non_blocking=True)
         run_step()
         for h, y in zip(outs_host, last):
-            src = y if world == 1 else y.view(world, M, -1).permute(1, 0, 2).reshape(M, -1)
-            h.copy_(src, non_blocking=True)
+            h.copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for _ in range(3):
@@ -259,6 +259,7 @@ def run_gpu(args):
     k1.record()
     barrier()
     ms_kernel = k0.elapsed_time(k1)
+    moe = None if args.no_moe else bench_moe(args, device, world, rank)
     status = _native.device_status(local_rank)
 
     times = torch.tensor([ms_total, ms_e2e, ms_kernel, float(bytes_per_step_local)], dtype=torch.float64,
@@ -308,6 +309,7 @@ def run_gpu(args):
         "gpu_launches": int(args.steps * n_linear * launches_per_linear + extra),
         "clocks": clocks.summary(),
         "device_status": status,
+        "moe": moe,
     }
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(args.format, M, seconds=20.0)
@@ -315,6 +317,70 @@ def run_gpu(args):
     if world > 1:
         dist.destroy_process_group()
 
+
+
+# ----------------------------------------------------------------------------- routed MoE leg
+MOE_SHAPE = dict(E=128, topk=8, hidden=2048, inter=768)          # benchmark configuration 3
+
+
+def bench_moe(args, device, world, rank):
+    """Grouped-MoE decode tokens/s for one routed layer of configuration 3 at T tokens PER RANK
+    (weak scaling: every rank brings its own batch, experts are split E/world per rank and rows
+    travel by NCCL all-to-all).  L2 is flushed between timed iterations."""
+    import torch
+    import torch.distributed as dist
+    from gridbook_b200 import synth
+    from gridbook_b200.moe import CBMoE
+    from gridbook_b200 import parallel
+
+    fmt, _ = get_format(args.format)
+    E, topk, hidden, inter = (MOE_SHAPE[k] for k in ("E", "topk", "hidden", "inter"))
+    e_local = E // world
+    gen = torch.Generator(device=device).manual_seed(77 + rank)
+    layers = []
+    for li in range(2):
+        moe = CBMoE(fmt, fmt, e_local, hidden, inter, synth.codebook_tables(fmt, 5), synth.codebook_tables(fmt, 6))
+        w13 = synth.make_packed_device(fmt, e_local * 2 * inter, hidden, gen, device).view(e_local, 2 * inter, -1)
+        w2 = synth.make_packed_device(fmt, e_local * hidden, inter, gen, device).view(e_local, hidden, -1)
+        s13 = s2 = None
+        if not fmt.is_fp4:
+            s13 = (torch.rand(e_local, 2 * inter, generator=gen, device=device) + 0.5) * 0.02
+            s2 = (torch.rand(e_local, hidden, generator=gen, device=device) + 0.5) * 0.02
+        moe.load(w13, w2, s13, s2, device)
+        if world > 1:
+            moe = parallel.ExpertParallelMoE(E, parallel.make_local_expert_fn(moe), parallel.kernel_combine)
+        layers.append(moe)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    out = {}
+    for T in (1, 16, 64, 256):
+        ids, tw = synth.make_routing(T, E, topk, seed=T + 13 * rank)
+        x = torch.randn(T, hidden, generator=gen, device=device).to(torch.bfloat16)
+        ids_d, tw_d = torch.from_numpy(ids).to(device), torch.from_numpy(tw).to(device)
+        for _ in range(3):
+            for m in layers:
+                m(x, tw_d, ids_d)
+        iters, total = 10, 0.0
+        for it in range(iters):
+            flush.fill_(it)
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for m in layers:
+                m(x, tw_d, ids_d)
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        t = torch.tensor([total], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_layer = float(t) / (iters * len(layers))
+        out[str(T)] = {"tok_s": round(world * T / (ms_layer * 1e-3), 1), "ms_per_layer": round(ms_layer, 4)}
+    return {"workload": f"routed MoE layer, {E} experts top-{topk}, hidden {hidden}, intermediate {inter}, "
+                        f"format {args.format}, T tokens per rank", "scaling": "weak",
+            "parallelism": f"expert-parallel x{world} (NCCL all-to-all)" if world > 1 else "1 GPU",
+            "tokens_per_rank": out}
 
 # ----------------------------------------------------------------------------- CPU arm
 def cpu_layer_inputs(fmt, gscale, M, seed=0):
@@ -403,6 +469,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-moe", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

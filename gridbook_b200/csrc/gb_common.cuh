@@ -175,9 +175,12 @@ GB_DEVINL uint64_t gb_globaltimer_ns() {
 
 // Returns false when the wait ran out of patience (two seconds of wall clock);
 // the caller raises the status word and leaves the kernel.
-GB_DEVINL bool gb_mbar_wait(uint64_t* bar, uint32_t parity) {
+// `tok` (optional) receives a value the compiler cannot see through; loads that must not move
+// above the wait take it as an operand.
+GB_DEVINL bool gb_mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* tok = nullptr) {
   const uint32_t addr = gb_smem_u32(bar);
   uint64_t t0 = 0;
+  if (tok) *tok = 0;
   for (uint32_t spin = 0;; ++spin) {
     uint32_t done;
     asm volatile(
@@ -189,7 +192,10 @@ GB_DEVINL bool gb_mbar_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(done)
         : "r"(addr), "r"(parity)
         : "memory");
-    if (done) return true;
+    if (done) {
+      if (tok) *tok = done;
+      return true;
+    }
     if ((spin & 255u) == 255u) {
       const uint64_t now = gb_globaltimer_ns();
       if (t0 == 0) t0 = now;
@@ -213,7 +219,8 @@ GB_DEVINL void gb_fence_barrier_init() {
 }
 
 GB_DEVINL void gb_mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
+  // not volatile: a pure function of its register operands, free to be interleaved
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])

@@ -167,6 +167,23 @@ GB_DEVINL uint4 lds_v4(uint32_t a) {
   return v;
 }
 
+// Hot-loop loads.  They are NOT volatile, so the compiler may batch and interleave them; the
+// extra `tok` operand is a value produced by the mbarrier wait of the current task, which
+// keeps every such load after that wait (and after the activation restage before it) and
+// makes loads of different tasks distinct expressions.
+GB_DEVINL uint4 ldt_v4(uint32_t a, uint32_t tok) {
+  uint4 v;
+  asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4]; // %5" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a), "r"(tok));
+  return v;
+}
+GB_DEVINL uint4 ldt_v4_if(uint32_t a, bool live, uint32_t tok) {
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  asm("{ .reg .pred q; setp.ne.u32 q, %5, 0; @q ld.shared.v4.u32 {%0,%1,%2,%3}, [%4]; } // %6"
+      : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+      : "r"(a), "r"((uint32_t)live), "r"(tok));
+  return v;
+}
+
 // 16-byte shared load that only lanes with `live` perform; the others get zeros and cost
 // no shared-memory bandwidth.
 GB_DEVINL uint4 lds_v4_if(uint32_t a, bool live) {
@@ -337,11 +354,18 @@ GB_DEVINL void stage_lut(const GemvParams& p, uint8_t* lut, int64_t cb_off, int 
     const uint16_t* src = reinterpret_cast<const uint16_t*>(p.codebook) + cb_off;
     const uint32_t bias = p.fmt.scale_coding == GB_SCALE_V1 ? kExpBias120 : 0u;
     if (p.lut_rep > 1) {
-      // entry e (eight values) -> eight copies at (e * 8 + r) * 16 bytes
-      for (int i = tid; i < p.cb_elems * 8; i += nthreads) {
-        const int e = i >> 6, r = (i >> 3) & 7, j = i & 7;
-        const uint32_t b = src[e * 8 + j];
-        dst[(e * 8 + r) * 8 + j] = (uint16_t)((b & 0x7FFFu) ? b + bias : b);
+      // entry e (eight values, 16 bytes) -> eight copies at (e * 8 + r) * 16 bytes
+      const uint32_t bias2 = bias | (bias << 16);
+      for (int i = tid; i < (p.cb_elems / 8) * 8; i += nthreads) {
+        const int e = i >> 3, r = i & 7;
+        uint4 v = *reinterpret_cast<const uint4*>(src + e * 8);
+        uint32_t* q = &v.x;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t nz = ((q[j] & 0x7FFFu) ? 0xFFFFu : 0u) | ((q[j] & 0x7FFF0000u) ? 0xFFFF0000u : 0u);
+          q[j] += bias2 & nz;
+        }
+        reinterpret_cast<uint4*>(lut)[e * 8 + r] = v;
       }
     } else {
       for (int i = tid; i < p.cb_elems; i += nthreads) {
@@ -375,7 +399,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);             // [warps][kMaxStages]
   uint16_t* sub_tab = reinterpret_cast<uint16_t*>(smem + 512);        // 16 bf16 two-tier multipliers
-  uint8_t* zero_strip = smem + 640;                                   // 640 zero bytes for idle MMA rows
   uint8_t* lut = smem + 1280;
   uint8_t* xs = lut + p.lut_bytes;
   uint8_t* rings = xs + p.x_rows * p.x_pitch;
@@ -387,7 +410,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     for (int s = 0; s < kWarps * kMaxStages; ++s) gb_mbar_init(&full_bar[s], 1);
     gb_fence_barrier_init();
   }
-  for (int i = tid; i < 160; i += kThreads) reinterpret_cast<uint32_t*>(zero_strip)[i] = 0u;
   if (tid < 16 && p.fmt.scale_coding == GB_SCALE_V2)
     sub_tab[tid] = (uint16_t)(__float_as_uint(p.compose[127 * 16 + tid]) >> 16);   // T[c], exact in bf16
   __syncthreads();
@@ -410,7 +432,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     if (!product) d.mask[0] = p.fmt.k_bits >= 32 ? 0xFFFFFFFFu : ((1u << p.fmt.k_bits) - 1u);
   }
   const uint32_t lut_s = gb_smem_u32(lut), xs_s = gb_smem_u32(xs), sub_s = gb_smem_u32(sub_tab);
-  const uint32_t zero_s = gb_smem_u32(zero_strip);
   // literal layout: byte selectors (index byte t4; scale byte 2(kb&1) + (t4>>1), duplicated into both halves)
   const uint32_t sel_idx = 0x4440u | (uint32_t)t4;
   const uint32_t sel_sc_even = 0x4040u | ((uint32_t)t4 >> 1) | (((uint32_t)t4 >> 1) << 8);
@@ -418,6 +439,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
   uint8_t* my_ring = rings + (size_t)warp * p.stages * p.stage_bytes;
   const uint32_t ring_s = gb_smem_u32(my_ring);
   uint64_t* my_bar = full_bar + warp * kMaxStages;
+  const uint32_t lut_lane = lut_s + d.rep_off;      // literal path: eight copies of every entry, pitch 128
   const uint32_t ts = (uint32_t)p.fmt.type_size;
   const bool v1 = p.fmt.scale_coding == GB_SCALE_V1;
 
@@ -481,7 +503,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     // A wait that runs out raises the status word and carries on (the output is then
     // garbage, and flagged): leaving here would strand the other warps at a CTA barrier.
 #ifndef GB_EXP_NO_TMA
-    if (!gb_mbar_wait(&my_bar[s], (it / p.stages) & 1)) atomicExch(p.status, 2);
+    uint32_t tok;
+    if (!gb_mbar_wait(&my_bar[s], (it / p.stages) & 1, &tok)) atomicExch(p.status, 2);
 #endif
     uint32_t sbp = ring_s + (uint32_t)s * (uint32_t)p.stage_bytes + (uint32_t)g * (uint32_t)p.row_pitch +
                    (row_ok ? (uint32_t)((uintptr_t)my_src & 15u) : 0u);
@@ -493,14 +516,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     }
 
     float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
-    // Lanes whose MMA row has no activation row this pass read a zeroed strip instead, and
-    // lanes whose weight row lies past the edge decode the task's first row (their results
-    // are never stored): the loop below is branch-free.
-    const bool lo_live = g < t.mcount, hi_live = g + 8 < t.mcount;
+    float accx[6][4] = {};         // further independent chains: an MMA result is ~30 cycles away
+    // MMA rows without an activation row this pass re-read the last live row (a broadcast,
+    // no extra shared-memory traffic): their output rows are simply never stored.  Lanes whose
+    // weight row lies past the edge decode the task's first row, likewise unused.  The loop
+    // below is branch-free.
     const uint32_t x_lane = (uint32_t)t4 * 16u;
-    uint32_t xa_s = (lo_live ? xs_s + (uint32_t)g * (uint32_t)p.x_pitch : zero_s) + x_lane;
-    uint32_t xb_s = (hi_live ? xs_s + (uint32_t)(g + 8) * (uint32_t)p.x_pitch : zero_s) + x_lane;
-    const uint32_t xa_step = lo_live ? 512u : 0u, xb_step = hi_live ? 512u : 0u;
+    uint32_t xa_s = xs_s + (uint32_t)min(g, t.mcount - 1) * (uint32_t)p.x_pitch + x_lane;
+    uint32_t xb_s = xs_s + (uint32_t)min(g + 8, t.mcount - 1) * (uint32_t)p.x_pitch + x_lane;
+    const uint32_t xa_step = 512u, xb_step = 512u;
     if (!row_ok) sbp = ring_s + (uint32_t)s * (uint32_t)p.stage_bytes + warp_head;
 
     if (uniform) {
@@ -512,7 +536,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
         uint32_t w[8][4], s2[8];
         uint4 xa[8];
         if constexpr (kLit) {
-          const uint4 iw0 = lds_v4(sbp), iw1 = lds_v4(sbp + 16), sw = lds_v4(sbp + 32);
+          const uint4 iw0 = ldt_v4(sbp, tok), iw1 = ldt_v4(sbp + 16, tok), sw = ldt_v4(sbp + 32, tok);
           const uint32_t iw[8] = {iw0.x, iw0.y, iw0.z, iw0.w, iw1.x, iw1.y, iw1.z, iw1.w};
           const uint32_t scw[4] = {sw.x, sw.y, sw.z, sw.w};
 #pragma unroll
@@ -521,7 +545,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
             const uint32_t cc = __byte_perm(iw[kb], 0u, sel_idx);
             const uint4 v = make_uint4(0x3F803F80u + cc, 0x3F803F80u, 0x3F803F80u ^ cc, 0x3F803F80u);
 #else
-            const uint4 v = lds_v4(lut_s + (__byte_perm(iw[kb], 0u, sel_idx) << d.ent_shift) + d.rep_off);
+            const uint4 v = ldt_v4(lut_lane + (__byte_perm(iw[kb], 0u, sel_idx) << 7), tok);
 #endif
             w[kb][0] = v.x; w[kb][1] = v.y; w[kb][2] = v.z; w[kb][3] = v.w;
           }
@@ -529,7 +553,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
 #ifdef GB_EXP_NO_X
           for (int kb = 0; kb < 8; ++kb) xa[kb] = make_uint4(xa_s + kb, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
 #else
-          for (int kb = 0; kb < 8; ++kb) xa[kb] = lds_v4_if(xa_s + kb * 64, lo_live);
+          for (int kb = 0; kb < 8; ++kb) xa[kb] = ldt_v4(xa_s + kb * 64, tok);
 #endif
 #pragma unroll
           for (int kb = 0; kb < 8; ++kb) {
@@ -555,7 +579,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
 #pragma unroll
           for (int kb = 0; kb < 8; ++kb) expand_code<kFmt, kWide>(d, lut_s, lo[kb], hi[kb], w[kb]);
 #pragma unroll
-          for (int kb = 0; kb < 8; ++kb) xa[kb] = lds_v4_if(xa_s + kb * 64, lo_live);
+          for (int kb = 0; kb < 8; ++kb) xa[kb] = ldt_v4(xa_s + kb * 64, tok);
           if constexpr (!fp8) {
             if (v1) {
 #pragma unroll
@@ -585,18 +609,28 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
 #pragma unroll
             for (int j = 0; j < 4; ++j) w[kb][j] = mul_bf16x2(w[kb][j], s2[kb]);
           }
-          uint4 xb = make_uint4(0, 0, 0, 0);
-          if (hi_any) xb = lds_v4_if(xb_s + kb * 64, hi_live);
+          uint4 xb = xa[kb];                     // M <= 8: rows 8..15 mirror rows 0..7, unused
+          if (hi_any) xb = ldt_v4(xb_s + kb * 64, tok);
           const uint32_t a0[4] = {xa[kb].x, xb.x, xa[kb].y, xb.y};
           const uint32_t a1[4] = {xa[kb].z, xb.z, xa[kb].w, xb.w};
 #ifdef GB_EXP_NO_MMA
           acc0[0] += __uint_as_float((a0[0] ^ a0[2] ^ w[kb][0] ^ w[kb][1]) & 0x3FFFFFFFu);
           acc1[0] += __uint_as_float((a1[0] ^ a1[2] ^ w[kb][2] ^ w[kb][3]) & 0x3FFFFFFFu);
 #else
-          gb_mma_bf16_16816(acc0, a0, w[kb][0], w[kb][1]);
-          gb_mma_bf16_16816(acc1, a1, w[kb][2], w[kb][3]);
+          if ((kb & 3) == 0) {
+            gb_mma_bf16_16816(acc0, a0, w[kb][0], w[kb][1]);
+            gb_mma_bf16_16816(acc1, a1, w[kb][2], w[kb][3]);
+          } else {
+            gb_mma_bf16_16816(accx[2 * (kb & 3) - 2], a0, w[kb][0], w[kb][1]);
+            gb_mma_bf16_16816(accx[2 * (kb & 3) - 1], a1, w[kb][2], w[kb][3]);
+          }
 #endif
         }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc0[i] += accx[0][i] + accx[2][i] + accx[4][i];
+        acc1[i] += accx[1][i] + accx[3][i] + accx[5][i];
       }
     } else {
       mixed_codebook_task<fp8>(p, d, sbp, nsb, my_cb_off, row_scale, xa_s, xb_s, xa_step, xb_step, sub_s, t4,
@@ -702,9 +736,9 @@ int plan(GemvParams& p, int m_rows, bool moe, int sms, size_t* smem_bytes) {
   p.n_sb = (int)(p.K / 256);
   p.split = gb_make_split(p.fmt.k_bits, p.fmt.mode == GB_MODE_PRODUCT ? p.fmt.n_sub : 1);
   p.cb_elems = (int)gb_codebook_elems(p.fmt);
-  // Replicating 16-byte entries eight times removes the table's bank conflicts but costs 32 KB of
-  // staging per CTA; measured a loss on every layer but the largest, so it stays off.
-  p.lut_rep = 1;
+  // The literal fast path keeps eight copies of every 16-byte entry (lane l reads copy l % 8), so
+  // a quarter-warp's eight lookups never collide on a bank: 4 wavefronts per lookup instead of ~10.
+  p.lut_rep = literal_aligned(p) ? 8 : 1;
   p.lut_bytes = (p.cb_elems * 2 * p.lut_rep + 127) & ~127;
   if (p.lut_bytes > 72 * 1024)
     return gb_fail(GB_EUNSUPPORTED, "codebook of %d entries does not fit the shared-memory table", p.cb_elems);

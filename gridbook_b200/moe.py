@@ -3,6 +3,8 @@
 routing, grouped codebook GEMV with fused SwiGLU, top-k weighted combine."""
 from __future__ import annotations
 
+import sys
+
 import torch
 
 from . import _native, codec, kernels
@@ -131,7 +133,8 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         from .ops import register_cb_layer
         layer._cb_layer_id = register_cb_layer(self, layer)
         print(f"[prismaquant-cb] {self.prefix}: decode=grouped-cuda (sm_100a) "
-              f"w13={self.fmt13.grid}/k{self.fmt13.k} w2={self.fmt2.grid}/k{self.fmt2.k}", flush=True)
+              f"w13={self.fmt13.grid}/k{self.fmt13.k} w2={self.fmt2.grid}/k{self.fmt2.k}",
+              file=sys.stderr, flush=True)
 
     # ------------------------------------------------------------------ forward
     def apply(self, layer, x, topk_weights, topk_ids, shared_experts=None, shared_experts_input=None,
