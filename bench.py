@@ -470,7 +470,12 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-moe", action="store_true")
+    ap.add_argument("--only", default=None, choices=[n for n, _, _ in PROJECTIONS],
+                    help="restrict the stack to one projection (small profiling captures)")
     args = ap.parse_args()
+    if args.only:
+        global PROJECTIONS
+        PROJECTIONS = tuple(p for p in PROJECTIONS if p[0] == args.only)
     if args.impl == "reference":
         run_reference(args)
     else:
