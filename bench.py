@@ -459,6 +459,7 @@ def run_reference(args):
 
 
 def main():
+    global PROJECTIONS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -474,7 +475,6 @@ def main():
                     help="restrict the stack to one projection (small profiling captures)")
     args = ap.parse_args()
     if args.only:
-        global PROJECTIONS
         PROJECTIONS = tuple(p for p in PROJECTIONS if p[0] == args.only)
     if args.impl == "reference":
         run_reference(args)
