@@ -14,6 +14,7 @@ import threading
 import torch
 
 GB_ABI_VERSION = 1
+GEMM_BF16, GEMM_E4M3 = 0, 1
 
 REQUIRED_SYMBOLS = (
     "gb_abi_version", "gb_last_error", "gb_prepare", "gb_device_status",
@@ -21,6 +22,7 @@ REQUIRED_SYMBOLS = (
     "gb_expand_fp8", "gb_expand_fp4_bf16", "gb_expand_fp4_nvfp4",
     "gb_gemv_workspace_bytes", "gb_gemv", "gb_gemv_static",
     "gb_moe_route", "gb_moe_gemv_workspace_bytes", "gb_moe_gemv", "gb_moe_combine",
+    "gb_fp8_quantize_rows", "gb_gemm_tn",
 )
 
 GRID_FP4, GRID_FP8 = 0, 1
@@ -85,6 +87,8 @@ def _declare(lib) -> None:
     lib.gb_moe_gemv_workspace_bytes.restype = i64
     lib.gb_moe_gemv.argtypes = [vp, vp, wp, i64, i64, vp, vp, i64, i32, vp, vp, i64, vp]
     lib.gb_moe_combine.argtypes = [vp, vp, i64, i64, i64, vp, vp]
+    lib.gb_fp8_quantize_rows.argtypes = [vp, vp, vp, i64, i64, i32, vp]
+    lib.gb_gemm_tn.argtypes = [vp, vp, vp, i64, i64, i64, i32, vp, vp, ctypes.c_float, vp]
     for name in REQUIRED_SYMBOLS:
         fn = getattr(lib, name)
         if fn.restype is ctypes.c_int:

@@ -128,6 +128,7 @@ int gb_prepare(int device) {
     rc = prepare_locked(device);
   }
   if (rc == GB_OK) rc = gb_prepare_kernels();
+  if (rc == GB_OK) rc = gb_prepare_gemm();
   cudaSetDevice(prev);
   return rc;
 }

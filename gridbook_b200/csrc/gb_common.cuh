@@ -41,6 +41,7 @@ int* gb_status_word();             // device int the kernels raise on a timed-ou
 int gb_check_format(const gb_format& f, int64_t K);
 int gb_check_weight(const gb_weight* w);
 int gb_prepare_kernels();          // per-device function attributes of the big kernels
+int gb_prepare_gemm();
 
 // ---------------------------------------------------------------------------
 // scalar formats

@@ -1,0 +1,321 @@
+// Prefill GEMM on the 5th-generation tensor cores: D[M,N] = A[M,K] . B[N,K]^T with both
+// operands K-major, bf16 x bf16 (kind::f16) or E4M3 x E4M3 (kind::f8f6f4), fp32 accumulators
+// in tensor memory, scaled bf16 epilogue.
+//
+// One CTA computes one 128 x 128 output tile.  Warp 4 (one thread) streams 128-byte-wide
+// K slabs of A and B into a shared-memory ring with tiled TMA loads (128-byte swizzle);
+// warp 5 (one thread) issues tcgen05.mma on shared-memory matrix descriptors and releases
+// ring stages with tcgen05.commit; warps 0..3 read the accumulator out of tensor memory
+// (tcgen05.ld, one 32-lane quarter each), apply the row / column / global scales and store
+// bf16.  B is the decoded weight tile the expanders write (gb_expand_fp8 /
+// gb_expand_fp4_bf16); A is the bucketed activation matrix.
+#include "gb_common.cuh"
+
+#include <cuda.h>
+#include <mutex>
+
+namespace {
+
+constexpr int kBM = 128, kBN = 128;
+constexpr int kSlabBytes = 128;                    // K bytes per row per stage (one swizzle span)
+constexpr int kStageBytes = (kBM + kBN) * kSlabBytes;   // 32 KiB
+constexpr int kStages = 6;
+constexpr int kTmemCols = 128;
+constexpr int kGemmThreads = 192;
+constexpr int kGemmSmem = kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
+
+struct GemmParams {
+  int64_t M, N, K;
+  int k_tiles;
+  int elem_bytes;            // 2 (bf16) or 1 (e4m3)
+  uint32_t idesc;
+  const float* a_scale;      // [M] or null
+  const float* b_scale;      // [N] or null
+  float global_scale;
+  uint16_t* D;
+  int* status;
+};
+
+GB_DEVINL void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(gb_smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(gb_smem_u32(bar))
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
+// 128-byte swizzle: 8-row groups are 1024 bytes apart.
+GB_DEVINL uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);          // start address, 16-byte units
+  d |= (uint64_t)(1024u >> 4) << 32;                      // stride between 8-row groups
+  d |= (uint64_t)1 << 46;                                 // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                                 // 128-byte swizzle
+  return d;
+}
+
+GB_DEVINL void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate, bool fp8) {
+  if (fp8) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
+  }
+}
+
+GB_DEVINL void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(gb_smem_u32(bar)) : "memory");
+}
+
+// A bounded wait that remembers a timeout for the rest of the CTA: later waits return at once.
+GB_DEVINL void wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (*abort_flag) return;
+  if (!gb_mbar_wait(bar, parity)) {
+    *abort_flag = 1;
+    atomicExch(status, code);
+  }
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* ring = smem;                                                   // kStages x (A slab | B slab)
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* accum_bar = empty_bar + kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * kBN;
+  const bool fp8 = p.elem_bytes == 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      gb_mbar_init(&full_bar[s], 1);
+      gb_mbar_init(&empty_bar[s], 1);
+    }
+    gb_mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    gb_fence_barrier_init();
+  }
+  if (warp == 5) {   // tensor memory for the 128 x 128 fp32 accumulator
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(gb_smem_u32(tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      const int slab_elems = kSlabBytes / p.elem_bytes;
+      for (int kt = 0; kt < p.k_tiles; ++kt) {
+        const int s = kt % kStages;
+        wait_or_abort(&empty_bar[s], ((kt / kStages) & 1) ^ 1, abort_flag, p.status, 11);
+        gb_mbar_expect_tx(&full_bar[s], kStageBytes);
+        uint8_t* a_dst = ring + (size_t)s * kStageBytes;
+        tma_load_2d(a_dst, &map_a, kt * slab_elems, m0, &full_bar[s]);
+        tma_load_2d(a_dst + kBM * kSlabBytes, &map_b, kt * slab_elems, n0, &full_bar[s]);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------- MMA issuer ---------------------------------
+    if (lane == 0) {
+      for (int kt = 0; kt < p.k_tiles; ++kt) {
+        const int s = kt % kStages;
+        wait_or_abort(&full_bar[s], (kt / kStages) & 1, abort_flag, p.status, 12);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = gb_smem_u32(ring + (size_t)s * kStageBytes);
+        const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + kBM * kSlabBytes);
+#pragma unroll
+        for (int k = 0; k < kSlabBytes / 32; ++k)       // 32 bytes of K per instruction
+          umma(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), p.idesc, kt > 0 || k > 0, fp8);
+        umma_commit(&empty_bar[s]);                      // stage free once these MMAs have read it
+      }
+      umma_commit(accum_bar);                            // accumulator complete
+    }
+  } else {
+    // ------------------------------- epilogue -----------------------------------
+    wait_or_abort(accum_bar, 0, abort_flag, p.status, 13);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int64_t row = (int64_t)m0 + warp * 32 + lane;
+    const float rs = (p.a_scale && row < p.M ? p.a_scale[row] : 1.0f) * p.global_scale;
+#pragma unroll 1
+    for (int c0 = 0; c0 < kBN; c0 += 32) {
+      uint32_t v[32];
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+          "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+          "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+          : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+            "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+            "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+            "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+          : "r"(taddr));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (row < p.M) {
+        uint16_t* out = p.D + row * p.N + n0 + c0;
+        const int64_t ncol = p.N - (n0 + c0);
+        if (ncol >= 32 && (p.N % 8) == 0) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int c = q * 8 + j * 2;
+              const float s0 = p.b_scale ? p.b_scale[n0 + c0 + c] : 1.0f;
+              const float s1 = p.b_scale ? p.b_scale[n0 + c0 + c + 1] : 1.0f;
+              w[j] = gb_f32_to_bf16_bits(__uint_as_float(v[c]) * rs * s0) |
+                     (gb_f32_to_bf16_bits(__uint_as_float(v[c + 1]) * rs * s1) << 16);
+            }
+            *reinterpret_cast<uint4*>(out + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        } else {
+          for (int c = 0; c < 32 && c < ncol; ++c) {
+            const float s0 = p.b_scale ? p.b_scale[n0 + c0 + c] : 1.0f;
+            out[c] = (uint16_t)gb_f32_to_bf16_bits(__uint_as_float(v[c]) * rs * s0);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
+                 : "memory");
+  }
+}
+
+// ---- per-token E4M3 quantisation of the activations (fp8-grid prefill) ----------------
+__global__ void __launch_bounds__(256)
+fp8_quantize_rows_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale_out,
+                         int64_t K, int scale_rule) {
+  const uint16_t* row = x + (int64_t)blockIdx.x * K;
+  uint8_t* qrow = q + (int64_t)blockIdx.x * K;
+  __shared__ float red[8];
+  __shared__ float s_scale;
+  float amax = 0.0f;
+  for (int64_t i = threadIdx.x; i < K; i += blockDim.x) amax = fmaxf(amax, fabsf(gb_bf16_bits_to_f32(row[i])));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = red[0];
+    for (int w = 1; w < 8; ++w) a = fmaxf(a, red[w]);
+    const float s = scale_rule == GB_SCALE_RULE_DIV ? __fdiv_rn(a, 448.0f) : __fmul_rn(a, 1.0f / 448.0f);
+    s_scale = fmaxf(s, 1.0f / (448.0f * 512.0f));
+    scale_out[blockIdx.x] = s_scale;
+  }
+  __syncthreads();
+  const float scale = s_scale;
+  for (int64_t i = threadIdx.x; i < K; i += blockDim.x) {
+    const float v = gb_bf16_bits_to_f32(row[i]);
+    qrow[i] = (uint8_t)gb_f32_to_e4m3(fminf(fmaxf(__fdiv_rn(v, scale), -448.0f), 448.0f));
+  }
+}
+
+// ---- tensor maps ------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+std::mutex g_encode_mutex;
+EncodeTiledFn g_encode = nullptr;
+
+int get_encoder(EncodeTiledFn* out) {
+  std::lock_guard<std::mutex> lock(g_encode_mutex);
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    GB_CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (!fn || qres != cudaDriverEntryPointSuccess)
+      return gb_fail(GB_ECUDA, "the driver does not export cuTensorMapEncodeTiled");
+    g_encode = (EncodeTiledFn)fn;
+  }
+  *out = g_encode;
+  return GB_OK;
+}
+
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int elem_bytes, int box_rows) {
+  EncodeTiledFn enc;
+  int rc = get_encoder(&enc);
+  if (rc != GB_OK) return rc;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * elem_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)(kSlabBytes / elem_bytes), (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return gb_fail(GB_ECUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return GB_OK;
+}
+
+}  // namespace
+
+int gb_prepare_gemm() {
+  GB_CUDA_OK(cudaFuncSetAttribute((const void*)gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
+  return GB_OK;
+}
+
+extern "C" {
+
+int gb_fp8_quantize_rows(const void* x, void* q, float* scale, int64_t M, int64_t K, int scale_rule, void* stream) {
+  GB_REQUIRE(x && q && scale, "null pointer argument");
+  GB_REQUIRE(M >= 0 && K > 0, "bad shape M=%lld K=%lld", (long long)M, (long long)K);
+  if (M == 0) return GB_OK;
+  fp8_quantize_rows_kernel<<<(unsigned)M, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)x, (uint8_t*)q, scale, K,
+                                                                        scale_rule);
+  GB_LAUNCH_OK("fp8_quantize_rows_kernel");
+  return GB_OK;
+}
+
+int gb_gemm_tn(const void* A, const void* B, void* D, int64_t M, int64_t N, int64_t K, int kind, const float* a_scale,
+               const float* b_scale, float global_scale, void* stream) {
+  GB_REQUIRE(A && B && D, "null pointer argument");
+  GB_REQUIRE(kind == GB_GEMM_BF16 || kind == GB_GEMM_E4M3, "unknown gemm kind %d", kind);
+  const int eb = kind == GB_GEMM_BF16 ? 2 : 1;
+  GB_REQUIRE(M > 0 && N > 0 && K > 0 && (K * eb) % kSlabBytes == 0, "K=%lld must be a multiple of %d elements",
+             (long long)K, kSlabBytes / eb);
+  GB_REQUIRE(((uintptr_t)A & 15u) == 0 && ((uintptr_t)B & 15u) == 0 && ((uintptr_t)D & 15u) == 0,
+             "operands must be 16-byte aligned");
+  GB_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "dimension too large");
+  if (gb_sm_count() <= 0) return gb_fail(GB_ECUDA, "no usable CUDA device: %s", gb_last_error());
+  CUtensorMap map_a, map_b;
+  int rc = make_map(&map_a, A, M, K, eb, kBM);
+  if (rc != GB_OK) return rc;
+  rc = make_map(&map_b, B, N, K, eb, kBN);
+  if (rc != GB_OK) return rc;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.k_tiles = (int)(K * eb / kSlabBytes);
+  p.elem_bytes = eb;
+  // instruction descriptor: fp32 accumulate, A/B format, both K-major, N >> 3, M >> 4
+  p.idesc = (1u << 4) | ((kind == GB_GEMM_BF16 ? 1u : 0u) << 7) | ((kind == GB_GEMM_BF16 ? 1u : 0u) << 10) |
+            ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+  p.a_scale = a_scale; p.b_scale = b_scale;
+  p.global_scale = global_scale == 0.0f ? 1.0f : global_scale;
+  p.D = (uint16_t*)D;
+  p.status = gb_status_word();
+  dim3 grid((unsigned)((N + kBN - 1) / kBN), (unsigned)((M + kBM - 1) / kBM));
+  gemm_tn_kernel<<<grid, kGemmThreads, kGemmSmem, (cudaStream_t)stream>>>(map_a, map_b, p);
+  GB_LAUNCH_OK("gemm_tn_kernel");
+  return GB_OK;
+}
+
+}  // extern "C"

@@ -222,3 +222,35 @@ def moe_combine(y: torch.Tensor, pair_w: torch.Tensor, T: int, topk: int) -> tor
     nat.check(lib.gb_moe_combine(_ptr(y), _ptr(pw), T, topk, H, _ptr(out),
                                  nat.stream_ptr(y.device)), lib)
     return out
+
+
+def fp8_quantize_rows(x: torch.Tensor, scale_rule: str = "recip"):
+    """Per-token E4M3 quantisation: (q [M, K] float8_e4m3fn, scale [M] fp32), x ~ q * scale."""
+    _need_cuda(x)
+    lib = nat.load("FP8 activation quantisation")
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    M, K = x2.shape
+    q = torch.empty((M, K), dtype=torch.uint8, device=x.device)
+    scale = torch.empty((M,), dtype=torch.float32, device=x.device)
+    nat.check(lib.gb_fp8_quantize_rows(_ptr(x2), _ptr(q), _ptr(scale), M, K, _rule(scale_rule),
+                                       nat.stream_ptr(x.device)), lib)
+    return q.view(torch.float8_e4m3fn), scale
+
+
+def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a_scale=None, b_scale=None, global_scale: float = 1.0):
+    """bf16 D[M, N] = scales * A[M, K] . B[N, K]^T on the tcgen05 tensor cores; A and B both bf16
+    or both float8_e4m3fn."""
+    _need_cuda(a, b, a_scale, b_scale)
+    lib = nat.load("prefill tensor-core GEMM")
+    if a.dtype is not b.dtype or a.dtype not in (torch.bfloat16, torch.float8_e4m3fn):
+        raise TypeError("gemm_tn takes two bf16 or two float8_e4m3fn operands")
+    a, b = a.contiguous(), b.contiguous()
+    M, K = a.shape
+    N = b.shape[0]
+    if b.shape[1] != K:
+        raise RuntimeError(f"gemm_tn: K mismatch {K} vs {b.shape[1]}")
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    kind = nat.GEMM_BF16 if a.dtype is torch.bfloat16 else nat.GEMM_E4M3
+    nat.check(lib.gb_gemm_tn(_ptr(a), _ptr(b), _ptr(out), M, N, K, kind, _ptr(a_scale), _ptr(b_scale),
+                             float(global_scale), nat.stream_ptr(a.device)), lib)
+    return out

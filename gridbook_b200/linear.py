@@ -128,22 +128,26 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         return self._apply_prefill(layer, x2).reshape(*x.shape[:-1], N)
 
     def _apply_prefill(self, layer, x2):
-        """M > 16: bucket the activations, expand the layer once into a transient tile and
-        run one dense GEMM over it (the reference's default route,
-        gridbook/linear.py:983-1023,1146-1152,1255-1264)."""
+        """M > 16: expand the layer once into a transient decoded tile and run one tensor-core
+        GEMM over it (tcgen05, accumulator in tensor memory).
+
+        fp4 grid: activations go through the group-16 bucket, the tile is the exact bf16 served
+        weight, kind::f16 MMA — the reference's expand + bf16 GEMM route with its numerics
+        (gridbook/linear.py:983-1023,1146-1152).  fp8 grid: activations are quantised per token to
+        E4M3, the tile is the E4M3 value plane, kind::f8f6f4 MMA, and both scales multiply the
+        fp32 accumulator — the reference's fp8 prefill lanes
+        (gridbook/linear.py:1221-1264; epilogue of gridbook/csrc/cb_fused_gemm.cu:476-486)."""
         from . import ops
         w = layer._cb_weight
         if self.is_fp4:
             xq = kernels.fp4_act_qdq(x2.contiguous(), ops.ACT_SCALE_RULE)
             wt = kernels.expand_fp4_bf16(w)
-        else:
-            xq = kernels.fp8_act_qdq(x2.contiguous(), ops.ACT_SCALE_RULE)
-            wt = (kernels.expand_fp8(w).to(torch.float32) * w.weight_scale[:, None]).to(torch.bfloat16)
-        if w.global_scale == 1.0:
-            return torch.matmul(xq, wt.t())
-        # keep the fp32 accumulator until the epilogue multiplier is in: one bf16 rounding
-        acc = torch.mm(xq, wt.t(), out_dtype=torch.float32)
-        return (acc * w.global_scale).to(torch.bfloat16)
+            layer._cb_route["prefill"] = "expand_fp4_bf16 + gemm_tn(kind::f16)"
+            return kernels.gemm_tn(xq, wt, global_scale=w.global_scale)
+        q, a_scale = kernels.fp8_quantize_rows(x2.contiguous(), ops.ACT_SCALE_RULE)
+        wt = kernels.expand_fp8(w)
+        layer._cb_route["prefill"] = "expand_fp8 + gemm_tn(kind::f8f6f4)"
+        return kernels.gemm_tn(q, wt, a_scale=a_scale, b_scale=w.weight_scale, global_scale=w.global_scale)
 
 
 def _scheme_of(fmt: CBFormat, global_scale: float = 1.0) -> dict:

@@ -130,6 +130,23 @@ GB_API int gb_gemv(const void* x_bf16, int64_t M, const gb_weight* w, int act, i
 GB_API int gb_gemv_static(const void* x_bf16, int64_t M, const gb_weight* w, int act, int scale_rule,
                           void* y_bf16, void* stream);
 
+/* ---- prefill (M > 16): tensor-core GEMM over decoded tiles --------------------------- */
+enum { GB_GEMM_BF16 = 0, GB_GEMM_E4M3 = 1 };
+/* Per-token dynamic E4M3 quantisation of bf16 activations: q[M,K] bytes and scale[M] with
+ * x ~ q * scale; replaces the reference's use of vLLM's dynamic_per_token_scaled_fp8_quant
+ * (gridbook/native_cutlass.py:158-168; arithmetic of gridbook/codec.py:428-437). */
+GB_API int gb_fp8_quantize_rows(const void* x_bf16, void* q_e4m3, float* scale, int64_t M, int64_t K,
+                                int scale_rule, void* stream);
+/* D[M,N] bf16 = bf16( global_scale * a_scale[m] * b_scale[n] * sum_k A[m,k] B[n,k] ), A [M,K] and
+ * B [N,K] row-major in bf16 (GB_GEMM_BF16) or E4M3 bytes (GB_GEMM_E4M3); scale vectors may be
+ * NULL.  K*elem_size must be a multiple of 128 bytes, pointers 16-byte aligned.  tcgen05
+ * kind::f16 / kind::f8f6f4 with the accumulator in tensor memory.  With B = gb_expand_fp8 /
+ * gb_expand_fp4_bf16 of a layer this replaces the reference's expand + GEMM prefill routes and
+ * the scaled epilogue of its fused FP8 lane (gridbook/linear.py:1146-1152,1255-1264;
+ * gridbook/csrc/cb_fused_gemm.cu:476-486). */
+GB_API int gb_gemm_tn(const void* A, const void* B, void* D_bf16, int64_t M, int64_t N, int64_t K, int kind,
+                      const float* a_scale, const float* b_scale, float global_scale, void* stream);
+
 /* ---- routed MoE -------------------------------------------------------------- */
 /* Device-side histogram + exclusive scan + stable expert-major permutation of the
  * P = T*topk routed pairs; replaces the torch chain of gridbook/moe.py:1609-1625 and

@@ -44,12 +44,19 @@ def test_linear_method_decode_and_prefill(dev, name):
     lin = CBLinear(fmt, K, [96, 96], [_tables(fmt, d["cb"][:n]), _tables(fmt, d["cb"][n:])], global_scale=gs)
     ws = None if fmt.is_fp4 else torch.from_numpy(d["weight_scale"])
     lin.load(torch.from_numpy(d["qw"]), ws, dev)
-    for M in (1, 7, 16, 40):
+    for M in (1, 7, 16, 40, 300):
         x = synth.make_activations(M, K, seed=M)
         y = lin(synth.bf16_tensor(x, dev).reshape(1, M, K))
         assert y.shape == (1, M, N)
         ref = oracle_linear(x, d, bucket=True, scale_rule="recip")
-        assert_close_bf16(f32_of(y).reshape(M, N), ref, f"{name} M={M}")
+        if M > 16 and not fmt.is_fp4:
+            # fp8 prefill multiplies both scales into the accumulator (the reference's fp8
+            # prefill epilogue) instead of rounding bf16(value*scale) per weight: acceptance bar
+            got = f32_of(y).reshape(M, N)
+            assert np.linalg.norm(got - ref) / np.linalg.norm(ref) <= 1e-2
+            assert np.abs(got - ref).max() <= 2e-2 * np.abs(ref).max()
+        else:
+            assert_close_bf16(f32_of(y).reshape(M, N), ref, f"{name} M={M}")
 
 
 def test_reference_signature_ops(dev):
