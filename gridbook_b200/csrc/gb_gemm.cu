@@ -2,7 +2,7 @@
 // operands K-major, bf16 x bf16 (kind::f16) or E4M3 x E4M3 (kind::f8f6f4), fp32 accumulators
 // in tensor memory, scaled bf16 epilogue.
 //
-// One CTA computes one 128 x 128 output tile.  Warp 4 (one thread) streams 128-byte-wide
+// One CTA computes one 128 x 256 output tile.  Warp 4 (one thread) streams 128-byte-wide
 // K slabs of A and B into a shared-memory ring with tiled TMA loads (128-byte swizzle);
 // warp 5 (one thread) issues tcgen05.mma on shared-memory matrix descriptors and releases
 // ring stages with tcgen05.commit; warps 0..3 read the accumulator out of tensor memory
@@ -16,11 +16,11 @@
 
 namespace {
 
-constexpr int kBM = 128, kBN = 128;
+constexpr int kBM = 128, kBN = 256;
 constexpr int kSlabBytes = 128;                    // K bytes per row per stage (one swizzle span)
 constexpr int kStageBytes = (kBM + kBN) * kSlabBytes;   // 32 KiB
-constexpr int kStages = 6;
-constexpr int kTmemCols = 128;
+constexpr int kStages = 4;
+constexpr int kTmemCols = 256;
 constexpr int kGemmThreads = 192;
 constexpr int kGemmSmem = kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
 
@@ -95,7 +95,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * kBN;
+  // M tiles vary fastest, so the CTAs resident together share a few B (weight) tiles and
+  // sweep A, which fits L2: the decoded weight tile is read from HBM once.
+  const int m0 = blockIdx.x * kBM, n0 = blockIdx.y * kBN;
   const bool fp8 = p.elem_bytes == 1;
 
   if (threadIdx.x == 0) {
@@ -107,7 +109,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     *abort_flag = 0;
     gb_fence_barrier_init();
   }
-  if (warp == 5) {   // tensor memory for the 128 x 128 fp32 accumulator
+  if (warp == 5) {   // tensor memory for the 128 x 256 fp32 accumulator
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  ::"r"(gb_smem_u32(tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -312,7 +314,7 @@ int gb_gemm_tn(const void* A, const void* B, void* D, int64_t M, int64_t N, int6
   p.global_scale = global_scale == 0.0f ? 1.0f : global_scale;
   p.D = (uint16_t*)D;
   p.status = gb_status_word();
-  dim3 grid((unsigned)((N + kBN - 1) / kBN), (unsigned)((M + kBM - 1) / kBM));
+  dim3 grid((unsigned)((M + kBM - 1) / kBM), (unsigned)((N + kBN - 1) / kBN));
   gemm_tn_kernel<<<grid, kGemmThreads, kGemmSmem, (cudaStream_t)stream>>>(map_a, map_b, p);
   GB_LAUNCH_OK("gemm_tn_kernel");
   return GB_OK;
