@@ -260,6 +260,7 @@ def run_gpu(args):
     barrier()
     ms_kernel = k0.elapsed_time(k1)
     moe = None if args.no_moe else bench_moe(args, device, world, rank)
+    prefill = bench_prefill(args, device) if (world == 1 and not args.no_prefill) else None
     status = _native.device_status(local_rank)
 
     times = torch.tensor([ms_total, ms_e2e, ms_kernel, float(bytes_per_step_local)], dtype=torch.float64,
@@ -310,6 +311,7 @@ def run_gpu(args):
         "clocks": clocks.summary(),
         "device_status": status,
         "moe": moe,
+        "prefill": prefill,
     }
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(args.format, M, seconds=20.0)
@@ -356,9 +358,22 @@ def bench_moe(args, device, world, rank):
         ids, tw = synth.make_routing(T, E, topk, seed=T + 13 * rank)
         x = torch.randn(T, hidden, generator=gen, device=device).to(torch.bfloat16)
         ids_d, tw_d = torch.from_numpy(ids).to(device), torch.from_numpy(tw).to(device)
-        for _ in range(3):
+        def run_layers():
             for m in layers:
                 m(x, tw_d, ids_d)
+
+        for _ in range(3):
+            run_layers()
+        runner = run_layers
+        if world == 1:
+            torch.cuda.synchronize()
+            try:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    run_layers()
+                runner = g.replay
+            except Exception:
+                torch.cuda.synchronize()
         iters, total = 10, 0.0
         for it in range(iters):
             flush.fill_(it)
@@ -367,8 +382,7 @@ def bench_moe(args, device, world, rank):
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for m in layers:
-                m(x, tw_d, ids_d)
+            runner()
             e1.record()
             torch.cuda.synchronize()
             total += e0.elapsed_time(e1)
@@ -381,6 +395,54 @@ def bench_moe(args, device, world, rank):
                         f"format {args.format}, T tokens per rank", "scaling": "weak",
             "parallelism": f"expert-parallel x{world} (NCCL all-to-all)" if world > 1 else "1 GPU",
             "tokens_per_rank": out}
+
+
+# ----------------------------------------------------------------------------- prefill leg
+def bench_prefill(args, device):
+    """Prefill (configuration 2) on the largest projection: gate_up 34816x5120 at M = 2048 through
+    the linear method (bucket / quantise + expand once + tcgen05 GEMM), and the GEMM alone."""
+    import torch
+    from gridbook_b200 import kernels, synth
+    from gridbook_b200.linear import CBLinear
+    fmt, gscale = get_format(args.format)
+    name, parts, K = PROJECTIONS[-2] if len(PROJECTIONS) > 1 else PROJECTIONS[0]
+    N, M = sum(parts), 2048
+    gen = torch.Generator(device=device).manual_seed(5)
+    lin = CBLinear(fmt, K, list(parts), [synth.codebook_tables(fmt, 3)], global_scale=gscale)
+    ws = None if fmt.is_fp4 else (torch.rand(N, generator=gen, device=device) + 0.5) * 0.02
+    lin.load(synth.make_packed_device(fmt, N, K, gen, device), ws, device)
+    x = torch.randn(M, K, generator=gen, device=device).to(torch.bfloat16)
+
+    def timed(fn, reps=5):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    ms_route = timed(lambda: lin(x))
+    w = lin._cb_weight
+    if fmt.is_fp4:
+        a, b = kernels.fp4_act_qdq(x), kernels.expand_fp4_bf16(w)
+        ms_gemm = timed(lambda: kernels.gemm_tn(a, b))
+        peaks, kind = measured_peaks()
+        peak, peak_name = peaks["bf16_tflops"], f"bf16 dense, {kind} (cuBLAS burst)"
+    else:
+        a, sa = kernels.fp8_quantize_rows(x)
+        b = kernels.expand_fp8(w)
+        ms_gemm = timed(lambda: kernels.gemm_tn(a, b, a_scale=sa, b_scale=w.weight_scale))
+        peak, peak_name = 4500.0, "fp8 dense, nominal"
+    flops = 2.0 * M * N * K
+    tf_gemm, tf_route = flops / ms_gemm / 1e9, flops / ms_route / 1e9
+    return {"workload": f"{name} {N}x{K}, M={M}, format {args.format}", "kernel": "gemm_tn_kernel",
+            "gemm_tflops": round(tf_gemm, 1), "route_tflops": round(tf_route, 1),
+            "gemm_ms": round(ms_gemm, 4), "route_ms": round(ms_route, 4),
+            "roofline": {"bound": "tensor", "achieved": round(tf_gemm, 1), "peak": peak, "unit": "TFLOP/s",
+                         "frac": round(tf_gemm / peak, 4), "peak_kind": peak_name}}
 
 # ----------------------------------------------------------------------------- CPU arm
 def cpu_layer_inputs(fmt, gscale, M, seed=0):
@@ -471,6 +533,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-moe", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--only", default=None, choices=[n for n, _, _ in PROJECTIONS],
                     help="restrict the stack to one projection (small profiling captures)")
     args = ap.parse_args()
