@@ -17,13 +17,10 @@
 
 namespace {
 
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * 32;
-constexpr int kTileRows = 8 * kWarps;     // 64 rows per tile, eight per warp
+constexpr int kMaxWarps = 16;             // the literal fast path (128 registers) runs 16 warps, the rest 8
 constexpr int kMaxStages = 4;
 constexpr int kSmemBig = 216 * 1024;      // one CTA per SM
 constexpr int kXBudget = 64 * 1024;
-constexpr int kTaskBytes = 10 * 1024;     // a warp's eight row slices should stay below this
 constexpr uint32_t kExpBias120 = 120u << 7;   // bf16 exponent offset of 2^120
 
 enum Fmt { kFp4Prod2 = 0, kFp4Signed = 1, kFp4Full = 2, kFp8Prod4 = 3, kFp8Prod2 = 4, kNumFmt = 5 };
@@ -54,6 +51,8 @@ struct GemvParams {
   int m_chunk;            // tokens per tile pass (MoE), <= 16
   // tiling
   int ksplit, sb_per_slice, n_sb;
+  int sb_per_chunk;       // a warp streams its rows through the ring in chunks of this many superblocks
+  int warps;              // warps per CTA (8 or 16); a tile is 8 * warps rows
   int n_row_tiles;
   int stages, stage_bytes, row_pitch;
   int x_pitch;            // bytes between activation rows in shared memory
@@ -73,6 +72,7 @@ struct Tile {
   int expert;
   int m0, mcount; // sorted-pair range of this pass (MoE) or [0, M)
   int slice;
+  int chunk, nchunks;   // this step's K chunk of the slice; accumulators live across a tile's chunks
 };
 
 // Every thread of the CTA enumerates the same tile sequence.
@@ -88,17 +88,18 @@ struct TileWalker {
       next_local = blockIdx.x / p.ksplit;
     }
   }
-  __device__ bool next(Tile& t) {
+  __device__ bool next_tile(Tile& t) {
+    const int tile_rows = 8 * p.warps;
     if constexpr (!kMoE) {
       if (next_local >= p.n_row_tiles) return false;
-      t.row0 = next_local * kTileRows;
-      t.nrows = min(kTileRows, (int)(p.N - t.row0));
+      t.row0 = next_local * tile_rows;
+      t.nrows = min(tile_rows, (int)(p.N - t.row0));
       t.expert = 0; t.m0 = 0; t.mcount = p.M;
       t.slice = blockIdx.x % p.ksplit;
       next_local += gridDim.x / p.ksplit;
       return true;
     } else {
-      const int half = p.swiglu ? kTileRows / 2 : kTileRows;
+      const int half = p.swiglu ? tile_rows / 2 : tile_rows;
       while (e < p.E) {
         const int cnt = p.offsets[e + 1] - p.offsets[e];
         const int nch = (cnt + p.m_chunk - 1) / p.m_chunk;
@@ -122,6 +123,22 @@ struct TileWalker {
       return false;
     }
   }
+  // One step = one K chunk of one tile; a tile's chunks come back to back.
+  Tile cur;
+  bool have = false;
+  __device__ bool next(Tile& t) {
+    if (have && cur.chunk + 1 < cur.nchunks) {
+      ++cur.chunk;
+    } else {
+      if (!next_tile(cur)) return false;
+      const int nsb = min(p.sb_per_slice, p.n_sb - cur.slice * p.sb_per_slice);
+      cur.chunk = 0;
+      cur.nchunks = (nsb + p.sb_per_chunk - 1) / p.sb_per_chunk;
+      have = true;
+    }
+    t = cur;
+    return true;
+  }
 };
 
 // Row g (0..7) of warp `warp`'s share of a tile: its first byte in global memory, or
@@ -137,7 +154,7 @@ GB_DEVINL const uint8_t* tile_row_ptr(const GemvParams& p, const Tile& t, int wa
   *out_row = row;
   if (local >= t.nrows) return nullptr;
   return p.qw + (int64_t)t.expert * p.expert_stride + row * p.row_stride +
-         (int64_t)t.slice * p.sb_per_slice * p.fmt.type_size;
+         ((int64_t)t.slice * p.sb_per_slice + (int64_t)t.chunk * p.sb_per_chunk) * p.fmt.type_size;
 }
 
 // shared-memory loads by 32-bit shared address
@@ -378,7 +395,8 @@ GB_DEVINL void stage_lut(const GemvParams& p, uint8_t* lut, int64_t cb_off, int 
 
 // Lanes 0..7 of a warp each copy one of the warp's eight rows of tile t into ring stage `dst`.
 GB_DEVINL void issue_task(const GemvParams& p, const Tile& t, int warp, int lane, uint8_t* dst, uint64_t* bar) {
-  const int nsb = min(p.sb_per_slice, p.n_sb - t.slice * p.sb_per_slice);
+  const int nsb_slice = min(p.sb_per_slice, p.n_sb - t.slice * p.sb_per_slice);
+  const int nsb = min(p.sb_per_chunk, nsb_slice - t.chunk * p.sb_per_chunk);
   int64_t row;
   const uint8_t* src = lane < 8 ? tile_row_ptr(p, t, warp, lane, &row) : nullptr;
   uint32_t bytes = 0, head = 0;
@@ -395,7 +413,8 @@ GB_DEVINL void issue_task(const GemvParams& p, const Tile& t, int warp, int lane
 }
 
 template <int kFmt, bool kMoE, bool kWide, bool kLit>
-__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant__ GemvParams p) {
+__global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_constant__ GemvParams p) {
+  const int kThreads = blockDim.x;
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);             // [warps][kMaxStages]
   uint16_t* sub_tab = reinterpret_cast<uint16_t*>(smem + 512);        // 16 bf16 two-tier multipliers
@@ -407,7 +426,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
   constexpr bool fp8 = (kFmt == kFp8Prod4 || kFmt == kFp8Prod2);
 
   if (tid == 0) {
-    for (int s = 0; s < kWarps * kMaxStages; ++s) gb_mbar_init(&full_bar[s], 1);
+    for (int s = 0; s < kMaxWarps * kMaxStages; ++s) gb_mbar_init(&full_bar[s], 1);
     gb_fence_barrier_init();
   }
   if (tid < 16 && p.fmt.scale_coding == GB_SCALE_V2)
@@ -456,10 +475,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
   int x_expert = -1, x_m0 = -1, cur_slice = -1;
   TileWalker<kMoE> walk(p);
   Tile t;
+  float acc0[4], acc1[4];
+  float accx[6][4];              // further independent chains: an MMA result is ~30 cycles away
   for (int it = 0; walk.next(t); ++it) {
     const int s = it % p.stages;
     const int sb0 = t.slice * p.sb_per_slice;
-    const int nsb = min(p.sb_per_slice, p.n_sb - sb0);
+    const int nsb_slice = min(p.sb_per_slice, p.n_sb - sb0);
+    const int nsb = min(p.sb_per_chunk, nsb_slice - t.chunk * p.sb_per_chunk);   // superblocks of this step
 
     // ---- this lane's row, and the codebook block(s) of the task's rows ----
     int64_t out_row;
@@ -483,7 +505,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
         lut_off = off_lo;
       }
       if (restage_x) {
-        const int vec_per_row = nsb * 32;     // 16-byte vectors of this K slice
+        const int vec_per_row = nsb_slice * 32;     // 16-byte vectors of this K slice
         for (int i = tid; i < t.mcount * vec_per_row; i += kThreads) {
           const int m = i / vec_per_row, v = i - m * vec_per_row;
           int64_t src_row = m;
@@ -515,15 +537,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
       if (row_ok) row_scale = p.weight_scale[(int64_t)t.expert * p.N + out_row];
     }
 
-    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
-    float accx[6][4] = {};         // further independent chains: an MMA result is ~30 cycles away
+    if (t.chunk == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc0[i] = 0.f; acc1[i] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 6; ++j) accx[j][i] = 0.f;
+      }
+    }
     // MMA rows without an activation row this pass re-read the last live row (a broadcast,
     // no extra shared-memory traffic): their output rows are simply never stored.  Lanes whose
     // weight row lies past the edge decode the task's first row, likewise unused.  The loop
     // below is branch-free.
     const uint32_t x_lane = (uint32_t)t4 * 16u;
-    uint32_t xa_s = xs_s + (uint32_t)min(g, t.mcount - 1) * (uint32_t)p.x_pitch + x_lane;
-    uint32_t xb_s = xs_s + (uint32_t)min(g + 8, t.mcount - 1) * (uint32_t)p.x_pitch + x_lane;
+    const uint32_t x_chunk = (uint32_t)(t.chunk * p.sb_per_chunk) * 512u;
+    uint32_t xa_s = xs_s + (uint32_t)min(g, t.mcount - 1) * (uint32_t)p.x_pitch + x_lane + x_chunk;
+    uint32_t xb_s = xs_s + (uint32_t)min(g + 8, t.mcount - 1) * (uint32_t)p.x_pitch + x_lane + x_chunk;
     const uint32_t xa_step = 512u, xb_step = 512u;
     if (!row_ok) sbp = ring_s + (uint32_t)s * (uint32_t)p.stage_bytes + warp_head;
 
@@ -627,11 +656,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
 #endif
         }
       }
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        acc0[i] += accx[0][i] + accx[2][i] + accx[4][i];
-        acc1[i] += accx[1][i] + accx[3][i] + accx[5][i];
-      }
     } else {
       mixed_codebook_task<fp8>(p, d, sbp, nsb, my_cb_off, row_scale, xa_s, xb_s, xa_step, xb_step, sub_s, t4,
                                acc0, acc1);
@@ -643,10 +667,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     if (more) issue_task(p, ta, warp, lane, my_ring + (size_t)s * p.stage_bytes, &my_bar[s]);
 #endif
 
+    if (t.chunk + 1 < t.nchunks) continue;          // more K chunks of this tile to come
+
     // ---- results: lane (g, t4) holds C[m = g (+8)][n = 2 t4 (+1)], n = row inside the task ----
-    float c[4];
+    float c[4], raw[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) c[i] = (acc0[i] + acc1[i]) * p.global_scale;
+    for (int i = 0; i < 4; ++i) {
+      raw[i] = (acc0[i] + acc1[i]) + (accx[0][i] + accx[1][i]) + (accx[2][i] + accx[3][i]) + (accx[4][i] + accx[5][i]);
+      c[i] = raw[i] * p.global_scale;
+    }
     if (p.swiglu) {
       // rows 0..3 of the task are gate rows, 4..7 the matching up rows held two lanes on
       float up[4];
@@ -672,7 +701,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
         if (m < t.mcount && 8 * warp + n < t.nrows) {
           const int64_t row = (int64_t)t.row0 + 8 * warp + n;
           if (p.ksplit > 1) {
-            atomicAdd(p.ws + (int64_t)m * p.N + row, acc0[i] + acc1[i]);
+            atomicAdd(p.ws + (int64_t)m * p.N + row, raw[i]);
           } else {
             int64_t orow = m;
             if constexpr (kMoE) orow = p.order[t.m0 + m];
@@ -734,6 +763,8 @@ int classify(const gb_format& f, int* out, bool* wide) {
 // the K slicing of the dense case so that the tiles cover the machine.
 int plan(GemvParams& p, int m_rows, bool moe, int sms, size_t* smem_bytes) {
   p.n_sb = (int)(p.K / 256);
+  p.warps = literal_aligned(p) ? 16 : 8;
+  const int tile_rows = 8 * p.warps;
   p.split = gb_make_split(p.fmt.k_bits, p.fmt.mode == GB_MODE_PRODUCT ? p.fmt.n_sub : 1);
   p.cb_elems = (int)gb_codebook_elems(p.fmt);
   // The literal fast path keeps eight copies of every 16-byte entry (lane l reads copy l % 8), so
@@ -743,16 +774,15 @@ int plan(GemvParams& p, int m_rows, bool moe, int sms, size_t* smem_bytes) {
   if (p.lut_bytes > 72 * 1024)
     return gb_fail(GB_EUNSUPPORTED, "codebook of %d entries does not fit the shared-memory table", p.cb_elems);
   p.x_rows = m_rows;
-  const int half = p.swiglu ? kTileRows / 2 : kTileRows;
+  const int half = p.swiglu ? tile_rows / 2 : tile_rows;
   const int64_t rows_out = p.swiglu ? p.N / 2 : p.N;
   p.n_row_tiles = (int)((rows_out + half - 1) / half);
-  // K slices: (a) the staged activation rows fit their budget, (b) a warp's eight row slices
-  // stay small enough for a multi-stage ring, (c) dense only: enough tiles to cover the SMs.
+  // K slices (partial sums added atomically): (a) the staged activation rows must fit their
+  // budget, (b) dense only: enough tiles to cover the SMs.
   int want = 1;
   while ((int64_t)p.x_rows * (((p.n_sb + want - 1) / want) * 512 + 64) > kXBudget) ++want;
-  while ((int64_t)8 * ((p.n_sb + want - 1) / want) * p.fmt.type_size > kTaskBytes && want < p.n_sb) ++want;
   if (!moe) {
-    while (p.n_row_tiles * want < 2 * sms && want < p.n_sb && (p.n_sb + want) / (want + 1) >= 2) ++want;
+    while (2 * p.n_row_tiles * want < 3 * sms && want < p.n_sb && (p.n_sb + want) / (want + 1) >= 2) ++want;
   } else if (want > 1) {
     return gb_fail(GB_EUNSUPPORTED, "K=%lld is too wide for the routed decode kernel at %d rows per pass",
                    (long long)p.K, m_rows);
@@ -760,18 +790,25 @@ int plan(GemvParams& p, int m_rows, bool moe, int sms, size_t* smem_bytes) {
   p.sb_per_slice = (p.n_sb + want - 1) / want;
   p.ksplit = (p.n_sb + p.sb_per_slice - 1) / p.sb_per_slice;
   p.x_pitch = p.sb_per_slice * 512 + 64;
-  // one row's slice, plus the alignment head and a tail the word-wise extraction may touch,
-  // on a pitch that is 16 mod 32 so the eight rows of a task start in different banks
-  const int64_t slice_bytes = (int64_t)p.sb_per_slice * p.fmt.type_size;
-  p.row_pitch = (int)(((slice_bytes + 15 + 16 + 31) & ~31ll) + 16);
-  p.stage_bytes = (8 * p.row_pitch + 127) & ~127;
+  // Ring geometry.  A stage holds one K chunk of a warp's eight rows: per row the chunk's
+  // bytes plus the alignment head and a tail the word-wise extraction may touch, on a pitch
+  // that is 16 mod 32 so the eight rows start in different banks.  The chunk is the largest
+  // that leaves every warp kMaxStages stages.
   const int64_t fixed = 1280 + p.lut_bytes + (int64_t)p.x_rows * p.x_pitch;
-  const int stages = (int)((kSmemBig - fixed) / ((int64_t)kWarps * p.stage_bytes));
+  const int64_t per_warp = (kSmemBig - fixed) / p.warps;
+  auto pitch_of = [&](int nsb) { return (int)((((int64_t)nsb * p.fmt.type_size + 15 + 16 + 31) & ~31ll) + 16); };
+  auto stage_of = [&](int nsb) { return (8 * pitch_of(nsb) + 127) & ~127; };
+  int chunk = p.sb_per_slice;
+  while (chunk > 1 && (int64_t)kMaxStages * stage_of(chunk) > per_warp) --chunk;
+  int stages = (int)(per_warp / stage_of(chunk));
   if (stages < 2)
-    return gb_fail(GB_EUNSUPPORTED, "task of %d bytes leaves no room for a two-stage ring (fixed %lld bytes)",
-                   p.stage_bytes, (long long)fixed);
+    return gb_fail(GB_EUNSUPPORTED, "a one-superblock stage of %d bytes leaves no room for a two-stage ring "
+                   "(fixed %lld bytes)", stage_of(chunk), (long long)fixed);
+  p.sb_per_chunk = chunk;
+  p.row_pitch = pitch_of(chunk);
+  p.stage_bytes = stage_of(chunk);
   p.stages = stages > kMaxStages ? kMaxStages : stages;
-  *smem_bytes = (size_t)(fixed + (int64_t)kWarps * p.stages * p.stage_bytes);
+  *smem_bytes = (size_t)(fixed + (int64_t)p.warps * p.stages * p.stage_bytes);
   return GB_OK;
 }
 
@@ -859,7 +896,7 @@ int gb_gemv(const void* x, int64_t M, const gb_weight* w, int act, int scale_rul
   if (grid > tiles) grid = tiles;
   grid = (grid / p.ksplit) * p.ksplit;
   if (grid < p.ksplit) grid = p.ksplit;
-  pick_kernel(fmt, false, wide, literal_aligned(p))<<<grid, kThreads, smem, stream>>>(p);
+  pick_kernel(fmt, false, wide, literal_aligned(p))<<<grid, 32 * p.warps, smem, stream>>>(p);
   GB_LAUNCH_OK("gemv_kernel");
   if (p.ksplit > 1) {
     const int64_t total = M * w->rows;
@@ -914,7 +951,7 @@ int gb_moe_gemv(const void* x, const int32_t* x_row, const gb_weight* w, int64_t
   size_t smem = 0;
   rc = plan(p, mc, true, sms, &smem);
   if (rc != GB_OK) return rc;
-  pick_kernel(fmt, true, wide, literal_aligned(p))<<<sms, kThreads, smem, stream>>>(p);
+  pick_kernel(fmt, true, wide, literal_aligned(p))<<<sms, 32 * p.warps, smem, stream>>>(p);
   GB_LAUNCH_OK("gemv_kernel (routed)");
   return GB_OK;
 }
