@@ -42,6 +42,14 @@ int gb_check_format(const gb_format& f, int64_t K);
 int gb_check_weight(const gb_weight* w);
 int gb_prepare_kernels();          // per-device function attributes of the big kernels
 int gb_prepare_gemm();
+int gb_prepare_dot();
+int gb_tensor_map_bytes_2d(void* map_out, const void* base, uint64_t inner_bytes, uint64_t rows,
+                           uint64_t pitch_bytes, uint32_t box_bytes, uint32_t box_rows);
+// M = 1 literal-format linear by per-column inner-product tables (gb_gemv_dot.cu); GB_EUNSUPPORTED when
+// the shape or layout is not its own, and the caller falls back to the MMA kernel.
+int gb_gemv_dot(const void* x, const gb_weight* w, int act, int scale_rule, void* y, void* workspace,
+                int64_t workspace_bytes, void* stream);
+int64_t gb_gemv_dot_workspace_bytes(int64_t N, int64_t K);
 
 // ---------------------------------------------------------------------------
 // scalar formats
@@ -79,6 +87,44 @@ GB_DEVINL uint32_t gb_f32_to_e4m3(float f) {
     r = (u >> 20) - (120u << 3);    // rebias exponent 127 -> 7
   }
   return (r & 0x7Fu) | sign;
+}
+
+// Round-to-nearest on the signed E2M1 grid {0, +-.5, +-1, +-1.5, +-2, +-3, +-4, +-6} with the
+// reference's tie rule (gridbook/codec.py:248-260): the upper neighbour wins only when it is
+// STRICTLY closer, so an exact midpoint goes to the lower (more negative) rung.
+GB_DEVINL float gb_e2m1_rtn(float v) {
+  const float grid[15] = {-6.0f, -4.0f, -3.0f, -2.0f, -1.5f, -1.0f, -0.5f, 0.0f,
+                          0.5f,  1.0f,  1.5f,  2.0f,  3.0f,  4.0f,  6.0f};
+  int idx = 15;  // first rung >= v  (bucketize, right = false)
+#pragma unroll
+  for (int i = 14; i >= 0; --i)
+    if (grid[i] >= v) idx = i;
+  const float lo = grid[idx > 0 ? idx - 1 : 0];
+  const float hi = grid[idx < 15 ? idx : 14];
+  return fabsf(__fsub_rn(hi, v)) < fabsf(__fsub_rn(v, lo)) ? hi : lo;
+}
+
+// Group-16 E2M1 bucket of sixteen bf16 values (eight packed words), in place.
+GB_DEVINL void gb_fp4_group16_qdq(uint32_t (&w)[8], int scale_rule) {
+  float v[16];
+  float amax = 0.0f;
+  bool has_nan = false;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[2 * i] = gb_bf16_bits_to_f32(w[i] & 0xFFFFu);
+    v[2 * i + 1] = gb_bf16_bits_to_f32(w[i] >> 16);
+    amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+    has_nan |= isnan(v[2 * i]) || isnan(v[2 * i + 1]);
+  }
+  amax = fmaxf(amax, 1e-8f);
+  float scale = scale_rule == GB_SCALE_RULE_DIV ? __fdiv_rn(amax, 6.0f) : __fmul_rn(amax, 1.0f / 6.0f);
+  if (has_nan) scale = __int_as_float(0x7FC00000);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float q0 = __fmul_rn(gb_e2m1_rtn(__fdiv_rn(v[2 * i], scale)), scale);
+    const float q1 = __fmul_rn(gb_e2m1_rtn(__fdiv_rn(v[2 * i + 1], scale)), scale);
+    w[i] = gb_f32_to_bf16_bits(q0) | (gb_f32_to_bf16_bits(q1) << 16);
+  }
 }
 
 // ---------------------------------------------------------------------------

@@ -11,23 +11,6 @@ constexpr int kThreads = 256;
 // ---------------------------------------------------------------------------
 // Activation buckets (gridbook/codec.py:248-260, 428-437)
 // ---------------------------------------------------------------------------
-// Signed E2M1 grid, ascending; +0 and -0 are one rung.
-__device__ __constant__ float kE2M1Grid[15] = {-6.0f, -4.0f, -3.0f, -2.0f, -1.5f, -1.0f, -0.5f, 0.0f,
-                                               0.5f,  1.0f,  1.5f,  2.0f,  3.0f,  4.0f,  6.0f};
-
-// Round-to-nearest on the signed grid with the reference's tie rule: the upper
-// neighbour wins only when it is STRICTLY closer, so an exact midpoint goes to
-// the lower (more negative) rung.
-GB_DEVINL float e2m1_rtn(float v) {
-  int idx = 15;  // first rung >= v  (bucketize, right = false)
-#pragma unroll
-  for (int i = 14; i >= 0; --i)
-    if (kE2M1Grid[i] >= v) idx = i;
-  const float lo = kE2M1Grid[idx > 0 ? idx - 1 : 0];
-  const float hi = kE2M1Grid[idx < 15 ? idx : 14];
-  return fabsf(__fsub_rn(hi, v)) < fabsf(__fsub_rn(v, lo)) ? hi : lo;
-}
-
 // One thread per group of 16: two 16-byte loads, amax, scale, 16 roundings.
 __global__ void __launch_bounds__(kThreads)
 fp4_group16_qdq_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out,
@@ -35,29 +18,9 @@ fp4_group16_qdq_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ ou
   const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (g >= n_groups) return;
   const uint4* src = reinterpret_cast<const uint4*>(x + g * 16);
-  uint4 raw[2] = {src[0], src[1]};
-  const uint32_t* w = reinterpret_cast<const uint32_t*>(raw);
-  float v[16];
-  float amax = 0.0f;
-  bool has_nan = false;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    v[2 * i] = gb_bf16_bits_to_f32(w[i] & 0xFFFFu);
-    v[2 * i + 1] = gb_bf16_bits_to_f32(w[i] >> 16);
-    amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
-    has_nan |= isnan(v[2 * i]) || isnan(v[2 * i + 1]);
-  }
-  amax = fmaxf(amax, 1e-8f);
-  float scale = scale_rule == GB_SCALE_RULE_DIV ? __fdiv_rn(amax, 6.0f)
-                                                : __fmul_rn(amax, 1.0f / 6.0f);
-  if (has_nan) scale = __int_as_float(0x7FC00000);
-  uint32_t packed[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float q0 = __fmul_rn(e2m1_rtn(__fdiv_rn(v[2 * i], scale)), scale);
-    const float q1 = __fmul_rn(e2m1_rtn(__fdiv_rn(v[2 * i + 1], scale)), scale);
-    packed[i] = gb_f32_to_bf16_bits(q0) | (gb_f32_to_bf16_bits(q1) << 16);
-  }
+  const uint4 r0 = src[0], r1 = src[1];
+  uint32_t packed[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+  gb_fp4_group16_qdq(packed, scale_rule);
   uint4* dst = reinterpret_cast<uint4*>(out + g * 16);
   dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
   dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);

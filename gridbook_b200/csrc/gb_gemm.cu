@@ -270,6 +270,24 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int el
 
 }  // namespace
 
+// Plain (unswizzled) byte tensor map over [rows][pitch_bytes], for kernels that stream
+// row slices of a packed weight matrix.  `map_out` points at a CUtensorMap.
+int gb_tensor_map_bytes_2d(void* map_out, const void* base, uint64_t inner_bytes, uint64_t rows,
+                           uint64_t pitch_bytes, uint32_t box_bytes, uint32_t box_rows) {
+  EncodeTiledFn enc;
+  int rc = get_encoder(&enc);
+  if (rc != GB_OK) return rc;
+  const cuuint64_t dims[2] = {(cuuint64_t)inner_bytes, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)pitch_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc((CUtensorMap*)map_out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
+                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return gb_fail(GB_ECUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return GB_OK;
+}
+
 int gb_prepare_gemm() {
   GB_CUDA_OK(cudaFuncSetAttribute((const void*)gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
   return GB_OK;

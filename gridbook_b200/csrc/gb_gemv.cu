@@ -842,7 +842,9 @@ extern "C" {
 // Room for the bucketed activations (fused `act`) plus the fp32 partial sums of a
 // K-sliced launch; an upper bound, valid for every format.
 int64_t gb_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-  return ((M * K * 2 + 255) & ~255ll) + M * N * (int64_t)sizeof(float);
+  const int64_t mma_path = ((M * K * 2 + 255) & ~255ll) + M * N * (int64_t)sizeof(float);
+  const int64_t dot_path = gb_gemv_dot_workspace_bytes(N, K);     // M = 1, literal format
+  return mma_path > dot_path ? mma_path : dot_path;
 }
 
 int gb_gemv(const void* x, int64_t M, const gb_weight* w, int act, int scale_rule, void* y,
@@ -855,6 +857,11 @@ int gb_gemv(const void* x, int64_t M, const gb_weight* w, int act, int scale_rul
   GB_REQUIRE(act == GB_ACT_NONE || act == GB_ACT_FP4_GROUP16 || act == GB_ACT_FP8_TOKEN, "unknown act %d", act);
   const int sms = gb_sm_count();
   if (sms <= 0) return gb_fail(GB_ECUDA, "no usable CUDA device: %s", gb_last_error());
+  if (M == 1) {
+    // one activation row of the literal format: inner-product tables instead of per-weight expansion
+    rc = gb_gemv_dot(x, w, act, scale_rule, y, workspace, workspace_bytes, stream_);
+    if (rc != GB_EUNSUPPORTED) return rc;
+  }
   int fmt;
   bool wide;
   rc = classify(w->fmt, &fmt, &wide);

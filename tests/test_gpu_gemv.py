@@ -157,3 +157,25 @@ def test_moe_literal_and_fp8_and_mixed(dev):
         got, ref = _moe_case(dev, _fmt(f13), _fmt(f2), E=8, hidden=512, inter=256, T=6, topk=2, seed=3)
         rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
         assert rel <= 1e-2, (f13, f2, rel)
+
+
+@pytest.mark.parametrize("N,K", [(512, 1024), (1000, 2304), (2048, 5120), (5120, 4352)])
+def test_literal_single_row_table_kernel(dev, N, K):
+    """M = 1 on the literal format with enough rows takes the inner-product-table kernel: ragged
+    row count, a last K slice shorter than four superblocks, padded row stride, bucket fused or
+    applied beforehand, including subnormal and zero scale bytes."""
+    from gridbook_b200 import kernels, synth
+    fmt = _fmt("lit")
+    d = synth.make_linear(fmt, N, K, seed=N + K, global_scale=1.0 / 448.0)
+    qw = d["qw"].reshape(N, K // 256, 48)
+    qw[::7, 0, 32:40] = np.arange(8, dtype=np.uint8)          # E4M3 zero and subnormal scales
+    d["qw"] = qw.reshape(N, -1)
+    x = synth.make_activations(1, K, seed=3)
+    ref = oracle_linear(x, d, bucket=True, scale_rule="recip")
+    for pad in (False, True):
+        w = synth.to_device_weight(d, dev, pad_rows=pad)
+        y = kernels.gemv(synth.bf16_tensor(x, dev), w, act="fp4")
+        assert_close_bf16(f32_of(y), ref, f"fused bucket pad={pad}")
+        xq = O.act_bucket(x, "fp4", "recip")
+        y2 = kernels.gemv(synth.bf16_tensor(xq, dev), w)
+        assert torch.equal(y, y2)

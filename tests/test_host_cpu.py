@@ -59,6 +59,7 @@ def test_argument_validation_without_a_device():
     rc = lib.gb_expand_fp4_bf16(ctypes.byref(w), 0, 8, ctypes.c_void_p(1), None)
     assert rc == 1 and b"multiple of 256" in lib.gb_last_error()
     assert lib.gb_gemv_workspace_bytes(16, 1024, 512) == 16 * 512 * 2 + 16 * 1024 * 4
+    assert lib.gb_gemv_workspace_bytes(1, 4096, 8192) == 8 * 4096 * 4      # M = 1: one slot per K slice
 
 
 def test_kernels_refuse_cpu_tensors():
