@@ -51,10 +51,18 @@ GB_DEVINL uint32_t lds_b16(uint32_t a) {
   asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1]; cvt.u32.u16 %0, t; }" : "=r"(v) : "r"(a));
   return v;
 }
-GB_DEVINL uint32_t lds_b8(uint32_t a) {
-  uint32_t v;
-  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
-  return v;
+// One superblock of one row for this lane's group: two table lookups, their sum, times the
+// group's scale.  The scale byte is loaded sign-extended, so one shift and one mask put its
+// exponent/mantissa into the fp32 fields (value * 2^-120, subnormal codes included) and its
+// sign into bit 31; the table carries the compensating 2^100 so products stay normal.
+GB_DEVINL float dot_superblock(uint32_t sbp, uint32_t tabA, uint32_t tabB, int l, uint32_t sel, float acc) {
+  const uint32_t idx2 = __byte_perm(lds_b16(sbp + 2u * l), 0u, sel);       // (code A) | (code B) << 8
+  const float tA = lds_f32(tabA + ((idx2 & 0xFFu) << 7));
+  const float tB = lds_f32(tabB + ((idx2 >> 8) << 7));
+  int32_t sc;
+  asm volatile("ld.shared.s8 %0, [%1];" : "=r"(sc) : "r"(sbp + 32u + l));
+  const float f = __uint_as_float(((uint32_t)sc << 20) & 0x87F00000u);
+  return fmaf(tA + tB, f, acc);
 }
 
 __global__ void __launch_bounds__(kDotThreads, 1)
@@ -124,16 +132,19 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
       float d[4] = {0.f, 0.f, 0.f, 0.f};
       gb_mma_bf16_16816(d, a, b0, 0u);
       float* row_lo = table + ((s * 256 + c_lo) * 32 + pblk * 8 + 2 * t);
-      *reinterpret_cast<float2*>(row_lo) = make_float2(d[0], d[1]);
-      *reinterpret_cast<float2*>(row_lo + 8 * 32) = make_float2(d[2], d[3]);
+      *reinterpret_cast<float2*>(row_lo) = make_float2(d[0] * 0x1p100f, d[1] * 0x1p100f);
+      *reinterpret_cast<float2*>(row_lo + 8 * 32) = make_float2(d[2] * 0x1p100f, d[3] * 0x1p100f);
     }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
 
   // ---- stream the rows ----
   const int h = lane >> 4, l = lane & 15;
-  const uint32_t table_s = gb_smem_u32(table);
-  const uint32_t posA = (uint32_t)(2 * l + h), posB = (uint32_t)(2 * l + 1 - h);   // half-warps swap the order
+  // Half-warp 0 looks up position 2l then 2l+1, half-warp 1 the other way round (its two index
+  // bytes are swapped once with a byte permute), so the 32 lanes of a lookup hit 32 banks.
+  const uint32_t sel = h ? 0x4401u : 0x4410u;
+  const uint32_t baseA = gb_smem_u32(table) + (uint32_t)(2 * l + h) * 4u;
+  const uint32_t baseB = gb_smem_u32(table) + (uint32_t)(2 * l + 1 - h) * 4u;
   const uint32_t ring_s = gb_smem_u32(ring);
   float* my_ws = p.ws + (int64_t)slice * p.N;
   for (int st = 0; st < n_stages; ++st) {
@@ -142,25 +153,18 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
 #pragma unroll
     for (int step = 0; step < 2; ++step) {
       const int row_local = 4 * warp + 2 * step + h;
-      uint32_t sbp = ring_s + (uint32_t)s * kStageBytes + (uint32_t)row_local * kRowBytes;
+      const uint32_t rowp = ring_s + (uint32_t)s * kStageBytes + (uint32_t)row_local * kRowBytes;
       float acc = 0.f;
-      for (int sb = 0; sb < ns; ++sb, sbp += 48u) {
-        const uint32_t idx2 = lds_b16(sbp + 2u * l);
-        const uint32_t c0 = idx2 & 0xFFu, c1 = idx2 >> 8;
-        const uint32_t cA = h ? c1 : c0, cB = h ? c0 : c1;
-        const float tA = lds_f32(table_s + ((((uint32_t)sb * 256u + cA) * 32u + posA) << 2));
-        const float tB = lds_f32(table_s + ((((uint32_t)sb * 256u + cB) * 32u + posB) << 2));
-        const uint32_t sc = lds_b8(sbp + 32u + l);
-        // E4M3 byte -> fp32: exponent and mantissa land in the fp32 fields, 2^120 rebiases (and
-        // renormalises the subnormal codes); bit 7 is the sign
-        float f = __uint_as_float((sc & 0x7Fu) << 20) * 0x1p120f;
-        f = (sc & 0x80u) ? -f : f;
-        acc = fmaf(tA + tB, f, acc);
+      if (ns == kS) {
+#pragma unroll
+        for (int sb = 0; sb < kS; ++sb) acc = dot_superblock(rowp + sb * 48, baseA + sb * 32768, baseB + sb * 32768, l, sel, acc);
+      } else {
+        for (int sb = 0; sb < ns; ++sb) acc = dot_superblock(rowp + sb * 48, baseA + sb * 32768, baseB + sb * 32768, l, sel, acc);
       }
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       const int64_t row = row_begin + (int64_t)st * kStageRows + row_local;
-      if (l == 0 && row < row_end) my_ws[row] = acc;
+      if (l == 0 && row < row_end) my_ws[row] = acc * 0x1p20f;       // table entries carry 2^100, scales 2^-120
     }
     __syncwarp();
     if (lane == 0) gb_mbar_arrive(&empty_bar[s]);
