@@ -58,6 +58,7 @@ struct GemvParams {
   int x_pitch;            // bytes between activation rows in shared memory
   int x_rows;             // activation rows staged (1..16); MMA rows beyond them are zero
   int lut_bytes;
+  int etab_bytes;         // routed: shared-memory bytes of the per-expert tile prefix and offsets
   int lut_rep;            // copies of each 16-byte table entry (1 or 8): lane l reads copy l % 8, so the
                           // eight lanes of a quarter-warp never collide on a bank
   // outputs
@@ -81,7 +82,9 @@ struct TileWalker {
   const GemvParams& p;
   int next_local;   // dense: next row-tile index; MoE: next global tile index for this CTA
   int e, base;      // MoE: current expert and the global index of its first tile
-  __device__ explicit TileWalker(const GemvParams& pp) : p(pp) {
+  const int* tile_base;   // MoE, shared memory: [E + 1] first global tile index of every expert
+  const int* offs;        // MoE, shared memory: [E + 1] copy of the routing offsets
+  __device__ TileWalker(const GemvParams& pp, const int* tb, const int* of) : p(pp), tile_base(tb), offs(of) {
     if constexpr (kMoE) {
       next_local = blockIdx.x; e = 0; base = 0;
     } else {
@@ -100,25 +103,28 @@ struct TileWalker {
       return true;
     } else {
       const int half = p.swiglu ? tile_rows / 2 : tile_rows;
-      while (e < p.E) {
-        const int cnt = p.offsets[e + 1] - p.offsets[e];
-        const int nch = (cnt + p.m_chunk - 1) / p.m_chunk;
-        const int ntiles = nch * p.n_row_tiles;
-        if (next_local < base + ntiles) {
-          const int local = next_local - base;
-          const int ch = local / p.n_row_tiles, rt = local - ch * p.n_row_tiles;
-          const int rows_out = p.swiglu ? (int)(p.N / 2) : (int)p.N;
-          t.row0 = rt * half;
-          t.nrows = min(half, rows_out - t.row0);
-          t.expert = e;
-          t.m0 = p.offsets[e] + ch * p.m_chunk;
-          t.mcount = min(p.m_chunk, cnt - ch * p.m_chunk);
-          t.slice = 0;
-          next_local += gridDim.x;
-          return true;
-        }
-        base += ntiles;
-        ++e;
+      if (next_local >= tile_base[p.E]) return false;
+      // the expert whose tile range holds next_local: the last e with tile_base[e] <= next_local
+      // (experts without tokens have empty ranges and are skipped by the search)
+      int lo = e, hi = p.E;
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (tile_base[mid] <= next_local) lo = mid; else hi = mid;
+      }
+      e = lo;
+      {
+        const int cnt = offs[e + 1] - offs[e];
+        const int local = next_local - tile_base[e];
+        const int ch = local / p.n_row_tiles, rt = local - ch * p.n_row_tiles;
+        const int rows_out = p.swiglu ? (int)(p.N / 2) : (int)p.N;
+        t.row0 = rt * half;
+        t.nrows = min(half, rows_out - t.row0);
+        t.expert = e;
+        t.m0 = offs[e] + ch * p.m_chunk;
+        t.mcount = min(p.m_chunk, cnt - ch * p.m_chunk);
+        t.slice = 0;
+        next_local += gridDim.x;
+        return true;
       }
       return false;
     }
@@ -418,7 +424,9 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);             // [warps][kMaxStages]
   uint16_t* sub_tab = reinterpret_cast<uint16_t*>(smem + 512);        // 16 bf16 two-tier multipliers
-  uint8_t* lut = smem + 1280;
+  int* tile_base_s = reinterpret_cast<int*>(smem + 1280);             // routed: [E + 1] tile prefix, [E + 1] offsets
+  int* offs_s = tile_base_s + (p.E + 1);
+  uint8_t* lut = smem + 1280 + p.etab_bytes;
   uint8_t* xs = lut + p.lut_bytes;
   uint8_t* rings = xs + p.x_rows * p.x_pitch;
 
@@ -431,6 +439,29 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
   }
   if (tid < 16 && p.fmt.scale_coding == GB_SCALE_V2)
     sub_tab[tid] = (uint16_t)(__float_as_uint(p.compose[127 * 16 + tid]) >> 16);   // T[c], exact in bf16
+  if constexpr (kMoE) {
+    // Every CTA walks the same global tile list; build its per-expert prefix once, in shared
+    // memory, so that finding a tile is a short search instead of a pass over all experts.
+    for (int e = tid; e <= p.E; e += kThreads) offs_s[e] = p.offsets[e];
+    __syncthreads();
+    if (warp == 0) {
+      int running = 0;
+      for (int base = 0; base < p.E; base += 32) {
+        const int e = base + lane;
+        const int cnt = e < p.E ? offs_s[e + 1] - offs_s[e] : 0;
+        const int v = ((cnt + p.m_chunk - 1) / p.m_chunk) * p.n_row_tiles;
+        int incl = v;
+#pragma unroll
+        for (int dd = 1; dd < 32; dd <<= 1) {
+          const int n = __shfl_up_sync(0xffffffffu, incl, dd);
+          if (lane >= dd) incl += n;
+        }
+        if (e < p.E) tile_base_s[e] = running + incl - v;
+        running += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) tile_base_s[p.E] = running;
+    }
+  }
   __syncthreads();
 
   const int g = lane >> 2, t4 = lane & 3;
@@ -463,7 +494,7 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
   const bool v1 = p.fmt.scale_coding == GB_SCALE_V1;
 
   // ---- fill this warp's ring: the weight stream does not depend on the activations ----
-  TileWalker<kMoE> ahead(p);
+  TileWalker<kMoE> ahead(p, tile_base_s, offs_s);
   Tile ta;
   bool more = true;
   for (int i = 0; i < p.stages; ++i) {
@@ -473,7 +504,7 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
 
   int64_t lut_off = -1;
   int x_expert = -1, x_m0 = -1, cur_slice = -1;
-  TileWalker<kMoE> walk(p);
+  TileWalker<kMoE> walk(p, tile_base_s, offs_s);
   Tile t;
   float acc0[4], acc1[4];
   float accx[6][4];              // further independent chains: an MMA result is ~30 cycles away
@@ -794,7 +825,8 @@ int plan(GemvParams& p, int m_rows, bool moe, int sms, size_t* smem_bytes) {
   // bytes plus the alignment head and a tail the word-wise extraction may touch, on a pitch
   // that is 16 mod 32 so the eight rows start in different banks.  The chunk is the largest
   // that leaves every warp kMaxStages stages.
-  const int64_t fixed = 1280 + p.lut_bytes + (int64_t)p.x_rows * p.x_pitch;
+  p.etab_bytes = moe ? (int)((2 * (p.E + 1) * sizeof(int) + 127) & ~127ull) : 0;
+  const int64_t fixed = 1280 + p.etab_bytes + p.lut_bytes + (int64_t)p.x_rows * p.x_pitch;
   const int64_t per_warp = (kSmemBig - fixed) / p.warps;
   auto pitch_of = [&](int nsb) { return (int)((((int64_t)nsb * p.fmt.type_size + 15 + 16 + 31) & ~31ll) + 16); };
   auto stage_of = [&](int nsb) { return (8 * pitch_of(nsb) + 127) & ~127; };

@@ -10,7 +10,8 @@ constexpr int kRouteThreads = 1024;
 // (token-ascending inside an expert) and identical from run to run.
 __global__ void __launch_bounds__(kRouteThreads)
 moe_route_kernel(const int32_t* __restrict__ ids, int P, int E, int32_t* __restrict__ counts,
-                 int32_t* __restrict__ offsets, int32_t* __restrict__ order) {
+                 int32_t* __restrict__ offsets, int32_t* __restrict__ order,
+                 const float* __restrict__ weights, float* __restrict__ pair_w) {
   extern __shared__ int32_t sh[];   // [E] counts, [E+1] offsets
   int32_t* cnt = sh;
   int32_t* off = sh + E;
@@ -19,7 +20,10 @@ moe_route_kernel(const int32_t* __restrict__ ids, int P, int E, int32_t* __restr
   __syncthreads();
   for (int i = tid; i < P; i += kRouteThreads) {
     const int id = ids[i];
-    if (id >= 0 && id < E) atomicAdd(&cnt[id], 1);
+    const bool live = id >= 0 && id < E;
+    if (live) atomicAdd(&cnt[id], 1);
+    // combine weight of the pair: the router weight rounded to bf16, zero for a dropped pair
+    if (pair_w) pair_w[i] = live ? gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(weights[i])) : 0.0f;
   }
   __syncthreads();
   if (warp == 0) {
@@ -58,14 +62,18 @@ moe_route_kernel(const int32_t* __restrict__ ids, int P, int E, int32_t* __restr
 
 // out[t][h] = bf16( sum_slot w[t*topk+slot] * y[t*topk+slot][h] ), fp32 accumulate.
 __global__ void __launch_bounds__(256)
-moe_combine_kernel(const uint16_t* __restrict__ y, const float* __restrict__ pair_w, int topk, int64_t H,
-                   uint16_t* __restrict__ out) {
+moe_combine_kernel(const uint16_t* __restrict__ y, const float* __restrict__ pair_w,
+                   const int32_t* __restrict__ ids, int E, int topk, int64_t H, uint16_t* __restrict__ out) {
   const int64_t t = blockIdx.y;
   const int64_t h2 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // pair of columns
   if (h2 * 2 >= H) return;
   float a0 = 0.f, a1 = 0.f;
   for (int s = 0; s < topk; ++s) {
     const int64_t p = t * topk + s;
+    if (ids) {                      // a dropped pair has no output row: nothing was written there
+      const int id = ids[p];
+      if (id < 0 || id >= E) continue;
+    }
     const float w = pair_w[p];
     const uint32_t v = *reinterpret_cast<const uint32_t*>(y + p * H + h2 * 2);
     a0 = fmaf(w, gb_bf16_bits_to_f32(v & 0xFFFFu), a0);
@@ -79,26 +87,27 @@ moe_combine_kernel(const uint16_t* __restrict__ y, const float* __restrict__ pai
 extern "C" {
 
 int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E, int32_t* counts,
-                 int32_t* offsets, int32_t* order, void* stream) {
+                 int32_t* offsets, int32_t* order, const float* topk_weights, float* pair_w, void* stream) {
   GB_REQUIRE(topk_ids && counts && offsets && order, "null pointer argument");
+  GB_REQUIRE((topk_weights == nullptr) == (pair_w == nullptr), "topk_weights and pair_w go together");
   GB_REQUIRE(T >= 0 && topk >= 1 && E >= 1 && E <= 4096, "bad routing shape T=%lld topk=%lld E=%lld",
              (long long)T, (long long)topk, (long long)E);
   GB_REQUIRE(T * topk < (1ll << 30), "too many routed pairs");
   moe_route_kernel<<<1, kRouteThreads, (size_t)(2 * E + 1) * sizeof(int32_t), (cudaStream_t)stream>>>(
-      topk_ids, (int)(T * topk), (int)E, counts, offsets, order);
+      topk_ids, (int)(T * topk), (int)E, counts, offsets, order, topk_weights, pair_w);
   GB_LAUNCH_OK("moe_route_kernel");
   return GB_OK;
 }
 
-int gb_moe_combine(const void* y, const float* pair_w, int64_t T, int64_t topk, int64_t H, void* out,
-                   void* stream) {
+int gb_moe_combine(const void* y, const float* pair_w, const int32_t* topk_ids, int64_t E, int64_t T,
+                   int64_t topk, int64_t H, void* out, void* stream) {
   GB_REQUIRE(y && pair_w && out, "null pointer argument");
   GB_REQUIRE(T >= 0 && topk >= 1 && H > 0 && H % 2 == 0, "bad combine shape T=%lld topk=%lld H=%lld",
              (long long)T, (long long)topk, (long long)H);
   if (T == 0) return GB_OK;
   dim3 grid((unsigned)((H / 2 + 255) / 256), (unsigned)T);
-  moe_combine_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)y, pair_w, (int)topk, H,
-                                                           (uint16_t*)out);
+  moe_combine_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)y, pair_w, topk_ids, (int)E,
+                                                           (int)topk, H, (uint16_t*)out);
   GB_LAUNCH_OK("moe_combine_kernel");
   return GB_OK;
 }

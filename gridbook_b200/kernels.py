@@ -176,9 +176,11 @@ def gemv(x: torch.Tensor, w: PackedWeight, *, act: str | None = None, scale_rule
     return out.reshape(*x.shape[:-1], w.rows)
 
 
-def moe_route(topk_ids: torch.Tensor, E: int):
-    """-> (counts [E], offsets [E+1], order [P]) int32, all on device, no host read."""
-    _need_cuda(topk_ids)
+def moe_route(topk_ids: torch.Tensor, E: int, topk_weights: torch.Tensor | None = None):
+    """-> (counts [E], offsets [E+1], order [P]) int32, all on device, no host read.  With
+    ``topk_weights`` a fourth result: pair_w [P] fp32, the bf16-rounded router weight of every
+    pair and zero for a dropped one, written by the same launch."""
+    _need_cuda(topk_ids, topk_weights)
     lib = nat.load("MoE routing")
     ids = topk_ids.to(torch.int32).contiguous()
     T, topk = ids.shape
@@ -186,15 +188,23 @@ def moe_route(topk_ids: torch.Tensor, E: int):
     counts = torch.empty(E, dtype=torch.int32, device=dev)
     offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
     order = torch.empty(max(T * topk, 1), dtype=torch.int32, device=dev)
+    tw = pw = None
+    if topk_weights is not None:
+        tw = topk_weights.reshape(-1).to(torch.float32).contiguous()
+        pw = torch.empty(max(T * topk, 1), dtype=torch.float32, device=dev)
     nat.check(lib.gb_moe_route(_ptr(ids), T, topk, E, _ptr(counts), _ptr(offsets), _ptr(order),
-                               nat.stream_ptr(dev)), lib)
-    return counts, offsets, order[:T * topk]
+                               _ptr(tw), _ptr(pw), nat.stream_ptr(dev)), lib)
+    if topk_weights is None:
+        return counts, offsets, order[:T * topk]
+    return counts, offsets, order[:T * topk], pw[:T * topk]
 
 
 def moe_gemv(x: torch.Tensor, w: PackedWeight, offsets: torch.Tensor, order: torch.Tensor, *,
              x_row: torch.Tensor | None = None, swiglu: bool = False,
-             out: torch.Tensor | None = None) -> torch.Tensor:
-    """Grouped GEMV over the routed pairs; y[p] for pair p (rows/2 wide with swiglu)."""
+             out: torch.Tensor | None = None, clear: bool = True) -> torch.Tensor:
+    """Grouped GEMV over the routed pairs; y[p] for pair p (rows/2 wide with swiglu).  Rows of
+    pairs that routing dropped are not written: they read zero, or are left unset when
+    ``clear`` is False (a caller that hands the dropped ids to :func:`moe_combine`)."""
     _need_cuda(x, offsets, order, x_row)
     lib = nat.load("grouped codebook decode GEMV")
     if x.dtype is not torch.bfloat16:
@@ -203,8 +213,8 @@ def moe_gemv(x: torch.Tensor, w: PackedWeight, offsets: torch.Tensor, order: tor
     P = order.numel()
     width = w.rows // 2 if swiglu else w.rows
     if out is None:
-        # pairs dropped by routing (padding sentinel) are never written: start from zero
-        out = torch.zeros((P, width), dtype=torch.bfloat16, device=x.device)
+        alloc = torch.zeros if clear else torch.empty
+        out = alloc((P, width), dtype=torch.bfloat16, device=x.device)
     nw = w.native()
     nat.check(lib.gb_moe_gemv(_ptr(x), _ptr(x_row), ctypes.byref(nw), w.expert_stride, w.experts,
                               _ptr(offsets), _ptr(order), P, 1 if swiglu else 0, _ptr(out),
@@ -212,14 +222,20 @@ def moe_gemv(x: torch.Tensor, w: PackedWeight, offsets: torch.Tensor, order: tor
     return out
 
 
-def moe_combine(y: torch.Tensor, pair_w: torch.Tensor, T: int, topk: int) -> torch.Tensor:
-    _need_cuda(y, pair_w)
+def moe_combine(y: torch.Tensor, pair_w: torch.Tensor, T: int, topk: int, *,
+                topk_ids: torch.Tensor | None = None, E: int = 0) -> torch.Tensor:
+    """out[t] = sum_slot pair_w * y, fp32 accumulate, one bf16 rounding.  ``topk_ids`` (int32,
+    with ``E``) names the pairs routing dropped, whose rows of ``y`` are then never read."""
+    _need_cuda(y, pair_w, topk_ids)
     lib = nat.load("grouped CB router combine")
     y = y.contiguous()
     H = y.shape[-1]
     out = torch.empty((T, H), dtype=torch.bfloat16, device=y.device)
     pw = pair_w.to(torch.float32).contiguous()
-    nat.check(lib.gb_moe_combine(_ptr(y), _ptr(pw), T, topk, H, _ptr(out),
+    ids = None
+    if topk_ids is not None:
+        ids = topk_ids.to(torch.int32).contiguous()
+    nat.check(lib.gb_moe_combine(_ptr(y), _ptr(pw), _ptr(ids), E, T, topk, H, _ptr(out),
                                  nat.stream_ptr(y.device)), lib)
     return out
 

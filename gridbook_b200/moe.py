@@ -169,17 +169,18 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         if T == 0:
             return torch.empty_like(x)
         x2 = x.reshape(T, -1).to(torch.bfloat16).contiguous()
-        _, offsets, order = kernels.moe_route(topk_ids, layer._cb_E)
+        ids = topk_ids.to(torch.int32).contiguous()
+        # the loop chain multiplies by the bf16-rounded router weight (gridbook/moe.py:2407-2408);
+        # the routing launch writes it, zeroed for padded pairs
+        _, offsets, order, pair_w = kernels.moe_route(ids, layer._cb_E, topk_weights)
         bucket13 = kernels.fp4_act_qdq if self.fmt13.is_fp4 else kernels.fp8_act_qdq
         bucket2 = kernels.fp4_act_qdq if self.fmt2.is_fp4 else kernels.fp8_act_qdq
         xq = bucket13(x2, rule)
         a = kernels.moe_gemv(xq, layer._cb_w13, offsets, order, x_row=self._x_row(layer, T, topk, x.device),
-                             swiglu=True)
+                             swiglu=True, clear=False)
         aq = bucket2(a, rule)
-        y = kernels.moe_gemv(aq, layer._cb_w2, offsets, order)
-        # the loop chain multiplies by the bf16-rounded router weight (gridbook/moe.py:2407-2408)
-        pair_w = topk_weights.reshape(-1).to(torch.bfloat16).to(torch.float32)
-        out = kernels.moe_combine(y, pair_w, T, topk)
+        y = kernels.moe_gemv(aq, layer._cb_w2, offsets, order, clear=False)
+        out = kernels.moe_combine(y, pair_w, T, topk, topk_ids=ids, E=layer._cb_E)
         return out.to(x.dtype).reshape(x.shape)
 
 

@@ -285,8 +285,10 @@ def _neutralize_moe_padding_sentinel(topk_weights, topk_ids):
 @torch.library.custom_op("prismaquant::cb_moe_forward", mutates_args=())
 def cb_moe_forward(x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                    layer_id: int) -> torch.Tensor:
+    # Padded routes (expert id -1) need no masking pass here: the routing launch drops them and
+    # zeroes their combine weight, which gives what the reference's (expert 0, weight 0)
+    # substitution gives (gridbook/ops.py:764-784) without its three elementwise launches.
     method, layer = _lookup_cb_layer(layer_id)
-    topk_weights, topk_ids = _neutralize_moe_padding_sentinel(topk_weights, topk_ids)
     return method._apply_inline(layer, x, topk_weights, topk_ids)
 
 

@@ -153,9 +153,13 @@ GB_API int gb_gemm_tn(const void* A, const void* B, void* D_bf16, int64_t M, int
  * gridbook/moe_routing.py:99-207.  ids < 0 (vLLM's padding sentinel,
  * gridbook/ops.py:764-784) are dropped from every expert.
  *   counts [E], offsets [E+1] (exclusive scan, offsets[E] = routed pairs kept),
- *   order [P]: sorted position -> flat pair index t*topk+slot (token-ascending per expert). */
+ *   order [P]: sorted position -> flat pair index t*topk+slot (token-ascending per expert).
+ * Optional (both or neither): topk_weights [P] fp32 in, pair_w [P] fp32 out = the combine
+ * weight of every pair, i.e. the router weight rounded to bf16 (gridbook/moe.py:2407-2408)
+ * and zero for a dropped pair (gridbook/ops.py:764-784), so no separate masking pass runs. */
 GB_API int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E,
-                 int32_t* counts, int32_t* offsets, int32_t* order, void* stream);
+                 int32_t* counts, int32_t* offsets, int32_t* order,
+                 const float* topk_weights, float* pair_w, void* stream);
 
 /* Grouped GEMV over routed pairs; replaces cb_moe_gemv_fp8 / cb_moe_gemv_fp4_v2 /
  * cb_moe_gemv_v2 (gridbook/csrc/cb_gemv.cu:1210-1681,1873-2138; gridbook/csrc/cb_gemv_v2.cu:233-366).
@@ -172,9 +176,11 @@ GB_API int gb_moe_gemv(const void* x_bf16, const int32_t* x_row, const gb_weight
 
 /* out[t] = sum over the token's topk pairs of w[p] * y[p], fp32 accumulate, one bf16
  * rounding; replaces cb_moe_combine (gridbook/csrc/cb_gemv.cu:1853-1871,2140-2158).
- * pair p = t*topk + slot. */
-GB_API int gb_moe_combine(const void* y_bf16, const float* pair_w, int64_t T, int64_t topk,
-                   int64_t H, void* out_bf16, void* stream);
+ * pair p = t*topk + slot.  topk_ids (optional, with E): pairs whose id lies outside [0, E)
+ * were dropped by gb_moe_route and have no row in y; they are skipped, so y needs no
+ * clearing beforehand. */
+GB_API int gb_moe_combine(const void* y_bf16, const float* pair_w, const int32_t* topk_ids,
+                   int64_t E, int64_t T, int64_t topk, int64_t H, void* out_bf16, void* stream);
 
 #ifdef __cplusplus
 }

@@ -120,6 +120,32 @@ def test_route_matches_oracle(dev):
         assert np.array_equal(order.cpu().numpy()[:n], rorder[:n])
 
 
+def test_route_weights_and_combine_skip_dropped_pairs(dev):
+    """The routing launch also writes the combine weights (bf16-rounded, zero for a dropped
+    pair), and a combine that is told the ids never reads a dropped pair's row."""
+    from gridbook_b200 import kernels, synth
+    T, E, topk, H = 9, 12, 4, 64
+    ids, tw = synth.make_routing(T, E, topk, seed=3)
+    ids[1, 2] = -1
+    ids[8, 0] = -1
+    idd = torch.from_numpy(ids).to(dev)
+    twd = torch.from_numpy(tw).to(dev)
+    c0, o0, r0 = kernels.moe_route(idd, E)
+    c1, o1, r1, pw = kernels.moe_route(idd, E, twd)
+    assert torch.equal(c0, c1) and torch.equal(o0, o1)
+    n = int(o0[-1])
+    assert torch.equal(r0[:n], r1[:n])
+    want = twd.to(torch.bfloat16).float().reshape(-1).masked_fill(idd.reshape(-1) < 0, 0.0)
+    assert torch.equal(pw, want)
+    rng = np.random.default_rng(0)
+    y = torch.from_numpy(rng.standard_normal((T * topk, H)).astype(np.float32)).to(dev).to(torch.bfloat16)
+    base = kernels.moe_combine(y.masked_fill((idd.reshape(-1) < 0)[:, None], 0.0), pw, T, topk)
+    poisoned = y.clone()
+    poisoned[idd.reshape(-1) < 0] = float("nan")          # what an uncleared buffer may hold
+    got = kernels.moe_combine(poisoned, pw, T, topk, topk_ids=idd, E=E)
+    assert torch.equal(got, base)
+
+
 def _moe_case(dev, fmt13, fmt2, E, hidden, inter, T, topk, seed):
     from gridbook_b200 import kernels, synth
     w13d, w2d = synth.make_moe(fmt13, fmt2, E, hidden, inter, seed=seed)
