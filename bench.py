@@ -102,7 +102,7 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- GPU arm
-def build_stack(fmt, gscale, layers, device, rank, world, seed=0):
+def build_stack(fmt, gscale, layers, device, rank, world, seed=0, peers=None, max_rows=16):
     """Random-init codebook stack; with world > 1 every projection keeps whole-role row
     ranges [r*n/world, (r+1)*n/world) of each role (column-parallel sharding)."""
     import torch
@@ -123,7 +123,10 @@ def build_stack(fmt, gscale, layers, device, rank, world, seed=0):
             lin.load(qw, ws, device)
             if world > 1:
                 from gridbook_b200.parallel import ShardedCBLinear
-                sh = ShardedCBLinear(lin, parts)
+                from gridbook_b200.peer import PeerShardedCBLinear
+                # all-gather by peer stores from this package's own kernel, or through NCCL
+                sh = (PeerShardedCBLinear(lin, parts, peers, max_rows=max_rows) if peers is not None
+                      else ShardedCBLinear(lin, parts))
                 sh._cb_weight, sh._cb_workspace = lin._cb_weight, lin._cb_workspace
                 lin = sh
             row.append(lin)
@@ -149,7 +152,14 @@ def run_gpu(args):
 
     fmt, gscale = get_format(args.format)
     M = args.m
-    stack = build_stack(fmt, gscale, args.layers, device, rank, world)
+    peers = None
+    if world > 1 and args.collective == "peer":
+        from gridbook_b200.peer import PeerGroup
+        dense_bytes = args.layers * sum(sum(parts) for _, parts, _ in PROJECTIONS) * 2 * M
+        moe_bytes = 2 * (2 * world * 256 * (MOE_SHAPE["hidden"] * 2 + MOE_SHAPE["topk"] * 4)
+                         + 256 * MOE_SHAPE["topk"] * MOE_SHAPE["hidden"] * 2)
+        peers = PeerGroup(dense_bytes + moe_bytes + (8 << 20), device)
+    stack = build_stack(fmt, gscale, args.layers, device, rank, world, peers=peers, max_rows=M)
     gen = torch.Generator(device=device).manual_seed(1234)
     inputs_dev = [torch.randn(M, K, generator=gen, device=device).to(torch.bfloat16) for _, _, K in PROJECTIONS]
     inputs_host = [t.cpu().pin_memory() for t in inputs_dev]
@@ -171,6 +181,8 @@ def run_gpu(args):
         return ys
 
     # warm-up eagerly (also settles allocator and NCCL), then capture one step
+    if world > 1:
+        dist.barrier()            # the peer exchange waits two seconds for a late rank, no longer
     for _ in range(2):
         last = step()
     torch.cuda.synchronize()
@@ -259,7 +271,8 @@ def run_gpu(args):
     k1.record()
     barrier()
     ms_kernel = k0.elapsed_time(k1)
-    moe = None if args.no_moe else bench_moe(args, device, world, rank)
+    used_graph = graph is not None
+    moe = None if args.no_moe else bench_moe(args, device, world, rank, peers)
     prefill = bench_prefill(args, device) if (world == 1 and not args.no_prefill) else None
     status = _native.device_status(local_rank)
 
@@ -275,9 +288,14 @@ def run_gpu(args):
     else:
         total_bytes = float(bytes_per_step_local)
 
+    if world > 1:
+        # Captured graphs hold the communicator's kernels: release them before anything tears the
+        # process group down, and leave together.
+        graph = kgraph = None
+        dist.barrier()
+        torch.cuda.synchronize()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        _leave(world)
         return
     peaks, peak_kind = measured_peaks()
     n_linear = args.layers * len(PROJECTIONS)
@@ -296,9 +314,10 @@ def run_gpu(args):
         "config": {"workload": f"dense decode stack: {args.layers} layers x (q 6144x5120, kv 2048x5120, "
                                f"o 5120x6144, gate_up 34816x5120, down 5120x17408), M={M}",
                    "format": f"{args.format}: {fmt.grid} grid, {fmt.mode} k={fmt.k}, type_size {fmt.type_size}",
-                   "weight_bytes_per_step": int(total_bytes), "parallelism": f"N-sharded x{world}" if world > 1 else "1 GPU",
+                   "weight_bytes_per_step": int(total_bytes), "parallelism": (f"N-sharded x{world}, all-gather by "
+                                   f"{'peer-memory stores' if peers is not None else 'NCCL'}") if world > 1 else "1 GPU",
                    "l2": "inputs larger than L2: every step streams all distinct layer weights",
-                   "cuda_graph": graph is not None},
+                   "cuda_graph": used_graph},
         "pct_hbm_peak": round(100.0 * gbs / (peaks["hbm_gbs"] * world), 2),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None, "peak_kind": peak_kind,
@@ -316,16 +335,25 @@ def run_gpu(args):
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(args.format, M, seconds=20.0)
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    _leave(world)
 
+
+
+def _leave(world):
+    """Multi-rank runs end the process here: every rank has passed the final barrier and has
+    nothing in flight, and a communicator teardown that waits on a peer which already left can
+    block for good."""
+    if world > 1:
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 # ----------------------------------------------------------------------------- routed MoE leg
 MOE_SHAPE = dict(E=128, topk=8, hidden=2048, inter=768)          # benchmark configuration 3
 
 
-def bench_moe(args, device, world, rank):
+def bench_moe(args, device, world, rank, peers=None):
     """Grouped-MoE decode tokens/s for one routed layer of configuration 3 at T tokens PER RANK
     (weak scaling: every rank brings its own batch, experts are split E/world per rank and rows
     travel by NCCL all-to-all).  L2 is flushed between timed iterations."""
@@ -349,7 +377,10 @@ def bench_moe(args, device, world, rank):
             s13 = (torch.rand(e_local, 2 * inter, generator=gen, device=device) + 0.5) * 0.02
             s2 = (torch.rand(e_local, hidden, generator=gen, device=device) + 0.5) * 0.02
         moe.load(w13, w2, s13, s2, device)
-        if world > 1:
+        if world > 1 and peers is not None:
+            from gridbook_b200.peer import PeerExpertParallelMoE
+            moe = PeerExpertParallelMoE(E, moe, peers, 256, topk, hidden)
+        elif world > 1:
             moe = parallel.ExpertParallelMoE(E, parallel.make_local_expert_fn(moe), parallel.kernel_combine)
         layers.append(moe)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
@@ -362,10 +393,12 @@ def bench_moe(args, device, world, rank):
             for m in layers:
                 m(x, tw_d, ids_d)
 
+        if world > 1:
+            dist.barrier()
         for _ in range(3):
             run_layers()
         runner = run_layers
-        if world == 1:
+        if world == 1 or peers is not None:        # no host read on these paths: one graph per batch size
             torch.cuda.synchronize()
             try:
                 g = torch.cuda.CUDAGraph()
@@ -393,7 +426,9 @@ def bench_moe(args, device, world, rank):
         out[str(T)] = {"tok_s": round(world * T / (ms_layer * 1e-3), 1), "ms_per_layer": round(ms_layer, 4)}
     return {"workload": f"routed MoE layer, {E} experts top-{topk}, hidden {hidden}, intermediate {inter}, "
                         f"format {args.format}, T tokens per rank", "scaling": "weak",
-            "parallelism": f"expert-parallel x{world} (NCCL all-to-all)" if world > 1 else "1 GPU",
+            "parallelism": (f"expert-parallel x{world} "
+                            f"({'peer-memory stores' if peers is not None else 'NCCL all-to-all'})"
+                            if world > 1 else "1 GPU"),
             "tokens_per_rank": out}
 
 
@@ -530,6 +565,8 @@ def main():
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--format", default="literal", choices=["literal", "k16v2", "fp8k32", "fp8lit"])
     ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: exchange by this package's peer-memory kernels, or through NCCL")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-moe", action="store_true")

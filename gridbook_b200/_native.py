@@ -23,7 +23,10 @@ REQUIRED_SYMBOLS = (
     "gb_gemv_workspace_bytes", "gb_gemv", "gb_gemv_static",
     "gb_moe_route", "gb_moe_gemv_workspace_bytes", "gb_moe_gemv", "gb_moe_combine",
     "gb_fp8_quantize_rows", "gb_gemm_tn",
+    "gb_peer_alloc", "gb_peer_free", "gb_peer_export", "gb_peer_open", "gb_peer_close",
+    "gb_peer_allgather", "gb_peer_barrier",
 )
+PEER_MAX, PEER_HANDLE_BYTES, PEER_FLAG_BYTES = 8, 64, 128
 
 GRID_FP4, GRID_FP8 = 0, 1
 MODE_PRODUCT, MODE_SIGNED, MODE_FULL = 0, 1, 2
@@ -54,6 +57,19 @@ class GbWeight(ctypes.Structure):
                 ("K", ctypes.c_int64), ("fmt", GbFormat)]
 
 
+class GbPeerGroup(ctypes.Structure):
+    _fields_ = [("rank", ctypes.c_int32), ("world", ctypes.c_int32), ("flags", ctypes.c_void_p * 8)]
+
+
+class GbPeerPiece(ctypes.Structure):
+    _fields_ = [("src", ctypes.c_void_p), ("dst", ctypes.c_void_p * 8), ("rows", ctypes.c_int64),
+                ("row_bytes", ctypes.c_int64), ("src_pitch", ctypes.c_int64), ("dst_pitch", ctypes.c_int64)]
+
+
+class GbPeerRows(ctypes.Structure):
+    _fields_ = [("base", ctypes.c_void_p * 8), ("rows_per_rank", ctypes.c_int64)]
+
+
 _LOCK = threading.Lock()
 _LIB = None
 _PREPARED: set[int] = set()
@@ -82,13 +98,20 @@ def _declare(lib) -> None:
     lib.gb_gemv_workspace_bytes.restype = i64
     lib.gb_gemv.argtypes = [vp, i64, wp, i32, i32, vp, vp, i64, vp]
     lib.gb_gemv_static.argtypes = [vp, i64, wp, i32, i32, vp, vp]
-    lib.gb_moe_route.argtypes = [vp, i64, i64, i64, vp, vp, vp, vp, vp, vp]
+    lib.gb_moe_route.argtypes = [vp, i64, i64, i64, i64, vp, vp, vp, vp, vp, vp]
     lib.gb_moe_gemv_workspace_bytes.argtypes = [i64, i64]
     lib.gb_moe_gemv_workspace_bytes.restype = i64
-    lib.gb_moe_gemv.argtypes = [vp, vp, wp, i64, i64, vp, vp, i64, i32, vp, vp, i64, vp]
+    lib.gb_moe_gemv.argtypes = [vp, vp, wp, i64, i64, vp, vp, i64, i32, vp, vp, vp, i64, vp]
     lib.gb_moe_combine.argtypes = [vp, vp, vp, i64, i64, i64, i64, vp, vp]
     lib.gb_fp8_quantize_rows.argtypes = [vp, vp, vp, i64, i64, i32, vp]
     lib.gb_gemm_tn.argtypes = [vp, vp, vp, i64, i64, i64, i32, vp, vp, ctypes.c_float, vp]
+    lib.gb_peer_alloc.argtypes = [i64, ctypes.POINTER(vp)]
+    lib.gb_peer_free.argtypes = [vp]
+    lib.gb_peer_export.argtypes = [vp, vp]
+    lib.gb_peer_open.argtypes = [vp, ctypes.POINTER(vp)]
+    lib.gb_peer_close.argtypes = [vp]
+    lib.gb_peer_allgather.argtypes = [ctypes.POINTER(GbPeerGroup), ctypes.POINTER(GbPeerPiece), i32, vp]
+    lib.gb_peer_barrier.argtypes = [ctypes.POINTER(GbPeerGroup), vp]
     for name in REQUIRED_SYMBOLS:
         fn = getattr(lib, name)
         if fn.restype is ctypes.c_int:

@@ -63,6 +63,8 @@ struct GemvParams {
                           // eight lanes of a quarter-warp never collide on a bank
   // outputs
   uint16_t* y;
+  uint16_t* y_peer[8];    // routed, optional: pair p's row lives in y_peer[p / pairs_per_rank]
+  int pairs_per_rank;     // 0 = all rows in y
   float* ws;              // [M, N] fp32 partial sums when ksplit > 1
   int* status;
 };
@@ -735,8 +737,16 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
             atomicAdd(p.ws + (int64_t)m * p.N + row, raw[i]);
           } else {
             int64_t orow = m;
-            if constexpr (kMoE) orow = p.order[t.m0 + m];
-            p.y[orow * p.N + row] = (uint16_t)gb_f32_to_bf16_bits(c[i]);
+            uint16_t* ybase = p.y;
+            if constexpr (kMoE) {
+              orow = p.order[t.m0 + m];
+              if (p.pairs_per_rank > 0) {       // the pair's home rank keeps its row (peer store)
+                const int home = (int)(orow / p.pairs_per_rank);
+                ybase = p.y_peer[home];
+                orow -= (int64_t)home * p.pairs_per_rank;
+              }
+            }
+            ybase[orow * p.N + row] = (uint16_t)gb_f32_to_bf16_bits(c[i]);
           }
         }
       }
@@ -952,12 +962,13 @@ int64_t gb_moe_gemv_workspace_bytes(int64_t P, int64_t rows) {
 
 int gb_moe_gemv(const void* x, const int32_t* x_row, const gb_weight* w, int64_t expert_stride,
                 int64_t E, const int32_t* offsets, const int32_t* order, int64_t P, int swiglu,
-                void* y, void* workspace, int64_t workspace_bytes, void* stream_) {
+                void* y, const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes, void* stream_) {
   (void)workspace; (void)workspace_bytes;
   cudaStream_t stream = (cudaStream_t)stream_;
   int rc = gb_check_weight(w);
   if (rc != GB_OK) return rc;
-  GB_REQUIRE(x && y && offsets && order, "null pointer argument");
+  GB_REQUIRE(x && (y || y_rows) && offsets && order, "null pointer argument");
+  GB_REQUIRE(!(y_rows && swiglu), "per-rank output rows are for the down projection, not the fused gate/up");
   GB_REQUIRE(E >= 1 && P >= 0, "bad E=%lld P=%lld", (long long)E, (long long)P);
   GB_REQUIRE(!swiglu || w->rows % 2 == 0, "swiglu needs an even row count");
   if (P == 0) return GB_OK;
@@ -978,6 +989,15 @@ int gb_moe_gemv(const void* x, const int32_t* x_row, const gb_weight* w, int64_t
   p.E = (int)E;
   p.swiglu = swiglu ? 1 : 0;
   p.y = (uint16_t*)y;
+  if (y_rows) {
+    GB_REQUIRE(y_rows->rows_per_rank > 0 && (P + y_rows->rows_per_rank - 1) / y_rows->rows_per_rank <= 8,
+               "bad per-rank output rows: %lld per rank for %lld pairs", (long long)y_rows->rows_per_rank, (long long)P);
+    for (int r = 0; r * y_rows->rows_per_rank < P; ++r) {
+      GB_REQUIRE(y_rows->base[r] != nullptr, "per-rank output rows: rank %d has no buffer", r);
+      p.y_peer[r] = (uint16_t*)y_rows->base[r];
+    }
+    p.pairs_per_rank = (int)y_rows->rows_per_rank;
+  }
   p.status = gb_status_word();
   // tokens per pass: as many (up to sixteen) as the activation budget holds
   const int64_t pitch = (w->K / 256) * 512 + 64;

@@ -9,7 +9,7 @@ constexpr int kRouteThreads = 1024;
 // fills whole experts in pair order with ballots, so the grouping is stable
 // (token-ascending inside an expert) and identical from run to run.
 __global__ void __launch_bounds__(kRouteThreads)
-moe_route_kernel(const int32_t* __restrict__ ids, int P, int E, int32_t* __restrict__ counts,
+moe_route_kernel(const int32_t* __restrict__ ids, int P, int E, int first_expert, int32_t* __restrict__ counts,
                  int32_t* __restrict__ offsets, int32_t* __restrict__ order,
                  const float* __restrict__ weights, float* __restrict__ pair_w) {
   extern __shared__ int32_t sh[];   // [E] counts, [E+1] offsets
@@ -19,7 +19,7 @@ moe_route_kernel(const int32_t* __restrict__ ids, int P, int E, int32_t* __restr
   for (int e = tid; e < E; e += kRouteThreads) cnt[e] = 0;
   __syncthreads();
   for (int i = tid; i < P; i += kRouteThreads) {
-    const int id = ids[i];
+    const int id = ids[i] - first_expert;
     const bool live = id >= 0 && id < E;
     if (live) atomicAdd(&cnt[id], 1);
     // combine weight of the pair: the router weight rounded to bf16, zero for a dropped pair
@@ -52,7 +52,7 @@ moe_route_kernel(const int32_t* __restrict__ ids, int P, int E, int32_t* __restr
     int pos = off[e];
     for (int base = 0; base < P; base += 32) {
       const int i = base + lane;
-      const bool hit = i < P && ids[i] == e;
+      const bool hit = i < P && ids[i] - first_expert == e;
       const unsigned mask = __ballot_sync(0xffffffffu, hit);
       if (hit) order[pos + __popc(mask & ((1u << lane) - 1u))] = i;
       pos += __popc(mask);
@@ -86,15 +86,15 @@ moe_combine_kernel(const uint16_t* __restrict__ y, const float* __restrict__ pai
 
 extern "C" {
 
-int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E, int32_t* counts,
-                 int32_t* offsets, int32_t* order, const float* topk_weights, float* pair_w, void* stream) {
+int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E, int64_t expert_base,
+                 int32_t* counts, int32_t* offsets, int32_t* order, const float* topk_weights, float* pair_w, void* stream) {
   GB_REQUIRE(topk_ids && counts && offsets && order, "null pointer argument");
   GB_REQUIRE((topk_weights == nullptr) == (pair_w == nullptr), "topk_weights and pair_w go together");
   GB_REQUIRE(T >= 0 && topk >= 1 && E >= 1 && E <= 4096, "bad routing shape T=%lld topk=%lld E=%lld",
              (long long)T, (long long)topk, (long long)E);
   GB_REQUIRE(T * topk < (1ll << 30), "too many routed pairs");
   moe_route_kernel<<<1, kRouteThreads, (size_t)(2 * E + 1) * sizeof(int32_t), (cudaStream_t)stream>>>(
-      topk_ids, (int)(T * topk), (int)E, counts, offsets, order, topk_weights, pair_w);
+      topk_ids, (int)(T * topk), (int)E, (int)expert_base, counts, offsets, order, topk_weights, pair_w);
   GB_LAUNCH_OK("moe_route_kernel");
   return GB_OK;
 }

@@ -176,10 +176,12 @@ def gemv(x: torch.Tensor, w: PackedWeight, *, act: str | None = None, scale_rule
     return out.reshape(*x.shape[:-1], w.rows)
 
 
-def moe_route(topk_ids: torch.Tensor, E: int, topk_weights: torch.Tensor | None = None):
+def moe_route(topk_ids: torch.Tensor, E: int, topk_weights: torch.Tensor | None = None, *,
+              expert_base: int = 0):
     """-> (counts [E], offsets [E+1], order [P]) int32, all on device, no host read.  With
     ``topk_weights`` a fourth result: pair_w [P] fp32, the bf16-rounded router weight of every
-    pair and zero for a dropped one, written by the same launch."""
+    pair and zero for a dropped one, written by the same launch.  ``expert_base``: the E experts
+    held here are the global ids [expert_base, expert_base + E); other ids are dropped."""
     _need_cuda(topk_ids, topk_weights)
     lib = nat.load("MoE routing")
     ids = topk_ids.to(torch.int32).contiguous()
@@ -192,7 +194,7 @@ def moe_route(topk_ids: torch.Tensor, E: int, topk_weights: torch.Tensor | None 
     if topk_weights is not None:
         tw = topk_weights.reshape(-1).to(torch.float32).contiguous()
         pw = torch.empty(max(T * topk, 1), dtype=torch.float32, device=dev)
-    nat.check(lib.gb_moe_route(_ptr(ids), T, topk, E, _ptr(counts), _ptr(offsets), _ptr(order),
+    nat.check(lib.gb_moe_route(_ptr(ids), T, topk, E, expert_base, _ptr(counts), _ptr(offsets), _ptr(order),
                                _ptr(tw), _ptr(pw), nat.stream_ptr(dev)), lib)
     if topk_weights is None:
         return counts, offsets, order[:T * topk]
@@ -201,10 +203,11 @@ def moe_route(topk_ids: torch.Tensor, E: int, topk_weights: torch.Tensor | None 
 
 def moe_gemv(x: torch.Tensor, w: PackedWeight, offsets: torch.Tensor, order: torch.Tensor, *,
              x_row: torch.Tensor | None = None, swiglu: bool = False,
-             out: torch.Tensor | None = None, clear: bool = True) -> torch.Tensor:
+             out: torch.Tensor | None = None, clear: bool = True, peer_rows=None) -> torch.Tensor | None:
     """Grouped GEMV over the routed pairs; y[p] for pair p (rows/2 wide with swiglu).  Rows of
     pairs that routing dropped are not written: they read zero, or are left unset when
-    ``clear`` is False (a caller that hands the dropped ids to :func:`moe_combine`)."""
+    ``clear`` is False (a caller that hands the dropped ids to :func:`moe_combine`).
+    ``peer_rows`` (a ``GbPeerRows``): rows go to their home rank's buffer instead of ``out``."""
     _need_cuda(x, offsets, order, x_row)
     lib = nat.load("grouped codebook decode GEMV")
     if x.dtype is not torch.bfloat16:
@@ -212,12 +215,13 @@ def moe_gemv(x: torch.Tensor, w: PackedWeight, offsets: torch.Tensor, order: tor
     x = x.contiguous()
     P = order.numel()
     width = w.rows // 2 if swiglu else w.rows
-    if out is None:
+    if out is None and peer_rows is None:
         alloc = torch.zeros if clear else torch.empty
         out = alloc((P, width), dtype=torch.bfloat16, device=x.device)
     nw = w.native()
     nat.check(lib.gb_moe_gemv(_ptr(x), _ptr(x_row), ctypes.byref(nw), w.expert_stride, w.experts,
                               _ptr(offsets), _ptr(order), P, 1 if swiglu else 0, _ptr(out),
+                              ctypes.byref(peer_rows) if peer_rows is not None else None,
                               _ZERO, 0, nat.stream_ptr(x.device)), lib)
     return out
 

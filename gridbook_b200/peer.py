@@ -1,0 +1,220 @@
+"""Multi-GPU hot path over peer memory (one NVSwitch node, one process per GPU).
+
+The dense all-gather and the expert-parallel dispatch/combine of :mod:`gridbook_b200.parallel`
+go through NCCL and, for the routed layer, through a host read of the split sizes.  Here the
+same exchanges are plain stores into the peers' buffers from this package's own kernels:
+
+* ``PeerShardedCBLinear``: the local column shard's output is copied into every rank's full
+  output row by one launch that also carries the flag exchange on both sides of the copy.
+* ``PeerExpertParallelMoE``: the bucketed activations and the routing ids are all-gathered the
+  same way, every rank runs the grouped kernels over the pairs routed to ITS experts, and the
+  down-projection GEMV stores every output row straight into the buffer of the rank the token
+  came from; a flag exchange later the home rank combines.  Eight launches, no host read.
+
+The reference is single-GPU (gridbook/config.py:565-576); nothing here has a counterpart there.
+Buffers are shared between the processes by CUDA IPC handles sent through the process group.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _native as nat
+from . import kernels
+
+
+class _RawDeviceMemory:
+    """Lets torch alias device memory this package allocated."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerArena:
+    """``nbytes`` of zero-filled device memory on every rank, each rank's block mapped into every
+    other rank.  ``carve`` hands out the same offsets on every rank as long as every rank makes
+    the same calls in the same order."""
+
+    def __init__(self, nbytes: int, device: torch.device, group=None):
+        self.lib = nat.load("peer-memory exchange")
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > nat.PEER_MAX:
+            raise ValueError(f"peer exchange serves up to {nat.PEER_MAX} ranks, got {self.world}")
+        self.device = device
+        self.nbytes = (int(nbytes) + 255) & ~255
+        own = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            nat.check(self.lib.gb_peer_alloc(self.nbytes, ctypes.byref(own)), self.lib)
+            handle = ctypes.create_string_buffer(nat.PEER_HANDLE_BYTES)
+            nat.check(self.lib.gb_peer_export(own, handle), self.lib)
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            self.ptrs = []
+            for r in range(self.world):
+                if r == self.rank:
+                    self.ptrs.append(own.value)
+                    continue
+                mapped = ctypes.c_void_p()
+                theirs = ctypes.create_string_buffer(bytes(handles[r]), nat.PEER_HANDLE_BYTES)
+                nat.check(self.lib.gb_peer_open(theirs, ctypes.byref(mapped)), self.lib)
+                self.ptrs.append(mapped.value)
+        self._own = own
+        self._top = 0
+        self._bytes = torch.as_tensor(_RawDeviceMemory(own.value, self.nbytes), device=device)
+
+    def carve(self, nbytes: int) -> int:
+        off = self._top
+        self._top = (off + int(nbytes) + 255) & ~255
+        if self._top > self.nbytes:
+            raise MemoryError(f"peer arena of {self.nbytes} bytes is full ({self._top} wanted)")
+        return off
+
+    def tensor(self, offset: int, shape, dtype) -> torch.Tensor:
+        """This rank's block at ``offset`` as a tensor (aliases the shared memory)."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        return self._bytes[offset:offset + nbytes].view(dtype).view(*shape)
+
+    def ptr(self, rank: int, offset: int) -> int:
+        return self.ptrs[rank] + offset
+
+
+class PeerGroup:
+    """Arena + flag block: what one exchange launch needs."""
+
+    def __init__(self, arena_bytes: int, device: torch.device, group=None):
+        self.arena = PeerArena(arena_bytes + 4096, device, group)
+        self.rank, self.world, self.device = self.arena.rank, self.arena.world, device
+        flag_off = self.arena.carve(nat.PEER_FLAG_BYTES)
+        self.native = nat.GbPeerGroup()
+        self.native.rank, self.native.world = self.rank, self.world
+        for r in range(self.world):
+            self.native.flags[r] = self.arena.ptr(r, flag_off)
+        dist.barrier(group)          # every rank has mapped every block before the first launch
+
+    def allgather(self, pieces) -> None:
+        """``pieces``: (src_ptr, rows, row_bytes, src_pitch, dst_offset, dst_pitch); the piece lands
+        at arena offset ``dst_offset`` on every rank."""
+        arr = (nat.GbPeerPiece * max(len(pieces), 1))()
+        for i, (src, rows, row_bytes, src_pitch, dst_off, dst_pitch) in enumerate(pieces):
+            q = arr[i]
+            q.src, q.rows, q.row_bytes, q.src_pitch, q.dst_pitch = src, rows, row_bytes, src_pitch, dst_pitch
+            for r in range(self.world):
+                q.dst[r] = self.arena.ptr(r, dst_off)
+        lib = self.arena.lib
+        nat.check(lib.gb_peer_allgather(ctypes.byref(self.native), arr, len(pieces),
+                                        nat.stream_ptr(self.device)), lib)
+
+    def barrier(self) -> None:
+        lib = self.arena.lib
+        nat.check(lib.gb_peer_barrier(ctypes.byref(self.native), nat.stream_ptr(self.device)), lib)
+
+
+class PeerShardedCBLinear(torch.nn.Module):
+    """Column-parallel linear whose all-gather is one peer-store launch.  ``local`` maps x[M, K]
+    to this rank's [M, N/world] columns, laid out role by role (an equal slice of every role,
+    :func:`gridbook_b200.parallel.shard_row_ranges`)."""
+
+    def __init__(self, local, partition_sizes, peers: PeerGroup, max_rows: int = 16):
+        super().__init__()
+        self.local, self.peers = local, peers
+        self.partition_sizes = [int(p) for p in partition_sizes]
+        world, rank = peers.world, peers.rank
+        for n in self.partition_sizes:
+            if n % world:
+                raise ValueError(f"role of {n} rows does not divide over {world} ranks")
+        self.N = sum(self.partition_sizes)
+        self.n_local = self.N // world
+        self.max_rows = max_rows
+        self.out_off = peers.arena.carve(max_rows * self.N * 2)
+        # (local column, global column, width) of every role's slice
+        self.roles, lcol, gcol = [], 0, 0
+        for n in self.partition_sizes:
+            per = n // world
+            self.roles.append((lcol, gcol + rank * per, per))
+            lcol += per
+            gcol += n
+        if len(self.roles) > 4:
+            raise ValueError("at most four roles per fused module")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = self.local(x)
+        lead = y.shape[:-1]
+        y2 = y.reshape(-1, self.n_local).contiguous()
+        M = y2.shape[0]
+        if M > self.max_rows:
+            raise ValueError(f"{M} rows exceed the {self.max_rows} this layer reserved peer memory for")
+        base = y2.data_ptr()
+        pieces = [(base + lc * 2, M, w * 2, self.n_local * 2, self.out_off + gc * 2, self.N * 2)
+                  for lc, gc, w in self.roles]
+        self.peers.allgather(pieces)
+        full = self.peers.arena.tensor(self.out_off, (M, self.N), torch.bfloat16)
+        return full.reshape(*lead, self.N)
+
+
+class PeerExpertParallelMoE(torch.nn.Module):
+    """Expert-parallel routed layer over peer memory.  ``moe_layer`` is a
+    :class:`gridbook_b200.moe.CBMoE` holding this rank's ``E / world`` experts (global ids
+    ``[rank * E/world, (rank+1) * E/world)``); every rank brings the same number of tokens."""
+
+    def __init__(self, num_experts: int, moe_layer, peers: PeerGroup, max_tokens: int, topk: int, hidden: int):
+        super().__init__()
+        self.E, self.layer, self.peers = num_experts, moe_layer, peers
+        self.world, self.rank = peers.world, peers.rank
+        if num_experts % self.world:
+            raise ValueError(f"{num_experts} experts do not divide over {self.world} ranks")
+        self.e_local = num_experts // self.world
+        self.max_tokens, self.topk, self.hidden = max_tokens, topk, hidden
+        a = peers.arena
+        self.x_off = a.carve(self.world * max_tokens * hidden * 2)
+        self.id_off = a.carve(self.world * max_tokens * topk * 4)
+        self.back_off = a.carve(max_tokens * topk * hidden * 2)
+        self._x_row = {}
+
+    def forward(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        from . import ops
+        rule = ops.ACT_SCALE_RULE
+        method, layer = self.layer.method, self.layer
+        T, topk = topk_ids.shape
+        H, world = self.hidden, self.world
+        if T > self.max_tokens or topk != self.topk or x.shape[-1] != H:
+            raise ValueError(f"batch [{T}, top-{topk}, {x.shape[-1]}] does not fit the reserved peer memory")
+        if T == 0:
+            raise ValueError("every rank must bring at least one token to the peer exchange")
+        dev = x.device
+        b13 = kernels.fp4_act_qdq if method.fmt13.is_fp4 else kernels.fp8_act_qdq
+        b2 = kernels.fp4_act_qdq if method.fmt2.is_fp4 else kernels.fp8_act_qdq
+        ids = topk_ids.to(torch.int32).contiguous()
+        # the bucket is per token, so it can run before the rows travel
+        xq = b13(x.reshape(T, H).to(torch.bfloat16).contiguous(), rule)
+        self.peers.allgather([
+            (xq.data_ptr(), 1, T * H * 2, T * H * 2, self.x_off + self.rank * T * H * 2, T * H * 2),
+            (ids.data_ptr(), 1, T * topk * 4, T * topk * 4, self.id_off + self.rank * T * topk * 4, T * topk * 4),
+        ])
+        x_all = self.peers.arena.tensor(self.x_off, (world * T, H), torch.bfloat16)
+        ids_all = self.peers.arena.tensor(self.id_off, (world * T, topk), torch.int32)
+        _, offsets, order = kernels.moe_route(ids_all, self.e_local, expert_base=self.rank * self.e_local)
+        key = (world * T, topk)
+        x_row = self._x_row.get(key)
+        if x_row is None:
+            x_row = (torch.arange(world * T * topk, device=dev, dtype=torch.int32) // topk).contiguous()
+            self._x_row[key] = x_row
+        a = kernels.moe_gemv(x_all, layer._cb_w13, offsets, order, x_row=x_row, swiglu=True, clear=False)
+        aq = b2(a, rule)
+        rows = nat.GbPeerRows()
+        rows.rows_per_rank = T * topk
+        for r in range(world):
+            rows.base[r] = self.peers.arena.ptr(r, self.back_off)
+        kernels.moe_gemv(aq, layer._cb_w2, offsets, order, peer_rows=rows)
+        self.peers.barrier()
+        back = self.peers.arena.tensor(self.back_off, (T * topk, H), torch.bfloat16)
+        # the loop chain multiplies by the bf16-rounded router weight (gridbook/moe.py:2407-2408)
+        pair_w = topk_weights.reshape(-1).to(torch.bfloat16).to(torch.float32)
+        out = kernels.moe_combine(back, pair_w, T, topk, topk_ids=ids, E=self.E)
+        return out.to(x.dtype).reshape(x.shape)

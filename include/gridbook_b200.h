@@ -156,8 +156,10 @@ GB_API int gb_gemm_tn(const void* A, const void* B, void* D_bf16, int64_t M, int
  *   order [P]: sorted position -> flat pair index t*topk+slot (token-ascending per expert).
  * Optional (both or neither): topk_weights [P] fp32 in, pair_w [P] fp32 out = the combine
  * weight of every pair, i.e. the router weight rounded to bf16 (gridbook/moe.py:2407-2408)
- * and zero for a dropped pair (gridbook/ops.py:764-784), so no separate masking pass runs. */
-GB_API int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E,
+ * and zero for a dropped pair (gridbook/ops.py:764-784), so no separate masking pass runs.
+ * expert_base: the experts held here are the global ids [expert_base, expert_base + E); ids
+ * outside that range are dropped like padding (expert parallelism; 0 on one GPU). */
+GB_API int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E, int64_t expert_base,
                  int32_t* counts, int32_t* offsets, int32_t* order,
                  const float* topk_weights, float* pair_w, void* stream);
 
@@ -167,12 +169,19 @@ GB_API int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_
  * weight_scale + e*rows.  Pairs come grouped by expert through (offsets, order); pair p
  * reads activation row x_row[p] (NULL = p) and writes y[p].  When `swiglu` is set the
  * kernel's output is silu(gate)*up of rows [0,rows/2) and [rows/2,rows) -> y[P, rows/2]
- * (replaces native_moe_activation, gridbook/native_cutlass.py:129-155). */
+ * (replaces native_moe_activation, gridbook/native_cutlass.py:129-155).
+ * y_rows (optional, not with swiglu): instead of y_bf16, pair p's output row goes to
+ * y_rows->base[p / rows_per_rank] + (p % rows_per_rank) * rows * 2 bytes, i.e. straight into
+ * the buffer of the rank the pair came from (expert-parallel combine over peer memory). */
+typedef struct gb_peer_rows {
+  void* base[8];
+  int64_t rows_per_rank;
+} gb_peer_rows;
 GB_API int64_t gb_moe_gemv_workspace_bytes(int64_t P, int64_t rows);
 GB_API int gb_moe_gemv(const void* x_bf16, const int32_t* x_row, const gb_weight* w,
                 int64_t expert_stride, int64_t E, const int32_t* offsets,
                 const int32_t* order, int64_t P, int swiglu, void* y_bf16,
-                void* workspace, int64_t workspace_bytes, void* stream);
+                const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes, void* stream);
 
 /* out[t] = sum over the token's topk pairs of w[p] * y[p], fp32 accumulate, one bf16
  * rounding; replaces cb_moe_combine (gridbook/csrc/cb_gemv.cu:1853-1871,2140-2158).
@@ -181,6 +190,38 @@ GB_API int gb_moe_gemv(const void* x_bf16, const int32_t* x_row, const gb_weight
  * clearing beforehand. */
 GB_API int gb_moe_combine(const void* y_bf16, const float* pair_w, const int32_t* topk_ids,
                    int64_t E, int64_t T, int64_t topk, int64_t H, void* out_bf16, void* stream);
+
+/* ---- peer-memory exchange on one NVSwitch node ------------------------------- */
+/* None of this has a counterpart in the reference, which runs on one GPU
+ * (gridbook/config.py:565-576).  One process per GPU; a buffer from gb_peer_alloc is exported
+ * as a 64-byte handle, sent to the other ranks by any host channel, and mapped there with
+ * gb_peer_open.  The allocation, export and mapping calls are setup-time only. */
+#define GB_PEER_MAX 8
+#define GB_PEER_HANDLE_BYTES 64
+#define GB_PEER_FLAG_BYTES 128
+GB_API int gb_peer_alloc(int64_t bytes, void** ptr);          /* zero-filled device buffer */
+GB_API int gb_peer_free(void* ptr);
+GB_API int gb_peer_export(void* ptr, void* handle64);
+GB_API int gb_peer_open(const void* handle64, void** ptr);
+GB_API int gb_peer_close(void* ptr);
+
+typedef struct gb_peer_group {
+  int32_t rank, world;              /* world <= GB_PEER_MAX */
+  void* flags[GB_PEER_MAX];         /* flags[r]: rank r's GB_PEER_FLAG_BYTES block (own: gb_peer_alloc; others: mapped) */
+} gb_peer_group;
+
+typedef struct gb_peer_piece {
+  const void* src;                  /* this rank's piece, rows x row_bytes at src_pitch */
+  void* dst[GB_PEER_MAX];           /* where the piece goes inside rank r's buffer (dst_pitch between rows) */
+  int64_t rows, row_bytes, src_pitch, dst_pitch;
+} gb_peer_piece;
+
+/* All-gather by peer stores: every rank copies its pieces (up to four) into every rank's
+ * buffer, between a "buffers are free" and a "stores are visible" exchange of flags, in one
+ * launch.  Every rank must make the same sequence of gb_peer_allgather / gb_peer_barrier calls.
+ * A peer that does not show up within two seconds raises gb_device_status (3); nothing hangs. */
+GB_API int gb_peer_allgather(const gb_peer_group* g, const gb_peer_piece* pieces, int n_pieces, void* stream);
+GB_API int gb_peer_barrier(const gb_peer_group* g, void* stream);
 
 #ifdef __cplusplus
 }
