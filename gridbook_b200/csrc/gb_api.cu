@@ -51,6 +51,14 @@ static int prepare_locked(int dev) {
   return GB_OK;
 }
 
+bool gb_pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("GRIDBOOK_B200_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
 int gb_sm_count() {
   const int dev = current_device_slot();
   if (dev < 0) return 0;

@@ -19,6 +19,25 @@ int gb_fail(int code, const char* fmt, ...);
 int gb_sm_count();                 // SMs of the current device (cached)
 int* gb_status_word();             // device int the kernels raise on a timed-out wait
 
+bool gb_pdl_enabled();             // false when GRIDBOOK_B200_PDL=0 (plain stream order)
+
+// Kernel launch with the programmatic-stream-serialization attribute (see gb_pdl_wait).
+template <typename... KArgs, typename... Args>
+inline cudaError_t gb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = gb_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 #define GB_REQUIRE(cond, ...)                           \
   do {                                                  \
     if (!(cond)) return gb_fail(GB_EINVAL, __VA_ARGS__); \
@@ -213,6 +232,15 @@ GB_DEVINL void gb_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 GB_DEVINL void gb_mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gb_smem_u32(bar)) : "memory");
 }
+
+// Programmatic dependent launch.  A kernel launched through gb_launch may start while the
+// kernel before it on the stream is still running; gb_pdl_wait() returns once that kernel
+// (and everything before it) has completed and its writes are visible, so it must come before
+// the first read of anything an earlier kernel produced and before the first global write.
+// What sits in front of it - barrier setup, the prefetch of weights, tables of constants -
+// overlaps the predecessor's tail.  gb_pdl_launch_dependents() lets the successor start.
+GB_DEVINL void gb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+GB_DEVINL void gb_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 GB_DEVINL uint64_t gb_globaltimer_ns() {
   uint64_t t;

@@ -15,6 +15,8 @@ constexpr int kThreads = 256;
 __global__ void __launch_bounds__(kThreads)
 fp4_group16_qdq_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out,
                        int64_t n_groups, int scale_rule) {
+  gb_pdl_launch_dependents();
+  gb_pdl_wait();
   const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (g >= n_groups) return;
   const uint4* src = reinterpret_cast<const uint4*>(x + g * 16);
@@ -31,6 +33,8 @@ fp4_group16_qdq_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ ou
 __global__ void __launch_bounds__(kThreads)
 fp8_token_qdq_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, int64_t K,
                      int scale_rule) {
+  gb_pdl_launch_dependents();
+  gb_pdl_wait();
   const uint16_t* row = x + (int64_t)blockIdx.x * K;
   uint16_t* orow = out + (int64_t)blockIdx.x * K;
   __shared__ float red[kThreads / 32];
@@ -213,9 +217,8 @@ int gb_fp4_act_qdq(const void* x, void* out, int64_t M, int64_t K, int scale_rul
   if (M == 0) return GB_OK;
   const int64_t groups = M * (K / 16);
   const unsigned blocks = (unsigned)((groups + kThreads - 1) / kThreads);
-  fp4_group16_qdq_kernel<<<blocks, kThreads, 0, (cudaStream_t)stream>>>(
-      (const uint16_t*)x, (uint16_t*)out, groups, scale_rule);
-  GB_LAUNCH_OK("fp4_group16_qdq_kernel");
+  GB_CUDA_OK(gb_launch(fp4_group16_qdq_kernel, dim3(blocks), dim3(kThreads), 0, (cudaStream_t)stream,
+                       (const uint16_t*)x, (uint16_t*)out, groups, scale_rule));
   return GB_OK;
 }
 
@@ -223,9 +226,8 @@ int gb_fp8_act_qdq(const void* x, void* out, int64_t M, int64_t K, int scale_rul
   GB_REQUIRE(x && out, "null activation pointer");
   GB_REQUIRE(M >= 0 && K > 0, "bad shape M=%lld K=%lld", (long long)M, (long long)K);
   if (M == 0) return GB_OK;
-  fp8_token_qdq_kernel<<<(unsigned)M, kThreads, 0, (cudaStream_t)stream>>>(
-      (const uint16_t*)x, (uint16_t*)out, K, scale_rule);
-  GB_LAUNCH_OK("fp8_token_qdq_kernel");
+  GB_CUDA_OK(gb_launch(fp8_token_qdq_kernel, dim3((unsigned)M), dim3(kThreads), 0, (cudaStream_t)stream,
+                       (const uint16_t*)x, (uint16_t*)out, K, scale_rule));
   return GB_OK;
 }
 

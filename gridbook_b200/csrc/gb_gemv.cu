@@ -441,7 +441,9 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
   }
   if (tid < 16 && p.fmt.scale_coding == GB_SCALE_V2)
     sub_tab[tid] = (uint16_t)(__float_as_uint(p.compose[127 * 16 + tid]) >> 16);   // T[c], exact in bf16
+  gb_pdl_launch_dependents();
   if constexpr (kMoE) {
+    gb_pdl_wait();                     // the routing tables come from the kernel before
     // Every CTA walks the same global tile list; build its per-expert prefix once, in shared
     // memory, so that finding a tile is a short search instead of a pass over all experts.
     for (int e = tid; e <= p.E; e += kThreads) offs_s[e] = p.offsets[e];
@@ -503,6 +505,10 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
     more = more && ahead.next(ta);
     if (more) issue_task(p, ta, warp, lane, my_ring + (size_t)i * p.stage_bytes, &my_bar[i]);
   }
+
+  // Dense: everything above read weights and constants only, and ran alongside the tail of
+  // the kernel before; the activations and the outputs are touched from here on.
+  if constexpr (!kMoE) gb_pdl_wait();
 
   int64_t lut_off = -1;
   int x_expert = -1, x_m0 = -1, cur_slice = -1;
@@ -756,6 +762,8 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
 
 __global__ void gemv_finalize_kernel(const float* __restrict__ ws, float global_scale,
                                      uint16_t* __restrict__ y, int64_t total) {
+  gb_pdl_launch_dependents();
+  gb_pdl_wait();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < total) y[i] = (uint16_t)gb_f32_to_bf16_bits(ws[i] * global_scale);
 }
@@ -945,12 +953,11 @@ int gb_gemv(const void* x, int64_t M, const gb_weight* w, int act, int scale_rul
   if (grid > tiles) grid = tiles;
   grid = (grid / p.ksplit) * p.ksplit;
   if (grid < p.ksplit) grid = p.ksplit;
-  pick_kernel(fmt, false, wide, literal_aligned(p))<<<grid, 32 * p.warps, smem, stream>>>(p);
-  GB_LAUNCH_OK("gemv_kernel");
+  GB_CUDA_OK(gb_launch(pick_kernel(fmt, false, wide, literal_aligned(p)), dim3(grid), dim3(32 * p.warps), smem, stream, p));
   if (p.ksplit > 1) {
     const int64_t total = M * w->rows;
-    gemv_finalize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(p.ws, p.global_scale, p.y, total);
-    GB_LAUNCH_OK("gemv_finalize_kernel");
+    GB_CUDA_OK(gb_launch(gemv_finalize_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                         (const float*)p.ws, p.global_scale, p.y, total));
   }
   return GB_OK;
 }
@@ -1010,8 +1017,7 @@ int gb_moe_gemv(const void* x, const int32_t* x_row, const gb_weight* w, int64_t
   size_t smem = 0;
   rc = plan(p, mc, true, sms, &smem);
   if (rc != GB_OK) return rc;
-  pick_kernel(fmt, true, wide, literal_aligned(p))<<<sms, 32 * p.warps, smem, stream>>>(p);
-  GB_LAUNCH_OK("gemv_kernel (routed)");
+  GB_CUDA_OK(gb_launch(pick_kernel(fmt, true, wide, literal_aligned(p)), dim3(sms), dim3(32 * p.warps), smem, stream, p));
   return GB_OK;
 }
 

@@ -89,24 +89,20 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
     }
     gb_fence_barrier_init();
   }
-  // ---- this slice of the activation row, through its bucket, into shared memory ----
-  if (tid < ns * 16) {
-    const uint4* src = reinterpret_cast<const uint4*>(p.x + (int64_t)sb0 * 256 + tid * 16);
-    const uint4 r0 = src[0], r1 = src[1];
-    uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-    if (p.act == GB_ACT_FP4_GROUP16) gb_fp4_group16_qdq(w, p.scale_rule);
-    uint4* dst = reinterpret_cast<uint4*>(xq + tid * 16);
-    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-  }
   __syncthreads();
+  gb_pdl_launch_dependents();
 
   if (warp == kConsumers) {
     // ------------------------------ producer ------------------------------
+    // The weight stream depends on nothing an earlier kernel wrote: the ring fills while the
+    // kernel before this one is still finishing.
     if (lane == 0) {
       for (int st = 0; st < n_stages; ++st) {
         const int s = st % kDotStages;
-        if (!gb_mbar_wait(&empty_bar[s], ((st / kDotStages) & 1) ^ 1)) atomicExch(p.status, 21);
+        if (!gb_mbar_wait(&empty_bar[s], ((st / kDotStages) & 1) ^ 1)) {
+          gb_pdl_wait();
+          atomicExch(p.status, 21);
+        }
         gb_mbar_expect_tx(&full_bar[s], kStageBytes);
         asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -118,22 +114,61 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
     return;
   }
 
-  // ---- inner-product tables: D[16 codes x 8 positions] = codebook[16 x 8] . x[8 x 8] per MMA ----
+  // ---- inner-product tables ----
+  // One unit = one superblock column x eight codes x all 32 positions: two MMAs with the
+  // activation segments as the 16 rows (A[m][k] = x[8 (16 h + m) + k], k < 8) and the eight
+  // codewords as the columns (B[k][n] = codebook[c0 + n][k]).  Warp w owns code blocks 2w and
+  // 2w + 1 for every column, so its two B fragments are loaded once, before the wait.
+  const int g = lane >> 2, t = lane & 3;
+  uint32_t bfrag[2];
   {
-    const int g = lane >> 2, t = lane & 3;
     const uint32_t* cb32 = reinterpret_cast<const uint32_t*>(p.codebook);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) bfrag[j] = __ldg(cb32 + ((2 * warp + j) * 8 + g) * 4 + t);
+  }
+
+  // ---- this slice of the activation row, through its bucket, into shared memory ----
+  gb_pdl_wait();                       // the activations (and the partial-sum slots) belong to earlier kernels
+  if (tid < ns * 16) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.x + (int64_t)sb0 * 256 + tid * 16);
+    const uint4 r0 = src[0], r1 = src[1];
+    uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+    if (p.act == GB_ACT_FP4_GROUP16) gb_fp4_group16_qdq(w, p.scale_rule);
+    uint4* dst = reinterpret_cast<uint4*>(xq + tid * 16);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
+
+  {
     const uint32_t* xq32 = reinterpret_cast<const uint32_t*>(xq);
-    for (int tile = warp; tile < ns * 64; tile += kConsumers) {
-      const int s = tile >> 6, cblk = (tile >> 2) & 15, pblk = tile & 3;
-      const int c_lo = cblk * 16 + g, pos = pblk * 8 + g;
-      // A[m][k] = codebook[c][k] for k < 8, zero above; B[k][n] = x[8 pos_n + k]
-      const uint32_t a[4] = {__ldg(cb32 + c_lo * 4 + t), __ldg(cb32 + (c_lo + 8) * 4 + t), 0u, 0u};
-      const uint32_t b0 = xq32[(s * 256 + pos * 8) / 2 + t];
-      float d[4] = {0.f, 0.f, 0.f, 0.f};
-      gb_mma_bf16_16816(d, a, b0, 0u);
-      float* row_lo = table + ((s * 256 + c_lo) * 32 + pblk * 8 + 2 * t);
-      *reinterpret_cast<float2*>(row_lo) = make_float2(d[0] * 0x1p100f, d[1] * 0x1p100f);
-      *reinterpret_cast<float2*>(row_lo + 8 * 32) = make_float2(d[2] * 0x1p100f, d[3] * 0x1p100f);
+    for (int s = 0; s < ns; ++s) {
+      uint32_t a[2][4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        a[h][0] = xq32[s * 128 + (16 * h + g) * 4 + t];
+        a[h][1] = xq32[s * 128 + (16 * h + g + 8) * 4 + t];
+        a[h][2] = 0u;
+        a[h][3] = 0u;
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
+        gb_mma_bf16_16816(d0, a[0], bfrag[j], 0u);      // positions g, g + 8
+        gb_mma_bf16_16816(d1, a[1], bfrag[j], 0u);      // positions 16 + g, 24 + g
+        // v[cc][pb]: code 2t + cc of the block, position 8 pb + g
+        float v[2][4] = {{d0[0], d0[2], d1[0], d1[2]}, {d0[1], d0[3], d1[1], d1[3]}};
+        // Store number q of a lane takes position block (t + q) & 3, so the four lanes that share
+        // g write four different bank octets: every store instruction covers all 32 banks once.
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          if (t & 1) { const float x0 = v[cc][0]; v[cc][0] = v[cc][1]; v[cc][1] = v[cc][2]; v[cc][2] = v[cc][3]; v[cc][3] = x0; }
+          if (t & 2) { const float x0 = v[cc][0], x1 = v[cc][1]; v[cc][0] = v[cc][2]; v[cc][1] = v[cc][3]; v[cc][2] = x0; v[cc][3] = x1; }
+          float* row = table + ((s * 256 + (2 * warp + j) * 8 + 2 * t + cc) * 32 + g);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) row[((t + q) & 3) * 8] = v[cc][q] * 0x1p100f;
+        }
+      }
     }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
@@ -173,6 +208,8 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
 
 __global__ void dot_finalize_kernel(const float* __restrict__ ws, int n_slices, int64_t N, float global_scale,
                                     uint16_t* __restrict__ y) {
+  gb_pdl_launch_dependents();
+  gb_pdl_wait();
   const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= N) return;
   float acc = 0.f;
@@ -224,10 +261,9 @@ int gb_gemv_dot(const void* x, const gb_weight* w, int act, int scale_rule, void
   int rc = gb_tensor_map_bytes_2d(&map, w->qw, (uint64_t)p.n_sb * 48u, (uint64_t)w->rows, (uint64_t)w->row_stride,
                                   kRowBytes, kStageRows);
   if (rc != GB_OK) return rc;
-  gemv_dot_kernel<<<p.n_slices * p.n_groups, kDotThreads, kDotSmem, stream>>>(map, p);
-  GB_LAUNCH_OK("gemv_dot_kernel");
+  GB_CUDA_OK(gb_launch(gemv_dot_kernel, dim3(p.n_slices * p.n_groups), dim3(kDotThreads), kDotSmem, stream, map, p));
   const float gs = w->global_scale == 0.0f ? 1.0f : w->global_scale;
-  dot_finalize_kernel<<<(unsigned)((w->rows + 255) / 256), 256, 0, stream>>>(p.ws, p.n_slices, w->rows, gs, (uint16_t*)y);
-  GB_LAUNCH_OK("dot_finalize_kernel");
+  GB_CUDA_OK(gb_launch(dot_finalize_kernel, dim3((unsigned)((w->rows + 255) / 256)), dim3(256), 0, stream,
+                       (const float*)p.ws, p.n_slices, (int64_t)w->rows, gs, (uint16_t*)y));
   return GB_OK;
 }

@@ -16,7 +16,9 @@ moe_route_kernel(const int32_t* __restrict__ ids, int P, int E, int first_expert
   int32_t* cnt = sh;
   int32_t* off = sh + E;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = kRouteThreads / 32;
+  gb_pdl_launch_dependents();
   for (int e = tid; e < E; e += kRouteThreads) cnt[e] = 0;
+  gb_pdl_wait();
   __syncthreads();
   for (int i = tid; i < P; i += kRouteThreads) {
     const int id = ids[i] - first_expert;
@@ -64,6 +66,8 @@ moe_route_kernel(const int32_t* __restrict__ ids, int P, int E, int first_expert
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const uint16_t* __restrict__ y, const float* __restrict__ pair_w,
                    const int32_t* __restrict__ ids, int E, int topk, int64_t H, uint16_t* __restrict__ out) {
+  gb_pdl_launch_dependents();
+  gb_pdl_wait();
   const int64_t t = blockIdx.y;
   const int64_t h2 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // pair of columns
   if (h2 * 2 >= H) return;
@@ -93,9 +97,9 @@ int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E, in
   GB_REQUIRE(T >= 0 && topk >= 1 && E >= 1 && E <= 4096, "bad routing shape T=%lld topk=%lld E=%lld",
              (long long)T, (long long)topk, (long long)E);
   GB_REQUIRE(T * topk < (1ll << 30), "too many routed pairs");
-  moe_route_kernel<<<1, kRouteThreads, (size_t)(2 * E + 1) * sizeof(int32_t), (cudaStream_t)stream>>>(
-      topk_ids, (int)(T * topk), (int)E, (int)expert_base, counts, offsets, order, topk_weights, pair_w);
-  GB_LAUNCH_OK("moe_route_kernel");
+  GB_CUDA_OK(gb_launch(moe_route_kernel, dim3(1), dim3(kRouteThreads), (size_t)(2 * E + 1) * sizeof(int32_t),
+                       (cudaStream_t)stream, topk_ids, (int)(T * topk), (int)E, (int)expert_base, counts, offsets,
+                       order, topk_weights, pair_w));
   return GB_OK;
 }
 
@@ -106,9 +110,8 @@ int gb_moe_combine(const void* y, const float* pair_w, const int32_t* topk_ids, 
              (long long)T, (long long)topk, (long long)H);
   if (T == 0) return GB_OK;
   dim3 grid((unsigned)((H / 2 + 255) / 256), (unsigned)T);
-  moe_combine_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)y, pair_w, topk_ids, (int)E,
-                                                           (int)topk, H, (uint16_t*)out);
-  GB_LAUNCH_OK("moe_combine_kernel");
+  GB_CUDA_OK(gb_launch(moe_combine_kernel, grid, dim3(256), 0, (cudaStream_t)stream, (const uint16_t*)y, pair_w,
+                       topk_ids, (int)E, (int)topk, H, (uint16_t*)out));
   return GB_OK;
 }
 

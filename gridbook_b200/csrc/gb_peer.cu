@@ -63,6 +63,8 @@ __global__ void __launch_bounds__(256) peer_exchange_kernel(const __grid_constan
   __shared__ int s_last;
   uint32_t* mine = p.flags[p.rank];
   const int tid = threadIdx.x;
+  gb_pdl_launch_dependents();
+  gb_pdl_wait();                      // arriving here says: everything enqueued before has finished
   if (tid == 0) s_epoch = *reinterpret_cast<volatile uint32_t*>(mine + 16) + 1u;
   __syncthreads();
   const uint32_t epoch = s_epoch;
@@ -206,8 +208,7 @@ int gb_peer_allgather(const gb_peer_group* g, const gb_peer_piece* pieces, int n
   int grid = (int)((bytes / 16 + 255) / 256);
   if (grid < 1) grid = 1;
   if (grid > 32) grid = 32;          // all CTAs resident at once; 32 saturate the links at these sizes
-  peer_exchange_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p);
-  GB_LAUNCH_OK("peer_exchange_kernel");
+  GB_CUDA_OK(gb_launch(peer_exchange_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, p));
   return GB_OK;
 }
 
