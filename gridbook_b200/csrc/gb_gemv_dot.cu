@@ -4,14 +4,21 @@
 // With one 256-entry codebook and one activation row, a codeword's contribution to the dot
 // product can only take 256 values per position: T[s][c][v] = <codebook[c], x[256 s + 8 v ..+8]>.
 // A CTA owns four superblock columns of K and a band of rows.  It builds T for its columns
-// once (tensor cores: codebook x activation segments, 128 KiB of fp32 in shared memory; the
+// once (tensor cores: activation segments x codebook, 128 KiB of fp32 in shared memory; the
 // fp4 activation bucket is applied on the way in), then streams its rows' 192-byte slices
-// through a TMA ring and spends, per 16 weights, two table lookups, one add and one scaled
-// accumulate.  That is about 7 warp instructions and 4 shared-memory wavefronts per 48 packed
-// bytes, against ~270 and ~80 for expanding every weight, which is what lets a 1.5-bit format
-// approach the HBM stream.  Lanes 0..15 of a warp walk one row, lanes 16..31 the next; lane l
-// owns group l (positions 2l, 2l+1) so its two lookups always fall in banks 2l and 2l+1, and
-// the two half-warps take them in opposite order: no bank conflicts.
+// through a TMA ring.  Per superblock a lane owns four codewords (two groups): one 32-bit load
+// of codes, four table lookups, one 16-bit load of scales, two adds and two scaled
+// accumulates - nine instructions per 16 weights against ~270 for expanding every weight,
+// which is what lets a 1.5-bit format approach the HBM stream.
+//
+// Shared-memory geometry.  A table row is 256 bytes: one codeword, two superblock columns, 32
+// positions each; columns {0,1} fill one 64 KiB region, columns {2,3} the next, and the
+// regions start on 64 KiB boundaries of the shared window.  A lookup address is then the
+// lane's constant (region + position) with the code dropped into byte 1: one byte permute,
+// no shift, no add.  The bank of a lookup is its position alone.  Eight lanes walk one row,
+// so a warp takes four rows at a time; row r of the four reads its positions in the order
+// j = q ^ r (q = 0..3), and rows 2,3 work two superblock columns ahead of rows 0,1, which
+// makes the code loads, the scale loads and all four lookups of a warp conflict-free.
 //
 // K slices write their partial sums to their own slot; a second tiny kernel adds the slots,
 // applies the global scale and rounds to bf16 once.
@@ -28,8 +35,14 @@ constexpr int kStageRows = 4 * kConsumers;    // 64 rows per stage, four per war
 constexpr int kRowBytes = kS * 48;            // 192 bytes of each row per stage
 constexpr int kStageBytes = kStageRows * kRowBytes;
 constexpr int kDotStages = 6;
-constexpr int kTableFloats = kS * 256 * 32;
-constexpr int kDotSmem = kTableFloats * 4 + kDotStages * kStageBytes + kS * 512 + 256 + 128;
+constexpr int kFrontStages = 5;               // ring stages in front of the tables, the rest behind
+constexpr uint32_t kRegion = 0x10000u;        // 64 KiB: 256 codes x 256-byte rows
+constexpr int kTableBytes = 2 * (int)kRegion;
+constexpr int kBackBytes = (kDotStages - kFrontStages) * kStageBytes + kS * 512 + 256;
+// Front ring + alignment slack up to the first 64 KiB boundary, tables, back part.  The
+// kernel checks at run time that the window it was given really holds this layout.
+constexpr int kDotSmem = (int)kRegion + kTableBytes + kBackBytes;
+static_assert(kFrontStages * kStageBytes + 4096 <= (int)kRegion, "front ring must end before the first boundary");
 
 struct DotParams {
   const uint16_t* x;        // [K] bf16
@@ -41,38 +54,73 @@ struct DotParams {
   int* status;
 };
 
-GB_DEVINL float lds_f32(uint32_t a) {
+// Shared-memory loads that depend on a token (the result of the barrier wait that made the
+// data visible): plain asm the scheduler may reorder freely, but never above that wait.
+template <int kImm>
+GB_DEVINL float ldt_f32(uint32_t a, uint32_t tok) {
   float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+  asm("ld.shared.f32 %0, [%1+%2]; // %3" : "=f"(v) : "r"(a), "n"(kImm), "r"(tok));
   return v;
 }
-GB_DEVINL uint32_t lds_b16(uint32_t a) {
+template <int kImm>
+GB_DEVINL uint32_t ldt_u32(uint32_t a, uint32_t tok) {
   uint32_t v;
-  asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1]; cvt.u32.u16 %0, t; }" : "=r"(v) : "r"(a));
+  asm("ld.shared.u32 %0, [%1+%2]; // %3" : "=r"(v) : "r"(a), "n"(kImm), "r"(tok));
   return v;
 }
-// One superblock of one row for this lane's group: two table lookups, their sum, times the
-// group's scale.  The scale byte is loaded sign-extended, so one shift and one mask put its
-// exponent/mantissa into the fp32 fields (value * 2^-120, subnormal codes included) and its
-// sign into bit 31; the table carries the compensating 2^100 so products stay normal.
-GB_DEVINL float dot_superblock(uint32_t sbp, uint32_t tabA, uint32_t tabB, int l, uint32_t sel, float acc) {
-  const uint32_t idx2 = __byte_perm(lds_b16(sbp + 2u * l), 0u, sel);       // (code A) | (code B) << 8
-  const float tA = lds_f32(tabA + ((idx2 & 0xFFu) << 7));
-  const float tB = lds_f32(tabB + ((idx2 >> 8) << 7));
-  int32_t sc;
-  asm volatile("ld.shared.s8 %0, [%1];" : "=r"(sc) : "r"(sbp + 32u + l));
-  const float f = __uint_as_float(((uint32_t)sc << 20) & 0x87F00000u);
-  return fmaf(tA + tB, f, acc);
+template <int kImm>
+GB_DEVINL uint32_t ldt_u16(uint32_t a, uint32_t tok) {
+  uint32_t v;
+  asm("{ .reg .u16 t; ld.shared.u16 t, [%1+%2]; cvt.u32.u16 %0, t; } // %3" : "=r"(v) : "r"(a), "n"(kImm), "r"(tok));
+  return v;
+}
+// Two E4M3 bytes (low 16 bits of w) -> two fp32, exactly (subnormal codes included).
+GB_DEVINL void e4m3x2_to_f32(uint32_t w, float& lo, float& hi) {
+  asm("{ .reg .b16 p, l, h; .reg .b32 q;\n"
+      "  cvt.u16.u32 p, %2;\n"
+      "  cvt.rn.f16x2.e4m3x2 q, p;\n"
+      "  mov.b32 {l, h}, q;\n"
+      "  cvt.f32.f16 %0, l;\n"
+      "  cvt.f32.f16 %1, h; }"
+      : "=f"(lo), "=f"(hi) : "r"(w));
+}
+
+// One superblock column of one row for this lane's two groups.  `rowp` already points at the
+// lane's superblock; kOff is the column's offset inside a table row (0 or 128).
+template <int kPtrOff, int kTabOff>
+GB_DEVINL void dot_superblock(uint32_t rowp_codes, uint32_t rowp_scales, const uint32_t (&base)[4], const uint32_t (&sel)[4],
+                              uint32_t sel_sc, uint32_t tok, float& acc0, float& acc1) {
+  const uint32_t codes = ldt_u32<kPtrOff>(rowp_codes, tok);
+  const uint32_t sc = ldt_u16<kPtrOff + 32>(rowp_scales, tok);
+  const float t0 = ldt_f32<kTabOff>(__byte_perm(codes, base[0], sel[0]), tok);
+  const float t1 = ldt_f32<kTabOff>(__byte_perm(codes, base[1], sel[1]), tok);
+  const float t2 = ldt_f32<kTabOff>(__byte_perm(codes, base[2], sel[2]), tok);
+  const float t3 = ldt_f32<kTabOff>(__byte_perm(codes, base[3], sel[3]), tok);
+  float f01, f23;
+  e4m3x2_to_f32(__byte_perm(sc, 0u, sel_sc), f01, f23);
+  acc0 = fmaf(t0 + t1, f01, acc0);
+  acc1 = fmaf(t2 + t3, f23, acc1);
 }
 
 __global__ void __launch_bounds__(kDotThreads, 1)
 gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
-  extern __shared__ __align__(128) uint8_t smem[];
-  float* table = reinterpret_cast<float*>(smem);
-  uint8_t* ring = smem + kTableFloats * 4;
-  uint16_t* xq = reinterpret_cast<uint16_t*>(ring + kDotStages * kStageBytes);      // kS * 256 bf16
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t base_s = gb_smem_u32(smem);
+  // absolute shared addresses of the layout
+  const uint32_t tab_s = (base_s + kFrontStages * kStageBytes + (kRegion - 1)) & ~(kRegion - 1);
+  const uint32_t back_s = tab_s + kTableBytes;
+  if (back_s + kBackBytes > base_s + kDotSmem) {       // same verdict in every thread, before any barrier
+    if (threadIdx.x == 0) atomicExch(p.status, 23);
+    return;
+  }
+  uint8_t* table_b = smem + (tab_s - base_s);
+  uint8_t* back = smem + (back_s - base_s);
+  uint16_t* xq = reinterpret_cast<uint16_t*>(back + (kDotStages - kFrontStages) * kStageBytes);    // kS * 256 bf16
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(xq) + kS * 512);
   uint64_t* empty_bar = full_bar + kDotStages;
+  auto stage_addr = [&](int s) -> uint32_t {
+    return s < kFrontStages ? base_s + (uint32_t)s * kStageBytes : back_s + (uint32_t)(s - kFrontStages) * kStageBytes;
+  };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int slice = blockIdx.x % p.n_slices, group = blockIdx.x / p.n_slices;
@@ -106,7 +154,7 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
         gb_mbar_expect_tx(&full_bar[s], kStageBytes);
         asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-            ::"r"(gb_smem_u32(ring + (size_t)s * kStageBytes)), "l"(reinterpret_cast<uint64_t>(&map_w)),
+            ::"r"(stage_addr(s)), "l"(reinterpret_cast<uint64_t>(&map_w)),
               "r"(sb0 * 48), "r"((int)(row_begin + (int64_t)st * kStageRows)), "r"(gb_smem_u32(&full_bar[s]))
             : "memory");
       }
@@ -151,6 +199,8 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
         a[h][2] = 0u;
         a[h][3] = 0u;
       }
+      // T(s, code, pos) lives at region (s >> 1), row `code`, float (s & 1) * 32 + pos
+      float* col = reinterpret_cast<float*>(table_b + (size_t)(s >> 1) * kRegion) + (s & 1) * 32 + g;
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -164,9 +214,9 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
         for (int cc = 0; cc < 2; ++cc) {
           if (t & 1) { const float x0 = v[cc][0]; v[cc][0] = v[cc][1]; v[cc][1] = v[cc][2]; v[cc][2] = v[cc][3]; v[cc][3] = x0; }
           if (t & 2) { const float x0 = v[cc][0], x1 = v[cc][1]; v[cc][0] = v[cc][2]; v[cc][1] = v[cc][3]; v[cc][2] = x0; v[cc][3] = x1; }
-          float* row = table + ((s * 256 + (2 * warp + j) * 8 + 2 * t + cc) * 32 + g);
+          float* row = col + ((2 * warp + j) * 8 + 2 * t + cc) * 64;
 #pragma unroll
-          for (int q = 0; q < 4; ++q) row[((t + q) & 3) * 8] = v[cc][q] * 0x1p100f;
+          for (int q = 0; q < 4; ++q) row[((t + q) & 3) * 8] = v[cc][q];
         }
       }
     }
@@ -174,33 +224,51 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
 
   // ---- stream the rows ----
-  const int h = lane >> 4, l = lane & 15;
-  // Half-warp 0 looks up position 2l then 2l+1, half-warp 1 the other way round (its two index
-  // bytes are swapped once with a byte permute), so the 32 lanes of a lookup hit 32 banks.
-  const uint32_t sel = h ? 0x4401u : 0x4410u;
-  const uint32_t baseA = gb_smem_u32(table) + (uint32_t)(2 * l + h) * 4u;
-  const uint32_t baseB = gb_smem_u32(table) + (uint32_t)(2 * l + 1 - h) * 4u;
-  const uint32_t ring_s = gb_smem_u32(ring);
+  const int r = lane >> 3, lp = lane & 7, rh = r >> 1;
+  uint32_t base_lo[4], base_hi[4], sel[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int j = q ^ r;                                    // this lookup's codeword of the lane's four
+    base_lo[q] = tab_s + (uint32_t)rh * kRegion + (uint32_t)(4 * lp + j) * 4u;          // columns rh*2 + {0,1}
+    base_hi[q] = tab_s + (uint32_t)(rh ^ 1) * kRegion + (uint32_t)(4 * lp + j) * 4u;    // the other two
+    sel[q] = 0x7604u | ((uint32_t)j << 4);                  // byte 1 <- code j, bytes 0,2,3 <- the base
+  }
+  // lookups 0,1 fall in group r >> 1 of the lane's two, lookups 2,3 in the other
+  const uint32_t sel_sc = rh ? 0x4401u : 0x4410u;
   float* my_ws = p.ws + (int64_t)slice * p.N;
   for (int st = 0; st < n_stages; ++st) {
     const int s = st % kDotStages;
-    if (!gb_mbar_wait(&full_bar[s], (st / kDotStages) & 1)) atomicExch(p.status, 22);
+    uint32_t tok;
+    if (!gb_mbar_wait(&full_bar[s], (st / kDotStages) & 1, &tok)) atomicExch(p.status, 22);
+    const uint32_t rowp = stage_addr(s) + (uint32_t)(4 * warp + r) * kRowBytes;
+    float acc0 = 0.f, acc1 = 0.f;
+    if (ns == kS) {
+      // rows 0,1 of the warp take columns 0,1,2,3; rows 2,3 take 2,3,0,1
+      const uint32_t pa = rowp + (uint32_t)rh * 96u, pb = rowp + (uint32_t)(rh ^ 1) * 96u;
+      const uint32_t ca = pa + 4u * lp, sa = pa + 2u * lp, cb = pb + 4u * lp, sb = pb + 2u * lp;
+      dot_superblock<0, 0>(ca, sa, base_lo, sel, sel_sc, tok, acc0, acc1);
+      dot_superblock<48, 128>(ca, sa, base_lo, sel, sel_sc, tok, acc0, acc1);
+      dot_superblock<0, 0>(cb, sb, base_hi, sel, sel_sc, tok, acc0, acc1);
+      dot_superblock<48, 128>(cb, sb, base_hi, sel, sel_sc, tok, acc0, acc1);
+    } else {
+      // a ragged last slice: every row walks the columns in order (two-way conflicts on the
+      // code and scale loads, correctness unchanged)
+      uint32_t b0[4], b1[4];
 #pragma unroll
-    for (int step = 0; step < 2; ++step) {
-      const int row_local = 4 * warp + 2 * step + h;
-      const uint32_t rowp = ring_s + (uint32_t)s * kStageBytes + (uint32_t)row_local * kRowBytes;
-      float acc = 0.f;
-      if (ns == kS) {
-#pragma unroll
-        for (int sb = 0; sb < kS; ++sb) acc = dot_superblock(rowp + sb * 48, baseA + sb * 32768, baseB + sb * 32768, l, sel, acc);
-      } else {
-        for (int sb = 0; sb < ns; ++sb) acc = dot_superblock(rowp + sb * 48, baseA + sb * 32768, baseB + sb * 32768, l, sel, acc);
+      for (int q = 0; q < 4; ++q) {
+        b0[q] = tab_s + (uint32_t)(4 * lp + (q ^ r)) * 4u;
+        b1[q] = b0[q] + kRegion;
       }
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      const int64_t row = row_begin + (int64_t)st * kStageRows + row_local;
-      if (l == 0 && row < row_end) my_ws[row] = acc * 0x1p20f;       // table entries carry 2^100, scales 2^-120
+      const uint32_t c0 = rowp + 4u * lp, s0 = rowp + 2u * lp;
+      if (ns > 0) dot_superblock<0, 0>(c0, s0, b0, sel, sel_sc, tok, acc0, acc1);
+      if (ns > 1) dot_superblock<48, 128>(c0, s0, b0, sel, sel_sc, tok, acc0, acc1);
+      if (ns > 2) dot_superblock<96, 0>(c0, s0, b1, sel, sel_sc, tok, acc0, acc1);
     }
+    float acc = acc0 + acc1;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    const int64_t row = row_begin + (int64_t)st * kStageRows + 4 * warp + r;
+    if (lp == 0 && row < row_end) my_ws[row] = acc;
     __syncwarp();
     if (lane == 0) gb_mbar_arrive(&empty_bar[s]);
   }
