@@ -24,7 +24,7 @@ REQUIRED_SYMBOLS = (
     "gb_moe_route", "gb_moe_gemv_workspace_bytes", "gb_moe_gemv", "gb_moe_combine",
     "gb_fp8_quantize_rows", "gb_gemm_tn",
     "gb_peer_alloc", "gb_peer_free", "gb_peer_export", "gb_peer_open", "gb_peer_close",
-    "gb_peer_allgather", "gb_peer_barrier",
+    "gb_peer_allgather", "gb_peer_barrier", "gb_launch_count",
 )
 PEER_MAX, PEER_HANDLE_BYTES, PEER_FLAG_BYTES = 8, 64, 128
 
@@ -105,6 +105,7 @@ def _declare(lib) -> None:
     lib.gb_moe_combine.argtypes = [vp, vp, vp, i64, i64, i64, i64, vp, vp]
     lib.gb_fp8_quantize_rows.argtypes = [vp, vp, vp, i64, i64, i32, vp]
     lib.gb_gemm_tn.argtypes = [vp, vp, vp, i64, i64, i64, i32, vp, vp, ctypes.c_float, vp]
+    lib.gb_launch_count.restype = i64
     lib.gb_peer_alloc.argtypes = [i64, ctypes.POINTER(vp)]
     lib.gb_peer_free.argtypes = [vp]
     lib.gb_peer_export.argtypes = [vp, vp]
@@ -170,6 +171,11 @@ def prepare(device: int | torch.device | None = None) -> None:
             return
         check(lib.gb_prepare(int(device)), lib)
         _PREPARED.add(device)
+
+
+def launch_count() -> int:
+    """Kernel launches the library has issued so far in this process."""
+    return int(load("launch counter").gb_launch_count())
 
 
 def device_status(device: int = 0) -> int:

@@ -2,6 +2,8 @@
 // set-up, argument validation.
 #include "gb_common.cuh"
 
+#include <atomic>
+
 #include <mutex>
 #include <string.h>
 
@@ -50,6 +52,10 @@ static int prepare_locked(int dev) {
   g_sm_count[dev] = sms;
   return GB_OK;
 }
+
+static std::atomic<long long> g_launches{0};
+void gb_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+extern "C" int64_t gb_launch_count() { return (int64_t)g_launches.load(std::memory_order_relaxed); }
 
 bool gb_pdl_enabled() {
   static const bool on = [] {

@@ -20,6 +20,7 @@ int gb_sm_count();                 // SMs of the current device (cached)
 int* gb_status_word();             // device int the kernels raise on a timed-out wait
 
 bool gb_pdl_enabled();             // false when GRIDBOOK_B200_PDL=0 (plain stream order)
+void gb_count_launch();            // every kernel launch of this library bumps gb_launch_count()
 
 // Kernel launch with the programmatic-stream-serialization attribute (see gb_pdl_wait).
 template <typename... KArgs, typename... Args>
@@ -35,6 +36,7 @@ inline cudaError_t gb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = gb_pdl_enabled() ? 1 : 0;
+  gb_count_launch();
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
@@ -112,14 +114,18 @@ GB_DEVINL uint32_t gb_f32_to_e4m3(float f) {
 // reference's tie rule (gridbook/codec.py:248-260): the upper neighbour wins only when it is
 // STRICTLY closer, so an exact midpoint goes to the lower (more negative) rung.
 GB_DEVINL float gb_e2m1_rtn(float v) {
-  const float grid[15] = {-6.0f, -4.0f, -3.0f, -2.0f, -1.5f, -1.0f, -0.5f, 0.0f,
-                          0.5f,  1.0f,  1.5f,  2.0f,  3.0f,  4.0f,  6.0f};
-  int idx = 15;  // first rung >= v  (bucketize, right = false)
+  constexpr float grid[15] = {-6.0f, -4.0f, -3.0f, -2.0f, -1.5f, -1.0f, -0.5f, 0.0f,
+                              0.5f,  1.0f,  1.5f,  2.0f,  3.0f,  4.0f,  6.0f};
+  // hi = first rung >= v (bucketize, right = false; the top rung when there is none),
+  // lo = the rung before it (the bottom rung when hi is the bottom).  Selects only: a
+  // dynamically indexed table would live in local memory.
+  float hi = grid[14], lo = grid[0];
 #pragma unroll
   for (int i = 14; i >= 0; --i)
-    if (grid[i] >= v) idx = i;
-  const float lo = grid[idx > 0 ? idx - 1 : 0];
-  const float hi = grid[idx < 15 ? idx : 14];
+    if (grid[i] >= v) hi = grid[i];
+#pragma unroll
+  for (int i = 0; i < 15; ++i)
+    if (!(grid[i] >= v)) lo = grid[i];
   return fabsf(__fsub_rn(hi, v)) < fabsf(__fsub_rn(v, lo)) ? hi : lo;
 }
 
@@ -144,6 +150,26 @@ GB_DEVINL void gb_fp4_group16_qdq(uint32_t (&w)[8], int scale_rule) {
     const float q1 = __fmul_rn(gb_e2m1_rtn(__fdiv_rn(v[2 * i + 1], scale)), scale);
     w[i] = gb_f32_to_bf16_bits(q0) | (gb_f32_to_bf16_bits(q1) << 16);
   }
+}
+
+// The same bucket with the group spread over eight consecutive lanes (lane % 8 = word of the
+// group): every lane of the warp must call it.  Bit-identical to gb_fp4_group16_qdq: the
+// maximum ignores NaNs and does not depend on the order, everything else is per value.
+GB_DEVINL uint32_t gb_fp4_group16_qdq_lanes(uint32_t w, int scale_rule) {
+  const float v0 = gb_bf16_bits_to_f32(w & 0xFFFFu), v1 = gb_bf16_bits_to_f32(w >> 16);
+  float amax = fmaxf(fabsf(v0), fabsf(v1));
+  uint32_t nan = (isnan(v0) || isnan(v1)) ? 1u : 0u;
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    nan |= __shfl_xor_sync(0xffffffffu, nan, o);
+  }
+  amax = fmaxf(amax, 1e-8f);
+  float scale = scale_rule == GB_SCALE_RULE_DIV ? __fdiv_rn(amax, 6.0f) : __fmul_rn(amax, 1.0f / 6.0f);
+  if (nan) scale = __int_as_float(0x7FC00000);
+  const float q0 = __fmul_rn(gb_e2m1_rtn(__fdiv_rn(v0, scale)), scale);
+  const float q1 = __fmul_rn(gb_e2m1_rtn(__fdiv_rn(v1, scale)), scale);
+  return gb_f32_to_bf16_bits(q0) | (gb_f32_to_bf16_bits(q1) << 16);
 }
 
 // ---------------------------------------------------------------------------
@@ -291,6 +317,13 @@ GB_DEVINL void gb_bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes,
 
 GB_DEVINL void gb_fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// D[16x8] = A[16x8] . B[8x8] (bf16 in, fp32 out, no accumulator input)
+GB_DEVINL void gb_mma_bf16_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(b0), "f"(0.0f));
 }
 
 GB_DEVINL void gb_mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {

@@ -246,6 +246,7 @@ int launch_expand(const gb_weight* w, int64_t row0, int64_t nrows, void* out0, v
   a.valid_bytes = (nrows - 1) * w->row_stride + (w->K / 256) * w->fmt.type_size;
   const int64_t units = nrows * (w->K / 256);
   const unsigned blocks = (unsigned)((units + kThreads / 32 - 1) / (kThreads / 32));
+  gb_count_launch();
   expand_kernel<kOut><<<blocks, kThreads, 0, (cudaStream_t)stream>>>(a, out0, (uint8_t*)out_sf,
                                                                     sf_swizzled);
   GB_LAUNCH_OK("expand_kernel");

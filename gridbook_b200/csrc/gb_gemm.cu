@@ -299,6 +299,7 @@ int gb_fp8_quantize_rows(const void* x, void* q, float* scale, int64_t M, int64_
   GB_REQUIRE(x && q && scale, "null pointer argument");
   GB_REQUIRE(M >= 0 && K > 0, "bad shape M=%lld K=%lld", (long long)M, (long long)K);
   if (M == 0) return GB_OK;
+  gb_count_launch();
   fp8_quantize_rows_kernel<<<(unsigned)M, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)x, (uint8_t*)q, scale, K,
                                                                         scale_rule);
   GB_LAUNCH_OK("fp8_quantize_rows_kernel");
@@ -333,6 +334,7 @@ int gb_gemm_tn(const void* A, const void* B, void* D, int64_t M, int64_t N, int6
   p.D = (uint16_t*)D;
   p.status = gb_status_word();
   dim3 grid((unsigned)((M + kBM - 1) / kBM), (unsigned)((N + kBN - 1) / kBN));
+  gb_count_launch();
   gemm_tn_kernel<<<grid, kGemmThreads, kGemmSmem, (cudaStream_t)stream>>>(map_a, map_b, p);
   GB_LAUNCH_OK("gemm_tn_kernel");
   return GB_OK;

@@ -26,6 +26,21 @@
 
 #include <cuda.h>
 
+#ifdef GB_EXP_TIMELINE
+__device__ unsigned long long g_tl[4096][8];
+__device__ unsigned int g_tl_n = 0;
+#define TL_DECL unsigned int tl_slot = 0; const bool tl_on = (blockIdx.x == 0 && threadIdx.x == 0); if (tl_on) tl_slot = atomicAdd(&g_tl_n, 1u) & 4095u;
+#define TL(i) do { if (tl_on) g_tl[tl_slot][i] = gb_globaltimer_ns(); } while (0)
+extern "C" __attribute__((visibility("default"))) int gb_debug_timeline(unsigned long long* out, unsigned int* n) {
+  cudaMemcpyFromSymbol(out, g_tl, sizeof(g_tl));
+  cudaMemcpyFromSymbol(n, g_tl_n, sizeof(unsigned int));
+  return 0;
+}
+#else
+#define TL_DECL
+#define TL(i)
+#endif
+
 namespace {
 
 constexpr int kS = 4;                         // superblock columns per CTA
@@ -123,12 +138,18 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
   };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  TL_DECL
+  TL(0);
   const int slice = blockIdx.x % p.n_slices, group = blockIdx.x / p.n_slices;
   const int sb0 = slice * kS;
   const int ns = min(kS, p.n_sb - sb0);
   const int64_t row_begin = (int64_t)group * p.rows_per_group;
   const int64_t row_end = min(p.N, row_begin + p.rows_per_group);
+#ifdef GB_EXP_NO_STREAM
+  const int n_stages = 0;
+#else
   const int n_stages = row_end > row_begin ? (int)((row_end - row_begin + kStageRows - 1) / kStageRows) : 0;
+#endif
 
   if (tid == 0) {
     for (int s = 0; s < kDotStages; ++s) {
@@ -164,7 +185,7 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
 
   // ---- inner-product tables ----
   // One unit = one superblock column x eight codes x all 32 positions: two MMAs with the
-  // activation segments as the 16 rows (A[m][k] = x[8 (16 h + m) + k], k < 8) and the eight
+  // activation segments as the 16 rows (A[m][k] = x[8 (16 h + m) + k]) and the eight
   // codewords as the columns (B[k][n] = codebook[c0 + n][k]).  Warp w owns code blocks 2w and
   // 2w + 1 for every column, so its two B fragments are loaded once, before the wait.
   const int g = lane >> 2, t = lane & 3;
@@ -177,35 +198,36 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
 
   // ---- this slice of the activation row, through its bucket, into shared memory ----
   gb_pdl_wait();                       // the activations (and the partial-sum slots) belong to earlier kernels
-  if (tid < ns * 16) {
-    const uint4* src = reinterpret_cast<const uint4*>(p.x + (int64_t)sb0 * 256 + tid * 16);
-    const uint4 r0 = src[0], r1 = src[1];
-    uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-    if (p.act == GB_ACT_FP4_GROUP16) gb_fp4_group16_qdq(w, p.scale_rule);
-    uint4* dst = reinterpret_cast<uint4*>(xq + tid * 16);
-    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  TL(1);
+  if (tid < ns * 128) {                // two values per thread, a bucket group per eight lanes
+    uint32_t w = reinterpret_cast<const uint32_t*>(p.x + (int64_t)sb0 * 256)[tid];
+    if (p.act == GB_ACT_FP4_GROUP16) w = gb_fp4_group16_qdq_lanes(w, p.scale_rule);
+    reinterpret_cast<uint32_t*>(xq)[tid] = w;
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
 
   {
     const uint32_t* xq32 = reinterpret_cast<const uint32_t*>(xq);
-    for (int s = 0; s < ns; ++s) {
-      uint32_t a[2][4];
+#ifdef GB_EXP_NO_TABLE
+    for (int s = 0; s < 0; ++s) {
+#else
+#pragma unroll
+    for (int s = 0; s < kS; ++s) {
+      if (s >= ns) break;
+#endif
+      uint32_t a[2][2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         a[h][0] = xq32[s * 128 + (16 * h + g) * 4 + t];
         a[h][1] = xq32[s * 128 + (16 * h + g + 8) * 4 + t];
-        a[h][2] = 0u;
-        a[h][3] = 0u;
       }
       // T(s, code, pos) lives at region (s >> 1), row `code`, float (s & 1) * 32 + pos
       float* col = reinterpret_cast<float*>(table_b + (size_t)(s >> 1) * kRegion) + (s & 1) * 32 + g;
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
-        gb_mma_bf16_16816(d0, a[0], bfrag[j], 0u);      // positions g, g + 8
-        gb_mma_bf16_16816(d1, a[1], bfrag[j], 0u);      // positions 16 + g, 24 + g
+        float d0[4], d1[4];
+        gb_mma_bf16_1688(d0, a[0][0], a[0][1], bfrag[j]);      // positions g, g + 8
+        gb_mma_bf16_1688(d1, a[1][0], a[1][1], bfrag[j]);      // positions 16 + g, 24 + g
         // v[cc][pb]: code 2t + cc of the block, position 8 pb + g
         float v[2][4] = {{d0[0], d0[2], d1[0], d1[2]}, {d0[1], d0[3], d1[1], d1[3]}};
         // Store number q of a lane takes position block (t + q) & 3, so the four lanes that share
@@ -223,6 +245,7 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
 
+  TL(2);
   // ---- stream the rows ----
   const int r = lane >> 3, lp = lane & 7, rh = r >> 1;
   uint32_t base_lo[4], base_hi[4], sel[4];
@@ -272,17 +295,22 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
     __syncwarp();
     if (lane == 0) gb_mbar_arrive(&empty_bar[s]);
   }
+  TL(3);
 }
 
 __global__ void dot_finalize_kernel(const float* __restrict__ ws, int n_slices, int64_t N, float global_scale,
                                     uint16_t* __restrict__ y) {
+  TL_DECL
+  TL(4);
   gb_pdl_launch_dependents();
   gb_pdl_wait();
+  TL(5);
   const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= N) return;
   float acc = 0.f;
   for (int s = 0; s < n_slices; ++s) acc += ws[(int64_t)s * N + n];
   y[n] = (uint16_t)gb_f32_to_bf16_bits(acc * global_scale);
+  TL(6);
 }
 
 }  // namespace
@@ -331,7 +359,11 @@ int gb_gemv_dot(const void* x, const gb_weight* w, int act, int scale_rule, void
   if (rc != GB_OK) return rc;
   GB_CUDA_OK(gb_launch(gemv_dot_kernel, dim3(p.n_slices * p.n_groups), dim3(kDotThreads), kDotSmem, stream, map, p));
   const float gs = w->global_scale == 0.0f ? 1.0f : w->global_scale;
+#ifndef GB_EXP_NO_FINALIZE
   GB_CUDA_OK(gb_launch(dot_finalize_kernel, dim3((unsigned)((w->rows + 255) / 256)), dim3(256), 0, stream,
                        (const float*)p.ws, p.n_slices, (int64_t)w->rows, gs, (uint16_t*)y));
+#else
+  (void)gs;
+#endif
   return GB_OK;
 }

@@ -191,6 +191,11 @@ GB_API int gb_moe_gemv(const void* x_bf16, const int32_t* x_row, const gb_weight
 GB_API int gb_moe_combine(const void* y_bf16, const float* pair_w, const int32_t* topk_ids,
                    int64_t E, int64_t T, int64_t topk, int64_t H, void* out_bf16, void* stream);
 
+/* Kernel launches this library has issued in this process so far (launches recorded into a
+ * CUDA graph count once, at capture).  No reference counterpart; used by the benchmark to
+ * report how many of its own kernels a step runs. */
+GB_API int64_t gb_launch_count(void);
+
 /* ---- peer-memory exchange on one NVSwitch node ------------------------------- */
 /* None of this has a counterpart in the reference, which runs on one GPU
  * (gridbook/config.py:565-576).  One process per GPU; a buffer from gb_peer_alloc is exported

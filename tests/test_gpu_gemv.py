@@ -185,16 +185,17 @@ def test_moe_literal_and_fp8_and_mixed(dev):
         assert rel <= 1e-2, (f13, f2, rel)
 
 
-@pytest.mark.parametrize("N,K", [(512, 1024), (1000, 2304), (2048, 5120), (5120, 4352)])
+@pytest.mark.parametrize("N,K", [(512, 1024), (1000, 2304), (640, 1536), (768, 2816), (2048, 5120), (5120, 4352)])
 def test_literal_single_row_table_kernel(dev, N, K):
     """M = 1 on the literal format with enough rows takes the inner-product-table kernel: ragged
-    row count, a last K slice shorter than four superblocks, padded row stride, bucket fused or
-    applied beforehand, including subnormal and zero scale bytes."""
+    row count, a last K slice of one, two or three superblocks, padded row stride, bucket fused
+    or applied beforehand, including zero, subnormal and negative scale bytes."""
     from gridbook_b200 import kernels, synth
     fmt = _fmt("lit")
     d = synth.make_linear(fmt, N, K, seed=N + K, global_scale=1.0 / 448.0)
     qw = d["qw"].reshape(N, K // 256, 48)
     qw[::7, 0, 32:40] = np.arange(8, dtype=np.uint8)          # E4M3 zero and subnormal scales
+    qw[::5, -1, 40:44] = np.array([0x88, 0xB8, 0xFE, 0x81], dtype=np.uint8)   # negative scales, -448 included
     d["qw"] = qw.reshape(N, -1)
     x = synth.make_activations(1, K, seed=3)
     ref = oracle_linear(x, d, bucket=True, scale_rule="recip")
