@@ -563,10 +563,8 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
 
     // A wait that runs out raises the status word and carries on (the output is then
     // garbage, and flagged): leaving here would strand the other warps at a CTA barrier.
-#ifndef GB_EXP_NO_TMA
     uint32_t tok;
     if (!gb_mbar_wait(&my_bar[s], (it / p.stages) & 1, &tok)) atomicExch(p.status, 2);
-#endif
     uint32_t sbp = ring_s + (uint32_t)s * (uint32_t)p.stage_bytes + (uint32_t)g * (uint32_t)p.row_pitch +
                    (row_ok ? (uint32_t)((uintptr_t)my_src & 15u) : 0u);
     const uint32_t warp_head = __shfl_sync(0xffffffffu, (uint32_t)((uintptr_t)my_src & 15u), 0);
@@ -609,20 +607,11 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
           const uint32_t scw[4] = {sw.x, sw.y, sw.z, sw.w};
 #pragma unroll
           for (int kb = 0; kb < 8; ++kb) {
-#ifdef GB_EXP_NO_LUT
-            const uint32_t cc = __byte_perm(iw[kb], 0u, sel_idx);
-            const uint4 v = make_uint4(0x3F803F80u + cc, 0x3F803F80u, 0x3F803F80u ^ cc, 0x3F803F80u);
-#else
             const uint4 v = ldt_v4(lut_lane + (__byte_perm(iw[kb], 0u, sel_idx) << 7), tok);
-#endif
             w[kb][0] = v.x; w[kb][1] = v.y; w[kb][2] = v.z; w[kb][3] = v.w;
           }
 #pragma unroll
-#ifdef GB_EXP_NO_X
-          for (int kb = 0; kb < 8; ++kb) xa[kb] = make_uint4(xa_s + kb, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
-#else
           for (int kb = 0; kb < 8; ++kb) xa[kb] = ldt_v4(xa_s + kb * 64, tok);
-#endif
 #pragma unroll
           for (int kb = 0; kb < 8; ++kb) {
             const uint32_t b2 = __byte_perm(scw[kb >> 1], 0u, (kb & 1) ? sel_sc_odd : sel_sc_even);
@@ -681,10 +670,6 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
           if (hi_any) xb = ldt_v4(xb_s + kb * 64, tok);
           const uint32_t a0[4] = {xa[kb].x, xb.x, xa[kb].y, xb.y};
           const uint32_t a1[4] = {xa[kb].z, xb.z, xa[kb].w, xb.w};
-#ifdef GB_EXP_NO_MMA
-          acc0[0] += __uint_as_float((a0[0] ^ a0[2] ^ w[kb][0] ^ w[kb][1]) & 0x3FFFFFFFu);
-          acc1[0] += __uint_as_float((a1[0] ^ a1[2] ^ w[kb][2] ^ w[kb][3]) & 0x3FFFFFFFu);
-#else
           if ((kb & 3) == 0) {
             gb_mma_bf16_16816(acc0, a0, w[kb][0], w[kb][1]);
             gb_mma_bf16_16816(acc1, a1, w[kb][2], w[kb][3]);
@@ -692,7 +677,6 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
             gb_mma_bf16_16816(accx[2 * (kb & 3) - 2], a0, w[kb][0], w[kb][1]);
             gb_mma_bf16_16816(accx[2 * (kb & 3) - 1], a1, w[kb][2], w[kb][3]);
           }
-#endif
         }
       }
     } else {
@@ -702,9 +686,7 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
     // ---- the stage is free: refill it with the task kMaxStages ahead ----
     __syncwarp();
     more = more && ahead.next(ta);
-#ifndef GB_EXP_NO_TMA
     if (more) issue_task(p, ta, warp, lane, my_ring + (size_t)s * p.stage_bytes, &my_bar[s]);
-#endif
 
     if (t.chunk + 1 < t.nchunks) continue;          // more K chunks of this tile to come
 

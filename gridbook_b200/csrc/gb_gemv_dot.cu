@@ -26,31 +26,19 @@
 
 #include <cuda.h>
 
-#ifdef GB_EXP_TIMELINE
-__device__ unsigned long long g_tl[4096][8];
-__device__ unsigned int g_tl_n = 0;
-#define TL_DECL unsigned int tl_slot = 0; const bool tl_on = (blockIdx.x == 0 && threadIdx.x == 0); if (tl_on) tl_slot = atomicAdd(&g_tl_n, 1u) & 4095u;
-#define TL(i) do { if (tl_on) g_tl[tl_slot][i] = gb_globaltimer_ns(); } while (0)
-extern "C" __attribute__((visibility("default"))) int gb_debug_timeline(unsigned long long* out, unsigned int* n) {
-  cudaMemcpyFromSymbol(out, g_tl, sizeof(g_tl));
-  cudaMemcpyFromSymbol(n, g_tl_n, sizeof(unsigned int));
-  return 0;
-}
-#else
-#define TL_DECL
-#define TL(i)
-#endif
 
 namespace {
 
 constexpr int kS = 4;                         // superblock columns per CTA
-constexpr int kConsumers = 16;                // warps
+constexpr int kConsumers = 16;                // warps (24 also fits the layout; measured no faster)
+constexpr int kBlocksPerWarp = 2;             // eight-code blocks of the table a warp builds per column: w, w + kConsumers
 constexpr int kDotThreads = (kConsumers + 1) * 32;
 constexpr int kStageRows = 4 * kConsumers;    // 64 rows per stage, four per warp
 constexpr int kRowBytes = kS * 48;            // 192 bytes of each row per stage
 constexpr int kStageBytes = kStageRows * kRowBytes;
-constexpr int kDotStages = 6;
-constexpr int kFrontStages = 5;               // ring stages in front of the tables, the rest behind
+constexpr int kDotStages = 6 * 16 / kConsumers;
+static_assert(kConsumers == 16 || kConsumers == 24, "stage geometry is laid out for 16 or 24 consumer warps");
+constexpr int kFrontStages = kDotStages - 1;  // ring stages in front of the tables, the rest behind
 constexpr uint32_t kRegion = 0x10000u;        // 64 KiB: 256 codes x 256-byte rows
 constexpr int kTableBytes = 2 * (int)kRegion;
 constexpr int kBackBytes = (kDotStages - kFrontStages) * kStageBytes + kS * 512 + 256;
@@ -138,18 +126,12 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
   };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  TL_DECL
-  TL(0);
   const int slice = blockIdx.x % p.n_slices, group = blockIdx.x / p.n_slices;
   const int sb0 = slice * kS;
   const int ns = min(kS, p.n_sb - sb0);
   const int64_t row_begin = (int64_t)group * p.rows_per_group;
   const int64_t row_end = min(p.N, row_begin + p.rows_per_group);
-#ifdef GB_EXP_NO_STREAM
-  const int n_stages = 0;
-#else
   const int n_stages = row_end > row_begin ? (int)((row_end - row_begin + kStageRows - 1) / kStageRows) : 0;
-#endif
 
   if (tid == 0) {
     for (int s = 0; s < kDotStages; ++s) {
@@ -186,19 +168,20 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
   // ---- inner-product tables ----
   // One unit = one superblock column x eight codes x all 32 positions: two MMAs with the
   // activation segments as the 16 rows (A[m][k] = x[8 (16 h + m) + k]) and the eight
-  // codewords as the columns (B[k][n] = codebook[c0 + n][k]).  Warp w owns code blocks 2w and
-  // 2w + 1 for every column, so its two B fragments are loaded once, before the wait.
+  // codewords as the columns (B[k][n] = codebook[c0 + n][k]).  Warp w owns code blocks w and
+  // w + kConsumers (where that exists) for every column, so its B fragments are loaded once,
+  // before the wait.
   const int g = lane >> 2, t = lane & 3;
-  uint32_t bfrag[2];
+  uint32_t bfrag[kBlocksPerWarp];
   {
     const uint32_t* cb32 = reinterpret_cast<const uint32_t*>(p.codebook);
 #pragma unroll
-    for (int j = 0; j < 2; ++j) bfrag[j] = __ldg(cb32 + ((2 * warp + j) * 8 + g) * 4 + t);
+    for (int j = 0; j < kBlocksPerWarp; ++j)
+      bfrag[j] = warp + j * kConsumers < 32 ? __ldg(cb32 + ((warp + j * kConsumers) * 8 + g) * 4 + t) : 0u;
   }
 
   // ---- this slice of the activation row, through its bucket, into shared memory ----
   gb_pdl_wait();                       // the activations (and the partial-sum slots) belong to earlier kernels
-  TL(1);
   if (tid < ns * 128) {                // two values per thread, a bucket group per eight lanes
     uint32_t w = reinterpret_cast<const uint32_t*>(p.x + (int64_t)sb0 * 256)[tid];
     if (p.act == GB_ACT_FP4_GROUP16) w = gb_fp4_group16_qdq_lanes(w, p.scale_rule);
@@ -208,13 +191,9 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
 
   {
     const uint32_t* xq32 = reinterpret_cast<const uint32_t*>(xq);
-#ifdef GB_EXP_NO_TABLE
-    for (int s = 0; s < 0; ++s) {
-#else
 #pragma unroll
     for (int s = 0; s < kS; ++s) {
       if (s >= ns) break;
-#endif
       uint32_t a[2][2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -224,7 +203,8 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
       // T(s, code, pos) lives at region (s >> 1), row `code`, float (s & 1) * 32 + pos
       float* col = reinterpret_cast<float*>(table_b + (size_t)(s >> 1) * kRegion) + (s & 1) * 32 + g;
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
+      for (int j = 0; j < kBlocksPerWarp; ++j) {
+        if (warp + j * kConsumers >= 32) break;            // same verdict in the whole warp
         float d0[4], d1[4];
         gb_mma_bf16_1688(d0, a[0][0], a[0][1], bfrag[j]);      // positions g, g + 8
         gb_mma_bf16_1688(d1, a[1][0], a[1][1], bfrag[j]);      // positions 16 + g, 24 + g
@@ -236,7 +216,7 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
         for (int cc = 0; cc < 2; ++cc) {
           if (t & 1) { const float x0 = v[cc][0]; v[cc][0] = v[cc][1]; v[cc][1] = v[cc][2]; v[cc][2] = v[cc][3]; v[cc][3] = x0; }
           if (t & 2) { const float x0 = v[cc][0], x1 = v[cc][1]; v[cc][0] = v[cc][2]; v[cc][1] = v[cc][3]; v[cc][2] = x0; v[cc][3] = x1; }
-          float* row = col + ((2 * warp + j) * 8 + 2 * t + cc) * 64;
+          float* row = col + ((warp + j * kConsumers) * 8 + 2 * t + cc) * 64;
 #pragma unroll
           for (int q = 0; q < 4; ++q) row[((t + q) & 3) * 8] = v[cc][q];
         }
@@ -244,8 +224,6 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
     }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
-
-  TL(2);
   // ---- stream the rows ----
   const int r = lane >> 3, lp = lane & 7, rh = r >> 1;
   uint32_t base_lo[4], base_hi[4], sel[4];
@@ -295,22 +273,17 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
     __syncwarp();
     if (lane == 0) gb_mbar_arrive(&empty_bar[s]);
   }
-  TL(3);
 }
 
 __global__ void dot_finalize_kernel(const float* __restrict__ ws, int n_slices, int64_t N, float global_scale,
                                     uint16_t* __restrict__ y) {
-  TL_DECL
-  TL(4);
   gb_pdl_launch_dependents();
   gb_pdl_wait();
-  TL(5);
   const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= N) return;
   float acc = 0.f;
   for (int s = 0; s < n_slices; ++s) acc += ws[(int64_t)s * N + n];
   y[n] = (uint16_t)gb_f32_to_bf16_bits(acc * global_scale);
-  TL(6);
 }
 
 }  // namespace
@@ -359,11 +332,7 @@ int gb_gemv_dot(const void* x, const gb_weight* w, int act, int scale_rule, void
   if (rc != GB_OK) return rc;
   GB_CUDA_OK(gb_launch(gemv_dot_kernel, dim3(p.n_slices * p.n_groups), dim3(kDotThreads), kDotSmem, stream, map, p));
   const float gs = w->global_scale == 0.0f ? 1.0f : w->global_scale;
-#ifndef GB_EXP_NO_FINALIZE
   GB_CUDA_OK(gb_launch(dot_finalize_kernel, dim3((unsigned)((w->rows + 255) / 256)), dim3(256), 0, stream,
                        (const float*)p.ws, p.n_slices, (int64_t)w->rows, gs, (uint16_t*)y));
-#else
-  (void)gs;
-#endif
   return GB_OK;
 }
