@@ -9,6 +9,8 @@
 //   [8..15]  done[r]:  rank r's stores of exchange number `epoch` are visible
 //   [16]     epoch of the last finished exchange (own use)
 //   [17]     CTA arrival counter of the running exchange (own use)
+//   [18]     number of the last finished flag-in-data exchange (own use)
+//   [19]     CTA arrival counter of the running flag-in-data exchange (own use)
 // Epochs only grow, and a waiter accepts any value at or past the one it waits for, so a
 // fast peer that is already one exchange ahead never strands a slow one.  Every wait is
 // bounded (two seconds); one that runs out raises the status word (value 3) and carries on.
@@ -57,7 +59,7 @@ GB_DEVINL bool wait_epoch(const uint32_t* slot, uint32_t epoch) {
 //   1. tell every peer this rank has arrived; wait until every peer has (their buffers are free)
 //   2. copy this rank's pieces into every rank's buffer (plain peer stores)
 //   3. the last CTA to finish tells every peer the stores are visible and waits for theirs
-// With n_seg == 0 this is a plain two-phase barrier.
+// With n_seg == 0 only step 3 runs: "everything I stored before this launch is visible".
 __global__ void __launch_bounds__(256) peer_exchange_kernel(const __grid_constant__ PeerParams p) {
   __shared__ uint32_t s_epoch;
   __shared__ int s_last;
@@ -68,11 +70,13 @@ __global__ void __launch_bounds__(256) peer_exchange_kernel(const __grid_constan
   if (tid == 0) s_epoch = *reinterpret_cast<volatile uint32_t*>(mine + 16) + 1u;
   __syncthreads();
   const uint32_t epoch = s_epoch;
-  if (tid < p.world) {
-    if (blockIdx.x == 0) st_release_sys(p.flags[tid] + p.rank, epoch);
-    if (!wait_epoch(mine + tid, epoch)) atomicExch(p.status, 3);
+  if (p.n_seg > 0) {                   // a plain barrier has no buffer to wait for
+    if (tid < p.world) {
+      if (blockIdx.x == 0) st_release_sys(p.flags[tid] + p.rank, epoch);
+      if (!wait_epoch(mine + tid, epoch)) atomicExch(p.status, 3);
+    }
+    __syncthreads();
   }
-  __syncthreads();
 
   for (int s = 0; s < p.n_seg; ++s) {
     const PeerSeg& g = p.seg[s];
@@ -119,6 +123,91 @@ __global__ void __launch_bounds__(256) peer_exchange_kernel(const __grid_constan
   if (tid == 0) {
     mine[17] = 0u;
     mine[16] = epoch;
+  }
+}
+
+// ---- flag-in-data all-gather ------------------------------------------------------------
+// For small pieces the two flag round trips above cost more than the data.  Here every 4-byte
+// word travels as an 8-byte store {word, exchange number} into a staging slot of the receiver,
+// who spins on the number and unpacks into its own buffer: one one-way trip, no fence, no
+// separate flag.  Slots alternate between two halves by the parity of the exchange number; a
+// sender can only reach exchange e + 2 after it has received everybody's e + 1, which they sent
+// after finishing e, so the half it overwrites has been read.
+struct LLSeg {
+  const uint8_t* src;
+  uint8_t* dst_local[GB_PEER_MAX];   // where rank s's piece lands in this rank's buffer
+  int64_t rows, row_words, src_pitch, dst_pitch, first_word;
+};
+struct LLParams {
+  uint32_t* flags;                   // own flag block
+  uint2* ll[GB_PEER_MAX];            // staging buffers, [parity][source rank][capacity]
+  int64_t capacity, total_words;
+  int rank, world, n_seg;
+  LLSeg seg[kMaxSeg];
+  int* status;
+};
+
+GB_DEVINL void st_ll(uint2* p, uint32_t word, uint32_t epoch) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(word), "r"(epoch) : "memory");
+}
+GB_DEVINL uint2 ld_ll(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(256) peer_ll_kernel(const __grid_constant__ LLParams p) {
+  __shared__ uint32_t s_epoch;
+  const int tid = threadIdx.x;
+  gb_pdl_launch_dependents();
+  gb_pdl_wait();
+  if (tid == 0) s_epoch = *reinterpret_cast<volatile uint32_t*>(p.flags + 18) + 1u;
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const int64_t half = (int64_t)(epoch & 1u) * p.world * p.capacity;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  // send: my words to every peer's staging slot, my own piece straight to its place
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + tid; i < p.total_words; i += stride) {
+    int s = 0;
+    while (s + 1 < p.n_seg && i >= p.seg[s + 1].first_word) ++s;
+    const LLSeg& g = p.seg[s];
+    const int64_t j = i - g.first_word, r = j / g.row_words, c = j - r * g.row_words;
+    const uint32_t word = *reinterpret_cast<const uint32_t*>(g.src + r * g.src_pitch + c * 4);
+    *reinterpret_cast<uint32_t*>(g.dst_local[p.rank] + r * g.dst_pitch + c * 4) = word;
+    for (int d = 0; d < p.world; ++d)
+      if (d != p.rank) st_ll(p.ll[d] + half + (int64_t)p.rank * p.capacity + i, word, epoch);
+  }
+  // receive: everybody else's words out of my staging slots
+  bool late = false;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + tid; i < p.total_words; i += stride) {
+    int s = 0;
+    while (s + 1 < p.n_seg && i >= p.seg[s + 1].first_word) ++s;
+    const LLSeg& g = p.seg[s];
+    const int64_t j = i - g.first_word, r = j / g.row_words, c = j - r * g.row_words;
+    for (int src = 0; src < p.world; ++src) {
+      if (src == p.rank) continue;
+      const uint2* slot = p.ll[p.rank] + half + (int64_t)src * p.capacity + i;
+      uint2 v = ld_ll(slot);
+      uint64_t t0 = 0;
+      for (uint32_t spin = 0; v.y != epoch && !late; ++spin) {
+        v = ld_ll(slot);
+        if ((spin & 63u) == 63u) {
+          const uint64_t now = gb_globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > 2000000000ull) late = true;
+        }
+      }
+      *reinterpret_cast<uint32_t*>(g.dst_local[src] + r * g.dst_pitch + c * 4) = v.x;
+    }
+  }
+  if (late) atomicExch(p.status, 3);
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned old = atomicAdd(p.flags + 19, 1u);
+    if (old == gridDim.x - 1) {       // every CTA has read the exchange number by now
+      p.flags[19] = 0u;
+      p.flags[18] = epoch;
+    }
   }
 }
 
@@ -209,6 +298,52 @@ int gb_peer_allgather(const gb_peer_group* g, const gb_peer_piece* pieces, int n
   if (grid < 1) grid = 1;
   if (grid > 32) grid = 32;          // all CTAs resident at once; 32 saturate the links at these sizes
   GB_CUDA_OK(gb_launch(peer_exchange_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, p));
+  return GB_OK;
+}
+
+int gb_peer_allgather_ll(const gb_peer_group* g, void* const* ll, int64_t ll_bytes, const gb_peer_ll_piece* pieces,
+                         int n_pieces, void* stream) {
+  int rc = check_group(g);
+  if (rc != GB_OK) return rc;
+  GB_REQUIRE(ll != nullptr && pieces != nullptr && n_pieces >= 1 && n_pieces <= kMaxSeg,
+             "flag-in-data all-gather takes 1..%d pieces, got %d", kMaxSeg, n_pieces);
+  LLParams p = {};
+  p.rank = g->rank;
+  p.world = g->world;
+  p.n_seg = n_pieces;
+  p.flags = (uint32_t*)g->flags[g->rank];
+  p.status = gb_status_word();
+  p.capacity = ll_bytes / (2 * (int64_t)g->world * 8);
+  for (int r = 0; r < g->world; ++r) {
+    GB_REQUIRE(ll[r] != nullptr && ((uintptr_t)ll[r] & 7) == 0, "staging buffer of rank %d is null or misaligned", r);
+    p.ll[r] = (uint2*)ll[r];
+  }
+  int64_t words = 0;
+  for (int s = 0; s < n_pieces; ++s) {
+    const gb_peer_ll_piece& q = pieces[s];
+    GB_REQUIRE(q.src && q.rows >= 0 && q.row_bytes >= 0, "piece %d: bad source", s);
+    GB_REQUIRE(((q.row_bytes | q.src_pitch | q.dst_pitch | (int64_t)(uintptr_t)q.src) & 3) == 0,
+               "piece %d: rows, pitches and pointers must be multiples of four bytes", s);
+    p.seg[s].src = (const uint8_t*)q.src;
+    p.seg[s].rows = q.rows;
+    p.seg[s].row_words = q.row_bytes / 4;
+    p.seg[s].src_pitch = q.src_pitch;
+    p.seg[s].dst_pitch = q.dst_pitch;
+    p.seg[s].first_word = words;
+    for (int r = 0; r < g->world; ++r) {
+      GB_REQUIRE(q.dst_local[r] != nullptr && ((uintptr_t)q.dst_local[r] & 3) == 0,
+                 "piece %d: bad local destination for rank %d", s, r);
+      p.seg[s].dst_local[r] = (uint8_t*)q.dst_local[r];
+    }
+    words += q.rows * (q.row_bytes / 4);
+  }
+  GB_REQUIRE(words <= p.capacity, "%lld words per rank exceed the staging capacity of %lld; use gb_peer_allgather",
+             (long long)words, (long long)p.capacity);
+  p.total_words = words;
+  int grid = (int)((words + 255) / 256);
+  if (grid < 1) grid = 1;
+  if (grid > 64) grid = 64;
+  GB_CUDA_OK(gb_launch(peer_ll_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, p));
   return GB_OK;
 }
 

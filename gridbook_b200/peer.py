@@ -86,32 +86,53 @@ class PeerArena:
 
 
 class PeerGroup:
-    """Arena + flag block: what one exchange launch needs."""
+    """Arena + flag block + staging buffer: what the exchange launches need."""
 
-    def __init__(self, arena_bytes: int, device: torch.device, group=None):
-        self.arena = PeerArena(arena_bytes + 4096, device, group)
+    def __init__(self, arena_bytes: int, device: torch.device, group=None, ll_words: int = 1 << 19):
+        world = dist.get_world_size(group)
+        self.ll_bytes = 2 * world * ll_words * 8          # two halves x one slot per source rank
+        self.ll_words = ll_words
+        self.arena = PeerArena(arena_bytes + self.ll_bytes + 8192, device, group)
         self.rank, self.world, self.device = self.arena.rank, self.arena.world, device
         flag_off = self.arena.carve(nat.PEER_FLAG_BYTES)
+        self.ll_off = self.arena.carve(self.ll_bytes)
         self.native = nat.GbPeerGroup()
         self.native.rank, self.native.world = self.rank, self.world
+        self._ll = (ctypes.c_void_p * 8)()
         for r in range(self.world):
             self.native.flags[r] = self.arena.ptr(r, flag_off)
+            self._ll[r] = self.arena.ptr(r, self.ll_off)
         dist.barrier(group)          # every rank has mapped every block before the first launch
 
     def allgather(self, pieces) -> None:
-        """``pieces``: (src_ptr, rows, row_bytes, src_pitch, dst_offset, dst_pitch); the piece lands
-        at arena offset ``dst_offset`` on every rank."""
-        arr = (nat.GbPeerPiece * max(len(pieces), 1))()
-        for i, (src, rows, row_bytes, src_pitch, dst_off, dst_pitch) in enumerate(pieces):
+        """``pieces``: (src_ptr, rows, row_bytes, src_pitch, dst_offsets, dst_pitch) with
+        ``dst_offsets[s]`` the arena offset at which rank s's piece lands (the same on every
+        rank).  Small exchanges go flag-in-data (one one-way trip), large ones as plain peer
+        stores between two flag exchanges."""
+        lib = self.arena.lib
+        words = sum(rows * row_bytes // 4 for _, rows, row_bytes, _, _, _ in pieces)
+        if words <= self.ll_words:
+            arr = (nat.GbPeerLLPiece * len(pieces))()
+            for i, (src, rows, row_bytes, src_pitch, dst_offs, dst_pitch) in enumerate(pieces):
+                q = arr[i]
+                q.src, q.rows, q.row_bytes, q.src_pitch, q.dst_pitch = src, rows, row_bytes, src_pitch, dst_pitch
+                for s in range(self.world):
+                    q.dst_local[s] = self.arena.ptr(self.rank, dst_offs[s])
+            nat.check(lib.gb_peer_allgather_ll(ctypes.byref(self.native), self._ll, self.ll_bytes, arr,
+                                               len(pieces), nat.stream_ptr(self.device)), lib)
+            return
+        arr = (nat.GbPeerPiece * len(pieces))()
+        for i, (src, rows, row_bytes, src_pitch, dst_offs, dst_pitch) in enumerate(pieces):
             q = arr[i]
             q.src, q.rows, q.row_bytes, q.src_pitch, q.dst_pitch = src, rows, row_bytes, src_pitch, dst_pitch
             for r in range(self.world):
-                q.dst[r] = self.arena.ptr(r, dst_off)
-        lib = self.arena.lib
+                q.dst[r] = self.arena.ptr(r, dst_offs[self.rank])
         nat.check(lib.gb_peer_allgather(ctypes.byref(self.native), arr, len(pieces),
                                         nat.stream_ptr(self.device)), lib)
 
     def barrier(self) -> None:
+        """Returns (on the stream) once every rank's stores enqueued before its own call are
+        visible here."""
         lib = self.arena.lib
         nat.check(lib.gb_peer_barrier(ctypes.byref(self.native), nat.stream_ptr(self.device)), lib)
 
@@ -133,11 +154,11 @@ class PeerShardedCBLinear(torch.nn.Module):
         self.n_local = self.N // world
         self.max_rows = max_rows
         self.out_off = peers.arena.carve(max_rows * self.N * 2)
-        # (local column, global column, width) of every role's slice
+        # (local column, global column of rank 0's slice, width) of every role
         self.roles, lcol, gcol = [], 0, 0
         for n in self.partition_sizes:
             per = n // world
-            self.roles.append((lcol, gcol + rank * per, per))
+            self.roles.append((lcol, gcol, per))
             lcol += per
             gcol += n
         if len(self.roles) > 4:
@@ -151,7 +172,9 @@ class PeerShardedCBLinear(torch.nn.Module):
         if M > self.max_rows:
             raise ValueError(f"{M} rows exceed the {self.max_rows} this layer reserved peer memory for")
         base = y2.data_ptr()
-        pieces = [(base + lc * 2, M, w * 2, self.n_local * 2, self.out_off + gc * 2, self.N * 2)
+        world = self.peers.world
+        pieces = [(base + lc * 2, M, w * 2, self.n_local * 2,
+                   [self.out_off + (gc + s * w) * 2 for s in range(world)], self.N * 2)
                   for lc, gc, w in self.roles]
         self.peers.allgather(pieces)
         full = self.peers.arena.tensor(self.out_off, (M, self.N), torch.bfloat16)
@@ -194,8 +217,9 @@ class PeerExpertParallelMoE(torch.nn.Module):
         # the bucket is per token, so it can run before the rows travel
         xq = b13(x.reshape(T, H).to(torch.bfloat16).contiguous(), rule)
         self.peers.allgather([
-            (xq.data_ptr(), 1, T * H * 2, T * H * 2, self.x_off + self.rank * T * H * 2, T * H * 2),
-            (ids.data_ptr(), 1, T * topk * 4, T * topk * 4, self.id_off + self.rank * T * topk * 4, T * topk * 4),
+            (xq.data_ptr(), 1, T * H * 2, T * H * 2, [self.x_off + s * T * H * 2 for s in range(world)], T * H * 2),
+            (ids.data_ptr(), 1, T * topk * 4, T * topk * 4,
+             [self.id_off + s * T * topk * 4 for s in range(world)], T * topk * 4),
         ])
         x_all = self.peers.arena.tensor(self.x_off, (world * T, H), torch.bfloat16)
         ids_all = self.peers.arena.tensor(self.id_off, (world * T, topk), torch.int32)

@@ -226,7 +226,20 @@ typedef struct gb_peer_piece {
  * launch.  Every rank must make the same sequence of gb_peer_allgather / gb_peer_barrier calls.
  * A peer that does not show up within two seconds raises gb_device_status (3); nothing hangs. */
 GB_API int gb_peer_allgather(const gb_peer_group* g, const gb_peer_piece* pieces, int n_pieces, void* stream);
-GB_API int gb_peer_barrier(const gb_peer_group* g, void* stream);
+GB_API int gb_peer_barrier(const gb_peer_group* g, void* stream);   /* "my stores before this call are visible" */
+
+/* The same all-gather for small pieces, flag-in-data: every 4-byte word is sent as an 8-byte
+ * {word, exchange number} store into a staging buffer of the receiver (ll[r]: rank r's buffer of
+ * ll_bytes, zero at first use, mapped here), who unpacks it into its own memory.  One one-way
+ * trip instead of two flag round trips.  dst_local[s] says where rank s's piece lands in THIS
+ * rank's buffer.  All pieces of a call together must fit ll_bytes / (16 * world) words. */
+typedef struct gb_peer_ll_piece {
+  const void* src;
+  void* dst_local[GB_PEER_MAX];
+  int64_t rows, row_bytes, src_pitch, dst_pitch;
+} gb_peer_ll_piece;
+GB_API int gb_peer_allgather_ll(const gb_peer_group* g, void* const* ll, int64_t ll_bytes,
+                                const gb_peer_ll_piece* pieces, int n_pieces, void* stream);
 
 #ifdef __cplusplus
 }

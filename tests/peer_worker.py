@@ -23,8 +23,20 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     _native.prepare(local)
-    peers = PeerGroup(64 << 20, dev)
+    # once with the flag-in-data exchange (pieces fit the staging buffer), once with a staging
+    # buffer too small for anything, which sends every exchange down the two-phase path
+    for ll_words in (1 << 19, 16):
+        check(PeerGroup(64 << 20, dev, ll_words=ll_words), rank, world, dev)
+    status = _native.device_status(local)
+    assert status == 0, f"a bounded wait inside a kernel ran out (status {status})"
+    dist.barrier()
+    torch.cuda.synchronize()
+    print(f"rank {rank}: peer paths ok", flush=True)
+    sys.stdout.flush()
+    os._exit(0)
 
+
+def check(peers, rank, world, dev):
     # ---- dense: column shards + peer all-gather == the unsharded layer ----
     fmt = formats.NVFP4_LITERAL
     K, parts = 1024, [512, 256, 256]
@@ -66,14 +78,6 @@ def main():
         got = ep(x, tw_d, ids_d)
         torch.cuda.synchronize()
         assert torch.equal(got, want), (T, float((got.float() - want.float()).abs().max()))
-
-    status = _native.device_status(local)
-    assert status == 0, f"a bounded wait inside a kernel ran out (status {status})"
-    dist.barrier()
-    torch.cuda.synchronize()
-    print(f"rank {rank}: peer paths ok", flush=True)
-    sys.stdout.flush()
-    os._exit(0)
 
 
 if __name__ == "__main__":
