@@ -304,7 +304,7 @@ int gb_gemv_dot(const void* x, const gb_weight* w, int act, int scale_rule, void
   const gb_format& f = w->fmt;
   const bool mine = f.grid == GB_GRID_FP4 && f.mode == GB_MODE_FULL && f.k_bits == 8 && f.scale_coding == GB_SCALE_V1 &&
                     w->cb_row_offset == nullptr && ((uintptr_t)w->qw & 15u) == 0 && w->row_stride % 16 == 0 &&
-                    (act == GB_ACT_NONE || act == GB_ACT_FP4_GROUP16) && w->rows >= 512 && w->K >= 256 * kS &&
+                    (act == GB_ACT_NONE || act == GB_ACT_FP4_GROUP16) && w->rows >= 256 && w->K >= 256 * kS &&
                     ((uintptr_t)x & 15u) == 0 && ((uintptr_t)w->codebook & 3u) == 0;
   if (!mine) return GB_EUNSUPPORTED;
   const int sms = gb_sm_count();

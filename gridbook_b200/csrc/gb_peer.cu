@@ -184,20 +184,25 @@ __global__ void __launch_bounds__(256) peer_ll_kernel(const __grid_constant__ LL
     while (s + 1 < p.n_seg && i >= p.seg[s + 1].first_word) ++s;
     const LLSeg& g = p.seg[s];
     const int64_t j = i - g.first_word, r = j / g.row_words, c = j - r * g.row_words;
-    for (int src = 0; src < p.world; ++src) {
-      if (src == p.rank) continue;
-      const uint2* slot = p.ll[p.rank] + half + (int64_t)src * p.capacity + i;
-      uint2 v = ld_ll(slot);
+    // all sources' slots are read at once; only those not there yet are polled
+    const uint2* slot0 = p.ll[p.rank] + half + i;
+    uint2 v[GB_PEER_MAX];
+#pragma unroll
+    for (int src = 0; src < GB_PEER_MAX; ++src)
+      if (src < p.world && src != p.rank) v[src] = ld_ll(slot0 + (int64_t)src * p.capacity);
+#pragma unroll
+    for (int src = 0; src < GB_PEER_MAX; ++src) {
+      if (src >= p.world || src == p.rank) continue;
       uint64_t t0 = 0;
-      for (uint32_t spin = 0; v.y != epoch && !late; ++spin) {
-        v = ld_ll(slot);
+      for (uint32_t spin = 0; v[src].y != epoch && !late; ++spin) {
+        v[src] = ld_ll(slot0 + (int64_t)src * p.capacity);
         if ((spin & 63u) == 63u) {
           const uint64_t now = gb_globaltimer_ns();
           if (t0 == 0) t0 = now;
           else if (now - t0 > 2000000000ull) late = true;
         }
       }
-      *reinterpret_cast<uint32_t*>(g.dst_local[src] + r * g.dst_pitch + c * 4) = v.x;
+      *reinterpret_cast<uint32_t*>(g.dst_local[src] + r * g.dst_pitch + c * 4) = v[src].x;
     }
   }
   if (late) atomicExch(p.status, 3);
