@@ -340,7 +340,7 @@ def run_gpu(args):
         "prefill": prefill,
     }
     if world == 1 and not args.no_cpu:
-        line["cpu_baseline"] = cpu_baseline(args.format, M, seconds=20.0)
+        line["cpu_baseline"] = cpu_baseline(args.format, M, seconds=12.0)
     print(json.dumps(line), flush=True)
     _leave(world)
 
@@ -518,7 +518,7 @@ def cpu_baseline(fmt_name, M, seconds=20.0):
     cpu_pass(layer)                                   # warm-up
     t0 = time.perf_counter()
     n, nbytes = 0, 0
-    while n < 1 or (time.perf_counter() - t0 < seconds and n < 64):
+    while n < 1 or (time.perf_counter() - t0 < seconds and n < 2000):
         nbytes += cpu_pass(layer)
         n += 1
     dt = time.perf_counter() - t0

@@ -106,7 +106,7 @@ def _declare(lib) -> None:
     lib.gb_moe_route.argtypes = [vp, i64, i64, i64, i64, vp, vp, vp, vp, vp, vp]
     lib.gb_moe_gemv_workspace_bytes.argtypes = [i64, i64]
     lib.gb_moe_gemv_workspace_bytes.restype = i64
-    lib.gb_moe_gemv.argtypes = [vp, vp, wp, i64, i64, vp, vp, i64, i32, vp, vp, vp, i64, vp]
+    lib.gb_moe_gemv.argtypes = [vp, vp, wp, i64, i64, vp, vp, i64, i32, i32, i32, vp, vp, vp, i64, vp]
     lib.gb_moe_combine.argtypes = [vp, vp, vp, i64, i64, i64, i64, vp, vp]
     lib.gb_fp8_quantize_rows.argtypes = [vp, vp, vp, i64, i64, i32, vp]
     lib.gb_gemm_tn.argtypes = [vp, vp, vp, i64, i64, i64, i32, vp, vp, ctypes.c_float, vp]

@@ -172,6 +172,34 @@ GB_DEVINL uint32_t gb_fp4_group16_qdq_lanes(uint32_t w, int scale_rule) {
   return gb_f32_to_bf16_bits(q0) | (gb_f32_to_bf16_bits(q1) << 16);
 }
 
+// The same bucket with a group split over two adjacent lanes (eight values each, lane ^ 1 holds
+// the other half): both lanes must call it.  Bit-identical to gb_fp4_group16_qdq.
+GB_DEVINL uint4 gb_fp4_group16_qdq_pair(uint4 in, int scale_rule) {
+  uint32_t w[4] = {in.x, in.y, in.z, in.w};
+  float v[8];
+  float amax = 0.0f;
+  uint32_t nan = 0u;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = gb_bf16_bits_to_f32(w[i] & 0xFFFFu);
+    v[2 * i + 1] = gb_bf16_bits_to_f32(w[i] >> 16);
+    amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+    nan |= (isnan(v[2 * i]) || isnan(v[2 * i + 1])) ? 1u : 0u;
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  nan |= __shfl_xor_sync(0xffffffffu, nan, 1);
+  amax = fmaxf(amax, 1e-8f);
+  float scale = scale_rule == GB_SCALE_RULE_DIV ? __fdiv_rn(amax, 6.0f) : __fmul_rn(amax, 1.0f / 6.0f);
+  if (nan) scale = __int_as_float(0x7FC00000);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float q0 = __fmul_rn(gb_e2m1_rtn(__fdiv_rn(v[2 * i], scale)), scale);
+    const float q1 = __fmul_rn(gb_e2m1_rtn(__fdiv_rn(v[2 * i + 1], scale)), scale);
+    w[i] = gb_f32_to_bf16_bits(q0) | (gb_f32_to_bf16_bits(q1) << 16);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // ---------------------------------------------------------------------------
 // bit-stream extraction (docs/SPEC.md:56-92): codeword c of a superblock
 // occupies stream bits [c*k, c*k+k), least significant bit first.

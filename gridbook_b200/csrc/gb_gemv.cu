@@ -48,6 +48,7 @@ struct GemvParams {
   const int32_t* order;
   int E;
   int swiglu;             // tile = 4 gate rows + 4 up rows, output silu(g)*u
+  int act, scale_rule;    // routed: fp4 group-16 bucket applied while the activation rows are staged
   int m_chunk;            // tokens per tile pass (MoE), <= 16
   // tiling
   int ksplit, sb_per_slice, n_sb;
@@ -552,7 +553,10 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
             const int pair = p.order[t.m0 + m];
             src_row = p.x_row ? p.x_row[pair] : pair;
           }
-          const uint4 val = *reinterpret_cast<const uint4*>(p.x + src_row * p.K + (int64_t)sb0 * 256 + v * 8);
+          uint4 val = *reinterpret_cast<const uint4*>(p.x + src_row * p.K + (int64_t)sb0 * 256 + v * 8);
+          // fused bucket: a group of 16 is this lane's vector and its neighbour's (whole warps
+          // enter the loop together: the vector count is a multiple of 32)
+          if (p.act == GB_ACT_FP4_GROUP16) val = gb_fp4_group16_qdq_pair(val, p.scale_rule);
           *reinterpret_cast<uint4*>(xs + m * p.x_pitch + v * 16) = val;
         }
         if constexpr (kMoE) { x_expert = t.expert; x_m0 = t.m0; }
@@ -951,7 +955,8 @@ int64_t gb_moe_gemv_workspace_bytes(int64_t P, int64_t rows) {
 
 int gb_moe_gemv(const void* x, const int32_t* x_row, const gb_weight* w, int64_t expert_stride,
                 int64_t E, const int32_t* offsets, const int32_t* order, int64_t P, int swiglu,
-                void* y, const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes, void* stream_) {
+                int act, int scale_rule, void* y, const gb_peer_rows* y_rows, void* workspace,
+                int64_t workspace_bytes, void* stream_) {
   (void)workspace; (void)workspace_bytes;
   cudaStream_t stream = (cudaStream_t)stream_;
   int rc = gb_check_weight(w);
@@ -960,6 +965,8 @@ int gb_moe_gemv(const void* x, const int32_t* x_row, const gb_weight* w, int64_t
   GB_REQUIRE(!(y_rows && swiglu), "per-rank output rows are for the down projection, not the fused gate/up");
   GB_REQUIRE(E >= 1 && P >= 0, "bad E=%lld P=%lld", (long long)E, (long long)P);
   GB_REQUIRE(!swiglu || w->rows % 2 == 0, "swiglu needs an even row count");
+  GB_REQUIRE(act == GB_ACT_NONE || act == GB_ACT_FP4_GROUP16,
+             "the routed kernel fuses the fp4 group-16 bucket only (act %d)", act);
   if (P == 0) return GB_OK;
   const int sms = gb_sm_count();
   if (sms <= 0) return gb_fail(GB_ECUDA, "no usable CUDA device: %s", gb_last_error());
@@ -977,6 +984,8 @@ int gb_moe_gemv(const void* x, const int32_t* x_row, const gb_weight* w, int64_t
   p.order = order;
   p.E = (int)E;
   p.swiglu = swiglu ? 1 : 0;
+  p.act = act;
+  p.scale_rule = scale_rule;
   p.y = (uint16_t*)y;
   if (y_rows) {
     GB_REQUIRE(y_rows->rows_per_rank > 0 && (P + y_rows->rows_per_rank - 1) / y_rows->rows_per_rank <= 8,

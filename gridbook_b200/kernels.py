@@ -203,11 +203,13 @@ def moe_route(topk_ids: torch.Tensor, E: int, topk_weights: torch.Tensor | None 
 
 def moe_gemv(x: torch.Tensor, w: PackedWeight, offsets: torch.Tensor, order: torch.Tensor, *,
              x_row: torch.Tensor | None = None, swiglu: bool = False,
-             out: torch.Tensor | None = None, clear: bool = True, peer_rows=None) -> torch.Tensor | None:
+             out: torch.Tensor | None = None, clear: bool = True, peer_rows=None,
+             act: str | None = None, scale_rule: str = "recip") -> torch.Tensor | None:
     """Grouped GEMV over the routed pairs; y[p] for pair p (rows/2 wide with swiglu).  Rows of
     pairs that routing dropped are not written: they read zero, or are left unset when
     ``clear`` is False (a caller that hands the dropped ids to :func:`moe_combine`).
-    ``peer_rows`` (a ``GbPeerRows``): rows go to their home rank's buffer instead of ``out``."""
+    ``peer_rows`` (a ``GbPeerRows``): rows go to their home rank's buffer instead of ``out``.
+    ``act="fp4"`` applies the fp4 group-16 bucket to ``x`` inside the kernel."""
     _need_cuda(x, offsets, order, x_row)
     lib = nat.load("grouped codebook decode GEMV")
     if x.dtype is not torch.bfloat16:
@@ -220,7 +222,8 @@ def moe_gemv(x: torch.Tensor, w: PackedWeight, offsets: torch.Tensor, order: tor
         out = alloc((P, width), dtype=torch.bfloat16, device=x.device)
     nw = w.native()
     nat.check(lib.gb_moe_gemv(_ptr(x), _ptr(x_row), ctypes.byref(nw), w.expert_stride, w.experts,
-                              _ptr(offsets), _ptr(order), P, 1 if swiglu else 0, _ptr(out),
+                              _ptr(offsets), _ptr(order), P, 1 if swiglu else 0,
+                              nat.ACT_FP4_GROUP16 if act == "fp4" else nat.ACT_NONE, _rule(scale_rule), _ptr(out),
                               ctypes.byref(peer_rows) if peer_rows is not None else None,
                               _ZERO, 0, nat.stream_ptr(x.device)), lib)
     return out

@@ -13,6 +13,9 @@ from ._vllm_compat import FusedMoEMethodBase
 from .formats import CBFormat
 
 
+FUSED_BUCKET_MAX_PAIRS = 32       # routed pairs up to which the grouped kernel buckets its own rows
+
+
 def _row_bytes(in_features: int, type_size: int) -> int:
     if in_features % codec.SUPERBLOCK:
         raise ValueError(f"in_features {in_features} not a multiple of {codec.SUPERBLOCK}")
@@ -161,7 +164,8 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
 
     def _apply_inline(self, layer, x, topk_weights, topk_ids):
         """route -> bucket -> grouped gate/up GEMV with SwiGLU -> bucket -> grouped down GEMV ->
-        combine.  Six launches, no host read, any token count (an expert's tokens are taken
+        combine.  Four launches for small batches (the buckets fused into the grouped kernels), six
+        otherwise; no host read, any token count (an expert's tokens are taken
         in passes of up to sixteen rows, its weights stream once per pass)."""
         from . import ops
         rule = ops.ACT_SCALE_RULE
@@ -173,13 +177,23 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         # the loop chain multiplies by the bf16-rounded router weight (gridbook/moe.py:2407-2408);
         # the routing launch writes it, zeroed for padded pairs
         _, offsets, order, pair_w = kernels.moe_route(ids, layer._cb_E, topk_weights)
-        bucket13 = kernels.fp4_act_qdq if self.fmt13.is_fp4 else kernels.fp8_act_qdq
-        bucket2 = kernels.fp4_act_qdq if self.fmt2.is_fp4 else kernels.fp8_act_qdq
-        xq = bucket13(x2, rule)
-        a = kernels.moe_gemv(xq, layer._cb_w13, offsets, order, x_row=self._x_row(layer, T, topk, x.device),
-                             swiglu=True, clear=False)
-        aq = bucket2(a, rule)
-        y = kernels.moe_gemv(aq, layer._cb_w2, offsets, order, clear=False)
+        # Small batches: the fp4 bucket runs inside the grouped kernel while it stages the rows
+        # (two launches fewer); large ones bucket once up front, since every row tile of an expert
+        # would otherwise bucket the same rows again.
+        fuse = T * topk <= FUSED_BUCKET_MAX_PAIRS
+        x_row = self._x_row(layer, T, topk, x.device)
+        if fuse and self.fmt13.is_fp4:
+            a = kernels.moe_gemv(x2, layer._cb_w13, offsets, order, x_row=x_row, swiglu=True, clear=False,
+                                 act="fp4", scale_rule=rule)
+        else:
+            bucket13 = kernels.fp4_act_qdq if self.fmt13.is_fp4 else kernels.fp8_act_qdq
+            a = kernels.moe_gemv(bucket13(x2, rule), layer._cb_w13, offsets, order, x_row=x_row, swiglu=True,
+                                 clear=False)
+        if fuse and self.fmt2.is_fp4:
+            y = kernels.moe_gemv(a, layer._cb_w2, offsets, order, clear=False, act="fp4", scale_rule=rule)
+        else:
+            bucket2 = kernels.fp4_act_qdq if self.fmt2.is_fp4 else kernels.fp8_act_qdq
+            y = kernels.moe_gemv(bucket2(a, rule), layer._cb_w2, offsets, order, clear=False)
         out = kernels.moe_combine(y, pair_w, T, topk, topk_ids=ids, E=layer._cb_E)
         return out.to(x.dtype).reshape(x.shape)
 

@@ -230,12 +230,15 @@ class PeerExpertParallelMoE(torch.nn.Module):
             x_row = (torch.arange(world * T * topk, device=dev, dtype=torch.int32) // topk).contiguous()
             self._x_row[key] = x_row
         a = kernels.moe_gemv(x_all, layer._cb_w13, offsets, order, x_row=x_row, swiglu=True, clear=False)
-        aq = b2(a, rule)
         rows = nat.GbPeerRows()
         rows.rows_per_rank = T * topk
         for r in range(world):
             rows.base[r] = self.peers.arena.ptr(r, self.back_off)
-        kernels.moe_gemv(aq, layer._cb_w2, offsets, order, peer_rows=rows)
+        from .moe import FUSED_BUCKET_MAX_PAIRS
+        if method.fmt2.is_fp4 and world * T * topk <= FUSED_BUCKET_MAX_PAIRS:
+            kernels.moe_gemv(a, layer._cb_w2, offsets, order, peer_rows=rows, act="fp4", scale_rule=rule)
+        else:
+            kernels.moe_gemv(b2(a, rule), layer._cb_w2, offsets, order, peer_rows=rows)
         self.peers.barrier()
         back = self.peers.arena.tensor(self.back_off, (T * topk, H), torch.bfloat16)
         # the loop chain multiplies by the bf16-rounded router weight (gridbook/moe.py:2407-2408)

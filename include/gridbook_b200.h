@@ -170,6 +170,9 @@ GB_API int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_
  * reads activation row x_row[p] (NULL = p) and writes y[p].  When `swiglu` is set the
  * kernel's output is silu(gate)*up of rows [0,rows/2) and [rows/2,rows) -> y[P, rows/2]
  * (replaces native_moe_activation, gridbook/native_cutlass.py:129-155).
+ * act: GB_ACT_NONE, or GB_ACT_FP4_GROUP16 to apply the fp4 activation bucket (scale_rule as
+ * in gb_fp4_act_qdq) while the rows are staged, which saves the separate bucket launch; every
+ * row tile of an expert buckets its rows again, so it pays for small batches only.
  * y_rows (optional, not with swiglu): instead of y_bf16, pair p's output row goes to
  * y_rows->base[p / rows_per_rank] + (p % rows_per_rank) * rows * 2 bytes, i.e. straight into
  * the buffer of the rank the pair came from (expert-parallel combine over peer memory). */
@@ -180,8 +183,9 @@ typedef struct gb_peer_rows {
 GB_API int64_t gb_moe_gemv_workspace_bytes(int64_t P, int64_t rows);
 GB_API int gb_moe_gemv(const void* x_bf16, const int32_t* x_row, const gb_weight* w,
                 int64_t expert_stride, int64_t E, const int32_t* offsets,
-                const int32_t* order, int64_t P, int swiglu, void* y_bf16,
-                const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes, void* stream);
+                const int32_t* order, int64_t P, int swiglu, int act, int scale_rule,
+                void* y_bf16, const gb_peer_rows* y_rows, void* workspace,
+                int64_t workspace_bytes, void* stream);
 
 /* out[t] = sum over the token's topk pairs of w[p] * y[p], fp32 accumulate, one bf16
  * rounding; replaces cb_moe_combine (gridbook/csrc/cb_gemv.cu:1853-1871,2140-2158).

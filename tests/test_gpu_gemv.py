@@ -170,6 +170,27 @@ def _moe_case(dev, fmt13, fmt2, E, hidden, inter, T, topk, seed):
     return f32_of(out), ref
 
 
+@pytest.mark.parametrize("name", ["k16v2", "lit"])
+def test_moe_fused_bucket_equals_separate_bucket(dev, name):
+    """The fp4 bucket applied while the grouped kernel stages its rows gives the bits of the
+    separate bucket launch, for the gate/up (gathered rows) and the down projection."""
+    from gridbook_b200 import kernels, synth
+    fmt = _fmt(name)
+    E, hidden, inter, T, topk = 8, 512, 256, 7, 3
+    w13d, w2d = synth.make_moe(fmt, fmt, E, hidden, inter, seed=9)
+    ids, _ = synth.make_routing(T, E, topk, seed=9)
+    w13, w2 = synth.to_device_weight(w13d, dev), synth.to_device_weight(w2d, dev)
+    xd = synth.bf16_tensor(synth.make_activations(T, hidden, seed=9), dev)
+    _, offsets, order = kernels.moe_route(torch.from_numpy(ids).to(dev), E)
+    x_row = (torch.arange(T * topk, device=dev, dtype=torch.int32) // topk).contiguous()
+    a_sep = kernels.moe_gemv(kernels.fp4_act_qdq(xd), w13, offsets, order, x_row=x_row, swiglu=True)
+    a_fused = kernels.moe_gemv(xd, w13, offsets, order, x_row=x_row, swiglu=True, act="fp4")
+    assert torch.equal(a_sep, a_fused)
+    y_sep = kernels.moe_gemv(kernels.fp4_act_qdq(a_sep), w2, offsets, order)
+    y_fused = kernels.moe_gemv(a_sep, w2, offsets, order, act="fp4")
+    assert torch.equal(y_sep, y_fused)
+
+
 @pytest.mark.parametrize("T", [1, 5, 16, 40])
 def test_moe_fp4_k16_matches_loop_chain(dev, T):
     fmt = _fmt("k16v2")
