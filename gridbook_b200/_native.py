@@ -22,12 +22,14 @@ REQUIRED_SYMBOLS = (
     "gb_expand_fp8", "gb_expand_fp4_bf16", "gb_expand_fp4_nvfp4",
     "gb_gemv_workspace_bytes", "gb_gemv", "gb_gemv_static",
     "gb_moe_route", "gb_moe_gemv_workspace_bytes", "gb_moe_gemv", "gb_moe_combine",
+    "gb_moe_gemv_pairs_workspace_bytes", "gb_moe_gemv_pairs",
     "gb_fp8_quantize_rows", "gb_gemm_tn",
     "gb_peer_alloc", "gb_peer_free", "gb_peer_export", "gb_peer_open", "gb_peer_close",
     "gb_peer_allgather", "gb_peer_allgather_ll", "gb_peer_barrier", "gb_launch_count",
 )
 PEER_MAX, PEER_HANDLE_BYTES, PEER_FLAG_BYTES = 8, 64, 128
 
+OK, EINVAL, ECUDA, EUNSUPPORTED, EWORKSPACE = 0, 1, 2, 3, 4       # status codes of the C ABI
 GRID_FP4, GRID_FP8 = 0, 1
 MODE_PRODUCT, MODE_SIGNED, MODE_FULL = 0, 1, 2
 SCALE_NONE, SCALE_V1, SCALE_V2 = 0, 1, 2
@@ -107,7 +109,10 @@ def _declare(lib) -> None:
     lib.gb_moe_gemv_workspace_bytes.argtypes = [i64, i64]
     lib.gb_moe_gemv_workspace_bytes.restype = i64
     lib.gb_moe_gemv.argtypes = [vp, vp, wp, i64, i64, vp, vp, i64, i32, i32, i32, vp, vp, vp, i64, vp]
-    lib.gb_moe_combine.argtypes = [vp, vp, vp, i64, i64, i64, i64, vp, vp]
+    lib.gb_moe_combine.argtypes = [vp, vp, vp, i64, i64, i64, i64, i32, vp, vp]
+    lib.gb_moe_gemv_pairs_workspace_bytes.argtypes = [i64, i64, i64]
+    lib.gb_moe_gemv_pairs_workspace_bytes.restype = i64
+    lib.gb_moe_gemv_pairs.argtypes = [vp, vp, wp, i64, i64, i64, vp, i64, i64, i32, i32, i32, vp, vp, vp, i64, vp]
     lib.gb_fp8_quantize_rows.argtypes = [vp, vp, vp, i64, i64, i32, vp]
     lib.gb_gemm_tn.argtypes = [vp, vp, vp, i64, i64, i64, i32, vp, vp, ctypes.c_float, vp]
     lib.gb_launch_count.restype = i64

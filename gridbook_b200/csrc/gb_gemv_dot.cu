@@ -53,9 +53,27 @@ struct DotParams {
   int act, scale_rule;
   int64_t N;
   int n_sb, n_slices, n_groups, rows_per_group;
-  float* ws;                // [n_slices][N] partial sums
+  float* ws;                // [n_slices][N] partial sums; pair mode: [n_slices][P][N]
   int* status;
+  // ---- pair mode: one independent GEMV per routed (token, expert) pair ----
+  const int32_t* pair_expert;   // [P] global expert id of every pair (outside [base, base+E): skipped)
+  const int32_t* x_row;         // [P] activation row of every pair (nullptr: the pair index)
+  int P, E, expert_base, bands; // bands: row bands per pair
+  uint16_t* y;                  // direct bf16 output when there is one K slice and no SwiGLU
+  uint16_t* y_peer[8];          // optional: pair p's row lives in y_peer[p / pairs_per_rank]
+  int pairs_per_rank;
+  int direct;                   // 1: store y from the kernel, 0: partial sums + the summing kernel
+  float global_scale;
 };
+
+// Output row of pair `pair` (width `width` elements): in y, or in its home rank's buffer.
+GB_DEVINL uint16_t* pair_out_row(const DotParams& p, int pair, int64_t width) {
+  if (p.pairs_per_rank > 0) {
+    const int home = pair / p.pairs_per_rank;
+    return p.y_peer[home] + (int64_t)(pair - home * p.pairs_per_rank) * width;
+  }
+  return p.y + (int64_t)pair * width;
+}
 
 // Shared-memory loads that depend on a token (the result of the barrier wait that made the
 // data visible): plain asm the scheduler may reorder freely, but never above that wait.
@@ -105,6 +123,7 @@ GB_DEVINL void dot_superblock(uint32_t rowp_codes, uint32_t rowp_scales, const u
   acc1 = fmaf(t2 + t3, f23, acc1);
 }
 
+template <bool kPairs>
 __global__ void __launch_bounds__(kDotThreads, 1)
 gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -126,7 +145,10 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
   };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int slice = blockIdx.x % p.n_slices, group = blockIdx.x / p.n_slices;
+  const int slice = blockIdx.x % p.n_slices;
+  // dense: a row band of the matrix; pair mode: (pair, row band of that pair's expert)
+  const int group = kPairs ? (int)(blockIdx.x / p.n_slices) % p.bands : (int)(blockIdx.x / p.n_slices);
+  const int pair = kPairs ? (int)(blockIdx.x / p.n_slices) / p.bands : 0;
   const int sb0 = slice * kS;
   const int ns = min(kS, p.n_sb - sb0);
   const int64_t row_begin = (int64_t)group * p.rows_per_group;
@@ -143,6 +165,16 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
   __syncthreads();
   gb_pdl_launch_dependents();
 
+  int64_t tma_row0 = row_begin;          // first row of the band in the tensor map's row space
+  const uint16_t* xsrc = p.x;
+  if constexpr (kPairs) {
+    gb_pdl_wait();                       // the routing and the activations come from earlier kernels
+    const int e = p.pair_expert[pair] - p.expert_base;
+    if (e < 0 || e >= p.E) return;       // padded route, or an expert another rank holds: whole CTA leaves
+    tma_row0 = (int64_t)e * p.N + row_begin;
+    xsrc = p.x + (int64_t)(p.x_row ? p.x_row[pair] : pair) * ((int64_t)p.n_sb * 256);
+  }
+
   if (warp == kConsumers) {
     // ------------------------------ producer ------------------------------
     // The weight stream depends on nothing an earlier kernel wrote: the ring fills while the
@@ -158,7 +190,7 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
         asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
             ::"r"(stage_addr(s)), "l"(reinterpret_cast<uint64_t>(&map_w)),
-              "r"(sb0 * 48), "r"((int)(row_begin + (int64_t)st * kStageRows)), "r"(gb_smem_u32(&full_bar[s]))
+              "r"(sb0 * 48), "r"((int)(tma_row0 + (int64_t)st * kStageRows)), "r"(gb_smem_u32(&full_bar[s]))
             : "memory");
       }
     }
@@ -183,7 +215,7 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
   // ---- this slice of the activation row, through its bucket, into shared memory ----
   gb_pdl_wait();                       // the activations (and the partial-sum slots) belong to earlier kernels
   if (tid < ns * 128) {                // two values per thread, a bucket group per eight lanes
-    uint32_t w = reinterpret_cast<const uint32_t*>(p.x + (int64_t)sb0 * 256)[tid];
+    uint32_t w = reinterpret_cast<const uint32_t*>(xsrc + (int64_t)sb0 * 256)[tid];
     if (p.act == GB_ACT_FP4_GROUP16) w = gb_fp4_group16_qdq_lanes(w, p.scale_rule);
     reinterpret_cast<uint32_t*>(xq)[tid] = w;
   }
@@ -236,7 +268,11 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
   }
   // lookups 0,1 fall in group r >> 1 of the lane's two, lookups 2,3 in the other
   const uint32_t sel_sc = rh ? 0x4401u : 0x4410u;
-  float* my_ws = p.ws + (int64_t)slice * p.N;
+  float* my_ws = kPairs ? p.ws + ((int64_t)slice * p.P + pair) * p.N : p.ws + (int64_t)slice * p.N;
+  uint16_t* my_y = nullptr;
+  if constexpr (kPairs) {
+    if (p.direct) my_y = pair_out_row(p, pair, p.N);
+  }
   for (int st = 0; st < n_stages; ++st) {
     const int s = st % kDotStages;
     uint32_t tok;
@@ -269,7 +305,10 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
 #pragma unroll
     for (int o = 4; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     const int64_t row = row_begin + (int64_t)st * kStageRows + 4 * warp + r;
-    if (lp == 0 && row < row_end) my_ws[row] = acc;
+    if (lp == 0 && row < row_end) {
+      if (kPairs && my_y) my_y[row] = (uint16_t)gb_f32_to_bf16_bits(acc * p.global_scale);
+      else my_ws[row] = acc;
+    }
     __syncwarp();
     if (lane == 0) gb_mbar_arrive(&empty_bar[s]);
   }
@@ -286,10 +325,40 @@ __global__ void dot_finalize_kernel(const float* __restrict__ ws, int n_slices, 
   y[n] = (uint16_t)gb_f32_to_bf16_bits(acc * global_scale);
 }
 
+// Pair mode: adds the K slices of every routed pair's rows, applies the global scale and, for
+// the fused gate/up projection, SwiGLU with the bf16 roundings of F.silu(gate) * up
+// (gridbook/native_cutlass.py:129-155), then rounds once.
+__global__ void dot_pairs_finalize_kernel(const __grid_constant__ DotParams p, int swiglu) {
+  gb_pdl_launch_dependents();
+  gb_pdl_wait();
+  const int64_t width = swiglu ? p.N / 2 : p.N;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)p.P * width) return;
+  const int pair = (int)(i / width);
+  const int64_t j = i - (int64_t)pair * width;
+  const int e = p.pair_expert[pair] - p.expert_base;
+  if (e < 0 || e >= p.E) return;
+  float a = 0.f, b = 0.f;
+  for (int s = 0; s < p.n_slices; ++s) {
+    const float* slot = p.ws + ((int64_t)s * p.P + pair) * p.N;
+    a += slot[j];
+    if (swiglu) b += slot[j + width];
+  }
+  float out = a * p.global_scale;
+  if (swiglu) {
+    const float gate = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(out));
+    const float up = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(b * p.global_scale));
+    const float sl = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(gate / (1.0f + __expf(-gate))));
+    out = sl * up;
+  }
+  pair_out_row(p, pair, width)[j] = (uint16_t)gb_f32_to_bf16_bits(out);
+}
+
 }  // namespace
 
 int gb_prepare_dot() {
-  GB_CUDA_OK(cudaFuncSetAttribute((const void*)gemv_dot_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDotSmem));
+  GB_CUDA_OK(cudaFuncSetAttribute((const void*)gemv_dot_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDotSmem));
+  GB_CUDA_OK(cudaFuncSetAttribute((const void*)gemv_dot_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDotSmem));
   return GB_OK;
 }
 
@@ -330,9 +399,95 @@ int gb_gemv_dot(const void* x, const gb_weight* w, int act, int scale_rule, void
   int rc = gb_tensor_map_bytes_2d(&map, w->qw, (uint64_t)p.n_sb * 48u, (uint64_t)w->rows, (uint64_t)w->row_stride,
                                   kRowBytes, kStageRows);
   if (rc != GB_OK) return rc;
-  GB_CUDA_OK(gb_launch(gemv_dot_kernel, dim3(p.n_slices * p.n_groups), dim3(kDotThreads), kDotSmem, stream, map, p));
+  GB_CUDA_OK(gb_launch(gemv_dot_kernel<false>, dim3(p.n_slices * p.n_groups), dim3(kDotThreads), kDotSmem, stream, map, p));
   const float gs = w->global_scale == 0.0f ? 1.0f : w->global_scale;
   GB_CUDA_OK(gb_launch(dot_finalize_kernel, dim3((unsigned)((w->rows + 255) / 256)), dim3(256), 0, stream,
                        (const float*)p.ws, p.n_slices, (int64_t)w->rows, gs, (uint16_t*)y));
+  return GB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Routed layer, small batches: every (token, expert) pair is its own M = 1 linear through the
+// table kernel above.  An expert's weights stream once per PAIR (as in the reference's grouped
+// GEMV, gridbook/csrc/cb_gemv.cu:1220-1233), so this pays while few pairs share an expert.
+// ---------------------------------------------------------------------------
+extern "C" int64_t gb_moe_gemv_pairs_workspace_bytes(int64_t P, int64_t rows, int64_t K) {
+  const int64_t n_slices = (K / 256 + kS - 1) / kS;
+  return n_slices * P * rows * (int64_t)sizeof(float);
+}
+
+extern "C" int gb_moe_gemv_pairs(const void* x, const int32_t* x_row, const gb_weight* w, int64_t expert_stride,
+                                 int64_t E, int64_t expert_base, const int32_t* pair_expert, int64_t P,
+                                 int64_t pairs_expected, int swiglu, int act, int scale_rule, void* y,
+                                 const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int rc = gb_check_weight(w);
+  if (rc != GB_OK) return rc;
+  GB_REQUIRE(x && pair_expert && (y || y_rows), "null pointer argument");
+  GB_REQUIRE(E >= 1 && P >= 0 && P < (1 << 24), "bad E=%lld P=%lld", (long long)E, (long long)P);
+  GB_REQUIRE(!swiglu || w->rows % 2 == 0, "swiglu needs an even row count");
+  const gb_format& f = w->fmt;
+  const bool mine = f.grid == GB_GRID_FP4 && f.mode == GB_MODE_FULL && f.k_bits == 8 && f.scale_coding == GB_SCALE_V1 &&
+                    w->cb_row_offset == nullptr && ((uintptr_t)w->qw & 15u) == 0 && w->row_stride % 16 == 0 &&
+                    expert_stride == w->rows * w->row_stride && E * w->rows < (1ll << 31) &&
+                    (act == GB_ACT_NONE || act == GB_ACT_FP4_GROUP16) && w->K >= 256 && w->K <= 256 * 64 &&
+                    ((uintptr_t)x & 15u) == 0 && ((uintptr_t)w->codebook & 3u) == 0;
+  if (!mine) return GB_EUNSUPPORTED;
+  if (P == 0) return GB_OK;
+  const int sms = gb_sm_count();
+  if (sms <= 0) return gb_fail(GB_ECUDA, "no usable CUDA device: %s", gb_last_error());
+  DotParams p = {};
+  p.x = (const uint16_t*)x;
+  p.x_row = x_row;
+  p.codebook = (const uint16_t*)w->codebook;
+  p.act = act;
+  p.scale_rule = scale_rule;
+  p.N = w->rows;
+  p.n_sb = (int)(w->K / 256);
+  p.n_slices = (p.n_sb + kS - 1) / kS;
+  p.pair_expert = pair_expert;
+  p.P = (int)P;
+  p.E = (int)E;
+  p.expert_base = (int)expert_base;
+  p.global_scale = w->global_scale == 0.0f ? 1.0f : w->global_scale;
+  p.status = gb_status_word();
+  p.y = (uint16_t*)y;
+  if (y_rows) {
+    GB_REQUIRE(y_rows->rows_per_rank > 0 && (P + y_rows->rows_per_rank - 1) / y_rows->rows_per_rank <= 8,
+               "bad per-rank output rows: %lld per rank for %lld pairs", (long long)y_rows->rows_per_rank, (long long)P);
+    for (int r = 0; r * y_rows->rows_per_rank < P; ++r) {
+      GB_REQUIRE(y_rows->base[r] != nullptr, "per-rank output rows: rank %d has no buffer", r);
+      p.y_peer[r] = (uint16_t*)y_rows->base[r];
+    }
+    p.pairs_per_rank = (int)y_rows->rows_per_rank;
+  }
+  // row bands per pair: enough CTAs to cover the machine with the pairs expected to be live here
+  int64_t live = pairs_expected > 0 && pairs_expected < P ? pairs_expected : P;
+  int bands = (int)(sms / (live * p.n_slices));
+  const int max_bands = (int)((w->rows + kStageRows - 1) / kStageRows);
+  if (bands > max_bands) bands = max_bands;
+  if (bands < 1) bands = 1;
+  p.bands = bands;
+  const int64_t per = (w->rows + bands - 1) / bands;
+  p.rows_per_group = (int)((per + kStageRows - 1) / kStageRows * kStageRows);
+  p.direct = (p.n_slices == 1 && !swiglu) ? 1 : 0;
+  if (!p.direct) {
+    const int64_t need = gb_moe_gemv_pairs_workspace_bytes(P, w->rows, w->K);
+    GB_REQUIRE(workspace != nullptr && workspace_bytes >= need, "workspace of %lld bytes is too small (need %lld)",
+               (long long)workspace_bytes, (long long)need);
+    p.ws = (float*)workspace;
+  }
+  CUtensorMap map;
+  rc = gb_tensor_map_bytes_2d(&map, w->qw, (uint64_t)p.n_sb * 48u, (uint64_t)(E * w->rows), (uint64_t)w->row_stride,
+                              kRowBytes, kStageRows);
+  if (rc != GB_OK) return rc;
+  const int64_t grid = P * p.n_slices * bands;
+  GB_REQUIRE(grid < (1ll << 31), "too many pairs for one launch");
+  GB_CUDA_OK(gb_launch(gemv_dot_kernel<true>, dim3((unsigned)grid), dim3(kDotThreads), kDotSmem, stream, map, p));
+  if (!p.direct) {
+    const int64_t total = P * (swiglu ? w->rows / 2 : w->rows);
+    GB_CUDA_OK(gb_launch(dot_pairs_finalize_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, p,
+                         swiglu ? 1 : 0));
+  }
   return GB_OK;
 }

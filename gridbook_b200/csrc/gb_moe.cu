@@ -65,7 +65,8 @@ moe_route_kernel(const int32_t* __restrict__ ids, int P, int E, int first_expert
 // out[t][h] = bf16( sum_slot w[t*topk+slot] * y[t*topk+slot][h] ), fp32 accumulate.
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const uint16_t* __restrict__ y, const float* __restrict__ pair_w,
-                   const int32_t* __restrict__ ids, int E, int topk, int64_t H, uint16_t* __restrict__ out) {
+                   const int32_t* __restrict__ ids, int E, int topk, int64_t H, int round_w,
+                   uint16_t* __restrict__ out) {
   gb_pdl_launch_dependents();
   gb_pdl_wait();
   const int64_t t = blockIdx.y;
@@ -78,7 +79,8 @@ moe_combine_kernel(const uint16_t* __restrict__ y, const float* __restrict__ pai
       const int id = ids[p];
       if (id < 0 || id >= E) continue;
     }
-    const float w = pair_w[p];
+    float w = pair_w[p];
+    if (round_w) w = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(w));
     const uint32_t v = *reinterpret_cast<const uint32_t*>(y + p * H + h2 * 2);
     a0 = fmaf(w, gb_bf16_bits_to_f32(v & 0xFFFFu), a0);
     a1 = fmaf(w, gb_bf16_bits_to_f32(v >> 16), a1);
@@ -104,14 +106,14 @@ int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E, in
 }
 
 int gb_moe_combine(const void* y, const float* pair_w, const int32_t* topk_ids, int64_t E, int64_t T,
-                   int64_t topk, int64_t H, void* out, void* stream) {
+                   int64_t topk, int64_t H, int round_weights, void* out, void* stream) {
   GB_REQUIRE(y && pair_w && out, "null pointer argument");
   GB_REQUIRE(T >= 0 && topk >= 1 && H > 0 && H % 2 == 0, "bad combine shape T=%lld topk=%lld H=%lld",
              (long long)T, (long long)topk, (long long)H);
   if (T == 0) return GB_OK;
   dim3 grid((unsigned)((H / 2 + 255) / 256), (unsigned)T);
   GB_CUDA_OK(gb_launch(moe_combine_kernel, grid, dim3(256), 0, (cudaStream_t)stream, (const uint16_t*)y, pair_w,
-                       topk_ids, (int)E, (int)topk, H, (uint16_t*)out));
+                       topk_ids, (int)E, (int)topk, H, round_weights ? 1 : 0, (uint16_t*)out));
   return GB_OK;
 }
 

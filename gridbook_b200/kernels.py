@@ -229,21 +229,54 @@ def moe_gemv(x: torch.Tensor, w: PackedWeight, offsets: torch.Tensor, order: tor
     return out
 
 
+def moe_gemv_pairs(x: torch.Tensor, w: PackedWeight, pair_expert: torch.Tensor, *,
+                   x_row: torch.Tensor | None = None, swiglu: bool = False, act: str | None = None,
+                   scale_rule: str = "recip", expert_base: int = 0, pairs_expected: int = 0,
+                   peer_rows=None) -> torch.Tensor | None | bool:
+    """The routed projection with every pair as its own M = 1 linear through the
+    inner-product-table kernel (literal format, small batches).  ``pair_expert`` [P] int32 holds
+    each pair's global expert id; ids outside this stack's range are skipped and their output
+    rows left unset.  Returns the [P, width] output (True with ``peer_rows``), or None when the
+    format has no such kernel and the caller should use :func:`moe_gemv`."""
+    _need_cuda(x, pair_expert, x_row)
+    lib = nat.load("per-pair table GEMV")
+    if x.dtype is not torch.bfloat16:
+        raise TypeError("the per-pair GEMV takes bf16 activations")
+    x = x.contiguous()
+    ids = pair_expert.reshape(-1).to(torch.int32).contiguous()
+    P = ids.numel()
+    width = w.rows // 2 if swiglu else w.rows
+    out = None if peer_rows is not None else torch.empty((P, width), dtype=torch.bfloat16, device=x.device)
+    need = lib.gb_moe_gemv_pairs_workspace_bytes(P, w.rows, w.K)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
+    nw = w.native()
+    rc = lib.gb_moe_gemv_pairs(_ptr(x), _ptr(x_row), ctypes.byref(nw), w.expert_stride, w.experts, expert_base,
+                               _ptr(ids), P, pairs_expected, 1 if swiglu else 0,
+                               nat.ACT_FP4_GROUP16 if act == "fp4" else nat.ACT_NONE, _rule(scale_rule), _ptr(out),
+                               ctypes.byref(peer_rows) if peer_rows is not None else None,
+                               _ptr(ws), ws.numel(), nat.stream_ptr(x.device))
+    if rc == nat.EUNSUPPORTED:
+        return None
+    nat.check(rc, lib)
+    return True if peer_rows is not None else out
+
+
 def moe_combine(y: torch.Tensor, pair_w: torch.Tensor, T: int, topk: int, *,
-                topk_ids: torch.Tensor | None = None, E: int = 0) -> torch.Tensor:
+                topk_ids: torch.Tensor | None = None, E: int = 0, round_weights: bool = False) -> torch.Tensor:
     """out[t] = sum_slot pair_w * y, fp32 accumulate, one bf16 rounding.  ``topk_ids`` (int32,
-    with ``E``) names the pairs routing dropped, whose rows of ``y`` are then never read."""
+    with ``E``) names the pairs routing dropped, whose rows of ``y`` are then never read.
+    ``round_weights``: ``pair_w`` are raw router weights, rounded to bf16 inside the kernel."""
     _need_cuda(y, pair_w, topk_ids)
     lib = nat.load("grouped CB router combine")
     y = y.contiguous()
     H = y.shape[-1]
     out = torch.empty((T, H), dtype=torch.bfloat16, device=y.device)
-    pw = pair_w.to(torch.float32).contiguous()
+    pw = pair_w.reshape(-1).to(torch.float32).contiguous()
     ids = None
     if topk_ids is not None:
         ids = topk_ids.to(torch.int32).contiguous()
-    nat.check(lib.gb_moe_combine(_ptr(y), _ptr(pw), _ptr(ids), E, T, topk, H, _ptr(out),
-                                 nat.stream_ptr(y.device)), lib)
+    nat.check(lib.gb_moe_combine(_ptr(y), _ptr(pw), _ptr(ids), E, T, topk, H, 1 if round_weights else 0,
+                                 _ptr(out), nat.stream_ptr(y.device)), lib)
     return out
 
 

@@ -13,6 +13,7 @@ from ._vllm_compat import FusedMoEMethodBase
 from .formats import CBFormat
 
 
+PAIR_KERNEL_MAX_PAIRS = 768       # routed pairs up to which every pair runs as its own table GEMV
 FUSED_BUCKET_MAX_PAIRS = 32       # routed pairs up to which the grouped kernel buckets its own rows
 
 
@@ -174,6 +175,10 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
             return torch.empty_like(x)
         x2 = x.reshape(T, -1).to(torch.bfloat16).contiguous()
         ids = topk_ids.to(torch.int32).contiguous()
+        if T * topk <= PAIR_KERNEL_MAX_PAIRS and self.fmt13.is_fp4 and self.fmt2.is_fp4:
+            out = self._apply_pairs(layer, x2, topk_weights, ids, rule)
+            if out is not None:
+                return out.to(x.dtype).reshape(x.shape)
         # the loop chain multiplies by the bf16-rounded router weight (gridbook/moe.py:2407-2408);
         # the routing launch writes it, zeroed for padded pairs
         _, offsets, order, pair_w = kernels.moe_route(ids, layer._cb_E, topk_weights)
@@ -196,6 +201,21 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
             y = kernels.moe_gemv(bucket2(a, rule), layer._cb_w2, offsets, order, clear=False)
         out = kernels.moe_combine(y, pair_w, T, topk, topk_ids=ids, E=layer._cb_E)
         return out.to(x.dtype).reshape(x.shape)
+
+
+    def _apply_pairs(self, layer, x2, topk_weights, ids, rule):
+        """Small batches of the literal format: every routed pair is its own M = 1 linear through
+        the inner-product-table kernel (bucket fused, SwiGLU in the slot-summing kernel), then the
+        combine.  Four launches, no routing tables.  None when the format has no such kernel."""
+        T, topk = ids.shape
+        x_row = self._x_row(layer, T, topk, x2.device)
+        a = kernels.moe_gemv_pairs(x2, layer._cb_w13, ids, x_row=x_row, swiglu=True, act="fp4", scale_rule=rule)
+        if a is None:
+            return None
+        y = kernels.moe_gemv_pairs(a, layer._cb_w2, ids, act="fp4", scale_rule=rule)
+        if y is None:
+            return None
+        return kernels.moe_combine(y, topk_weights, T, topk, topk_ids=ids, E=layer._cb_E, round_weights=True)
 
 
 class CBMoE(torch.nn.Module):

@@ -23,6 +23,7 @@ import torch.distributed as dist
 
 from . import _native as nat
 from . import kernels
+from ._native import NativeKernelUnavailableError
 
 
 class _RawDeviceMemory:
@@ -199,6 +200,12 @@ class PeerExpertParallelMoE(torch.nn.Module):
         self.id_off = a.carve(self.world * max_tokens * topk * 4)
         self.back_off = a.carve(max_tokens * topk * hidden * 2)
         self._x_row = {}
+        # whether the layer's formats have the per-pair table kernel (decided once, the same on
+        # every rank: all ranks must make the same sequence of exchange calls)
+        w13, w2 = moe_layer._cb_w13, moe_layer._cb_w2
+        self._pairs_ok = all(f.is_fp4 and f.mode == "full" and f.k == 8 and f.scale_coding == "v1"
+                             for f in (moe_layer.method.fmt13, moe_layer.method.fmt2)) and \
+            all(wt.row_stride % 16 == 0 for wt in (w13, w2))
 
     def forward(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         from . import ops
@@ -214,8 +221,14 @@ class PeerExpertParallelMoE(torch.nn.Module):
         b13 = kernels.fp4_act_qdq if method.fmt13.is_fp4 else kernels.fp8_act_qdq
         b2 = kernels.fp4_act_qdq if method.fmt2.is_fp4 else kernels.fp8_act_qdq
         ids = topk_ids.to(torch.int32).contiguous()
-        # the bucket is per token, so it can run before the rows travel
-        xq = b13(x.reshape(T, H).to(torch.bfloat16).contiguous(), rule)
+        from .moe import FUSED_BUCKET_MAX_PAIRS, PAIR_KERNEL_MAX_PAIRS
+        pairs_all = world * T * topk
+        # small batches of the literal format: every pair is its own table GEMV (bucket fused)
+        per_pair = pairs_all <= PAIR_KERNEL_MAX_PAIRS and self._pairs_ok
+        x2 = x.reshape(T, H).to(torch.bfloat16).contiguous()
+        # the bucket is per token, so it can run before the rows travel (the per-pair kernel
+        # applies it itself)
+        xq = x2 if per_pair else b13(x2, rule)
         self.peers.allgather([
             (xq.data_ptr(), 1, T * H * 2, T * H * 2, [self.x_off + s * T * H * 2 for s in range(world)], T * H * 2),
             (ids.data_ptr(), 1, T * topk * 4, T * topk * 4,
@@ -223,22 +236,35 @@ class PeerExpertParallelMoE(torch.nn.Module):
         ])
         x_all = self.peers.arena.tensor(self.x_off, (world * T, H), torch.bfloat16)
         ids_all = self.peers.arena.tensor(self.id_off, (world * T, topk), torch.int32)
-        _, offsets, order = kernels.moe_route(ids_all, self.e_local, expert_base=self.rank * self.e_local)
         key = (world * T, topk)
         x_row = self._x_row.get(key)
         if x_row is None:
             x_row = (torch.arange(world * T * topk, device=dev, dtype=torch.int32) // topk).contiguous()
             self._x_row[key] = x_row
-        a = kernels.moe_gemv(x_all, layer._cb_w13, offsets, order, x_row=x_row, swiglu=True, clear=False)
         rows = nat.GbPeerRows()
         rows.rows_per_rank = T * topk
         for r in range(world):
             rows.base[r] = self.peers.arena.ptr(r, self.back_off)
-        from .moe import FUSED_BUCKET_MAX_PAIRS
-        if method.fmt2.is_fp4 and world * T * topk <= FUSED_BUCKET_MAX_PAIRS:
-            kernels.moe_gemv(a, layer._cb_w2, offsets, order, peer_rows=rows, act="fp4", scale_rule=rule)
-        else:
-            kernels.moe_gemv(b2(a, rule), layer._cb_w2, offsets, order, peer_rows=rows)
+        base = self.rank * self.e_local
+        done = False
+        if per_pair:
+            expect = max(1, pairs_all // world)
+            a = kernels.moe_gemv_pairs(x_all, layer._cb_w13, ids_all, x_row=x_row, swiglu=True, act="fp4",
+                                       scale_rule=rule, expert_base=base, pairs_expected=expect)
+            if a is None:
+                # every rank holds the same formats, so every rank takes this branch together
+                raise NativeKernelUnavailableError(
+                    "per-pair table GEMV refused a format the layer was built for")
+            kernels.moe_gemv_pairs(a, layer._cb_w2, ids_all, act="fp4", scale_rule=rule, expert_base=base,
+                                   pairs_expected=expect, peer_rows=rows)
+            done = True
+        if not done:
+            _, offsets, order = kernels.moe_route(ids_all, self.e_local, expert_base=base)
+            a = kernels.moe_gemv(x_all, layer._cb_w13, offsets, order, x_row=x_row, swiglu=True, clear=False)
+            if method.fmt2.is_fp4 and pairs_all <= FUSED_BUCKET_MAX_PAIRS:
+                kernels.moe_gemv(a, layer._cb_w2, offsets, order, peer_rows=rows, act="fp4", scale_rule=rule)
+            else:
+                kernels.moe_gemv(b2(a, rule), layer._cb_w2, offsets, order, peer_rows=rows)
         self.peers.barrier()
         back = self.peers.arena.tensor(self.back_off, (T * topk, H), torch.bfloat16)
         # the loop chain multiplies by the bf16-rounded router weight (gridbook/moe.py:2407-2408)

@@ -187,13 +187,31 @@ GB_API int gb_moe_gemv(const void* x_bf16, const int32_t* x_row, const gb_weight
                 void* y_bf16, const gb_peer_rows* y_rows, void* workspace,
                 int64_t workspace_bytes, void* stream);
 
+/* The same routed projection for SMALL batches of the literal format (fp4 grid, full mode,
+ * k = 8, E4M3-direct scales, one codebook per stack): every routed pair p is its own M = 1 linear
+ * through the inner-product-table kernel, y[p] = W[pair_expert[p]] . x[x_row[p]] (NULL x_row:
+ * row p).  No routing tables are needed; pairs whose expert lies outside
+ * [expert_base, expert_base + E) are skipped.  An expert's weights stream once per pair, as in
+ * the reference's grouped GEMV (gridbook/csrc/cb_gemv.cu:1220-1233), so this pays while few
+ * pairs share an expert; pairs_expected (0 = P) sizes the grid for the pairs expected to be
+ * live on this rank.  Returns GB_EUNSUPPORTED for any other format (use gb_moe_gemv).
+ * swiglu / act / y_rows as in gb_moe_gemv. */
+GB_API int64_t gb_moe_gemv_pairs_workspace_bytes(int64_t P, int64_t rows, int64_t K);
+GB_API int gb_moe_gemv_pairs(const void* x_bf16, const int32_t* x_row, const gb_weight* w,
+                int64_t expert_stride, int64_t E, int64_t expert_base, const int32_t* pair_expert,
+                int64_t P, int64_t pairs_expected, int swiglu, int act, int scale_rule, void* y_bf16,
+                const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* out[t] = sum over the token's topk pairs of w[p] * y[p], fp32 accumulate, one bf16
  * rounding; replaces cb_moe_combine (gridbook/csrc/cb_gemv.cu:1853-1871,2140-2158).
  * pair p = t*topk + slot.  topk_ids (optional, with E): pairs whose id lies outside [0, E)
  * were dropped by gb_moe_route and have no row in y; they are skipped, so y needs no
- * clearing beforehand. */
+ * clearing beforehand.
+ * round_weights: pair_w holds raw router weights; round each to bf16 first
+ * (gridbook/moe.py:2407-2408), for callers that did not get them from gb_moe_route. */
 GB_API int gb_moe_combine(const void* y_bf16, const float* pair_w, const int32_t* topk_ids,
-                   int64_t E, int64_t T, int64_t topk, int64_t H, void* out_bf16, void* stream);
+                   int64_t E, int64_t T, int64_t topk, int64_t H, int round_weights,
+                   void* out_bf16, void* stream);
 
 /* Kernel launches this library has issued in this process so far (launches recorded into a
  * CUDA graph count once, at capture).  No reference counterpart; used by the benchmark to

@@ -55,29 +55,30 @@ def check(peers, rank, world, dev):
         assert_close_bf16(got.float().cpu().numpy(), want.float().cpu().numpy(), f"peer all-gather M={M}")
 
     # ---- routed layer: expert-parallel over peer memory == all experts on one GPU ----
-    E, topk, hidden, inter = 16, 4, 512, 256
-    e_local = E // world
-    mfmt = formats.NVFP4_CB_K16
-    gen = torch.Generator(device=dev).manual_seed(23)
-    w13 = synth.make_packed_device(mfmt, E * 2 * inter, hidden, gen, dev).view(E, 2 * inter, -1)
-    w2 = synth.make_packed_device(mfmt, E * hidden, inter, gen, dev).view(E, hidden, -1)
-    t13, t2 = synth.codebook_tables(mfmt, 5), synth.codebook_tables(mfmt, 6)
-    whole = CBMoE(mfmt, mfmt, E, hidden, inter, t13, t2, prefix="whole").load(w13, w2, None, None, dev)
-    mine = CBMoE(mfmt, mfmt, e_local, hidden, inter, t13, t2, prefix="mine").load(
-        w13[rank * e_local:(rank + 1) * e_local].contiguous(), w2[rank * e_local:(rank + 1) * e_local].contiguous(),
-        None, None, dev)
-    ep = PeerExpertParallelMoE(E, mine, peers, max_tokens=64, topk=topk, hidden=hidden)
-    for T in (1, 5, 40, 5):
-        ids, tw = synth.make_routing(T, E, topk, seed=100 * T + rank)        # every rank its own batch
-        if T == 5:
-            ids[2, 1] = -1                                                    # a padded route
-        xg = torch.Generator(device=dev).manual_seed(1000 + 10 * T + rank)
-        x = torch.randn(T, hidden, generator=xg, device=dev).to(torch.bfloat16)
-        ids_d, tw_d = torch.from_numpy(ids).to(dev), torch.from_numpy(tw).to(dev)
-        want = whole(x, tw_d, ids_d)
-        got = ep(x, tw_d, ids_d)
-        torch.cuda.synchronize()
-        assert torch.equal(got, want), (T, float((got.float() - want.float()).abs().max()))
+    # k16v2 runs the grouped kernels, the literal format the per-pair table kernel (small batches)
+    for mfmt in (formats.NVFP4_CB_K16, formats.NVFP4_LITERAL):
+        E, topk, hidden, inter = 16, 4, 512, 256
+        e_local = E // world
+        gen = torch.Generator(device=dev).manual_seed(23)
+        w13 = synth.make_packed_device(mfmt, E * 2 * inter, hidden, gen, dev).view(E, 2 * inter, -1)
+        w2 = synth.make_packed_device(mfmt, E * hidden, inter, gen, dev).view(E, hidden, -1)
+        t13, t2 = synth.codebook_tables(mfmt, 5), synth.codebook_tables(mfmt, 6)
+        whole = CBMoE(mfmt, mfmt, E, hidden, inter, t13, t2, prefix="whole").load(w13, w2, None, None, dev)
+        mine = CBMoE(mfmt, mfmt, e_local, hidden, inter, t13, t2, prefix="mine").load(
+            w13[rank * e_local:(rank + 1) * e_local].contiguous(),
+            w2[rank * e_local:(rank + 1) * e_local].contiguous(), None, None, dev)
+        ep = PeerExpertParallelMoE(E, mine, peers, max_tokens=64, topk=topk, hidden=hidden)
+        for T in (1, 5, 40, 5):
+            ids, tw = synth.make_routing(T, E, topk, seed=100 * T + rank)        # every rank its own batch
+            if T == 5:
+                ids[2, 1] = -1                                                    # a padded route
+            xg = torch.Generator(device=dev).manual_seed(1000 + 10 * T + rank)
+            x = torch.randn(T, hidden, generator=xg, device=dev).to(torch.bfloat16)
+            ids_d, tw_d = torch.from_numpy(ids).to(dev), torch.from_numpy(tw).to(dev)
+            want = whole(x, tw_d, ids_d)
+            got = ep(x, tw_d, ids_d)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), (str(mfmt), T, float((got.float() - want.float()).abs().max()))
 
 
 if __name__ == "__main__":

@@ -191,6 +191,51 @@ def test_moe_fused_bucket_equals_separate_bucket(dev, name):
     assert torch.equal(y_sep, y_fused)
 
 
+@pytest.mark.parametrize("T", [1, 7, 40])
+def test_moe_per_pair_table_kernel_matches_grouped_kernel(dev, T):
+    """Literal format: every routed pair as its own table GEMV (gate/up K = 2048: two K slices and
+    SwiGLU in the summing kernel; down K = 768: one ragged slice, stored straight from the kernel)
+    against the grouped MMA kernel on the same bits and against the loop-chain oracle, with a
+    padded route."""
+    from gridbook_b200 import kernels, synth
+    fmt = _fmt("lit")
+    E, hidden, inter, topk = 8, 2048, 768, 3
+    w13d, w2d = synth.make_moe(fmt, fmt, E, hidden, inter, seed=T)
+    ids, tw = synth.make_routing(T, E, topk, seed=T)
+    if T > 1:
+        ids[1, 0] = -1
+    x = synth.make_activations(T, hidden, seed=T)
+    w13, w2 = synth.to_device_weight(w13d, dev), synth.to_device_weight(w2d, dev)
+    xd = synth.bf16_tensor(x, dev)
+    idd = torch.from_numpy(ids).to(dev)
+    x_row = (torch.arange(T * topk, device=dev, dtype=torch.int32) // topk).contiguous()
+    _, offsets, order = kernels.moe_route(idd, E)
+    a_ref = kernels.moe_gemv(kernels.fp4_act_qdq(xd), w13, offsets, order, x_row=x_row, swiglu=True)
+    a = kernels.moe_gemv_pairs(xd, w13, idd, x_row=x_row, swiglu=True, act="fp4")
+    assert a is not None
+    live = (idd.reshape(-1) >= 0)
+    # SwiGLU rounds gate and up to bf16 first: a last-bit difference of the two summation orders in
+    # either one moves the product by a few steps, hence the wider elementwise gate here
+    assert_close_bf16(f32_of(a[live]), f32_of(a_ref[live]), "per-pair gate/up vs grouped", ulps=8.0)
+    y_ref = kernels.moe_gemv(kernels.fp4_act_qdq(a), w2, offsets, order)
+    y = kernels.moe_gemv_pairs(a, w2, idd, act="fp4")
+    assert_close_bf16(f32_of(y[live]), f32_of(y_ref[live]), "per-pair down vs grouped")
+    out = kernels.moe_combine(y, torch.from_numpy(tw).to(dev), T, topk, topk_ids=idd, E=E, round_weights=True)
+    keep = ids >= 0
+    ref = O.moe_loop_chain(x, np.where(keep, ids, 0), np.where(keep, tw, 0.0).astype(np.float32), w13d, w2d, E=E,
+                           hidden=hidden, inter=inter, fmt13=fmt.oracle_kwargs(), fmt2=fmt.oracle_kwargs(),
+                           scale_rule="recip")
+    got = f32_of(out)
+    rel = np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-9)
+    assert rel <= 1e-2, rel
+    # a format without the kernel is refused, not served some other way
+    k16 = _fmt("k16v2")
+    o13, _ = synth.make_moe(k16, k16, 4, 512, 256, seed=1)
+    assert kernels.moe_gemv_pairs(synth.bf16_tensor(synth.make_activations(2, 512, seed=1), dev),
+                                  synth.to_device_weight(o13, dev),
+                                  torch.zeros(2, dtype=torch.int32, device=dev), swiglu=True) is None
+
+
 @pytest.mark.parametrize("T", [1, 5, 16, 40])
 def test_moe_fp4_k16_matches_loop_chain(dev, T):
     fmt = _fmt("k16v2")
