@@ -267,7 +267,7 @@ class PeerExpertParallelMoE(torch.nn.Module):
                 kernels.moe_gemv(b2(a, rule), layer._cb_w2, offsets, order, peer_rows=rows)
         self.peers.barrier()
         back = self.peers.arena.tensor(self.back_off, (T * topk, H), torch.bfloat16)
-        # the loop chain multiplies by the bf16-rounded router weight (gridbook/moe.py:2407-2408)
-        pair_w = topk_weights.reshape(-1).to(torch.bfloat16).to(torch.float32)
-        out = kernels.moe_combine(back, pair_w, T, topk, topk_ids=ids, E=self.E)
+        # the loop chain multiplies by the bf16-rounded router weight (gridbook/moe.py:2407-2408):
+        # the combine rounds the raw weights itself
+        out = kernels.moe_combine(back, topk_weights, T, topk, topk_ids=ids, E=self.E, round_weights=True)
         return out.to(x.dtype).reshape(x.shape)
