@@ -85,11 +85,18 @@ struct TileWalker {
   const GemvParams& p;
   int next_local;   // dense: next row-tile index; MoE: next global tile index for this CTA
   int e, base;      // MoE: current expert and the global index of its first tile
+  int last = 0;     // MoE: one past this CTA's last tile
   const int* tile_base;   // MoE, shared memory: [E + 1] first global tile index of every expert
   const int* offs;        // MoE, shared memory: [E + 1] copy of the routing offsets
   __device__ TileWalker(const GemvParams& pp, const int* tb, const int* of) : p(pp), tile_base(tb), offs(of) {
     if constexpr (kMoE) {
-      next_local = blockIdx.x; e = 0; base = 0;
+      // A CTA takes a contiguous run of the global tile list: consecutive tiles are mostly row
+      // tiles of the same (expert, token pass), whose activation rows are then staged once.
+      const int total = tile_base[p.E];
+      const int run = (total + (int)gridDim.x - 1) / (int)gridDim.x;
+      next_local = (int)blockIdx.x * run;
+      last = min(total, next_local + run);
+      e = 0; base = 0;
     } else {
       next_local = blockIdx.x / p.ksplit;
     }
@@ -106,7 +113,7 @@ struct TileWalker {
       return true;
     } else {
       const int half = p.swiglu ? tile_rows / 2 : tile_rows;
-      if (next_local >= tile_base[p.E]) return false;
+      if (next_local >= last) return false;
       // the expert whose tile range holds next_local: the last e with tile_base[e] <= next_local
       // (experts without tokens have empty ranges and are skipped by the search)
       int lo = e, hi = p.E;
@@ -126,7 +133,7 @@ struct TileWalker {
         t.m0 = offs[e] + ch * p.m_chunk;
         t.mcount = min(p.m_chunk, cnt - ch * p.m_chunk);
         t.slice = 0;
-        next_local += gridDim.x;
+        next_local += 1;
         return true;
       }
       return false;
@@ -427,6 +434,7 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);             // [warps][kMaxStages]
   uint16_t* sub_tab = reinterpret_cast<uint16_t*>(smem + 512);        // 16 bf16 two-tier multipliers
+  int* xsrc_s = reinterpret_cast<int*>(smem + 576);                   // routed: source rows of the staged pass (<= 16)
   int* tile_base_s = reinterpret_cast<int*>(smem + 1280);             // routed: [E + 1] tile prefix, [E + 1] offsets
   int* offs_s = tile_base_s + (p.E + 1);
   uint8_t* lut = smem + 1280 + p.etab_bytes;
@@ -546,13 +554,20 @@ __global__ void __launch_bounds__(kLit ? 512 : 256, 1) gemv_kernel(const __grid_
       }
       if (restage_x) {
         const int vec_per_row = nsb_slice * 32;     // 16-byte vectors of this K slice
+        if constexpr (kMoE) {
+          // the pass's source rows first (two dependent global loads each), so that the copy
+          // loop below is one independent load per vector
+          if (tid < t.mcount) {
+            const int pair = p.order[t.m0 + tid];
+            xsrc_s[tid] = p.x_row ? p.x_row[pair] : pair;
+          }
+          __syncthreads();
+        }
+#pragma unroll 4
         for (int i = tid; i < t.mcount * vec_per_row; i += kThreads) {
           const int m = i / vec_per_row, v = i - m * vec_per_row;
           int64_t src_row = m;
-          if constexpr (kMoE) {
-            const int pair = p.order[t.m0 + m];
-            src_row = p.x_row ? p.x_row[pair] : pair;
-          }
+          if constexpr (kMoE) src_row = xsrc_s[m];
           uint4 val = *reinterpret_cast<const uint4*>(p.x + src_row * p.K + (int64_t)sb0 * 256 + v * 8);
           // fused bucket: a group of 16 is this lane's vector and its neighbour's (whole warps
           // enter the loop together: the vector count is a multiple of 32)
