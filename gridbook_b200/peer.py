@@ -138,6 +138,22 @@ class PeerGroup:
         nat.check(lib.gb_peer_barrier(ctypes.byref(self.native), nat.stream_ptr(self.device)), lib)
 
 
+def role_slices(partition_sizes, world: int):
+    """Per role of a fused module: (first local column, first global column of rank 0's slice,
+    slice width).  Rank s's slice of the role sits at local column ``lcol`` of its shard and at
+    global column ``gcol + s * width`` of the full output (an equal slice of every role per rank,
+    as :func:`gridbook_b200.parallel.shard_row_ranges` lays the shards out)."""
+    roles, lcol, gcol = [], 0, 0
+    for n in partition_sizes:
+        if n % world:
+            raise ValueError(f"role of {n} rows does not divide over {world} ranks")
+        per = n // world
+        roles.append((lcol, gcol, per))
+        lcol += per
+        gcol += n
+    return roles
+
+
 class PeerShardedCBLinear(torch.nn.Module):
     """Column-parallel linear whose all-gather is one peer-store launch.  ``local`` maps x[M, K]
     to this rank's [M, N/world] columns, laid out role by role (an equal slice of every role,
@@ -155,13 +171,7 @@ class PeerShardedCBLinear(torch.nn.Module):
         self.n_local = self.N // world
         self.max_rows = max_rows
         self.out_off = peers.arena.carve(max_rows * self.N * 2)
-        # (local column, global column of rank 0's slice, width) of every role
-        self.roles, lcol, gcol = [], 0, 0
-        for n in self.partition_sizes:
-            per = n // world
-            self.roles.append((lcol, gcol, per))
-            lcol += per
-            gcol += n
+        self.roles = role_slices(self.partition_sizes, world)
         if len(self.roles) > 4:
             raise ValueError("at most four roles per fused module")
 

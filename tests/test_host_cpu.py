@@ -208,3 +208,20 @@ def test_methods_fail_closed_before_load():
         lin.method.apply(lin, torch.zeros(1, 512), bias=torch.zeros(16))
     with pytest.raises(NativeKernelUnavailableError, match="CUDA device"):
         lin.method.process_weights_after_loading(lin)
+
+
+def test_peer_role_slices_agree_with_the_gather_permutation():
+    """The peer all-gather writes rank s's slice of every role at gcol + s * width; that must be
+    the column order the NCCL path reaches through its permutation."""
+    import torch
+    from gridbook_b200 import parallel, peer
+    for parts, world in (([6144], 2), ([1024, 1024], 4), ([512, 256, 256], 2), ([17408, 17408], 8)):
+        roles = peer.role_slices(parts, world)
+        n_local = sum(p // world for p in parts)
+        full = torch.full((sum(parts),), -1, dtype=torch.int64)
+        for s in range(world):
+            for lcol, gcol, w in roles:
+                full[gcol + s * w: gcol + (s + 1) * w] = s * n_local + lcol + torch.arange(w)
+        assert torch.equal(full, parallel.gather_permutation(parts, world))
+    with pytest.raises(ValueError):
+        peer.role_slices([10], 4)
