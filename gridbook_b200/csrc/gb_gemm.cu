@@ -2,12 +2,14 @@
 // operands K-major, bf16 x bf16 (kind::f16) or E4M3 x E4M3 (kind::f8f6f4), fp32 accumulators
 // in tensor memory, scaled bf16 epilogue.
 //
-// One CTA computes one 128 x 256 output tile.  Warp 4 (one thread) streams 128-byte-wide
-// K slabs of A and B into a shared-memory ring with tiled TMA loads (128-byte swizzle);
-// warp 5 (one thread) issues tcgen05.mma on shared-memory matrix descriptors and releases
-// ring stages with tcgen05.commit; warps 0..3 read the accumulator out of tensor memory
-// (tcgen05.ld, one 32-lane quarter each), apply the row / column / global scales and store
-// bf16.  B is the decoded weight tile the expanders write (gb_expand_fp8 /
+// Persistent CTAs (one per SM) walk the 128 x 256 output tiles, M fastest.  Warp 4 (one
+// thread) streams 128-byte-wide K slabs of A and B into a shared-memory ring with tiled TMA
+// loads (128-byte swizzle); warp 5 (one thread) issues tcgen05.mma on shared-memory matrix
+// descriptors and releases ring stages with tcgen05.commit; warps 0..3 read the accumulator
+// out of tensor memory (tcgen05.ld, one 32-lane quarter each), apply the row / column /
+// global scales and store bf16.  Tensor memory holds TWO accumulators (512 columns): while
+// the epilogue warps drain one, the MMAs of the next tile already fill the other, and the
+// TMA ring never drains between tiles.  B is the decoded weight tile the expanders write (gb_expand_fp8 /
 // gb_expand_fp4_bf16); A is the bucketed activation matrix.
 #include "gb_common.cuh"
 
@@ -18,15 +20,16 @@ namespace {
 
 constexpr int kBM = 128, kBN = 256;
 constexpr int kSlabBytes = 128;                    // K bytes per row per stage (one swizzle span)
-constexpr int kStageBytes = (kBM + kBN) * kSlabBytes;   // 32 KiB
+constexpr int kStageBytes = (kBM + kBN) * kSlabBytes;   // 48 KiB
 constexpr int kStages = 4;
-constexpr int kTmemCols = 256;
+constexpr int kTmemCols = 512;                     // two 128 x 256 fp32 accumulators
 constexpr int kGemmThreads = 192;
 constexpr int kGemmSmem = kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
 
 struct GemmParams {
   int64_t M, N, K;
   int k_tiles;
+  int m_tiles, n_tiles;      // output tiles along M and N
   int elem_bytes;            // 2 (bf16) or 1 (e4m3)
   uint32_t idesc;
   const float* a_scale;      // [M] or null
@@ -90,26 +93,28 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint8_t* ring = smem;                                                   // kStages x (A slab | B slab)
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
   uint64_t* empty_bar = full_bar + kStages;
-  uint64_t* accum_bar = empty_bar + kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  uint64_t* acc_full = empty_bar + kStages;          // [2] accumulator complete (one commit)
+  uint64_t* acc_empty = acc_full + 2;                // [2] accumulator drained (four epilogue warps)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // M tiles vary fastest, so the CTAs resident together share a few B (weight) tiles and
-  // sweep A, which fits L2: the decoded weight tile is read from HBM once.
-  const int m0 = blockIdx.x * kBM, n0 = blockIdx.y * kBN;
   const bool fp8 = p.elem_bytes == 1;
+  const int total_tiles = p.m_tiles * p.n_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       gb_mbar_init(&full_bar[s], 1);
       gb_mbar_init(&empty_bar[s], 1);
     }
-    gb_mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      gb_mbar_init(&acc_full[b], 1);
+      gb_mbar_init(&acc_empty[b], 4);
+    }
     *abort_flag = 0;
     gb_fence_barrier_init();
   }
-  if (warp == 5) {   // tensor memory for the 128 x 256 fp32 accumulator
+  if (warp == 5) {   // tensor memory for two 128 x 256 fp32 accumulators
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  ::"r"(gb_smem_u32(tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -119,76 +124,102 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
+  // Every role walks the same tile sequence: tile = blockIdx.x, + gridDim.x, ...; M tiles vary
+  // fastest, so the CTAs working at the same time share a few B (weight) tiles and sweep A,
+  // which fits L2: the decoded weight tile is read from HBM once.
   if (warp == 4) {
     // ------------------------------- TMA producer -------------------------------
     if (lane == 0) {
       const int slab_elems = kSlabBytes / p.elem_bytes;
-      for (int kt = 0; kt < p.k_tiles; ++kt) {
-        const int s = kt % kStages;
-        wait_or_abort(&empty_bar[s], ((kt / kStages) & 1) ^ 1, abort_flag, p.status, 11);
-        gb_mbar_expect_tx(&full_bar[s], kStageBytes);
-        uint8_t* a_dst = ring + (size_t)s * kStageBytes;
-        tma_load_2d(a_dst, &map_a, kt * slab_elems, m0, &full_bar[s]);
-        tma_load_2d(a_dst + kBM * kSlabBytes, &map_b, kt * slab_elems, n0, &full_bar[s]);
+      int kk = 0;                                        // K slabs issued so far, over all tiles
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        const int m0 = (tile % p.m_tiles) * kBM, n0 = (tile / p.m_tiles) * kBN;
+        for (int kt = 0; kt < p.k_tiles; ++kt, ++kk) {
+          const int s = kk % kStages;
+          wait_or_abort(&empty_bar[s], ((kk / kStages) & 1) ^ 1, abort_flag, p.status, 11);
+          gb_mbar_expect_tx(&full_bar[s], kStageBytes);
+          uint8_t* a_dst = ring + (size_t)s * kStageBytes;
+          tma_load_2d(a_dst, &map_a, kt * slab_elems, m0, &full_bar[s]);
+          tma_load_2d(a_dst + kBM * kSlabBytes, &map_b, kt * slab_elems, n0, &full_bar[s]);
+        }
       }
     }
   } else if (warp == 5) {
     // ------------------------------- MMA issuer ---------------------------------
     if (lane == 0) {
-      for (int kt = 0; kt < p.k_tiles; ++kt) {
-        const int s = kt % kStages;
-        wait_or_abort(&full_bar[s], (kt / kStages) & 1, abort_flag, p.status, 12);
+      int kk = 0, it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        // the epilogue must have drained this accumulator (its use two tiles ago)
+        wait_or_abort(&acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag, p.status, 14);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = gb_smem_u32(ring + (size_t)s * kStageBytes);
-        const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + kBM * kSlabBytes);
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kBN);
+        for (int kt = 0; kt < p.k_tiles; ++kt, ++kk) {
+          const int s = kk % kStages;
+          wait_or_abort(&full_bar[s], (kk / kStages) & 1, abort_flag, p.status, 12);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = gb_smem_u32(ring + (size_t)s * kStageBytes);
+          const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + kBM * kSlabBytes);
 #pragma unroll
-        for (int k = 0; k < kSlabBytes / 32; ++k)       // 32 bytes of K per instruction
-          umma(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), p.idesc, kt > 0 || k > 0, fp8);
-        umma_commit(&empty_bar[s]);                      // stage free once these MMAs have read it
+          for (int k = 0; k < kSlabBytes / 32; ++k)       // 32 bytes of K per instruction
+            umma(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), p.idesc, kt > 0 || k > 0, fp8);
+          umma_commit(&empty_bar[s]);                      // stage free once these MMAs have read it
+        }
+        umma_commit(&acc_full[buf]);                       // accumulator complete
       }
-      umma_commit(accum_bar);                            // accumulator complete
     }
   } else {
     // ------------------------------- epilogue -----------------------------------
-    wait_or_abort(accum_bar, 0, abort_flag, p.status, 13);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int64_t row = (int64_t)m0 + warp * 32 + lane;
-    const float rs = (p.a_scale && row < p.M ? p.a_scale[row] : 1.0f) * p.global_scale;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const int m0 = (tile % p.m_tiles) * kBM, n0 = (tile / p.m_tiles) * kBN;
+      wait_or_abort(&acc_full[buf], (it >> 1) & 1, abort_flag, p.status, 13);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int64_t row = (int64_t)m0 + warp * 32 + lane;
+      const float rs = (p.a_scale && row < p.M ? p.a_scale[row] : 1.0f) * p.global_scale;
 #pragma unroll 1
-    for (int c0 = 0; c0 < kBN; c0 += 32) {
-      uint32_t v[32];
-      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
-      asm volatile(
-          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-          "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-          "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-          : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-            "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-            "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-            "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-          : "r"(taddr));
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (row < p.M) {
-        uint16_t* out = p.D + row * p.N + n0 + c0;
-        const int64_t ncol = p.N - (n0 + c0);
-        if (ncol >= 32 && (p.N % 8) == 0) {
+      for (int c0 = 0; c0 < kBN; c0 += 32) {
+        uint32_t v[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * kBN + c0);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+            "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+              "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+              "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+              "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (c0 + 32 == kBN) {
+          // every column of this accumulator is in registers: hand it back before the stores
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) gb_mbar_arrive(&acc_empty[buf]);
+        }
+        if (row < p.M) {
+          uint16_t* out = p.D + row * p.N + n0 + c0;
+          const int64_t ncol = p.N - (n0 + c0);
+          if (ncol >= 32 && (p.N % 8) == 0) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint32_t w[4];
+            for (int q = 0; q < 4; ++q) {
+              uint32_t w[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int c = q * 8 + j * 2;
-              const float s0 = p.b_scale ? p.b_scale[n0 + c0 + c] : 1.0f;
-              const float s1 = p.b_scale ? p.b_scale[n0 + c0 + c + 1] : 1.0f;
-              w[j] = gb_f32_to_bf16_bits(__uint_as_float(v[c]) * rs * s0) |
-                     (gb_f32_to_bf16_bits(__uint_as_float(v[c + 1]) * rs * s1) << 16);
+              for (int j = 0; j < 4; ++j) {
+                const int c = q * 8 + j * 2;
+                const float s0 = p.b_scale ? p.b_scale[n0 + c0 + c] : 1.0f;
+                const float s1 = p.b_scale ? p.b_scale[n0 + c0 + c + 1] : 1.0f;
+                w[j] = gb_f32_to_bf16_bits(__uint_as_float(v[c]) * rs * s0) |
+                       (gb_f32_to_bf16_bits(__uint_as_float(v[c + 1]) * rs * s1) << 16);
+              }
+              *reinterpret_cast<uint4*>(out + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            *reinterpret_cast<uint4*>(out + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        } else {
-          for (int c = 0; c < 32 && c < ncol; ++c) {
-            const float s0 = p.b_scale ? p.b_scale[n0 + c0 + c] : 1.0f;
-            out[c] = (uint16_t)gb_f32_to_bf16_bits(__uint_as_float(v[c]) * rs * s0);
+          } else {
+            for (int c = 0; c < 32 && c < ncol; ++c) {
+              const float s0 = p.b_scale ? p.b_scale[n0 + c0 + c] : 1.0f;
+              out[c] = (uint16_t)gb_f32_to_bf16_bits(__uint_as_float(v[c]) * rs * s0);
+            }
           }
         }
       }
@@ -325,6 +356,8 @@ int gb_gemm_tn(const void* A, const void* B, void* D, int64_t M, int64_t N, int6
   GemmParams p = {};
   p.M = M; p.N = N; p.K = K;
   p.k_tiles = (int)(K * eb / kSlabBytes);
+  p.m_tiles = (int)((M + kBM - 1) / kBM);
+  p.n_tiles = (int)((N + kBN - 1) / kBN);
   p.elem_bytes = eb;
   // instruction descriptor: fp32 accumulate, A/B format, both K-major, N >> 3, M >> 4
   p.idesc = (1u << 4) | ((kind == GB_GEMM_BF16 ? 1u : 0u) << 7) | ((kind == GB_GEMM_BF16 ? 1u : 0u) << 10) |
@@ -333,7 +366,10 @@ int gb_gemm_tn(const void* A, const void* B, void* D, int64_t M, int64_t N, int6
   p.global_scale = global_scale == 0.0f ? 1.0f : global_scale;
   p.D = (uint16_t*)D;
   p.status = gb_status_word();
-  dim3 grid((unsigned)((M + kBM - 1) / kBM), (unsigned)((N + kBN - 1) / kBN));
+  const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
+  GB_REQUIRE(tiles < (1ll << 31), "too many output tiles");
+  const int sms = gb_sm_count();
+  dim3 grid((unsigned)(tiles < sms ? tiles : sms));          // persistent: one CTA per SM
   gb_count_launch();
   gemm_tn_kernel<<<grid, kGemmThreads, kGemmSmem, (cudaStream_t)stream>>>(map_a, map_b, p);
   GB_LAUNCH_OK("gemm_tn_kernel");
