@@ -234,7 +234,9 @@ class PeerExpertParallelMoE(torch.nn.Module):
         from .moe import FUSED_BUCKET_MAX_PAIRS, PAIR_KERNEL_MAX_PAIRS
         pairs_all = world * T * topk
         # small batches of the literal format: every pair is its own table GEMV (bucket fused)
-        per_pair = pairs_all <= PAIR_KERNEL_MAX_PAIRS and self._pairs_ok
+        # (pairs of other ranks' experts cost a CTA that leaves at once; bound those too)
+        per_pair = (self._pairs_ok and pairs_all // world <= PAIR_KERNEL_MAX_PAIRS
+                    and pairs_all <= 4 * PAIR_KERNEL_MAX_PAIRS)
         x2 = x.reshape(T, H).to(torch.bfloat16).contiguous()
         # the bucket is per token, so it can run before the rows travel (the per-pair kernel
         # applies it itself)
