@@ -271,6 +271,42 @@ def run_gpu(args):
     barrier()
     ms_kernel = k0.elapsed_time(k1)
     used_graph = graph is not None
+    # ---- the other decode batch sizes of the configuration (same stack, through the linear method) ----
+    dense_m = {}
+    if world == 1 and not args.no_msweep:
+        for m_other in (4, 16):
+            if m_other == M:
+                continue
+            xs = [torch.randn(m_other, K, generator=gen, device=device).to(torch.bfloat16) for _, _, K in PROJECTIONS]
+
+            def m_step():
+                for row in stack:
+                    for lin, x in zip(row, xs):
+                        lin(x)
+
+            m_step()
+            torch.cuda.synchronize()
+            runner = m_step
+            try:
+                mg = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(mg):
+                    m_step()
+                runner = mg.replay
+            except Exception:
+                torch.cuda.synchronize()
+            for _ in range(3):
+                runner()
+            torch.cuda.synchronize()
+            m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            m0.record()
+            for _ in range(5):
+                runner()
+            m1.record()
+            torch.cuda.synchronize()
+            ms_m = m0.elapsed_time(m1) / 5
+            dense_m[str(m_other)] = {"gb_s": round(bytes_per_step_local / (ms_m * 1e-3) / 1e9, 1),
+                                     "ms_per_step": round(ms_m, 3)}
+            mg = None
     moe = None if args.no_moe else bench_moe(args, device, world, rank, peers)
     prefill = bench_prefill(args, device) if (world == 1 and not args.no_prefill) else None
     status = _native.device_status(local_rank)
@@ -336,6 +372,7 @@ def run_gpu(args):
         "gpu_launches": int(args.steps * launches_per_step),
         "clocks": clocks.summary(),
         "device_status": status,
+        "dense_other_m": dense_m or None,
         "moe": moe,
         "prefill": prefill,
     }
@@ -578,6 +615,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-moe", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-msweep", action="store_true", help="skip the M = 4 / 16 legs of the dense stack")
     ap.add_argument("--only", default=None, choices=[n for n, _, _ in PROJECTIONS],
                     help="restrict the stack to one projection (small profiling captures)")
     args = ap.parse_args()

@@ -68,6 +68,9 @@ int gb_tensor_map_bytes_2d(void* map_out, const void* base, uint64_t inner_bytes
                            uint64_t pitch_bytes, uint32_t box_bytes, uint32_t box_rows);
 // M = 1 literal-format linear by per-column inner-product tables (gb_gemv_dot.cu); GB_EUNSUPPORTED when
 // the shape or layout is not its own, and the caller falls back to the MMA kernel.
+int gb_gemv_dot_rows(const void* x, int64_t M, const gb_weight* w, int act, int scale_rule, void* y, void* workspace,
+                     int64_t workspace_bytes, void* stream);
+int64_t gb_gemv_dot_rows_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int gb_gemv_dot(const void* x, const gb_weight* w, int act, int scale_rule, void* y, void* workspace,
                 int64_t workspace_bytes, void* stream);
 int64_t gb_gemv_dot_workspace_bytes(int64_t N, int64_t K);

@@ -794,6 +794,16 @@ bool literal_aligned(const GemvParams& p) {
          p.expert_stride % 16 == 0;
 }
 
+constexpr int kDotRowsMax = 8;      // most activation rows ever served by per-row table GEMVs
+int dot_rows_max() {                // rows up to which they are actually used (GRIDBOOK_B200_DOT_ROWS overrides)
+  static const int v = [] {
+    const char* e = getenv("GRIDBOOK_B200_DOT_ROWS");
+    int n = e ? atoi(e) : 4;
+    return n < 1 ? 1 : (n > kDotRowsMax ? kDotRowsMax : n);
+  }();
+  return v;
+}
+
 int classify(const gb_format& f, int* out, bool* wide) {
   *wide = f.k_bits > 32;
   if (f.grid == GB_GRID_FP4) {
@@ -895,7 +905,9 @@ extern "C" {
 int64_t gb_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   const int64_t mma_path = ((M * K * 2 + 255) & ~255ll) + M * N * (int64_t)sizeof(float);
   const int64_t dot_path = gb_gemv_dot_workspace_bytes(N, K);     // M = 1, literal format
-  return mma_path > dot_path ? mma_path : dot_path;
+  const int64_t rows_path = gb_gemv_dot_rows_workspace_bytes(M < dot_rows_max() ? M : dot_rows_max(), N, K);   // rows 2..dot_rows_max()
+  int64_t need = mma_path > dot_path ? mma_path : dot_path;
+  return need > rows_path ? need : rows_path;
 }
 
 int gb_gemv(const void* x, int64_t M, const gb_weight* w, int act, int scale_rule, void* y,
@@ -911,6 +923,10 @@ int gb_gemv(const void* x, int64_t M, const gb_weight* w, int act, int scale_rul
   if (M == 1) {
     // one activation row of the literal format: inner-product tables instead of per-weight expansion
     rc = gb_gemv_dot(x, w, act, scale_rule, y, workspace, workspace_bytes, stream_);
+    if (rc != GB_EUNSUPPORTED) return rc;
+  } else if (M <= dot_rows_max()) {
+    // a few rows of the literal format: one table GEMV per row beats expanding every weight
+    rc = gb_gemv_dot_rows(x, M, w, act, scale_rule, y, workspace, workspace_bytes, stream_);
     if (rc != GB_EUNSUPPORTED) return rc;
   }
   int fmt;

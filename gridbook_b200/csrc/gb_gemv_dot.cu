@@ -169,7 +169,7 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
   const uint16_t* xsrc = p.x;
   if constexpr (kPairs) {
     gb_pdl_wait();                       // the routing and the activations come from earlier kernels
-    const int e = p.pair_expert[pair] - p.expert_base;
+    const int e = p.pair_expert ? p.pair_expert[pair] - p.expert_base : 0;
     if (e < 0 || e >= p.E) return;       // padded route, or an expert another rank holds: whole CTA leaves
     tma_row0 = (int64_t)e * p.N + row_begin;
     xsrc = p.x + (int64_t)(p.x_row ? p.x_row[pair] : pair) * ((int64_t)p.n_sb * 256);
@@ -336,7 +336,7 @@ __global__ void dot_pairs_finalize_kernel(const __grid_constant__ DotParams p, i
   if (i >= (int64_t)p.P * width) return;
   const int pair = (int)(i / width);
   const int64_t j = i - (int64_t)pair * width;
-  const int e = p.pair_expert[pair] - p.expert_base;
+  const int e = p.pair_expert ? p.pair_expert[pair] - p.expert_base : 0;
   if (e < 0 || e >= p.E) return;
   float a = 0.f, b = 0.f;
   for (int s = 0; s < p.n_slices; ++s) {
@@ -416,21 +416,49 @@ extern "C" int64_t gb_moe_gemv_pairs_workspace_bytes(int64_t P, int64_t rows, in
   return n_slices * P * rows * (int64_t)sizeof(float);
 }
 
+static int dot_pairs_launch(const void* x, const int32_t* x_row, const gb_weight* w, int64_t expert_stride,
+                            int64_t E, int64_t expert_base, const int32_t* pair_expert, int64_t P,
+                            int64_t pairs_expected, int swiglu, int act, int scale_rule, void* y,
+                            const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes, void* stream_);
+
 extern "C" int gb_moe_gemv_pairs(const void* x, const int32_t* x_row, const gb_weight* w, int64_t expert_stride,
                                  int64_t E, int64_t expert_base, const int32_t* pair_expert, int64_t P,
                                  int64_t pairs_expected, int swiglu, int act, int scale_rule, void* y,
                                  const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes, void* stream_) {
+  GB_REQUIRE(pair_expert != nullptr, "null pair_expert");
+  return dot_pairs_launch(x, x_row, w, expert_stride, E, expert_base, pair_expert, P, pairs_expected, swiglu, act,
+                          scale_rule, y, y_rows, workspace, workspace_bytes, stream_);
+}
+
+// A few activation rows against ONE matrix: row m is "pair" m of a one-expert stack, so the
+// weights stream once per row (the second and later passes mostly out of L2).  Worth it while
+// that beats expanding every weight for the MMA kernel; the caller decides up to which M.
+int gb_gemv_dot_rows(const void* x, int64_t M, const gb_weight* w, int act, int scale_rule, void* y, void* workspace,
+                     int64_t workspace_bytes, void* stream_) {
+  if (w->rows < 256) return GB_EUNSUPPORTED;
+  return dot_pairs_launch(x, nullptr, w, w->rows * w->row_stride, 1, 0, nullptr, M, 0, 0, act, scale_rule, y, nullptr,
+                          workspace, workspace_bytes, stream_);
+}
+
+int64_t gb_gemv_dot_rows_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  return gb_moe_gemv_pairs_workspace_bytes(M, N, K);
+}
+
+static int dot_pairs_launch(const void* x, const int32_t* x_row, const gb_weight* w, int64_t expert_stride,
+                            int64_t E, int64_t expert_base, const int32_t* pair_expert, int64_t P,
+                            int64_t pairs_expected, int swiglu, int act, int scale_rule, void* y,
+                            const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   int rc = gb_check_weight(w);
   if (rc != GB_OK) return rc;
-  GB_REQUIRE(x && pair_expert && (y || y_rows), "null pointer argument");
+  GB_REQUIRE(x && (y || y_rows), "null pointer argument");
   GB_REQUIRE(E >= 1 && P >= 0 && P < (1 << 24), "bad E=%lld P=%lld", (long long)E, (long long)P);
   GB_REQUIRE(!swiglu || w->rows % 2 == 0, "swiglu needs an even row count");
   const gb_format& f = w->fmt;
   const bool mine = f.grid == GB_GRID_FP4 && f.mode == GB_MODE_FULL && f.k_bits == 8 && f.scale_coding == GB_SCALE_V1 &&
                     w->cb_row_offset == nullptr && ((uintptr_t)w->qw & 15u) == 0 && w->row_stride % 16 == 0 &&
                     expert_stride == w->rows * w->row_stride && E * w->rows < (1ll << 31) &&
-                    (act == GB_ACT_NONE || act == GB_ACT_FP4_GROUP16) && w->K >= 256 && w->K <= 256 * 64 &&
+                    (act == GB_ACT_NONE || act == GB_ACT_FP4_GROUP16) && w->K >= 256 &&
                     ((uintptr_t)x & 15u) == 0 && ((uintptr_t)w->codebook & 3u) == 0;
   if (!mine) return GB_EUNSUPPORTED;
   if (P == 0) return GB_OK;
