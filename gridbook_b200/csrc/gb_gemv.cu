@@ -853,14 +853,16 @@ int plan(GemvParams& p, int m_rows, bool moe, int sms, size_t* smem_bytes) {
   // Ring geometry.  A stage holds one K chunk of a warp's eight rows: per row the chunk's
   // bytes plus the alignment head and a tail the word-wise extraction may touch, on a pitch
   // that is 16 mod 32 so the eight rows start in different banks.  The chunk is the largest
-  // that leaves every warp kMaxStages stages.
+  // that leaves every warp two stages (up to kMaxStages when there is room).
   p.etab_bytes = moe ? (int)((2 * (p.E + 1) * sizeof(int) + 127) & ~127ull) : 0;
   const int64_t fixed = 1280 + p.etab_bytes + p.lut_bytes + (int64_t)p.x_rows * p.x_pitch;
   const int64_t per_warp = (kSmemBig - fixed) / p.warps;
   auto pitch_of = [&](int nsb) { return (int)((((int64_t)nsb * p.fmt.type_size + 15 + 16 + 31) & ~31ll) + 16); };
   auto stage_of = [&](int nsb) { return (8 * pitch_of(nsb) + 127) & ~127; };
   int chunk = p.sb_per_slice;
-  while (chunk > 1 && (int64_t)kMaxStages * stage_of(chunk) > per_warp) --chunk;
+  // Two stages are enough to keep a copy in flight while a stage is consumed; beyond that a
+  // bigger chunk (fewer steps, each with its walk / issue / wait overhead) is worth more than depth.
+  while (chunk > 1 && (int64_t)2 * stage_of(chunk) > per_warp) --chunk;
   int stages = (int)(per_warp / stage_of(chunk));
   if (stages < 2)
     return gb_fail(GB_EUNSUPPORTED, "a one-superblock stage of %d bytes leaves no room for a two-stage ring "
