@@ -325,6 +325,90 @@ __global__ void dot_finalize_kernel(const float* __restrict__ ws, int n_slices, 
   y[n] = (uint16_t)gb_f32_to_bf16_bits(acc * global_scale);
 }
 
+// ---- column-parallel linear: sum the K slices and all-gather the shard in the same launch ----
+// Thread i finishes outputs 2i, 2i+1 of this rank's shard, stores them at their place in this
+// rank's full output row, sends the pair as one 8-byte {word, exchange number} store into every
+// peer's staging slot and then collects the peers' words the same way (see gb_peer.cu for the
+// flag-in-data protocol: two slot halves by parity, bounded polling, status 3 on a timeout).
+struct GatherParams {
+  const float* ws;
+  int n_slices;
+  int64_t n_local;                 // columns of this rank's shard (even)
+  float global_scale;
+  uint16_t* y_full;                // this rank's full output row [N]
+  int n_roles;
+  int lcol[4], gcol0[4], width[4]; // shard column, global column of rank 0's slice, slice width (all even)
+  uint2* ll[GB_PEER_MAX];
+  uint32_t* flags;                 // own flag block: [18] exchange number, [19] CTA counter
+  int64_t capacity;
+  int rank, world;
+  int* status;
+};
+
+__global__ void __launch_bounds__(256) dot_finalize_allgather_kernel(const __grid_constant__ GatherParams p) {
+  __shared__ uint32_t s_epoch;
+  gb_pdl_launch_dependents();
+  gb_pdl_wait();
+  if (threadIdx.x == 0) s_epoch = *reinterpret_cast<volatile uint32_t*>(p.flags + 18) + 1u;
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const int64_t half = (int64_t)(epoch & 1u) * p.world * p.capacity;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  bool late = false;
+  if (2 * i < p.n_local) {
+    const int64_t n = 2 * i;
+    float a0 = 0.f, a1 = 0.f;
+    for (int s = 0; s < p.n_slices; ++s) {
+      const float2 v = *reinterpret_cast<const float2*>(p.ws + (int64_t)s * p.n_local + n);
+      a0 += v.x;
+      a1 += v.y;
+    }
+    const uint32_t word = gb_f32_to_bf16_bits(a0 * p.global_scale) | (gb_f32_to_bf16_bits(a1 * p.global_scale) << 16);
+    int r = 0;
+    while (r + 1 < p.n_roles && n >= p.lcol[r + 1]) ++r;
+    const int64_t off = n - p.lcol[r];                         // column inside the role's slice
+    uint32_t* out32 = reinterpret_cast<uint32_t*>(p.y_full);
+    out32[(p.gcol0[r] + (int64_t)p.rank * p.width[r] + off) >> 1] = word;
+#pragma unroll
+    for (int d = 0; d < GB_PEER_MAX; ++d)
+      if (d < p.world && d != p.rank) {
+        uint2* slot = p.ll[d] + half + (int64_t)p.rank * p.capacity + i;
+        asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(slot), "r"(word), "r"(epoch) : "memory");
+      }
+    const uint2* slot0 = p.ll[p.rank] + half + i;
+    uint2 v[GB_PEER_MAX];
+#pragma unroll
+    for (int src = 0; src < GB_PEER_MAX; ++src)
+      if (src < p.world && src != p.rank)
+        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];"
+                     : "=r"(v[src].x), "=r"(v[src].y) : "l"(slot0 + (int64_t)src * p.capacity) : "memory");
+#pragma unroll
+    for (int src = 0; src < GB_PEER_MAX; ++src) {
+      if (src >= p.world || src == p.rank) continue;
+      uint64_t t0 = 0;
+      for (uint32_t spin = 0; v[src].y != epoch && !late; ++spin) {
+        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];"
+                     : "=r"(v[src].x), "=r"(v[src].y) : "l"(slot0 + (int64_t)src * p.capacity) : "memory");
+        if ((spin & 63u) == 63u) {
+          const uint64_t now = gb_globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > 2000000000ull) late = true;
+        }
+      }
+      out32[(p.gcol0[r] + (int64_t)src * p.width[r] + off) >> 1] = v[src].x;
+    }
+  }
+  if (late) atomicExch(p.status, 3);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned old = atomicAdd(p.flags + 19, 1u);
+    if (old == gridDim.x - 1) {       // every CTA has read the exchange number by now
+      p.flags[19] = 0u;
+      p.flags[18] = epoch;
+    }
+  }
+}
+
 // Pair mode: adds the K slices of every routed pair's rows, applies the global scale and, for
 // the fused gate/up projection, SwiGLU with the bf16 roundings of F.silu(gate) * up
 // (gridbook/native_cutlass.py:129-155), then rounds once.
@@ -367,9 +451,9 @@ int64_t gb_gemv_dot_workspace_bytes(int64_t N, int64_t K) {
   return n_slices * N * (int64_t)sizeof(float);
 }
 
-int gb_gemv_dot(const void* x, const gb_weight* w, int act, int scale_rule, void* y, void* workspace,
-                int64_t workspace_bytes, void* stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
+// Launches gemv_dot_kernel<false> for one activation row; the partial sums land in `workspace`.
+static int dot_launch(const void* x, const gb_weight* w, int act, int scale_rule, void* workspace,
+                      int64_t workspace_bytes, cudaStream_t stream, DotParams* out) {
   const gb_format& f = w->fmt;
   const bool mine = f.grid == GB_GRID_FP4 && f.mode == GB_MODE_FULL && f.k_bits == 8 && f.scale_coding == GB_SCALE_V1 &&
                     w->cb_row_offset == nullptr && ((uintptr_t)w->qw & 15u) == 0 && w->row_stride % 16 == 0 &&
@@ -400,9 +484,66 @@ int gb_gemv_dot(const void* x, const gb_weight* w, int act, int scale_rule, void
                                   kRowBytes, kStageRows);
   if (rc != GB_OK) return rc;
   GB_CUDA_OK(gb_launch(gemv_dot_kernel<false>, dim3(p.n_slices * p.n_groups), dim3(kDotThreads), kDotSmem, stream, map, p));
+  *out = p;
+  return GB_OK;
+}
+
+int gb_gemv_dot(const void* x, const gb_weight* w, int act, int scale_rule, void* y, void* workspace,
+                int64_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  DotParams p;
+  int rc = dot_launch(x, w, act, scale_rule, workspace, workspace_bytes, stream, &p);
+  if (rc != GB_OK) return rc;
   const float gs = w->global_scale == 0.0f ? 1.0f : w->global_scale;
   GB_CUDA_OK(gb_launch(dot_finalize_kernel, dim3((unsigned)((w->rows + 255) / 256)), dim3(256), 0, stream,
                        (const float*)p.ws, p.n_slices, (int64_t)w->rows, gs, (uint16_t*)y));
+  return GB_OK;
+}
+
+// One activation row of a column-parallel linear: this rank's shard through the table kernel,
+// then ONE launch that adds the K slices, rounds, and exchanges the shards between the ranks.
+extern "C" int gb_gemv_allgather(const void* x, const gb_weight* w, int act, int scale_rule,
+                                 const gb_peer_group* g, void* const* ll, int64_t ll_bytes,
+                                 const gb_gather_layout* layout, void* y_full, void* workspace,
+                                 int64_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int rc = gb_check_weight(w);
+  if (rc != GB_OK) return rc;
+  GB_REQUIRE(x && g && ll && layout && y_full, "null pointer argument");
+  GB_REQUIRE(g->world >= 1 && g->world <= GB_PEER_MAX && g->rank >= 0 && g->rank < g->world, "bad peer group");
+  GB_REQUIRE(layout->n_roles >= 1 && layout->n_roles <= 4, "1..4 roles, got %d", layout->n_roles);
+  GatherParams q = {};
+  int64_t cols = 0;
+  for (int r = 0; r < layout->n_roles; ++r) {
+    GB_REQUIRE(layout->width[r] > 0 && layout->width[r] % 2 == 0 && layout->gcol0[r] % 2 == 0 && layout->lcol[r] == cols,
+               "role %d: slices must be even, contiguous in the shard and start on even columns", r);
+    q.lcol[r] = (int)layout->lcol[r];
+    q.gcol0[r] = (int)layout->gcol0[r];
+    q.width[r] = (int)layout->width[r];
+    cols += layout->width[r];
+  }
+  GB_REQUIRE(cols == w->rows, "the roles cover %lld columns, the shard has %lld rows", (long long)cols, (long long)w->rows);
+  GB_REQUIRE(((uintptr_t)y_full & 3u) == 0, "output must be 4-byte aligned");
+  q.capacity = ll_bytes / (2 * (int64_t)g->world * 8);
+  if (cols / 2 > q.capacity) return GB_EUNSUPPORTED;      // staging buffer too small: take the two-launch route
+  for (int r = 0; r < g->world; ++r) {
+    GB_REQUIRE(ll[r] != nullptr && g->flags[r] != nullptr, "peer buffers of rank %d missing", r);
+    q.ll[r] = (uint2*)ll[r];
+  }
+  DotParams p;
+  rc = dot_launch(x, w, act, scale_rule, workspace, workspace_bytes, stream, &p);
+  if (rc != GB_OK) return rc;           // GB_EUNSUPPORTED: the caller runs gb_gemv + gb_peer_allgather_ll
+  q.ws = p.ws;
+  q.n_slices = p.n_slices;
+  q.n_local = w->rows;
+  q.global_scale = w->global_scale == 0.0f ? 1.0f : w->global_scale;
+  q.y_full = (uint16_t*)y_full;
+  q.n_roles = layout->n_roles;
+  q.flags = (uint32_t*)g->flags[g->rank];
+  q.rank = g->rank;
+  q.world = g->world;
+  q.status = gb_status_word();
+  GB_CUDA_OK(gb_launch(dot_finalize_allgather_kernel, dim3((unsigned)((cols / 2 + 255) / 256)), dim3(256), 0, stream, q));
   return GB_OK;
 }
 

@@ -172,10 +172,50 @@ class PeerShardedCBLinear(torch.nn.Module):
         self.max_rows = max_rows
         self.out_off = peers.arena.carve(max_rows * self.N * 2)
         self.roles = role_slices(self.partition_sizes, world)
+        self._layout = None
+        self._fused_ok = None
         if len(self.roles) > 4:
             raise ValueError("at most four roles per fused module")
 
+    def _fused(self, x: torch.Tensor):
+        """One activation row through a CBLinear shard: the table kernel, then one launch that
+        sums the K slices and exchanges the shards.  None when the layer has no such kernel."""
+        if self._fused_ok is False:
+            return None
+        local = self.local
+        w = getattr(local, "_cb_weight", None)
+        method = getattr(local, "method", None)
+        if w is None or method is None or not method.fmt.is_fp4:
+            self._fused_ok = False
+            return None
+        from . import ops
+        peers = self.peers
+        if self._layout is None:
+            lay = nat.GbGatherLayout()
+            lay.n_roles = len(self.roles)
+            for i, (lc, gc, wd) in enumerate(self.roles):
+                lay.lcol[i], lay.gcol0[i], lay.width[i] = lc, gc, wd
+            self._layout = lay
+        x2 = x.reshape(1, -1).contiguous()
+        ws = local._cb_workspace
+        nw = w.native()
+        lib = peers.arena.lib
+        rc = lib.gb_gemv_allgather(ctypes.c_void_p(x2.data_ptr()), ctypes.byref(nw), nat.ACT_FP4_GROUP16,
+                                   nat.SCALE_RULE_DIV if ops.ACT_SCALE_RULE == "div" else nat.SCALE_RULE_RECIP,
+                                   ctypes.byref(peers.native), peers._ll, peers.ll_bytes, ctypes.byref(self._layout),
+                                   ctypes.c_void_p(peers.arena.ptr(peers.rank, self.out_off)),
+                                   ctypes.c_void_p(ws.data_ptr()), ws.numel(), nat.stream_ptr(peers.device))
+        if rc == nat.EUNSUPPORTED:
+            self._fused_ok = False          # same verdict on every rank: the format is the same everywhere
+            return None
+        nat.check(rc, lib)
+        return peers.arena.tensor(self.out_off, (1, self.N), torch.bfloat16)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.numel() == x.shape[-1] and x.dtype is torch.bfloat16:        # a single activation row
+            full = self._fused(x)
+            if full is not None:
+                return full.reshape(*x.shape[:-1], self.N)
         y = self.local(x)
         lead = y.shape[:-1]
         y2 = y.reshape(-1, self.n_local).contiguous()

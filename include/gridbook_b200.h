@@ -263,6 +263,24 @@ typedef struct gb_peer_ll_piece {
 GB_API int gb_peer_allgather_ll(const gb_peer_group* g, void* const* ll, int64_t ll_bytes,
                                 const gb_peer_ll_piece* pieces, int n_pieces, void* stream);
 
+/* Column-parallel decode linear, compute and collective in one pass: this rank's row shard of a
+ * fused module (an equal slice of every role) times ONE activation row through the
+ * inner-product-table kernel, then a single launch that adds the K slices, rounds to bf16 and
+ * all-gathers the shards flag-in-data (as gb_peer_allgather_ll) into every rank's full output
+ * row y_full [N].  layout: per role the first column of the slice inside the shard (lcol), the
+ * global column of rank 0's slice (gcol0) and the slice width; rank s's slice of role r lands at
+ * gcol0[r] + s * width[r].  Returns GB_EUNSUPPORTED for formats/shapes without the table kernel:
+ * run gb_gemv and gb_peer_allgather_ll instead (every rank gets the same answer, the format is
+ * the same everywhere).  Counts as one exchange in the ranks' common call sequence. */
+typedef struct gb_gather_layout {
+  int32_t n_roles;
+  int64_t lcol[4], gcol0[4], width[4];
+} gb_gather_layout;
+GB_API int gb_gemv_allgather(const void* x_bf16, const gb_weight* w, int act, int scale_rule,
+                             const gb_peer_group* g, void* const* ll, int64_t ll_bytes,
+                             const gb_gather_layout* layout, void* y_full_bf16, void* workspace,
+                             int64_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
