@@ -25,7 +25,7 @@ REQUIRED_SYMBOLS = (
     "gb_moe_gemv_pairs_workspace_bytes", "gb_moe_gemv_pairs",
     "gb_fp8_quantize_rows", "gb_gemm_tn",
     "gb_peer_alloc", "gb_peer_free", "gb_peer_export", "gb_peer_open", "gb_peer_close",
-    "gb_peer_allgather", "gb_peer_allgather_ll", "gb_peer_barrier", "gb_launch_count", "gb_gemv_allgather",
+    "gb_peer_allgather", "gb_peer_allgather_ll", "gb_peer_barrier", "gb_launch_count", "gb_gemv_allgather", "gb_moe_combine_peer",
 )
 PEER_MAX, PEER_HANDLE_BYTES, PEER_FLAG_BYTES = 8, 64, 128
 
@@ -128,6 +128,7 @@ def _declare(lib) -> None:
     lib.gb_peer_close.argtypes = [vp]
     lib.gb_peer_allgather.argtypes = [ctypes.POINTER(GbPeerGroup), ctypes.POINTER(GbPeerPiece), i32, vp]
     lib.gb_peer_barrier.argtypes = [ctypes.POINTER(GbPeerGroup), vp]
+    lib.gb_moe_combine_peer.argtypes = [vp, vp, vp, i64, i64, i64, i64, i32, vp, ctypes.POINTER(GbPeerGroup), vp]
     lib.gb_gemv_allgather.argtypes = [vp, wp, i32, i32, ctypes.POINTER(GbPeerGroup), ctypes.POINTER(vp), i64,
                                       ctypes.POINTER(GbGatherLayout), vp, vp, i64, vp]
     lib.gb_peer_allgather_ll.argtypes = [ctypes.POINTER(GbPeerGroup), ctypes.POINTER(vp), i64,

@@ -62,13 +62,57 @@ moe_route_kernel(const int32_t* __restrict__ ids, int P, int E, int first_expert
   }
 }
 
+// Optional cross-GPU part of the combine (expert parallelism): before any row of y is read,
+// tell every peer "my stores into your buffers are visible" and wait for the same from them
+// (the second half of the exchange protocol in gb_peer.cu: flag words 8..15, exchange number in
+// word 16, CTA counter in word 17).
+struct CombinePeers {
+  uint32_t* flags[GB_PEER_MAX];
+  int rank, world;       // world == 0: no exchange
+  int* status;
+};
+
 // out[t][h] = bf16( sum_slot w[t*topk+slot] * y[t*topk+slot][h] ), fp32 accumulate.
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const uint16_t* __restrict__ y, const float* __restrict__ pair_w,
                    const int32_t* __restrict__ ids, int E, int topk, int64_t H, int round_w,
-                   uint16_t* __restrict__ out) {
+                   uint16_t* __restrict__ out, const __grid_constant__ CombinePeers peers) {
   gb_pdl_launch_dependents();
   gb_pdl_wait();
+  if (peers.world > 0) {
+    __shared__ uint32_t s_epoch;
+    uint32_t* mine = peers.flags[peers.rank];
+    if (threadIdx.x == 0) s_epoch = *reinterpret_cast<volatile uint32_t*>(mine + 16) + 1u;
+    __syncthreads();
+    const uint32_t epoch = s_epoch;
+    if ((int)threadIdx.x < peers.world) {
+      const int d = threadIdx.x;
+      if (blockIdx.x == 0 && blockIdx.y == 0) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flags[d] + 8 + peers.rank), "r"(epoch) : "memory");
+      }
+      uint64_t t0 = 0;
+      for (uint32_t spin = 0;; ++spin) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + 8 + d) : "memory");
+        if ((int32_t)(v - epoch) >= 0) break;
+        if ((spin & 63u) == 63u) {
+          const uint64_t now = gb_globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > 2000000000ull) { atomicExch(peers.status, 3); break; }
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned total = gridDim.x * gridDim.y;
+      const unsigned old = atomicAdd(mine + 17, 1u);
+      if (old == total - 1) {          // every CTA has read the exchange number by now
+        mine[17] = 0u;
+        mine[16] = epoch;
+      }
+    }
+  }
   const int64_t t = blockIdx.y;
   const int64_t h2 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // pair of columns
   if (h2 * 2 >= H) return;
@@ -105,16 +149,39 @@ int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E, in
   return GB_OK;
 }
 
-int gb_moe_combine(const void* y, const float* pair_w, const int32_t* topk_ids, int64_t E, int64_t T,
-                   int64_t topk, int64_t H, int round_weights, void* out, void* stream) {
+static int combine_launch(const void* y, const float* pair_w, const int32_t* topk_ids, int64_t E, int64_t T,
+                          int64_t topk, int64_t H, int round_weights, void* out, const gb_peer_group* g, void* stream) {
   GB_REQUIRE(y && pair_w && out, "null pointer argument");
   GB_REQUIRE(T >= 0 && topk >= 1 && H > 0 && H % 2 == 0, "bad combine shape T=%lld topk=%lld H=%lld",
              (long long)T, (long long)topk, (long long)H);
+  CombinePeers peers = {};
+  if (g) {
+    GB_REQUIRE(g->world >= 1 && g->world <= GB_PEER_MAX && g->rank >= 0 && g->rank < g->world, "bad peer group");
+    GB_REQUIRE(T > 0, "the combine that closes an exchange needs at least one token");
+    for (int r = 0; r < g->world; ++r) {
+      GB_REQUIRE(g->flags[r] != nullptr, "peer group: flag block of rank %d is null", r);
+      peers.flags[r] = (uint32_t*)g->flags[r];
+    }
+    peers.rank = g->rank;
+    peers.world = g->world;
+    peers.status = gb_status_word();
+  }
   if (T == 0) return GB_OK;
   dim3 grid((unsigned)((H / 2 + 255) / 256), (unsigned)T);
   GB_CUDA_OK(gb_launch(moe_combine_kernel, grid, dim3(256), 0, (cudaStream_t)stream, (const uint16_t*)y, pair_w,
-                       topk_ids, (int)E, (int)topk, H, round_weights ? 1 : 0, (uint16_t*)out));
+                       topk_ids, (int)E, (int)topk, H, round_weights ? 1 : 0, (uint16_t*)out, peers));
   return GB_OK;
+}
+
+int gb_moe_combine(const void* y, const float* pair_w, const int32_t* topk_ids, int64_t E, int64_t T,
+                   int64_t topk, int64_t H, int round_weights, void* out, void* stream) {
+  return combine_launch(y, pair_w, topk_ids, E, T, topk, H, round_weights, out, nullptr, stream);
+}
+
+int gb_moe_combine_peer(const void* y, const float* pair_w, const int32_t* topk_ids, int64_t E, int64_t T,
+                        int64_t topk, int64_t H, int round_weights, void* out, const gb_peer_group* g, void* stream) {
+  GB_REQUIRE(g != nullptr, "null peer group");
+  return combine_launch(y, pair_w, topk_ids, E, T, topk, H, round_weights, out, g, stream);
 }
 
 }  // extern "C"

@@ -262,10 +262,13 @@ def moe_gemv_pairs(x: torch.Tensor, w: PackedWeight, pair_expert: torch.Tensor, 
 
 
 def moe_combine(y: torch.Tensor, pair_w: torch.Tensor, T: int, topk: int, *,
-                topk_ids: torch.Tensor | None = None, E: int = 0, round_weights: bool = False) -> torch.Tensor:
+                topk_ids: torch.Tensor | None = None, E: int = 0, round_weights: bool = False,
+                peer_group=None) -> torch.Tensor:
     """out[t] = sum_slot pair_w * y, fp32 accumulate, one bf16 rounding.  ``topk_ids`` (int32,
     with ``E``) names the pairs routing dropped, whose rows of ``y`` are then never read.
-    ``round_weights``: ``pair_w`` are raw router weights, rounded to bf16 inside the kernel."""
+    ``round_weights``: ``pair_w`` are raw router weights, rounded to bf16 inside the kernel.
+    ``peer_group`` (a ``GbPeerGroup``): the launch first exchanges "stores visible" flags with the
+    other ranks, whose down projections wrote the rows of ``y``."""
     _need_cuda(y, pair_w, topk_ids)
     lib = nat.load("grouped CB router combine")
     y = y.contiguous()
@@ -275,6 +278,10 @@ def moe_combine(y: torch.Tensor, pair_w: torch.Tensor, T: int, topk: int, *,
     ids = None
     if topk_ids is not None:
         ids = topk_ids.to(torch.int32).contiguous()
+    if peer_group is not None:
+        nat.check(lib.gb_moe_combine_peer(_ptr(y), _ptr(pw), _ptr(ids), E, T, topk, H, 1 if round_weights else 0,
+                                          _ptr(out), ctypes.byref(peer_group), nat.stream_ptr(y.device)), lib)
+        return out
     nat.check(lib.gb_moe_combine(_ptr(y), _ptr(pw), _ptr(ids), E, T, topk, H, 1 if round_weights else 0,
                                  _ptr(out), nat.stream_ptr(y.device)), lib)
     return out

@@ -9,7 +9,8 @@ same exchanges are plain stores into the peers' buffers from this package's own 
 * ``PeerExpertParallelMoE``: the bucketed activations and the routing ids are all-gathered the
   same way, every rank runs the grouped kernels over the pairs routed to ITS experts, and the
   down-projection GEMV stores every output row straight into the buffer of the rank the token
-  came from; a flag exchange later the home rank combines.  Eight launches, no host read.
+  came from; the home rank's combine waits for the peers' "stores visible" flags in its own launch.  Five to
+  seven launches, no host read.
 
 The reference is single-GPU (gridbook/config.py:565-576); nothing here has a counterpart there.
 Buffers are shared between the processes by CUDA IPC handles sent through the process group.
@@ -317,9 +318,10 @@ class PeerExpertParallelMoE(torch.nn.Module):
                 kernels.moe_gemv(a, layer._cb_w2, offsets, order, peer_rows=rows, act="fp4", scale_rule=rule)
             else:
                 kernels.moe_gemv(b2(a, rule), layer._cb_w2, offsets, order, peer_rows=rows)
-        self.peers.barrier()
         back = self.peers.arena.tensor(self.back_off, (T * topk, H), torch.bfloat16)
         # the loop chain multiplies by the bf16-rounded router weight (gridbook/moe.py:2407-2408):
         # the combine rounds the raw weights itself
-        out = kernels.moe_combine(back, topk_weights, T, topk, topk_ids=ids, E=self.E, round_weights=True)
+        # ... and first waits, inside the same launch, until every rank's rows have landed
+        out = kernels.moe_combine(back, topk_weights, T, topk, topk_ids=ids, E=self.E, round_weights=True,
+                                  peer_group=self.peers.native)
         return out.to(x.dtype).reshape(x.shape)

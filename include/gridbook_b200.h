@@ -249,6 +249,12 @@ typedef struct gb_peer_piece {
  * A peer that does not show up within two seconds raises gb_device_status (3); nothing hangs. */
 GB_API int gb_peer_allgather(const gb_peer_group* g, const gb_peer_piece* pieces, int n_pieces, void* stream);
 GB_API int gb_peer_barrier(const gb_peer_group* g, void* stream);   /* "my stores before this call are visible" */
+/* gb_moe_combine that first does gb_peer_barrier's exchange inside the same launch: the rows of
+ * y were stored by the peers' down projections (gb_moe_gemv / gb_moe_gemv_pairs with y_rows).
+ * Counts as one exchange in the ranks' common call sequence. */
+GB_API int gb_moe_combine_peer(const void* y_bf16, const float* pair_w, const int32_t* topk_ids,
+                   int64_t E, int64_t T, int64_t topk, int64_t H, int round_weights,
+                   void* out_bf16, const gb_peer_group* g, void* stream);
 
 /* The same all-gather for small pieces, flag-in-data: every 4-byte word is sent as an 8-byte
  * {word, exchange number} store into a staging buffer of the receiver (ll[r]: rank r's buffer of
