@@ -23,6 +23,7 @@ REQUIRED_SYMBOLS = (
     "gb_gemv_workspace_bytes", "gb_gemv", "gb_gemv_static",
     "gb_moe_route", "gb_moe_gemv_workspace_bytes", "gb_moe_gemv", "gb_moe_combine",
     "gb_moe_gemv_pairs_workspace_bytes", "gb_moe_gemv_pairs",
+    "gb_moe_mlp_pairs_workspace_bytes", "gb_moe_mlp_pairs",
     "gb_fp8_quantize_rows", "gb_gemm_tn",
     "gb_peer_alloc", "gb_peer_free", "gb_peer_export", "gb_peer_open", "gb_peer_close",
     "gb_peer_allgather", "gb_peer_allgather_ll", "gb_peer_barrier", "gb_launch_count", "gb_gemv_allgather", "gb_moe_combine_peer",
@@ -117,6 +118,9 @@ def _declare(lib) -> None:
     lib.gb_moe_combine.argtypes = [vp, vp, vp, i64, i64, i64, i64, i32, vp, vp]
     lib.gb_moe_gemv_pairs_workspace_bytes.argtypes = [i64, i64, i64]
     lib.gb_moe_gemv_pairs_workspace_bytes.restype = i64
+    lib.gb_moe_mlp_pairs_workspace_bytes.argtypes = [i64, i64, i64]
+    lib.gb_moe_mlp_pairs_workspace_bytes.restype = i64
+    lib.gb_moe_mlp_pairs.argtypes = [vp, vp, wp, i64, wp, i64, i64, i64, vp, i64, i64, i32, i32, vp, vp, vp, i64, vp]
     lib.gb_moe_gemv_pairs.argtypes = [vp, vp, wp, i64, i64, i64, vp, i64, i64, i32, i32, i32, vp, vp, vp, i64, vp]
     lib.gb_fp8_quantize_rows.argtypes = [vp, vp, vp, i64, i64, i32, vp]
     lib.gb_gemm_tn.argtypes = [vp, vp, vp, i64, i64, i64, i32, vp, vp, ctypes.c_float, vp]

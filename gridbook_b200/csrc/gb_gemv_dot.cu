@@ -64,6 +64,12 @@ struct DotParams {
   int pairs_per_rank;
   int direct;                   // 1: store y from the kernel, 0: partial sums + the summing kernel
   float global_scale;
+  // pair mode, second projection of an MLP: the activation row of pair p is
+  // silu(gate) * up of the FIRST projection's partial sums (its K slices still unsummed)
+  const float* xws;             // [xws_slices][P][xws_N] partial sums of the gate/up projection, or nullptr
+  int xws_slices;
+  int64_t xws_N;                // rows of the gate/up projection (= 2 x this projection's K)
+  float xws_scale;              // its global scale
 };
 
 // Output row of pair `pair` (width `width` elements): in y, or in its home rank's buffer.
@@ -215,7 +221,27 @@ gemv_dot_kernel(const __grid_constant__ CUtensorMap map_w, const DotParams p) {
   // ---- this slice of the activation row, through its bucket, into shared memory ----
   gb_pdl_wait();                       // the activations (and the partial-sum slots) belong to earlier kernels
   if (tid < ns * 128) {                // two values per thread, a bucket group per eight lanes
-    uint32_t w = reinterpret_cast<const uint32_t*>(xsrc + (int64_t)sb0 * 256)[tid];
+    uint32_t w;
+    if (kPairs && p.xws) {
+      // sum the gate/up projection's K slices, SwiGLU with the bf16 roundings of F.silu(gate) * up
+      const int64_t j = (int64_t)sb0 * 256 + 2 * tid, half = p.xws_N / 2;
+      float g0 = 0.f, g1 = 0.f, u0 = 0.f, u1 = 0.f;
+      for (int sl = 0; sl < p.xws_slices; ++sl) {
+        const float* slot = p.xws + ((int64_t)sl * p.P + pair) * p.xws_N;
+        const float2 gv = *reinterpret_cast<const float2*>(slot + j);
+        const float2 uv = *reinterpret_cast<const float2*>(slot + half + j);
+        g0 += gv.x; g1 += gv.y; u0 += uv.x; u1 += uv.y;
+      }
+      auto act1 = [&](float graw, float uraw) {
+        const float gate = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(graw * p.xws_scale));
+        const float up = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(uraw * p.xws_scale));
+        const float sl = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(gate / (1.0f + __expf(-gate))));
+        return gb_f32_to_bf16_bits(sl * up);
+      };
+      w = act1(g0, u0) | (act1(g1, u1) << 16);
+    } else {
+      w = reinterpret_cast<const uint32_t*>(xsrc + (int64_t)sb0 * 256)[tid];
+    }
     if (p.act == GB_ACT_FP4_GROUP16) w = gb_fp4_group16_qdq_lanes(w, p.scale_rule);
     reinterpret_cast<uint32_t*>(xq)[tid] = w;
   }
@@ -557,10 +583,17 @@ extern "C" int64_t gb_moe_gemv_pairs_workspace_bytes(int64_t P, int64_t rows, in
   return n_slices * P * rows * (int64_t)sizeof(float);
 }
 
+struct PairChain {            // set for the second projection of gb_moe_mlp_pairs
+  const float* xws;
+  int slices;
+  int64_t N;
+  float scale;
+};
 static int dot_pairs_launch(const void* x, const int32_t* x_row, const gb_weight* w, int64_t expert_stride,
                             int64_t E, int64_t expert_base, const int32_t* pair_expert, int64_t P,
                             int64_t pairs_expected, int swiglu, int act, int scale_rule, void* y,
-                            const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes, void* stream_);
+                            const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes, void* stream_,
+                            bool leave_partials = false, const PairChain* chain = nullptr);
 
 extern "C" int gb_moe_gemv_pairs(const void* x, const int32_t* x_row, const gb_weight* w, int64_t expert_stride,
                                  int64_t E, int64_t expert_base, const int32_t* pair_expert, int64_t P,
@@ -588,11 +621,12 @@ int64_t gb_gemv_dot_rows_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 static int dot_pairs_launch(const void* x, const int32_t* x_row, const gb_weight* w, int64_t expert_stride,
                             int64_t E, int64_t expert_base, const int32_t* pair_expert, int64_t P,
                             int64_t pairs_expected, int swiglu, int act, int scale_rule, void* y,
-                            const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes, void* stream_) {
+                            const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes, void* stream_,
+                            bool leave_partials, const PairChain* chain) {
   cudaStream_t stream = (cudaStream_t)stream_;
   int rc = gb_check_weight(w);
   if (rc != GB_OK) return rc;
-  GB_REQUIRE(x && (y || y_rows), "null pointer argument");
+  GB_REQUIRE((x || chain) && (y || y_rows || leave_partials), "null pointer argument");
   GB_REQUIRE(E >= 1 && P >= 0 && P < (1 << 24), "bad E=%lld P=%lld", (long long)E, (long long)P);
   GB_REQUIRE(!swiglu || w->rows % 2 == 0, "swiglu needs an even row count");
   const gb_format& f = w->fmt;
@@ -603,6 +637,7 @@ static int dot_pairs_launch(const void* x, const int32_t* x_row, const gb_weight
                     ((uintptr_t)x & 15u) == 0 && ((uintptr_t)w->codebook & 3u) == 0;
   if (!mine) return GB_EUNSUPPORTED;
   if (P == 0) return GB_OK;
+  if (chain) GB_REQUIRE(chain->xws && chain->N == 2 * w->K, "chained input must be a gate/up projection of 2 x K rows");
   const int sms = gb_sm_count();
   if (sms <= 0) return gb_fail(GB_ECUDA, "no usable CUDA device: %s", gb_last_error());
   DotParams p = {};
@@ -639,7 +674,13 @@ static int dot_pairs_launch(const void* x, const int32_t* x_row, const gb_weight
   p.bands = bands;
   const int64_t per = (w->rows + bands - 1) / bands;
   p.rows_per_group = (int)((per + kStageRows - 1) / kStageRows * kStageRows);
-  p.direct = (p.n_slices == 1 && !swiglu) ? 1 : 0;
+  p.direct = (p.n_slices == 1 && !swiglu && !leave_partials) ? 1 : 0;
+  if (chain) {
+    p.xws = chain->xws;
+    p.xws_slices = chain->slices;
+    p.xws_N = chain->N;
+    p.xws_scale = chain->scale;
+  }
   if (!p.direct) {
     const int64_t need = gb_moe_gemv_pairs_workspace_bytes(P, w->rows, w->K);
     GB_REQUIRE(workspace != nullptr && workspace_bytes >= need, "workspace of %lld bytes is too small (need %lld)",
@@ -653,10 +694,40 @@ static int dot_pairs_launch(const void* x, const int32_t* x_row, const gb_weight
   const int64_t grid = P * p.n_slices * bands;
   GB_REQUIRE(grid < (1ll << 31), "too many pairs for one launch");
   GB_CUDA_OK(gb_launch(gemv_dot_kernel<true>, dim3((unsigned)grid), dim3(kDotThreads), kDotSmem, stream, map, p));
-  if (!p.direct) {
+  if (!p.direct && !leave_partials) {
     const int64_t total = P * (swiglu ? w->rows / 2 : w->rows);
     GB_CUDA_OK(gb_launch(dot_pairs_finalize_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, p,
                          swiglu ? 1 : 0));
   }
   return GB_OK;
+}
+
+// Both projections of the routed MLP for small batches, in two launches: the gate/up table
+// GEMVs leave their K-slice partial sums in the workspace, and the down projection's kernels
+// sum them, apply SwiGLU and the fp4 bucket while they stage their activation row.
+extern "C" int64_t gb_moe_mlp_pairs_workspace_bytes(int64_t P, int64_t hidden, int64_t inter) {
+  return gb_moe_gemv_pairs_workspace_bytes(P, 2 * inter, hidden) + gb_moe_gemv_pairs_workspace_bytes(P, hidden, inter);
+}
+
+extern "C" int gb_moe_mlp_pairs(const void* x, const int32_t* x_row, const gb_weight* w13, int64_t stride13,
+                                const gb_weight* w2, int64_t stride2, int64_t E, int64_t expert_base,
+                                const int32_t* pair_expert, int64_t P, int64_t pairs_expected, int act, int scale_rule,
+                                void* y, const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes,
+                                void* stream) {
+  GB_REQUIRE(w13 && w2 && pair_expert, "null pointer argument");
+  GB_REQUIRE(w13->rows == 2 * w2->K && w2->rows == w13->K, "gate/up is %lld x %lld, down %lld x %lld: not an MLP",
+             (long long)w13->rows, (long long)w13->K, (long long)w2->rows, (long long)w2->K);
+  const int64_t ws13 = gb_moe_gemv_pairs_workspace_bytes(P, w13->rows, w13->K);
+  GB_REQUIRE(workspace && workspace_bytes >= gb_moe_mlp_pairs_workspace_bytes(P, w13->K, w2->K),
+             "workspace of %lld bytes is too small", (long long)workspace_bytes);
+  int rc = dot_pairs_launch(x, x_row, w13, stride13, E, expert_base, pair_expert, P, pairs_expected, 0, act, scale_rule,
+                            nullptr, nullptr, workspace, ws13, stream, /*leave_partials=*/true, nullptr);
+  if (rc != GB_OK) return rc;
+  PairChain chain;
+  chain.xws = (const float*)workspace;
+  chain.slices = (int)((w13->K / 256 + kS - 1) / kS);
+  chain.N = w13->rows;
+  chain.scale = w13->global_scale == 0.0f ? 1.0f : w13->global_scale;
+  return dot_pairs_launch(nullptr, nullptr, w2, stride2, E, expert_base, pair_expert, P, pairs_expected, 0, act,
+                          scale_rule, y, y_rows, (uint8_t*)workspace + ws13, workspace_bytes - ws13, stream, false, &chain);
 }

@@ -261,6 +261,35 @@ def moe_gemv_pairs(x: torch.Tensor, w: PackedWeight, pair_expert: torch.Tensor, 
     return True if peer_rows is not None else out
 
 
+def moe_mlp_pairs(x: torch.Tensor, w13: PackedWeight, w2: PackedWeight, pair_expert: torch.Tensor, *,
+                  x_row: torch.Tensor | None = None, act: str | None = "fp4", scale_rule: str = "recip",
+                  expert_base: int = 0, pairs_expected: int = 0, peer_rows=None):
+    """Both projections of the routed MLP for small batches of the literal format, two launches
+    (see :func:`moe_gemv_pairs`): y[p] = W2[e_p] . bucket(silu(gate) * up) with gate/up =
+    W13[e_p] . bucket(x[x_row[p]]).  Returns [P, hidden] (True with ``peer_rows``), or None when
+    the formats have no such kernel."""
+    _need_cuda(x, pair_expert, x_row)
+    lib = nat.load("per-pair table MLP")
+    if x.dtype is not torch.bfloat16:
+        raise TypeError("the per-pair MLP takes bf16 activations")
+    x = x.contiguous()
+    ids = pair_expert.reshape(-1).to(torch.int32).contiguous()
+    P = ids.numel()
+    out = None if peer_rows is not None else torch.empty((P, w2.rows), dtype=torch.bfloat16, device=x.device)
+    need = lib.gb_moe_mlp_pairs_workspace_bytes(P, w13.K, w2.K)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
+    n13, n2 = w13.native(), w2.native()
+    rc = lib.gb_moe_mlp_pairs(_ptr(x), _ptr(x_row), ctypes.byref(n13), w13.expert_stride, ctypes.byref(n2),
+                              w2.expert_stride, w13.experts, expert_base, _ptr(ids), P, pairs_expected,
+                              nat.ACT_FP4_GROUP16 if act == "fp4" else nat.ACT_NONE, _rule(scale_rule), _ptr(out),
+                              ctypes.byref(peer_rows) if peer_rows is not None else None,
+                              _ptr(ws), ws.numel(), nat.stream_ptr(x.device))
+    if rc == nat.EUNSUPPORTED:
+        return None
+    nat.check(rc, lib)
+    return True if peer_rows is not None else out
+
+
 def moe_combine(y: torch.Tensor, pair_w: torch.Tensor, T: int, topk: int, *,
                 topk_ids: torch.Tensor | None = None, E: int = 0, round_weights: bool = False,
                 peer_group=None) -> torch.Tensor:

@@ -205,14 +205,12 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
 
     def _apply_pairs(self, layer, x2, topk_weights, ids, rule):
         """Small batches of the literal format: every routed pair is its own M = 1 linear through
-        the inner-product-table kernel (bucket fused, SwiGLU in the slot-summing kernel), then the
-        combine.  Four launches, no routing tables.  None when the format has no such kernel."""
+        the inner-product-table kernel (bucket fused; the down projection sums the gate/up K
+        slices and applies SwiGLU while it stages its rows), then the combine.  Three launches, no
+        routing tables.  None when the format has no such kernel."""
         T, topk = ids.shape
         x_row = self._x_row(layer, T, topk, x2.device)
-        a = kernels.moe_gemv_pairs(x2, layer._cb_w13, ids, x_row=x_row, swiglu=True, act="fp4", scale_rule=rule)
-        if a is None:
-            return None
-        y = kernels.moe_gemv_pairs(a, layer._cb_w2, ids, act="fp4", scale_rule=rule)
+        y = kernels.moe_mlp_pairs(x2, layer._cb_w13, layer._cb_w2, ids, x_row=x_row, act="fp4", scale_rule=rule)
         if y is None:
             return None
         return kernels.moe_combine(y, topk_weights, T, topk, topk_ids=ids, E=layer._cb_E, round_weights=True)

@@ -302,14 +302,12 @@ class PeerExpertParallelMoE(torch.nn.Module):
         done = False
         if per_pair:
             expect = max(1, pairs_all // world)
-            a = kernels.moe_gemv_pairs(x_all, layer._cb_w13, ids_all, x_row=x_row, swiglu=True, act="fp4",
-                                       scale_rule=rule, expert_base=base, pairs_expected=expect)
-            if a is None:
+            ok = kernels.moe_mlp_pairs(x_all, layer._cb_w13, layer._cb_w2, ids_all, x_row=x_row, act="fp4",
+                                       scale_rule=rule, expert_base=base, pairs_expected=expect, peer_rows=rows)
+            if ok is None:
                 # every rank holds the same formats, so every rank takes this branch together
                 raise NativeKernelUnavailableError(
-                    "per-pair table GEMV refused a format the layer was built for")
-            kernels.moe_gemv_pairs(a, layer._cb_w2, ids_all, act="fp4", scale_rule=rule, expert_base=base,
-                                   pairs_expected=expect, peer_rows=rows)
+                    "per-pair table MLP refused a format the layer was built for")
             done = True
         if not done:
             _, offsets, order = kernels.moe_route(ids_all, self.e_local, expert_base=base)

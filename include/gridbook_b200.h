@@ -202,6 +202,18 @@ GB_API int gb_moe_gemv_pairs(const void* x_bf16, const int32_t* x_row, const gb_
                 int64_t P, int64_t pairs_expected, int swiglu, int act, int scale_rule, void* y_bf16,
                 const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Both projections of the routed MLP through gb_moe_gemv_pairs' kernels in TWO launches: the
+ * gate/up GEMVs leave their K-slice partial sums in the workspace, and the down projection sums
+ * them, applies SwiGLU and the activation bucket while it stages each pair's row (replaces
+ * cb_moe_gemv_* + native_moe_activation + the second bucket of gridbook/moe.py:2388-2504 for
+ * small batches).  w13: one expert's [2*inter, hidden] matrix, w2: [hidden, inter]. */
+GB_API int64_t gb_moe_mlp_pairs_workspace_bytes(int64_t P, int64_t hidden, int64_t inter);
+GB_API int gb_moe_mlp_pairs(const void* x_bf16, const int32_t* x_row, const gb_weight* w13, int64_t stride13,
+                const gb_weight* w2, int64_t stride2, int64_t E, int64_t expert_base,
+                const int32_t* pair_expert, int64_t P, int64_t pairs_expected, int act, int scale_rule,
+                void* y_bf16, const gb_peer_rows* y_rows, void* workspace, int64_t workspace_bytes,
+                void* stream);
+
 /* out[t] = sum over the token's topk pairs of w[p] * y[p], fp32 accumulate, one bf16
  * rounding; replaces cb_moe_combine (gridbook/csrc/cb_gemv.cu:1853-1871,2140-2158).
  * pair p = t*topk + slot.  topk_ids (optional, with E): pairs whose id lies outside [0, E)

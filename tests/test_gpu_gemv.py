@@ -220,6 +220,9 @@ def test_moe_per_pair_table_kernel_matches_grouped_kernel(dev, T):
     y_ref = kernels.moe_gemv(kernels.fp4_act_qdq(a), w2, offsets, order)
     y = kernels.moe_gemv_pairs(a, w2, idd, act="fp4")
     assert_close_bf16(f32_of(y[live]), f32_of(y_ref[live]), "per-pair down vs grouped")
+    # both projections chained (the down projection sums the gate/up slices itself): same bits
+    y_chain = kernels.moe_mlp_pairs(xd, w13, w2, idd, x_row=x_row)
+    assert torch.equal(y_chain[live], y[live])
     out = kernels.moe_combine(y, torch.from_numpy(tw).to(dev), T, topk, topk_ids=idd, E=E, round_weights=True)
     keep = ids >= 0
     ref = O.moe_loop_chain(x, np.where(keep, ids, 0), np.where(keep, tw, 0.0).astype(np.float32), w13d, w2d, E=E,
