@@ -68,6 +68,20 @@ class PeerArena:
         self._top = 0
         self._bytes = torch.as_tensor(_RawDeviceMemory(own.value, self.nbytes), device=device)
 
+    def close(self) -> None:
+        """Unmaps the peers' blocks and frees this rank's.  Call on every rank, after a barrier
+        that guarantees nobody still stores into a block that is about to disappear."""
+        if self._own is None:
+            return
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            for r, ptr in enumerate(self.ptrs):
+                if r != self.rank and ptr:
+                    nat.check(self.lib.gb_peer_close(ctypes.c_void_p(ptr)), self.lib)
+            self._bytes = None
+            nat.check(self.lib.gb_peer_free(self._own), self.lib)
+        self._own, self.ptrs = None, []
+
     def carve(self, nbytes: int) -> int:
         off = self._top
         self._top = (off + int(nbytes) + 255) & ~255
@@ -131,6 +145,10 @@ class PeerGroup:
                 q.dst[r] = self.arena.ptr(r, dst_offs[self.rank])
         nat.check(lib.gb_peer_allgather(ctypes.byref(self.native), arr, len(pieces),
                                         nat.stream_ptr(self.device)), lib)
+
+    def close(self) -> None:
+        dist.barrier(self.arena.group)
+        self.arena.close()
 
     def barrier(self) -> None:
         """Returns (on the stream) once every rank's stores enqueued before its own call are

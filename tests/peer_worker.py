@@ -26,7 +26,10 @@ def main():
     # once with the flag-in-data exchange (pieces fit the staging buffer), once with a staging
     # buffer too small for anything, which sends every exchange down the two-phase path
     for ll_words in (1 << 19, 16):
-        check(PeerGroup(64 << 20, dev, ll_words=ll_words), rank, world, dev)
+        peers = PeerGroup(64 << 20, dev, ll_words=ll_words)
+        check(peers, rank, world, dev)
+        torch.cuda.synchronize()
+        peers.close()
     status = _native.device_status(local)
     assert status == 0, f"a bounded wait inside a kernel ran out (status {status})"
     dist.barrier()
