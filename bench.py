@@ -571,6 +571,10 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # the multi-process launcher pins every rank to one OpenMP thread; this arm runs on rank 0
+    # alone and is meant to use every host core (set before the OpenMP runtime starts)
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     from oracle import c_oracle as C
     fmt, gscale = get_format(args.format)
     layer = cpu_layer_inputs(fmt, gscale, args.m)
