@@ -191,15 +191,15 @@ def test_moe_fused_bucket_equals_separate_bucket(dev, name):
     assert torch.equal(y_sep, y_fused)
 
 
-@pytest.mark.parametrize("T", [1, 7, 40])
-def test_moe_per_pair_table_kernel_matches_grouped_kernel(dev, T):
+@pytest.mark.parametrize("T,inter", [(1, 768), (7, 768), (40, 768), (5, 1280)])
+def test_moe_per_pair_table_kernel_matches_grouped_kernel(dev, T, inter):
     """Literal format: every routed pair as its own table GEMV (gate/up K = 2048: two K slices and
     SwiGLU in the summing kernel; down K = 768: one ragged slice, stored straight from the kernel)
     against the grouped MMA kernel on the same bits and against the loop-chain oracle, with a
     padded route."""
     from gridbook_b200 import kernels, synth
     fmt = _fmt("lit")
-    E, hidden, inter, topk = 8, 2048, 768, 3
+    E, hidden, topk = 8, 2048, 3            # inter = 1280: the down projection has two K slices too
     w13d, w2d = synth.make_moe(fmt, fmt, E, hidden, inter, seed=T)
     ids, tw = synth.make_routing(T, E, topk, seed=T)
     if T > 1:
