@@ -85,6 +85,9 @@ class PrismaQuantConfig(QuantizationConfig):
                 self.target_scheme[target] = scheme
         self.ignore = list(full.get("ignore", []))
         self.codebook_file = full.get("codebook_file", self.raw.get("codebook_file", "cb_codebooks.pqcb"))
+        # artifact-external digests of the sidecar's tables (docs/SPEC.md:326-378); None = not declared
+        prov = full.get("provenance")
+        self.codebook_sha256 = prov.get("codebook_sha256") if isinstance(prov, dict) else None
         self._resolved = True
 
     def get_codebooks(self) -> dict[str, torch.Tensor]:
@@ -97,6 +100,14 @@ class PrismaQuantConfig(QuantizationConfig):
             else:
                 from safetensors.torch import load_file
                 self._codebooks = load_file(os.path.join(self.model_dir, self.codebook_file))
+            # declared digests are checked before any table is used; an undeclared mapping loads
+            # without the check, an empty one does not equal absence
+            from .artifact import verify_codebook_digests
+            try:
+                verify_codebook_digests(self._codebooks, self.codebook_sha256)
+            except Exception:
+                self._codebooks = None
+                raise
         return self._codebooks
 
     def _tables(self, scheme: dict) -> list[torch.Tensor]:

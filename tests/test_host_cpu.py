@@ -225,3 +225,81 @@ def test_peer_role_slices_agree_with_the_gather_permutation():
         assert torch.equal(full, parallel.gather_permutation(parts, world))
     with pytest.raises(ValueError):
         peer.role_slices([10], 4)
+
+
+def _write_artifact(tmp_path, books, provenance="auto", tensors=None):
+    """A minimal published directory: pointer stub, assignment, sidecar (+ optional tensors)."""
+    from safetensors.torch import save_file
+    from gridbook_b200.artifact import codebook_sha256
+    full = _quant_config()
+    if provenance == "auto":
+        full["provenance"] = {"codebook_sha256": {n: codebook_sha256(t) for n, t in books.items()}}
+    elif provenance is not None:
+        full["provenance"] = {"codebook_sha256": provenance}
+    (tmp_path / "config.json").write_text(json.dumps({"quantization_config": {"quant_method": "gridbook"}}))
+    (tmp_path / "quant_config.json").write_text(json.dumps(full))
+    save_file({n: t.to(torch.float16).contiguous() for n, t in books.items()}, str(tmp_path / "cb_codebooks.pqcb"))
+    if tensors:
+        save_file(tensors, str(tmp_path / "model.safetensors"))
+    return full
+
+
+def _books():
+    g = torch.Generator().manual_seed(0)
+    books = {n: torch.randint(-6, 7, (256, 4), generator=g).float() * 0.5
+             for n in ("cb.K16.sub0", "cb.K16.sub1", "cb.K16b.sub0", "cb.K16b.sub1")}
+    books.update({f"cb.F32.sub{i}": torch.randint(-8, 9, (256, 2), generator=g).float() for i in range(4)})
+    return books
+
+
+def test_artifact_codebook_digests(tmp_path):
+    """Declared digests must cover the sidecar exactly and match; no declaration loads unchecked;
+    an empty declaration is not the same as none (docs/SPEC.md:326-378)."""
+    from gridbook_b200.artifact import Artifact, codebook_sha256
+    books = _books()
+    good = tmp_path / "good"
+    good.mkdir()
+    _write_artifact(good, books, tensors={"model.layers.0.self_attn.o_proj.cb_qweight":
+                                          torch.zeros(4, 128, dtype=torch.uint8)})
+    art = Artifact(str(good))
+    assert art.has("model.layers.0.self_attn.o_proj.cb_qweight") and not art.has("nope")
+    assert art.tensor("model.layers.0.self_attn.o_proj.cb_qweight").shape == (4, 128)
+    assert art.config.get_quant_method(torch.nn.Identity(), "lm_head") is None
+    # the digest is the SHA-256 of the fp16 row-major bytes
+    import hashlib
+    t = books["cb.K16.sub0"]
+    assert codebook_sha256(t) == hashlib.sha256(t.to(torch.float16).numpy().tobytes()).hexdigest()
+
+    undeclared = tmp_path / "undeclared"
+    undeclared.mkdir()
+    _write_artifact(undeclared, books, provenance=None)
+    Artifact(str(undeclared))
+
+    digests = {n: codebook_sha256(t) for n, t in books.items()}
+    cases = {
+        "wrong": dict(digests, **{"cb.K16.sub1": "0" * 64}),
+        "missing": {n: d for n, d in digests.items() if n != "cb.F32.sub3"},
+        "extra": dict(digests, **{"cb.ghost": "1" * 64}),
+        "empty": {},
+        "malformed": dict(digests, **{"cb.K16.sub0": "XYZ"}),
+    }
+    for tag, mapping in cases.items():
+        d = tmp_path / tag
+        d.mkdir()
+        _write_artifact(d, books, provenance=mapping)
+        with pytest.raises(ValueError, match="prismaquant"):
+            Artifact(str(d))
+    # a sidecar swapped for another intact one with the same names fails too
+    swapped = tmp_path / "swapped"
+    swapped.mkdir()
+    _write_artifact(swapped, books, provenance=digests)
+    from safetensors.torch import save_file
+    other = {n: (t + 0.5).to(torch.float16) for n, t in books.items()}
+    save_file(other, str(swapped / "cb_codebooks.pqcb"))
+    with pytest.raises(ValueError, match="does not match"):
+        Artifact(str(swapped))
+    with pytest.raises(ValueError, match="no gridbook"):
+        bad = tmp_path / "plain"
+        bad.mkdir()
+        (bad / "config.json").write_text("{}")
+        Artifact(str(bad))
