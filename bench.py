@@ -429,7 +429,8 @@ def bench_moe(args, device, world, rank, peers=None):
         layers.append(moe)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     out = {}
-    for T in (1, 16, 64, 256):
+    # one GPU also times a prefill batch: it takes the grouped tensor-core route
+    for T in ((1, 16, 64, 256, 4096) if world == 1 else (1, 16, 64, 256)):
         ids, tw = synth.make_routing(T, E, topk, seed=T + 13 * rank)
         x = torch.randn(T, hidden, generator=gen, device=device).to(torch.bfloat16)
         ids_d, tw_d = torch.from_numpy(ids).to(device), torch.from_numpy(tw).to(device)
@@ -467,7 +468,21 @@ def bench_moe(args, device, world, rank, peers=None):
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_layer = float(t) / (iters * len(layers))
-        out[str(T)] = {"tok_s": round(world * T / (ms_layer * 1e-3), 1), "ms_per_layer": round(ms_layer, 4)}
+        entry = {"tok_s": round(world * T / (ms_layer * 1e-3), 1), "ms_per_layer": round(ms_layer, 4)}
+        if world == 1:
+            # roofline view: packed bytes of the experts this batch touches, each counted once
+            import numpy as np
+            touched = int(np.unique(ids[ids >= 0]).size)
+            per_expert = fmt.row_bytes(hidden) * 2 * inter + fmt.row_bytes(inter) * hidden
+            gbs = touched * per_expert / (ms_layer * 1e-3) / 1e9
+            entry.update({"experts_touched": touched, "weight_gb_s": round(gbs, 1),
+                          "pct_hbm_peak": round(100.0 * gbs / measured_peaks()[0]["hbm_gbs"], 2)})
+            route = getattr(layers[0], "_cb_route", "")
+            if isinstance(route, str) and route.startswith("grouped prefill"):
+                tf = 2.0 * int((ids >= 0).sum()) * 3 * inter * hidden / (ms_layer * 1e-3) / 1e12
+                entry.update({"route": route, "tflops": round(tf, 1),
+                              "pct_bf16_peak": round(100.0 * tf / measured_peaks()[0]["bf16_tflops"], 2)})
+        out[str(T)] = entry
     return {"workload": f"routed MoE layer, {E} experts top-{topk}, hidden {hidden}, intermediate {inter}, "
                         f"format {args.format}, T tokens per rank", "scaling": "weak",
             "parallelism": (f"expert-parallel x{world} "

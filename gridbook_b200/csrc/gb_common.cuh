@@ -225,11 +225,12 @@ GB_DEVINL uint64_t gb_extract_bits(Ptr words, uint32_t bit, int k_bits) {
 GB_DEVINL uint64_t gb_extract_bits_bytes(const uint8_t* p, int64_t nbytes_valid,
                                          uint32_t bit, int k_bits) {
   const uint32_t byte0 = bit >> 3, s = bit & 7u;
+  const int nb = (int)(s + (uint32_t)k_bits + 7u) >> 3;     // bytes the field touches
   uint64_t win = 0;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int64_t idx = (int64_t)byte0 + i;
-    const uint64_t v = idx < nbytes_valid ? (uint64_t)p[idx] : 0ull;
+    const uint64_t v = (i < nb && idx < nbytes_valid) ? (uint64_t)p[idx] : 0ull;
     win |= v << (8 * i);
   }
   return (win >> s) & ((1ull << k_bits) - 1ull);

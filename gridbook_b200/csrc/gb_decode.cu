@@ -74,6 +74,7 @@ struct ExpandArgs {
   const void* codebook;
   const int32_t* cb_row_offset;
   const float* compose;
+  const float* weight_scale;   // fp8 grid: per-row scale, indexed by the absolute row
   int64_t row0, nrows, K;
   gb_format fmt;
   GbSplit split;
@@ -89,6 +90,20 @@ GB_DEVINL void gather_values(const ExpandArgs& a, int64_t cb_base, uint64_t code
       return gb_bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(a.codebook)[cb_base + idx]);
   };
   if (a.fmt.mode == GB_MODE_FULL) {
+    if constexpr (!kFp8) {
+      // a full codeword is eight consecutive bf16: one 16-byte load when the block is aligned
+      const uint16_t* entry = reinterpret_cast<const uint16_t*>(a.codebook) + cb_base + (int64_t)code * 8;
+      if ((reinterpret_cast<uintptr_t>(entry) & 15u) == 0) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(entry));
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          val[2 * j] = gb_bf16_bits_to_f32(w[j] & 0xffffu);
+          val[2 * j + 1] = gb_bf16_bits_to_f32(w[j] >> 16);
+        }
+        return;
+      }
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) val[j] = load((int64_t)code * 8 + j);
   } else if (a.fmt.mode == GB_MODE_SIGNED) {
@@ -125,7 +140,7 @@ GB_DEVINL float fp4_group_scale(const ExpandArgs& a, const uint8_t* sb, int v, u
   return s;
 }
 
-enum { kOutFp8 = 0, kOutBf16 = 1, kOutNvfp4 = 2 };
+enum { kOutFp8 = 0, kOutBf16 = 1, kOutNvfp4 = 2, kOutFp8Bf16 = 3 };
 
 template <int kOut>
 __global__ void __launch_bounds__(kThreads)
@@ -134,7 +149,9 @@ expand_kernel(ExpandArgs a, void* __restrict__ out0, uint8_t* __restrict__ out_s
   const int64_t n_sb = a.K / 256;
   const int64_t unit = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
   if (unit >= a.nrows * n_sb) return;
-  const int64_t r = unit / n_sb, s = unit - r * n_sb;
+  // the unit index fits 32 bits whenever the grid does (8 units per CTA): one short division
+  const int64_t r = unit < (1ll << 32) ? (int64_t)((uint32_t)unit / (uint32_t)n_sb) : unit / n_sb;
+  const int64_t s = unit - r * n_sb;
   const int64_t row = a.row0 + r;
   const int64_t sb_off = r * a.row_stride + s * a.fmt.type_size;
   const uint8_t* sb = a.qw + sb_off;   // a.qw is the first byte of row0
@@ -142,7 +159,7 @@ expand_kernel(ExpandArgs a, void* __restrict__ out0, uint8_t* __restrict__ out_s
       gb_extract_bits_bytes(sb, a.valid_bytes - sb_off, (uint32_t)(lane * a.fmt.k_bits), a.fmt.k_bits);
   const int64_t cb_base = a.cb_row_offset ? (int64_t)a.cb_row_offset[row] : 0;
   float val[8];
-  gather_values<kOut == kOutFp8>(a, cb_base, code, val);
+  gather_values<kOut == kOutFp8 || kOut == kOutFp8Bf16>(a, cb_base, code, val);
   const int64_t col = s * 256 + lane * 8;
 
   if constexpr (kOut == kOutFp8) {
@@ -153,6 +170,16 @@ expand_kernel(ExpandArgs a, void* __restrict__ out0, uint8_t* __restrict__ out_s
       hi |= gb_f32_to_e4m3(val[4 + j]) << (8 * j);
     }
     *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(out0) + r * a.K + col) = make_uint2(lo, hi);
+  } else if constexpr (kOut == kOutFp8Bf16) {
+    // the served fp8-grid weight: bf16(value * row scale)
+    const float scale = a.weight_scale[row];
+    uint32_t p[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      p[j] = gb_f32_to_bf16_bits(__fmul_rn(val[2 * j], scale)) |
+             (gb_f32_to_bf16_bits(__fmul_rn(val[2 * j + 1], scale)) << 16);
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out0) + r * a.K + col) =
+        make_uint4(p[0], p[1], p[2], p[3]);
   } else if constexpr (kOut == kOutBf16) {
     uint32_t sbyte;
     const float scale = fp4_group_scale(a, sb, lane, &sbyte);
@@ -198,6 +225,7 @@ int make_expand_args(const gb_weight* w, int64_t row0, int64_t nrows, ExpandArgs
   a->codebook = w->codebook;
   a->cb_row_offset = w->cb_row_offset;
   a->compose = w->compose;
+  a->weight_scale = w->weight_scale;
   a->row0 = row0;
   a->nrows = nrows;
   a->K = w->K;
@@ -259,6 +287,11 @@ extern "C" {
 int gb_expand_fp8(const gb_weight* w, int64_t row0, int64_t nrows, void* out, void* stream) {
   GB_REQUIRE(w && w->fmt.grid == GB_GRID_FP8, "gb_expand_fp8 wants an fp8-grid weight");
   return launch_expand<kOutFp8>(w, row0, nrows, out, nullptr, 0, stream);
+}
+
+int gb_expand_fp8_bf16(const gb_weight* w, int64_t row0, int64_t nrows, void* out, void* stream) {
+  GB_REQUIRE(w && w->fmt.grid == GB_GRID_FP8 && w->weight_scale, "gb_expand_fp8_bf16 wants an fp8-grid weight with its row scales");
+  return launch_expand<kOutFp8Bf16>(w, row0, nrows, out, nullptr, 0, stream);
 }
 
 int gb_expand_fp4_bf16(const gb_weight* w, int64_t row0, int64_t nrows, void* out, void* stream) {

@@ -11,6 +11,13 @@
 // the epilogue warps drain one, the MMAs of the next tile already fill the other, and the
 // TMA ring never drains between tiles.  B is the decoded weight tile the expanders write (gb_expand_fp8 /
 // gb_expand_fp4_bf16); A is the bucketed activation matrix.
+//
+// Grouped mode (routed prefill): A holds the routed rows sorted by expert, B the decoded stack
+// [E*N, K]; expert e owns rows [seg[e], seg[e+1]) of A.  Every CTA builds the per-expert tile
+// prefix from the device-side segment offsets (no host read), walks tiles N fastest so the CTAs
+// running together share an expert's decoded weights through L2, and the epilogue masks the
+// rows past the segment end (a row tile may run into the next expert's rows) and can scatter
+// its rows through a row map.
 #include "gb_common.cuh"
 
 #include <cuda.h>
@@ -25,6 +32,8 @@ constexpr int kStages = 4;
 constexpr int kTmemCols = 512;                     // two 128 x 256 fp32 accumulators
 constexpr int kGemmThreads = 192;
 constexpr int kGemmSmem = kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
+constexpr int kMaxGroups = 1024;                   // experts of one grouped launch
+constexpr int kGroupSmem = 2 * (kMaxGroups + 1) * 4 + 8;   // segment offsets + row-tile prefix
 
 struct GemmParams {
   int64_t M, N, K;
@@ -37,7 +46,42 @@ struct GemmParams {
   float global_scale;
   uint16_t* D;
   int* status;
+  // grouped mode
+  const int32_t* seg;        // [E+1] first sorted row of every expert, seg[E] = routed rows
+  const int32_t* row_map;    // [P] output row of a sorted row, or null = identity
+  int E;
 };
+
+// One output tile of either mode: first A row, end of the valid rows, first B row, first
+// output column, and the B-scale offset of the expert.
+struct Tile {
+  int m0, m_end, b_row0, n0, scale0;
+};
+
+template <bool kGrouped>
+GB_DEVINL Tile tile_of(const GemmParams& p, int tile, const int* seg_s, const int* base_s) {
+  Tile t;
+  if (!kGrouped) {
+    t.m0 = (tile % p.m_tiles) * kBM;
+    t.n0 = (tile / p.m_tiles) * kBN;
+    t.m_end = (int)p.M;
+    t.b_row0 = t.n0;
+    t.scale0 = 0;
+  } else {
+    const int gm = tile / p.n_tiles;
+    t.n0 = (tile % p.n_tiles) * kBN;
+    int lo = 0, hi = p.E;                 // largest e with base_s[e] <= gm
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (base_s[mid] <= gm) lo = mid; else hi = mid;
+    }
+    t.m0 = seg_s[lo] + (gm - base_s[lo]) * kBM;
+    t.m_end = seg_s[lo + 1];
+    t.scale0 = lo * (int)p.N;
+    t.b_row0 = t.scale0 + t.n0;
+  }
+  return t;
+}
 
 GB_DEVINL void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
   asm volatile(
@@ -85,6 +129,7 @@ GB_DEVINL void wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort
   }
 }
 
+template <bool kGrouped>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const GemmParams p) {
@@ -97,10 +142,34 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint64_t* acc_empty = acc_full + 2;                // [2] accumulator drained (four epilogue warps)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* seg_s = reinterpret_cast<int*>(smem + kStages * kStageBytes + 256);   // [E+1], grouped mode
+  int* base_s = seg_s + kMaxGroups + 1;                                       // [E+1] row-tile prefix
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool fp8 = p.elem_bytes == 1;
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  if (kGrouped && warp == 0) {
+    // row tiles of expert e: ceil(rows / 128); exclusive prefix by one warp, 32 experts a pass
+    int carry = 0;
+    for (int e0 = 0; e0 < p.E; e0 += 32) {
+      const int e = e0 + lane;
+      const int lo = e < p.E ? p.seg[e] : 0, hi = e < p.E ? p.seg[e + 1] : 0;
+      int tiles = (hi - lo + kBM - 1) / kBM, incl = tiles;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      if (e < p.E) {
+        seg_s[e] = lo;
+        base_s[e] = carry + incl - tiles;
+      }
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) {
+      seg_s[p.E] = p.seg[p.E];
+      base_s[p.E] = carry;
+    }
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -123,6 +192,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = kGrouped ? base_s[p.E] * p.n_tiles : p.m_tiles * p.n_tiles;
 
   // Every role walks the same tile sequence: tile = blockIdx.x, + gridDim.x, ...; M tiles vary
   // fastest, so the CTAs working at the same time share a few B (weight) tiles and sweep A,
@@ -133,14 +203,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int slab_elems = kSlabBytes / p.elem_bytes;
       int kk = 0;                                        // K slabs issued so far, over all tiles
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-        const int m0 = (tile % p.m_tiles) * kBM, n0 = (tile / p.m_tiles) * kBN;
+        const Tile t = tile_of<kGrouped>(p, tile, seg_s, base_s);
         for (int kt = 0; kt < p.k_tiles; ++kt, ++kk) {
           const int s = kk % kStages;
           wait_or_abort(&empty_bar[s], ((kk / kStages) & 1) ^ 1, abort_flag, p.status, 11);
           gb_mbar_expect_tx(&full_bar[s], kStageBytes);
           uint8_t* a_dst = ring + (size_t)s * kStageBytes;
-          tma_load_2d(a_dst, &map_a, kt * slab_elems, m0, &full_bar[s]);
-          tma_load_2d(a_dst + kBM * kSlabBytes, &map_b, kt * slab_elems, n0, &full_bar[s]);
+          tma_load_2d(a_dst, &map_a, kt * slab_elems, t.m0, &full_bar[s]);
+          tma_load_2d(a_dst + kBM * kSlabBytes, &map_b, kt * slab_elems, t.b_row0, &full_bar[s]);
         }
       }
     }
@@ -173,11 +243,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int it = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
       const int buf = it & 1;
-      const int m0 = (tile % p.m_tiles) * kBM, n0 = (tile / p.m_tiles) * kBN;
+      const Tile t = tile_of<kGrouped>(p, tile, seg_s, base_s);
+      const int n0 = t.n0;
       wait_or_abort(&acc_full[buf], (it >> 1) & 1, abort_flag, p.status, 13);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int64_t row = (int64_t)m0 + warp * 32 + lane;
-      const float rs = (p.a_scale && row < p.M ? p.a_scale[row] : 1.0f) * p.global_scale;
+      const int64_t row = (int64_t)t.m0 + warp * 32 + lane;
+      const bool row_ok = row < t.m_end;
+      const float rs = (p.a_scale && row_ok ? p.a_scale[row] : 1.0f) * p.global_scale;
+      const float* b_scale = p.b_scale ? p.b_scale + t.scale0 : nullptr;
+      const int64_t out_row = kGrouped && p.row_map && row_ok ? p.row_map[row] : row;
 #pragma unroll 1
       for (int c0 = 0; c0 < kBN; c0 += 32) {
         uint32_t v[32];
@@ -198,8 +272,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           __syncwarp();
           if (lane == 0) gb_mbar_arrive(&acc_empty[buf]);
         }
-        if (row < p.M) {
-          uint16_t* out = p.D + row * p.N + n0 + c0;
+        if (row_ok) {
+          uint16_t* out = p.D + out_row * p.N + n0 + c0;
           const int64_t ncol = p.N - (n0 + c0);
           if (ncol >= 32 && (p.N % 8) == 0) {
 #pragma unroll
@@ -208,8 +282,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const int c = q * 8 + j * 2;
-                const float s0 = p.b_scale ? p.b_scale[n0 + c0 + c] : 1.0f;
-                const float s1 = p.b_scale ? p.b_scale[n0 + c0 + c + 1] : 1.0f;
+                const float s0 = b_scale ? b_scale[n0 + c0 + c] : 1.0f;
+                const float s1 = b_scale ? b_scale[n0 + c0 + c + 1] : 1.0f;
                 w[j] = gb_f32_to_bf16_bits(__uint_as_float(v[c]) * rs * s0) |
                        (gb_f32_to_bf16_bits(__uint_as_float(v[c + 1]) * rs * s1) << 16);
               }
@@ -217,7 +291,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
           } else {
             for (int c = 0; c < 32 && c < ncol; ++c) {
-              const float s0 = p.b_scale ? p.b_scale[n0 + c0 + c] : 1.0f;
+              const float s0 = b_scale ? b_scale[n0 + c0 + c] : 1.0f;
               out[c] = (uint16_t)gb_f32_to_bf16_bits(__uint_as_float(v[c]) * rs * s0);
             }
           }
@@ -259,6 +333,49 @@ fp8_quantize_rows_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ q
   for (int64_t i = threadIdx.x; i < K; i += blockDim.x) {
     const float v = gb_bf16_bits_to_f32(row[i]);
     qrow[i] = (uint8_t)gb_f32_to_e4m3(fminf(fmaxf(__fdiv_rn(v, scale), -448.0f), 448.0f));
+  }
+}
+
+// ---- routed prefill helpers: rows in expert order ---------------------------------------
+// out[j] = x[x_row[order[j]]] (or x[order[j]] without x_row) for the sorted rows j < *n_rows.
+__global__ void __launch_bounds__(128)
+moe_gather_rows_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ x_row,
+                       const int32_t* __restrict__ order, const int32_t* __restrict__ n_rows, int vecs,
+                       uint4* __restrict__ out) {
+  const int j = blockIdx.x;
+  if (j >= *n_rows) return;
+  const int pair = order[j];
+  const int64_t src = x_row ? x_row[pair] : pair;
+  const uint4* in = x + src * vecs;
+  uint4* o = out + (int64_t)j * vecs;
+  for (int i = threadIdx.x; i < vecs; i += blockDim.x) o[i] = in[i];
+}
+
+// out[j][c] = bf16(bf16(silu(gate)) * up), gate = h[j][c], up = h[j][inter + c]: every torch bf16
+// op of the reference chain rounds (F.silu on bf16, then a bf16 multiply).
+__global__ void __launch_bounds__(128)
+moe_swiglu_rows_kernel(const uint4* __restrict__ h, const int32_t* __restrict__ n_rows, int vecs,
+                       uint4* __restrict__ out) {
+  const int j = blockIdx.x;
+  if (j >= *n_rows) return;
+  const uint4* row = h + (int64_t)j * 2 * vecs;
+  for (int i = threadIdx.x; i < vecs; i += blockDim.x) {
+    const uint4 g = row[i], u = row[vecs + i];
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t r[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t packed = 0;
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        const float gate = gb_bf16_bits_to_f32((gw[q] >> (16 * hlf)) & 0xffffu);
+        const float up = gb_bf16_bits_to_f32((uw[q] >> (16 * hlf)) & 0xffffu);
+        const float sl = gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(gate / (1.0f + __expf(-gate))));
+        packed |= gb_f32_to_bf16_bits(sl * up) << (16 * hlf);
+      }
+      r[q] = packed;
+    }
+    out[(int64_t)j * vecs + i] = make_uint4(r[0], r[1], r[2], r[3]);
   }
 }
 
@@ -320,7 +437,10 @@ int gb_tensor_map_bytes_2d(void* map_out, const void* base, uint64_t inner_bytes
 }
 
 int gb_prepare_gemm() {
-  GB_CUDA_OK(cudaFuncSetAttribute((const void*)gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
+  GB_CUDA_OK(cudaFuncSetAttribute((const void*)gemm_tn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kGemmSmem));
+  GB_CUDA_OK(cudaFuncSetAttribute((const void*)gemm_tn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kGemmSmem + kGroupSmem));
   return GB_OK;
 }
 
@@ -371,8 +491,79 @@ int gb_gemm_tn(const void* A, const void* B, void* D, int64_t M, int64_t N, int6
   const int sms = gb_sm_count();
   dim3 grid((unsigned)(tiles < sms ? tiles : sms));          // persistent: one CTA per SM
   gb_count_launch();
-  gemm_tn_kernel<<<grid, kGemmThreads, kGemmSmem, (cudaStream_t)stream>>>(map_a, map_b, p);
+  gemm_tn_kernel<false><<<grid, kGemmThreads, kGemmSmem, (cudaStream_t)stream>>>(map_a, map_b, p);
   GB_LAUNCH_OK("gemm_tn_kernel");
+  return GB_OK;
+}
+
+int gb_gemm_tn_grouped(const void* A, const void* B, void* D, int64_t P, int64_t N, int64_t K, int kind, int64_t E,
+                       const int32_t* seg_offsets, const int32_t* row_map, const float* a_scale, const float* b_scale,
+                       float global_scale, void* stream) {
+  GB_REQUIRE(A && B && D && seg_offsets, "null pointer argument");
+  GB_REQUIRE(kind == GB_GEMM_BF16 || kind == GB_GEMM_E4M3, "unknown gemm kind %d", kind);
+  const int eb = kind == GB_GEMM_BF16 ? 2 : 1;
+  GB_REQUIRE(P >= 0 && N > 0 && K > 0 && (K * eb) % kSlabBytes == 0, "K=%lld must be a multiple of %d elements",
+             (long long)K, kSlabBytes / eb);
+  GB_REQUIRE(E > 0 && E <= kMaxGroups, "expert count %lld outside [1, %d]", (long long)E, kMaxGroups);
+  GB_REQUIRE(((uintptr_t)A & 15u) == 0 && ((uintptr_t)B & 15u) == 0 && ((uintptr_t)D & 15u) == 0,
+             "operands must be 16-byte aligned");
+  GB_REQUIRE(P < (1ll << 30) && E * N < (1ll << 31) && K < (1ll << 31), "dimension too large");
+  if (P == 0) return GB_OK;
+  if (gb_sm_count() <= 0) return gb_fail(GB_ECUDA, "no usable CUDA device: %s", gb_last_error());
+  CUtensorMap map_a, map_b;
+  int rc = make_map(&map_a, A, P, K, eb, kBM);
+  if (rc != GB_OK) return rc;
+  rc = make_map(&map_b, B, E * N, K, eb, kBN);
+  if (rc != GB_OK) return rc;
+  GemmParams p = {};
+  p.M = P; p.N = N; p.K = K;
+  p.k_tiles = (int)(K * eb / kSlabBytes);
+  p.m_tiles = 0;                                   // counted on the device from seg_offsets
+  p.n_tiles = (int)((N + kBN - 1) / kBN);
+  p.elem_bytes = eb;
+  p.idesc = (1u << 4) | ((kind == GB_GEMM_BF16 ? 1u : 0u) << 7) | ((kind == GB_GEMM_BF16 ? 1u : 0u) << 10) |
+            ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+  p.a_scale = a_scale; p.b_scale = b_scale;
+  p.global_scale = global_scale == 0.0f ? 1.0f : global_scale;
+  p.D = (uint16_t*)D;
+  p.status = gb_status_word();
+  p.seg = seg_offsets; p.row_map = row_map; p.E = (int)E;
+  // at most ceil(P/128) + E row tiles, whatever the routing
+  const int64_t tiles = ((P + kBM - 1) / kBM + E) * p.n_tiles;
+  GB_REQUIRE(tiles < (1ll << 31), "too many output tiles");
+  const int sms = gb_sm_count();
+  dim3 grid((unsigned)(tiles < sms ? tiles : sms));
+  gb_count_launch();
+  gemm_tn_kernel<true><<<grid, kGemmThreads, kGemmSmem + kGroupSmem, (cudaStream_t)stream>>>(map_a, map_b, p);
+  GB_LAUNCH_OK("gemm_tn_kernel<grouped>");
+  return GB_OK;
+}
+
+int gb_moe_gather_rows(const void* x, const int32_t* x_row, const int32_t* order, const int32_t* seg_offsets,
+                       int64_t E, int64_t P, int64_t K, void* out, void* stream) {
+  GB_REQUIRE(x && order && seg_offsets && out, "null pointer argument");
+  GB_REQUIRE(P >= 0 && E > 0 && K > 0 && K % 8 == 0, "bad shape P=%lld E=%lld K=%lld", (long long)P, (long long)E,
+             (long long)K);
+  GB_REQUIRE(((uintptr_t)x & 15u) == 0 && ((uintptr_t)out & 15u) == 0, "rows must be 16-byte aligned");
+  if (P == 0) return GB_OK;
+  gb_count_launch();
+  moe_gather_rows_kernel<<<(unsigned)P, 128, 0, (cudaStream_t)stream>>>(
+      (const uint4*)x, x_row, order, seg_offsets + E, (int)(K / 8), (uint4*)out);
+  GB_LAUNCH_OK("moe_gather_rows_kernel");
+  return GB_OK;
+}
+
+int gb_moe_swiglu_rows(const void* h, const int32_t* seg_offsets, int64_t E, int64_t P, int64_t inter, void* out,
+                       void* stream) {
+  GB_REQUIRE(h && seg_offsets && out, "null pointer argument");
+  GB_REQUIRE(P >= 0 && E > 0 && inter > 0 && inter % 8 == 0, "bad shape P=%lld E=%lld inter=%lld", (long long)P,
+             (long long)E, (long long)inter);
+  GB_REQUIRE(((uintptr_t)h & 15u) == 0 && ((uintptr_t)out & 15u) == 0, "rows must be 16-byte aligned");
+  if (P == 0) return GB_OK;
+  gb_count_launch();
+  moe_swiglu_rows_kernel<<<(unsigned)P, 128, 0, (cudaStream_t)stream>>>((const uint4*)h, seg_offsets + E,
+                                                                       (int)(inter / 8), (uint4*)out);
+  GB_LAUNCH_OK("moe_swiglu_rows_kernel");
   return GB_OK;
 }
 

@@ -11,8 +11,8 @@ constexpr int kRouteThreads = 1024;
 __global__ void __launch_bounds__(kRouteThreads)
 moe_route_kernel(const int32_t* __restrict__ ids, int P, int E, int first_expert, int32_t* __restrict__ counts,
                  int32_t* __restrict__ offsets, int32_t* __restrict__ order,
-                 const float* __restrict__ weights, float* __restrict__ pair_w) {
-  extern __shared__ int32_t sh[];   // [E] counts, [E+1] offsets
+                 const float* __restrict__ weights, float* __restrict__ pair_w, int tiled) {
+  extern __shared__ int32_t sh[];   // [E] counts, [E+1] offsets; tiled: + [E][32] + [E]
   int32_t* cnt = sh;
   int32_t* off = sh + E;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = kRouteThreads / 32;
@@ -49,16 +49,55 @@ moe_route_kernel(const int32_t* __restrict__ ids, int P, int E, int first_expert
   for (int e = tid; e < E; e += kRouteThreads) counts[e] = cnt[e];
   for (int e = tid; e <= E; e += kRouteThreads) offsets[e] = off[e];
   for (int i = off[E] + tid; i < P; i += kRouteThreads) order[i] = 0;   // dropped (padding) pairs
-  for (int e = warp; e < E; e += nwarps) {
-    if (cnt[e] == 0) continue;
-    int pos = off[e];
-    for (int base = 0; base < P; base += 32) {
-      const int i = base + lane;
-      const bool hit = i < P && ids[i] - first_expert == e;
-      const unsigned mask = __ballot_sync(0xffffffffu, hit);
-      if (hit) order[pos + __popc(mask & ((1u << lane) - 1u))] = i;
-      pos += __popc(mask);
+  if (!tiled) {
+    for (int e = warp; e < E; e += nwarps) {
+      if (cnt[e] == 0) continue;
+      int pos = off[e];
+      for (int base = 0; base < P; base += 32) {
+        const int i = base + lane;
+        const bool hit = i < P && ids[i] - first_expert == e;
+        const unsigned mask = __ballot_sync(0xffffffffu, hit);
+        if (hit) order[pos + __popc(mask & ((1u << lane) - 1u))] = i;
+        pos += __popc(mask);
+      }
     }
+    return;
+  }
+  // Many pairs: walk them in tiles of one pair per thread, in pair order.  Inside a tile a pair's
+  // place among its expert's pairs = (pairs of that expert in earlier warps) + (its rank among
+  // the warp's lanes with the same expert); wcnt[e][w] holds warp w's count, then its start.
+  int32_t* wcnt = off + E + 1;            // [E][32]
+  int32_t* cursor = wcnt + E * nwarps;    // [E] next free place of every expert
+  for (int e = tid; e < E; e += kRouteThreads) cursor[e] = off[e];
+  for (int base = 0; base < P; base += kRouteThreads) {
+    for (int k = tid; k < E * nwarps; k += kRouteThreads) wcnt[k] = 0;
+    __syncthreads();
+    const int i = base + tid;
+    int id = -1;
+    if (i < P) {
+      const int v = ids[i] - first_expert;
+      if (v >= 0 && v < E) id = v;
+    }
+    const unsigned same = __match_any_sync(0xffffffffu, id);
+    const int rank = __popc(same & ((1u << lane) - 1u));
+    if (id >= 0 && rank == 0) wcnt[id * nwarps + warp] = __popc(same);
+    __syncthreads();
+    for (int e = warp; e < E; e += nwarps) {          // lane w scans warp w's count of expert e
+      const int v = wcnt[e * nwarps + lane];
+      int incl = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += n;
+      }
+      const int start = cursor[e];
+      wcnt[e * nwarps + lane] = start + incl - v;
+      __syncwarp();
+      if (lane == 31) cursor[e] = start + incl;
+    }
+    __syncthreads();
+    if (id >= 0) order[wcnt[id * nwarps + warp] + rank] = i;
+    __syncthreads();
   }
 }
 
@@ -143,9 +182,13 @@ int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E, in
   GB_REQUIRE(T >= 0 && topk >= 1 && E >= 1 && E <= 4096, "bad routing shape T=%lld topk=%lld E=%lld",
              (long long)T, (long long)topk, (long long)E);
   GB_REQUIRE(T * topk < (1ll << 30), "too many routed pairs");
-  GB_CUDA_OK(gb_launch(moe_route_kernel, dim3(1), dim3(kRouteThreads), (size_t)(2 * E + 1) * sizeof(int32_t),
-                       (cudaStream_t)stream, topk_ids, (int)(T * topk), (int)E, (int)expert_base, counts, offsets,
-                       order, topk_weights, pair_w));
+  // a warp per expert scanning all pairs costs E*P; from a few thousand pairs on, tiles of
+  // 1024 pairs in pair order are cheaper (the per-warp counts need E*33 words of shared memory)
+  const int tiled = T * topk >= 4096 && E <= 256;
+  const size_t smem = (size_t)(2 * E + 1 + (tiled ? E * (kRouteThreads / 32 + 1) : 0)) * sizeof(int32_t);
+  GB_CUDA_OK(gb_launch(moe_route_kernel, dim3(1), dim3(kRouteThreads), smem, (cudaStream_t)stream, topk_ids,
+                       (int)(T * topk), (int)E, (int)expert_base, counts, offsets, order, topk_weights, pair_w,
+                       tiled));
   return GB_OK;
 }
 

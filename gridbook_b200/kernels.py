@@ -122,6 +122,17 @@ def expand_fp8(w: PackedWeight, row0: int = 0, nrows: int | None = None) -> torc
     return out
 
 
+def expand_fp8_bf16(w: PackedWeight, row0: int = 0, nrows: int | None = None) -> torch.Tensor:
+    """The served fp8-grid weight bf16(value * row scale) as a [nrows, K] bf16 tile."""
+    lib = nat.load("FP8-CB transient expansion to bf16")
+    nrows = w.rows - row0 if nrows is None else nrows
+    out = torch.empty((nrows, w.K), dtype=torch.bfloat16, device=w.qw.device)
+    nw = w.native()
+    nat.check(lib.gb_expand_fp8_bf16(ctypes.byref(nw), row0, nrows, _ptr(out),
+                                     nat.stream_ptr(w.qw.device)), lib)
+    return out
+
+
 def expand_fp4_bf16(w: PackedWeight, row0: int = 0, nrows: int | None = None) -> torch.Tensor:
     lib = nat.load("FP4-CB transient expansion")
     nrows = w.rows - row0 if nrows is None else nrows
@@ -346,3 +357,69 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a_scale=None, b_scale=None, glo
     nat.check(lib.gb_gemm_tn(_ptr(a), _ptr(b), _ptr(out), M, N, K, kind, _ptr(a_scale), _ptr(b_scale),
                              float(global_scale), nat.stream_ptr(a.device)), lib)
     return out
+
+
+def gemm_tn_grouped(a: torch.Tensor, b: torch.Tensor, offsets: torch.Tensor, n_per_expert: int, *,
+                    row_map: torch.Tensor | None = None, a_scale=None, b_scale=None,
+                    global_scale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Grouped GEMM over expert segments: ``a`` [P, K] rows sorted by expert (expert e owns rows
+    ``offsets[e]:offsets[e+1]``), ``b`` [E * n_per_expert, K] the decoded stack; -> [P, n_per_expert]
+    bf16, row j at ``row_map[j]`` (or j).  Rows past ``offsets[E]`` are left unwritten."""
+    _need_cuda(a, b, offsets, row_map, a_scale, b_scale)
+    lib = nat.load("grouped prefill tensor-core GEMM")
+    if a.dtype is not b.dtype or a.dtype not in (torch.bfloat16, torch.float8_e4m3fn):
+        raise TypeError("gemm_tn_grouped takes two bf16 or two float8_e4m3fn operands")
+    a, b = a.contiguous(), b.contiguous()
+    P, K = a.shape
+    E = offsets.numel() - 1
+    if b.shape != (E * n_per_expert, K):
+        raise RuntimeError(f"gemm_tn_grouped: decoded stack is {tuple(b.shape)}, expected {(E * n_per_expert, K)}")
+    if out is None:
+        out = torch.empty((P, n_per_expert), dtype=torch.bfloat16, device=a.device)
+    kind = nat.GEMM_BF16 if a.dtype is torch.bfloat16 else nat.GEMM_E4M3
+    nat.check(lib.gb_gemm_tn_grouped(_ptr(a), _ptr(b), _ptr(out), P, n_per_expert, K, kind, E, _ptr(offsets),
+                                     _ptr(row_map), _ptr(a_scale), _ptr(b_scale), float(global_scale),
+                                     nat.stream_ptr(a.device)), lib)
+    return out
+
+
+def moe_gather_rows(x: torch.Tensor, order: torch.Tensor, offsets: torch.Tensor, *,
+                    x_row: torch.Tensor | None = None) -> torch.Tensor:
+    """The routed rows of ``x`` [T, K] bf16 in expert order: out[j] = x[x_row[order[j]]] for
+    j < offsets[E]; later rows are left unset."""
+    _need_cuda(x, order, offsets, x_row)
+    lib = nat.load("routed row gather")
+    if x.dtype is not torch.bfloat16:
+        raise TypeError("moe_gather_rows takes bf16 rows")
+    x = x.contiguous()
+    P, K = order.numel(), x.shape[-1]
+    out = torch.empty((P, K), dtype=torch.bfloat16, device=x.device)
+    nat.check(lib.gb_moe_gather_rows(_ptr(x), _ptr(x_row), _ptr(order), _ptr(offsets), offsets.numel() - 1, P, K,
+                                     _ptr(out), nat.stream_ptr(x.device)), lib)
+    return out
+
+
+def moe_swiglu_rows(h: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
+    """bf16 silu(gate) * up over the sorted rows: h [P, 2I] -> [P, I] (rows past offsets[E] unset)."""
+    _need_cuda(h, offsets)
+    lib = nat.load("routed SwiGLU")
+    if h.dtype is not torch.bfloat16:
+        raise TypeError("moe_swiglu_rows takes bf16 rows")
+    h = h.contiguous()
+    P, two_i = h.shape
+    out = torch.empty((P, two_i // 2), dtype=torch.bfloat16, device=h.device)
+    nat.check(lib.gb_moe_swiglu_rows(_ptr(h), _ptr(offsets), offsets.numel() - 1, P, two_i // 2, _ptr(out),
+                                     nat.stream_ptr(h.device)), lib)
+    return out
+
+
+def stack_rows(w: PackedWeight) -> PackedWeight:
+    """An expert stack [E, rows, bytes] seen as one matrix of E * rows rows (the experts are
+    contiguous), for the expanders."""
+    if w.experts == 1:
+        return w
+    if w.expert_stride != w.rows * w.row_stride or w.cb_row_offset is not None:
+        raise RuntimeError("the expert stack is not one contiguous matrix with a single codebook")
+    ws = None if w.weight_scale is None else w.weight_scale.reshape(-1)
+    return PackedWeight(w.qw, w.codebook, w.fmt, w.K, w.experts * w.rows, w.row_stride, w.cb_row_offset,
+                        w.compose, ws, w.global_scale)

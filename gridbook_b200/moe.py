@@ -3,6 +3,7 @@
 routing, grouped codebook GEMV with fused SwiGLU, top-k weighted combine."""
 from __future__ import annotations
 
+import os
 import sys
 
 import torch
@@ -15,6 +16,13 @@ from .formats import CBFormat
 
 PAIR_KERNEL_MAX_PAIRS = 768       # routed pairs up to which every pair runs as its own table GEMV
 FUSED_BUCKET_MAX_PAIRS = 32       # routed pairs up to which the grouped kernel buckets its own rows
+# From this many routed pairs per expert (on average) the routed layer decodes each stack once
+# and runs grouped tensor-core GEMMs instead of the decode kernel's 16-row passes.
+PREFILL_MIN_PAIRS_PER_EXPERT = 72
+
+
+def prefill_min_pairs_per_expert() -> int:
+    return int(os.environ.get("GRIDBOOK_B200_MOE_PREFILL_MIN", PREFILL_MIN_PAIRS_PER_EXPERT))
 
 
 def _row_bytes(in_features: int, type_size: int) -> int:
@@ -175,9 +183,12 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
             return torch.empty_like(x)
         x2 = x.reshape(T, -1).to(torch.bfloat16).contiguous()
         ids = topk_ids.to(torch.int32).contiguous()
+        if T * topk >= prefill_min_pairs_per_expert() * layer._cb_E:
+            return self._apply_prefill(layer, x2, topk_weights, ids, rule).to(x.dtype).reshape(x.shape)
         if T * topk <= PAIR_KERNEL_MAX_PAIRS and self.fmt13.is_fp4 and self.fmt2.is_fp4:
             out = self._apply_pairs(layer, x2, topk_weights, ids, rule)
             if out is not None:
+                layer._cb_route = "per-pair table kernel"
                 return out.to(x.dtype).reshape(x.shape)
         # the loop chain multiplies by the bf16-rounded router weight (gridbook/moe.py:2407-2408);
         # the routing launch writes it, zeroed for padded pairs
@@ -200,8 +211,41 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
             bucket2 = kernels.fp4_act_qdq if self.fmt2.is_fp4 else kernels.fp8_act_qdq
             y = kernels.moe_gemv(bucket2(a, rule), layer._cb_w2, offsets, order, clear=False)
         out = kernels.moe_combine(y, pair_w, T, topk, topk_ids=ids, E=layer._cb_E)
+        layer._cb_route = "grouped decode kernel"
         return out.to(x.dtype).reshape(x.shape)
 
+
+    def _apply_prefill(self, layer, x2, topk_weights, ids, rule):
+        """Many tokens per expert: decode each stack once into a transient bf16 tile of the exact
+        served weights and run one grouped tensor-core GEMM over the expert segments per
+        projection (tcgen05 kind::f16, accumulators in tensor memory; segment offsets stay on the
+        device) - the reference's grouped bf16 route (gridbook/moe.py:2388-2504 with
+        gridbook/ops.py:137-306).  Both grids keep the decode contract here (bucketed bf16 rows,
+        per-weight bf16(value * scale)): the buckets between the two projections are coarse
+        enough to turn a last-place difference of the first projection into whole quantisation
+        steps, so the fp8 grid does not take the scales-in-the-epilogue E4M3 GEMM of the dense
+        prefill."""
+        T, topk = ids.shape
+        E = layer._cb_E
+        _, offsets, order, pair_w = kernels.moe_route(ids, E, topk_weights)
+        x_row = self._x_row(layer, T, topk, x2.device)
+
+        def bucket(rows, w):
+            return (kernels.fp4_act_qdq if w.fmt.is_fp4 else kernels.fp8_act_qdq)(rows, rule)
+
+        def stage(rows_sorted, w, row_map):
+            wm = kernels.stack_rows(w)
+            tile = kernels.expand_fp4_bf16(wm) if w.fmt.is_fp4 else kernels.expand_fp8_bf16(wm)
+            return kernels.gemm_tn_grouped(rows_sorted, tile, offsets, w.rows, row_map=row_map,
+                                           global_scale=w.global_scale)
+
+        w13, w2 = layer._cb_w13, layer._cb_w2
+        # bucket the T rows once, then bring them into expert order
+        a = kernels.moe_gather_rows(bucket(x2, w13), order, offsets, x_row=x_row)
+        h = kernels.moe_swiglu_rows(stage(a, w13, None), offsets)
+        y = stage(bucket(h, w2), w2, order)                   # rows back in pair order
+        layer._cb_route = "grouped prefill: expand + gemm_tn_grouped"
+        return kernels.moe_combine(y, pair_w, T, topk, topk_ids=ids, E=E)
 
     def _apply_pairs(self, layer, x2, topk_weights, ids, rule):
         """Small batches of the literal format: every routed pair is its own M = 1 linear through

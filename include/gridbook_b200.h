@@ -90,6 +90,11 @@ GB_API int gb_fp4_act_qdq(const void* x_bf16, void* out_bf16, int64_t M, int64_t
  * rows [row0, row0+nrows) -> [nrows, K] E4M3 bytes */
 GB_API int gb_expand_fp8(const gb_weight* w, int64_t row0, int64_t nrows, void* out_e4m3,
                   void* stream);
+/* The served fp8-grid weight of rows [row0, row0+nrows): -> [nrows, K] bf16 =
+ * bf16(value * weight_scale[row]), the per-weight rounding of the decode contract
+ * (gridbook/csrc/cb_gemv.cu:20-27,219-228), for bf16 tensor-core routes that must keep it. */
+GB_API int gb_expand_fp8_bf16(const gb_weight* w, int64_t row0, int64_t nrows, void* out_bf16,
+                              void* stream);
 /* replaces cb_expand_v2 (gridbook/csrc/cb_gemv_v2.cu:374-439,802-863, gridbook/ops.py:119-134)
  * for every fp4 mode and scale coding: -> [nrows, K] bf16 = bf16(value * group scale) */
 GB_API int gb_expand_fp4_bf16(const gb_weight* w, int64_t row0, int64_t nrows, void* out_bf16,
@@ -146,6 +151,29 @@ GB_API int gb_fp8_quantize_rows(const void* x_bf16, void* q_e4m3, float* scale, 
  * gridbook/csrc/cb_fused_gemm.cu:476-486). */
 GB_API int gb_gemm_tn(const void* A, const void* B, void* D_bf16, int64_t M, int64_t N, int64_t K, int kind,
                       const float* a_scale, const float* b_scale, float global_scale, void* stream);
+/* The same GEMM over expert segments (routed prefill): A [P,K] holds the routed rows sorted by
+ * expert, expert e owning rows [seg_offsets[e], seg_offsets[e+1]) (gb_moe_route's offsets, read
+ * on the device: no host read); B [E*N,K] is the decoded stack (gb_expand_* over all E*N rows);
+ * sorted row j of expert e gets D[r, n] = global_scale * a_scale[j] * b_scale[e*N+n] * <A[j], B[e*N+n]>
+ * with r = row_map[j] (row_map = gb_moe_route's order puts the result in pair order) or r = j
+ * when row_map is NULL.  Rows at or past seg_offsets[E] are neither read into a result nor
+ * written.  E <= 1024.  Replaces the grouped bf16 GEMM over expert segments and the grouped
+ * decode-in-mainloop prefill (gridbook/ops.py:137-306,309-428;
+ * gridbook/csrc/cb_bf16_grouped_gemm.cu:228-245,547-610;
+ * gridbook/csrc/cb_moe_persistent_b.cu:1645-1960). */
+GB_API int gb_gemm_tn_grouped(const void* A, const void* B, void* D_bf16, int64_t P, int64_t N, int64_t K, int kind,
+                              int64_t E, const int32_t* seg_offsets, const int32_t* row_map, const float* a_scale,
+                              const float* b_scale, float global_scale, void* stream);
+/* out[j, :] = x[x_row[order[j]], :] (x[order[j]] when x_row is NULL) for the sorted rows
+ * j < seg_offsets[E]: the routed rows of a [T,K] bf16 batch in expert order (the reference sorts
+ * with torch indexing, gridbook/moe.py:1609-1625).  K a multiple of 8. */
+GB_API int gb_moe_gather_rows(const void* x_bf16, const int32_t* x_row, const int32_t* order,
+                              const int32_t* seg_offsets, int64_t E, int64_t P, int64_t K, void* out_bf16,
+                              void* stream);
+/* out[j, c] = bf16(bf16(silu(h[j, c])) * h[j, inter + c]) for the sorted rows j < seg_offsets[E];
+ * h [P, 2*inter] bf16 (the chain of tests/test_cuda_gemv.py:336-338).  inter a multiple of 8. */
+GB_API int gb_moe_swiglu_rows(const void* h_bf16, const int32_t* seg_offsets, int64_t E, int64_t P, int64_t inter,
+                              void* out_bf16, void* stream);
 
 /* ---- routed MoE -------------------------------------------------------------- */
 /* Device-side histogram + exclusive scan + stable expert-major permutation of the

@@ -67,6 +67,9 @@ def test_expand_bit_exact(dev, idx):
         vals = O.decode_values(d["qw"], d["cb"], d["cb_row_offset"], N=N, K=K, k_bits=fmt.k, n_sub=fmt.n_sub,
                                type_size=fmt.type_size)
         assert np.array_equal(got.view(torch.uint8).cpu().numpy(), O.f32_to_e4m3(vals))
+        # the served weight bf16(value * row scale), whole and over a row window
+        assert np.array_equal(bits_of(kernels.expand_fp8_bf16(w)), O.f32_to_bf16_bits(ref))
+        assert np.array_equal(bits_of(kernels.expand_fp8_bf16(w, 5, 11)), O.f32_to_bf16_bits(ref[5:16]))
 
 
 def test_expand_matches_reference_fixtures(dev, golden):

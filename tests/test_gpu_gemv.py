@@ -108,9 +108,13 @@ def test_gemv_shape_errors(dev):
 # ---- routed MoE -----------------------------------------------------------------
 def test_route_matches_oracle(dev):
     from gridbook_b200 import kernels, synth
-    for T, E, topk in ((1, 128, 8), (16, 128, 8), (256, 128, 8), (37, 9, 3)):
+    # the last three take the tiled ordering (4096 pairs and more, up to 256 experts)
+    for T, E, topk in ((1, 128, 8), (16, 128, 8), (256, 128, 8), (37, 9, 3), (512, 128, 8), (4099, 7, 1),
+                       (3001, 256, 6)):
         ids, _ = synth.make_routing(T, E, topk, seed=T)
-        ids[0, 0] = -1 if T == 37 else ids[0, 0]            # padding sentinel is dropped
+        if T in (37, 4099, 3001):
+            ids[0, 0] = -1                                    # padding sentinel is dropped
+            ids[T // 2, topk - 1] = -1
         counts, offsets, order = kernels.moe_route(torch.from_numpy(ids).to(dev), E)
         keep = ids.reshape(-1) >= 0
         rc, ro, rorder = O.route_by_expert(np.where(keep, ids.reshape(-1), E).reshape(ids.shape), E + 1)
