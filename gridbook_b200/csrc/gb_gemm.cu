@@ -352,15 +352,21 @@ moe_gather_rows_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ 
 }
 
 // out[j][c] = bf16(bf16(silu(gate)) * up), gate = h[j][c], up = h[j][inter + c]: every torch bf16
-// op of the reference chain rounds (F.silu on bf16, then a bf16 multiply).
+// op of the reference chain rounds (F.silu on bf16, then a bf16 multiply).  With kBucket the fp4
+// group-16 activation bucket of the next projection is applied to the result in registers (a
+// thread holds eight values, its neighbour lane the other half of the group).
+template <bool kBucket>
 __global__ void __launch_bounds__(128)
-moe_swiglu_rows_kernel(const uint4* __restrict__ h, const int32_t* __restrict__ n_rows, int vecs,
+moe_swiglu_rows_kernel(const uint4* __restrict__ h, const int32_t* __restrict__ n_rows, int vecs, int scale_rule,
                        uint4* __restrict__ out) {
   const int j = blockIdx.x;
   if (j >= *n_rows) return;
   const uint4* row = h + (int64_t)j * 2 * vecs;
-  for (int i = threadIdx.x; i < vecs; i += blockDim.x) {
-    const uint4 g = row[i], u = row[vecs + i];
+  for (int i0 = 0; i0 < vecs; i0 += blockDim.x) {          // warp-uniform trip count: the bucket shuffles
+    const int i = i0 + threadIdx.x;
+    const bool live = i < vecs;
+    const int ii = live ? i : 0;
+    const uint4 g = row[ii], u = row[vecs + ii];
     const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
     uint32_t r[4];
 #pragma unroll
@@ -375,7 +381,9 @@ moe_swiglu_rows_kernel(const uint4* __restrict__ h, const int32_t* __restrict__ 
       }
       r[q] = packed;
     }
-    out[(int64_t)j * vecs + i] = make_uint4(r[0], r[1], r[2], r[3]);
+    uint4 res = make_uint4(r[0], r[1], r[2], r[3]);
+    if (kBucket) res = gb_fp4_group16_qdq_pair(res, scale_rule);
+    if (live) out[(int64_t)j * vecs + i] = res;
   }
 }
 
@@ -553,16 +561,24 @@ int gb_moe_gather_rows(const void* x, const int32_t* x_row, const int32_t* order
   return GB_OK;
 }
 
-int gb_moe_swiglu_rows(const void* h, const int32_t* seg_offsets, int64_t E, int64_t P, int64_t inter, void* out,
-                       void* stream) {
+int gb_moe_swiglu_rows(const void* h, const int32_t* seg_offsets, int64_t E, int64_t P, int64_t inter, int act,
+                       int scale_rule, void* out, void* stream) {
   GB_REQUIRE(h && seg_offsets && out, "null pointer argument");
   GB_REQUIRE(P >= 0 && E > 0 && inter > 0 && inter % 8 == 0, "bad shape P=%lld E=%lld inter=%lld", (long long)P,
              (long long)E, (long long)inter);
+  GB_REQUIRE(act == GB_ACT_NONE || (act == GB_ACT_FP4_GROUP16 && inter % 16 == 0),
+             "the fused bucket is the fp4 group-16 one and wants inter %% 16 == 0");
   GB_REQUIRE(((uintptr_t)h & 15u) == 0 && ((uintptr_t)out & 15u) == 0, "rows must be 16-byte aligned");
   if (P == 0) return GB_OK;
   gb_count_launch();
-  moe_swiglu_rows_kernel<<<(unsigned)P, 128, 0, (cudaStream_t)stream>>>((const uint4*)h, seg_offsets + E,
-                                                                       (int)(inter / 8), (uint4*)out);
+  const int vecs = (int)(inter / 8);
+  const unsigned threads = vecs >= 128 ? 128u : (unsigned)((vecs + 31) / 32 * 32);   // whole warps, few idle lanes
+  if (act == GB_ACT_FP4_GROUP16)
+    moe_swiglu_rows_kernel<true><<<(unsigned)P, threads, 0, (cudaStream_t)stream>>>(
+        (const uint4*)h, seg_offsets + E, (int)(inter / 8), scale_rule, (uint4*)out);
+  else
+    moe_swiglu_rows_kernel<false><<<(unsigned)P, threads, 0, (cudaStream_t)stream>>>(
+        (const uint4*)h, seg_offsets + E, (int)(inter / 8), scale_rule, (uint4*)out);
   GB_LAUNCH_OK("moe_swiglu_rows_kernel");
   return GB_OK;
 }

@@ -69,13 +69,16 @@ moe_route_kernel(const int32_t* __restrict__ ids, int P, int E, int first_expert
   int32_t* wcnt = off + E + 1;            // [E][32]
   int32_t* cursor = wcnt + E * nwarps;    // [E] next free place of every expert
   for (int e = tid; e < E; e += kRouteThreads) cursor[e] = off[e];
+  int next_raw = tid < P ? ids[tid] : -1;               // the next tile's id is loaded a tile ahead
   for (int base = 0; base < P; base += kRouteThreads) {
     for (int k = tid; k < E * nwarps; k += kRouteThreads) wcnt[k] = 0;
-    __syncthreads();
     const int i = base + tid;
+    const int raw = next_raw;
+    next_raw = i + kRouteThreads < P ? ids[i + kRouteThreads] : -1;
+    __syncthreads();
     int id = -1;
     if (i < P) {
-      const int v = ids[i] - first_expert;
+      const int v = raw - first_expert;
       if (v >= 0 && v < E) id = v;
     }
     const unsigned same = __match_any_sync(0xffffffffu, id);

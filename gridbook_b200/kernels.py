@@ -399,8 +399,10 @@ def moe_gather_rows(x: torch.Tensor, order: torch.Tensor, offsets: torch.Tensor,
     return out
 
 
-def moe_swiglu_rows(h: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
-    """bf16 silu(gate) * up over the sorted rows: h [P, 2I] -> [P, I] (rows past offsets[E] unset)."""
+def moe_swiglu_rows(h: torch.Tensor, offsets: torch.Tensor, *, act: str | None = None,
+                    scale_rule: str = "recip") -> torch.Tensor:
+    """bf16 silu(gate) * up over the sorted rows: h [P, 2I] -> [P, I] (rows past offsets[E] unset).
+    ``act="fp4"`` also applies the fp4 group-16 bucket to the result in the same launch."""
     _need_cuda(h, offsets)
     lib = nat.load("routed SwiGLU")
     if h.dtype is not torch.bfloat16:
@@ -408,8 +410,9 @@ def moe_swiglu_rows(h: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
     h = h.contiguous()
     P, two_i = h.shape
     out = torch.empty((P, two_i // 2), dtype=torch.bfloat16, device=h.device)
-    nat.check(lib.gb_moe_swiglu_rows(_ptr(h), _ptr(offsets), offsets.numel() - 1, P, two_i // 2, _ptr(out),
-                                     nat.stream_ptr(h.device)), lib)
+    nat.check(lib.gb_moe_swiglu_rows(_ptr(h), _ptr(offsets), offsets.numel() - 1, P, two_i // 2,
+                                     nat.ACT_FP4_GROUP16 if act == "fp4" else nat.ACT_NONE, _rule(scale_rule),
+                                     _ptr(out), nat.stream_ptr(h.device)), lib)
     return out
 
 

@@ -18,7 +18,7 @@ PAIR_KERNEL_MAX_PAIRS = 768       # routed pairs up to which every pair runs as 
 FUSED_BUCKET_MAX_PAIRS = 32       # routed pairs up to which the grouped kernel buckets its own rows
 # From this many routed pairs per expert (on average) the routed layer decodes each stack once
 # and runs grouped tensor-core GEMMs instead of the decode kernel's 16-row passes.
-PREFILL_MIN_PAIRS_PER_EXPERT = 72
+PREFILL_MIN_PAIRS_PER_EXPERT = 56
 
 
 def prefill_min_pairs_per_expert() -> int:
@@ -242,8 +242,11 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         w13, w2 = layer._cb_w13, layer._cb_w2
         # bucket the T rows once, then bring them into expert order
         a = kernels.moe_gather_rows(bucket(x2, w13), order, offsets, x_row=x_row)
-        h = kernels.moe_swiglu_rows(stage(a, w13, None), offsets)
-        y = stage(bucket(h, w2), w2, order)                   # rows back in pair order
+        if w2.fmt.is_fp4 and layer._cb_inter % 16 == 0:       # SwiGLU and the fp4 bucket in one launch
+            h = kernels.moe_swiglu_rows(stage(a, w13, None), offsets, act="fp4", scale_rule=rule)
+        else:
+            h = bucket(kernels.moe_swiglu_rows(stage(a, w13, None), offsets), w2)
+        y = stage(h, w2, order)                               # rows back in pair order
         layer._cb_route = "grouped prefill: expand + gemm_tn_grouped"
         return kernels.moe_combine(y, pair_w, T, topk, topk_ids=ids, E=E)
 

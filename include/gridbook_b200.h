@@ -171,9 +171,11 @@ GB_API int gb_moe_gather_rows(const void* x_bf16, const int32_t* x_row, const in
                               const int32_t* seg_offsets, int64_t E, int64_t P, int64_t K, void* out_bf16,
                               void* stream);
 /* out[j, c] = bf16(bf16(silu(h[j, c])) * h[j, inter + c]) for the sorted rows j < seg_offsets[E];
- * h [P, 2*inter] bf16 (the chain of tests/test_cuda_gemv.py:336-338).  inter a multiple of 8. */
+ * h [P, 2*inter] bf16 (the chain of tests/test_cuda_gemv.py:336-338).  inter a multiple of 8.
+ * act = GB_ACT_FP4_GROUP16 also applies the next projection's fp4 group-16 bucket to the result
+ * (same bits as gb_fp4_act_qdq on it; inter a multiple of 16), GB_ACT_NONE leaves it as it is. */
 GB_API int gb_moe_swiglu_rows(const void* h_bf16, const int32_t* seg_offsets, int64_t E, int64_t P, int64_t inter,
-                              void* out_bf16, void* stream);
+                              int act, int scale_rule, void* out_bf16, void* stream);
 
 /* ---- routed MoE -------------------------------------------------------------- */
 /* Device-side histogram + exclusive scan + stable expert-major permutation of the

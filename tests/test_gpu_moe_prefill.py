@@ -99,6 +99,9 @@ def test_gather_and_swiglu_rows(dev):
     # the device exponential differs from libm's in the last place: a bf16 step at most, rarely
     assert np.abs(got - ref[:routed]).max() <= np.abs(ref).max() * 2.0 ** -7
     assert np.mean(got != ref[:routed]) < 0.02
+    # with the fused bucket: the same bits as the bucket kernel on the plain result
+    fused = kernels.moe_swiglu_rows(synth.bf16_tensor(h, dev), offsets, act="fp4")
+    assert torch.equal(fused[:routed], kernels.fp4_act_qdq(a)[:routed])
 
 
 @pytest.mark.parametrize("f13,f2,T", [("lit", "lit", 300), ("k16v2", "k16v2", 150), ("f8k32", "f8k32", 130),
