@@ -21,7 +21,7 @@ REQUIRED_SYMBOLS = (
     "gb_fp8_act_qdq", "gb_fp4_act_qdq",
     "gb_expand_fp8", "gb_expand_fp4_bf16", "gb_expand_fp4_nvfp4",
     "gb_gemv_workspace_bytes", "gb_gemv", "gb_gemv_static",
-    "gb_moe_route", "gb_moe_gemv_workspace_bytes", "gb_moe_gemv", "gb_moe_combine",
+    "gb_moe_route", "gb_moe_route_ws", "gb_moe_route_workspace_bytes", "gb_moe_gemv_workspace_bytes", "gb_moe_gemv", "gb_moe_combine",
     "gb_moe_gemv_pairs_workspace_bytes", "gb_moe_gemv_pairs",
     "gb_moe_mlp_pairs_workspace_bytes", "gb_moe_mlp_pairs",
     "gb_expand_fp8_bf16", "gb_fp8_quantize_rows", "gb_gemm_tn", "gb_gemm_tn_grouped", "gb_moe_gather_rows", "gb_moe_swiglu_rows",
@@ -113,6 +113,9 @@ def _declare(lib) -> None:
     lib.gb_gemv.argtypes = [vp, i64, wp, i32, i32, vp, vp, i64, vp]
     lib.gb_gemv_static.argtypes = [vp, i64, wp, i32, i32, vp, vp]
     lib.gb_moe_route.argtypes = [vp, i64, i64, i64, i64, vp, vp, vp, vp, vp, vp]
+    lib.gb_moe_route_ws.argtypes = [vp, i64, i64, i64, i64, vp, vp, vp, vp, vp, vp, i64, vp]
+    lib.gb_moe_route_workspace_bytes.argtypes = [i64, i64, i64]
+    lib.gb_moe_route_workspace_bytes.restype = i64
     lib.gb_moe_gemv_workspace_bytes.argtypes = [i64, i64]
     lib.gb_moe_gemv_workspace_bytes.restype = i64
     lib.gb_moe_gemv.argtypes = [vp, vp, wp, i64, i64, vp, vp, i64, i32, i32, i32, vp, vp, vp, i64, vp]

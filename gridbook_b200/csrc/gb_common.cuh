@@ -84,6 +84,12 @@ GB_DEVINL uint32_t gb_f32_to_bf16_bits(float v) {
   return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
 
+// Two fp32 -> one word of two bf16 (a in the low half), round to nearest even: one conversion.
+GB_DEVINL uint32_t gb_pack_bf16x2(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 // E4M3 byte -> fp32, exact (no NaN handling: 0x7F/0xFF decode as 480, never stored).
 GB_DEVINL float gb_e4m3_to_f32(uint32_t b) {
   const uint32_t mag = b & 0x7Fu;

@@ -204,8 +204,7 @@ expand_kernel(ExpandArgs a, void* __restrict__ out0, uint8_t* __restrict__ out_s
       uint32_t p[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j)
-        p[j] = gb_f32_to_bf16_bits(__fmul_rn(val[u][2 * j], scale[u])) |
-               (gb_f32_to_bf16_bits(__fmul_rn(val[u][2 * j + 1], scale[u])) << 16);
+        p[j] = gb_pack_bf16x2(__fmul_rn(val[u][2 * j], scale[u]), __fmul_rn(val[u][2 * j + 1], scale[u]));
       *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out0) + at) = make_uint4(p[0], p[1], p[2], p[3]);
     } else {
       uint32_t nib = 0;

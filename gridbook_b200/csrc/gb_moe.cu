@@ -104,6 +104,114 @@ moe_route_kernel(const int32_t* __restrict__ ids, int P, int E, int first_expert
   }
 }
 
+// ---- routing over many pairs: three launches that use the whole GPU ---------------------
+// Tiles of 1024 pairs.  (1) every tile counts its pairs per expert; (2) one CTA turns the counts
+// into per-expert totals, segment offsets and, per tile, the number of an expert's pairs in
+// earlier tiles; (3) every tile places its pairs: segment start + pairs in earlier tiles + pairs
+// of that expert in earlier warps of the tile + rank among the warp's lanes with the same
+// expert.  The same stable expert-major order as the one-CTA kernel.
+__global__ void __launch_bounds__(kRouteThreads)
+route_hist_kernel(const int32_t* __restrict__ ids, int P, int E, int first_expert, int32_t* __restrict__ hist,
+                  const float* __restrict__ weights, float* __restrict__ pair_w) {
+  extern __shared__ int32_t sh[];   // [E]
+  gb_pdl_launch_dependents();
+  for (int e = threadIdx.x; e < E; e += kRouteThreads) sh[e] = 0;
+  gb_pdl_wait();                    // nothing is written before the launch ahead has finished
+  __syncthreads();
+  const int i = blockIdx.x * kRouteThreads + threadIdx.x;
+  if (i < P) {
+    const int id = ids[i] - first_expert;
+    const bool live = id >= 0 && id < E;
+    if (live) atomicAdd(&sh[id], 1);
+    if (pair_w) pair_w[i] = live ? gb_bf16_bits_to_f32(gb_f32_to_bf16_bits(weights[i])) : 0.0f;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += kRouteThreads) hist[(int64_t)blockIdx.x * E + e] = sh[e];
+}
+
+__global__ void __launch_bounds__(kRouteThreads)
+route_scan_kernel(int32_t* __restrict__ hist, int tiles, int P, int E, int32_t* __restrict__ counts,
+                  int32_t* __restrict__ offsets, int32_t* __restrict__ order) {
+  extern __shared__ int32_t sh[];   // [E] counts, [E+1] offsets
+  int32_t* cnt = sh;
+  int32_t* off = sh + E;
+  const int tid = threadIdx.x, lane = tid & 31;
+  gb_pdl_launch_dependents();
+  gb_pdl_wait();
+  for (int e = tid >> 5; e < E; e += kRouteThreads / 32) {   // a warp per expert, lanes over tiles
+    int run = 0;
+    for (int t0 = 0; t0 < tiles; t0 += 32) {     // exclusive prefix over the tiles, in place
+      const int t = t0 + lane;
+      const int v = t < tiles ? hist[(int64_t)t * E + e] : 0;
+      int incl = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += n;
+      }
+      if (t < tiles) hist[(int64_t)t * E + e] = run + incl - v;
+      run += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) cnt[e] = run;
+  }
+  __syncthreads();
+  if (tid < 32) {
+    int running = 0;
+    for (int base = 0; base < E; base += 32) {
+      const int e = base + lane;
+      const int v = e < E ? cnt[e] : 0;
+      int incl = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += n;
+      }
+      if (e < E) off[e] = running + incl - v;
+      running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) off[E] = running;
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += kRouteThreads) counts[e] = cnt[e];
+  for (int e = tid; e <= E; e += kRouteThreads) offsets[e] = off[e];
+  for (int i = off[E] + tid; i < P; i += kRouteThreads) order[i] = 0;   // dropped (padding) pairs
+}
+
+__global__ void __launch_bounds__(kRouteThreads)
+route_scatter_kernel(const int32_t* __restrict__ ids, int P, int E, int first_expert,
+                     const int32_t* __restrict__ hist, const int32_t* __restrict__ offsets,
+                     int32_t* __restrict__ order) {
+  extern __shared__ int32_t wcnt[];   // [E][32]: warp w's count of expert e, then its start
+  constexpr int nwarps = kRouteThreads / 32;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  gb_pdl_launch_dependents();
+  for (int k = tid; k < E * nwarps; k += kRouteThreads) wcnt[k] = 0;
+  gb_pdl_wait();
+  const int i = blockIdx.x * kRouteThreads + tid;
+  int id = -1;
+  if (i < P) {
+    const int v = ids[i] - first_expert;
+    if (v >= 0 && v < E) id = v;
+  }
+  __syncthreads();
+  const unsigned same = __match_any_sync(0xffffffffu, id);
+  const int rank = __popc(same & ((1u << lane) - 1u));
+  if (id >= 0 && rank == 0) wcnt[id * nwarps + warp] = __popc(same);
+  __syncthreads();
+  for (int e = warp; e < E; e += nwarps) {
+    const int v = wcnt[e * nwarps + lane];
+    int incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += n;
+    }
+    wcnt[e * nwarps + lane] = offsets[e] + hist[(int64_t)blockIdx.x * E + e] + incl - v;
+  }
+  __syncthreads();
+  if (id >= 0) order[wcnt[id * nwarps + warp] + rank] = i;
+}
+
 // Optional cross-GPU part of the combine (expert parallelism): before any row of y is read,
 // tell every peer "my stores into your buffers are visible" and wait for the same from them
 // (the second half of the exchange protocol in gb_peer.cu: flag words 8..15, exchange number in
@@ -178,21 +286,51 @@ moe_combine_kernel(const uint16_t* __restrict__ y, const float* __restrict__ pai
 
 extern "C" {
 
-int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E, int64_t expert_base,
-                 int32_t* counts, int32_t* offsets, int32_t* order, const float* topk_weights, float* pair_w, void* stream) {
+int64_t gb_moe_route_workspace_bytes(int64_t T, int64_t topk, int64_t E) {
+  const int64_t P = T * topk;
+  if (P < 4096 || E > 256 || E < 1) return 0;                 // the one-CTA kernel needs none
+  return ((P + kRouteThreads - 1) / kRouteThreads) * E * (int64_t)sizeof(int32_t);
+}
+
+int gb_moe_route_ws(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E, int64_t expert_base,
+                    int32_t* counts, int32_t* offsets, int32_t* order, const float* topk_weights, float* pair_w,
+                    void* workspace, int64_t ws_bytes, void* stream) {
   GB_REQUIRE(topk_ids && counts && offsets && order, "null pointer argument");
   GB_REQUIRE((topk_weights == nullptr) == (pair_w == nullptr), "topk_weights and pair_w go together");
   GB_REQUIRE(T >= 0 && topk >= 1 && E >= 1 && E <= 4096, "bad routing shape T=%lld topk=%lld E=%lld",
              (long long)T, (long long)topk, (long long)E);
   GB_REQUIRE(T * topk < (1ll << 30), "too many routed pairs");
+  const int64_t need = gb_moe_route_workspace_bytes(T, topk, E);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (need > 0 && workspace != nullptr) {
+    if (ws_bytes < need) return gb_fail(GB_EWORKSPACE, "routing workspace: %lld bytes given, %lld needed",
+                                        (long long)ws_bytes, (long long)need);
+    GB_REQUIRE(((uintptr_t)workspace & 3u) == 0, "routing workspace must be 4-byte aligned");
+    const int P = (int)(T * topk), tiles = (P + kRouteThreads - 1) / kRouteThreads;
+    int32_t* hist = (int32_t*)workspace;
+    GB_CUDA_OK(gb_launch(route_hist_kernel, dim3(tiles), dim3(kRouteThreads), (size_t)E * sizeof(int32_t), st,
+                         topk_ids, P, (int)E, (int)expert_base, hist, topk_weights, pair_w));
+    GB_CUDA_OK(gb_launch(route_scan_kernel, dim3(1), dim3(kRouteThreads), (size_t)(2 * E + 1) * sizeof(int32_t), st,
+                         hist, tiles, P, (int)E, counts, offsets, order));
+    GB_CUDA_OK(gb_launch(route_scatter_kernel, dim3(tiles), dim3(kRouteThreads),
+                         (size_t)E * (kRouteThreads / 32) * sizeof(int32_t), st, topk_ids, P, (int)E,
+                         (int)expert_base, (const int32_t*)hist, (const int32_t*)offsets, order));
+    return GB_OK;
+  }
   // a warp per expert scanning all pairs costs E*P; from a few thousand pairs on, tiles of
   // 1024 pairs in pair order are cheaper (the per-warp counts need E*33 words of shared memory)
   const int tiled = T * topk >= 4096 && E <= 256;
   const size_t smem = (size_t)(2 * E + 1 + (tiled ? E * (kRouteThreads / 32 + 1) : 0)) * sizeof(int32_t);
-  GB_CUDA_OK(gb_launch(moe_route_kernel, dim3(1), dim3(kRouteThreads), smem, (cudaStream_t)stream, topk_ids,
+  GB_CUDA_OK(gb_launch(moe_route_kernel, dim3(1), dim3(kRouteThreads), smem, st, topk_ids,
                        (int)(T * topk), (int)E, (int)expert_base, counts, offsets, order, topk_weights, pair_w,
                        tiled));
   return GB_OK;
+}
+
+int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E, int64_t expert_base,
+                 int32_t* counts, int32_t* offsets, int32_t* order, const float* topk_weights, float* pair_w, void* stream) {
+  return gb_moe_route_ws(topk_ids, T, topk, E, expert_base, counts, offsets, order, topk_weights, pair_w, nullptr, 0,
+                         stream);
 }
 
 static int combine_launch(const void* y, const float* pair_w, const int32_t* topk_ids, int64_t E, int64_t T,

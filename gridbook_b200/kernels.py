@@ -205,8 +205,10 @@ def moe_route(topk_ids: torch.Tensor, E: int, topk_weights: torch.Tensor | None 
     if topk_weights is not None:
         tw = topk_weights.reshape(-1).to(torch.float32).contiguous()
         pw = torch.empty(max(T * topk, 1), dtype=torch.float32, device=dev)
-    nat.check(lib.gb_moe_route(_ptr(ids), T, topk, E, expert_base, _ptr(counts), _ptr(offsets), _ptr(order),
-                               _ptr(tw), _ptr(pw), nat.stream_ptr(dev)), lib)
+    need = lib.gb_moe_route_workspace_bytes(T, topk, E)       # large batches: tiles over the whole GPU
+    ws = torch.empty(need, dtype=torch.uint8, device=dev) if need else None
+    nat.check(lib.gb_moe_route_ws(_ptr(ids), T, topk, E, expert_base, _ptr(counts), _ptr(offsets), _ptr(order),
+                                  _ptr(tw), _ptr(pw), _ptr(ws), need, nat.stream_ptr(dev)), lib)
     if topk_weights is None:
         return counts, offsets, order[:T * topk]
     return counts, offsets, order[:T * topk], pw[:T * topk]

@@ -192,6 +192,15 @@ GB_API int gb_moe_swiglu_rows(const void* h_bf16, const int32_t* seg_offsets, in
 GB_API int gb_moe_route(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E, int64_t expert_base,
                  int32_t* counts, int32_t* offsets, int32_t* order,
                  const float* topk_weights, float* pair_w, void* stream);
+/* The same with a workspace of gb_moe_route_workspace_bytes(T, topk, E) bytes (0 below 4096
+ * pairs or above 256 experts: one CTA does it all).  With the workspace the routing of a large
+ * batch runs as three launches over tiles of 1024 pairs that use the whole GPU (per-tile
+ * histograms, scan, placement) instead of one CTA; same outputs, same stable order.
+ * workspace = NULL: gb_moe_route. */
+GB_API int64_t gb_moe_route_workspace_bytes(int64_t T, int64_t topk, int64_t E);
+GB_API int gb_moe_route_ws(const int32_t* topk_ids, int64_t T, int64_t topk, int64_t E, int64_t expert_base,
+                           int32_t* counts, int32_t* offsets, int32_t* order, const float* topk_weights,
+                           float* pair_w, void* workspace, int64_t ws_bytes, void* stream);
 
 /* Grouped GEMV over routed pairs; replaces cb_moe_gemv_fp8 / cb_moe_gemv_fp4_v2 /
  * cb_moe_gemv_v2 (gridbook/csrc/cb_gemv.cu:1210-1681,1873-2138; gridbook/csrc/cb_gemv_v2.cu:233-366).

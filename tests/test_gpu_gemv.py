@@ -122,6 +122,18 @@ def test_route_matches_oracle(dev):
         assert np.array_equal(offsets.cpu().numpy(), ro[:E + 1])
         n = int(ro[E])
         assert np.array_equal(order.cpu().numpy()[:n], rorder[:n])
+        if T * topk >= 4096:
+            # the wrapper took the three-launch route; the entry point without a workspace orders
+            # the same batch inside one CTA
+            import ctypes
+            from gridbook_b200 import _native as nat
+            lib = nat.load("MoE routing")
+            idd = torch.from_numpy(ids).to(dev).to(torch.int32).contiguous()
+            c2, o2, ord2 = torch.empty_like(counts), torch.empty_like(offsets), torch.empty(T * topk, dtype=torch.int32, device=dev)
+            vp = lambda t: ctypes.c_void_p(t.data_ptr())
+            nat.check(lib.gb_moe_route(vp(idd), T, topk, E, 0, vp(c2), vp(o2), vp(ord2), None, None,
+                                       nat.stream_ptr(dev)), lib)
+            assert torch.equal(c2, counts) and torch.equal(o2, offsets) and torch.equal(ord2[:n], order[:n])
 
 
 def test_route_weights_and_combine_skip_dropped_pairs(dev):
