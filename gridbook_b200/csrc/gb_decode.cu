@@ -143,9 +143,11 @@ GB_DEVINL float fp4_group_scale(const ExpandArgs& a, const uint8_t* sb, int v, u
 enum { kOutFp8 = 0, kOutBf16 = 1, kOutNvfp4 = 2, kOutFp8Bf16 = 3 };
 
 // Every warp takes kUnitsPerWarp consecutive (row, superblock) units and runs them in phases:
-// all code loads, then all codebook and scale loads, then all stores.  One unit per warp measured
-// fastest (four units: more loads in flight per lane but a third of the resident warps, 5 % slower).
-constexpr int kUnitsPerWarp = 1;
+// all code loads, then all codebook and scale loads, then all stores, so that two independent
+// load chains are in flight per lane.  Measured on the 805 MB bf16 tile of a 128-expert stack:
+// one unit 327 us, two 291 us, four 372 us (fewer resident warps); at two the kernel writes
+// 2.8 TB/s, close to the write half of a device copy.
+constexpr int kUnitsPerWarp = 2;
 
 template <int kOut>
 __global__ void __launch_bounds__(kThreads)
@@ -175,11 +177,21 @@ expand_kernel(ExpandArgs a, void* __restrict__ out0, uint8_t* __restrict__ out_s
 
   float val[kUnitsPerWarp][8], scale[kUnitsPerWarp];
   uint32_t sbyte[kUnitsPerWarp];
+  uint4 raw[kUnitsPerWarp];          // bf16 tile of a full-mode codeword: the eight bf16 as loaded
+  bool have_raw[kUnitsPerWarp];
 #pragma unroll
   for (int u = 0; u < kUnitsPerWarp; ++u) {
     const int64_t row = a.row0 + r[u];
     const int64_t cb_base = a.cb_row_offset ? (int64_t)a.cb_row_offset[row] : 0;
-    gather_values<kFp8Grid>(a, cb_base, code[u], val[u]);
+    have_raw[u] = false;
+    if constexpr (kOut == kOutBf16) {
+      const uint16_t* entry = reinterpret_cast<const uint16_t*>(a.codebook) + cb_base + (int64_t)code[u] * 8;
+      if (a.fmt.mode == GB_MODE_FULL && (reinterpret_cast<uintptr_t>(entry) & 15u) == 0) {
+        raw[u] = __ldg(reinterpret_cast<const uint4*>(entry));
+        have_raw[u] = true;
+      }
+    }
+    if (!have_raw[u]) gather_values<kFp8Grid>(a, cb_base, code[u], val[u]);
     sbyte[u] = 0;
     if constexpr (kOut == kOutFp8Bf16) scale[u] = a.weight_scale[row];     // the served weight's row scale
     else if constexpr (kOut == kOutFp8) scale[u] = 1.0f;
@@ -202,9 +214,27 @@ expand_kernel(ExpandArgs a, void* __restrict__ out0, uint8_t* __restrict__ out_s
     } else if constexpr (kOut == kOutBf16 || kOut == kOutFp8Bf16) {
       // bf16(value * scale): the group scale (fp4 grid) or the row scale (fp8 grid)
       uint32_t p[4];
+      const uint32_t sbits = __float_as_uint(scale[u]);
+      if (kOut == kOutBf16 && have_raw[u] && (sbits & 0xFFFFu) == 0) {
+        // the scale is a bf16 number (every E4M3 byte is): the packed bf16 multiply rounds the
+        // exact product once, the same bits as bf16(f32(value) * f32(scale))
+        const uint32_t s2 = (sbits >> 16) * 0x10001u;
+        const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        p[j] = gb_pack_bf16x2(__fmul_rn(val[u][2 * j], scale[u]), __fmul_rn(val[u][2 * j + 1], scale[u]));
+        for (int j = 0; j < 4; ++j) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(p[j]) : "r"(w[j]), "r"(s2));
+      } else {
+        if (kOut == kOutBf16 && have_raw[u]) {
+          const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            val[u][2 * j] = gb_bf16_bits_to_f32(w[j] & 0xffffu);
+            val[u][2 * j + 1] = gb_bf16_bits_to_f32(w[j] >> 16);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          p[j] = gb_pack_bf16x2(__fmul_rn(val[u][2 * j], scale[u]), __fmul_rn(val[u][2 * j + 1], scale[u]));
+      }
       *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out0) + at) = make_uint4(p[0], p[1], p[2], p[3]);
     } else {
       uint32_t nib = 0;
