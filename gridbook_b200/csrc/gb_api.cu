@@ -144,6 +144,7 @@ int gb_prepare(int device) {
   if (rc == GB_OK) rc = gb_prepare_kernels();
   if (rc == GB_OK) rc = gb_prepare_gemm();
   if (rc == GB_OK) rc = gb_prepare_dot();
+  if (rc == GB_OK) rc = gb_prepare_umma();
   cudaSetDevice(prev);
   return rc;
 }

@@ -444,6 +444,10 @@ int gb_tensor_map_bytes_2d(void* map_out, const void* base, uint64_t inner_bytes
   return GB_OK;
 }
 
+int gb_tensor_map_operand(void* map_out, const void* base, int64_t rows, int64_t K, int elem_bytes, int box_rows) {
+  return make_map((CUtensorMap*)map_out, base, rows, K, elem_bytes, box_rows);
+}
+
 int gb_prepare_gemm() {
   GB_CUDA_OK(cudaFuncSetAttribute((const void*)gemm_tn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   kGemmSmem));

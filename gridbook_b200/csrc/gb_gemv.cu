@@ -795,6 +795,15 @@ bool literal_aligned(const GemvParams& p) {
 }
 
 constexpr int kDotRowsMax = 8;      // most activation rows ever served by per-row table GEMVs
+int umma_min_rows() {               // rows from which the tensor-core decode kernel is tried (GRIDBOOK_B200_UMMA_MIN_M)
+  static const int v = [] {
+    const char* e = getenv("GRIDBOOK_B200_UMMA_MIN_M");
+    const int n = e ? atoi(e) : 2;
+    return n < 2 ? 2 : n;
+  }();
+  return v;
+}
+
 int dot_rows_max() {                // rows up to which they are actually used (GRIDBOOK_B200_DOT_ROWS overrides)
   static const int v = [] {
     const char* e = getenv("GRIDBOOK_B200_DOT_ROWS");
@@ -908,7 +917,9 @@ int64_t gb_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   const int64_t mma_path = ((M * K * 2 + 255) & ~255ll) + M * N * (int64_t)sizeof(float);
   const int64_t dot_path = gb_gemv_dot_workspace_bytes(N, K);     // M = 1, literal format
   const int64_t rows_path = gb_gemv_dot_rows_workspace_bytes(M < dot_rows_max() ? M : dot_rows_max(), N, K);   // rows 2..dot_rows_max()
+  const int64_t umma_path = gb_gemv_umma_workspace_bytes(M, N, K);   // rows 2..128, literal format
   int64_t need = mma_path > dot_path ? mma_path : dot_path;
+  if (umma_path > need) need = umma_path;
   return need > rows_path ? need : rows_path;
 }
 
@@ -918,10 +929,19 @@ int gb_gemv(const void* x, int64_t M, const gb_weight* w, int act, int scale_rul
   int rc = gb_check_weight(w);
   if (rc != GB_OK) return rc;
   GB_REQUIRE(x && y, "null activation or output pointer");
-  GB_REQUIRE(M >= 1 && M <= 16, "decode-batch kernel takes 1..16 rows, got M=%lld", (long long)M);
+  GB_REQUIRE(M >= 1 && M <= 128, "decode-batch kernels take 1..128 rows, got M=%lld", (long long)M);
   GB_REQUIRE(act == GB_ACT_NONE || act == GB_ACT_FP4_GROUP16 || act == GB_ACT_FP8_TOKEN, "unknown act %d", act);
   const int sms = gb_sm_count();
   if (sms <= 0) return gb_fail(GB_ECUDA, "no usable CUDA device: %s", gb_last_error());
+  if (M >= umma_min_rows()) {
+    // a batch of rows of the literal format: decode into shared memory, tensor-core MMA with the
+    // weights on the M side; every weight is decoded once whatever the row count
+    rc = gb_gemv_umma(x, M, w, act, scale_rule, y, workspace, workspace_bytes, stream_);
+    if (rc != GB_EUNSUPPORTED) return rc;
+  }
+  if (M > 16)
+    return gb_fail(GB_EUNSUPPORTED, "more than 16 rows are served for the literal fp4 format only (M=%lld)",
+                   (long long)M);
   if (M == 1) {
     // one activation row of the literal format: inner-product tables instead of per-weight expansion
     rc = gb_gemv_dot(x, w, act, scale_rule, y, workspace, workspace_bytes, stream_);

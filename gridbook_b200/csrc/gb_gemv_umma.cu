@@ -1,0 +1,370 @@
+// Decode-batch linear of the literal format on the tensor cores, without a decoded copy in HBM:
+// y[M, N] = x[M, K] . W^T for 2 <= M <= 128 activation rows.
+//
+// The WEIGHTS are the M side of the MMA: a CTA owns 128 weight rows and a K slice.  One warp
+// streams the packed rows (4 superblocks = 192 bytes per row and stage) into shared memory with
+// tiled TMA loads, one warp streams the matching 64-wide K slabs of the (bucketed) activations
+// with the 128-byte swizzle, eight warps decode: a thread takes one codeword (code byte ->
+// 16-byte codebook entry from a shared-memory copy, group scale byte -> bf16 pair from a
+// 256-entry table, four packed bf16 multiplies = bf16(value * scale), the decode contract) and
+// stores the eight weights as one 16-byte chunk at its swizzled place of a K-major 128 x 64 bf16
+// slab.  One thread issues tcgen05.mma (M = 128 weight rows, N = activation rows padded to 16,
+// kind::f16) on the decoded slab and the activation slab; the fp32 accumulator lives in tensor
+// memory and never leaves it during the K loop.  The decoders read it out at the end (lane =
+// weight row, column = activation row) and store bf16, or fp32 partial sums per K slice that a
+// small second kernel adds.
+#include "gb_common.cuh"
+
+#include <cuda.h>
+
+namespace {
+
+constexpr int kBM = 128;                                  // weight rows per CTA
+constexpr int kRawSb = 4;                                 // superblocks per raw stage
+constexpr int kSbBytes = 48;                              // literal superblock: 32 codes + 16 scales
+constexpr int kRawRowBytes = kRawSb * kSbBytes;           // 192
+constexpr int kRawStageBytes = kBM * kRawRowBytes;        // 24 KiB
+constexpr int kRawStages = 3;
+constexpr int kSlabStages = 4;
+constexpr int kASlabBytes = kBM * 128;                    // 128 rows x 64 bf16
+constexpr int kDecWarps = 8;
+constexpr int kCtlWarps = 3;                              // raw producer, x producer, MMA issuer
+constexpr int kUmmaThreads = 32 * (kCtlWarps + kDecWarps);
+constexpr int kMaxRows = 128;                             // activation rows
+
+struct UmmaParams {
+  int64_t N, K;
+  int M, Mpad;
+  int n_sb;                 // superblocks per weight row
+  int stages_per_slice;     // raw stages (4 superblocks each) per K slice
+  int slices;
+  const uint4* codebook;    // 256 entries of eight bf16
+  float global_scale;
+  uint16_t* y;              // [M, N] bf16 (one slice)
+  float* partial;           // [slices, M, N] fp32 (several slices)
+  uint32_t idesc;
+  uint32_t tmem_cols;
+  int* status;
+};
+
+GB_DEVINL void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(gb_smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(gb_smem_u32(bar))
+      : "memory");
+}
+
+// K-major tile of 128-byte rows with the 128-byte swizzle: 8-row groups 1024 bytes apart.
+GB_DEVINL uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(1024u >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+GB_DEVINL void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
+}
+
+GB_DEVINL void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(gb_smem_u32(bar)) : "memory");
+}
+
+// A bounded wait that remembers a timeout for the rest of the CTA: later waits return at once.
+GB_DEVINL void wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (*abort_flag) return;
+  if (!gb_mbar_wait(bar, parity)) {
+    *abort_flag = 1;
+    atomicExch(status, code);
+  }
+}
+
+__global__ void __launch_bounds__(kUmmaThreads, 1)
+umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                   const UmmaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int b_bytes = p.Mpad * 128;                        // one activation slab
+  const int slab_bytes = kASlabBytes + b_bytes;
+  uint8_t* slabs = smem;                                   // kSlabStages x (A slab | x slab)
+  uint8_t* raw = slabs + kSlabStages * slab_bytes;         // kRawStages x packed rows
+  uint4* cb_s = reinterpret_cast<uint4*>(raw + kRawStages * kRawStageBytes);
+  uint32_t* lut_s = reinterpret_cast<uint32_t*>(cb_s + 256);
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(lut_s + 256);
+  uint64_t* raw_empty = raw_full + kRawStages;
+  uint64_t* slab_full = raw_empty + kRawStages;
+  uint64_t* slab_empty = slab_full + kSlabStages;
+  uint64_t* acc_full = slab_empty + kSlabStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * kBM;
+  const int n_raw = (p.n_sb + kRawSb - 1) / kRawSb;
+  const int r_begin = blockIdx.y * p.stages_per_slice;
+  const int r_end = min(n_raw, r_begin + p.stages_per_slice);
+
+  gb_pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kRawStages; ++s) {
+      gb_mbar_init(&raw_full[s], 1);
+      gb_mbar_init(&raw_empty[s], kDecWarps);
+    }
+    for (int s = 0; s < kSlabStages; ++s) {
+      gb_mbar_init(&slab_full[s], 1 + kDecWarps);          // the x slab's bytes + every decoder warp
+      gb_mbar_init(&slab_empty[s], 1);
+    }
+    gb_mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    gb_fence_barrier_init();
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(gb_smem_u32(tmem_slot)), "r"(p.tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (warp >= kCtlWarps) {
+    // constants of the layer: the codebook and the E4M3 -> bf16 pair table of the group scales
+    const int d = threadIdx.x - 32 * kCtlWarps;
+    cb_s[d] = __ldg(p.codebook + d);
+    const uint32_t bits = __float_as_uint(gb_e4m3_to_f32((uint32_t)d)) >> 16;
+    lut_s[d] = bits * 0x10001u;
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  gb_pdl_wait();                                           // x may come from the launch ahead
+
+  if (warp == 0) {
+    // ------------------------- packed weight rows -------------------------
+    if (lane == 0) {
+      for (int r = r_begin, it = 0; r < r_end; ++r, ++it) {
+        const int rs = it % kRawStages;
+        wait_or_abort(&raw_empty[rs], ((it / kRawStages) & 1) ^ 1, abort_flag, p.status, 21);
+        gb_mbar_expect_tx(&raw_full[rs], kRawStageBytes);
+        tma_load_2d(raw + (size_t)rs * kRawStageBytes, &map_w, r * kRawRowBytes, n0, &raw_full[rs]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------- activation slabs ---------------------------
+    if (lane == 0) {
+      int slab = 0;
+      for (int r = r_begin; r < r_end; ++r) {
+        const int n_here = min(kRawSb, p.n_sb - r * kRawSb) * 4;       // slabs of this raw stage
+        for (int q = 0; q < n_here; ++q, ++slab) {
+          const int s = slab % kSlabStages;
+          wait_or_abort(&slab_empty[s], ((slab / kSlabStages) & 1) ^ 1, abort_flag, p.status, 22);
+          gb_mbar_expect_tx(&slab_full[s], (uint32_t)b_bytes);
+          tma_load_2d(slabs + (size_t)s * slab_bytes + kASlabBytes, &map_x, r * (kRawSb * 256) + q * 64, 0,
+                      &slab_full[s]);
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------- MMA issuer ----------------------------------
+    if (lane == 0) {
+      int slab = 0;
+      for (int r = r_begin; r < r_end; ++r) {
+        const int n_here = min(kRawSb, p.n_sb - r * kRawSb) * 4;
+        for (int q = 0; q < n_here; ++q, ++slab) {
+          const int s = slab % kSlabStages;
+          wait_or_abort(&slab_full[s], (slab / kSlabStages) & 1, abort_flag, p.status, 23);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = gb_smem_u32(slabs + (size_t)s * slab_bytes);
+          const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + kASlabBytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)                        // 16 weights of K per instruction
+            umma_bf16(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), p.idesc, slab > 0 || k > 0);
+          umma_commit(&slab_empty[s]);
+        }
+      }
+      umma_commit(acc_full);
+    }
+  } else {
+    // ------------------------- decoders -------------------------------------
+    const int d = threadIdx.x - 32 * kCtlWarps;
+    const int j = d & 7, rsub = d >> 3;                      // codeword of the slab row, row inside a 32-row band
+    int slab = 0;
+    for (int r = r_begin, it = 0; r < r_end; ++r, ++it) {
+      const int rs = it % kRawStages;
+      wait_or_abort(&raw_full[rs], (it / kRawStages) & 1, abort_flag, p.status, 24);
+      const uint8_t* stage = raw + (size_t)rs * kRawStageBytes;
+      const int sb_here = min(kRawSb, p.n_sb - r * kRawSb);
+      for (int sbi = 0; sbi < sb_here; ++sbi) {
+        for (int q = 0; q < 4; ++q, ++slab) {
+          const int s = slab % kSlabStages;
+          wait_or_abort(&slab_empty[s], ((slab / kSlabStages) & 1) ^ 1, abort_flag, p.status, 25);
+          uint8_t* a_slab = slabs + (size_t)s * slab_bytes;
+          uint32_t code[4], sc[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint8_t* rp = stage + (i * 32 + rsub) * kRawRowBytes + sbi * kSbBytes;
+            code[i] = rp[q * 8 + j];
+            sc[i] = rp[32 + q * 4 + (j >> 1)];
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int row = i * 32 + rsub;
+            const uint4 e = cb_s[code[i]];
+            const uint32_t s2 = lut_s[sc[i]];
+            uint4 w;
+            asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(w.x) : "r"(e.x), "r"(s2));
+            asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(w.y) : "r"(e.y), "r"(s2));
+            asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(w.z) : "r"(e.z), "r"(s2));
+            asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(w.w) : "r"(e.w), "r"(s2));
+            *reinterpret_cast<uint4*>(a_slab + (row >> 3) * 1024 + (row & 7) * 128 + ((j ^ (row & 7)) << 4)) = w;
+          }
+          // generic-proxy stores -> visible to the tensor core's async proxy, then one arrival per warp
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) gb_mbar_arrive(&slab_full[s]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) gb_mbar_arrive(&raw_empty[rs]);
+    }
+
+    // ------------------------- read-out ------------------------------------
+    wait_or_abort(acc_full, 0, abort_flag, p.status, 26);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int quarter = warp & 3;                            // the tensor-memory lanes this warp may read
+    const int half = (warp - kCtlWarps) >> 2;                // column chunks: even / odd
+    const int64_t row = (int64_t)n0 + quarter * 32 + lane;
+    const bool ok = *abort_flag == 0;
+    for (int c = half; c < p.Mpad / 8; c += 2) {
+      uint32_t v[8];
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 8);
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                   : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                   : "r"(taddr));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (ok && row < p.N) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int m = c * 8 + i;
+          if (m < p.M) {
+            if (p.slices > 1)
+              p.partial[((int64_t)blockIdx.y * p.M + m) * p.N + row] = __uint_as_float(v[i]);
+            else
+              p.y[(int64_t)m * p.N + row] = (uint16_t)gb_f32_to_bf16_bits(__uint_as_float(v[i]) * p.global_scale);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols)
+                 : "memory");
+  }
+}
+
+// y[m][n] = bf16(global_scale * sum over the K slices), in slice order.
+__global__ void __launch_bounds__(256)
+umma_finalize_kernel(const float* __restrict__ partial, int slices, int64_t MN, float global_scale,
+                     uint16_t* __restrict__ y) {
+  gb_pdl_launch_dependents();
+  gb_pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= MN) return;
+  float acc = 0.0f;
+  for (int s = 0; s < slices; ++s) acc += partial[(int64_t)s * MN + i];
+  y[i] = (uint16_t)gb_f32_to_bf16_bits(acc * global_scale);
+}
+
+int umma_smem_bytes(int Mpad) {
+  return 1024 + kSlabStages * (kASlabBytes + Mpad * 128) + kRawStages * kRawStageBytes + 4096 + 1024 + 256;
+}
+
+// K slices: enough CTAs for the SMs when the layer has few 128-row tiles.
+void umma_plan(int64_t N, int n_sb, int sms, int* slices, int* stages_per_slice) {
+  const int tiles = (int)((N + kBM - 1) / kBM);
+  const int n_raw = (n_sb + kRawSb - 1) / kRawSb;
+  int want = sms / tiles;
+  if (want < 1) want = 1;
+  if (want > n_raw) want = n_raw;
+  *stages_per_slice = (n_raw + want - 1) / want;
+  *slices = (n_raw + *stages_per_slice - 1) / *stages_per_slice;
+}
+
+bool umma_applies(const gb_weight* w, int64_t M) {
+  const gb_format& f = w->fmt;
+  return M >= 2 && M <= kMaxRows && f.grid == GB_GRID_FP4 && f.mode == GB_MODE_FULL && f.k_bits == 8 &&
+         f.scale_coding == GB_SCALE_V1 && f.type_size == kSbBytes && w->cb_row_offset == nullptr &&
+         w->K >= 1024 && w->rows >= kBM && (w->row_stride % 16) == 0 && ((uintptr_t)w->qw & 15u) == 0 &&
+         ((uintptr_t)w->codebook & 15u) == 0;
+}
+
+}  // namespace
+
+int gb_prepare_umma() {
+  GB_CUDA_OK(cudaFuncSetAttribute((const void*)umma_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  umma_smem_bytes(kMaxRows)));
+  return GB_OK;
+}
+
+int64_t gb_gemv_umma_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M < 2 || M > kMaxRows || K < 1024 || N < kBM) return 0;
+  const int64_t xq = (M * K * 2 + 255) & ~255ll;
+  int sms = gb_sm_count();
+  if (sms <= 0) sms = 148;
+  int slices, per;
+  umma_plan(N, (int)(K / 256), sms, &slices, &per);
+  return xq + (slices > 1 ? (int64_t)slices * M * N * 4 : 0);
+}
+
+int gb_gemv_umma(const void* x, int64_t M, const gb_weight* w, int act, int scale_rule, void* y, void* workspace,
+                 int64_t workspace_bytes, void* stream_) {
+  if (!umma_applies(w, M) || ((uintptr_t)x & 15u) != 0 || act == GB_ACT_FP8_TOKEN) return GB_EUNSUPPORTED;
+  const int sms = gb_sm_count();
+  if (sms <= 0) return gb_fail(GB_ECUDA, "no usable CUDA device: %s", gb_last_error());
+  const int64_t N = w->rows, K = w->K;
+  UmmaParams p = {};
+  p.N = N; p.K = K; p.M = (int)M; p.Mpad = (int)((M + 15) / 16 * 16);
+  p.n_sb = (int)(K / 256);
+  umma_plan(N, p.n_sb, sms, &p.slices, &p.stages_per_slice);
+  const int64_t xq_bytes = act == GB_ACT_NONE ? 0 : ((M * K * 2 + 255) & ~255ll);
+  const int64_t part_bytes = p.slices > 1 ? (int64_t)p.slices * M * N * 4 : 0;
+  if (xq_bytes + part_bytes > 0 && (workspace == nullptr || workspace_bytes < xq_bytes + part_bytes))
+    return gb_fail(GB_EWORKSPACE, "workspace of %lld bytes is too small (need %lld)", (long long)workspace_bytes,
+                   (long long)(xq_bytes + part_bytes));
+  const void* xin = x;
+  if (act == GB_ACT_FP4_GROUP16) {
+    int rc = gb_fp4_act_qdq(x, workspace, M, K, scale_rule, stream_);
+    if (rc != GB_OK) return rc;
+    xin = workspace;
+  }
+  CUtensorMap map_w, map_x;
+  int rc = gb_tensor_map_bytes_2d(&map_w, w->qw, (uint64_t)p.n_sb * kSbBytes, (uint64_t)N, (uint64_t)w->row_stride,
+                                  kRawRowBytes, kBM);
+  if (rc != GB_OK) return rc;
+  rc = gb_tensor_map_operand(&map_x, xin, M, K, 2, p.Mpad);
+  if (rc != GB_OK) return rc;
+  p.codebook = (const uint4*)w->codebook;
+  p.global_scale = w->global_scale == 0.0f ? 1.0f : w->global_scale;
+  p.y = (uint16_t*)y;
+  p.partial = p.slices > 1 ? (float*)((uint8_t*)workspace + xq_bytes) : nullptr;
+  // fp32 accumulate, bf16 x bf16, both K-major, N = activation rows (padded), M = 128 weight rows
+  p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.Mpad >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+  p.tmem_cols = 32;
+  while ((int)p.tmem_cols < p.Mpad) p.tmem_cols <<= 1;
+  p.status = gb_status_word();
+  dim3 grid((unsigned)((N + kBM - 1) / kBM), (unsigned)p.slices);
+  GB_CUDA_OK(gb_launch(umma_decode_kernel, grid, dim3(kUmmaThreads), (size_t)umma_smem_bytes(p.Mpad),
+                       (cudaStream_t)stream_, map_w, map_x, p));
+  if (p.slices > 1) {
+    const int64_t MN = M * N;
+    GB_CUDA_OK(gb_launch(umma_finalize_kernel, dim3((unsigned)((MN + 255) / 256)), dim3(256), 0,
+                         (cudaStream_t)stream_, (const float*)p.partial, p.slices, MN, p.global_scale,
+                         (uint16_t*)y));
+  }
+  return GB_OK;
+}

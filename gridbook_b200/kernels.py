@@ -167,9 +167,22 @@ _ACT = {None: nat.ACT_NONE, "none": nat.ACT_NONE, "fp4": nat.ACT_FP4_GROUP16,
         "fp8": nat.ACT_FP8_TOKEN}
 
 
+ROW_BATCH_MAX_M = 128      # rows the tensor-core decode kernel of the literal format takes
+
+
+def row_batch_kernel_applies(w: PackedWeight) -> bool:
+    """Whether 2..128 activation rows of this weight are served by the kernel that decodes into
+    shared memory and multiplies on the tensor cores (the conditions the library checks)."""
+    f = w.fmt
+    return (f.is_fp4 and f.mode == "full" and f.k == 8 and f.scale_coding == "v1" and w.experts == 1
+            and w.cb_row_offset is None and w.K >= 1024 and w.rows >= 128 and w.row_stride % 16 == 0
+            and w.qw.data_ptr() % 16 == 0 and w.codebook.data_ptr() % 16 == 0)
+
+
 def gemv(x: torch.Tensor, w: PackedWeight, *, act: str | None = None, scale_rule: str = "recip",
          out: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
-    """y[..., N] = bucket(x)[..., K] . W^T for up to 16 activation rows."""
+    """y[..., N] = bucket(x)[..., K] . W^T for up to 16 activation rows (up to 128 where
+    :func:`row_batch_kernel_applies`)."""
     _need_cuda(x)
     lib = nat.load("codebook decode GEMV")
     if x.dtype is not torch.bfloat16:

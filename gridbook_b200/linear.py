@@ -3,6 +3,8 @@
 1025-1264), dispatching to the sm_100a kernels through the C ABI."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _native, codec, kernels
@@ -12,6 +14,11 @@ from ._vllm_compat import (ChannelQuantScaleParameter, LinearMethodBase, ModelWe
 from .formats import CBFormat
 
 DECODE_MAX_M = 16          # the decode-batch kernels take up to sixteen rows
+MIDM_MAX_M = 128           # ... and the literal format's tensor-core decode kernel up to this many
+
+
+def midm_max_rows() -> int:
+    return min(int(os.environ.get("GRIDBOOK_B200_MIDM_MAX_M", MIDM_MAX_M)), kernels.ROW_BATCH_MAX_M)
 
 
 @register_weight_loader_v2_supported_method
@@ -122,7 +129,8 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         M = x2.shape[0]
         if M == 0:
             return x.new_empty((*x.shape[:-1], N))
-        if M <= DECODE_MAX_M:
+        if M <= DECODE_MAX_M or (M <= midm_max_rows() and kernels.row_batch_kernel_applies(w)):
+            # past sixteen rows: the literal format's tensor-core decode kernel, no decoded transient
             return kernels.gemv(x2, w, act=self.fmt.grid, scale_rule=ops.ACT_SCALE_RULE,
                                 workspace=layer._cb_workspace).reshape(*x.shape[:-1], N)
         return self._apply_prefill(layer, x2).reshape(*x.shape[:-1], N)

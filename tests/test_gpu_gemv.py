@@ -291,3 +291,29 @@ def test_literal_single_row_table_kernel(dev, N, K):
         xq = O.act_bucket(x, "fp4", "recip")
         y2 = kernels.gemv(synth.bf16_tensor(xq, dev), w)
         assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("N,K,M", [(256, 1024, 2), (384, 2048, 16), (1000, 2304, 5), (640, 1536, 100),
+                                   (2048, 5120, 9), (5120, 4352, 128), (300, 1280, 33)])
+def test_literal_row_batch_tensor_core_decode_kernel(dev, N, K, M):
+    """2..128 rows of the literal format take the kernel that decodes into shared memory and runs
+    tcgen05 MMAs with the weights on the M side: ragged row counts on both sides, a last raw stage
+    of one to three superblocks, one or several K slices, padded row stride, bucket applied by the
+    call or beforehand, zero / subnormal / negative scale bytes."""
+    from gridbook_b200 import _native, kernels, synth
+    fmt = _fmt("lit")
+    d = synth.make_linear(fmt, N, K, seed=N + K + M, global_scale=1.0 / 448.0)
+    qw = d["qw"].reshape(N, K // 256, 48)
+    qw[::7, 0, 32:40] = np.arange(8, dtype=np.uint8)
+    qw[::5, -1, 40:44] = np.array([0x88, 0xB8, 0xFE, 0x81], dtype=np.uint8)
+    d["qw"] = qw.reshape(N, -1)
+    x = synth.make_activations(M, K, seed=M)
+    ref = oracle_linear(x, d, bucket=True, scale_rule="recip")
+    for pad in (False, True):
+        w = synth.to_device_weight(d, dev, pad_rows=pad)
+        y = kernels.gemv(synth.bf16_tensor(x, dev), w, act="fp4")
+        torch.cuda.synchronize()
+        assert _native.device_status(0) == 0
+        assert_close_bf16(f32_of(y), ref, f"M={M} pad={pad}")
+        y2 = kernels.gemv(synth.bf16_tensor(O.act_bucket(x, "fp4", "recip"), dev), w)
+        assert torch.equal(y, y2)
