@@ -795,13 +795,14 @@ bool literal_aligned(const GemvParams& p) {
 }
 
 constexpr int kDotRowsMax = 8;      // most activation rows ever served by per-row table GEMVs
-int umma_min_rows() {               // rows from which the tensor-core decode kernel is tried (GRIDBOOK_B200_UMMA_MIN_M)
-  static const int v = [] {
-    const char* e = getenv("GRIDBOOK_B200_UMMA_MIN_M");
-    const int n = e ? atoi(e) : 2;
-    return n < 2 ? 2 : n;
-  }();
-  return v;
+// Rows from which the tensor-core decode kernel (gb_gemv_umma.cu) is tried.  Measured on the
+// benchmark's projections it is flat in the row count (gate_up: 86 us at 2..16 rows, 110 us at
+// 128) and passes the expanding kernel past sixteen rows; below that the table and expanding
+// kernels are faster on the large projections.  GRIDBOOK_B200_UMMA_MIN_M overrides (read per call).
+int umma_min_rows() {
+  const char* e = getenv("GRIDBOOK_B200_UMMA_MIN_M");
+  const int n = e ? atoi(e) : 17;
+  return n < 2 ? 2 : n;
 }
 
 int dot_rows_max() {                // rows up to which they are actually used (GRIDBOOK_B200_DOT_ROWS overrides)

@@ -295,12 +295,13 @@ def test_literal_single_row_table_kernel(dev, N, K):
 
 @pytest.mark.parametrize("N,K,M", [(256, 1024, 2), (384, 2048, 16), (1000, 2304, 5), (640, 1536, 100),
                                    (2048, 5120, 9), (5120, 4352, 128), (300, 1280, 33)])
-def test_literal_row_batch_tensor_core_decode_kernel(dev, N, K, M):
+def test_literal_row_batch_tensor_core_decode_kernel(dev, monkeypatch, N, K, M):
     """2..128 rows of the literal format take the kernel that decodes into shared memory and runs
     tcgen05 MMAs with the weights on the M side: ragged row counts on both sides, a last raw stage
     of one to three superblocks, one or several K slices, padded row stride, bucket applied by the
     call or beforehand, zero / subnormal / negative scale bytes."""
     from gridbook_b200 import _native, kernels, synth
+    monkeypatch.setenv("GRIDBOOK_B200_UMMA_MIN_M", "2")       # by default it serves 17 rows and more
     fmt = _fmt("lit")
     d = synth.make_linear(fmt, N, K, seed=N + K + M, global_scale=1.0 / 448.0)
     qw = d["qw"].reshape(N, K // 256, 48)
