@@ -274,7 +274,7 @@ def run_gpu(args):
     # ---- the other decode batch sizes of the configuration (same stack, through the linear method) ----
     dense_m = {}
     if world == 1 and not args.no_msweep:
-        for m_other in (4, 16):
+        for m_other in (4, 16, 64):
             if m_other == M:
                 continue
             xs = [torch.randn(m_other, K, generator=gen, device=device).to(torch.bfloat16) for _, _, K in PROJECTIONS]

@@ -107,11 +107,17 @@ GB_API int gb_expand_fp4_bf16(const gb_weight* w, int64_t row0, int64_t nrows, v
 GB_API int gb_expand_fp4_nvfp4(const gb_weight* w, int64_t row0, int64_t nrows, void* out_packed,
                         void* out_sf, int sf_swizzled, void* stream);
 
-/* ---- decode-batch linear (M <= 16) ------------------------------------------ */
+/* ---- decode-batch linear (M <= 16; M <= 128 for the literal fp4 format) -------- */
 /* replaces cb_gemv_fp8 / cb_gemv_fp4_v2 (gridbook/csrc/cb_gemv.cu:658-712,1138-1198;
  * gridbook/ops.py:52-93).  y[M,N] = bucket(x)[M,K] . W^T, fp32 accumulate, one bf16
  * rounding.  `act` selects a fused activation bucket applied to x first (GB_ACT_NONE
- * when x is already bucketed).  workspace: gb_gemv_workspace_bytes() bytes. */
+ * when x is already bucketed).  workspace: gb_gemv_workspace_bytes() bytes.
+ * 17 <= M <= 128 is served for the literal format (fp4 grid, full mode, k = 8, v1 scales, one
+ * codebook, K >= 1024, N >= 128, 16-byte aligned rows) by a kernel that decodes the packed rows
+ * into shared memory and multiplies on the tensor cores (tcgen05, weights on the M side) - the
+ * decode-in-mainloop band of the reference (gridbook/csrc/cb_fused_fp4v2_gemm.cu, M <= 128)
+ * with the decode contract kept; other formats return GB_EUNSUPPORTED there and take the
+ * expand + gb_gemm_tn route. */
 GB_API int64_t gb_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K);
 GB_API int gb_gemv(const void* x_bf16, int64_t M, const gb_weight* w, int act, int scale_rule,
             void* y_bf16, void* workspace, int64_t workspace_bytes, void* stream);
