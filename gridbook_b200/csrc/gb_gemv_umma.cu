@@ -5,8 +5,8 @@
 // streams the packed rows (4 superblocks = 192 bytes per row and stage) into shared memory with
 // tiled TMA loads, one warp streams the matching 64-wide K slabs of the (bucketed) activations
 // with the 128-byte swizzle, eight warps decode: a thread takes one codeword (code byte ->
-// 16-byte codebook entry from a shared-memory copy, group scale byte -> bf16 pair from a
-// 256-entry table, four packed bf16 multiplies = bf16(value * scale), the decode contract) and
+// 16-byte codebook entry from a shared-memory copy, group scale byte -> bf16 pair by three
+// integer operations, four packed bf16 multiplies = bf16(value * scale), the decode contract) and
 // stores the eight weights as one 16-byte chunk at its swizzled place of a K-major 128 x 64 bf16
 // slab.  One thread issues tcgen05.mma (M = 128 weight rows, N = activation rows padded to 16,
 // kind::f16) on the decoded slab and the activation slab; the fp32 accumulator lives in tensor
@@ -24,6 +24,7 @@ constexpr int kRawSb = 4;                                 // superblocks per raw
 constexpr int kSbBytes = 48;                              // literal superblock: 32 codes + 16 scales
 constexpr int kRawRowBytes = kRawSb * kSbBytes;           // 192
 constexpr int kRawStageBytes = kBM * kRawRowBytes;        // 24 KiB
+constexpr int kRawSbBytes = kBM * kSbBytes;               // one superblock column of a stage: 48-byte rows
 constexpr int kRawStages = 3;
 constexpr int kSlabStages = 4;
 constexpr int kASlabBytes = kBM * 128;                    // 128 rows x 64 bf16
@@ -95,8 +96,7 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   uint8_t* slabs = smem;                                   // kSlabStages x (A slab | x slab)
   uint8_t* raw = slabs + kSlabStages * slab_bytes;         // kRawStages x packed rows
   uint4* cb_s = reinterpret_cast<uint4*>(raw + kRawStages * kRawStageBytes);
-  uint32_t* lut_s = reinterpret_cast<uint32_t*>(cb_s + 256);
-  uint64_t* raw_full = reinterpret_cast<uint64_t*>(lut_s + 256);
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(cb_s + 256);
   uint64_t* raw_empty = raw_full + kRawStages;
   uint64_t* slab_full = raw_empty + kRawStages;
   uint64_t* slab_empty = slab_full + kSlabStages;
@@ -130,11 +130,19 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (warp >= kCtlWarps) {
-    // constants of the layer: the codebook and the E4M3 -> bf16 pair table of the group scales
+    // constant of the layer: the codebook
     const int d = threadIdx.x - 32 * kCtlWarps;
-    cb_s[d] = __ldg(p.codebook + d);
-    const uint32_t bits = __float_as_uint(gb_e4m3_to_f32((uint32_t)d)) >> 16;
-    lut_s[d] = bits * 0x10001u;
+    // The group scale is used as the E4M3 byte moved into bf16's fields, i.e. 2^-120 times its
+    // value (exact, subnormal codes included); the codebook copy carries the 2^120 (exact for the
+    // fp4 grid's values), so the packed multiply still rounds the exact product value * scale once.
+    const uint4 e = __ldg(p.codebook + d);
+    uint4 w;
+    const uint32_t two120 = 0x7B807B80u;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(w.x) : "r"(e.x), "r"(two120));
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(w.y) : "r"(e.y), "r"(two120));
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(w.z) : "r"(e.z), "r"(two120));
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(w.w) : "r"(e.w), "r"(two120));
+    cb_s[d] = w;
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -149,7 +157,12 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const int rs = it % kRawStages;
         wait_or_abort(&raw_empty[rs], ((it / kRawStages) & 1) ^ 1, abort_flag, p.status, 21);
         gb_mbar_expect_tx(&raw_full[rs], kRawStageBytes);
-        tma_load_2d(raw + (size_t)rs * kRawStageBytes, &map_w, r * kRawRowBytes, n0, &raw_full[rs]);
+        // one box per superblock column: with 48-byte rows in shared memory the four rows a decoder
+        // warp reads at a time sit on different banks (192-byte rows would share two)
+#pragma unroll
+        for (int sbi = 0; sbi < kRawSb; ++sbi)
+          tma_load_2d(raw + (size_t)rs * kRawStageBytes + sbi * kRawSbBytes, &map_w,
+                      r * kRawRowBytes + sbi * kSbBytes, n0, &raw_full[rs]);
       }
     }
   } else if (warp == 1) {
@@ -205,7 +218,7 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           uint32_t code[4], sc[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const uint8_t* rp = stage + (i * 32 + rsub) * kRawRowBytes + sbi * kSbBytes;
+            const uint8_t* rp = stage + sbi * kRawSbBytes + (i * 32 + rsub) * kSbBytes;
             code[i] = rp[q * 8 + j];
             sc[i] = rp[32 + q * 4 + (j >> 1)];
           }
@@ -213,7 +226,7 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           for (int i = 0; i < 4; ++i) {
             const int row = i * 32 + rsub;
             const uint4 e = cb_s[code[i]];
-            const uint32_t s2 = lut_s[sc[i]];
+            const uint32_t s2 = (((sc[i] & 0x7Fu) << 4) | ((sc[i] & 0x80u) << 8)) * 0x10001u;
             uint4 w;
             asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(w.x) : "r"(e.x), "r"(s2));
             asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(w.y) : "r"(e.y), "r"(s2));
@@ -281,7 +294,7 @@ umma_finalize_kernel(const float* __restrict__ partial, int slices, int64_t MN, 
 }
 
 int umma_smem_bytes(int Mpad) {
-  return 1024 + kSlabStages * (kASlabBytes + Mpad * 128) + kRawStages * kRawStageBytes + 4096 + 1024 + 256;
+  return 1024 + kSlabStages * (kASlabBytes + Mpad * 128) + kRawStages * kRawStageBytes + 4096 + 256;
 }
 
 // K slices: enough CTAs for the SMs when the layer has few 128-row tiles.
@@ -344,7 +357,7 @@ int gb_gemv_umma(const void* x, int64_t M, const gb_weight* w, int act, int scal
   }
   CUtensorMap map_w, map_x;
   int rc = gb_tensor_map_bytes_2d(&map_w, w->qw, (uint64_t)p.n_sb * kSbBytes, (uint64_t)N, (uint64_t)w->row_stride,
-                                  kRawRowBytes, kBM);
+                                  kSbBytes, kBM);
   if (rc != GB_OK) return rc;
   rc = gb_tensor_map_operand(&map_x, xin, M, K, 2, p.Mpad);
   if (rc != GB_OK) return rc;
