@@ -342,10 +342,11 @@ def run_gpu(args):
     achieved = launch_bytes / (launch_ms * 1e-3) / 1e9
     # M = 1 on the literal format runs the inner-product-table kernel (plus its slot-summing
     # kernel, timed with it); everything else the expanding MMA kernel
-    dominant_kernel = "gemv_dot_kernel" if (M == 1 and args.format == "literal") else "gemv_kernel"
+    dominant_kernel = ("gemv_dot_kernel" if (M == 1 and args.format == "literal")
+                       else "umma_decode_kernel" if (M > 16 and args.format == "literal") else "gemv_kernel")
     # DRAM bytes per launch over algorithmic bytes, from the committed ncu captures of these
     # kernels (profiles/): the weight stream is read once and nothing else reaches DRAM
-    traffic_ratio = {"gemv_dot_kernel": 1.002, "gemv_kernel": 1.01}[dominant_kernel]
+    traffic_ratio = {"gemv_dot_kernel": 1.002, "gemv_kernel": 1.01, "umma_decode_kernel": 1.02}[dominant_kernel]
     line = {
         "metric": "CB GEMV weight GB/s (% HBM peak); grouped-MoE decode tok/s at 1/2/4/8 B200",
         "value": round(gbs, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
