@@ -941,7 +941,8 @@ int gb_gemv(const void* x, int64_t M, const gb_weight* w, int act, int scale_rul
     if (rc != GB_EUNSUPPORTED) return rc;
   }
   if (M > 16)
-    return gb_fail(GB_EUNSUPPORTED, "more than 16 rows are served for the literal fp4 format only (M=%lld)",
+    return gb_fail(GB_EUNSUPPORTED,
+                   "more than 16 rows (M=%lld) are served for the literal fp4 format with K >= 1024 and N >= 128 only",
                    (long long)M);
   if (M == 1) {
     // one activation row of the literal format: inner-product tables instead of per-weight expansion

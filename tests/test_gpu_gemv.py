@@ -101,8 +101,11 @@ def test_gemv_shape_errors(dev):
     from gridbook_b200 import kernels, synth
     d = synth.make_linear(_fmt("lit"), 16, 256, seed=1)
     w = synth.to_device_weight(d, dev)
-    with pytest.raises(RuntimeError, match="1..16 rows"):
+    # a small layer has no 17..128-row kernel; no layer has one past 128 rows
+    with pytest.raises(RuntimeError, match="more than 16 rows"):
         kernels.gemv(torch.zeros(17, 256, dtype=torch.bfloat16, device=dev), w)
+    with pytest.raises(RuntimeError, match="1..128 rows"):
+        kernels.gemv(torch.zeros(129, 256, dtype=torch.bfloat16, device=dev), w)
 
 
 # ---- routed MoE -----------------------------------------------------------------
