@@ -430,8 +430,8 @@ def bench_moe(args, device, world, rank, peers=None):
         layers.append(moe)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     out = {}
-    # one GPU also times a prefill batch: it takes the grouped tensor-core route
-    for T in ((1, 16, 64, 256, 4096) if world == 1 else (1, 16, 64, 256)):
+    # one GPU also times two larger batches: they take the sorted-rows and the grouped-GEMM tensor-core routes
+    for T in ((1, 16, 64, 256, 1024, 4096) if world == 1 else (1, 16, 64, 256)):
         ids, tw = synth.make_routing(T, E, topk, seed=T + 13 * rank)
         x = torch.randn(T, hidden, generator=gen, device=device).to(torch.bfloat16)
         ids_d, tw_d = torch.from_numpy(ids).to(device), torch.from_numpy(tw).to(device)
@@ -479,7 +479,7 @@ def bench_moe(args, device, world, rank, peers=None):
             entry.update({"experts_touched": touched, "weight_gb_s": round(gbs, 1),
                           "pct_hbm_peak": round(100.0 * gbs / measured_peaks()[0]["hbm_gbs"], 2)})
             route = getattr(layers[0], "_cb_route", "")
-            if isinstance(route, str) and route.startswith("grouped prefill"):
+            if isinstance(route, str) and (route.startswith("grouped prefill") or route.startswith("sorted rows")):
                 tf = 2.0 * int((ids >= 0).sum()) * 3 * inter * hidden / (ms_layer * 1e-3) / 1e12
                 entry.update({"route": route, "tflops": round(tf, 1),
                               "pct_bf16_peak": round(100.0 * tf / measured_peaks()[0]["bf16_tflops"], 2)})

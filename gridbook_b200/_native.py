@@ -24,7 +24,7 @@ REQUIRED_SYMBOLS = (
     "gb_moe_route", "gb_moe_route_ws", "gb_moe_route_workspace_bytes", "gb_moe_gemv_workspace_bytes", "gb_moe_gemv", "gb_moe_combine",
     "gb_moe_gemv_pairs_workspace_bytes", "gb_moe_gemv_pairs",
     "gb_moe_mlp_pairs_workspace_bytes", "gb_moe_mlp_pairs",
-    "gb_expand_fp8_bf16", "gb_fp8_quantize_rows", "gb_gemm_tn", "gb_gemm_tn_grouped", "gb_moe_gather_rows", "gb_moe_swiglu_rows",
+    "gb_expand_fp8_bf16", "gb_fp8_quantize_rows", "gb_gemm_tn", "gb_gemm_tn_grouped", "gb_moe_gather_rows", "gb_moe_swiglu_rows", "gb_moe_gemv_sorted",
     "gb_peer_alloc", "gb_peer_free", "gb_peer_export", "gb_peer_open", "gb_peer_close",
     "gb_peer_allgather", "gb_peer_allgather_ll", "gb_peer_barrier", "gb_launch_count", "gb_gemv_allgather", "gb_moe_combine_peer",
 )
@@ -130,6 +130,7 @@ def _declare(lib) -> None:
     lib.gb_gemm_tn.argtypes = [vp, vp, vp, i64, i64, i64, i32, vp, vp, ctypes.c_float, vp]
     lib.gb_gemm_tn_grouped.argtypes = [vp, vp, vp, i64, i64, i64, i32, i64, vp, vp, vp, vp, ctypes.c_float, vp]
     lib.gb_moe_gather_rows.argtypes = [vp, vp, vp, vp, i64, i64, i64, vp, vp]
+    lib.gb_moe_gemv_sorted.argtypes = [vp, wp, i64, i64, vp, vp, i64, vp, vp]
     lib.gb_moe_swiglu_rows.argtypes = [vp, vp, i64, i64, i64, i32, i32, vp, vp]
     lib.gb_launch_count.restype = i64
     lib.gb_peer_alloc.argtypes = [i64, ctypes.POINTER(vp)]

@@ -43,10 +43,16 @@ struct UmmaParams {
   float global_scale;
   uint16_t* y;              // [M, N] bf16 (one slice)
   float* partial;           // [slices, M, N] fp32 (several slices)
-  uint32_t idesc;
+  uint32_t idesc;            // with N = Mpad (dense); grouped mode sets N per pass
   uint32_t tmem_cols;
   int* status;
+  // grouped mode (routed experts): x rows are sorted by expert, expert e owns rows [seg[e], seg[e+1])
+  const int32_t* seg;        // [E+1]
+  const int32_t* row_map;    // [P] output row of a sorted row, or null = identity
+  int tiles_n;               // 128-row tiles per expert
 };
+
+constexpr int kGroupRows = 64;                            // activation rows per pass in grouped mode
 
 GB_DEVINL void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
   asm volatile(
@@ -86,6 +92,7 @@ GB_DEVINL void wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort
   }
 }
 
+template <bool kGrouped>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    const UmmaParams p) {
@@ -101,16 +108,30 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   uint64_t* slab_full = raw_empty + kRawStages;
   uint64_t* slab_empty = slab_full + kSlabStages;
   uint64_t* acc_full = slab_empty + kSlabStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* acc_empty = acc_full + 1;                      // grouped mode: the accumulator has been read out
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * kBM;
   const int n_raw = (p.n_sb + kRawSb - 1) / kRawSb;
   const int r_begin = blockIdx.y * p.stages_per_slice;
   const int r_end = min(n_raw, r_begin + p.stages_per_slice);
 
   gb_pdl_launch_dependents();
+  // Dense: one pass over rows [0, M) of x.  Grouped: the CTA's expert, its rows of the sorted x in
+  // passes of 64 (the weights are decoded again per pass), nothing to do for an expert without rows.
+  int n0 = blockIdx.x * kBM, w_row0 = n0, seg_lo = 0, cnt = p.M;
+  if (kGrouped) {
+    gb_pdl_wait();                                         // the segment offsets come from the routing launch
+    const int e = blockIdx.x / p.tiles_n;
+    n0 = (blockIdx.x - e * p.tiles_n) * kBM;
+    w_row0 = e * (int)p.N + n0;
+    seg_lo = p.seg[e];
+    cnt = p.seg[e + 1] - seg_lo;
+    if (cnt <= 0) return;
+  }
+  const int pass_rows = kGrouped ? kGroupRows : p.Mpad;
+  const int n_pass = (cnt + pass_rows - 1) / pass_rows;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRawStages; ++s) {
       gb_mbar_init(&raw_full[s], 1);
@@ -121,6 +142,7 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       gb_mbar_init(&slab_empty[s], 1);
     }
     gb_mbar_init(acc_full, 1);
+    gb_mbar_init(acc_empty, kDecWarps);
     *abort_flag = 0;
     gb_fence_barrier_init();
   }
@@ -153,7 +175,8 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   if (warp == 0) {
     // ------------------------- packed weight rows -------------------------
     if (lane == 0) {
-      for (int r = r_begin, it = 0; r < r_end; ++r, ++it) {
+      for (int pass = 0, it = 0; pass < n_pass; ++pass)
+      for (int r = r_begin; r < r_end; ++r, ++it) {
         const int rs = it % kRawStages;
         wait_or_abort(&raw_empty[rs], ((it / kRawStages) & 1) ^ 1, abort_flag, p.status, 21);
         gb_mbar_expect_tx(&raw_full[rs], kRawStageBytes);
@@ -162,21 +185,22 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
         for (int sbi = 0; sbi < kRawSb; ++sbi)
           tma_load_2d(raw + (size_t)rs * kRawStageBytes + sbi * kRawSbBytes, &map_w,
-                      r * kRawRowBytes + sbi * kSbBytes, n0, &raw_full[rs]);
+                      r * kRawRowBytes + sbi * kSbBytes, w_row0, &raw_full[rs]);
       }
     }
   } else if (warp == 1) {
     // ------------------------- activation slabs ---------------------------
     if (lane == 0) {
       int slab = 0;
+      for (int pass = 0; pass < n_pass; ++pass)
       for (int r = r_begin; r < r_end; ++r) {
         const int n_here = min(kRawSb, p.n_sb - r * kRawSb) * 4;       // slabs of this raw stage
         for (int q = 0; q < n_here; ++q, ++slab) {
           const int s = slab % kSlabStages;
           wait_or_abort(&slab_empty[s], ((slab / kSlabStages) & 1) ^ 1, abort_flag, p.status, 22);
           gb_mbar_expect_tx(&slab_full[s], (uint32_t)b_bytes);
-          tma_load_2d(slabs + (size_t)s * slab_bytes + kASlabBytes, &map_x, r * (kRawSb * 256) + q * 64, 0,
-                      &slab_full[s]);
+          tma_load_2d(slabs + (size_t)s * slab_bytes + kASlabBytes, &map_x, r * (kRawSb * 256) + q * 64,
+                      seg_lo + pass * pass_rows, &slab_full[s]);
         }
       }
     }
@@ -184,6 +208,18 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     // ------------------------- MMA issuer ----------------------------------
     if (lane == 0) {
       int slab = 0;
+      for (int pass = 0; pass < n_pass; ++pass) {
+      // grouped mode: N = this pass's rows rounded up to 16; the previous pass must have been read out
+      uint32_t idesc = p.idesc;
+      if (kGrouped) {
+        const int rows = min(pass_rows, cnt - pass * pass_rows);
+        idesc = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)(((rows + 15) / 16 * 16) >> 3) << 17);
+        if (pass > 0) {
+          wait_or_abort(acc_empty, (pass - 1) & 1, abort_flag, p.status, 28);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+      }
+      const int slab0 = slab;
       for (int r = r_begin; r < r_end; ++r) {
         const int n_here = min(kRawSb, p.n_sb - r * kRawSb) * 4;
         for (int q = 0; q < n_here; ++q, ++slab) {
@@ -194,18 +230,20 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + kASlabBytes);
 #pragma unroll
           for (int k = 0; k < 4; ++k)                        // 16 weights of K per instruction
-            umma_bf16(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), p.idesc, slab > 0 || k > 0);
+            umma_bf16(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, slab > slab0 || k > 0);
           umma_commit(&slab_empty[s]);
         }
       }
       umma_commit(acc_full);
+      }
     }
   } else {
     // ------------------------- decoders -------------------------------------
     const int d = threadIdx.x - 32 * kCtlWarps;
     const int j = d & 7, rsub = d >> 3;                      // codeword of the slab row, row inside a 32-row band
-    int slab = 0;
-    for (int r = r_begin, it = 0; r < r_end; ++r, ++it) {
+    int slab = 0, it = 0;
+    for (int pass = 0; pass < n_pass; ++pass) {
+    for (int r = r_begin; r < r_end; ++r, ++it) {
       const int rs = it % kRawStages;
       wait_or_abort(&raw_full[rs], (it / kRawStages) & 1, abort_flag, p.status, 24);
       const uint8_t* stage = raw + (size_t)rs * kRawStageBytes;
@@ -245,31 +283,43 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
 
     // ------------------------- read-out ------------------------------------
-    wait_or_abort(acc_full, 0, abort_flag, p.status, 26);
+    wait_or_abort(acc_full, pass & 1, abort_flag, p.status, 26);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int quarter = warp & 3;                            // the tensor-memory lanes this warp may read
-    const int half = (warp - kCtlWarps) >> 2;                // column chunks: even / odd
-    const int64_t row = (int64_t)n0 + quarter * 32 + lane;
+    const int col_half = (warp - kCtlWarps) >> 2;            // column chunks: even / odd
+    const int64_t out_col = (int64_t)n0 + quarter * 32 + lane;
     const bool ok = *abort_flag == 0;
-    for (int c = half; c < p.Mpad / 8; c += 2) {
+    const int rows = min(pass_rows, cnt - pass * pass_rows);
+    for (int c = col_half; c < (rows + 7) / 8; c += 2) {
       uint32_t v[8];
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 8);
       asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
                    : "r"(taddr));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (ok && row < p.N) {
+      if (ok && out_col < p.N) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int m = c * 8 + i;
-          if (m < p.M) {
-            if (p.slices > 1)
-              p.partial[((int64_t)blockIdx.y * p.M + m) * p.N + row] = __uint_as_float(v[i]);
-            else
-              p.y[(int64_t)m * p.N + row] = (uint16_t)gb_f32_to_bf16_bits(__uint_as_float(v[i]) * p.global_scale);
+          if (m < rows) {
+            if (kGrouped) {
+              const int jrow = seg_lo + pass * pass_rows + m;          // sorted position of the row
+              const int64_t orow = p.row_map ? p.row_map[jrow] : jrow;
+              p.y[orow * p.N + out_col] = (uint16_t)gb_f32_to_bf16_bits(__uint_as_float(v[i]) * p.global_scale);
+            } else if (p.slices > 1) {
+              p.partial[((int64_t)blockIdx.y * p.M + m) * p.N + out_col] = __uint_as_float(v[i]);
+            } else {
+              p.y[(int64_t)m * p.N + out_col] = (uint16_t)gb_f32_to_bf16_bits(__uint_as_float(v[i]) * p.global_scale);
+            }
           }
         }
       }
+    }
+    if (kGrouped && pass + 1 < n_pass) {                     // hand the accumulator back for the next pass
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) gb_mbar_arrive(acc_empty);
+    }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -319,8 +369,10 @@ bool umma_applies(const gb_weight* w, int64_t M) {
 }  // namespace
 
 int gb_prepare_umma() {
-  GB_CUDA_OK(cudaFuncSetAttribute((const void*)umma_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  umma_smem_bytes(kMaxRows)));
+  GB_CUDA_OK(cudaFuncSetAttribute((const void*)umma_decode_kernel<false>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, umma_smem_bytes(kMaxRows)));
+  GB_CUDA_OK(cudaFuncSetAttribute((const void*)umma_decode_kernel<true>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, umma_smem_bytes(kGroupRows)));
   return GB_OK;
 }
 
@@ -371,7 +423,7 @@ int gb_gemv_umma(const void* x, int64_t M, const gb_weight* w, int act, int scal
   while ((int)p.tmem_cols < p.Mpad) p.tmem_cols <<= 1;
   p.status = gb_status_word();
   dim3 grid((unsigned)((N + kBM - 1) / kBM), (unsigned)p.slices);
-  GB_CUDA_OK(gb_launch(umma_decode_kernel, grid, dim3(kUmmaThreads), (size_t)umma_smem_bytes(p.Mpad),
+  GB_CUDA_OK(gb_launch(umma_decode_kernel<false>, grid, dim3(kUmmaThreads), (size_t)umma_smem_bytes(p.Mpad),
                        (cudaStream_t)stream_, map_w, map_x, p));
   if (p.slices > 1) {
     const int64_t MN = M * N;
@@ -381,3 +433,47 @@ int gb_gemv_umma(const void* x, int64_t M, const gb_weight* w, int act, int scal
   }
   return GB_OK;
 }
+
+extern "C" {
+
+int gb_moe_gemv_sorted(const void* x_sorted, const gb_weight* w, int64_t expert_stride, int64_t E,
+                       const int32_t* seg_offsets, const int32_t* row_map, int64_t P, void* y, void* stream_) {
+  GB_REQUIRE(x_sorted && w && seg_offsets && y, "null pointer argument");
+  GB_REQUIRE(E >= 1 && P >= 0, "bad shape E=%lld P=%lld", (long long)E, (long long)P);
+  int rc = gb_check_weight(w);
+  if (rc != GB_OK) return rc;
+  const gb_format& f = w->fmt;
+  const int64_t N = w->rows, K = w->K;
+  if (!(f.grid == GB_GRID_FP4 && f.mode == GB_MODE_FULL && f.k_bits == 8 && f.scale_coding == GB_SCALE_V1 &&
+        f.type_size == kSbBytes && w->cb_row_offset == nullptr && N % kBM == 0 && (w->row_stride % 16) == 0 &&
+        expert_stride == N * w->row_stride && ((uintptr_t)w->qw & 15u) == 0 && ((uintptr_t)w->codebook & 15u) == 0 &&
+        ((uintptr_t)x_sorted & 15u) == 0 && E * N < (1ll << 31)))
+    return gb_fail(GB_EUNSUPPORTED, "the sorted-rows expert kernel takes contiguous stacks of the literal fp4 format with N %% 128 == 0");
+  if (P == 0) return GB_OK;
+  if (gb_sm_count() <= 0) return gb_fail(GB_ECUDA, "no usable CUDA device: %s", gb_last_error());
+  UmmaParams p = {};
+  p.N = N; p.K = K; p.M = kGroupRows; p.Mpad = kGroupRows;
+  p.n_sb = (int)(K / 256);
+  p.slices = 1;
+  p.stages_per_slice = (p.n_sb + kRawSb - 1) / kRawSb;
+  CUtensorMap map_w, map_x;
+  rc = gb_tensor_map_bytes_2d(&map_w, w->qw, (uint64_t)p.n_sb * kSbBytes, (uint64_t)(E * N), (uint64_t)w->row_stride,
+                              kSbBytes, kBM);
+  if (rc != GB_OK) return rc;
+  rc = gb_tensor_map_operand(&map_x, x_sorted, P, K, 2, kGroupRows);
+  if (rc != GB_OK) return rc;
+  p.codebook = (const uint4*)w->codebook;
+  p.global_scale = w->global_scale == 0.0f ? 1.0f : w->global_scale;
+  p.y = (uint16_t*)y;
+  p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kGroupRows >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+  p.tmem_cols = kGroupRows;
+  p.status = gb_status_word();
+  p.seg = seg_offsets; p.row_map = row_map;
+  p.tiles_n = (int)(N / kBM);
+  dim3 grid((unsigned)(E * p.tiles_n), 1);
+  GB_CUDA_OK(gb_launch(umma_decode_kernel<true>, grid, dim3(kUmmaThreads), (size_t)umma_smem_bytes(kGroupRows),
+                       (cudaStream_t)stream_, map_w, map_x, p));
+  return GB_OK;
+}
+
+}  // extern "C"

@@ -18,7 +18,17 @@ PAIR_KERNEL_MAX_PAIRS = 768       # routed pairs up to which every pair runs as 
 FUSED_BUCKET_MAX_PAIRS = 32       # routed pairs up to which the grouped kernel buckets its own rows
 # From this many routed pairs per expert (on average) the routed layer decodes each stack once
 # and runs grouped tensor-core GEMMs instead of the decode kernel's 16-row passes.
-PREFILL_MIN_PAIRS_PER_EXPERT = 56
+PREFILL_MIN_PAIRS_PER_EXPERT = 104
+
+
+# Between the two: from this many routed pairs per expert on, the rows are sorted by expert and
+# every (expert, 128-row tile) decodes its weights once into shared memory for a tensor-core MMA
+# (literal fp4 stacks only); below it the decode kernel's 16-row passes are faster.
+SORTED_MIN_PAIRS_PER_EXPERT = 18
+
+
+def sorted_min_pairs_per_expert() -> int:
+    return int(os.environ.get("GRIDBOOK_B200_MOE_SORTED_MIN", SORTED_MIN_PAIRS_PER_EXPERT))
 
 
 def prefill_min_pairs_per_expert() -> int:
@@ -185,6 +195,10 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         ids = topk_ids.to(torch.int32).contiguous()
         if T * topk >= prefill_min_pairs_per_expert() * layer._cb_E:
             return self._apply_prefill(layer, x2, topk_weights, ids, rule).to(x.dtype).reshape(x.shape)
+        if T * topk >= sorted_min_pairs_per_expert() * layer._cb_E:
+            out = self._apply_sorted(layer, x2, topk_weights, ids, rule)
+            if out is not None:
+                return out.to(x.dtype).reshape(x.shape)
         if T * topk <= PAIR_KERNEL_MAX_PAIRS and self.fmt13.is_fp4 and self.fmt2.is_fp4:
             out = self._apply_pairs(layer, x2, topk_weights, ids, rule)
             if out is not None:
@@ -248,6 +262,31 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
             h = bucket(kernels.moe_swiglu_rows(stage(a, w13, None), offsets), w2)
         y = stage(h, w2, order)                               # rows back in pair order
         layer._cb_route = "grouped prefill: expand + gemm_tn_grouped"
+        return kernels.moe_combine(y, pair_w, T, topk, topk_ids=ids, E=E)
+
+    def _apply_sorted(self, layer, x2, topk_weights, ids, rule):
+        """Mid-size batches of literal fp4 stacks: route, bucket, bring the rows into expert order,
+        then per projection one launch in which every (expert, 128-row tile) decodes its packed rows
+        into shared memory and multiplies them with the expert's rows on the tensor cores (tcgen05,
+        64 rows per pass); SwiGLU and the second bucket in one launch between them; the down
+        projection stores its rows back in pair order for the combine.  None when the stacks are not
+        of that format."""
+        w13, w2 = layer._cb_w13, layer._cb_w2
+        if not (w13.fmt.is_fp4 and w2.fmt.is_fp4 and layer._cb_inter % 16 == 0):
+            return None
+        T, topk = ids.shape
+        E = layer._cb_E
+        _, offsets, order, pair_w = kernels.moe_route(ids, E, topk_weights)
+        x_row = self._x_row(layer, T, topk, x2.device)
+        a = kernels.moe_gather_rows(kernels.fp4_act_qdq(x2, rule), order, offsets, x_row=x_row)
+        h13 = kernels.moe_gemv_sorted(a, w13, offsets)
+        if h13 is None:
+            return None
+        h = kernels.moe_swiglu_rows(h13, offsets, act="fp4", scale_rule=rule)
+        y = kernels.moe_gemv_sorted(h, w2, offsets, row_map=order)
+        if y is None:
+            return None
+        layer._cb_route = "sorted rows: decode in shared memory + tcgen05"
         return kernels.moe_combine(y, pair_w, T, topk, topk_ids=ids, E=E)
 
     def _apply_pairs(self, layer, x2, topk_weights, ids, rule):

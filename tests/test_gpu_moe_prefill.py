@@ -132,3 +132,34 @@ def test_moe_method_prefill_route_matches_loop_chain(dev, monkeypatch, f13, f2, 
     rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
     assert rel <= 1e-2, rel                                         # acceptance bar of the path
     assert np.abs(got - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
+
+
+@pytest.mark.parametrize("T", [40, 150, 700])
+def test_moe_method_sorted_rows_route_matches_loop_chain(dev, monkeypatch, T):
+    """The routed layer on the sorted-rows route (decode in shared memory + tcgen05 per expert tile),
+    forced on for this small shape: experts with no rows, with a few, and with more than one
+    64-row pass; a padded (-1) slot."""
+    from gridbook_b200 import _native, synth
+    from gridbook_b200.moe import CBMoE
+    from tests.test_gpu_plugin import _formats, _tables
+    monkeypatch.setenv("GRIDBOOK_B200_MOE_SORTED_MIN", "1")
+    monkeypatch.setenv("GRIDBOOK_B200_MOE_PREFILL_MIN", "1000000")
+    fmt = _formats()["lit"]
+    E, hidden, inter, topk = 8, 1024, 512, 2
+    w13d, w2d = synth.make_moe(fmt, fmt, E, hidden, inter, seed=T)
+    ids, tw = synth.make_routing(T, E - 1, topk, seed=T)          # expert E-1 stays empty
+    x = synth.make_activations(T, hidden, seed=T + 1)
+    ids[2, 1] = -1
+    ids_ref = np.where(ids < 0, 0, ids)
+    tw_ref = np.where(ids < 0, 0.0, tw).astype(np.float32)
+    ref = O.moe_loop_chain(x, ids_ref, tw_ref, w13d, w2d, E=E, hidden=hidden, inter=inter,
+                           fmt13=fmt.oracle_kwargs(), fmt2=fmt.oracle_kwargs(), scale_rule="recip")
+    moe = CBMoE(fmt, fmt, E, hidden, inter, _tables(fmt, w13d["cb"]), _tables(fmt, w2d["cb"]))
+    moe.load(torch.from_numpy(w13d["qw"]), torch.from_numpy(w2d["qw"]), None, None, dev)
+    got = f32_of(moe(synth.bf16_tensor(x, dev), torch.from_numpy(tw).to(dev), torch.from_numpy(ids).to(dev)))
+    torch.cuda.synchronize()
+    assert _native.device_status(0) == 0
+    assert "sorted rows" in moe._cb_route
+    rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+    assert rel <= 1e-2, rel                                         # acceptance bar of the path
+    assert np.abs(got - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
