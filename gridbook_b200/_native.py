@@ -130,7 +130,7 @@ def _declare(lib) -> None:
     lib.gb_gemm_tn.argtypes = [vp, vp, vp, i64, i64, i64, i32, vp, vp, ctypes.c_float, vp]
     lib.gb_gemm_tn_grouped.argtypes = [vp, vp, vp, i64, i64, i64, i32, i64, vp, vp, vp, vp, ctypes.c_float, vp]
     lib.gb_moe_gather_rows.argtypes = [vp, vp, vp, vp, i64, i64, i64, vp, vp]
-    lib.gb_moe_gemv_sorted.argtypes = [vp, wp, i64, i64, vp, vp, i64, vp, vp]
+    lib.gb_moe_gemv_sorted.argtypes = [vp, wp, i64, i64, vp, vp, i64, vp, vp, vp]
     lib.gb_moe_swiglu_rows.argtypes = [vp, vp, i64, i64, i64, i32, i32, vp, vp]
     lib.gb_launch_count.restype = i64
     lib.gb_peer_alloc.argtypes = [i64, ctypes.POINTER(vp)]

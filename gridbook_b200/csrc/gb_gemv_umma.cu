@@ -50,6 +50,8 @@ struct UmmaParams {
   const int32_t* seg;        // [E+1]
   const int32_t* row_map;    // [P] output row of a sorted row, or null = identity
   int tiles_n;               // 128-row tiles per expert
+  uint16_t* y_peer[GB_PEER_MAX];   // optional: output row r lives in y_peer[r / rows_per_rank]
+  int64_t rows_per_rank;     // 0 = all rows in y
 };
 
 constexpr int kGroupRows = 64;                            // activation rows per pass in grouped mode
@@ -304,8 +306,14 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           if (m < rows) {
             if (kGrouped) {
               const int jrow = seg_lo + pass * pass_rows + m;          // sorted position of the row
-              const int64_t orow = p.row_map ? p.row_map[jrow] : jrow;
-              p.y[orow * p.N + out_col] = (uint16_t)gb_f32_to_bf16_bits(__uint_as_float(v[i]) * p.global_scale);
+              int64_t orow = p.row_map ? p.row_map[jrow] : jrow;
+              uint16_t* ybase = p.y;
+              if (p.rows_per_rank > 0) {                     // the row's home rank keeps it (peer store)
+                const int64_t home = orow / p.rows_per_rank;
+                ybase = p.y_peer[home];
+                orow -= home * p.rows_per_rank;
+              }
+              ybase[orow * p.N + out_col] = (uint16_t)gb_f32_to_bf16_bits(__uint_as_float(v[i]) * p.global_scale);
             } else if (p.slices > 1) {
               p.partial[((int64_t)blockIdx.y * p.M + m) * p.N + out_col] = __uint_as_float(v[i]);
             } else {
@@ -437,8 +445,9 @@ int gb_gemv_umma(const void* x, int64_t M, const gb_weight* w, int act, int scal
 extern "C" {
 
 int gb_moe_gemv_sorted(const void* x_sorted, const gb_weight* w, int64_t expert_stride, int64_t E,
-                       const int32_t* seg_offsets, const int32_t* row_map, int64_t P, void* y, void* stream_) {
-  GB_REQUIRE(x_sorted && w && seg_offsets && y, "null pointer argument");
+                       const int32_t* seg_offsets, const int32_t* row_map, int64_t P, void* y,
+                       const gb_peer_rows* y_rows, void* stream_) {
+  GB_REQUIRE(x_sorted && w && seg_offsets && (y || y_rows), "null pointer argument");
   GB_REQUIRE(E >= 1 && P >= 0, "bad shape E=%lld P=%lld", (long long)E, (long long)P);
   int rc = gb_check_weight(w);
   if (rc != GB_OK) return rc;
@@ -470,6 +479,16 @@ int gb_moe_gemv_sorted(const void* x_sorted, const gb_weight* w, int64_t expert_
   p.status = gb_status_word();
   p.seg = seg_offsets; p.row_map = row_map;
   p.tiles_n = (int)(N / kBM);
+  if (y_rows) {
+    GB_REQUIRE(y_rows->rows_per_rank > 0, "per-rank output rows need rows_per_rank > 0");
+    const int64_t ranks = (P + y_rows->rows_per_rank - 1) / y_rows->rows_per_rank;
+    GB_REQUIRE(ranks <= GB_PEER_MAX, "output rows span %lld ranks", (long long)ranks);
+    for (int r = 0; r < (int)ranks; ++r) {
+      GB_REQUIRE(y_rows->base[r] != nullptr, "output buffer of rank %d is null", r);
+      p.y_peer[r] = (uint16_t*)y_rows->base[r];
+    }
+    p.rows_per_rank = y_rows->rows_per_rank;
+  }
   dim3 grid((unsigned)(E * p.tiles_n), 1);
   GB_CUDA_OK(gb_launch(umma_decode_kernel<true>, grid, dim3(kUmmaThreads), (size_t)umma_smem_bytes(kGroupRows),
                        (cudaStream_t)stream_, map_w, map_x, p));

@@ -443,22 +443,29 @@ def stack_rows(w: PackedWeight) -> PackedWeight:
                         w.compose, ws, w.global_scale)
 
 
+def moe_gemv_sorted_applies(w: PackedWeight) -> bool:
+    f = w.fmt
+    return (f.is_fp4 and f.mode == "full" and f.k == 8 and f.scale_coding == "v1" and w.cb_row_offset is None
+            and w.rows % 128 == 0 and w.row_stride % 16 == 0 and w.expert_stride == w.rows * w.row_stride)
+
+
 def moe_gemv_sorted(x_sorted: torch.Tensor, w: PackedWeight, offsets: torch.Tensor, *,
-                    row_map: torch.Tensor | None = None) -> torch.Tensor | None:
+                    row_map: torch.Tensor | None = None, peer_rows=None) -> torch.Tensor | None:
     """Grouped linear over rows already in expert order, for mid-size batches: every (expert, 128-row
     tile) decodes its packed rows into shared memory and multiplies on the tensor cores.  -> [P, rows]
     bf16 (row j at ``row_map[j]`` or j; rows past ``offsets[E]`` unset), or None when the stack is
-    not the literal fp4 format in a contiguous layout with rows a multiple of 128."""
+    not the literal fp4 format in a contiguous layout with rows a multiple of 128.  ``peer_rows``
+    (a ``GbPeerRows``): rows go to their home rank's buffer instead, nothing is returned."""
     _need_cuda(x_sorted, offsets, row_map)
     lib = nat.load("sorted-rows expert kernel")
-    f = w.fmt
-    if not (f.is_fp4 and f.mode == "full" and f.k == 8 and f.scale_coding == "v1" and w.cb_row_offset is None
-            and w.rows % 128 == 0 and w.row_stride % 16 == 0 and w.expert_stride == w.rows * w.row_stride):
+    if not moe_gemv_sorted_applies(w):
         return None
     x_sorted = x_sorted.contiguous()
     P = x_sorted.shape[0]
-    out = torch.empty((P, w.rows), dtype=torch.bfloat16, device=x_sorted.device)
+    out = None if peer_rows is not None else torch.empty((P, w.rows), dtype=torch.bfloat16, device=x_sorted.device)
     nw = w.native()
     nat.check(lib.gb_moe_gemv_sorted(_ptr(x_sorted), ctypes.byref(nw), w.expert_stride, w.experts, _ptr(offsets),
-                                     _ptr(row_map), P, _ptr(out), nat.stream_ptr(x_sorted.device)), lib)
-    return out
+                                     _ptr(row_map), P, _ptr(out),
+                                     ctypes.byref(peer_rows) if peer_rows is not None else None,
+                                     nat.stream_ptr(x_sorted.device)), lib)
+    return out if peer_rows is None else True

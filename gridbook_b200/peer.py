@@ -275,6 +275,9 @@ class PeerExpertParallelMoE(torch.nn.Module):
         self._pairs_ok = all(f.is_fp4 and f.mode == "full" and f.k == 8 and f.scale_coding == "v1"
                              for f in (moe_layer.method.fmt13, moe_layer.method.fmt2)) and \
             all(wt.row_stride % 16 == 0 for wt in (w13, w2))
+        # ... and the sorted-rows tensor-core kernel for many rows per local expert
+        self._sorted_ok = (kernels.moe_gemv_sorted_applies(w13) and kernels.moe_gemv_sorted_applies(w2)
+                           and moe_layer._cb_inter % 16 == 0)
 
     def forward(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         from . import ops
@@ -326,6 +329,18 @@ class PeerExpertParallelMoE(torch.nn.Module):
                 # every rank holds the same formats, so every rank takes this branch together
                 raise NativeKernelUnavailableError(
                     "per-pair table MLP refused a format the layer was built for")
+            done = True
+        from .moe import sorted_min_pairs_per_expert
+        if (not done and self._sorted_ok and method.fmt2.is_fp4
+                and pairs_all >= sorted_min_pairs_per_expert() * self.E):
+            # many rows per local expert: sort them, decode every (expert, 128-row tile) in shared
+            # memory and multiply on the tensor cores; the down projection stores each row into its
+            # home rank's buffer
+            _, offsets, order = kernels.moe_route(ids_all, self.e_local, expert_base=base)
+            a = kernels.moe_gather_rows(x_all, order, offsets, x_row=x_row)
+            h = kernels.moe_swiglu_rows(kernels.moe_gemv_sorted(a, layer._cb_w13, offsets), offsets, act="fp4",
+                                        scale_rule=rule)
+            kernels.moe_gemv_sorted(h, layer._cb_w2, offsets, row_map=order, peer_rows=rows)
             done = True
         if not done:
             _, offsets, order = kernels.moe_route(ids_all, self.e_local, expert_base=base)

@@ -183,18 +183,6 @@ GB_API int gb_moe_gather_rows(const void* x_bf16, const int32_t* x_row, const in
 GB_API int gb_moe_swiglu_rows(const void* h_bf16, const int32_t* seg_offsets, int64_t E, int64_t P, int64_t inter,
                               int act, int scale_rule, void* out_bf16, void* stream);
 
-/* Grouped linear over rows ALREADY in expert order (gb_moe_gather_rows), for batches between the
- * decode kernels and the grouped GEMM: x_sorted [P,K] bf16 (bucketed), expert e owns rows
- * [seg_offsets[e], seg_offsets[e+1]); y[r, :] = x_sorted[j] . W_e^T with r = row_map[j] (or j).
- * Every (expert, 128-row tile) CTA decodes its packed rows into shared memory and multiplies on
- * the tensor cores (tcgen05, weights on the M side), 64 routed rows per pass; experts without rows
- * cost nothing.  Literal fp4 format, contiguous stack (expert_stride = rows * row_stride), rows a
- * multiple of 128; GB_EUNSUPPORTED otherwise.  Replaces the grouped decode-in-mainloop kernels of
- * the reference for mid-size batches (gridbook/csrc/cb_moe_persistent_b.cu:1645-1960). */
-GB_API int gb_moe_gemv_sorted(const void* x_sorted_bf16, const gb_weight* w, int64_t expert_stride, int64_t E,
-                              const int32_t* seg_offsets, const int32_t* row_map, int64_t P, void* y_bf16,
-                              void* stream);
-
 /* ---- routed MoE -------------------------------------------------------------- */
 /* Device-side histogram + exclusive scan + stable expert-major permutation of the
  * P = T*topk routed pairs; replaces the torch chain of gridbook/moe.py:1609-1625 and
@@ -243,6 +231,19 @@ GB_API int gb_moe_gemv(const void* x_bf16, const int32_t* x_row, const gb_weight
                 const int32_t* order, int64_t P, int swiglu, int act, int scale_rule,
                 void* y_bf16, const gb_peer_rows* y_rows, void* workspace,
                 int64_t workspace_bytes, void* stream);
+
+/* Grouped linear over rows ALREADY in expert order (gb_moe_gather_rows), for batches between the
+ * decode kernels and the grouped GEMM: x_sorted [P,K] bf16 (bucketed), expert e owns rows
+ * [seg_offsets[e], seg_offsets[e+1]); y[r, :] = x_sorted[j] . W_e^T with r = row_map[j] (or j).
+ * Every (expert, 128-row tile) CTA decodes its packed rows into shared memory and multiplies on
+ * the tensor cores (tcgen05, weights on the M side), 64 routed rows per pass; experts without rows
+ * cost nothing.  Literal fp4 format, contiguous stack (expert_stride = rows * row_stride), rows a
+ * multiple of 128; GB_EUNSUPPORTED otherwise.  y_rows (optional): row r goes to its home rank's
+ * buffer base[r / rows_per_rank] + (r % rows_per_rank) * rows instead of y_bf16, as in gb_moe_gemv.  Replaces the grouped decode-in-mainloop kernels of
+ * the reference for mid-size batches (gridbook/csrc/cb_moe_persistent_b.cu:1645-1960). */
+GB_API int gb_moe_gemv_sorted(const void* x_sorted_bf16, const gb_weight* w, int64_t expert_stride, int64_t E,
+                              const int32_t* seg_offsets, const int32_t* row_map, int64_t P, void* y_bf16,
+                              const gb_peer_rows* y_rows, void* stream);
 
 /* The same routed projection for SMALL batches of the literal format (fp4 grid, full mode,
  * k = 8, E4M3-direct scales, one codebook per stack): every routed pair p is its own M = 1 linear

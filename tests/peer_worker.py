@@ -71,7 +71,7 @@ def check(peers, rank, world, dev):
             w13[rank * e_local:(rank + 1) * e_local].contiguous(),
             w2[rank * e_local:(rank + 1) * e_local].contiguous(), None, None, dev)
         ep = PeerExpertParallelMoE(E, mine, peers, max_tokens=64, topk=topk, hidden=hidden)
-        for T in (1, 5, 40, 5):
+        for T in (1, 5, 40, 64, 5):
             ids, tw = synth.make_routing(T, E, topk, seed=100 * T + rank)        # every rank its own batch
             if T == 5:
                 ids[2, 1] = -1                                                    # a padded route
@@ -81,7 +81,14 @@ def check(peers, rank, world, dev):
             want = whole(x, tw_d, ids_d)
             got = ep(x, tw_d, ids_d)
             torch.cuda.synchronize()
-            assert torch.equal(got, want), (str(mfmt), T, float((got.float() - want.float()).abs().max()))
+            if T <= 5:
+                assert torch.equal(got, want), (str(mfmt), T, float((got.float() - want.float()).abs().max()))
+            else:
+                # from 18 routed pairs per expert on, the literal format takes the sorted-rows tensor-core
+                # kernel, and the two sides cross that line at different batch sizes (the ranks route
+                # 2 T tokens together): same operands, another summation order
+                rel = float((got.float() - want.float()).norm() / want.float().norm())
+                assert rel <= 1e-2, (str(mfmt), T, rel)
 
 
 if __name__ == "__main__":
