@@ -167,9 +167,20 @@ def run_gpu(args):
     bytes_per_step_local = sum(lin._cb_weight.packed_bytes for row in stack for lin in row)
     outs_host = [torch.empty(M, n * world, dtype=torch.bfloat16).pin_memory() for n in n_local]
 
+    # q and kv read the same activation row (the block's normed hidden state): at M = 1 on one GPU
+    # they go out as ONE launch of the table kernel (linear.apply_shared_row); --no-share-row keeps them apart
+    share_row = world == 1 and M == 1 and not args.no_share_row and len(PROJECTIONS) == 5
+    if share_row:
+        inputs_dev[1] = inputs_dev[0]
+
     def step():
+        from gridbook_b200.linear import apply_shared_row
         ys = None
         for row in stack:
+            if share_row:
+                ys = apply_shared_row(row[:2], inputs_dev[0])
+                ys += [lin(x) for lin, x in zip(row[2:], inputs_dev[2:])]
+                continue
             ys = []
             for lin, x in zip(row, inputs_dev):
                 ys.append(lin(x))          # N > 1: local shard + NCCL all-gather inside
@@ -243,10 +254,15 @@ def run_gpu(args):
     xq = [(kernels.fp4_act_qdq if fmt.is_fp4 else kernels.fp8_act_qdq)(x) for x in inputs_dev]
     outs = [[torch.empty(M, n, dtype=torch.bfloat16, device=device) for n in n_local] for _ in range(1)]
 
+    tab = world == 1 and M == 1 and all(getattr(lin, "_cb_slots", None) is not None for lin in stack[0])
+
     def kernel_step():
         for row in stack:
             for lin, x, o in zip(row, xq, outs[0]):
-                kernels.gemv(x, lin._cb_weight, out=o, workspace=lin._cb_workspace)
+                if tab:      # the one-launch table kernel, activations already bucketed
+                    kernels.gemv_tab(x, [lin._cb_weight], lin._cb_slots, act=None, outs=[o])
+                else:
+                    kernels.gemv(x, lin._cb_weight, out=o, workspace=lin._cb_workspace)
 
     n0 = _native.launch_count()
     kernel_step()
@@ -342,11 +358,11 @@ def run_gpu(args):
     achieved = launch_bytes / (launch_ms * 1e-3) / 1e9
     # M = 1 on the literal format runs the inner-product-table kernel (plus its slot-summing
     # kernel, timed with it); everything else the expanding MMA kernel
-    dominant_kernel = ("gemv_dot_kernel" if (M == 1 and args.format == "literal")
+    dominant_kernel = ("gemv_tab_kernel" if tab else "gemv_dot_kernel" if (M == 1 and args.format == "literal")
                        else "umma_decode_kernel" if (M > 16 and args.format == "literal") else "gemv_kernel")
     # DRAM bytes per launch over algorithmic bytes, from the committed ncu captures of these
     # kernels (profiles/): the weight stream is read once and nothing else reaches DRAM
-    traffic_ratio = {"gemv_dot_kernel": 1.002, "gemv_kernel": 1.01, "umma_decode_kernel": 1.02}[dominant_kernel]
+    traffic_ratio = {"gemv_tab_kernel": 1.002, "gemv_dot_kernel": 1.002, "gemv_kernel": 1.01, "umma_decode_kernel": 1.02}[dominant_kernel]
     line = {
         "metric": "CB GEMV weight GB/s (% HBM peak); grouped-MoE decode tok/s at 1/2/4/8 B200",
         "value": round(gbs, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -632,6 +648,8 @@ def main():
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: exchange by this package's peer-memory kernels, or through NCCL")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-share-row", action="store_true",
+                    help="M = 1: launch q and kv separately although they read the same row")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-moe", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")

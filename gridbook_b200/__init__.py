@@ -1,6 +1,6 @@
 """gridbook_b200 — sm_100a kernels for the gridbook codebook-decode linear and
 routed-MoE hot path, behind the reference's vLLM plugin surface."""
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 
 
 def register() -> None:

@@ -13,7 +13,7 @@ import threading
 
 import torch
 
-GB_ABI_VERSION = 1
+GB_ABI_VERSION = 2
 GEMM_BF16, GEMM_E4M3 = 0, 1
 
 REQUIRED_SYMBOLS = (
@@ -21,6 +21,7 @@ REQUIRED_SYMBOLS = (
     "gb_fp8_act_qdq", "gb_fp4_act_qdq",
     "gb_expand_fp8", "gb_expand_fp4_bf16", "gb_expand_fp4_nvfp4",
     "gb_gemv_workspace_bytes", "gb_gemv", "gb_gemv_static",
+    "gb_gemv_tab_slots_bytes", "gb_gemv_tab_arm", "gb_gemv_tab", "gb_device_status_reset", "gb_set_wait_limit_ms",
     "gb_moe_route", "gb_moe_route_ws", "gb_moe_route_workspace_bytes", "gb_moe_gemv_workspace_bytes", "gb_moe_gemv", "gb_moe_combine",
     "gb_moe_gemv_pairs_workspace_bytes", "gb_moe_gemv_pairs",
     "gb_moe_mlp_pairs_workspace_bytes", "gb_moe_mlp_pairs",
@@ -112,6 +113,13 @@ def _declare(lib) -> None:
     lib.gb_gemv_workspace_bytes.restype = i64
     lib.gb_gemv.argtypes = [vp, i64, wp, i32, i32, vp, vp, i64, vp]
     lib.gb_gemv_static.argtypes = [vp, i64, wp, i32, i32, vp, vp]
+    wpp = ctypes.POINTER(wp)
+    lib.gb_gemv_tab_slots_bytes.argtypes = [wpp, i32]
+    lib.gb_gemv_tab_slots_bytes.restype = i64
+    lib.gb_gemv_tab_arm.argtypes = [vp, i64, vp]
+    lib.gb_gemv_tab.argtypes = [vp, wpp, ctypes.POINTER(vp), i32, i32, i32, vp, i64, vp]
+    lib.gb_device_status_reset.argtypes = [i32]
+    lib.gb_set_wait_limit_ms.argtypes = [i32]
     lib.gb_moe_route.argtypes = [vp, i64, i64, i64, i64, vp, vp, vp, vp, vp, vp]
     lib.gb_moe_route_ws.argtypes = [vp, i64, i64, i64, i64, vp, vp, vp, vp, vp, vp, i64, vp]
     lib.gb_moe_route_workspace_bytes.argtypes = [i64, i64, i64]
@@ -215,6 +223,18 @@ def device_status(device: int = 0) -> int:
     out = ctypes.c_int(0)
     check(lib.gb_device_status(int(device), ctypes.byref(out)), lib)
     return out.value
+
+
+def device_status_reset(device: int = 0) -> None:
+    lib = load()
+    check(lib.gb_device_status_reset(int(device)), lib)
+
+
+def set_wait_limit_ms(ms: int) -> None:
+    """Test hook: how long the exchange kernels and the one-launch table GEMV spin before a wait
+    gives up (0 restores the default of two seconds)."""
+    lib = load()
+    check(lib.gb_set_wait_limit_ms(int(ms)), lib)
 
 
 def stream_ptr(device=None) -> int:

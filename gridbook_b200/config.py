@@ -76,10 +76,20 @@ class PrismaQuantConfig(QuantizationConfig):
             path = os.path.join(self.model_dir, full.get("config_file", "quant_config.json"))
             with open(path) as fh:
                 full = json.load(fh)
+        self.delegated_targets: dict[str, str] = {}
         for gname, group in full.get("config_groups", {}).items():
-            scheme = dict(group["scheme"])
-            if "scale_coding" not in scheme and full.get("layout_version") == 2 and scheme.get("grid") == "fp4":
-                scheme["scale_coding"] = {"kind": "two_tier"}
+            raw_scheme = group.get("scheme")
+            if not isinstance(raw_scheme, dict) or "grid" not in raw_scheme:
+                # stock / passthrough groups carry no codebook scheme (the reference hands them to
+                # other backends, gridbook/config.py:803-957): remembered so that a lookup can say
+                # so instead of raising a bare KeyError or running them unquantized by accident
+                for target in group.get("targets", []):
+                    self.delegated_targets[target] = gname
+                continue
+            # v1 / v2 is decided by the group's OWN scale_coding: absent means v1 (E4M3-direct),
+            # whatever the artifact's layout_version says (docs/SPEC.md:130-177; the reference's
+            # linear method sets is_v2 = False when the key is missing, gridbook/linear.py:206-231)
+            scheme = dict(raw_scheme)
             scheme.setdefault("_group", gname)
             for target in group.get("targets", []):
                 self.target_scheme[target] = scheme
@@ -136,12 +146,28 @@ class PrismaQuantConfig(QuantizationConfig):
             return [prefix]
         return []
 
+    # wrapper prefixes a serving class may put in front of (or strip from) the checkpoint's names
+    _WRAPPERS = ("model", "language_model", "language_model.model", "model.language_model", "text_model")
+
     def _lookup(self, key: str) -> dict | None:
         if key in self.target_scheme:
             return self.target_scheme[key]
-        for stored, scheme in self.target_scheme.items():       # class wrappers: language_model.model.* etc.
-            if key.endswith("." + stored) or stored.endswith("." + key):
-                return scheme
+        # Only a known wrapper prefix may separate the two names: a second tower whose modules
+        # end in the same tail (vision_tower.layers.0.mlp...) must not pick up this scheme.
+        for stored, scheme in self.target_scheme.items():
+            for wrap in self._WRAPPERS:
+                if key == f"{wrap}.{stored}" or stored == f"{wrap}.{key}":
+                    return scheme
+        return None
+
+    def _delegated_group(self, key: str) -> str | None:
+        table = getattr(self, "delegated_targets", {})
+        if key in table:
+            return table[key]
+        for stored, gname in table.items():
+            for wrap in self._WRAPPERS:
+                if key == f"{wrap}.{stored}" or stored == f"{wrap}.{key}":
+                    return gname
         return None
 
     def _scheme_for_prefix(self, prefix: str) -> dict | None:
@@ -150,11 +176,15 @@ class PrismaQuantConfig(QuantizationConfig):
             return None
         schemes = [self._lookup(k) for k in keys]
         first = schemes[0]
-        fields = ("grid", "mode", "k", "n_sub", "type_size")
+        # the physical packed representation and the activation ABI one resident parameter set
+        # shares; codebook refs may differ by role (gridbook/config.py:612-618)
+        fields = ("grid", "mode", "k", "n_sub", "type_size", "group_size", "vec_dim", "scale_coding",
+                  "activation_contract")
         for other in schemes[1:]:
-            if any(other.get(f) != first.get(f) for f in fields):
-                raise ValueError(f"[prismaquant] {prefix}: fused roles use different formats; one method "
-                                 "cannot serve them")
+            diff = [f for f in fields if other.get(f) != first.get(f)]
+            if diff:
+                raise ValueError(f"[prismaquant] {prefix}: fused roles differ in {diff}; one method cannot "
+                                 "serve them")
         return first
 
     def codebooks_for_prefix(self, prefix: str, scheme: dict) -> list[list[torch.Tensor]]:
@@ -198,6 +228,12 @@ class PrismaQuantConfig(QuantizationConfig):
                                           scheme_down=pair[1])
         scheme = self._scheme_for_prefix(prefix)
         if scheme is None:
+            for key in self.shard_target_keys(prefix, unfused_fallback=True):
+                gname = self._delegated_group(key)
+                if gname is not None:
+                    raise NativeKernelUnavailableError(
+                        f"[prismaquant] {prefix}: group {gname!r} carries no codebook scheme (a stock or "
+                        "passthrough group); delegated groups are not served by gridbook_b200")
             return _unquantized(layer)
         from .linear import PrismaQuantCBLinearMethod
         return PrismaQuantCBLinearMethod(self, scheme, prefix)

@@ -57,6 +57,9 @@ static std::atomic<long long> g_launches{0};
 void gb_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 extern "C" int64_t gb_launch_count() { return (int64_t)g_launches.load(std::memory_order_relaxed); }
 
+static std::atomic<unsigned long long> g_wait_ns{2000000000ull};
+unsigned long long gb_wait_limit_ns() { return g_wait_ns.load(std::memory_order_relaxed); }
+
 bool gb_pdl_enabled() {
   static const bool on = [] {
     const char* v = getenv("GRIDBOOK_B200_PDL");
@@ -145,6 +148,7 @@ int gb_prepare(int device) {
   if (rc == GB_OK) rc = gb_prepare_gemm();
   if (rc == GB_OK) rc = gb_prepare_dot();
   if (rc == GB_OK) rc = gb_prepare_umma();
+  if (rc == GB_OK) rc = gb_prepare_tab();
   cudaSetDevice(prev);
   return rc;
 }
@@ -154,6 +158,19 @@ int gb_device_status(int device, int* status_out) {
   GB_REQUIRE(device >= 0 && device < kMaxDevices && g_status[device] != nullptr,
              "device %d was not prepared", device);
   GB_CUDA_OK(cudaMemcpy(status_out, g_status[device], sizeof(int), cudaMemcpyDeviceToHost));
+  return GB_OK;
+}
+
+int gb_device_status_reset(int device) {
+  GB_REQUIRE(device >= 0 && device < kMaxDevices && g_status[device] != nullptr, "device %d was not prepared", device);
+  const int zero = 0;
+  GB_CUDA_OK(cudaMemcpy(g_status[device], &zero, sizeof(int), cudaMemcpyHostToDevice));
+  return GB_OK;
+}
+
+int gb_set_wait_limit_ms(int ms) {
+  GB_REQUIRE(ms >= 0 && ms <= 60000, "wait limit of %d ms is out of range (0 restores the default)", ms);
+  g_wait_ns.store(ms == 0 ? 2000000000ull : (unsigned long long)ms * 1000000ull, std::memory_order_relaxed);
   return GB_OK;
 }
 

@@ -65,6 +65,10 @@ int gb_prepare_kernels();          // per-device function attributes of the big 
 int gb_prepare_gemm();
 int gb_prepare_dot();
 int gb_prepare_umma();
+int gb_prepare_tab();
+// Longest a device-side wait may spin before it gives up and raises the status word
+// (two seconds unless gb_set_wait_limit_ms changed it).
+unsigned long long gb_wait_limit_ns();
 // Swizzled (128-byte) operand map over a row-major [rows, K] matrix of 2- or 1-byte elements:
 // box = 128 bytes of K x box_rows rows, rows past the end read zero.
 int gb_tensor_map_operand(void* map_out, const void* base, int64_t rows, int64_t K, int elem_bytes, int box_rows);

@@ -13,6 +13,7 @@
 // rows or a warp's rows would not fit) add into an fp32 workspace instead.
 #include "gb_common.cuh"
 
+#include <atomic>
 #include <mutex>
 
 namespace {
@@ -1079,7 +1080,7 @@ __device__ __align__(256) static unsigned char g_gemv_static_scratch[GB_GEMV_STA
 
 namespace {
 std::mutex g_static_mutex;
-void* g_static_ptr[64] = {nullptr};   // device address of the array, per device ordinal
+std::atomic<void*> g_static_ptr[64];  // device address of the array, per device ordinal (null until looked up)
 }  // namespace
 
 extern "C" int gb_gemv_static(const void* x, int64_t M, const gb_weight* w, int act, int scale_rule,
@@ -1095,17 +1096,17 @@ extern "C" int gb_gemv_static(const void* x, int64_t M, const gb_weight* w, int 
   int dev = -1;
   GB_CUDA_OK(cudaGetDevice(&dev));
   GB_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
-  void* scratch = g_static_ptr[dev];
+  void* scratch = g_static_ptr[dev].load(std::memory_order_acquire);
   if (scratch == nullptr) {
     // Once per device, with that device current.  In host code the array's name is only a
     // handle: the address a kernel may use has to be asked for.
     std::lock_guard<std::mutex> lock(g_static_mutex);
-    if (g_static_ptr[dev] == nullptr) {
+    if (g_static_ptr[dev].load(std::memory_order_relaxed) == nullptr) {
       void* p = nullptr;
       GB_CUDA_OK(cudaGetSymbolAddress(&p, g_gemv_static_scratch));
-      g_static_ptr[dev] = p;
+      g_static_ptr[dev].store(p, std::memory_order_release);
     }
-    scratch = g_static_ptr[dev];
+    scratch = g_static_ptr[dev].load(std::memory_order_relaxed);
   }
   // gb_gemv overwrites the activation part and clears the partial sums it uses (an async
   // memset on the caller's stream, not an allocation) before the kernel adds into them.

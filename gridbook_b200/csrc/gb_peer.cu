@@ -13,7 +13,7 @@
 //   [19]     CTA arrival counter of the running flag-in-data exchange (own use)
 // Epochs only grow, and a waiter accepts any value at or past the one it waits for, so a
 // fast peer that is already one exchange ahead never strands a slow one.  Every wait is
-// bounded (two seconds); one that runs out raises the status word (value 3) and carries on.
+// bounded (two seconds unless gb_set_wait_limit_ms says otherwise); one that runs out raises the status word (value 3) and carries on.
 #include "gb_common.cuh"
 
 namespace {
@@ -31,6 +31,7 @@ struct PeerParams {
   int rank, world, n_seg;
   PeerSeg seg[kMaxSeg];
   int* status;
+  unsigned long long wait_ns;       // how long a wait may spin
 };
 
 GB_DEVINL void st_release_sys(uint32_t* p, uint32_t v) {
@@ -42,15 +43,15 @@ GB_DEVINL uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-// Spin until *slot has reached `epoch`; false after two seconds.
-GB_DEVINL bool wait_epoch(const uint32_t* slot, uint32_t epoch) {
+// Spin until *slot has reached `epoch`; false once `limit_ns` have passed.
+GB_DEVINL bool wait_epoch(const uint32_t* slot, uint32_t epoch, unsigned long long limit_ns) {
   uint64_t t0 = 0;
   for (uint32_t spin = 0;; ++spin) {
     if ((int32_t)(ld_acquire_sys(slot) - epoch) >= 0) return true;
     if ((spin & 63u) == 63u) {
       const uint64_t now = gb_globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > 2000000000ull) return false;
+      else if (now - t0 > limit_ns) return false;
     }
   }
 }
@@ -73,7 +74,7 @@ __global__ void __launch_bounds__(256) peer_exchange_kernel(const __grid_constan
   if (p.n_seg > 0) {                   // a plain barrier has no buffer to wait for
     if (tid < p.world) {
       if (blockIdx.x == 0) st_release_sys(p.flags[tid] + p.rank, epoch);
-      if (!wait_epoch(mine + tid, epoch)) atomicExch(p.status, 3);
+      if (!wait_epoch(mine + tid, epoch, p.wait_ns)) atomicExch(p.status, 3);
     }
     __syncthreads();
   }
@@ -117,7 +118,7 @@ __global__ void __launch_bounds__(256) peer_exchange_kernel(const __grid_constan
   if (tid < p.world) {
     __threadfence_system();
     st_release_sys(p.flags[tid] + 8 + p.rank, epoch);
-    if (!wait_epoch(mine + 8 + tid, epoch)) atomicExch(p.status, 3);
+    if (!wait_epoch(mine + 8 + tid, epoch, p.wait_ns)) atomicExch(p.status, 3);
   }
   __syncthreads();
   if (tid == 0) {
@@ -145,6 +146,7 @@ struct LLParams {
   int rank, world, n_seg;
   LLSeg seg[kMaxSeg];
   int* status;
+  unsigned long long wait_ns;
 };
 
 GB_DEVINL void st_ll(uint2* p, uint32_t word, uint32_t epoch) {
@@ -199,7 +201,7 @@ __global__ void __launch_bounds__(256) peer_ll_kernel(const __grid_constant__ LL
         if ((spin & 63u) == 63u) {
           const uint64_t now = gb_globaltimer_ns();
           if (t0 == 0) t0 = now;
-          else if (now - t0 > 2000000000ull) late = true;
+          else if (now - t0 > p.wait_ns) late = true;
         }
       }
       *reinterpret_cast<uint32_t*>(g.dst_local[src] + r * g.dst_pitch + c * 4) = v[src].x;
@@ -281,6 +283,7 @@ int gb_peer_allgather(const gb_peer_group* g, const gb_peer_piece* pieces, int n
   p.world = g->world;
   p.n_seg = n_pieces;
   p.status = gb_status_word();
+  p.wait_ns = gb_wait_limit_ns();
   for (int r = 0; r < g->world; ++r) p.flags[r] = (uint32_t*)g->flags[r];
   int64_t bytes = 0;
   for (int s = 0; s < n_pieces; ++s) {
@@ -318,6 +321,7 @@ int gb_peer_allgather_ll(const gb_peer_group* g, void* const* ll, int64_t ll_byt
   p.n_seg = n_pieces;
   p.flags = (uint32_t*)g->flags[g->rank];
   p.status = gb_status_word();
+  p.wait_ns = gb_wait_limit_ns();
   p.capacity = ll_bytes / (2 * (int64_t)g->world * 8);
   for (int r = 0; r < g->world; ++r) {
     GB_REQUIRE(ll[r] != nullptr && ((uintptr_t)ll[r] & 7) == 0, "staging buffer of rank %d is null or misaligned", r);

@@ -200,6 +200,60 @@ def gemv(x: torch.Tensor, w: PackedWeight, *, act: str | None = None, scale_rule
     return out.reshape(*x.shape[:-1], w.rows)
 
 
+def table_kernel_applies(w: PackedWeight) -> bool:
+    """Whether ONE activation row of this weight is served by the one-launch table kernel
+    (:func:`gemv_tab`): the conditions the library checks."""
+    f = w.fmt
+    return (f.is_fp4 and f.mode == "full" and f.k == 8 and f.scale_coding == "v1" and w.experts == 1
+            and w.cb_row_offset is None and w.rows >= 64 and w.row_stride % 16 == 0
+            and w.qw.data_ptr() % 16 == 0 and w.K // 1024 + (1 if w.K % 1024 else 0) <= 148)
+
+
+def _weight_array(ws):
+    natives = [w.native() for w in ws]
+    arr = (ctypes.POINTER(nat.GbWeight) * len(ws))(*[ctypes.pointer(n) for n in natives])
+    return natives, arr
+
+
+def new_tab_slots(ws, device=None) -> torch.Tensor:
+    """An armed slot buffer (every byte 0xFF) large enough for :func:`gemv_tab` over the weights
+    ``ws`` together.  Allocate once per module, or once per stream for modules that run one after
+    the other: every call leaves the buffer armed again."""
+    lib = nat.load("one-launch table GEMV")
+    ws = list(ws)
+    _natives, arr = _weight_array(ws)
+    need = lib.gb_gemv_tab_slots_bytes(arr, len(ws))
+    if need <= 0:
+        raise RuntimeError("gemv_tab takes one to four weight matrices")
+    return torch.full((need,), 0xFF, dtype=torch.uint8, device=device or ws[0].qw.device)
+
+
+def gemv_tab(x: torch.Tensor, ws, slots: torch.Tensor, *, act: str | None = "fp4", scale_rule: str = "recip",
+             outs=None):
+    """One activation row against up to four weights that read it, in ONE launch (literal format):
+    -> list of [1, N_i] bf16 outputs, or None when a weight has no such kernel (use :func:`gemv`).
+    ``slots`` is an armed buffer from :func:`new_tab_slots`."""
+    _need_cuda(x, slots)
+    lib = nat.load("one-launch table GEMV")
+    if x.dtype is not torch.bfloat16:
+        raise TypeError("the table GEMV takes bf16 activations")
+    ws = list(ws)
+    x2 = x.reshape(-1, ws[0].K).contiguous()
+    if x2.shape[0] != 1:
+        raise RuntimeError(f"gemv_tab takes exactly one activation row, got {x2.shape[0]}")
+    if outs is None:
+        outs = [torch.empty((1, w.rows), dtype=torch.bfloat16, device=x.device) for w in ws]
+    natives, arr = _weight_array(ws)
+    yarr = (ctypes.c_void_p * len(ws))(*[o.data_ptr() for o in outs])
+    rc = lib.gb_gemv_tab(_ptr(x2), arr, yarr, len(ws), nat.ACT_FP4_GROUP16 if act == "fp4" else nat.ACT_NONE,
+                         _rule(scale_rule), _ptr(slots), slots.numel(), nat.stream_ptr(x.device))
+    del natives
+    if rc == nat.EUNSUPPORTED:
+        return None
+    nat.check(rc, lib)
+    return outs
+
+
 def moe_route(topk_ids: torch.Tensor, E: int, topk_weights: torch.Tensor | None = None, *,
               expert_base: int = 0):
     """-> (counts [E], offsets [E+1], order [P]) int32, all on device, no host read.  With

@@ -109,6 +109,9 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         from .ops import register_cb_layer
         layer._cb_layer_id = register_cb_layer(self, layer)
         layer._cb_route = {"kernel": "gemv_kernel", "format": str(self.fmt), "N": N, "K": K}
+        # one activation row of the literal format: the one-launch table kernel and its armed slots
+        layer._cb_slots = (kernels.new_tab_slots([layer._cb_weight])
+                           if kernels.table_kernel_applies(layer._cb_weight) else None)
 
     # ------------------------------------------------------------------ forward
     def apply(self, layer, x, bias=None):
@@ -129,6 +132,10 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         M = x2.shape[0]
         if M == 0:
             return x.new_empty((*x.shape[:-1], N))
+        if M == 1 and getattr(layer, "_cb_slots", None) is not None:
+            outs = kernels.gemv_tab(x2, [w], layer._cb_slots, act=self.fmt.grid, scale_rule=ops.ACT_SCALE_RULE)
+            if outs is not None:
+                return outs[0].reshape(*x.shape[:-1], N)
         if M <= DECODE_MAX_M or (M <= midm_max_rows() and kernels.row_batch_kernel_applies(w)):
             # past sixteen rows: the literal format's tensor-core decode kernel, no decoded transient
             return kernels.gemv(x2, w, act=self.fmt.grid, scale_rule=ops.ACT_SCALE_RULE,
@@ -156,6 +163,28 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         wt = kernels.expand_fp8(w)
         layer._cb_route["prefill"] = "expand_fp8 + gemm_tn(kind::f8f6f4)"
         return kernels.gemm_tn(q, wt, a_scale=a_scale, b_scale=w.weight_scale, global_scale=w.global_scale)
+
+
+def apply_shared_row(layers, x: torch.Tensor):
+    """Several CB Linears that read the SAME activation row (q and kv of an attention block, gate
+    and up kept as separate modules): one launch builds the inner-product tables once per CTA and
+    streams all of them.  Falls back to one call per layer when the batch is not a single row or a
+    layer's format has no table kernel.  -> list of outputs, in the order of ``layers``."""
+    from . import ops
+    layers = list(layers)
+    ws = [l._cb_weight for l in layers]
+    x2 = x.reshape(-1, ws[0].K)
+    if (x2.shape[0] == 1 and 1 < len(layers) <= 4 and all(getattr(l, "_cb_slots", None) is not None for l in layers)
+            and all(w.K == ws[0].K for w in ws)):
+        key = tuple(l._cb_layer_id for l in layers)
+        cache = layers[0].__dict__.setdefault("_cb_shared_slots", {})
+        slots = cache.get(key)
+        if slots is None:
+            slots = cache[key] = kernels.new_tab_slots(ws)
+        outs = kernels.gemv_tab(x2, ws, slots, act=ws[0].fmt.grid, scale_rule=ops.ACT_SCALE_RULE)
+        if outs is not None:
+            return [o.reshape(*x.shape[:-1], w.rows) for o, w in zip(outs, ws)]
+    return [l(x) for l in layers]
 
 
 def _scheme_of(fmt: CBFormat, global_scale: float = 1.0) -> dict:

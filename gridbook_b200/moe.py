@@ -140,7 +140,21 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         return kernels.make_weight(packed, cb_dev, fmt, k_in, compose=compose, weight_scale=ws,
                                    global_scale=float(scheme.get("weight_global_scale", 1.0)))
 
+    def _require_served_contract(self, layer) -> None:
+        """Fail closed at load on anything but SiLU-gated experts with router weights applied to the
+        output (the reference resolves the activation and refuses weights-on-input the same way,
+        gridbook/moe.py:920-921,972-974): the kernels fuse silu(gate) * up and nothing else."""
+        act = getattr(layer, "activation", None)
+        act = getattr(act, "value", act)
+        if act is not None and str(act).lower() not in ("silu", "swiglu", "moeactivation.silu"):
+            raise NativeKernelUnavailableError(
+                f"{self.prefix} routed activation: activation {act!r} has no native Gridbook operator")
+        if getattr(layer, "apply_router_weight_on_input", False):
+            raise NativeKernelUnavailableError(
+                f"{self.prefix}: apply_router_weight_on_input unsupported for CB MoE")
+
     def process_weights_after_loading(self, layer) -> None:
+        self._require_served_contract(layer)
         _native.load(f"{self.prefix}: CB routed experts")
         if not layer.w13_cb_qweight.is_cuda:
             raise NativeKernelUnavailableError(
@@ -159,13 +173,27 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
               file=sys.stderr, flush=True)
 
     # ------------------------------------------------------------------ forward
+    # keyword arguments an engine may pass that do not change what is computed
+    _INERT_KWARGS = ("shared_experts", "shared_experts_input", "global_num_experts", "enable_eplb",
+                     "expert_load_view", "logical_to_physical_map", "logical_replica_count")
+
     def apply(self, layer, x, topk_weights, topk_ids, shared_experts=None, shared_experts_input=None,
-              apply_router_weight_on_input: bool = False, **_ignored):
+              apply_router_weight_on_input: bool = False, **kwargs):
         """Routed-only output; the shared expert is the engine's business
         (gridbook/moe.py:957-989)."""
-        if apply_router_weight_on_input:
+        if apply_router_weight_on_input or getattr(layer, "apply_router_weight_on_input", False):
             raise NativeKernelUnavailableError(
-                f"{self.prefix}: apply_router_weight_on_input has no native Gridbook operator")
+                f"{self.prefix}: apply_router_weight_on_input unsupported for CB MoE")
+        for key, val in kwargs.items():
+            if key in self._INERT_KWARGS or val is None or val is False:
+                continue
+            if key == "activation" and str(getattr(val, "value", val)).lower() in ("silu", "swiglu"):
+                continue
+            # an expert_map, a different activation, a custom routing function ...: anything that
+            # would change the result and that this method does not implement
+            raise NativeKernelUnavailableError(
+                f"{self.prefix}: argument {key}={val!r} changes the routed computation and has no native "
+                "Gridbook operator")
         lid = getattr(layer, "_cb_layer_id", None)
         if lid is None:
             raise NativeKernelUnavailableError(

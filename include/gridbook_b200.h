@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define GB_ABI_VERSION 1
+#define GB_ABI_VERSION 2
 #define GB_API __attribute__((visibility("default")))
 
 enum { GB_OK = 0, GB_EINVAL = 1, GB_ECUDA = 2, GB_EUNSUPPORTED = 3, GB_EWORKSPACE = 4 };
@@ -76,6 +76,13 @@ GB_API int gb_prepare(int device);
 
 /* Device error word written by kernels whose bounded waits ran out; 0 when healthy. */
 GB_API int gb_device_status(int device, int* status_out);
+
+/* Clears the device error word (after the cause has been dealt with). */
+GB_API int gb_device_status_reset(int device);
+/* How long a device-side wait of the exchange kernels and of gb_gemv_tab may spin before it gives
+ * up and raises the status word: `ms` milliseconds, 0 = the default of two seconds.  Host-side
+ * setting read at launch; meant for tests that make a wait run out on purpose. */
+GB_API int gb_set_wait_limit_ms(int ms);
 
 /* ---- activation buckets ---------------------------------------------------- */
 /* replaces fp8_act_qdq (gridbook/csrc/cb_gemv.cu:135-172, gridbook/ops.py:441-447) */
@@ -140,6 +147,23 @@ GB_API int gb_gemv(const void* x_bf16, int64_t M, const gb_weight* w, int act, i
 #define GB_GEMV_STATIC_SCRATCH_BYTES (4u << 20)
 GB_API int gb_gemv_static(const void* x_bf16, int64_t M, const gb_weight* w, int act, int scale_rule,
                           void* y_bf16, void* stream);
+
+/* One activation row of the literal format (fp4 grid, full mode, k = 8, v1 scales, one codebook
+ * per matrix, 16-byte aligned rows, >= 64 rows) against n_weights <= 4 matrices that read the SAME
+ * row - q and kv, gate and up - in one launch: y[i][N_i] = bucket(x)[K] . W_i^T.  Replaces the
+ * same reference entries as gb_gemv (gridbook/csrc/cb_gemv.cu:1138-1198) for M = 1, one launch
+ * where gb_gemv needs two per matrix.  The K-slice partial sums travel through `slots`, an
+ * "armed" buffer of gb_gemv_tab_slots_bytes() bytes (256-byte aligned): every byte must read 0xFF
+ * before the first call (gb_gemv_tab_arm), and every call leaves it in that state again, so one
+ * buffer serves any number of consecutive calls, of any shapes it is large enough for, on one
+ * stream.  Calls that may overlap on the GPU need a buffer each.  A buffer that was never armed
+ * raises the device status word (24); after any non-zero status, arm the buffer again.
+ * act: GB_ACT_NONE or GB_ACT_FP4_GROUP16.  Returns GB_EUNSUPPORTED for other formats or layouts
+ * and for K so wide that one wave of CTAs cannot hold every K slice (use gb_gemv). */
+GB_API int64_t gb_gemv_tab_slots_bytes(const gb_weight* const* w, int n_weights);
+GB_API int gb_gemv_tab_arm(void* slots, int64_t bytes, void* stream);
+GB_API int gb_gemv_tab(const void* x_bf16, const gb_weight* const* w, void* const* y_bf16, int n_weights,
+                       int act, int scale_rule, void* slots, int64_t slots_bytes, void* stream);
 
 /* ---- prefill (M > 16): tensor-core GEMM over decoded tiles --------------------------- */
 enum { GB_GEMM_BF16 = 0, GB_GEMM_E4M3 = 1 };

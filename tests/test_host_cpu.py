@@ -303,3 +303,93 @@ def test_artifact_codebook_digests(tmp_path):
         bad.mkdir()
         (bad / "config.json").write_text("{}")
         Artifact(str(bad))
+
+
+def test_scale_coding_comes_from_the_group_not_from_layout_version():
+    """A layout_version-2 artifact may hold v1 groups: absence of scale_coding means E4M3-direct
+    bytes (docs/SPEC.md:130-177), and mixed v1 / v2 groups resolve side by side."""
+    from gridbook_b200.config import PrismaQuantConfig
+    v1 = {"grid": "fp4", "mode": "product", "k": 16, "n_sub": 2, "type_size": 80, "codebook_ref": ["a", "b"]}
+    v2 = {"grid": "fp4", "mode": "product", "k": 16, "n_sub": 2, "type_size": 73, "codebook_ref": ["a", "b"],
+          "scale_coding": {"kind": "two_tier"}}
+    cfg = PrismaQuantConfig({"quant_method": "gridbook", "layout_version": 2, "config_groups": {
+        "old": {"targets": ["model.layers.0.mlp.down_proj"], "scheme": v1},
+        "new": {"targets": ["model.layers.1.mlp.down_proj"], "scheme": v2}},
+        "_codebooks": {"a": torch.zeros(256, 4), "b": torch.zeros(256, 4)}})
+
+    class Linear(torch.nn.Module):
+        pass
+
+    old = cfg.get_quant_method(Linear(), "model.layers.0.mlp.down_proj")
+    new = cfg.get_quant_method(Linear(), "model.layers.1.mlp.down_proj")
+    assert old.fmt.scale_coding == "v1" and old.fmt.type_size == 80 and not old.is_v2
+    assert new.fmt.scale_coding == "v2" and new.fmt.type_size == 73 and new.is_v2
+
+
+def test_fused_roles_must_share_scale_coding_and_stock_groups_are_named():
+    from gridbook_b200._native import NativeKernelUnavailableError
+    from gridbook_b200.config import PrismaQuantConfig
+    base = {"grid": "fp4", "mode": "product", "k": 16, "n_sub": 2, "codebook_ref": ["a", "b"]}
+    v1 = dict(base, type_size=80)
+    v2 = dict(base, type_size=73, scale_coding={"kind": "two_tier"})
+    v2_other_table = dict(base, type_size=73, scale_coding={"kind": "two_tier", "table": [1.0] * 16})
+    groups = {
+        "g0": {"targets": ["model.layers.0.self_attn.q_proj", "model.layers.0.self_attn.k_proj"], "scheme": v2},
+        "g1": {"targets": ["model.layers.0.self_attn.v_proj"], "scheme": v2_other_table},
+        "g2": {"targets": ["model.layers.0.mlp.gate_proj"], "scheme": v2},
+        "g3": {"targets": ["model.layers.0.mlp.up_proj"], "scheme": dict(v2, activation_contract="static_nvfp4")},
+        "stock": {"targets": ["model.layers.0.self_attn.o_proj"], "format": "float-quantized"},
+        "tower": {"targets": ["layers.3.mlp.down_proj"], "scheme": v1},
+    }
+    cfg = PrismaQuantConfig({"quant_method": "gridbook", "config_groups": groups})
+
+    class Linear(torch.nn.Module):
+        pass
+
+    with pytest.raises(ValueError, match="scale_coding"):
+        cfg.get_quant_method(Linear(), "model.layers.0.self_attn.qkv_proj")
+    with pytest.raises(ValueError, match="activation_contract"):
+        cfg.get_quant_method(Linear(), "model.layers.0.mlp.gate_up_proj")
+    with pytest.raises(NativeKernelUnavailableError, match="delegated groups are not served"):
+        cfg.get_quant_method(Linear(), "model.layers.0.self_attn.o_proj")
+    # suffix matches need a known wrapper prefix: another tower with the same tail is not a target
+    assert cfg.get_quant_method(Linear(), "model.layers.3.mlp.down_proj") is not None
+    assert cfg.get_quant_method(Linear(), "vision_tower.layers.3.mlp.down_proj") is None
+
+
+def test_routed_method_fails_closed_on_other_activations_and_weights_on_input():
+    from gridbook_b200._native import NativeKernelUnavailableError
+    from gridbook_b200.moe import PrismaQuantCBMoEMethod
+    scheme = {"grid": "fp4", "mode": "full", "k": 8, "n_sub": 1, "type_size": 48}
+    method = PrismaQuantCBMoEMethod(None, None, scheme, "model.layers.0.mlp.experts")
+
+    class Act:
+        def __init__(self, value):
+            self.value = value
+
+    class Layer(torch.nn.Module):
+        pass
+
+    gelu = Layer()
+    gelu.activation = Act("gelu")
+    with pytest.raises(NativeKernelUnavailableError, match="activation 'gelu'"):
+        method.process_weights_after_loading(gelu)
+    on_input = Layer()
+    on_input.activation = Act("silu")
+    on_input.apply_router_weight_on_input = True
+    with pytest.raises(NativeKernelUnavailableError, match="apply_router_weight_on_input"):
+        method.process_weights_after_loading(on_input)
+    ok = Layer()
+    ok.activation = Act("silu")
+    ok._cb_layer_id = 1
+    x, w, ids = torch.zeros(1, 8), torch.zeros(1, 2), torch.zeros(1, 2, dtype=torch.int32)
+    with pytest.raises(NativeKernelUnavailableError, match="apply_router_weight_on_input"):
+        method.apply(ok, x, w, ids, apply_router_weight_on_input=True)
+    ok.apply_router_weight_on_input = True
+    with pytest.raises(NativeKernelUnavailableError, match="apply_router_weight_on_input"):
+        method.apply(ok, x, w, ids)
+    ok.apply_router_weight_on_input = False
+    with pytest.raises(NativeKernelUnavailableError, match="expert_map"):
+        method.apply(ok, x, w, ids, expert_map=torch.arange(4))
+    with pytest.raises(NativeKernelUnavailableError, match="activation"):
+        method.apply(ok, x, w, ids, activation="gelu")

@@ -32,7 +32,8 @@ def _static_gemv(x, w, act):
     return rc, y, lib
 
 
-@pytest.mark.parametrize("name,M,N,K", [("lit", 3, 200, 1024), ("k16v2", 16, 264, 6144), ("f8k32", 9, 136, 7168)])
+@pytest.mark.parametrize("name,M,N,K", [("lit", 3, 200, 1024), ("k16v2", 16, 264, 6144), ("f8k32", 9, 136, 7168),
+                                        ("lit", 1, 512, 2048), ("lit", 3, 384, 1280)])
 def test_static_scratch_matches_workspace_entry(name, M, N, K):
     from gridbook_b200 import _native, kernels, synth
     from gridbook_b200.formats import CBFormat
@@ -50,6 +51,28 @@ def test_static_scratch_matches_workspace_entry(name, M, N, K):
         assert rc == 0, lib.gb_last_error().decode()
         torch.cuda.synchronize()
         assert_close_bf16(f32_of(got), f32_of(ref), f"{name} call {call}")
+    assert _native.device_status(0) == 0
+
+
+def test_static_scratch_table_kernels_after_a_larger_call_against_the_oracle():
+    """The literal format's table kernels (one row; a few rows, one table GEMV per row) write
+    every (K slice, row) slot they later add and never clear the array.  A larger call first
+    leaves its partial sums behind; the smaller calls that follow must not pick them up.
+    Checked against the oracle, not only against gb_gemv."""
+    from gridbook_b200 import _native, synth
+    from gridbook_b200.formats import CBFormat
+    from tests.helpers import oracle_linear
+    _native.prepare(0)
+    dev = torch.device("cuda:0")
+    fmt = CBFormat("fp4", 8, mode="full", scale_coding="v1")
+    for M, N, K in ((4, 1024, 4096), (1, 512, 2048), (3, 256, 1024), (1, 320, 1280)):
+        d = synth.make_linear(fmt, N, K, seed=N + K + M, global_scale=1.0 / 448.0)
+        w = synth.to_device_weight(d, dev)
+        xh = synth.make_activations(M, K, seed=M + N)
+        rc, got, lib = _static_gemv(synth.bf16_tensor(xh, dev), w, "fp4")
+        assert rc == 0, lib.gb_last_error().decode()
+        torch.cuda.synchronize()
+        assert_close_bf16(f32_of(got), oracle_linear(xh, d), f"static literal M={M} {N}x{K}")
     assert _native.device_status(0) == 0
 
 
