@@ -22,6 +22,7 @@ REQUIRED_SYMBOLS = (
     "gb_expand_fp8", "gb_expand_fp4_bf16", "gb_expand_fp4_nvfp4",
     "gb_gemv_workspace_bytes", "gb_gemv", "gb_gemv_static",
     "gb_gemv_tab_slots_bytes", "gb_gemv_tab_arm", "gb_gemv_tab", "gb_device_status_reset", "gb_set_wait_limit_ms",
+    "gb_nvfp4_sf_bytes", "gb_nvfp4_quantize_rows", "gb_gemm_fp4",
     "gb_moe_route", "gb_moe_route_ws", "gb_moe_route_workspace_bytes", "gb_moe_gemv_workspace_bytes", "gb_moe_gemv", "gb_moe_combine",
     "gb_moe_gemv_pairs_workspace_bytes", "gb_moe_gemv_pairs",
     "gb_moe_mlp_pairs_workspace_bytes", "gb_moe_mlp_pairs",
@@ -118,6 +119,10 @@ def _declare(lib) -> None:
     lib.gb_gemv_tab_slots_bytes.restype = i64
     lib.gb_gemv_tab_arm.argtypes = [vp, i64, vp]
     lib.gb_gemv_tab.argtypes = [vp, wpp, ctypes.POINTER(vp), i32, i32, i32, vp, i64, vp]
+    lib.gb_nvfp4_sf_bytes.argtypes = [i64, i64]
+    lib.gb_nvfp4_sf_bytes.restype = i64
+    lib.gb_nvfp4_quantize_rows.argtypes = [vp, i64, i64, ctypes.c_float, vp, vp, vp, vp]
+    lib.gb_gemm_fp4.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_float, vp]
     lib.gb_device_status_reset.argtypes = [i32]
     lib.gb_set_wait_limit_ms.argtypes = [i32]
     lib.gb_moe_route.argtypes = [vp, i64, i64, i64, i64, vp, vp, vp, vp, vp, vp]

@@ -10,7 +10,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libgridbook_b200.so")
-SOURCES = ("gb_api.cu", "gb_decode.cu", "gb_gemv.cu", "gb_moe.cu", "gb_gemm.cu", "gb_gemv_dot.cu", "gb_peer.cu", "gb_gemv_umma.cu", "gb_gemv_tab.cu")
+SOURCES = ("gb_api.cu", "gb_decode.cu", "gb_gemv.cu", "gb_moe.cu", "gb_gemm.cu", "gb_gemv_dot.cu", "gb_peer.cu", "gb_gemv_umma.cu", "gb_gemv_tab.cu", "gb_gemm_fp4.cu")
 HEADERS = ("gb_common.cuh", os.path.join("..", "..", "include", "gridbook_b200.h"))
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -149,6 +149,7 @@ int gb_prepare(int device) {
   if (rc == GB_OK) rc = gb_prepare_dot();
   if (rc == GB_OK) rc = gb_prepare_umma();
   if (rc == GB_OK) rc = gb_prepare_tab();
+  if (rc == GB_OK) rc = gb_prepare_gemm_fp4();
   cudaSetDevice(prev);
   return rc;
 }

@@ -66,6 +66,7 @@ int gb_prepare_gemm();
 int gb_prepare_dot();
 int gb_prepare_umma();
 int gb_prepare_tab();
+int gb_prepare_gemm_fp4();
 // Longest a device-side wait may spin before it gives up and raises the status word
 // (two seconds unless gb_set_wait_limit_ms changed it).
 unsigned long long gb_wait_limit_ns();

@@ -245,6 +245,12 @@ expand_kernel(ExpandArgs a, void* __restrict__ out0, uint8_t* __restrict__ out_s
         const uint32_t c = m < 2.0f ? (uint32_t)(m * 2.0f) : (m < 4.0f ? (uint32_t)m + 2u : (m < 6.0f ? 6u : 7u));
         nib |= (c | (val[u][j] < 0.0f ? 8u : 0u)) << (4 * j);
       }
+      if (sf_swizzled == 2 && (sbyte[u] & 0x80u)) {
+        // operand form of the block-scaled MMA, whose scale factors carry no sign: a negative
+        // group scale moves its sign into the group's sixteen values, (-s) * v = s * (-v)
+        nib ^= 0x88888888u;
+        sbyte[u] &= 0x7Fu;
+      }
       reinterpret_cast<uint32_t*>(out0)[at >> 3] = nib;
       if ((lane & 1) == 0) {
         const int64_t groups = a.K / 16;
@@ -327,6 +333,84 @@ int launch_expand(const gb_weight* w, int64_t row0, int64_t nrows, void* out0, v
   GB_LAUNCH_OK("expand_kernel");
   return GB_OK;
 }
+
+// ---- the literal format's native NVFP4 view, fast -------------------------------------------
+// Full mode, k = 8, E4M3-direct scales, one codebook: a codeword is one byte and its eight E2M1
+// values are one 32-bit word of a 256-entry table kept in shared memory.  Eight lanes take one
+// (row, superblock): each loads four codes as one word, looks them up and stores sixteen bytes
+// (128 contiguous bytes per unit); the first four of them also write the unit's sixteen group
+// scales, one word per 128 x 4 atom.  Memory-bound: 48 bytes read and 144 written per 256 weights.
+constexpr int kLitUnroll = 4;                              // steps in flight per warp, four units each
+
+__global__ void __launch_bounds__(kThreads)
+expand_literal_nvfp4_kernel(const uint8_t* __restrict__ qw, int64_t row_stride, const uint16_t* __restrict__ codebook,
+                            int64_t nrows, int64_t n_sb, uint4* __restrict__ out_packed,
+                            uint8_t* __restrict__ out_sf, int fold_sign) {
+  __shared__ uint32_t lut[256];
+  {
+    const uint4 e = __ldg(reinterpret_cast<const uint4*>(codebook) + threadIdx.x);     // kThreads == 256 entries
+    const uint32_t w[4] = {e.x, e.y, e.z, e.w};
+    uint32_t nib = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float v = gb_bf16_bits_to_f32((w[j >> 1] >> (16 * (j & 1))) & 0xffffu);
+      const float m = fabsf(v);
+      const uint32_t c = m < 2.0f ? (uint32_t)(m * 2.0f) : (m < 4.0f ? (uint32_t)m + 2u : (m < 6.0f ? 6u : 7u));
+      nib |= (c | (v < 0.0f ? 8u : 0u)) << (4 * j);
+    }
+    lut[threadIdx.x] = nib;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, sub = lane & 7, which = lane >> 3;
+  const int64_t units = nrows * n_sb;
+  const int64_t k_atoms = n_sb * 4;                        // atoms along K of one 128-row tile
+  const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
+  for (int64_t u0 = ((int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5)) * (4 * kLitUnroll); u0 < units;
+       u0 += warps * (4 * kLitUnroll)) {
+    uint32_t codes[kLitUnroll], sc2[kLitUnroll], sc4[kLitUnroll];
+#pragma unroll
+    for (int i = 0; i < kLitUnroll; ++i) {
+      const int64_t u = u0 + 4 * i + which < units ? u0 + 4 * i + which : u0;
+      const int64_t r = u / n_sb, sb = u - r * n_sb;
+      const uint8_t* p = qw + r * row_stride + sb * 48;    // 16-byte aligned: rows are, and 48 is a multiple of 16
+      codes[i] = __ldg(reinterpret_cast<const uint32_t*>(p) + sub);
+      sc2[i] = __ldg(reinterpret_cast<const uint16_t*>(p + 32) + sub);                      // groups 2 sub, 2 sub + 1
+      sc4[i] = sub < 4 ? __ldg(reinterpret_cast<const uint32_t*>(p + 32) + sub) : 0u;       // the scales of atom `sub`
+    }
+#pragma unroll
+    for (int i = 0; i < kLitUnroll; ++i) {
+      const int64_t u = u0 + 4 * i + which;
+      if (u >= units) continue;
+      const int64_t r = u / n_sb, sb = u - r * n_sb;
+      uint32_t w0 = lut[codes[i] & 0xffu], w1 = lut[(codes[i] >> 8) & 0xffu];
+      uint32_t w2 = lut[(codes[i] >> 16) & 0xffu], w3 = lut[codes[i] >> 24];
+      if (fold_sign) {
+        if (sc2[i] & 0x80u) { w0 ^= 0x88888888u; w1 ^= 0x88888888u; }
+        if (sc2[i] & 0x8000u) { w2 ^= 0x88888888u; w3 ^= 0x88888888u; }
+      }
+      out_packed[u * 8 + sub] = make_uint4(w0, w1, w2, w3);
+      if (sub < 4) {
+        const int64_t off = (r / 128) * (512 * k_atoms) + (sb * 4 + sub) * 512 + (r % 32) * 16 + ((r / 32) % 4) * 4;
+        *reinterpret_cast<uint32_t*>(out_sf + off) = fold_sign ? (sc4[i] & 0x7F7F7F7Fu) : sc4[i];
+      }
+    }
+  }
+}
+
+int launch_expand_literal(const gb_weight* w, int64_t row0, int64_t nrows, void* out_packed, void* out_sf,
+                          int fold_sign, void* stream) {
+  const int64_t n_sb = w->K / 256, units = nrows * n_sb;
+  const int64_t per_cta = (kThreads / 32) * 4 * kLitUnroll;
+  int64_t blocks = (units + per_cta - 1) / per_cta;
+  const int64_t cap = (int64_t)gb_sm_count() * 16;
+  if (cap > 0 && blocks > cap) blocks = cap;
+  gb_count_launch();
+  expand_literal_nvfp4_kernel<<<(unsigned)blocks, kThreads, 0, (cudaStream_t)stream>>>(
+      w->qw + row0 * w->row_stride, w->row_stride, (const uint16_t*)w->codebook, nrows, n_sb, (uint4*)out_packed,
+      (uint8_t*)out_sf, fold_sign);
+  GB_LAUNCH_OK("expand_literal_nvfp4_kernel");
+  return GB_OK;
+}
 }  // namespace
 
 extern "C" {
@@ -350,6 +434,16 @@ int gb_expand_fp4_nvfp4(const gb_weight* w, int64_t row0, int64_t nrows, void* o
                         void* out_sf, int sf_swizzled, void* stream) {
   GB_REQUIRE(w && w->fmt.grid == GB_GRID_FP4, "gb_expand_fp4_nvfp4 wants an fp4-grid weight");
   GB_REQUIRE(out_sf != nullptr, "null scale-factor output");
+  const gb_format& f = w->fmt;
+  if (sf_swizzled != 0 && f.mode == GB_MODE_FULL && f.k_bits == 8 && f.scale_coding == GB_SCALE_V1 &&
+      w->cb_row_offset == nullptr && ((uintptr_t)w->codebook & 15u) == 0 && ((uintptr_t)out_packed & 15u) == 0 &&
+      ((uintptr_t)out_sf & 3u) == 0 && ((uintptr_t)w->qw & 15u) == 0 && w->row_stride % 16 == 0 && kThreads == 256) {
+    int rc = gb_check_weight(w);
+    if (rc != GB_OK) return rc;
+    GB_REQUIRE(out_packed != nullptr && row0 >= 0 && nrows >= 0 && row0 + nrows <= w->rows, "bad row window");
+    if (nrows == 0) return GB_OK;
+    return launch_expand_literal(w, row0, nrows, out_packed, out_sf, sf_swizzled == 2, stream);
+  }
   return launch_expand<kOutNvfp4>(w, row0, nrows, out_packed, out_sf, sf_swizzled, stream);
 }
 

@@ -144,14 +144,16 @@ def expand_fp4_bf16(w: PackedWeight, row0: int = 0, nrows: int | None = None) ->
 
 
 def expand_fp4_nvfp4(w: PackedWeight, row0: int = 0, nrows: int | None = None,
-                     swizzled: bool = False):
+                     swizzled: bool = False, operand: bool = False):
     """-> (packed E2M1 [nrows, K/2] uint8, E4M3 group scales: [nrows, K/16] or the flat
-    128x4-atom plane)."""
+    128x4-atom plane).  ``operand``: the atom plane in the form the block-scaled MMA takes (a
+    negative group scale hands its sign to the group's values)."""
     lib = nat.load("NVFP4 tile expansion")
     nrows = w.rows - row0 if nrows is None else nrows
     dev = w.qw.device
     packed = torch.empty((nrows, w.K // 2), dtype=torch.uint8, device=dev)
     groups = w.K // 16
+    swizzled = swizzled or operand
     if swizzled:
         sf = torch.zeros(((nrows + 127) // 128 * 128) * ((groups + 3) // 4 * 4),
                          dtype=torch.uint8, device=dev)
@@ -159,7 +161,7 @@ def expand_fp4_nvfp4(w: PackedWeight, row0: int = 0, nrows: int | None = None,
         sf = torch.empty((nrows, groups), dtype=torch.uint8, device=dev)
     nw = w.native()
     nat.check(lib.gb_expand_fp4_nvfp4(ctypes.byref(nw), row0, nrows, _ptr(packed), _ptr(sf),
-                                      1 if swizzled else 0, nat.stream_ptr(dev)), lib)
+                                      2 if operand else (1 if swizzled else 0), nat.stream_ptr(dev)), lib)
     return packed, sf
 
 
@@ -409,6 +411,43 @@ def fp8_quantize_rows(x: torch.Tensor, scale_rule: str = "recip"):
     return q.view(torch.float8_e4m3fn), scale
 
 
+NVFP4_ACT_RANGE = 448.0      # a row's largest group scale factor: the top of the UE4M3 range
+
+
+def nvfp4_quantize_rows(x: torch.Tensor, range_multiplier: float = NVFP4_ACT_RANGE):
+    """Native NVFP4 quantisation of bf16 rows: (packed [M, K/2] uint8, scale-factor plane in the
+    128x4 atom layout uint8, a_scale [M] fp32), x ~ a_scale * SF * E2M1."""
+    _need_cuda(x)
+    lib = nat.load("NVFP4 activation quantisation")
+    if x.dtype is not torch.bfloat16:
+        raise TypeError("the NVFP4 quantiser takes bf16 rows")
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    M, K = x2.shape
+    packed = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
+    sf = torch.empty(lib.gb_nvfp4_sf_bytes(M, K), dtype=torch.uint8, device=x.device)
+    a_scale = torch.empty((M,), dtype=torch.float32, device=x.device)
+    nat.check(lib.gb_nvfp4_quantize_rows(_ptr(x2), M, K, float(range_multiplier), _ptr(packed), _ptr(sf),
+                                         _ptr(a_scale), nat.stream_ptr(x.device)), lib)
+    return packed, sf, a_scale
+
+
+def gemm_fp4(a_packed: torch.Tensor, sfa: torch.Tensor, b_packed: torch.Tensor, sfb: torch.Tensor, *,
+             a_scale: torch.Tensor | None = None, global_scale: float = 1.0) -> torch.Tensor:
+    """bf16 D[M, N] = global_scale * a_scale[m] * (A SFA)(B SFB)^T on the block-scaled FP4 tensor
+    cores (tcgen05 kind::mxf4nvf4); operands packed E2M1 [rows, K/2], scale planes in the atom layout."""
+    _need_cuda(a_packed, sfa, b_packed, sfb, a_scale)
+    lib = nat.load("block-scaled FP4 GEMM")
+    a_packed, b_packed = a_packed.contiguous(), b_packed.contiguous()
+    M, kb = a_packed.shape
+    N = b_packed.shape[0]
+    if b_packed.shape[1] != kb:
+        raise RuntimeError(f"gemm_fp4: K mismatch {2 * kb} vs {2 * b_packed.shape[1]}")
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=a_packed.device)
+    nat.check(lib.gb_gemm_fp4(_ptr(a_packed), _ptr(sfa), _ptr(b_packed), _ptr(sfb), _ptr(out), M, N, 2 * kb,
+                              _ptr(a_scale), float(global_scale), nat.stream_ptr(a_packed.device)), lib)
+    return out
+
+
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a_scale=None, b_scale=None, global_scale: float = 1.0):
     """bf16 D[M, N] = scales * A[M, K] . B[N, K]^T on the tcgen05 tensor cores; A and B both bf16
     or both float8_e4m3fn."""
@@ -504,7 +543,8 @@ def moe_gemv_sorted_applies(w: PackedWeight) -> bool:
 
 
 def moe_gemv_sorted(x_sorted: torch.Tensor, w: PackedWeight, offsets: torch.Tensor, *,
-                    row_map: torch.Tensor | None = None, peer_rows=None) -> torch.Tensor | None:
+                    row_map: torch.Tensor | None = None, peer_rows=None,
+                    out: torch.Tensor | None = None) -> torch.Tensor | None:
     """Grouped linear over rows already in expert order, for mid-size batches: every (expert, 128-row
     tile) decodes its packed rows into shared memory and multiplies on the tensor cores.  -> [P, rows]
     bf16 (row j at ``row_map[j]`` or j; rows past ``offsets[E]`` unset), or None when the stack is
@@ -516,7 +556,10 @@ def moe_gemv_sorted(x_sorted: torch.Tensor, w: PackedWeight, offsets: torch.Tens
         return None
     x_sorted = x_sorted.contiguous()
     P = x_sorted.shape[0]
-    out = None if peer_rows is not None else torch.empty((P, w.rows), dtype=torch.bfloat16, device=x_sorted.device)
+    if peer_rows is not None:
+        out = None
+    elif out is None:
+        out = torch.empty((P, w.rows), dtype=torch.bfloat16, device=x_sorted.device)
     nw = w.native()
     nat.check(lib.gb_moe_gemv_sorted(_ptr(x_sorted), ctypes.byref(nw), w.expert_stride, w.experts, _ptr(offsets),
                                      _ptr(row_map), P, _ptr(out),

@@ -39,6 +39,10 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         sc = scheme.get("scale_coding")
         self._sub_table = (sc.get("table") if isinstance(sc, dict) else None) or codec.TWO_TIER_SUB_TABLE
         self.global_scale = float(scheme.get("weight_global_scale", 1.0))
+        # fp4 grid, past the decode batches: "nvfp4" = native NVFP4 activations x the native NVFP4
+        # view of the layer on the block-scaled tensor cores; "bf16" = the decode contract kept
+        # (bucketed bf16 rows x bf16(value * scale)) on the bf16 tensor cores
+        self.prefill_route = "nvfp4"
 
     # ------------------------------------------------------------------ parameters
     def create_weights(self, layer, input_size_per_partition, output_partition_sizes, input_size,
@@ -146,14 +150,25 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         """M > 16: expand the layer once into a transient decoded tile and run one tensor-core
         GEMM over it (tcgen05, accumulator in tensor memory).
 
-        fp4 grid: activations go through the group-16 bucket, the tile is the exact bf16 served
-        weight, kind::f16 MMA — the reference's expand + bf16 GEMM route with its numerics
+        fp4 grid, route "nvfp4" (default): the rows are quantised to native NVFP4 (per-row scale,
+        UE4M3 group scale factors, nearest-even E2M1), the layer is expanded to its native NVFP4
+        view (packed E2M1 + E4M3 group scales, 0.56 bytes per weight) and the two meet in a
+        block-scaled kind::mxf4nvf4 MMA — the reference's fused FP4 prefill lane
+        (gridbook/csrc/cb_fused_fp4_gemm.cu:758-903); its activation bucket is NOT the decode
+        contract's (UE4M3 scale factors instead of fp32 amax / 6).  Route "bf16": activations go
+        through the group-16 bucket, the tile is the exact bf16 served weight, kind::f16 MMA —
+        the reference's expand + bf16 GEMM route with the decode numerics
         (gridbook/linear.py:983-1023,1146-1152).  fp8 grid: activations are quantised per token to
         E4M3, the tile is the E4M3 value plane, kind::f8f6f4 MMA, and both scales multiply the
         fp32 accumulator — the reference's fp8 prefill lanes
         (gridbook/linear.py:1221-1264; epilogue of gridbook/csrc/cb_fused_gemm.cu:476-486)."""
         from . import ops
         w = layer._cb_weight
+        if self.is_fp4 and self.prefill_route == "nvfp4":
+            a, sfa, a_scale = kernels.nvfp4_quantize_rows(x2.contiguous())
+            b, sfb = kernels.expand_fp4_nvfp4(w, operand=True)
+            layer._cb_route["prefill"] = "nvfp4 activations + expand_fp4_nvfp4 + gemm_fp4(kind::mxf4nvf4)"
+            return kernels.gemm_fp4(a, sfa, b, sfb, a_scale=a_scale, global_scale=w.global_scale)
         if self.is_fp4:
             xq = kernels.fp4_act_qdq(x2.contiguous(), ops.ACT_SCALE_RULE)
             wt = kernels.expand_fp4_bf16(w)

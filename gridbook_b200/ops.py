@@ -234,6 +234,142 @@ def _(y, pair_w, tok_start, T):
     return torch.empty((T, y.shape[1]), dtype=y.dtype, device=y.device)
 
 
+# --------------------------------------------------------------------------- grouped prefill
+def _segments(expert_ends: torch.Tensor, expert_start: int, n_local: int) -> torch.Tensor:
+    """Cumulative row ends of the FULL expert stack -> first-row offsets [n_local + 1] of the
+    local slice, on the device (no host read)."""
+    ends = expert_ends.to(torch.int32).reshape(-1)
+    starts = torch.cat([ends.new_zeros(1), ends])
+    return starts[expert_start:expert_start + n_local + 1].contiguous()
+
+
+@torch.library.custom_op("prismaquant::cb_bf16_grouped_mm_out", mutates_args=("out",))
+def cb_bf16_grouped_mm_out(out: torch.Tensor, a: torch.Tensor, weights: torch.Tensor, expert_ends: torch.Tensor,
+                           expert_start: int = 0) -> None:
+    """Grouped bf16 GEMM over expert segments into a caller-owned [P, N] (gridbook/ops.py:163-178):
+    ``a`` [P, K] rows sorted by expert, ``weights`` [E_local, N, K] the local slice of the decoded
+    stack, ``expert_ends`` the cumulative row ends of the full stack.  Rows of other experts are
+    left as they are."""
+    e_local, n, k = weights.shape
+    seg = _segments(expert_ends, int(expert_start), e_local)
+    kernels.gemm_tn_grouped(a, weights.reshape(e_local * n, k), seg, n, out=out)
+
+
+@cb_bf16_grouped_mm_out.register_fake
+def _(out, a, weights, expert_ends, expert_start=0):
+    return None
+
+
+@torch.library.custom_op("prismaquant::cb_bf16_grouped_mm", mutates_args=())
+def cb_bf16_grouped_mm(a: torch.Tensor, weights: torch.Tensor, expert_ends: torch.Tensor,
+                       expert_start: int = 0) -> torch.Tensor:
+    """The allocating form (gridbook/ops.py:137-160): rows outside the local expert slice are zero."""
+    out = torch.zeros((a.shape[0], weights.shape[1]), dtype=torch.bfloat16, device=a.device)
+    cb_bf16_grouped_mm_out(out, a, weights, expert_ends, expert_start)
+    return out
+
+
+@cb_bf16_grouped_mm.register_fake
+def _(a, weights, expert_ends, expert_start=0):
+    return torch.empty((a.shape[0], weights.shape[1]), dtype=torch.bfloat16, device=a.device)
+
+
+def _persistent_b(out, a, w, expert_ends):
+    """One projection of the routed prefill over exact segments: the sorted-rows kernel that
+    decodes in shared memory where the format has it, else decode once + grouped GEMM."""
+    seg = _segments(expert_ends, 0, w.experts)
+    if kernels.moe_gemv_sorted_applies(w) and a.shape[0] <= 128 * w.experts:
+        if kernels.moe_gemv_sorted(a, w, seg, out=out) is not None:
+            return
+    wm = kernels.stack_rows(w)
+    tile = kernels.expand_fp4_bf16(wm) if w.fmt.is_fp4 else kernels.expand_fp8_bf16(wm)
+    kernels.gemm_tn_grouped(a, tile, seg, w.rows, global_scale=w.global_scale, out=out)
+
+
+@torch.library.custom_op("prismaquant::cb_moe_persistent_b_prefill", mutates_args=("out",))
+def cb_moe_persistent_b_prefill(out: torch.Tensor, a: torch.Tensor, qw: torch.Tensor, lut: torch.Tensor,
+                                compose: torch.Tensor, expert_ends: torch.Tensor, k_bits: int, type_size: int,
+                                cfg: int) -> None:
+    """Grouped decode + GEMM over the exact routed segments into a caller-owned [P, N]
+    (gridbook/ops.py:309-331): ``a`` [P, K] bucketed bf16 rows sorted by expert, ``qw`` [E, N, bytes]
+    packed fp4 product codewords, ``lut`` the flat bf16 codebook.  ``cfg`` selected a tile shape of
+    the reference's kernel and is accepted and ignored."""
+    w = kernels.make_weight(qw, lut, _fmt_fp4(k_bits, 2, type_size), a.shape[-1], compose=compose)
+    _persistent_b(out, a, w, expert_ends)
+
+
+@cb_moe_persistent_b_prefill.register_fake
+def _(out, a, qw, lut, compose, expert_ends, k_bits, type_size, cfg):
+    return None
+
+
+@torch.library.custom_op("prismaquant::cb_moe_persistent_b_prefill_d2r", mutates_args=("out",))
+def cb_moe_persistent_b_prefill_d2r(out: torch.Tensor, a: torch.Tensor, qw: torch.Tensor, lut: torch.Tensor,
+                                    compose: torch.Tensor, expert_ends: torch.Tensor, k_bits: int, type_size: int,
+                                    cfg: int) -> None:
+    """Same operands and result as cb_moe_persistent_b_prefill (gridbook/ops.py:334-355; the
+    reference's variant differs only in how its mainloop builds fragments)."""
+    w = kernels.make_weight(qw, lut, _fmt_fp4(k_bits, 2, type_size), a.shape[-1], compose=compose)
+    _persistent_b(out, a, w, expert_ends)
+
+
+@cb_moe_persistent_b_prefill_d2r.register_fake
+def _(out, a, qw, lut, compose, expert_ends, k_bits, type_size, cfg):
+    return None
+
+
+def _fp8_codebook_bytes(lut_f32: torch.Tensor) -> torch.Tensor:
+    """The fp32 table the reference converts from the E4M3 codebook at load, back to its bytes
+    (exact: every entry is an E4M3 value)."""
+    return lut_f32.to(torch.float32).to(torch.float8_e4m3fn).view(torch.uint8).contiguous()
+
+
+@torch.library.custom_op("prismaquant::cb_moe_persistent_b_prefill_fp8", mutates_args=("out",))
+def cb_moe_persistent_b_prefill_fp8(out: torch.Tensor, a: torch.Tensor, qw: torch.Tensor, lut_f32: torch.Tensor,
+                                    scale: torch.Tensor, expert_ends: torch.Tensor, k_bits: int, type_size: int,
+                                    cfg: int) -> None:
+    """The FP8-CB form (gridbook/ops.py:380-404): n_sub = 4 product codewords, per-(expert, row)
+    fp32 ``scale`` applied before the single bf16 rounding of every weight."""
+    w = kernels.make_weight(qw, _fp8_codebook_bytes(lut_f32), _fmt_fp8(k_bits, 4, type_size), a.shape[-1],
+                            weight_scale=scale.to(torch.float32).contiguous())
+    _persistent_b(out, a, w, expert_ends)
+
+
+@cb_moe_persistent_b_prefill_fp8.register_fake
+def _(out, a, qw, lut_f32, scale, expert_ends, k_bits, type_size, cfg):
+    return None
+
+
+@torch.library.custom_op("prismaquant::cb_moe_persistent_b_decode", mutates_args=())
+def cb_moe_persistent_b_decode(qw_flat: torch.Tensor, lut: torch.Tensor, compose: torch.Tensor, row0: int,
+                               nrows: int, K: int, k_bits: int, type_size: int) -> torch.Tensor:
+    """The decode stage alone (gridbook/ops.py:358-377): rows [row0, row0 + nrows) of the flattened
+    stack -> [nrows, K] bf16 = bf16(value * group scale)."""
+    qw2 = qw_flat.reshape(-1, qw_flat.shape[-1])
+    w = kernels.make_weight(qw2, lut, _fmt_fp4(k_bits, 2, type_size), K, compose=compose)
+    return kernels.expand_fp4_bf16(w, row0, nrows)
+
+
+@cb_moe_persistent_b_decode.register_fake
+def _(qw_flat, lut, compose, row0, nrows, K, k_bits, type_size):
+    return qw_flat.new_empty((nrows, K), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("prismaquant::cb_moe_persistent_b_decode_fp8", mutates_args=())
+def cb_moe_persistent_b_decode_fp8(qw_flat: torch.Tensor, lut_f32: torch.Tensor, scale: torch.Tensor, row0: int,
+                                   nrows: int, K: int, k_bits: int, type_size: int) -> torch.Tensor:
+    """The FP8 decode stage alone (gridbook/ops.py:407-428): bf16(value * scale[row])."""
+    qw2 = qw_flat.reshape(-1, qw_flat.shape[-1])
+    w = kernels.make_weight(qw2, _fp8_codebook_bytes(lut_f32), _fmt_fp8(k_bits, 4, type_size), K,
+                            weight_scale=scale.reshape(-1).to(torch.float32).contiguous())
+    return kernels.expand_fp8_bf16(w, row0, nrows)
+
+
+@cb_moe_persistent_b_decode_fp8.register_fake
+def _(qw_flat, lut_f32, scale, row0, nrows, K, k_bits, type_size):
+    return qw_flat.new_empty((nrows, K), dtype=torch.bfloat16)
+
+
 # --------------------------------------------------------------------------- layer registry
 # Weak, monotonic integer indirection so the two whole-dispatch ops stay opaque to Dynamo
 # (gridbook/ops.py:686-728).

@@ -11,7 +11,8 @@ def register(registry=None) -> None:
     """Register PrismaQuantConfig.  ``registry`` (a callable ``name -> class decorator``) is
     for tests; by default vLLM's ``register_quantization_config`` is used."""
     global _REGISTERED
-    if _REGISTERED and registry is None:
+    engine = registry is None
+    if _REGISTERED and engine:
         return
     from . import _native
     _native.load("gridbook_b200 plugin")           # fail closed at start-up, not at first forward
@@ -24,4 +25,5 @@ def register(registry=None) -> None:
         except (ValueError, AssertionError) as exc:      # already registered by an earlier load
             if "already" not in str(exc).lower():
                 raise
-    _REGISTERED = True
+    if engine:
+        _REGISTERED = True

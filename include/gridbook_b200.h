@@ -110,7 +110,9 @@ GB_API int gb_expand_fp4_bf16(const gb_weight* w, int64_t row0, int64_t nrows, v
  * GEMM, gridbook/csrc/cb_fused_fp4_gemm.cu:25-60): packed E2M1 [nrows, K/2] (even element
  * in the low nibble) and E4M3 group scales, either row-major [nrows, K/16]
  * (sf_swizzled = 0) or in the 128x4 atom layout of gridbook/codec.py:353-374
- * (sf_swizzled = 1, plane padded to 128 rows x 4 groups, caller zero-fills). */
+ * (sf_swizzled = 1, plane padded to 128 rows x 4 groups, caller zero-fills).  sf_swizzled = 2:
+ * the same atom layout in the operand form of the block-scaled MMA, whose UE4M3 scale factors
+ * carry no sign - a negative group scale moves its sign into the group's sixteen values. */
 GB_API int gb_expand_fp4_nvfp4(const gb_weight* w, int64_t row0, int64_t nrows, void* out_packed,
                         void* out_sf, int sf_swizzled, void* stream);
 
@@ -181,6 +183,28 @@ GB_API int gb_fp8_quantize_rows(const void* x_bf16, void* q_e4m3, float* scale, 
  * gridbook/csrc/cb_fused_gemm.cu:476-486). */
 GB_API int gb_gemm_tn(const void* A, const void* B, void* D_bf16, int64_t M, int64_t N, int64_t K, int kind,
                       const float* a_scale, const float* b_scale, float global_scale, void* stream);
+/* ---- prefill on the block-scaled FP4 tensor cores ----------------------------------- */
+/* Bytes of a scale-factor plane in the 128 x 4 atom layout for `rows` rows of K elements
+ * (rows padded to 128, groups of sixteen padded to four). */
+GB_API int64_t gb_nvfp4_sf_bytes(int64_t rows, int64_t K);
+/* Native NVFP4 quantisation of bf16 activation rows with one scale per row, chosen so that the
+ * row's largest group scale is `range` (<= 448): packed E2M1 [M, K/2] (even element in the low
+ * nibble), UE4M3 group-of-16 scale factors in the atom layout (gb_nvfp4_sf_bytes(M, K) bytes,
+ * the padding rows of the last tile are cleared), a_scale[M] with x ~ a_scale * SF * code.
+ * Replaces cb_nvfp4_quantize_rows (gridbook/csrc/cb_fused_fp4_gemm.cu:291-450,459-479) with
+ * the exactly rounded arithmetic of its torch statement (gridbook/codec.py:377-425). */
+GB_API int gb_nvfp4_quantize_rows(const void* x_bf16, int64_t M, int64_t K, float range, void* packed,
+                                  void* sf, float* a_scale, void* stream);
+/* D[M,N] bf16 = bf16(global_scale * a_scale[m] * sum_k (A SFA)[m,k] (B SFB)[n,k]): A [M,K/2] and
+ * B [N,K/2] packed E2M1, SFA / SFB their scale-factor planes in the atom layout, K a multiple of
+ * 256.  tcgen05 kind::mxf4nvf4 (block16, UE4M3 scale factors in tensor memory), fp32 accumulate.
+ * With B, SFB = gb_expand_fp4_nvfp4(.., sf_swizzled = 2) of a layer and A, SFA, a_scale =
+ * gb_nvfp4_quantize_rows this replaces the reference's block-scaled prefill
+ * (gridbook/csrc/cb_fused_fp4_gemm.cu:758-903; mainloop
+ * gridbook/csrc/cutlass_fork/sm120_cb_fused_fp4_mma.hpp:661-805). */
+GB_API int gb_gemm_fp4(const void* A, const void* sfa, const void* B, const void* sfb, void* D_bf16, int64_t M,
+                       int64_t N, int64_t K, const float* a_scale, float global_scale, void* stream);
+
 /* The same GEMM over expert segments (routed prefill): A [P,K] holds the routed rows sorted by
  * expert, expert e owning rows [seg_offsets[e], seg_offsets[e+1]) (gb_moe_route's offsets, read
  * on the device: no host read); B [E*N,K] is the decoded stack (gb_expand_* over all E*N rows);

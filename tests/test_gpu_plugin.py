@@ -44,6 +44,7 @@ def test_linear_method_decode_and_prefill(dev, name):
     lin = CBLinear(fmt, K, [96, 96], [_tables(fmt, d["cb"][:n]), _tables(fmt, d["cb"][n:])], global_scale=gs)
     ws = None if fmt.is_fp4 else torch.from_numpy(d["weight_scale"])
     lin.load(torch.from_numpy(d["qw"]), ws, dev)
+    lin.method.prefill_route = "bf16"        # the route that keeps the decode contract (the block-scaled one: test_gpu_gemm_fp4)
     for M in (1, 7, 16, 40, 300):
         x = synth.make_activations(M, K, seed=M)
         y = lin(synth.bf16_tensor(x, dev).reshape(1, M, K))
