@@ -9,13 +9,13 @@
 // Scale factors travel in the 128 x 4 atom layout (gridbook/codec.py:353-374): 512 bytes hold the
 // scale bytes of 128 rows x 4 groups, row r and group g at (r % 32) * 16 + (r / 32) * 4 + g; the
 // atoms of one 128-row tile follow each other along K.  One atom is exactly what one MMA
-// (K = 64) needs for 128 rows: tcgen05.cp (32x128b, broadcast to the four lane quarters) puts it
-// into four columns of tensor memory, row r at lane r % 32, column r / 32.
+// (K = 64) needs for 128 rows: four columns of tensor memory, row r's four bytes at lane r % 32
+// of every lane quarter, column r / 32.
 //
 // Persistent CTAs walk 128 x 256 output tiles, M fastest.  Warp 4 streams 256-element K slabs
 // of A and B (tiled TMA, 128-byte swizzle) and their scale-factor atoms (bulk copies) into a
-// four-stage ring; warp 5 copies the atoms to tensor memory and issues four MMAs per stage;
-// warps 0-3 drain the accumulator.  Tensor memory: 256 accumulator columns and two sets of 16 SFA
+// four-stage ring; warps 6-9 move the atoms from shared to tensor memory (one thread per lane);
+// warp 5 issues four MMAs per stage; warps 0-3 drain the accumulator.  Tensor memory: 256 accumulator columns and two sets of 16 SFA
 // + 32 SFB columns - there is no room for a second accumulator beside them, so the epilogue of a
 // tile only overlaps the loads of the next one.
 #include "gb_common.cuh"
@@ -34,7 +34,7 @@ constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;   // 54 K
 constexpr int kStages = 4;
 constexpr int kTmemCols = 512;
 constexpr uint32_t kAccCol = 0, kSfaCol = 256, kSfbCol = 272, kSfSet = 48;   // two sets of SF columns, used in turn
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;                      // 4 epilogue warps, producer, MMA issuer, 4 scale-factor warps
 constexpr int kSmem = kStages * kStageBytes + 1024 + 256;
 
 struct Fp4Params {
@@ -72,21 +72,6 @@ GB_DEVINL uint64_t desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
-// One scale-factor atom as the source of tcgen05.cp: 32 rows of 16 bytes, unswizzled, the
-// 8-row groups 128 bytes apart.
-GB_DEVINL uint64_t desc_sf_atom(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)(16u >> 4) << 16;
-  d |= (uint64_t)(128u >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  return d;
-}
-
-GB_DEVINL void sf_to_tmem(uint32_t tmem_col, uint64_t desc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_col), "l"(desc) : "memory");
-}
-
 GB_DEVINL void umma_fp4(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t sfa, uint32_t sfb,
                         bool accumulate) {
   asm volatile(
@@ -106,6 +91,14 @@ GB_DEVINL void wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort
     *abort_flag = 1;
     atomicExch(status, code);
   }
+}
+
+GB_DEVINL void tmem_st16(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
 }
 
 GB_DEVINL void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
@@ -154,7 +147,9 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* acc_full = empty_bar + kStages;
   uint64_t* acc_empty = acc_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+  uint64_t* sf_full = acc_empty + 1;                 // [2] a column set holds a stage's scale factors (four warps)
+  uint64_t* sf_empty = sf_full + 2;                  // [2] the MMAs that read a column set are done (one commit)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -165,6 +160,10 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
     gb_mbar_init(acc_full, 1);
     gb_mbar_init(acc_empty, 4);
+    for (int b = 0; b < 2; ++b) {
+      gb_mbar_init(&sf_full[b], 4);
+      gb_mbar_init(&sf_empty[b], 1);
+    }
     *abort_flag = 0;
     gb_fence_barrier_init();
   }
@@ -206,29 +205,16 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   } else if (warp == 5) {
     // ------------------------------- MMA issuer ---------------------------------
     if (lane == 0) {
-      // One flat sequence of stages over all of this CTA's tiles.  The scale factors of stage
-      // g + 1 are copied to tensor memory BEFORE the MMAs of stage g are issued (two column sets,
-      // used in turn), so the copies run under the MMAs instead of in front of them.
+      // One flat sequence of stages over all of this CTA's tiles.  The scale factors of a stage
+      // are put into tensor memory by warps 6-9 (two column sets, used in turn), so the tensor
+      // pipe runs MMAs only.
       const int my_tiles = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
       const int total = my_tiles * p.k_tiles;
-      auto copy_sf = [&](int g) {
-        const int s = g % kStages;
-        wait_or_abort(&full_bar[s], (g / kStages) & 1, abort_flag, p.status, 32);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t sf_s = ring + (uint32_t)s * kStageBytes + kABytes + kBBytes;
-        const uint32_t sfa_t = tmem_base + kSfaCol + (uint32_t)(g & 1) * kSfSet;
-        const uint32_t sfb_t = tmem_base + kSfbCol + (uint32_t)(g & 1) * kSfSet;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {                      // the atoms of the stage's four MMAs
-          sf_to_tmem(sfa_t + 4u * k, desc_sf_atom(sf_s + 512u * k));
-          sf_to_tmem(sfb_t + 8u * k, desc_sf_atom(sf_s + kSfaBytes + 512u * k));
-          sf_to_tmem(sfb_t + 8u * k + 4u, desc_sf_atom(sf_s + 2 * kSfaBytes + 512u * k));
-        }
-      };
-      if (total > 0) copy_sf(0);
       for (int g = 0; g < total; ++g) {
-        const int kt = g % p.k_tiles, it = g / p.k_tiles, s = g % kStages;
-        if (g + 1 < total) copy_sf(g + 1);
+        const int kt = g % p.k_tiles, it = g / p.k_tiles, s = g % kStages, set = g & 1;
+        wait_or_abort(&full_bar[s], (g / kStages) & 1, abort_flag, p.status, 32);
+        wait_or_abort(&sf_full[set], (g >> 1) & 1, abort_flag, p.status, 35);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (kt == 0) {                                     // the epilogue drained the last tile
           wait_or_abort(acc_empty, (it & 1) ^ 1, abort_flag, p.status, 34);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -242,10 +228,44 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           umma_fp4(tmem_base + kAccCol, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), p.idesc, sfa_t + 4u * k,
                    sfb_t + 8u * k, kt > 0 || k > 0);
         umma_commit(&empty_bar[s]);
+        umma_commit(&sf_empty[set]);
         if (kt == p.k_tiles - 1) umma_commit(acc_full);
       }
     }
-  } else {
+  } else if (warp >= 6) {
+    // --------------------------- scale factors -> tensor memory ---------------------------
+    // Thread = one lane of tensor memory (quarter warp % 4, lane in the quarter).  A 512-byte atom
+    // holds, in its 16-byte line l, the scale bytes of rows l, l + 32, l + 64, l + 96 for the four
+    // groups of one MMA: exactly the four columns that lane l of EVERY quarter must hold.  Twelve
+    // 16-byte loads and 48 columns stored per stage and thread - what tcgen05.cp would do inside
+    // the tensor pipe, where each copy costs MMA issue slots.
+    const int my_tiles = total_tiles > (int)blockIdx.x ? (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int total = my_tiles * p.k_tiles;
+    const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    for (int g = 0; g < total; ++g) {
+      const int s = g % kStages, set = g & 1;
+      wait_or_abort(&full_bar[s], (g / kStages) & 1, abort_flag, p.status, 36);
+      wait_or_abort(&sf_empty[set], ((g >> 1) & 1) ^ 1, abort_flag, p.status, 37);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint4* atoms = reinterpret_cast<const uint4*>(smem + (size_t)s * kStageBytes + kABytes + kBBytes) + lane;
+      uint32_t v[48];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint4 a = atoms[32 * k], b0 = atoms[32 * (4 + k)], b1 = atoms[32 * (8 + k)];
+        v[4 * k] = a.x; v[4 * k + 1] = a.y; v[4 * k + 2] = a.z; v[4 * k + 3] = a.w;
+        v[16 + 8 * k] = b0.x; v[17 + 8 * k] = b0.y; v[18 + 8 * k] = b0.z; v[19 + 8 * k] = b0.w;
+        v[20 + 8 * k] = b1.x; v[21 + 8 * k] = b1.y; v[22 + 8 * k] = b1.z; v[23 + 8 * k] = b1.w;
+      }
+      const uint32_t col = lane_base + kSfaCol + (uint32_t)set * kSfSet;       // SFA columns, then SFB right behind
+      tmem_st16(col, &v[0]);
+      tmem_st16(col + 16u, &v[16]);
+      tmem_st16(col + 32u, &v[32]);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) gb_mbar_arrive(&sf_full[set]);
+    }
+  } else if (warp < 4) {
     // ------------------------------- epilogue -----------------------------------
     int it = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
