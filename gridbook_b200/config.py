@@ -193,6 +193,9 @@ class PrismaQuantConfig(QuantizationConfig):
         base = prefix
         for tail in (".w13", ".w2"):
             if prefix.endswith(tail):
+                refs = scheme.get("_role_refs")
+                if tail == ".w13" and refs and json.dumps(refs[0]) != json.dumps(refs[1]):
+                    return [self._tables(dict(scheme, codebook_ref=r)) for r in refs]
                 return [self._tables(scheme)]
         keys = self.shard_target_keys(base, unfused_fallback=True)
         schemes = [self._lookup(k) or scheme for k in keys]
@@ -203,12 +206,33 @@ class PrismaQuantConfig(QuantizationConfig):
 
     def _moe_scheme_for_prefix(self, prefix: str):
         """(gate_up scheme, down scheme) of a routed stack, or None
-        (gridbook/config.py:1605-1641).  Unlike the reference, the two projections may differ."""
+        (gridbook/config.py:1605-1641).  Unlike the reference, the two projections may differ.
+        The gate_up scheme may come from a fused `gate_up_proj` target (one book for both roles)
+        or from separate `gate_proj` / `up_proj` targets with their own books
+        (docs/SPEC.md:480-527); then it carries `_role_refs`, the codebook_ref of each role."""
         self._ensure_resolved()
-        up = self._lookup(f"{prefix}.gate_up_proj")
+        fused = self._lookup(f"{prefix}.gate_up_proj")
+        gate, up_role = self._lookup(f"{prefix}.gate_proj"), self._lookup(f"{prefix}.up_proj")
         down = self._lookup(f"{prefix}.down_proj")
-        if up is None and down is None:
+        if fused is None and gate is None and up_role is None and down is None:
             return None
+        if (gate is None) != (up_role is None):
+            raise ValueError(f"[prismaquant] {prefix}: only one of gate_proj / up_proj is a CB target; a role "
+                             "is left without a book")
+        if fused is not None and gate is not None:
+            for name, role in (("gate", gate), ("up", up_role)):
+                if json.dumps(role.get("codebook_ref")) != json.dumps(fused.get("codebook_ref")):
+                    raise ValueError(f"[prismaquant] {prefix}: gate_up_proj and {name}_proj claim the {name} role "
+                                     "with different codebooks")
+        up = fused
+        if up is None and gate is not None:
+            fields = ("grid", "mode", "k", "n_sub", "type_size", "scale_coding", "activation_contract")
+            diff = [f for f in fields if gate.get(f) != up_role.get(f)]
+            if diff:
+                raise ValueError(f"[prismaquant] {prefix}: gate_proj and up_proj differ in {diff}; only the "
+                                 "codebook may differ between the roles of a routed stack")
+            up = dict(gate)
+            up["_role_refs"] = [gate["codebook_ref"], up_role["codebook_ref"]]
         if up is None or down is None:
             raise ValueError(f"[prismaquant] {prefix}: only one of gate_up_proj / down_proj is a CB target")
         return up, down

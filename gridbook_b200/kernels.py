@@ -526,13 +526,20 @@ def moe_swiglu_rows(h: torch.Tensor, offsets: torch.Tensor, *, act: str | None =
 
 def stack_rows(w: PackedWeight) -> PackedWeight:
     """An expert stack [E, rows, bytes] seen as one matrix of E * rows rows (the experts are
-    contiguous), for the expanders."""
+    contiguous), for the expanders.  Per-row codebook offsets (gate and up with their own books)
+    repeat for every expert."""
     if w.experts == 1:
         return w
-    if w.expert_stride != w.rows * w.row_stride or w.cb_row_offset is not None:
-        raise RuntimeError("the expert stack is not one contiguous matrix with a single codebook")
+    if w.expert_stride != w.rows * w.row_stride:
+        raise RuntimeError("the expert stack is not one contiguous matrix")
     ws = None if w.weight_scale is None else w.weight_scale.reshape(-1)
-    return PackedWeight(w.qw, w.codebook, w.fmt, w.K, w.experts * w.rows, w.row_stride, w.cb_row_offset,
+    off = None
+    if w.cb_row_offset is not None:
+        off = getattr(w, "_stack_offsets", None)
+        if off is None:
+            off = w.cb_row_offset.repeat(w.experts).contiguous()
+            w._stack_offsets = off
+    return PackedWeight(w.qw, w.codebook, w.fmt, w.K, w.experts * w.rows, w.row_stride, off,
                         w.compose, ws, w.global_scale)
 
 

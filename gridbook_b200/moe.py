@@ -122,12 +122,22 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
             raise NativeKernelUnavailableError(f"{self.prefix}: no quantization config to resolve codebooks")
         scheme = self.scheme if role == "w13" else self.scheme_down
         roles = qc.codebooks_for_prefix(f"{self.prefix}.{role}", scheme)
-        if len(roles) != 1:
+        # Per-role books (docs/SPEC.md:480-527; the reference serves them for FP8-CB only,
+        # gridbook/moe.py:2252-2273): gate and up may carry their own book at the same rung, w13
+        # splits at exactly `inter` rows, and every kernel selects the book by row.  w2 is a
+        # one-role stack.
+        if role == "w2" and len(roles) != 1:
             raise NativeKernelUnavailableError(
-                f"{self.prefix}: a routed stack shares one codebook per projection; got {len(roles)}")
-        flat = codec.build_flat_codebook([t.to(torch.float32) for t in roles[0]], prefix=self.prefix, grid=fmt.grid)
-        if flat.numel() != fmt.codebook_elems():
-            raise ValueError(f"{self.prefix}: codebook has {flat.numel()} entries, {fmt} wants {fmt.codebook_elems()}")
+                f"{self.prefix}: the down projection is a one-role stack; got {len(roles)} codebooks")
+        if role == "w13" and len(roles) not in (1, 2):
+            raise NativeKernelUnavailableError(
+                f"{self.prefix}: gate_up takes one shared codebook or one each for gate and up; got {len(roles)}")
+        blocks = [codec.build_flat_codebook([t.to(torch.float32) for t in tabs], prefix=self.prefix, grid=fmt.grid)
+                  for tabs in roles]
+        for b in blocks:
+            if b.numel() != fmt.codebook_elems():
+                raise ValueError(f"{self.prefix}: codebook has {b.numel()} entries, {fmt} wants {fmt.codebook_elems()}")
+        flat = torch.cat(blocks)
         p = getattr(layer, qw_name)
         dev = p.device
         packed = codec.with_tail_slack(p.data)
@@ -137,8 +147,13 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         table = (sc.get("table") if isinstance(sc, dict) else None) or codec.TWO_TIER_SUB_TABLE
         compose = codec.build_compose_table(table).to(dev) if fmt.scale_coding == "v2" else None
         ws = getattr(layer, scale_name).data.float().contiguous() if not fmt.is_fp4 else None
-        return kernels.make_weight(packed, cb_dev, fmt, k_in, compose=compose, weight_scale=ws,
-                                   global_scale=float(scheme.get("weight_global_scale", 1.0)))
+        cb_row_offset = None
+        if len(blocks) == 2:
+            inter = layer._cb_inter
+            cb_row_offset = torch.cat([torch.zeros(inter, dtype=torch.int32),
+                                       torch.full((inter,), fmt.codebook_elems(), dtype=torch.int32)]).to(dev)
+        return kernels.make_weight(packed, cb_dev, fmt, k_in, cb_row_offset=cb_row_offset, compose=compose,
+                                   weight_scale=ws, global_scale=float(scheme.get("weight_global_scale", 1.0)))
 
     def _require_served_contract(self, layer) -> None:
         """Fail closed at load on anything but SiLU-gated experts with router weights applied to the
@@ -338,7 +353,9 @@ class CBMoE(torch.nn.Module):
                  codebooks13, codebooks2, *, prefix: str = "cb_moe"):
         super().__init__()
         from .linear import _scheme_of
-        books = {f"{prefix}.w13": [codebooks13], f"{prefix}.w2": [codebooks2]}
+        # codebooks13: the tables of one shared book, or [gate tables, up tables] for per-role books
+        roles13 = list(codebooks13) if isinstance(codebooks13[0], (list, tuple)) else [codebooks13]
+        books = {f"{prefix}.w13": roles13, f"{prefix}.w2": [codebooks2]}
         self.method = PrismaQuantCBMoEMethod(_PrefixCodebooks(books), None, _scheme_of(fmt13), prefix,
                                              scheme_down=_scheme_of(fmt2))
         self.method.create_weights(self, num_experts, hidden, inter, torch.bfloat16)

@@ -170,3 +170,33 @@ def test_config4_one_ranks_experts(dev):
     assert _native.device_status(0) == 0
     assert int((local >= 0).sum()) > 400                  # about 512 routed pairs land on this rank
     _assert_moe_close(f32_of(out), ref, f"config 4 rank share ({getattr(moe, '_cb_route', '?')})")
+
+
+@pytest.mark.parametrize("name,T", [("lit", 3), ("lit", 40), ("lit", 450), ("f8k32", 5), ("f8k32", 450)])
+def test_per_role_routed_codebooks(dev, name, T):
+    """gate, up and down with a codebook each (configuration 3's wording; docs/SPEC.md:480-527):
+    the gate and up rows of w13 select their book by row in the decode kernel and in the decoded
+    prefill tile."""
+    from gridbook_b200 import _native, synth
+    from gridbook_b200.moe import CBMoE
+    fmt = _fmt(name)
+    E, topk, hidden, inter = 16, 4, 512, 256
+    w13d, w2d = synth.make_moe(fmt, fmt, E, hidden, inter, seed=8)
+    up_book = synth.make_codebook(fmt, np.random.default_rng(99))
+    gate_book = w13d["cb"]
+    w13d["cb"] = np.concatenate([gate_book, up_book])
+    w13d["cb_row_offset"] = np.concatenate([np.zeros(inter, np.int32),
+                                            np.full(inter, fmt.codebook_elems(), np.int32)])
+    ids, tw = synth.make_routing(T, E, topk, seed=T)
+    x = synth.make_activations(T, hidden, seed=T)
+    ref = O.moe_loop_chain(x, ids, tw, w13d, w2d, E=E, hidden=hidden, inter=inter, fmt13=fmt.oracle_kwargs(),
+                           fmt2=fmt.oracle_kwargs(), scale_rule="recip")
+    moe = CBMoE(fmt, fmt, E, hidden, inter, [_tables(fmt, gate_book), _tables(fmt, up_book)], _tables(fmt, w2d["cb"]))
+    s13 = None if fmt.is_fp4 else torch.from_numpy(w13d["scale"])
+    s2 = None if fmt.is_fp4 else torch.from_numpy(w2d["scale"])
+    moe.load(torch.from_numpy(w13d["qw"]), torch.from_numpy(w2d["qw"]), s13, s2, dev)
+    assert moe._cb_w13.cb_row_offset is not None
+    out = moe(synth.bf16_tensor(x, dev), torch.from_numpy(tw).to(dev), torch.from_numpy(ids).to(dev))
+    torch.cuda.synchronize()
+    assert _native.device_status(0) == 0
+    _assert_moe_close(f32_of(out), ref, f"per-role books {name} T={T} ({getattr(moe, '_cb_route', '?')})")

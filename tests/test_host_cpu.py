@@ -393,3 +393,47 @@ def test_routed_method_fails_closed_on_other_activations_and_weights_on_input():
         method.apply(ok, x, w, ids, expert_map=torch.arange(4))
     with pytest.raises(NativeKernelUnavailableError, match="activation"):
         method.apply(ok, x, w, ids, activation="gelu")
+
+
+def test_per_role_routed_codebooks_resolve_and_conflicts_refuse():
+    """gate_proj / up_proj / down_proj as separate targets with their own books
+    (docs/SPEC.md:480-527): w13 gets two role books, w2 one; a role claimed twice with different
+    books, or a role without a book, is refused."""
+    from gridbook_b200.config import PrismaQuantConfig
+    from gridbook_b200.moe import PrismaQuantCBMoEMethod
+
+    def scheme(ref):
+        return {"grid": "fp8", "mode": "product", "k": 32, "n_sub": 4, "type_size": 128,
+                "codebook_ref": [f"{ref}.{i}" for i in range(4)]}
+
+    books = {f"{r}.{i}": torch.full((256, 2), float(j)) for j, r in enumerate(("g", "u", "d")) for i in range(4)}
+    pre = "model.layers.1.mlp.experts"
+    groups = {"a": {"targets": [f"{pre}.gate_proj"], "scheme": scheme("g")},
+              "b": {"targets": [f"{pre}.up_proj"], "scheme": scheme("u")},
+              "c": {"targets": [f"{pre}.down_proj"], "scheme": scheme("d")}}
+    cfg = PrismaQuantConfig({"quant_method": "gridbook", "config_groups": groups, "_codebooks": books})
+
+    class FusedMoE(torch.nn.Module):
+        pass
+
+    m = cfg.get_quant_method(FusedMoE(), pre)
+    assert isinstance(m, PrismaQuantCBMoEMethod)
+    r13 = cfg.codebooks_for_prefix(f"{pre}.w13", m.scheme)
+    r2 = cfg.codebooks_for_prefix(f"{pre}.w2", m.scheme_down)
+    assert len(r13) == 2 and len(r2) == 1
+    assert float(r13[0][0][0, 0]) == 0.0 and float(r13[1][0][0, 0]) == 1.0 and float(r2[0][0][0, 0]) == 2.0
+    # the same book for both roles collapses to a uniform stack
+    same = dict(groups, b={"targets": [f"{pre}.up_proj"], "scheme": scheme("g")})
+    cfg2 = PrismaQuantConfig({"quant_method": "gridbook", "config_groups": same, "_codebooks": books})
+    m2 = cfg2.get_quant_method(FusedMoE(), pre)
+    assert len(cfg2.codebooks_for_prefix(f"{pre}.w13", m2.scheme)) == 1
+    # a role left without a book / claimed twice with different books
+    missing = {k: v for k, v in groups.items() if k != "b"}
+    with pytest.raises(ValueError, match="without a book"):
+        PrismaQuantConfig({"quant_method": "gridbook", "config_groups": missing}).get_quant_method(FusedMoE(), pre)
+    twice = dict(groups, d={"targets": [f"{pre}.gate_up_proj"], "scheme": scheme("u")})
+    with pytest.raises(ValueError, match="different codebooks"):
+        PrismaQuantConfig({"quant_method": "gridbook", "config_groups": twice}).get_quant_method(FusedMoE(), pre)
+    other_k = dict(groups, b={"targets": [f"{pre}.up_proj"], "scheme": dict(scheme("u"), k=28, type_size=112)})
+    with pytest.raises(ValueError, match="differ in"):
+        PrismaQuantConfig({"quant_method": "gridbook", "config_groups": other_k}).get_quant_method(FusedMoE(), pre)
