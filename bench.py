@@ -568,12 +568,13 @@ def cpu_layer_inputs(fmt, gscale, M, seed=0):
 
 def cpu_pass(layer):
     from oracle import c_oracle as C
+    from oracle import oracle_kwargs
     nbytes = 0
     for d, x in layer:
         fmt = d["fmt"]
         xq = C.act_qdq(x, fmt.grid, "recip")
         C.linear(xq, d["qw"], d["cb"], None, N=d["N"], K=d["K"], compose=d["compose"],
-                 weight_scale=d["weight_scale"], global_scale=d["global_scale"], **fmt.oracle_kwargs())
+                 weight_scale=d["weight_scale"], global_scale=d["global_scale"], **oracle_kwargs(fmt))
         nbytes += d["N"] * fmt.row_bytes(d["K"])
     return nbytes
 

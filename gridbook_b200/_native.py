@@ -22,7 +22,7 @@ REQUIRED_SYMBOLS = (
     "gb_expand_fp8", "gb_expand_fp4_bf16", "gb_expand_fp4_nvfp4",
     "gb_gemv_workspace_bytes", "gb_gemv", "gb_gemv_static",
     "gb_gemv_tab_slots_bytes", "gb_gemv_tab_arm", "gb_gemv_tab", "gb_device_status_reset", "gb_set_wait_limit_ms",
-    "gb_nvfp4_sf_bytes", "gb_nvfp4_quantize_rows", "gb_gemm_fp4",
+    "gb_set_row_routes", "gb_nvfp4_sf_bytes", "gb_nvfp4_quantize_rows", "gb_gemm_fp4",
     "gb_moe_route", "gb_moe_route_ws", "gb_moe_route_workspace_bytes", "gb_moe_gemv_workspace_bytes", "gb_moe_gemv", "gb_moe_combine",
     "gb_moe_gemv_pairs_workspace_bytes", "gb_moe_gemv_pairs",
     "gb_moe_mlp_pairs_workspace_bytes", "gb_moe_mlp_pairs",
@@ -123,6 +123,7 @@ def _declare(lib) -> None:
     lib.gb_nvfp4_sf_bytes.restype = i64
     lib.gb_nvfp4_quantize_rows.argtypes = [vp, i64, i64, ctypes.c_float, vp, vp, vp, vp]
     lib.gb_gemm_fp4.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, vp, ctypes.c_float, vp]
+    lib.gb_set_row_routes.argtypes = [i32, i32]
     lib.gb_device_status_reset.argtypes = [i32]
     lib.gb_set_wait_limit_ms.argtypes = [i32]
     lib.gb_moe_route.argtypes = [vp, i64, i64, i64, i64, vp, vp, vp, vp, vp, vp]
@@ -240,6 +241,12 @@ def set_wait_limit_ms(ms: int) -> None:
     gives up (0 restores the default of two seconds)."""
     lib = load()
     check(lib.gb_set_wait_limit_ms(int(ms)), lib)
+
+
+def set_row_routes(dot_rows: int = 0, umma_min: int = 0) -> None:
+    """Row counts at which the dense decode entry changes kernel for the literal format (0 = default)."""
+    lib = load()
+    check(lib.gb_set_row_routes(int(dot_rows), int(umma_min)), lib)
 
 
 def stream_ptr(device=None) -> int:

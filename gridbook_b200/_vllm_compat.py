@@ -6,13 +6,12 @@ benchmarks, the GPU box without an engine) light stand-ins with the same call
 surface are used instead, so the hot path can be driven without importing vLLM."""
 from __future__ import annotations
 
-import os
 import sys
 
 import torch
 
 HAVE_VLLM = False
-if "vllm" in sys.modules or os.environ.get("GRIDBOOK_B200_IMPORT_VLLM") == "1":
+if "vllm" in sys.modules:
     try:
         from vllm.model_executor.layers.fused_moe import FusedMoEMethodBase  # type: ignore
         from vllm.model_executor.layers.linear import (LinearMethodBase,  # type: ignore

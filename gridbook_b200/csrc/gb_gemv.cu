@@ -796,24 +796,14 @@ bool literal_aligned(const GemvParams& p) {
 }
 
 constexpr int kDotRowsMax = 8;      // most activation rows ever served by per-row table GEMVs
-// Rows from which the tensor-core decode kernel (gb_gemv_umma.cu) is tried.  Measured on the
-// benchmark's projections it is flat in the row count (gate_up: 86 us at 2..16 rows, 110 us at
-// 128) and passes the expanding kernel past sixteen rows; below that the table and expanding
-// kernels are faster on the large projections.  GRIDBOOK_B200_UMMA_MIN_M overrides (read per call).
-int umma_min_rows() {
-  const char* e = getenv("GRIDBOOK_B200_UMMA_MIN_M");
-  const int n = e ? atoi(e) : 17;
-  return n < 2 ? 2 : n;
-}
-
-int dot_rows_max() {                // rows up to which they are actually used (GRIDBOOK_B200_DOT_ROWS overrides)
-  static const int v = [] {
-    const char* e = getenv("GRIDBOOK_B200_DOT_ROWS");
-    int n = e ? atoi(e) : 4;
-    return n < 1 ? 1 : (n > kDotRowsMax ? kDotRowsMax : n);
-  }();
-  return v;
-}
+// Row counts at which gb_gemv changes kernel for the literal format, as measured on the
+// benchmark's projections: up to four rows one table GEMV per row (weights re-streamed, mostly
+// out of L2) beats expanding every weight; from seventeen rows on the tensor-core decode kernel
+// (flat in the row count: gate_up 86 us at 2..16 rows, 110 us at 128) passes the expanding one.
+// gb_set_row_routes moves them (a process-wide setting, meant for tests and for tuning).
+std::atomic<int> g_dot_rows_max{4}, g_umma_min_rows{17};
+int umma_min_rows() { return g_umma_min_rows.load(std::memory_order_relaxed); }
+int dot_rows_max() { return g_dot_rows_max.load(std::memory_order_relaxed); }
 
 int classify(const gb_format& f, int* out, bool* wide) {
   *wide = f.k_bits > 32;
@@ -1082,6 +1072,14 @@ namespace {
 std::mutex g_static_mutex;
 std::atomic<void*> g_static_ptr[64];  // device address of the array, per device ordinal (null until looked up)
 }  // namespace
+
+extern "C" int gb_set_row_routes(int dot_rows, int umma_min) {
+  GB_REQUIRE(dot_rows >= 0 && dot_rows <= kDotRowsMax, "per-row table GEMVs serve up to %d rows, got %d", kDotRowsMax, dot_rows);
+  GB_REQUIRE(umma_min >= 0 && umma_min <= 129, "tensor-core decode threshold %d outside [0, 129]", umma_min);
+  g_dot_rows_max.store(dot_rows == 0 ? 4 : dot_rows, std::memory_order_relaxed);
+  g_umma_min_rows.store(umma_min == 0 ? 17 : (umma_min < 2 ? 2 : umma_min), std::memory_order_relaxed);
+  return GB_OK;
+}
 
 extern "C" int gb_gemv_static(const void* x, int64_t M, const gb_weight* w, int act, int scale_rule,
                               void* y, void* stream) {

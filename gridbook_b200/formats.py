@@ -75,12 +75,6 @@ class CBFormat:
             scale_coding={"none": nat.SCALE_NONE, "v1": nat.SCALE_V1,
                           "v2": nat.SCALE_V2}[self.scale_coding])
 
-    def oracle_kwargs(self) -> dict:
-        """Keyword arguments of the CPU oracle's decode functions."""
-        return dict(k_bits=self.k, n_sub=self.n_sub, type_size=self.type_size,
-                    grid=self.grid, mode=self.mode,
-                    scale_coding=self.scale_coding if self.is_fp4 else "v1")
-
     @classmethod
     def from_scheme(cls, scheme: dict) -> "CBFormat":
         """Parse a reference scheme dict (gridbook/linear.py:206-231)."""

@@ -3,8 +3,6 @@
 1025-1264), dispatching to the sm_100a kernels through the C ABI."""
 from __future__ import annotations
 
-import os
-
 import torch
 
 from . import _native, codec, kernels
@@ -15,10 +13,6 @@ from .formats import CBFormat
 
 DECODE_MAX_M = 16          # the decode-batch kernels take up to sixteen rows
 MIDM_MAX_M = 128           # ... and the literal format's tensor-core decode kernel up to this many
-
-
-def midm_max_rows() -> int:
-    return min(int(os.environ.get("GRIDBOOK_B200_MIDM_MAX_M", MIDM_MAX_M)), kernels.ROW_BATCH_MAX_M)
 
 
 @register_weight_loader_v2_supported_method
@@ -43,6 +37,7 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         # view of the layer on the block-scaled tensor cores; "bf16" = the decode contract kept
         # (bucketed bf16 rows x bf16(value * scale)) on the bf16 tensor cores
         self.prefill_route = "nvfp4"
+        self.midm_max_rows = MIDM_MAX_M      # rows up to which the literal format decodes in the main loop
 
     # ------------------------------------------------------------------ parameters
     def create_weights(self, layer, input_size_per_partition, output_partition_sizes, input_size,
@@ -140,7 +135,7 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
             outs = kernels.gemv_tab(x2, [w], layer._cb_slots, act=self.fmt.grid, scale_rule=ops.ACT_SCALE_RULE)
             if outs is not None:
                 return outs[0].reshape(*x.shape[:-1], N)
-        if M <= DECODE_MAX_M or (M <= midm_max_rows() and kernels.row_batch_kernel_applies(w)):
+        if M <= DECODE_MAX_M or (M <= min(self.midm_max_rows, kernels.ROW_BATCH_MAX_M) and kernels.row_batch_kernel_applies(w)):
             # past sixteen rows: the literal format's tensor-core decode kernel, no decoded transient
             return kernels.gemv(x2, w, act=self.fmt.grid, scale_rule=ops.ACT_SCALE_RULE,
                                 workspace=layer._cb_workspace).reshape(*x.shape[:-1], N)

@@ -3,7 +3,6 @@
 routing, grouped codebook GEMV with fused SwiGLU, top-k weighted combine."""
 from __future__ import annotations
 
-import os
 import sys
 
 import torch
@@ -14,25 +13,19 @@ from ._vllm_compat import FusedMoEMethodBase
 from .formats import CBFormat
 
 
+# Route thresholds, in routed pairs (per expert where it says so).  They are crossovers measured on
+# one B200 with 128 experts, hidden 2048, intermediate 768 (literal fp4 format); every method
+# instance carries its own copy (attributes of the same lower-case names) that a caller may set
+# for another shape.
 PAIR_KERNEL_MAX_PAIRS = 768       # routed pairs up to which every pair runs as its own table GEMV
 FUSED_BUCKET_MAX_PAIRS = 32       # routed pairs up to which the grouped kernel buckets its own rows
 # From this many routed pairs per expert (on average) the routed layer decodes each stack once
 # and runs grouped tensor-core GEMMs instead of the decode kernel's 16-row passes.
 PREFILL_MIN_PAIRS_PER_EXPERT = 104
-
-
 # Between the two: from this many routed pairs per expert on, the rows are sorted by expert and
 # every (expert, 128-row tile) decodes its weights once into shared memory for a tensor-core MMA
 # (literal fp4 stacks only); below it the decode kernel's 16-row passes are faster.
 SORTED_MIN_PAIRS_PER_EXPERT = 18
-
-
-def sorted_min_pairs_per_expert() -> int:
-    return int(os.environ.get("GRIDBOOK_B200_MOE_SORTED_MIN", SORTED_MIN_PAIRS_PER_EXPERT))
-
-
-def prefill_min_pairs_per_expert() -> int:
-    return int(os.environ.get("GRIDBOOK_B200_MOE_PREFILL_MIN", PREFILL_MIN_PAIRS_PER_EXPERT))
 
 
 def _row_bytes(in_features: int, type_size: int) -> int:
@@ -56,6 +49,9 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         self.fmt2 = CBFormat.from_scheme(self.scheme_down)
         self.is_fp4 = self.fmt13.is_fp4
         self.k, self.n_sub, self.type_size = self.fmt13.k, self.fmt13.n_sub, self.fmt13.type_size
+        self.pair_kernel_max_pairs = PAIR_KERNEL_MAX_PAIRS
+        self.sorted_min_pairs_per_expert = SORTED_MIN_PAIRS_PER_EXPERT
+        self.prefill_min_pairs_per_expert = PREFILL_MIN_PAIRS_PER_EXPERT
 
     # ------------------------------------------------------------------ parameters
     def create_weights(self, layer, num_experts: int, hidden_size: int,
@@ -236,13 +232,13 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
             return torch.empty_like(x)
         x2 = x.reshape(T, -1).to(torch.bfloat16).contiguous()
         ids = topk_ids.to(torch.int32).contiguous()
-        if T * topk >= prefill_min_pairs_per_expert() * layer._cb_E:
+        if T * topk >= self.prefill_min_pairs_per_expert * layer._cb_E:
             return self._apply_prefill(layer, x2, topk_weights, ids, rule).to(x.dtype).reshape(x.shape)
-        if T * topk >= sorted_min_pairs_per_expert() * layer._cb_E:
+        if T * topk >= self.sorted_min_pairs_per_expert * layer._cb_E:
             out = self._apply_sorted(layer, x2, topk_weights, ids, rule)
             if out is not None:
                 return out.to(x.dtype).reshape(x.shape)
-        if T * topk <= PAIR_KERNEL_MAX_PAIRS and self.fmt13.is_fp4 and self.fmt2.is_fp4:
+        if T * topk <= self.pair_kernel_max_pairs and self.fmt13.is_fp4 and self.fmt2.is_fp4:
             out = self._apply_pairs(layer, x2, topk_weights, ids, rule)
             if out is not None:
                 layer._cb_route = "per-pair table kernel"

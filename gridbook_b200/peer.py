@@ -293,7 +293,8 @@ class PeerExpertParallelMoE(torch.nn.Module):
         b13 = kernels.fp4_act_qdq if method.fmt13.is_fp4 else kernels.fp8_act_qdq
         b2 = kernels.fp4_act_qdq if method.fmt2.is_fp4 else kernels.fp8_act_qdq
         ids = topk_ids.to(torch.int32).contiguous()
-        from .moe import FUSED_BUCKET_MAX_PAIRS, PAIR_KERNEL_MAX_PAIRS
+        from .moe import FUSED_BUCKET_MAX_PAIRS
+        PAIR_KERNEL_MAX_PAIRS = method.pair_kernel_max_pairs
         pairs_all = world * T * topk
         # small batches of the literal format: every pair is its own table GEMV (bucket fused)
         # (pairs of other ranks' experts cost a CTA that leaves at once; bound those too)
@@ -330,9 +331,8 @@ class PeerExpertParallelMoE(torch.nn.Module):
                 raise NativeKernelUnavailableError(
                     "per-pair table MLP refused a format the layer was built for")
             done = True
-        from .moe import sorted_min_pairs_per_expert
         if (not done and self._sorted_ok and method.fmt2.is_fp4
-                and pairs_all >= sorted_min_pairs_per_expert() * self.E):
+                and pairs_all >= method.sorted_min_pairs_per_expert * self.E):
             # many rows per local expert: sort them, decode every (expert, 128-row tile) in shared
             # memory and multiply on the tensor cores; the down projection stores each row into its
             # home rank's buffer

@@ -131,6 +131,12 @@ GB_API int64_t gb_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K);
 GB_API int gb_gemv(const void* x_bf16, int64_t M, const gb_weight* w, int act, int scale_rule,
             void* y_bf16, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Row counts at which gb_gemv changes kernel for the literal format: up to `dot_rows` rows run one
+ * inner-product-table GEMV per row (default 4, at most 8), from `umma_min` rows on the tensor-core
+ * decode kernel (default 17).  0 restores a default.  Process-wide; for tests and tuning.  No
+ * counterpart in the reference, whose lane selection is a set of environment flags. */
+GB_API int gb_set_row_routes(int dot_rows, int umma_min);
+
 /* Same computation as gb_gemv for callers that are not allowed to allocate device memory
  * and have no workspace to hand over: a runtime that has already given every byte of the
  * device to its own pools, a serving loop whose allocator is frozen once graphs are being

@@ -3,6 +3,7 @@ import numpy as np
 import torch
 
 from oracle import cb_oracle as O
+from oracle import oracle_kwargs
 
 
 def bits_of(t: torch.Tensor) -> np.ndarray:
@@ -19,7 +20,7 @@ def oracle_weight(d):
     if off is None:
         off = np.zeros(d["N"], np.int32)
     return O.reconstruct_weight(d["qw"], d["cb"], off, N=d["N"], K=d["K"], compose=d.get("compose"),
-                                weight_scale=d.get("weight_scale"), **fmt.oracle_kwargs())
+                                weight_scale=d.get("weight_scale"), **oracle_kwargs(fmt))
 
 
 def oracle_linear(x, d, bucket=True, scale_rule="recip"):
@@ -30,7 +31,7 @@ def oracle_linear(x, d, bucket=True, scale_rule="recip"):
     xq = O.act_bucket(x, fmt.grid, scale_rule) if bucket else x
     return O.cb_linear(xq, d["qw"], d["cb"], off, N=d["N"], K=d["K"], compose=d.get("compose"),
                        weight_scale=d.get("weight_scale"), global_scale=d.get("global_scale"),
-                       **fmt.oracle_kwargs())
+                       **oracle_kwargs(fmt))
 
 
 def assert_close_bf16(got: np.ndarray, ref: np.ndarray, tag: str, ulps: float = 2.0, rel_l2: float = 1e-3,

@@ -8,6 +8,7 @@ import pytest
 import torch
 
 from oracle import cb_oracle as O
+from oracle import oracle_kwargs
 from tests.helpers import assert_close_bf16, f32_of, oracle_linear
 
 pytestmark = pytest.mark.gpu
@@ -88,7 +89,7 @@ def test_directory_round_trip(tmp_path):
     xm = synth.make_activations(T, hidden, seed=2)
     out = moe(synth.bf16_tensor(xm, dev), torch.from_numpy(tw).to(dev), torch.from_numpy(ids).to(dev))
     ref = O.moe_loop_chain(xm, ids, tw, w13d, w2d, E=E, hidden=hidden, inter=inter,
-                           fmt13=FP8_CB_K32.oracle_kwargs(), fmt2=fp4.oracle_kwargs(), scale_rule="recip")
+                           fmt13=oracle_kwargs(FP8_CB_K32), fmt2=oracle_kwargs(fp4), scale_rule="recip")
     got = f32_of(out)
     assert np.linalg.norm(got - ref) / np.linalg.norm(ref) <= 1e-2
     assert np.abs(got - ref).max() <= 2e-2 * np.abs(ref).max()

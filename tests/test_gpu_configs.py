@@ -14,6 +14,7 @@ import pytest
 import torch
 
 from oracle import c_oracle as C
+from oracle import oracle_kwargs
 from oracle import cb_oracle as O
 from tests.helpers import assert_close_bf16, f32_of, nvfp4_dequant, nvfp4_quantize_rows_ref
 
@@ -44,7 +45,7 @@ def _c_linear(xq, d, rows=None, expert=None):
         qw = np.ascontiguousarray(qw[rows])
         ws = None if ws is None else np.ascontiguousarray(ws[rows])
     return C.linear(xq, qw, d["cb"], None, N=qw.shape[0], K=d["K"], compose=d.get("compose"), weight_scale=ws,
-                    global_scale=d.get("global_scale"), **fmt.oracle_kwargs())
+                    global_scale=d.get("global_scale"), **oracle_kwargs(fmt))
 
 
 def c_loop_chain(x, ids, tw, w13, w2, experts, hidden, inter, scale_rule="recip"):
@@ -189,8 +190,8 @@ def test_per_role_routed_codebooks(dev, name, T):
                                             np.full(inter, fmt.codebook_elems(), np.int32)])
     ids, tw = synth.make_routing(T, E, topk, seed=T)
     x = synth.make_activations(T, hidden, seed=T)
-    ref = O.moe_loop_chain(x, ids, tw, w13d, w2d, E=E, hidden=hidden, inter=inter, fmt13=fmt.oracle_kwargs(),
-                           fmt2=fmt.oracle_kwargs(), scale_rule="recip")
+    ref = O.moe_loop_chain(x, ids, tw, w13d, w2d, E=E, hidden=hidden, inter=inter, fmt13=oracle_kwargs(fmt),
+                           fmt2=oracle_kwargs(fmt), scale_rule="recip")
     moe = CBMoE(fmt, fmt, E, hidden, inter, [_tables(fmt, gate_book), _tables(fmt, up_book)], _tables(fmt, w2d["cb"]))
     s13 = None if fmt.is_fp4 else torch.from_numpy(w13d["scale"])
     s2 = None if fmt.is_fp4 else torch.from_numpy(w2d["scale"])

@@ -5,6 +5,7 @@ import pytest
 import torch
 
 from oracle import cb_oracle as O
+from oracle import oracle_kwargs
 from tests.helpers import bits_of, oracle_weight
 
 pytestmark = pytest.mark.gpu
@@ -57,7 +58,7 @@ def test_expand_bit_exact(dev, idx):
         assert np.array_equal(bits_of(part), O.f32_to_bf16_bits(ref[5:16]))
         packed, sf = kernels.expand_fp4_nvfp4(w)
         rp, rs = O.decode_nvfp4_tile(d["qw"], d["cb"], d["cb_row_offset"], N=N, K=K, compose=d["compose"],
-                                     **{k: v for k, v in fmt.oracle_kwargs().items() if k != "grid"})
+                                     **{k: v for k, v in oracle_kwargs(fmt).items() if k != "grid"})
         assert np.array_equal(packed.cpu().numpy(), rp)
         assert np.array_equal(sf.cpu().numpy(), rs)
         _, sfs = kernels.expand_fp4_nvfp4(w, swizzled=True)

@@ -8,6 +8,7 @@ import pytest
 import torch
 
 from oracle import c_oracle as C
+from oracle import oracle_kwargs
 from oracle import cb_oracle as O
 from tests.helpers import assert_close_bf16, f32_of
 
@@ -30,7 +31,7 @@ def _c_linear(x, d, scale_rule="recip"):
     fmt = d["fmt"]
     xq = C.act_qdq(x, fmt.grid, scale_rule)
     return C.linear(xq, d["qw"], d["cb"], None, N=d["N"], K=d["K"], compose=d.get("compose"),
-                    weight_scale=d.get("weight_scale"), global_scale=d.get("global_scale"), **fmt.oracle_kwargs())
+                    weight_scale=d.get("weight_scale"), global_scale=d.get("global_scale"), **oracle_kwargs(fmt))
 
 
 @pytest.mark.parametrize("N,K,M", [(4096, 4096, 1),            # configuration 0
@@ -73,8 +74,8 @@ def test_routed_layer_full_size_against_loop_chain(dev):
     w13d, w2d = synth.make_moe(fmt, fmt, E, hidden, inter, seed=2)
     ids, tw = synth.make_routing(T, E, topk, seed=2)
     x = synth.make_activations(T, hidden, seed=2)
-    ref = O.moe_loop_chain(x, ids, tw, w13d, w2d, E=E, hidden=hidden, inter=inter, fmt13=fmt.oracle_kwargs(),
-                           fmt2=fmt.oracle_kwargs(), scale_rule="recip")
+    ref = O.moe_loop_chain(x, ids, tw, w13d, w2d, E=E, hidden=hidden, inter=inter, fmt13=oracle_kwargs(fmt),
+                           fmt2=oracle_kwargs(fmt), scale_rule="recip")
     w13, w2 = synth.to_device_weight(w13d, dev), synth.to_device_weight(w2d, dev)
     xd, idd = synth.bf16_tensor(x, dev), torch.from_numpy(ids).to(dev)
     twd = torch.from_numpy(tw).to(dev)

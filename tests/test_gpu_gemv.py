@@ -5,6 +5,7 @@ import pytest
 import torch
 
 from oracle import cb_oracle as O
+from oracle import oracle_kwargs
 from tests.helpers import assert_close_bf16, assert_linear_close, f32_of, oracle_linear
 
 pytestmark = pytest.mark.gpu
@@ -170,8 +171,8 @@ def _moe_case(dev, fmt13, fmt2, E, hidden, inter, T, topk, seed):
     w13d, w2d = synth.make_moe(fmt13, fmt2, E, hidden, inter, seed=seed)
     ids, tw = synth.make_routing(T, E, topk, seed=seed)
     x = synth.make_activations(T, hidden, seed=seed)
-    f13 = fmt13.oracle_kwargs()
-    f2 = fmt2.oracle_kwargs()
+    f13 = oracle_kwargs(fmt13)
+    f2 = oracle_kwargs(fmt2)
     ref = O.moe_loop_chain(x, ids, tw, w13d, w2d, E=E, hidden=hidden, inter=inter, fmt13=f13, fmt2=f2,
                            scale_rule="recip")
     w13 = synth.to_device_weight(w13d, dev)
@@ -245,7 +246,7 @@ def test_moe_per_pair_table_kernel_matches_grouped_kernel(dev, T, inter):
     out = kernels.moe_combine(y, torch.from_numpy(tw).to(dev), T, topk, topk_ids=idd, E=E, round_weights=True)
     keep = ids >= 0
     ref = O.moe_loop_chain(x, np.where(keep, ids, 0), np.where(keep, tw, 0.0).astype(np.float32), w13d, w2d, E=E,
-                           hidden=hidden, inter=inter, fmt13=fmt.oracle_kwargs(), fmt2=fmt.oracle_kwargs(),
+                           hidden=hidden, inter=inter, fmt13=oracle_kwargs(fmt), fmt2=oracle_kwargs(fmt),
                            scale_rule="recip")
     got = f32_of(out)
     rel = np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-9)
@@ -298,13 +299,14 @@ def test_literal_single_row_table_kernel(dev, N, K):
 
 @pytest.mark.parametrize("N,K,M", [(256, 1024, 2), (384, 2048, 16), (1000, 2304, 5), (640, 1536, 100),
                                    (2048, 5120, 9), (5120, 4352, 128), (300, 1280, 33)])
-def test_literal_row_batch_tensor_core_decode_kernel(dev, monkeypatch, N, K, M):
+def test_literal_row_batch_tensor_core_decode_kernel(dev, request, N, K, M):
     """2..128 rows of the literal format take the kernel that decodes into shared memory and runs
     tcgen05 MMAs with the weights on the M side: ragged row counts on both sides, a last raw stage
     of one to three superblocks, one or several K slices, padded row stride, bucket applied by the
     call or beforehand, zero / subnormal / negative scale bytes."""
     from gridbook_b200 import _native, kernels, synth
-    monkeypatch.setenv("GRIDBOOK_B200_UMMA_MIN_M", "2")       # by default it serves 17 rows and more
+    _native.set_row_routes(umma_min=2)                        # by default it serves 17 rows and more
+    request.addfinalizer(lambda: _native.set_row_routes())
     fmt = _fmt("lit")
     d = synth.make_linear(fmt, N, K, seed=N + K + M, global_scale=1.0 / 448.0)
     qw = d["qw"].reshape(N, K // 256, 48)

@@ -7,6 +7,7 @@ import pytest
 import torch
 
 from oracle import c_oracle as C
+from oracle import oracle_kwargs
 from tests.helpers import assert_close_bf16, f32_of, oracle_linear
 
 pytestmark = pytest.mark.gpu
@@ -28,7 +29,7 @@ def _c_linear(x, d):
     fmt = d["fmt"]
     xq = C.act_qdq(x, fmt.grid, "recip")
     return C.linear(xq, d["qw"], d["cb"], None, N=d["N"], K=d["K"], compose=None, weight_scale=None,
-                    global_scale=d.get("global_scale"), **fmt.oracle_kwargs())
+                    global_scale=d.get("global_scale"), **oracle_kwargs(fmt))
 
 
 @pytest.mark.parametrize("N,K", [(64, 256), (200, 1024), (264, 1280), (1000, 2816), (6144, 5120), (5120, 6144),

@@ -7,6 +7,7 @@ import pytest
 import torch
 
 from oracle import cb_oracle as O
+from oracle import oracle_kwargs
 from tests.helpers import f32_of
 
 pytestmark = pytest.mark.gpu
@@ -112,7 +113,6 @@ def test_moe_method_prefill_route_matches_loop_chain(dev, monkeypatch, f13, f2, 
     from gridbook_b200 import synth
     from gridbook_b200.moe import CBMoE
     from tests.test_gpu_plugin import _formats, _tables
-    monkeypatch.setenv("GRIDBOOK_B200_MOE_PREFILL_MIN", "1")
     fmt13, fmt2 = _formats()[f13], _formats()[f2]
     E, hidden, inter, topk = 8, 512, 256, 2
     w13d, w2d = synth.make_moe(fmt13, fmt2, E, hidden, inter, seed=T)
@@ -122,11 +122,12 @@ def test_moe_method_prefill_route_matches_loop_chain(dev, monkeypatch, f13, f2, 
     ids_ref = np.where(ids < 0, 0, ids)
     tw_ref = np.where(ids < 0, 0.0, tw).astype(np.float32)
     ref = O.moe_loop_chain(x, ids_ref, tw_ref, w13d, w2d, E=E, hidden=hidden, inter=inter,
-                           fmt13=fmt13.oracle_kwargs(), fmt2=fmt2.oracle_kwargs(), scale_rule="recip")
+                           fmt13=oracle_kwargs(fmt13), fmt2=oracle_kwargs(fmt2), scale_rule="recip")
     moe = CBMoE(fmt13, fmt2, E, hidden, inter, _tables(fmt13, w13d["cb"]), _tables(fmt2, w2d["cb"]))
     moe.load(torch.from_numpy(w13d["qw"]), torch.from_numpy(w2d["qw"]),
              None if w13d["scale"] is None else torch.from_numpy(w13d["scale"]),
              None if w2d["scale"] is None else torch.from_numpy(w2d["scale"]), dev)
+    moe.method.prefill_min_pairs_per_expert = 1            # the route's threshold is an attribute of the method
     got = f32_of(moe(synth.bf16_tensor(x, dev), torch.from_numpy(tw).to(dev), torch.from_numpy(ids).to(dev)))
     assert "grouped prefill" in moe._cb_route
     rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
@@ -142,8 +143,6 @@ def test_moe_method_sorted_rows_route_matches_loop_chain(dev, monkeypatch, T):
     from gridbook_b200 import _native, synth
     from gridbook_b200.moe import CBMoE
     from tests.test_gpu_plugin import _formats, _tables
-    monkeypatch.setenv("GRIDBOOK_B200_MOE_SORTED_MIN", "1")
-    monkeypatch.setenv("GRIDBOOK_B200_MOE_PREFILL_MIN", "1000000")
     fmt = _formats()["lit"]
     E, hidden, inter, topk = 8, 1024, 512, 2
     w13d, w2d = synth.make_moe(fmt, fmt, E, hidden, inter, seed=T)
@@ -153,9 +152,11 @@ def test_moe_method_sorted_rows_route_matches_loop_chain(dev, monkeypatch, T):
     ids_ref = np.where(ids < 0, 0, ids)
     tw_ref = np.where(ids < 0, 0.0, tw).astype(np.float32)
     ref = O.moe_loop_chain(x, ids_ref, tw_ref, w13d, w2d, E=E, hidden=hidden, inter=inter,
-                           fmt13=fmt.oracle_kwargs(), fmt2=fmt.oracle_kwargs(), scale_rule="recip")
+                           fmt13=oracle_kwargs(fmt), fmt2=oracle_kwargs(fmt), scale_rule="recip")
     moe = CBMoE(fmt, fmt, E, hidden, inter, _tables(fmt, w13d["cb"]), _tables(fmt, w2d["cb"]))
     moe.load(torch.from_numpy(w13d["qw"]), torch.from_numpy(w2d["qw"]), None, None, dev)
+    moe.method.sorted_min_pairs_per_expert = 1              # the routes' thresholds are attributes of the method
+    moe.method.prefill_min_pairs_per_expert = 1000000
     got = f32_of(moe(synth.bf16_tensor(x, dev), torch.from_numpy(tw).to(dev), torch.from_numpy(ids).to(dev)))
     torch.cuda.synchronize()
     assert _native.device_status(0) == 0

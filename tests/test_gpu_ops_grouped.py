@@ -7,6 +7,7 @@ import pytest
 import torch
 
 from oracle import cb_oracle as O
+from oracle import oracle_kwargs
 from tests.helpers import assert_close_bf16, bits_of, f32_of
 
 pytestmark = pytest.mark.gpu
@@ -73,7 +74,7 @@ def test_cb_moe_persistent_b_prefill_fp4(dev, name):
         if counts[e]:
             ref[starts[e]:starts[e + 1]] = O.cb_linear(aq[starts[e]:starts[e + 1]], w13["qw"][e], w13["cb"],
                                                        np.zeros(N, np.int32), N=N, K=K, compose=w13["compose"],
-                                                       **fmt.oracle_kwargs())
+                                                       **oracle_kwargs(fmt))
     a_d = torch.from_numpy(aq).to(torch.bfloat16).to(dev)
     ends_d = torch.from_numpy(ends).to(dev)
     if name == "lit":
@@ -92,7 +93,7 @@ def test_cb_moe_persistent_b_prefill_fp4(dev, name):
     flat = w.qw.reshape(E * N, -1)
     tile = P_.cb_moe_persistent_b_decode(flat, w.codebook, compose, N + 8, 100, K, fmt.k, fmt.type_size)
     want = O.reconstruct_weight(w13["qw"][1], w13["cb"], np.zeros(N, np.int32), N=N, K=K, compose=w13["compose"],
-                                **fmt.oracle_kwargs())[8:108]
+                                **oracle_kwargs(fmt))[8:108]
     assert np.array_equal(bits_of(tile), O.f32_to_bf16_bits(want))
 
 
@@ -115,7 +116,7 @@ def test_cb_moe_persistent_b_prefill_fp8(dev):
         if counts[e]:
             ref[starts[e]:starts[e + 1]] = O.cb_linear(aq[starts[e]:starts[e + 1]], w13["qw"][e], w13["cb"],
                                                        np.zeros(N, np.int32), N=N, K=K, weight_scale=w13["scale"][e],
-                                                       **fmt.oracle_kwargs())
+                                                       **oracle_kwargs(fmt))
     out = torch.zeros((a.shape[0], N), dtype=torch.bfloat16, device=dev)
     P_.cb_moe_persistent_b_prefill_fp8(out, torch.from_numpy(aq).to(torch.bfloat16).to(dev), w.qw, lut_f32, scale,
                                        torch.from_numpy(ends).to(dev), fmt.k, fmt.type_size, 0)
@@ -123,5 +124,5 @@ def test_cb_moe_persistent_b_prefill_fp8(dev):
     tile = P_.cb_moe_persistent_b_decode_fp8(w.qw.reshape(E * N, -1), lut_f32, scale.reshape(-1), 2 * N + 5, 64, K,
                                              fmt.k, fmt.type_size)
     want = O.reconstruct_weight(w13["qw"][2], w13["cb"], np.zeros(N, np.int32), N=N, K=K,
-                                weight_scale=w13["scale"][2], **fmt.oracle_kwargs())[5:69]
+                                weight_scale=w13["scale"][2], **oracle_kwargs(fmt))[5:69]
     assert np.array_equal(bits_of(tile), O.f32_to_bf16_bits(want))

@@ -5,6 +5,7 @@ import pytest
 import torch
 
 from oracle import cb_oracle as O
+from oracle import oracle_kwargs
 from tests.helpers import assert_close_bf16, bits_of, f32_of, oracle_linear, oracle_weight
 
 pytestmark = pytest.mark.gpu
@@ -120,7 +121,7 @@ def test_reference_signature_moe_ops(dev):
     for p in range(T * topk):
         e, t = int(ids_sorted.reshape(-1)[p]), p // topk
         ref = O.cb_linear(xq[t:t + 1], w13d["qw"][e], w13d["cb"], np.zeros(rows, np.int32), N=rows, K=hidden,
-                          compose=w13d["compose"], **fmt.oracle_kwargs())
+                          compose=w13d["compose"], **oracle_kwargs(fmt))
         assert_close_bf16(f32_of(y[p:p + 1]), ref, f"pair {p}")
     pw = torch.from_numpy(tw.reshape(-1)).to(dev)
     out = P.cb_moe_combine(y, pw, torch.arange(T + 1, dtype=torch.int32, device=dev) * topk, T)
@@ -146,7 +147,7 @@ def test_moe_method_matches_loop_chain(dev, f13, f2, T):
     ids_ref = np.where(ids < 0, 0, ids)
     tw_ref = np.where(ids < 0, 0.0, tw).astype(np.float32)
     ref = O.moe_loop_chain(x, ids_ref, tw_ref, w13d, w2d, E=E, hidden=hidden, inter=inter,
-                           fmt13=fmt13.oracle_kwargs(), fmt2=fmt2.oracle_kwargs(), scale_rule="recip")
+                           fmt13=oracle_kwargs(fmt13), fmt2=oracle_kwargs(fmt2), scale_rule="recip")
     moe = CBMoE(fmt13, fmt2, E, hidden, inter, _tables(fmt13, w13d["cb"]), _tables(fmt2, w2d["cb"]))
     moe.load(torch.from_numpy(w13d["qw"]), torch.from_numpy(w2d["qw"]),
              None if w13d["scale"] is None else torch.from_numpy(w13d["scale"]),

@@ -6,6 +6,7 @@ import pytest
 from gridbook_b200 import synth
 from gridbook_b200.formats import CBFormat
 from oracle import c_oracle as C
+from oracle import oracle_kwargs
 from oracle import cb_oracle as O
 
 
@@ -53,7 +54,7 @@ def test_c_activation_fixture(golden):
 def test_c_matches_numpy_on_synthetic(fmt):
     N, K = 50, 768
     d = synth.make_linear(fmt, N, K, seed=3, n_books=2, super_span=None)
-    kw = dict(N=N, K=K, compose=d["compose"], weight_scale=d["weight_scale"], **fmt.oracle_kwargs())
+    kw = dict(N=N, K=K, compose=d["compose"], weight_scale=d["weight_scale"], **oracle_kwargs(fmt))
     wn = O.reconstruct_weight(d["qw"], d["cb"], d["cb_row_offset"], **kw)
     wc = C.reconstruct(d["qw"], d["cb"], d["cb_row_offset"], **kw)
     assert np.array_equal(wn.view(np.uint32), wc.view(np.uint32))
