@@ -193,6 +193,10 @@ class PeerShardedCBLinear(torch.nn.Module):
         self.roles = role_slices(self.partition_sizes, world)
         self._layout = None
         self._fused_ok = None
+        # one activation row: "tab" = the shard's one-launch table kernel, then the flag-in-data
+        # all-gather; "fused" = the two-launch table kernel whose second launch sums the K slices
+        # and exchanges the shards
+        self.single_row = "tab" if getattr(local, "_cb_slots", None) is not None else "fused"
         if len(self.roles) > 4:
             raise ValueError("at most four roles per fused module")
 
@@ -231,7 +235,7 @@ class PeerShardedCBLinear(torch.nn.Module):
         return peers.arena.tensor(self.out_off, (1, self.N), torch.bfloat16)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if x.numel() == x.shape[-1] and x.dtype is torch.bfloat16:        # a single activation row
+        if x.numel() == x.shape[-1] and x.dtype is torch.bfloat16 and self.single_row == "fused":
             full = self._fused(x)
             if full is not None:
                 return full.reshape(*x.shape[:-1], self.N)
