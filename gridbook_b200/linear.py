@@ -105,8 +105,9 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         layer._cb_N, layer._cb_K = N, K
         layer._cb_workspace = torch.empty(
             _native.load().gb_gemv_workspace_bytes(DECODE_MAX_M, N, K), dtype=torch.uint8, device=dev)
-        from .ops import register_cb_layer
+        from .ops import register_cb_layer, warn_if_capture_sizes_exceed_the_decode_gates
         layer._cb_layer_id = register_cb_layer(self, layer)
+        warn_if_capture_sizes_exceed_the_decode_gates()
         layer._cb_route = {"kernel": "gemv_kernel", "format": str(self.fmt), "N": N, "K": K}
         # one activation row of the literal format: the one-launch table kernel and its armed slots
         layer._cb_slots = (kernels.new_tab_slots([layer._cb_weight])

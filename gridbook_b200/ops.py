@@ -377,6 +377,35 @@ _LAYER_IDS = itertools.count(1)
 _LAYER_REGISTRY: dict[int, tuple] = {}
 
 
+_CAPTURE_NOTE_DONE: list[bool] = []
+
+
+def warn_if_capture_sizes_exceed_the_decode_gates() -> None:
+    """The reference warns here when the engine's cudagraph_capture_sizes reach past its decode
+    gates, because its prefill arms read routing counts on the host and cannot be captured
+    (gridbook/ops.py:644-683).  No arm of this package reads a device value on the host - the
+    routing, the segment offsets and the route choice all stay on the device or depend on shapes
+    only - so every size is capturable and there is nothing to warn about.  What is still worth
+    one line, once per process: sizes past the sixteen rows the per-layer workspace is laid out
+    for allocate their transient tiles inside the capture (from the graph's private pool), which
+    is legal but costs memory per captured size."""
+    if _CAPTURE_NOTE_DONE:
+        return
+    _CAPTURE_NOTE_DONE.append(True)
+    try:
+        from vllm.config import get_current_vllm_config
+        compilation = get_current_vllm_config().compilation_config
+        sizes = [int(s) for s in (getattr(compilation, "cudagraph_capture_sizes", None) or ())]
+    except Exception:  # advisory only; never break a load
+        return
+    over = sorted(s for s in sizes if s > 16)
+    if over:
+        import sys
+        print(f"[prismaquant-cb] note: cudagraph_capture_sizes {over} are past the decode batches; these captures "
+              "hold a decoded weight tile each (prefill routes). All routes are capture-safe.", file=sys.stderr,
+              flush=True)
+
+
 def register_cb_layer(method, layer) -> int:
     layer_id = next(_LAYER_IDS)
 
