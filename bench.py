@@ -740,13 +740,15 @@ def bench_prefill(args, device):
     headline = None
     for name, parts, K in PROJECTIONS:
         N = sum(parts)
+        if args.prefill_shape and name != args.prefill_shape:
+            continue
         for variant in ("literal", "fp8lit"):
             fmt, gscale = get_format(variant)
             lin = CBLinear(fmt, K, list(parts), [synth.codebook_tables(fmt, 3)], global_scale=gscale)
             ws = None if fmt.is_fp4 else (torch.rand(N, generator=gen, device=device) + 0.5) * 0.02
             lin.load(synth.make_packed_device(fmt, N, K, gen, device), ws, device)
             w = lin._cb_weight
-            for M in (2048, 8192):
+            for M in ((args.prefill_m,) if args.prefill_m else (2048, 8192)):
                 x = torch.randn(M, K, generator=gen, device=device).to(torch.bfloat16)
                 flops = 2.0 * M * N * K
                 lin(x)
@@ -770,7 +772,7 @@ def bench_prefill(args, device):
                     ms_b = timed_ms(lambda: lin(x), 3, sync)
                     lin.method.prefill_route = "nvfp4"
                     entry["bf16_route_tflops"] = round(flops / ms_b / 1e9, 1)
-                    if name == "gate_up_proj" and M == 2048:
+                    if name == "gate_up_proj" and M == 2048 or headline is None:
                         headline = {"bound": "tensor", "achieved": round(tf, 1), "peak": NOMINAL_TFLOPS["fp4"],
                                     "unit": "TFLOP/s", "frac": round(tf / NOMINAL_TFLOPS["fp4"], 4),
                                     "peak_kind": "fp4 dense, nominal (no measured fp4 figure on this pool)",
@@ -988,6 +990,9 @@ def main():
     ap.add_argument("--no-formats", action="store_true", help="skip the M = 1 stack in the reference-native formats")
     ap.add_argument("--no-nccl", action="store_true", help="N > 1: skip the NCCL formulation's figures")
     ap.add_argument("--no-msweep", action="store_true", help="skip the M = 4 / 16 / 64 legs of the dense stack")
+    ap.add_argument("--prefill-shape", default=None, choices=[n for n, _, _ in PROJECTIONS],
+                    help="prefill leg: this projection only (small profiling captures)")
+    ap.add_argument("--prefill-m", type=int, default=0, help="prefill leg: this row count only")
     ap.add_argument("--only", default=None, choices=[n for n, _, _ in PROJECTIONS],
                     help="restrict the stack to one projection (small profiling captures)")
     args = ap.parse_args()
