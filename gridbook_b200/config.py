@@ -238,8 +238,23 @@ class PrismaQuantConfig(QuantizationConfig):
         return up, down
 
     # ---- dispatch (gridbook/config.py:1422-1571) --------------------------------------
+    def _require_single_gpu_engine(self) -> None:
+        """The engine-facing methods serve tensor-parallel size 1 only, like the reference
+        (gridbook/config.py:565-576): its loaders never shard the packed rows.  Sharding lives
+        beside the engine (peer.py / parallel.py wrap the stand-alone modules)."""
+        if getattr(self, "_tp_checked", False):
+            return
+        world = _engine_tensor_parallel_world_size()
+        if world is None:
+            return
+        if world != 1:
+            raise ValueError("[prismaquant] gridbook_b200's engine methods support tensor-parallel size 1 only; "
+                             f"the live vLLM worker reports TP={world}")
+        self._tp_checked = True
+
     def get_quant_method(self, layer, prefix: str):
         self._ensure_resolved()
+        self._require_single_gpu_engine()
         if any(prefix == ig or prefix.startswith(ig + ".") for ig in self.ignore):
             return _unquantized(layer)
         kind = type(layer).__name__
@@ -261,6 +276,19 @@ class PrismaQuantConfig(QuantizationConfig):
             return _unquantized(layer)
         from .linear import PrismaQuantCBLinearMethod
         return PrismaQuantCBLinearMethod(self, scheme, prefix)
+
+
+def _engine_tensor_parallel_world_size():
+    """TP world size of a live vLLM worker, None when no engine (or no initialised group) is there."""
+    if not HAVE_VLLM:
+        return None
+    try:
+        from vllm.distributed import parallel_state
+        if not parallel_state.model_parallel_is_initialized():
+            return None
+        return int(parallel_state.get_tensor_model_parallel_world_size())
+    except Exception:            # pragma: no cover - depends on the installed vLLM
+        return None
 
 
 def _unquantized(layer):

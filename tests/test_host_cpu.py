@@ -437,3 +437,23 @@ def test_per_role_routed_codebooks_resolve_and_conflicts_refuse():
     other_k = dict(groups, b={"targets": [f"{pre}.up_proj"], "scheme": dict(scheme("u"), k=28, type_size=112)})
     with pytest.raises(ValueError, match="differ in"):
         PrismaQuantConfig({"quant_method": "gridbook", "config_groups": other_k}).get_quant_method(FusedMoE(), pre)
+
+
+def test_engine_methods_refuse_a_tensor_parallel_world(monkeypatch):
+    """Like the reference (gridbook/config.py:565-576): the engine-facing methods serve TP = 1 only."""
+    from gridbook_b200 import config as C
+    v2 = {"grid": "fp4", "mode": "product", "k": 16, "n_sub": 2, "type_size": 73, "codebook_ref": ["a", "b"],
+          "scale_coding": {"kind": "two_tier"}}
+    raw = {"quant_method": "gridbook", "config_groups": {"g": {"targets": ["m.down_proj"], "scheme": v2}},
+           "_codebooks": {"a": torch.zeros(256, 4), "b": torch.zeros(256, 4)}}
+
+    class Linear(torch.nn.Module):
+        pass
+
+    monkeypatch.setattr(C, "_engine_tensor_parallel_world_size", lambda: 2)
+    with pytest.raises(ValueError, match="tensor-parallel size 1 only"):
+        C.PrismaQuantConfig(dict(raw)).get_quant_method(Linear(), "m.down_proj")
+    monkeypatch.setattr(C, "_engine_tensor_parallel_world_size", lambda: 1)
+    assert C.PrismaQuantConfig(dict(raw)).get_quant_method(Linear(), "m.down_proj") is not None
+    monkeypatch.setattr(C, "_engine_tensor_parallel_world_size", lambda: None)       # no engine: stand-alone use
+    assert C.PrismaQuantConfig(dict(raw)).get_quant_method(Linear(), "m.down_proj") is not None
