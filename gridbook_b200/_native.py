@@ -13,11 +13,11 @@ import threading
 
 import torch
 
-GB_ABI_VERSION = 2
+GB_ABI_VERSION = 3
 GEMM_BF16, GEMM_E4M3 = 0, 1
 
 REQUIRED_SYMBOLS = (
-    "gb_abi_version", "gb_last_error", "gb_prepare", "gb_device_status",
+    "gb_abi_version", "gb_last_error", "gb_prepare", "gb_device_status", "gb_gemv_row_batch_max",
     "gb_fp8_act_qdq", "gb_fp4_act_qdq",
     "gb_expand_fp8", "gb_expand_fp4_bf16", "gb_expand_fp4_nvfp4",
     "gb_gemv_workspace_bytes", "gb_gemv", "gb_gemv_static",
@@ -103,6 +103,8 @@ def _declare(lib) -> None:
     lib.gb_abi_version.restype = i32
     lib.gb_last_error.restype = ctypes.c_char_p
     lib.gb_prepare.argtypes = [i32]
+    lib.gb_gemv_row_batch_max.argtypes = [ctypes.POINTER(GbWeight)]
+    lib.gb_gemv_row_batch_max.restype = i32
     lib.gb_device_status.argtypes = [i32, ctypes.POINTER(ctypes.c_int)]
     lib.gb_fp8_act_qdq.argtypes = [vp, vp, i64, i64, i32, vp]
     lib.gb_fp4_act_qdq.argtypes = [vp, vp, i64, i64, i32, vp]

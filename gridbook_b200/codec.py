@@ -77,6 +77,22 @@ def pad_qweight(qw: torch.Tensor) -> torch.Tensor:
     return torch.nn.functional.pad(qw.contiguous(), (0, PAD_BYTES), value=0).contiguous()
 
 
+def pad_superblocks(qw: torch.Tensor, type_size: int, stride: int) -> torch.Tensor:
+    """Packed rows [..., n_sb * type_size] with every superblock moved to a `stride`-byte slot (zero
+    filled): the resident layout the tensor-core decode kernel needs for superblocks whose size is
+    not a multiple of 16 (tiled TMA cannot fetch 73-byte pieces).  Nothing is decoded: the index and
+    scale bytes are the shipped ones."""
+    if stride < type_size:
+        raise ValueError(f"stride {stride} is smaller than the superblock ({type_size} bytes)")
+    *lead, row_bytes = qw.shape
+    if row_bytes % type_size:
+        raise ValueError(f"row of {row_bytes} bytes is not a whole number of {type_size}-byte superblocks")
+    n_sb = row_bytes // type_size
+    out = torch.zeros((*lead, n_sb, stride), dtype=torch.uint8, device=qw.device)
+    out[..., :type_size] = qw.reshape(*lead, n_sb, type_size)
+    return out.reshape(*lead, n_sb * stride)
+
+
 def with_tail_slack(qw: torch.Tensor) -> torch.Tensor:
     """Same bytes in a buffer that stays readable for 16 bytes past the last row, which
     is what the kernels' aligned windows may touch."""

@@ -106,9 +106,11 @@ int gb_check_format(const gb_format& f, int64_t K) {
   } else {
     GB_REQUIRE(f.scale_coding == GB_SCALE_NONE, "fp8 grid carries no scale plane");
   }
-  GB_REQUIRE(f.type_size == 4 * f.k_bits + scale_bytes,
-             "type_size %d does not match 4*%d+%d for this grid/scale coding", f.type_size,
-             f.k_bits, scale_bytes);
+  // The superblock stride may exceed the packed bytes by up to 15 (padding after the scale plane,
+  // ignored by every kernel): a host that wants 16-byte superblocks pads once at load.
+  GB_REQUIRE(f.type_size >= 4 * f.k_bits + scale_bytes && f.type_size <= 4 * f.k_bits + scale_bytes + 15,
+             "type_size %d does not match 4*%d+%d (plus at most 15 padding bytes) for this grid/scale coding",
+             f.type_size, f.k_bits, scale_bytes);
   return GB_OK;
 }
 

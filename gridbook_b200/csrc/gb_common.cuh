@@ -73,11 +73,14 @@ unsigned long long gb_wait_limit_ns();
 // Swizzled (128-byte) operand map over a row-major [rows, K] matrix of 2- or 1-byte elements:
 // box = 128 bytes of K x box_rows rows, rows past the end read zero.
 int gb_tensor_map_operand(void* map_out, const void* base, int64_t rows, int64_t K, int elem_bytes, int box_rows);
-// 2..128 activation rows of the literal format: decode into shared memory, tcgen05 MMA with the
-// weights on the M side (gb_gemv_umma.cu); GB_EUNSUPPORTED when the format or layout is not its own.
+// 1..128 activation rows of the literal format, the two-tier k = 16 format with 80-byte superblocks
+// or the fp8 k = 32 format: decode into tensor memory, tcgen05 MMA with the weights on the M side
+// (gb_gemv_umma.cu); GB_EUNSUPPORTED when the format, layout or row count is not its own.
 int gb_gemv_umma(const void* x, int64_t M, const gb_weight* w, int act, int scale_rule, void* y, void* workspace,
                  int64_t workspace_bytes, void* stream);
 int64_t gb_gemv_umma_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int gb_gemv_umma_max_rows(const gb_weight* w);
+bool gb_gemv_umma_is_literal(const gb_weight* w);
 int gb_tensor_map_bytes_2d(void* map_out, const void* base, uint64_t inner_bytes, uint64_t rows,
                            uint64_t pitch_bytes, uint32_t box_bytes, uint32_t box_rows);
 // M = 1 literal-format linear by per-column inner-product tables (gb_gemv_dot.cu); GB_EUNSUPPORTED when

@@ -801,7 +801,7 @@ constexpr int kDotRowsMax = 8;      // most activation rows ever served by per-r
 // out of L2) beats expanding every weight; from seventeen rows on the tensor-core decode kernel
 // (flat in the row count: gate_up 86 us at 2..16 rows, 110 us at 128) passes the expanding one.
 // gb_set_row_routes moves them (a process-wide setting, meant for tests and for tuning).
-std::atomic<int> g_dot_rows_max{4}, g_umma_min_rows{17};
+std::atomic<int> g_dot_rows_max{4}, g_umma_min_rows{5};
 int umma_min_rows() { return g_umma_min_rows.load(std::memory_order_relaxed); }
 int dot_rows_max() { return g_dot_rows_max.load(std::memory_order_relaxed); }
 
@@ -915,6 +915,12 @@ int64_t gb_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   return need > rows_path ? need : rows_path;
 }
 
+int gb_gemv_row_batch_max(const gb_weight* w) {
+  if (gb_check_weight(w) != GB_OK) return 0;
+  const int m = gb_gemv_umma_max_rows(w);
+  return m > 16 ? m : 16;
+}
+
 int gb_gemv(const void* x, int64_t M, const gb_weight* w, int act, int scale_rule, void* y,
             void* workspace, int64_t workspace_bytes, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
@@ -925,15 +931,17 @@ int gb_gemv(const void* x, int64_t M, const gb_weight* w, int act, int scale_rul
   GB_REQUIRE(act == GB_ACT_NONE || act == GB_ACT_FP4_GROUP16 || act == GB_ACT_FP8_TOKEN, "unknown act %d", act);
   const int sms = gb_sm_count();
   if (sms <= 0) return gb_fail(GB_ECUDA, "no usable CUDA device: %s", gb_last_error());
-  if (M >= umma_min_rows()) {
-    // a batch of rows of the literal format: decode into shared memory, tensor-core MMA with the
-    // weights on the M side; every weight is decoded once whatever the row count
+  if (M >= umma_min_rows() || !gb_gemv_umma_is_literal(w)) {
+    // decode into tensor memory, tensor-core MMA with the weights on the M side; every weight is
+    // decoded once whatever the row count.  The literal format has faster table kernels for a few
+    // rows; the product formats it serves (padded two-tier k = 16, fp8 k = 32) take it from one row on.
     rc = gb_gemv_umma(x, M, w, act, scale_rule, y, workspace, workspace_bytes, stream_);
     if (rc != GB_EUNSUPPORTED) return rc;
   }
   if (M > 16)
     return gb_fail(GB_EUNSUPPORTED,
-                   "more than 16 rows (M=%lld) are served for the literal fp4 format with K >= 1024 and N >= 128 only",
+                   "more than 16 rows (M=%lld) are served up to gb_gemv_row_batch_max() rows, for the formats and layouts "
+                   "of the tensor-core decode kernel only",
                    (long long)M);
   if (M == 1) {
     // one activation row of the literal format: inner-product tables instead of per-weight expansion
@@ -1077,7 +1085,7 @@ extern "C" int gb_set_row_routes(int dot_rows, int umma_min) {
   GB_REQUIRE(dot_rows >= 0 && dot_rows <= kDotRowsMax, "per-row table GEMVs serve up to %d rows, got %d", kDotRowsMax, dot_rows);
   GB_REQUIRE(umma_min >= 0 && umma_min <= 129, "tensor-core decode threshold %d outside [0, 129]", umma_min);
   g_dot_rows_max.store(dot_rows == 0 ? 4 : dot_rows, std::memory_order_relaxed);
-  g_umma_min_rows.store(umma_min == 0 ? 17 : (umma_min < 2 ? 2 : umma_min), std::memory_order_relaxed);
+  g_umma_min_rows.store(umma_min == 0 ? 5 : (umma_min < 2 ? 2 : umma_min), std::memory_order_relaxed);
   return GB_OK;
 }
 

@@ -2,7 +2,7 @@
 and docs/SPEC.md:382-460) and their C-ABI mirror."""
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 
 from . import _native as nat
 
@@ -16,6 +16,7 @@ class CBFormat:
     n_sub: int = 2            # product sub-indices (1 for signed / full)
     mode: str = "product"     # "product" | "signed" | "full"
     scale_coding: str = "v1"  # fp4: "v1" (16 E4M3 bytes) | "v2" (two-tier); fp8: "none"
+    sb_pad: int = 0           # unused bytes after each superblock (0..15): a resident layout, never on disk
 
     def __post_init__(self):
         if self.grid not in ("fp4", "fp8"):
@@ -28,16 +29,31 @@ class CBFormat:
             raise ValueError(f"fp4 scale coding must be v1 or v2, got {self.scale_coding!r}")
         if self.mode != "product":
             object.__setattr__(self, "n_sub", 1)
+        if not 0 <= self.sb_pad <= 15:
+            raise ValueError(f"superblock padding must be 0..15 bytes, got {self.sb_pad}")
 
     @property
     def is_fp4(self) -> bool:
         return self.grid == "fp4"
 
     @property
-    def type_size(self) -> int:
+    def packed_type_size(self) -> int:
+        """Bytes of a superblock as shipped (docs/SPEC.md:195-214)."""
         if not self.is_fp4:
             return 4 * self.k
         return 4 * self.k + (9 if self.scale_coding == "v2" else 16)
+
+    @property
+    def type_size(self) -> int:
+        """Superblock stride in memory: the shipped bytes plus the resident padding."""
+        return self.packed_type_size + self.sb_pad
+
+    def padded(self, stride: int) -> "CBFormat":
+        """The same format with superblocks `stride` bytes apart."""
+        pad = stride - self.packed_type_size
+        if not 0 <= pad <= 15:
+            raise ValueError(f"cannot pad {self.packed_type_size}-byte superblocks to {stride}")
+        return replace(self, sb_pad=pad)
 
     @property
     def sub_dim(self) -> int:
@@ -63,8 +79,12 @@ class CBFormat:
             raise ValueError(f"in_features {K} not a multiple of {SUPERBLOCK}")
         return (K // SUPERBLOCK) * self.type_size
 
+    def packed_row_bytes(self, K: int) -> int:
+        """Shipped (algorithmic) bytes of one row."""
+        return (K // SUPERBLOCK) * self.packed_type_size
+
     def bits_per_weight(self) -> float:
-        return self.type_size * 8 / SUPERBLOCK
+        return self.packed_type_size * 8 / SUPERBLOCK
 
     def to_native(self) -> nat.GbFormat:
         return nat.GbFormat(
@@ -89,8 +109,8 @@ class CBFormat:
             mode = "signed"           # the reference encodes signed as n_sub == 1
         fmt = cls(grid=grid, k=int(scheme["k"]), n_sub=n_sub, mode=mode, scale_coding=coding)
         ts = scheme.get("type_size")
-        if ts is not None and int(ts) != fmt.type_size:
-            raise ValueError(f"scheme type_size {ts} does not match {fmt.type_size} for {fmt}")
+        if ts is not None and int(ts) != fmt.packed_type_size:
+            raise ValueError(f"scheme type_size {ts} does not match {fmt.packed_type_size} for {fmt}")
         return fmt
 
 

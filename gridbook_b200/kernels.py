@@ -54,7 +54,7 @@ class PackedWeight:
     @property
     def packed_bytes(self) -> int:
         """Algorithmic weight-stream bytes of one pass over this matrix (all experts)."""
-        return self.experts * self.rows * self.fmt.row_bytes(self.K)
+        return self.experts * self.rows * self.fmt.packed_row_bytes(self.K)
 
 
 def make_weight(qw, codebook, fmt: CBFormat, K: int, *, cb_row_offset=None, compose=None,
@@ -172,13 +172,23 @@ _ACT = {None: nat.ACT_NONE, "none": nat.ACT_NONE, "fp4": nat.ACT_FP4_GROUP16,
 ROW_BATCH_MAX_M = 128      # rows the tensor-core decode kernel of the literal format takes
 
 
+def row_batch_max_rows(w: PackedWeight) -> int:
+    """Most activation rows :func:`gemv` takes for this weight: 16, or up to 128 where the kernel that
+    decodes into tensor memory and multiplies on the tensor cores serves the format and layout (the
+    library decides)."""
+    if w.experts != 1:
+        return 16
+    cached = w.__dict__.get("_row_batch_max")
+    if cached is None:
+        nw = w.native()
+        cached = int(nat.load("codebook decode GEMV").gb_gemv_row_batch_max(ctypes.byref(nw)))
+        w.__dict__["_row_batch_max"] = cached
+    return cached
+
+
 def row_batch_kernel_applies(w: PackedWeight) -> bool:
-    """Whether 2..128 activation rows of this weight are served by the kernel that decodes into
-    shared memory and multiplies on the tensor cores (the conditions the library checks)."""
-    f = w.fmt
-    return (f.is_fp4 and f.mode == "full" and f.k == 8 and f.scale_coding == "v1" and w.experts == 1
-            and w.cb_row_offset is None and w.K >= 1024 and w.rows >= 128 and w.row_stride % 16 == 0
-            and w.qw.data_ptr() % 16 == 0 and w.codebook.data_ptr() % 16 == 0)
+    """Whether more than 16 activation rows of this weight are served without a decoded transient."""
+    return row_batch_max_rows(w) > 16
 
 
 def gemv(x: torch.Tensor, w: PackedWeight, *, act: str | None = None, scale_rule: str = "recip",

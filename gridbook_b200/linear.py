@@ -37,7 +37,8 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         # view of the layer on the block-scaled tensor cores; "bf16" = the decode contract kept
         # (bucketed bf16 rows x bf16(value * scale)) on the bf16 tensor cores
         self.prefill_route = "nvfp4"
-        self.midm_max_rows = MIDM_MAX_M      # rows up to which the literal format decodes in the main loop
+        self.midm_max_rows = MIDM_MAX_M      # rows up to which the tensor-core decode kernel is preferred to expand + GEMM
+        self.pad_two_tier_superblocks = True   # fp4 k = 16 two-tier: 73-byte superblocks kept in 80-byte slots (TMA-fetchable)
 
     # ------------------------------------------------------------------ parameters
     def create_weights(self, layer, input_size_per_partition, output_partition_sizes, input_size,
@@ -96,10 +97,17 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         flat = torch.cat(blocks)
         cb_dev = (flat if self.is_fp4 else codec.flat_codebook_fp8(flat, self.prefix)).to(dev)
         compose = codec.build_compose_table(self._sub_table).to(dev) if self.is_v2 else None
+        fmt = self.fmt
+        if (self.pad_two_tier_superblocks and fmt.is_fp4 and fmt.mode == "product" and fmt.k == 16 and fmt.n_sub == 2
+                and fmt.scale_coding == "v2" and cb_row_offset is None and N >= 128 and K >= 1024):
+            # 73-byte superblocks -> 80-byte slots, once: the rows become fetchable by TMA and every
+            # batch size runs on the tensor-core decode kernel (the bytes themselves stay packed)
+            fmt = fmt.padded(80)
+            qw = codec.pad_superblocks(qw, self.fmt.type_size, 80)
         packed = codec.with_tail_slack(qw)
         layer.cb_qweight.data = packed          # same bytes, slack-backed storage
         ws = layer.weight_scale.data.float().contiguous() if not self.is_fp4 else None
-        layer._cb_weight = kernels.make_weight(packed, cb_dev, self.fmt, K, cb_row_offset=cb_row_offset,
+        layer._cb_weight = kernels.make_weight(packed, cb_dev, fmt, K, cb_row_offset=cb_row_offset,
                                                compose=compose, weight_scale=ws,
                                                global_scale=self.global_scale)
         layer._cb_N, layer._cb_K = N, K
@@ -136,7 +144,7 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
             outs = kernels.gemv_tab(x2, [w], layer._cb_slots, act=self.fmt.grid, scale_rule=ops.ACT_SCALE_RULE)
             if outs is not None:
                 return outs[0].reshape(*x.shape[:-1], N)
-        if M <= DECODE_MAX_M or (M <= min(self.midm_max_rows, kernels.ROW_BATCH_MAX_M) and kernels.row_batch_kernel_applies(w)):
+        if M <= DECODE_MAX_M or M <= min(self.midm_max_rows, kernels.row_batch_max_rows(w)):
             # past sixteen rows: the literal format's tensor-core decode kernel, no decoded transient
             return kernels.gemv(x2, w, act=self.fmt.grid, scale_rule=ops.ACT_SCALE_RULE,
                                 workspace=layer._cb_workspace).reshape(*x.shape[:-1], N)

@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define GB_ABI_VERSION 2
+#define GB_ABI_VERSION 3
 #define GB_API __attribute__((visibility("default")))
 
 enum { GB_OK = 0, GB_EINVAL = 1, GB_ECUDA = 2, GB_EUNSUPPORTED = 3, GB_EWORKSPACE = 4 };
@@ -116,24 +116,31 @@ GB_API int gb_expand_fp4_bf16(const gb_weight* w, int64_t row0, int64_t nrows, v
 GB_API int gb_expand_fp4_nvfp4(const gb_weight* w, int64_t row0, int64_t nrows, void* out_packed,
                         void* out_sf, int sf_swizzled, void* stream);
 
-/* ---- decode-batch linear (M <= 16; M <= 128 for the literal fp4 format) -------- */
+/* ---- decode-batch linear (M <= 16; up to gb_gemv_row_batch_max rows where that is larger) ---- */
 /* replaces cb_gemv_fp8 / cb_gemv_fp4_v2 (gridbook/csrc/cb_gemv.cu:658-712,1138-1198;
  * gridbook/ops.py:52-93).  y[M,N] = bucket(x)[M,K] . W^T, fp32 accumulate, one bf16
  * rounding.  `act` selects a fused activation bucket applied to x first (GB_ACT_NONE
  * when x is already bucketed).  workspace: gb_gemv_workspace_bytes() bytes.
- * 17 <= M <= 128 is served for the literal format (fp4 grid, full mode, k = 8, v1 scales, one
- * codebook, K >= 1024, N >= 128, 16-byte aligned rows) by a kernel that decodes the packed rows
- * into shared memory and multiplies on the tensor cores (tcgen05, weights on the M side) - the
- * decode-in-mainloop band of the reference (gridbook/csrc/cb_fused_fp4v2_gemm.cu, M <= 128)
- * with the decode contract kept; other formats return GB_EUNSUPPORTED there and take the
- * expand + gb_gemm_tn route. */
+ * Three formats - the literal one (fp4 grid, full mode, k = 8, v1 scales), the two-tier product
+ * format fp4 k = 16 with its superblocks padded to 80 bytes (fmt.type_size = 80: the 73 shipped
+ * bytes, then 7 ignored ones), and the fp8 product format k = 32 - with one codebook, K >= 1024,
+ * N >= 128 and 16-byte aligned rows are also served, up to gb_gemv_row_batch_max() rows, by a
+ * kernel that decodes the packed rows into TENSOR MEMORY and multiplies on the tensor cores
+ * (tcgen05, weights on the M side, no decoded copy anywhere) - the decode-in-mainloop band of
+ * the reference (gridbook/csrc/cb_fused_fp4v2_gemm.cu, M <= 128) with the decode contract kept.
+ * The literal format takes it from gb_set_row_routes' `umma_min` rows on (its table kernels are
+ * faster below), the other two from one row on.  Other formats return GB_EUNSUPPORTED past 16
+ * rows and take the expand + gb_gemm_tn route. */
 GB_API int64_t gb_gemv_workspace_bytes(int64_t M, int64_t N, int64_t K);
 GB_API int gb_gemv(const void* x_bf16, int64_t M, const gb_weight* w, int act, int scale_rule,
             void* y_bf16, void* workspace, int64_t workspace_bytes, void* stream);
+/* Most rows gb_gemv takes for this weight: 16, or what the tensor-core decode kernel serves for its
+ * format and layout (up to 128).  No counterpart in the reference. */
+GB_API int gb_gemv_row_batch_max(const gb_weight* w);
 
 /* Row counts at which gb_gemv changes kernel for the literal format: up to `dot_rows` rows run one
  * inner-product-table GEMV per row (default 4, at most 8), from `umma_min` rows on the tensor-core
- * decode kernel (default 17).  0 restores a default.  Process-wide; for tests and tuning.  No
+ * decode kernel (default 5).  0 restores a default.  Process-wide; for tests and tuning.  No
  * counterpart in the reference, whose lane selection is a set of environment flags. */
 GB_API int gb_set_row_routes(int dot_rows, int umma_min);
 

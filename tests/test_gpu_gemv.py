@@ -323,3 +323,52 @@ def test_literal_row_batch_tensor_core_decode_kernel(dev, request, N, K, M):
         assert_close_bf16(f32_of(y), ref, f"M={M} pad={pad}")
         y2 = kernels.gemv(synth.bf16_tensor(O.act_bucket(x, "fp4", "recip"), dev), w)
         assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("name,N,K,M", [("k16v2", 256, 1024, 1), ("k16v2", 1000, 2304, 5), ("k16v2", 384, 2048, 16),
+                                        ("k16v2", 640, 1536, 64), ("k16v2", 2048, 5120, 96),
+                                        ("f8k32", 256, 1024, 1), ("f8k32", 1000, 2304, 7), ("f8k32", 384, 2048, 16),
+                                        ("f8k32", 640, 1536, 48), ("f8k32", 2048, 5120, 80)])
+def test_product_formats_on_the_tensor_core_decode_kernel(dev, name, N, K, M):
+    """The two-tier fp4 k = 16 format (its 73-byte superblocks kept in 80-byte slots) and the fp8
+    k = 32 format run on the kernel that decodes into tensor memory from ONE row on: ragged row
+    counts on both sides, a last raw stage of one superblock, one or several K slices, legal and
+    extreme super-block exponents, against the oracle on the unpadded bytes."""
+    from gridbook_b200 import _native, codec, kernels, synth
+    fmt = _fmt(name)
+    d = synth.make_linear(fmt, N, K, seed=N + K + M, super_span=None if name == "k16v2" else 4)
+    x = synth.make_activations(M, K, seed=M)
+    ref = oracle_linear(x, d, bucket=True, scale_rule="recip")
+    if name == "k16v2":
+        dp = dict(d, fmt=fmt.padded(80), qw=codec.pad_superblocks(torch.from_numpy(d["qw"]), 73, 80).numpy())
+    else:
+        dp = d
+    w = synth.to_device_weight(dp, dev)
+    assert kernels.row_batch_max_rows(w) >= M
+    y = kernels.gemv(synth.bf16_tensor(x, dev), w, act=fmt.grid)
+    torch.cuda.synchronize()
+    assert _native.device_status(0) == 0
+    # several accumulators added at the end and sums of thousands of large terms that cancel (the
+    # whole range of super-block exponents): an absolute allowance next to the two ULPs
+    assert_close_bf16(f32_of(y), ref, f"{name} M={M}", atol_rel=2e-4)
+    # the padded layout decodes to the same weights through the generic kernels too
+    wt = kernels.expand_fp4_bf16(w) if fmt.is_fp4 else kernels.expand_fp8_bf16(w)
+    wu = synth.to_device_weight(d, dev)
+    wt_u = kernels.expand_fp4_bf16(wu) if fmt.is_fp4 else kernels.expand_fp8_bf16(wu)
+    assert torch.equal(wt, wt_u)
+
+
+def test_two_tier_scale_table_that_is_not_exact_in_bf16_takes_the_fp32_path(dev):
+    """A custom sub-table with more than eight significant bits: the kernel notices while it converts
+    the table and multiplies in fp32, so the served weight is still bf16(value * scale)."""
+    from gridbook_b200 import codec, kernels, synth
+    fmt = _fmt("k16v2")
+    N, K, M = 256, 1024, 4
+    d = synth.make_linear(fmt, N, K, seed=5)
+    table = np.array([1.0 + i * (1.0 / 16) + 2.0 ** -12 for i in range(16)], dtype=np.float64)
+    d["compose"] = synth.compose_table(tuple(table))
+    x = synth.make_activations(M, K, seed=2)
+    ref = oracle_linear(x, d, bucket=True, scale_rule="recip")
+    dp = dict(d, fmt=fmt.padded(80), qw=codec.pad_superblocks(torch.from_numpy(d["qw"]), 73, 80).numpy())
+    y = kernels.gemv(synth.bf16_tensor(x, dev), synth.to_device_weight(dp, dev), act="fp4")
+    assert_close_bf16(f32_of(y), ref, "inexact table")
