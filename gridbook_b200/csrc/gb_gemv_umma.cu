@@ -163,37 +163,43 @@ GB_DEVINL void wait_fast(uint64_t* bar, uint32_t parity, volatile int* abort_fla
 }
 
 // Literal format: four codewords (the bytes of `codes`) of one weight row -> 16 bf16 pairs; `sc2`
-// holds the two group scale bytes they share (low byte: codewords 0 and 1).  The scale byte moved
-// into bf16's fields is 2^-120 times its value; the codebook copies carry the 2^120.
-GB_DEVINL void lit_decode4(const uint4* lut, uint32_t codes, uint32_t sc2, uint32_t (&v)[16]) {
+// holds the two group scale bytes they share in its low half (low byte: codewords 0 and 1).  A scale
+// byte moved into bf16's fields is 2^-120 times its value; the codebook copies carry the 2^120.
+// `lut` is the lane's copy of entry 0 as a shared-memory address; entries are 128 bytes apart.
+GB_DEVINL void lit_decode4(uint32_t lut, uint32_t codes, uint32_t sc2, uint32_t (&v)[16]) {
+  // both scale bytes at once: byte -> (byte & 0x7f) << 4 | (byte & 0x80) << 8 in each half
+  const uint32_t x = __byte_perm(sc2, 0u, 0x4140) << 4;                      // [b1 << 4 | b0 << 4] in the halves
+  const uint32_t y = (x & 0x07F007F0u) | ((x << 4) & 0x80008000u);
+  const uint32_t s2[2] = {__byte_perm(y, y, 0x1010), __byte_perm(y, y, 0x3232)};
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const uint32_t sc = (sc2 >> (8 * h)) & 0xFFu;
-    const uint32_t s2 = (((sc & 0x7Fu) << 4) | ((sc & 0x80u) << 8)) * 0x10001u;
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int c = h * 2 + i;
-      const uint4 e = lut[((codes >> (8 * c)) & 0xFFu) * 8];
-      v[c * 4 + 0] = mul_bf16x2(e.x, s2);
-      v[c * 4 + 1] = mul_bf16x2(e.y, s2);
-      v[c * 4 + 2] = mul_bf16x2(e.z, s2);
-      v[c * 4 + 3] = mul_bf16x2(e.w, s2);
-    }
+  for (int c = 0; c < 4; ++c) {
+    // entry offset = code * 128, straight from the byte's place in the word
+    const uint32_t off = (c == 0 ? codes << 7 : codes >> (8 * c - 7)) & 0x7F80u;
+    uint4 e;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(e.x), "=r"(e.y), "=r"(e.z), "=r"(e.w) : "r"(lut + off));
+    v[c * 4 + 0] = mul_bf16x2(e.x, s2[c >> 1]);
+    v[c * 4 + 1] = mul_bf16x2(e.y, s2[c >> 1]);
+    v[c * 4 + 2] = mul_bf16x2(e.z, s2[c >> 1]);
+    v[c * 4 + 3] = mul_bf16x2(e.w, s2[c >> 1]);
   }
 }
 
 // Two-tier product format, k = 16: two index words (four codewords: low byte = first sub-table,
-// high byte = second) and the two group scales they use, as bf16 bits (exact) or as fp32.
+// high byte = second) and the two group scales they use, as bf16 bits (exact) or as fp32.  `lut0` /
+// `lut1` are the lane's copies of entry 0 of the two sub-tables (shared-memory addresses, entries
+// 128 bytes apart).
 template <bool kExact>
-GB_DEVINL void k16_decode4(const uint2* lut0, const uint2* lut1, uint32_t wa, uint32_t wb, uint32_t sa, uint32_t sb,
+GB_DEVINL void k16_decode4(uint32_t lut0, uint32_t lut1, uint32_t wa, uint32_t wb, uint32_t sa, uint32_t sb,
                            float fa, float fb, uint32_t (&v)[16]) {
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    const uint32_t w = (c < 2 ? wa : wb) >> (16 * (c & 1));
-    const uint2 e0 = lut0[(w & 0xFFu) * 16];
-    const uint2 e1 = lut1[((w >> 8) & 0xFFu) * 16];
+    const uint32_t w = c < 2 ? wa : wb;
+    const uint32_t off0 = ((c & 1) ? w >> 9 : w << 7) & 0x7F80u, off1 = ((c & 1) ? w >> 17 : w >> 1) & 0x7F80u;
+    uint2 e0, e1;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(e0.x), "=r"(e0.y) : "r"(lut0 + off0));
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(e1.x), "=r"(e1.y) : "r"(lut1 + off1));
     if (kExact) {
-      const uint32_t s2 = (c < 2 ? sa : sb) * 0x10001u;
+      const uint32_t s1 = c < 2 ? sa : sb, s2 = __byte_perm(s1, s1, 0x1010);
       v[c * 4 + 0] = mul_bf16x2(e0.x, s2);
       v[c * 4 + 1] = mul_bf16x2(e0.y, s2);
       v[c * 4 + 2] = mul_bf16x2(e1.x, s2);
@@ -209,14 +215,17 @@ GB_DEVINL void k16_decode4(const uint2* lut0, const uint2* lut1, uint32_t wa, ui
 }
 
 // fp8 product format, k = 32: four codewords of four sub-indices; every sub-table entry is two E4M3
-// values; weight = bf16(value * row scale), the product taken in fp32.
-GB_DEVINL void fp8_decode4(const uint16_t* lut, uint4 cw, float rs, uint32_t (&v)[16]) {
+// values; weight = bf16(value * row scale), the product taken in fp32.  `lut` is the lane's copy of
+// entry 0 of the first sub-table (entries 64 bytes apart, sub-tables 16 KiB apart).
+GB_DEVINL void fp8_decode4(uint32_t lut, uint4 cw, float rs, uint32_t (&v)[16]) {
   const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const uint16_t e = lut[(j * 256 + ((w4[c] >> (8 * j)) & 0xFFu)) * 32];
+      const uint32_t off = (j == 0 ? w4[c] << 6 : w4[c] >> (8 * j - 6)) & 0x3FC0u;
+      uint16_t e;
+      asm volatile("ld.shared.u16 %0, [%1];" : "=h"(e) : "r"(lut + (uint32_t)(j * 16384) + off));
       uint32_t h2;
       asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(e));
       const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
@@ -456,7 +465,7 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         uint32_t v0[16], v1[16];
         // ---- first eight codewords into registers, then wait for the operand buffer ----
         if constexpr (F == kFmtLit) {
-          const uint4* lut = reinterpret_cast<const uint4*>(cb_s) + (lane & 7);
+          const uint32_t lut = gb_smem_u32(cb_s) + (uint32_t)(lane & 7) * 16u;
           const uint4 cw = rp[h];
           const uint2 sc = reinterpret_cast<const uint2*>(rp + 2)[h];
           lit_decode4(lut, cw.x, sc.x & 0xFFFFu, v0);
@@ -470,8 +479,7 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           tmem_st16(col + 32u, v0);
           tmem_st16(col + 48u, v1);
         } else if constexpr (F == kFmtK16) {
-          const uint2* lut0 = reinterpret_cast<const uint2*>(cb_s) + (lane & 15);
-          const uint2* lut1 = lut0 + 256 * 16;
+          const uint32_t lut0 = gb_smem_u32(cb_s) + (uint32_t)(lane & 15) * 8u, lut1 = lut0 + 256u * 16u * 8u;
           const uint16_t* comp_s = reinterpret_cast<const uint16_t*>(cb_s + 2 * 256 * 16 * 8);
           const uint4 ia = rp[2 * h], ib = rp[2 * h + 1], q4 = rp[4];    // eight index words: sixteen codewords
           const uint16_t* crow = comp_s + (q4.x & 0xFFu) * 16;
@@ -493,7 +501,7 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           tmem_st16(col + 32u, v0);
           tmem_st16(col + 48u, v1);
         } else {
-          const uint16_t* lut = reinterpret_cast<const uint16_t*>(cb_s) + lane;
+          const uint32_t lut = gb_smem_u32(cb_s) + (uint32_t)lane * 2u;
           fp8_decode4(lut, rp[4 * h], rs, v0);
           fp8_decode4(lut, rp[4 * h + 1], rs, v1);
           if (sb_in_pass >= 2) wait_fast(&done[(g - 4) & xs_mask], (uint32_t)((g - 4) >> xs_log) & 1u, abort_flag, p.status, 25);
