@@ -41,7 +41,7 @@ constexpr int kMaxXStages = 8;
 constexpr int kMaxRawStages = 3;
 constexpr int kSmemCap = 227 * 1024;
 
-enum { kFmtLit = 0, kFmtK16 = 1, kFmtFp8 = 2 };
+enum { kFmtLit = 0, kFmtK16 = 1, kFmtFp8 = 2, kFmtF8L = 3 };
 
 // Per format: bytes of a superblock, how a raw stage is cut into TMA boxes, ring depth, and the
 // bytes of the replicated codebook copies (+ scale table).
@@ -57,6 +57,10 @@ template <> struct Fm<kFmtK16> {
 template <> struct Fm<kFmtFp8> {
   static constexpr int kSb = 128, kSbPerBox = 1, kBoxes = 2, kStages = 2;
   static constexpr int kLut = 4 * 256 * 32 * 2;           // four sub-tables of 2-byte entries, 32 copies
+};
+template <> struct Fm<kFmtF8L> {
+  static constexpr int kSb = 64, kSbPerBox = 3, kBoxes = 1, kStages = 2;
+  static constexpr int kLut = 2 * 256 * 32 * 4;           // two sub-tables of 4-byte entries, 32 copies
 };
 template <int F> struct Geo {
   static constexpr int kPitch = Fm<F>::kSbPerBox * Fm<F>::kSb + 16;   // an odd number of 16-byte units
@@ -230,6 +234,30 @@ GB_DEVINL void fp8_decode4(uint32_t lut, uint4 cw, float rs, uint32_t (&v)[16]) 
       asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(e));
       const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
       v[c * 4 + j] = gb_pack_bf16x2(f.x * rs, f.y * rs);
+    }
+  }
+}
+
+// fp8 product format, k = 16: two index words (four codewords: low byte = first sub-table, high byte
+// = second); every sub-table entry is four E4M3 values (entries 128 bytes apart, the second
+// sub-table 32 KiB after the first).
+GB_DEVINL void f8l_decode4(uint32_t lut, uint32_t wa, uint32_t wb, float rs, uint32_t (&v)[16]) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t w = c < 2 ? wa : wb;
+    const uint32_t off0 = ((c & 1) ? w >> 9 : w << 7) & 0x7F80u, off1 = ((c & 1) ? w >> 17 : w >> 1) & 0x7F80u;
+    uint32_t e[2];
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(e[0]) : "r"(lut + off0));
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(e[1]) : "r"(lut + 32768u + off1));
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      uint32_t lo, hi;
+      asm("{\n.reg .b16 a, b;\nmov.b32 {a, b}, %2;\ncvt.rn.f16x2.e4m3x2 %0, a;\ncvt.rn.f16x2.e4m3x2 %1, b;\n}\n"
+          : "=r"(lo), "=r"(hi) : "r"(e[t]));
+      const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+      const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+      v[c * 4 + 2 * t] = gb_pack_bf16x2(f0.x * rs, f0.y * rs);
+      v[c * 4 + 2 * t + 1] = gb_pack_bf16x2(f1.x * rs, f1.y * rs);
     }
   }
 }
@@ -421,6 +449,12 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         comp_s[d * 8 + j] = (uint16_t)b;
       }
       if (bad) atomicOr(inexact, 1);
+    } else if constexpr (F == kFmtF8L) {
+      // two sub-tables of 256 entries x four E4M3 bytes, 32 copies each (one per lane)
+      const uint32_t e = __ldg(reinterpret_cast<const uint32_t*>(p.codebook) + dh * 256 + de);
+      uint4* l = reinterpret_cast<uint4*>(cb_s) + (dh * 256 + de) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) l[j] = make_uint4(e, e, e, e);
     } else {
       // four sub-tables of 256 entries x two E4M3 bytes, 32 copies each (one per lane)
       const uint16_t* cb = reinterpret_cast<const uint16_t*>(p.codebook);
@@ -444,7 +478,7 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const uint32_t col = lane_base + kACol0 + (uint32_t)(wg * kABufCols);
     const bool exact = *inexact == 0;
     float rs = 0.0f;                                         // fp8 grid: this row's scale
-    if constexpr (F == kFmtFp8) {
+    if constexpr (F == kFmtFp8 || F == kFmtF8L) {
       if ((int64_t)w_row0 + row < p.rows_total) rs = __ldg(p.row_scale + w_row0 + row);
     }
     int it = 0, g_sb = 0;                                    // raw stages so far, superblocks so far (over all passes)
@@ -498,6 +532,19 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           tmem_st16(col + 16u, v1);
           four(ib.x, ib.y, nib >> 16, v0);
           four(ib.z, ib.w, nib >> 24, v1);
+          tmem_st16(col + 32u, v0);
+          tmem_st16(col + 48u, v1);
+        } else if constexpr (F == kFmtF8L) {
+          const uint32_t lut = gb_smem_u32(cb_s) + (uint32_t)lane * 4u;
+          const uint4 ia = rp[2 * h], ib = rp[2 * h + 1];    // eight index words: sixteen codewords
+          f8l_decode4(lut, ia.x, ia.y, rs, v0);
+          f8l_decode4(lut, ia.z, ia.w, rs, v1);
+          if (sb_in_pass >= 2) wait_fast(&done[(g - 4) & xs_mask], (uint32_t)((g - 4) >> xs_log) & 1u, abort_flag, p.status, 25);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          tmem_st16(col, v0);
+          tmem_st16(col + 16u, v1);
+          f8l_decode4(lut, ib.x, ib.y, rs, v0);
+          f8l_decode4(lut, ib.z, ib.w, rs, v1);
           tmem_st16(col + 32u, v0);
           tmem_st16(col + 48u, v1);
         } else {
@@ -611,6 +658,7 @@ FmtInfo fmt_info(int F) {
   switch (F) {
     case kFmtLit: return {Fm<kFmtLit>::kSb, Geo<kFmtLit>::kSbPerStage, Geo<kFmtLit>::kPitch, Geo<kFmtLit>::kFixed};
     case kFmtK16: return {Fm<kFmtK16>::kSb, Geo<kFmtK16>::kSbPerStage, Geo<kFmtK16>::kPitch, Geo<kFmtK16>::kFixed};
+    case kFmtF8L: return {Fm<kFmtF8L>::kSb, Geo<kFmtF8L>::kSbPerStage, Geo<kFmtF8L>::kPitch, Geo<kFmtF8L>::kFixed};
     default: return {Fm<kFmtFp8>::kSb, Geo<kFmtFp8>::kSbPerStage, Geo<kFmtFp8>::kPitch, Geo<kFmtFp8>::kFixed};
   }
 }
@@ -655,6 +703,9 @@ int umma_format(const gb_weight* w) {
   if (f.grid == GB_GRID_FP8 && f.mode == GB_MODE_PRODUCT && f.n_sub == 4 && f.k_bits == 32 &&
       f.type_size == Fm<kFmtFp8>::kSb && w->weight_scale != nullptr)
     return kFmtFp8;
+  if (f.grid == GB_GRID_FP8 && f.mode == GB_MODE_PRODUCT && f.n_sub == 2 && f.k_bits == 16 &&
+      f.type_size == Fm<kFmtF8L>::kSb && w->weight_scale != nullptr)
+    return kFmtF8L;
   return -1;
 }
 
@@ -669,6 +720,7 @@ cudaError_t launch_umma(int F, dim3 grid, size_t smem, cudaStream_t stream, cons
   switch (F) {
     case kFmtLit: return gb_launch(umma_decode_kernel<kGrouped, kFmtLit>, grid, dim3(kUmmaThreads), smem, stream, map_w, map_x, p);
     case kFmtK16: return gb_launch(umma_decode_kernel<kGrouped, kFmtK16>, grid, dim3(kUmmaThreads), smem, stream, map_w, map_x, p);
+    case kFmtF8L: return gb_launch(umma_decode_kernel<kGrouped, kFmtF8L>, grid, dim3(kUmmaThreads), smem, stream, map_w, map_x, p);
     default: return gb_launch(umma_decode_kernel<kGrouped, kFmtFp8>, grid, dim3(kUmmaThreads), smem, stream, map_w, map_x, p);
   }
 }
@@ -690,9 +742,11 @@ int gb_prepare_umma() {
   GB_UMMA_ATTR(false, kFmtLit, kMaxRows);
   GB_UMMA_ATTR(false, kFmtK16, kMaxRows);
   GB_UMMA_ATTR(false, kFmtFp8, kMaxRows);
+  GB_UMMA_ATTR(false, kFmtF8L, kMaxRows);
   GB_UMMA_ATTR(true, kFmtLit, kGroupRows);
   GB_UMMA_ATTR(true, kFmtK16, kGroupRows);
   GB_UMMA_ATTR(true, kFmtFp8, kGroupRows);
+  GB_UMMA_ATTR(true, kFmtF8L, kGroupRows);
 #undef GB_UMMA_ATTR
   return GB_OK;
 }
@@ -705,7 +759,7 @@ int64_t gb_gemv_umma_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   int sms = gb_sm_count();
   if (sms <= 0) sms = 148;
   int most = 1;
-  for (int F = 0; F < 3; ++F) {
+  for (int F = 0; F < 4; ++F) {
     int slices, per;
     umma_plan(F, N, (int)(K / 256), sms, &slices, &per);
     if (slices > most) most = slices;
@@ -790,7 +844,7 @@ int gb_moe_gemv_sorted(const void* x_sorted, const gb_weight* w, int64_t expert_
         E * N < (1ll << 31)))
     return gb_fail(GB_EUNSUPPORTED,
                    "the sorted-rows expert kernel takes contiguous stacks of the literal fp4 format, the two-tier k = 16 "
-                   "format with 80-byte superblocks or the fp8 k = 32 format, with N %% 128 == 0 and one codebook");
+                   "format with 80-byte superblocks or the fp8 product formats k = 32 / k = 16, with N %% 128 == 0 and one codebook");
   if (P == 0) return GB_OK;
   if (gb_sm_count() <= 0) return gb_fail(GB_ECUDA, "no usable CUDA device: %s", gb_last_error());
   const FmtInfo fi = fmt_info(F);

@@ -353,6 +353,12 @@ def moe_gemv_pairs(x: torch.Tensor, w: PackedWeight, pair_expert: torch.Tensor, 
     return True if peer_rows is not None else out
 
 
+def pair_kernel_applies(w: PackedWeight) -> bool:
+    """Whether the stack is of the literal fp4 format, the one the per-pair table kernel serves."""
+    f = w.fmt
+    return f.is_fp4 and f.mode == "full" and f.k == 8 and f.scale_coding == "v1" and f.type_size == 48
+
+
 def moe_mlp_pairs(x: torch.Tensor, w13: PackedWeight, w2: PackedWeight, pair_expert: torch.Tensor, *,
                   x_row: torch.Tensor | None = None, act: str | None = "fp4", scale_rule: str = "recip",
                   expert_base: int = 0, pairs_expected: int = 0, peer_rows=None):
@@ -554,18 +560,27 @@ def stack_rows(w: PackedWeight) -> PackedWeight:
 
 
 def moe_gemv_sorted_applies(w: PackedWeight) -> bool:
+    """Formats and layouts the sorted-rows expert kernel decodes (the conditions the library checks):
+    the literal fp4 format, the two-tier fp4 k = 16 format in 80-byte superblock slots, the fp8
+    product formats k = 32 (n_sub 4) and k = 16 (n_sub 2); one codebook, rows a multiple of 128,
+    16-byte aligned rows, a contiguous stack."""
     f = w.fmt
-    return (f.is_fp4 and f.mode == "full" and f.k == 8 and f.scale_coding == "v1" and w.cb_row_offset is None
-            and w.rows % 128 == 0 and w.row_stride % 16 == 0 and w.expert_stride == w.rows * w.row_stride)
+    served = ((f.is_fp4 and f.mode == "full" and f.k == 8 and f.scale_coding == "v1" and f.type_size == 48)
+              or (f.is_fp4 and f.mode == "product" and f.k == 16 and f.n_sub == 2 and f.scale_coding == "v2"
+                  and f.type_size == 80)
+              or (not f.is_fp4 and f.mode == "product" and ((f.k == 32 and f.n_sub == 4) or (f.k == 16 and f.n_sub == 2))))
+    return (served and w.cb_row_offset is None and w.rows % 128 == 0 and w.row_stride % 16 == 0
+            and w.expert_stride == w.rows * w.row_stride and w.qw.data_ptr() % 16 == 0
+            and w.codebook.data_ptr() % 16 == 0)
 
 
 def moe_gemv_sorted(x_sorted: torch.Tensor, w: PackedWeight, offsets: torch.Tensor, *,
                     row_map: torch.Tensor | None = None, peer_rows=None,
                     out: torch.Tensor | None = None) -> torch.Tensor | None:
     """Grouped linear over rows already in expert order, for mid-size batches: every (expert, 128-row
-    tile) decodes its packed rows into shared memory and multiplies on the tensor cores.  -> [P, rows]
-    bf16 (row j at ``row_map[j]`` or j; rows past ``offsets[E]`` unset), or None when the stack is
-    not the literal fp4 format in a contiguous layout with rows a multiple of 128.  ``peer_rows``
+    tile) decodes its packed rows into tensor memory and multiplies on the tensor cores.  -> [P, rows]
+    bf16 (row j at ``row_map[j]`` or j; rows past ``offsets[E]`` unset), or None when
+    :func:`moe_gemv_sorted_applies` says the stack is not served.  ``peer_rows``
     (a ``GbPeerRows``): rows go to their home rank's buffer instead, nothing is returned."""
     _need_cuda(x_sorted, offsets, row_map)
     lib = nat.load("sorted-rows expert kernel")

@@ -20,12 +20,17 @@ from .formats import CBFormat
 PAIR_KERNEL_MAX_PAIRS = 768       # routed pairs up to which every pair runs as its own table GEMV
 FUSED_BUCKET_MAX_PAIRS = 32       # routed pairs up to which the grouped kernel buckets its own rows
 # From this many routed pairs per expert (on average) the routed layer decodes each stack once
-# and runs grouped tensor-core GEMMs instead of the decode kernel's 16-row passes.
-PREFILL_MIN_PAIRS_PER_EXPERT = 104
-# Between the two: from this many routed pairs per expert on, the rows are sorted by expert and
-# every (expert, 128-row tile) decodes its weights once into shared memory for a tensor-core MMA
-# (literal fp4 stacks only); below it the decode kernel's 16-row passes are faster.
-SORTED_MIN_PAIRS_PER_EXPERT = 18
+# into a transient and runs grouped tensor-core GEMMs (sorted rows: 0.98 ms at 256 pairs per expert
+# and +0.20 us per token; decoded stack + grouped GEMM: 1.12 ms and +0.13 us per token).
+PREFILL_MIN_PAIRS_PER_EXPERT = 384
+# Below that, from this many routed pairs per expert on, the rows are sorted by expert and every
+# (expert, 128-row tile) decodes its weights once into tensor memory for a tensor-core MMA.  Literal
+# fp4 stacks have the per-pair table kernel below it (164 us against 212 us at 4 pairs per expert,
+# 278 against 224 at 8); stacks without that kernel (two-tier k = 16, the fp8 grid) take the sorted
+# rows from SORTED_MIN_PAIRS_OTHER routed pairs in all (two tokens at top-8: 223 us against 272 us
+# on 32 experts of hidden 7168, intermediate 2048).
+SORTED_MIN_PAIRS_PER_EXPERT = 6
+SORTED_MIN_PAIRS_OTHER = 16
 
 
 def _row_bytes(in_features: int, type_size: int) -> int:
@@ -51,6 +56,8 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         self.k, self.n_sub, self.type_size = self.fmt13.k, self.fmt13.n_sub, self.fmt13.type_size
         self.pair_kernel_max_pairs = PAIR_KERNEL_MAX_PAIRS
         self.sorted_min_pairs_per_expert = SORTED_MIN_PAIRS_PER_EXPERT
+        self.sorted_min_pairs_other = SORTED_MIN_PAIRS_OTHER
+        self.pad_two_tier_superblocks = True   # fp4 k = 16 two-tier stacks: 73-byte superblocks in 80-byte slots
         self.prefill_min_pairs_per_expert = PREFILL_MIN_PAIRS_PER_EXPERT
 
     # ------------------------------------------------------------------ parameters
@@ -136,7 +143,13 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         flat = torch.cat(blocks)
         p = getattr(layer, qw_name)
         dev = p.device
-        packed = codec.with_tail_slack(p.data)
+        qw = p.data
+        if (self.pad_two_tier_superblocks and fmt.is_fp4 and fmt.mode == "product" and fmt.k == 16 and fmt.n_sub == 2
+                and fmt.scale_coding == "v2" and len(blocks) == 1 and qw.shape[1] % 128 == 0 and k_in >= 256):
+            # 73-byte superblocks -> 80-byte slots, once (the sorted-rows kernel fetches rows by TMA)
+            qw = codec.pad_superblocks(qw, fmt.type_size, 80)
+            fmt = fmt.padded(80)
+        packed = codec.with_tail_slack(qw)
         p.data = packed
         cb_dev = (flat if fmt.is_fp4 else codec.flat_codebook_fp8(flat, self.prefix)).to(dev)
         sc = scheme.get("scale_coding")
@@ -234,7 +247,8 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         ids = topk_ids.to(torch.int32).contiguous()
         if T * topk >= self.prefill_min_pairs_per_expert * layer._cb_E:
             return self._apply_prefill(layer, x2, topk_weights, ids, rule).to(x.dtype).reshape(x.shape)
-        if T * topk >= self.sorted_min_pairs_per_expert * layer._cb_E:
+        pair_kernel = kernels.pair_kernel_applies(layer._cb_w13) and kernels.pair_kernel_applies(layer._cb_w2)
+        if T * topk >= (self.sorted_min_pairs_per_expert * layer._cb_E if pair_kernel else self.sorted_min_pairs_other):
             out = self._apply_sorted(layer, x2, topk_weights, ids, rule)
             if out is not None:
                 return out.to(x.dtype).reshape(x.shape)
@@ -304,28 +318,35 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         return kernels.moe_combine(y, pair_w, T, topk, topk_ids=ids, E=E)
 
     def _apply_sorted(self, layer, x2, topk_weights, ids, rule):
-        """Mid-size batches of literal fp4 stacks: route, bucket, bring the rows into expert order,
-        then per projection one launch in which every (expert, 128-row tile) decodes its packed rows
-        into shared memory and multiplies them with the expert's rows on the tensor cores (tcgen05,
-        64 rows per pass); SwiGLU and the second bucket in one launch between them; the down
-        projection stores its rows back in pair order for the combine.  None when the stacks are not
-        of that format."""
+        """Mid-size batches: route, bucket, bring the rows into expert order, then per projection one
+        launch in which every (expert, 128-row tile) decodes its packed rows into tensor memory and
+        multiplies them with the expert's rows on the tensor cores (tcgen05, 64 rows per pass);
+        SwiGLU and the second bucket between them; the down projection stores its rows back in pair
+        order for the combine.  The two stacks may be of different grids (an fp8-grid gate_up over an
+        fp4-grid down): each projection's rows go through its own grid's bucket.  None when a stack
+        is not of a format that kernel decodes (kernels.moe_gemv_sorted_applies)."""
         w13, w2 = layer._cb_w13, layer._cb_w2
-        if not (w13.fmt.is_fp4 and w2.fmt.is_fp4 and layer._cb_inter % 16 == 0):
+        if not (kernels.moe_gemv_sorted_applies(w13) and kernels.moe_gemv_sorted_applies(w2)):
+            return None
+        if w2.fmt.is_fp4 and layer._cb_inter % 16:
             return None
         T, topk = ids.shape
         E = layer._cb_E
         _, offsets, order, pair_w = kernels.moe_route(ids, E, topk_weights)
         x_row = self._x_row(layer, T, topk, x2.device)
-        a = kernels.moe_gather_rows(kernels.fp4_act_qdq(x2, rule), order, offsets, x_row=x_row)
+        xq = kernels.fp4_act_qdq(x2, rule) if w13.fmt.is_fp4 else kernels.fp8_act_qdq(x2, rule)
+        a = kernels.moe_gather_rows(xq, order, offsets, x_row=x_row)
         h13 = kernels.moe_gemv_sorted(a, w13, offsets)
         if h13 is None:
             return None
-        h = kernels.moe_swiglu_rows(h13, offsets, act="fp4", scale_rule=rule)
+        if w2.fmt.is_fp4:
+            h = kernels.moe_swiglu_rows(h13, offsets, act="fp4", scale_rule=rule)
+        else:
+            h = kernels.fp8_act_qdq(kernels.moe_swiglu_rows(h13, offsets), rule)
         y = kernels.moe_gemv_sorted(h, w2, offsets, row_map=order)
         if y is None:
             return None
-        layer._cb_route = "sorted rows: decode in shared memory + tcgen05"
+        layer._cb_route = "sorted rows: decode into tensor memory + tcgen05"
         return kernels.moe_combine(y, pair_w, T, topk, topk_ids=ids, E=E)
 
     def _apply_pairs(self, layer, x2, topk_weights, ids, rule):

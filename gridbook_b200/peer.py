@@ -302,7 +302,10 @@ class PeerExpertParallelMoE(torch.nn.Module):
         pairs_all = world * T * topk
         # small batches of the literal format: every pair is its own table GEMV (bucket fused)
         # (pairs of other ranks' experts cost a CTA that leaves at once; bound those too)
-        per_pair = (self._pairs_ok and pairs_all // world <= PAIR_KERNEL_MAX_PAIRS
+        # enough rows per expert (all ranks' tokens together): the sorted-rows tensor-core route
+        use_sorted = self._sorted_ok and pairs_all >= (method.sorted_min_pairs_per_expert * self.E if self._pairs_ok
+                                                       else method.sorted_min_pairs_other)
+        per_pair = (not use_sorted and self._pairs_ok and pairs_all // world <= PAIR_KERNEL_MAX_PAIRS
                     and pairs_all <= 4 * PAIR_KERNEL_MAX_PAIRS)
         x2 = x.reshape(T, H).to(torch.bfloat16).contiguous()
         # the bucket is per token, so it can run before the rows travel (the per-pair kernel
@@ -335,15 +338,17 @@ class PeerExpertParallelMoE(torch.nn.Module):
                 raise NativeKernelUnavailableError(
                     "per-pair table MLP refused a format the layer was built for")
             done = True
-        if (not done and self._sorted_ok and method.fmt2.is_fp4
-                and pairs_all >= method.sorted_min_pairs_per_expert * self.E):
-            # many rows per local expert: sort them, decode every (expert, 128-row tile) in shared
+        if not done and use_sorted:
+            # many rows per local expert: sort them, decode every (expert, 128-row tile) into tensor
             # memory and multiply on the tensor cores; the down projection stores each row into its
             # home rank's buffer
             _, offsets, order = kernels.moe_route(ids_all, self.e_local, expert_base=base)
             a = kernels.moe_gather_rows(x_all, order, offsets, x_row=x_row)
-            h = kernels.moe_swiglu_rows(kernels.moe_gemv_sorted(a, layer._cb_w13, offsets), offsets, act="fp4",
-                                        scale_rule=rule)
+            h13 = kernels.moe_gemv_sorted(a, layer._cb_w13, offsets)
+            if method.fmt2.is_fp4:
+                h = kernels.moe_swiglu_rows(h13, offsets, act="fp4", scale_rule=rule)
+            else:
+                h = kernels.fp8_act_qdq(kernels.moe_swiglu_rows(h13, offsets), rule)
             kernels.moe_gemv_sorted(h, layer._cb_w2, offsets, row_map=order, peer_rows=rows)
             done = True
         if not done:

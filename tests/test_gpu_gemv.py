@@ -328,10 +328,12 @@ def test_literal_row_batch_tensor_core_decode_kernel(dev, request, N, K, M):
 @pytest.mark.parametrize("name,N,K,M", [("k16v2", 256, 1024, 1), ("k16v2", 1000, 2304, 5), ("k16v2", 384, 2048, 16),
                                         ("k16v2", 640, 1536, 64), ("k16v2", 2048, 5120, 96),
                                         ("f8k32", 256, 1024, 1), ("f8k32", 1000, 2304, 7), ("f8k32", 384, 2048, 16),
-                                        ("f8k32", 640, 1536, 48), ("f8k32", 2048, 5120, 80)])
+                                        ("f8k32", 640, 1536, 48), ("f8k32", 2048, 5120, 80),
+                                        ("f8lit", 256, 1024, 1), ("f8lit", 1000, 2304, 7), ("f8lit", 640, 1536, 64),
+                                        ("f8lit", 2048, 5120, 96)])
 def test_product_formats_on_the_tensor_core_decode_kernel(dev, name, N, K, M):
     """The two-tier fp4 k = 16 format (its 73-byte superblocks kept in 80-byte slots) and the fp8
-    k = 32 format run on the kernel that decodes into tensor memory from ONE row on: ragged row
+    product formats k = 32 and k = 16 run on the kernel that decodes into tensor memory from ONE row on: ragged row
     counts on both sides, a last raw stage of one superblock, one or several K slices, legal and
     extreme super-block exponents, against the oracle on the unpadded bytes."""
     from gridbook_b200 import _native, codec, kernels, synth

@@ -135,27 +135,34 @@ def test_moe_method_prefill_route_matches_loop_chain(dev, monkeypatch, f13, f2, 
     assert np.abs(got - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max())
 
 
-@pytest.mark.parametrize("T", [40, 150, 700])
-def test_moe_method_sorted_rows_route_matches_loop_chain(dev, monkeypatch, T):
-    """The routed layer on the sorted-rows route (decode in shared memory + tcgen05 per expert tile),
-    forced on for this small shape: experts with no rows, with a few, and with more than one
-    64-row pass; a padded (-1) slot."""
+@pytest.mark.parametrize("f13,f2,T", [("lit", "lit", 40), ("lit", "lit", 150), ("lit", "lit", 700),
+                                      ("k16v2", "k16v2", 150), ("f8k32", "f8k32", 150), ("f8lit", "lit", 150),
+                                      ("f8lit", "lit", 3), ("lit", "f8k32", 300)])
+def test_moe_method_sorted_rows_route_matches_loop_chain(dev, monkeypatch, f13, f2, T):
+    """The routed layer on the sorted-rows route (decode into tensor memory + tcgen05 per expert
+    tile), forced on for this small shape: experts with no rows, with a few, and with more than one
+    64-row pass; a padded (-1) slot; every format the kernel decodes, also two grids in one layer
+    (each projection's rows through its own grid's bucket) and two-tier stacks, which the method
+    keeps in 80-byte superblock slots."""
     from gridbook_b200 import _native, synth
     from gridbook_b200.moe import CBMoE
     from tests.test_gpu_plugin import _formats, _tables
-    fmt = _formats()["lit"]
+    fmt, fmt_2 = _formats()[f13], _formats()[f2]
     E, hidden, inter, topk = 8, 1024, 512, 2
-    w13d, w2d = synth.make_moe(fmt, fmt, E, hidden, inter, seed=T)
+    w13d, w2d = synth.make_moe(fmt, fmt_2, E, hidden, inter, seed=T)
     ids, tw = synth.make_routing(T, E - 1, topk, seed=T)          # expert E-1 stays empty
     x = synth.make_activations(T, hidden, seed=T + 1)
     ids[2, 1] = -1
     ids_ref = np.where(ids < 0, 0, ids)
     tw_ref = np.where(ids < 0, 0.0, tw).astype(np.float32)
     ref = O.moe_loop_chain(x, ids_ref, tw_ref, w13d, w2d, E=E, hidden=hidden, inter=inter,
-                           fmt13=oracle_kwargs(fmt), fmt2=oracle_kwargs(fmt), scale_rule="recip")
-    moe = CBMoE(fmt, fmt, E, hidden, inter, _tables(fmt, w13d["cb"]), _tables(fmt, w2d["cb"]))
-    moe.load(torch.from_numpy(w13d["qw"]), torch.from_numpy(w2d["qw"]), None, None, dev)
-    moe.method.sorted_min_pairs_per_expert = 1              # the routes' thresholds are attributes of the method
+                           fmt13=oracle_kwargs(fmt), fmt2=oracle_kwargs(fmt_2), scale_rule="recip")
+    moe = CBMoE(fmt, fmt_2, E, hidden, inter, _tables(fmt, w13d["cb"]), _tables(fmt_2, w2d["cb"]))
+    moe.load(torch.from_numpy(w13d["qw"]), torch.from_numpy(w2d["qw"]),
+             None if w13d["scale"] is None else torch.from_numpy(w13d["scale"]),
+             None if w2d["scale"] is None else torch.from_numpy(w2d["scale"]), dev)
+    moe.method.sorted_min_pairs_per_expert = 0              # the routes' thresholds are attributes of the method
+    moe.method.sorted_min_pairs_other = 0
     moe.method.prefill_min_pairs_per_expert = 1000000
     got = f32_of(moe(synth.bf16_tensor(x, dev), torch.from_numpy(tw).to(dev), torch.from_numpy(ids).to(dev)))
     torch.cuda.synchronize()
