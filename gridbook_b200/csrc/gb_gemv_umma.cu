@@ -33,7 +33,6 @@ constexpr int kDecWarps = 16;                             // four warpgroups, on
 constexpr int kCtlWarps = 6;                              // raw producer, x producer, four MMA issuers
 constexpr int kUmmaThreads = 32 * (kCtlWarps + kDecWarps);
 constexpr int kMaxRows = 128;                             // activation rows
-constexpr int kABufs = 4;                                 // operand buffers in tensor memory
 constexpr int kABufCols = 64;                             // half a superblock: 128 weights of K as bf16 pairs
 constexpr uint32_t kACol0 = 256;                          // columns [0, 256): one accumulator per MMA issuer
 constexpr uint32_t kTmemCols = 512;
@@ -92,6 +91,7 @@ struct UmmaParams {
   const int32_t* seg;        // [E+1]
   const int32_t* row_map;    // [P] output row of a sorted row, or null = identity
   int tiles_n;               // 128-row tiles per expert
+  int n_tiles;               // tiles of the launch (dense: row tiles; grouped: experts x tiles_n)
   uint16_t* y_peer[GB_PEER_MAX];   // optional: output row r lives in y_peer[r / rows_per_rank]
   int64_t rows_per_rank;     // 0 = all rows in y
 };
@@ -295,20 +295,27 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const int xs_log = p.x_stages == 8 ? 3 : 2;
 
   gb_pdl_launch_dependents();
-  // Dense: one pass over rows [0, M) of x.  Grouped: the CTA's expert, its rows of the sorted x in
-  // passes of 64 (the weights are decoded again per pass), nothing to do for an expert without rows.
-  int n0 = blockIdx.x * kBM, w_row0 = n0, seg_lo = 0, cnt = p.M;
-  if (kGrouped) {
-    gb_pdl_wait();                                         // the segment offsets come from the routing launch
-    const int e = blockIdx.x / p.tiles_n;
-    n0 = (blockIdx.x - e * p.tiles_n) * kBM;
-    w_row0 = e * (int)p.N + n0;
-    seg_lo = p.seg[e];
-    cnt = p.seg[e + 1] - seg_lo;
-    if (cnt <= 0) return;
-  }
+  // A CTA walks the 128-row tiles blockIdx.x, blockIdx.x + gridDim.x, ... (codebook copies, tensor
+  // memory and barriers are set up once; the rings run on across tiles).  Dense: one pass over rows
+  // [0, M) of x per tile.  Grouped: tile = (expert, 128 rows of it), the expert's rows of the sorted
+  // x in passes of 64 (the weights are decoded again per pass), nothing to do for an expert
+  // without rows.
+  if (kGrouped) gb_pdl_wait();                             // the segment offsets come from the routing launch
   const int pass_rows = kGrouped ? kGroupRows : p.Mpad;
-  const int n_pass = (cnt + pass_rows - 1) / pass_rows;
+  struct Tile { int n0, w_row0, seg_lo, cnt, n_pass; };
+  auto tile_at = [&](int t) {
+    Tile T;
+    T.n0 = t * kBM; T.w_row0 = T.n0; T.seg_lo = 0; T.cnt = p.M;
+    if (kGrouped) {
+      const int e = t / p.tiles_n;
+      T.n0 = (t - e * p.tiles_n) * kBM;
+      T.w_row0 = e * (int)p.N + T.n0;
+      T.seg_lo = p.seg[e];
+      T.cnt = p.seg[e + 1] - T.seg_lo;
+    }
+    T.n_pass = T.cnt > 0 ? (T.cnt + pass_rows - 1) / pass_rows : 0;
+    return T;
+  };
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRawStages; ++s) {
       gb_mbar_init(&raw_full[s], 1);
@@ -346,7 +353,10 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   if (warp == 0) {
     // ------------------------- packed weight rows -------------------------
     if (lane == 0) {
-      for (int pass = 0, it = 0; pass < n_pass; ++pass)
+      int it = 0;
+      for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x) {
+      const Tile T = tile_at(t);
+      for (int pass = 0; pass < T.n_pass; ++pass)
       for (int r = r_begin; r < r_end; ++r, ++it) {
         const int rs = it % kRawStages;
         wait_or_abort(&raw_empty[rs], ((it / kRawStages) & 1) ^ 1, abort_flag, p.status, 21);
@@ -354,7 +364,8 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
         for (int bx = 0; bx < Fm<F>::kBoxes; ++bx)
           tma_load_2d(raw + (size_t)rs * G::kStageBytes + bx * G::kBoxBytes, &map_w,
-                      (r * kSbPerStage + bx * Fm<F>::kSbPerBox) * kSb, w_row0, &raw_full[rs]);
+                      (r * kSbPerStage + bx * Fm<F>::kSbPerBox) * kSb, T.w_row0, &raw_full[rs]);
+      }
       }
     }
   } else if (warp == 1) {
@@ -362,15 +373,19 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (lane == 0) {
       gb_pdl_wait();                                         // x may come from the launch ahead
       const int k_base = r_begin * kSbPerStage * 256;
-      for (int pass = 0, g = 0; pass < n_pass; ++pass)
-      for (int u = 0; u < units; ++u, ++g) {                 // g: units since the start, over all passes
+      int g = 0;                                             // units since the start, over all tiles and passes
+      for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x) {
+      const Tile T = tile_at(t);
+      for (int pass = 0; pass < T.n_pass; ++pass)
+      for (int u = 0; u < units; ++u, ++g) {
         const int s = g & xs_mask;
         wait_or_abort(&done[s], ((uint32_t)(g >> xs_log) & 1u) ^ 1u, abort_flag, p.status, 22);
         gb_mbar_expect_tx(&full[s], (uint32_t)x_stage_bytes);
         uint8_t* dst = xs + (size_t)s * x_stage_bytes;
         const int k0 = k_base + u * 128;
-        tma_load_2d(dst, &map_x, k0, seg_lo + pass * pass_rows, &full[s]);
-        tma_load_2d(dst + slab_bytes, &map_x, k0 + 64, seg_lo + pass * pass_rows, &full[s]);
+        tma_load_2d(dst, &map_x, k0, T.seg_lo + pass * pass_rows, &full[s]);
+        tma_load_2d(dst + slab_bytes, &map_x, k0 + 64, T.seg_lo + pass * pass_rows, &full[s]);
+      }
       }
     }
   } else if (warp < kCtlWarps) {
@@ -383,16 +398,19 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       const uint32_t acc = tmem_base + (uint32_t)i * (kACol0 / (uint32_t)p.n_iss);
       const uint32_t slab16 = (uint32_t)slab_bytes >> 4;
       const uint64_t desc0 = smem_desc_sw128(gb_smem_u32(xs));
-      for (int pass = 0, g0 = 0; pass < n_pass; ++pass, g0 += units) {
-        // grouped mode: N = this pass's rows rounded up to 16; the previous pass must have been read out
+      int g0 = 0, item = 0;                                  // units / (tile, pass) items since the start
+      for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x) {
+      const Tile T = tile_at(t);
+      for (int pass = 0; pass < T.n_pass; ++pass, g0 += units, ++item) {
+        // grouped mode: N = this pass's rows rounded up to 16.  The item before must have been read out.
         uint32_t idesc = p.idesc;
         if (kGrouped) {
-          const int rows = min(pass_rows, cnt - pass * pass_rows);
+          const int rows = min(pass_rows, T.cnt - pass * pass_rows);
           idesc = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)(((rows + 15) / 16 * 16) >> 3) << 17);
-          if (pass > 0) {
-            wait_or_abort(acc_empty, (pass - 1) & 1, abort_flag, p.status, 28);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          }
+        }
+        if (item > 0) {
+          wait_or_abort(acc_empty, (item - 1) & 1, abort_flag, p.status, 28);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
         bool first = true;
         for (int u = 0; u < units; ++u) {
@@ -417,6 +435,7 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           umma_commit(&done[s]);
         }
         umma_commit(acc_full);
+      }
       }
     }
   } else {
@@ -477,12 +496,14 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const uint32_t col = lane_base + kACol0 + (uint32_t)(wg * kABufCols);
     const bool exact = *inexact == 0;
+    int it = 0, g_sb = 0, item = 0;                          // raw stages, superblocks, (tile, pass) items so far
+    for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x) {
+    const Tile T = tile_at(t);
     float rs = 0.0f;                                         // fp8 grid: this row's scale
     if constexpr (F == kFmtFp8 || F == kFmtF8L) {
-      if ((int64_t)w_row0 + row < p.rows_total) rs = __ldg(p.row_scale + w_row0 + row);
+      if (T.n_pass > 0 && (int64_t)T.w_row0 + row < p.rows_total) rs = __ldg(p.row_scale + T.w_row0 + row);
     }
-    int it = 0, g_sb = 0;                                    // raw stages so far, superblocks so far (over all passes)
-    for (int pass = 0; pass < n_pass; ++pass) {
+    for (int pass = 0; pass < T.n_pass; ++pass, ++item) {
     for (int r = r_begin; r < r_end; ++r, ++it) {
       const int rs_i = it % kRawStages;
       wait_or_abort(&raw_full[rs_i], (it / kRawStages) & 1, abort_flag, p.status, 24);
@@ -570,15 +591,15 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
 
     // ------------------------- read-out ------------------------------------
-    wait_or_abort(acc_full, pass & 1, abort_flag, p.status, 26);
+    wait_or_abort(acc_full, item & 1, abort_flag, p.status, 26);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int col_part = (warp - kCtlWarps) >> 2;            // column chunks: every fourth
     // issuers that had no unit in this slice leave their accumulator untouched
     const int n_accs = min(p.n_iss, p.n_iss == 4 ? units : sb_slice);
     const uint32_t acc_stride = kACol0 / (uint32_t)p.n_iss;
-    const int64_t out_col = (int64_t)n0 + row;
+    const int64_t out_col = (int64_t)T.n0 + row;
     const bool ok = *abort_flag == 0;
-    const int rows = min(pass_rows, cnt - pass * pass_rows);
+    const int rows = min(pass_rows, T.cnt - pass * pass_rows);
     for (int c = col_part; c < (rows + 7) / 8; c += kDecWarps / 4) {
       uint32_t v[8];
       const uint32_t taddr = lane_base + (uint32_t)(c * 8);
@@ -601,7 +622,7 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           const int m = c * 8 + i;
           if (m < rows) {
             if (kGrouped) {
-              const int jrow = seg_lo + pass * pass_rows + m;          // sorted position of the row
+              const int jrow = T.seg_lo + pass * pass_rows + m;        // sorted position of the row
               int64_t orow = p.row_map ? p.row_map[jrow] : jrow;
               uint16_t* ybase = p.y;
               if (p.rows_per_rank > 0) {                     // the row's home rank keeps it (peer store)
@@ -619,10 +640,10 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
       }
     }
-    if (kGrouped && pass + 1 < n_pass) {                     // hand the accumulators back for the next pass
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) gb_mbar_arrive(acc_empty);
+    // hand the accumulators back for the next item (pass or tile)
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) gb_mbar_arrive(acc_empty);
     }
     }
   }
@@ -805,7 +826,10 @@ int gb_gemv_umma(const void* x, int64_t M, const gb_weight* w, int act, int scal
   p.x_stages = umma_x_stages(F, p.Mpad);
   p.n_iss = p.Mpad <= 64 ? 4 : 2;
   p.status = gb_status_word();
-  dim3 grid((unsigned)((N + kBM - 1) / kBM), (unsigned)p.slices);
+  // one CTA per SM at most: a CTA walks several row tiles when the layer has more of them
+  p.n_tiles = (int)((N + kBM - 1) / kBM);
+  const int ctas_x = p.n_tiles * p.slices <= sms ? p.n_tiles : (sms / p.slices > 0 ? sms / p.slices : 1);
+  dim3 grid((unsigned)ctas_x, (unsigned)p.slices);
   GB_CUDA_OK(launch_umma<false>(F, grid, (size_t)umma_smem_bytes(F, p.Mpad), (cudaStream_t)stream_, map_w, map_x, p));
   if (p.slices > 1) {
     const int64_t MN = M * N;
@@ -877,7 +901,9 @@ int gb_moe_gemv_sorted(const void* x_sorted, const gb_weight* w, int64_t expert_
     }
     p.rows_per_rank = y_rows->rows_per_rank;
   }
-  dim3 grid((unsigned)(E * p.tiles_n), 1);
+  p.n_tiles = (int)(E * p.tiles_n);
+  const int sms = gb_sm_count();
+  dim3 grid((unsigned)(p.n_tiles < sms ? p.n_tiles : sms), 1);
   GB_CUDA_OK(launch_umma<true>(F, grid, (size_t)umma_smem_bytes(F, kGroupRows), (cudaStream_t)stream_, map_w, map_x, p));
   return GB_OK;
 }
