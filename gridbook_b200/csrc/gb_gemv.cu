@@ -931,10 +931,11 @@ int gb_gemv(const void* x, int64_t M, const gb_weight* w, int act, int scale_rul
   GB_REQUIRE(act == GB_ACT_NONE || act == GB_ACT_FP4_GROUP16 || act == GB_ACT_FP8_TOKEN, "unknown act %d", act);
   const int sms = gb_sm_count();
   if (sms <= 0) return gb_fail(GB_ECUDA, "no usable CUDA device: %s", gb_last_error());
-  if (M >= umma_min_rows() || !gb_gemv_umma_is_literal(w)) {
+  if (M >= umma_min_rows() || (umma_min_rows() <= 128 && !gb_gemv_umma_is_literal(w))) {
     // decode into tensor memory, tensor-core MMA with the weights on the M side; every weight is
     // decoded once whatever the row count.  The literal format has faster table kernels for a few
-    // rows; the product formats it serves (padded two-tier k = 16, fp8 k = 32) take it from one row on.
+    // rows; the product formats it serves (padded two-tier k = 16, fp8 k = 32 and k = 16) take it from
+    // one row on.  A threshold past 128 switches the kernel off for every format.
     rc = gb_gemv_umma(x, M, w, act, scale_rule, y, workspace, workspace_bytes, stream_);
     if (rc != GB_EUNSUPPORTED) return rc;
   }

@@ -25,8 +25,9 @@ FUSED_BUCKET_MAX_PAIRS = 32       # routed pairs up to which the grouped kernel 
 PREFILL_MIN_PAIRS_PER_EXPERT = 384
 # Below that, from this many routed pairs per expert on, the rows are sorted by expert and every
 # (expert, 128-row tile) decodes its weights once into tensor memory for a tensor-core MMA.  Literal
-# fp4 stacks have the per-pair table kernel below it (measured at 128 experts, hidden 2048, intermediate 768:
-# the per-pair kernel 164 us against 157 us at 4 pairs per expert, the decode kernel 280 against 166 at 8); stacks without that kernel (two-tier k = 16, the fp8 grid) take the sorted
+# fp4 stacks have the per-pair table kernel below it (measured at 128 experts, hidden 2048,
+# intermediate 768: per-pair kernel 164 us against 157 us at 4 pairs per expert, decode kernel 280
+# against 166 at 8).  Stacks without that kernel (two-tier k = 16, the fp8 grid) take the sorted
 # rows from SORTED_MIN_PAIRS_OTHER routed pairs in all (two tokens at top-8: 223 us against 272 us
 # on 32 experts of hidden 7168, intermediate 2048).
 SORTED_MIN_PAIRS_PER_EXPERT = 4

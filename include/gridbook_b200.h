@@ -140,7 +140,7 @@ GB_API int gb_gemv_row_batch_max(const gb_weight* w);
 
 /* Row counts at which gb_gemv changes kernel for the literal format: up to `dot_rows` rows run one
  * inner-product-table GEMV per row (default 4, at most 8), from `umma_min` rows on the tensor-core
- * decode kernel (default 5).  0 restores a default.  Process-wide; for tests and tuning.  No
+ * decode kernel (default 5; 129 switches that kernel off for every format).  0 restores a default.  Process-wide; for tests and tuning.  No
  * counterpart in the reference, whose lane selection is a set of environment flags. */
 GB_API int gb_set_row_routes(int dot_rows, int umma_min);
 

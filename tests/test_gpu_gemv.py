@@ -35,8 +35,14 @@ def _fmt(name):
 
 @pytest.mark.parametrize("name", ["lit", "k16v2", "k13v2", "k20v1", "s13", "f8k32", "f8k30", "f8k44", "f8lit"])
 @pytest.mark.parametrize("M", [1, 2, 4, 8, 16])
-def test_gemv_matches_oracle(dev, name, M):
-    from gridbook_b200 import kernels, synth
+@pytest.mark.parametrize("route", ["default", "no tensor-core decode"])
+def test_gemv_matches_oracle(dev, request, name, M, route):
+    """Every format at decode batch sizes, on the default routes and with the tensor-core decode kernel
+    switched off (the generic decode kernel and the per-row table route of the literal format)."""
+    from gridbook_b200 import _native, kernels, synth
+    if route != "default":
+        _native.set_row_routes(umma_min=129)
+        request.addfinalizer(lambda: _native.set_row_routes())
     fmt = _fmt(name)
     N, K = 203, 1024                     # ragged last tile
     d = synth.make_linear(fmt, N, K, seed=5, global_scale=(1.0 / 448.0 if name == "lit" else None))
@@ -305,7 +311,7 @@ def test_literal_row_batch_tensor_core_decode_kernel(dev, request, N, K, M):
     of one to three superblocks, one or several K slices, padded row stride, bucket applied by the
     call or beforehand, zero / subnormal / negative scale bytes."""
     from gridbook_b200 import _native, kernels, synth
-    _native.set_row_routes(umma_min=2)                        # by default it serves 17 rows and more
+    _native.set_row_routes(umma_min=2)                        # by default it serves 5 rows and more
     request.addfinalizer(lambda: _native.set_row_routes())
     fmt = _fmt("lit")
     d = synth.make_linear(fmt, N, K, seed=N + K + M, global_scale=1.0 / 448.0)
