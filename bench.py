@@ -43,7 +43,9 @@ NOMINAL_TFLOPS = {"bf16": 2250.0, "fp8": 4500.0, "fp4": 9000.0}       # dense, p
 TRAFFIC = {"gemv_tab_kernel": (1.002, "profiles/gemv_tab_kernel_literal_m1_gate_up.md"),
            "gemv_dot_kernel": (1.002, "profiles/gemv_dot_kernel_literal_m1_gate_up.md"),
            "gemv_kernel": (1.01, "profiles/gemv_kernel_k16v2_m1_gate_up.md"),
-           "umma_decode_kernel": (1.02, "profiles/umma_decode_kernel_literal_m64_gate_up.md")}
+           "umma_decode_kernel": (1.006, "profiles/umma_decode_kernel_literal_k16v2_m16_gate_up.md"),
+           # two-tier layers are fetched in 80-byte superblock slots: 80 / 73 of the algorithmic bytes
+           "umma_decode_kernel/k16v2": (1.10, "profiles/umma_decode_kernel_literal_k16v2_m16_gate_up.md")}
 
 
 def get_format(name):
@@ -120,6 +122,15 @@ def physical_gpu_index(local_rank: int):
         if local_rank < len(parts):
             return parts[local_rank]
     return local_rank
+
+
+_T0 = time.time()
+
+
+def progress(what):
+    """One stderr line per leg (rank 0): where a run that is cut off had got to."""
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(f"[bench {time.time() - _T0:7.1f}s] {what}", file=sys.stderr, flush=True)
 
 
 def timed_ms(fn, reps, sync):
@@ -216,7 +227,9 @@ def run_gpu(args):
         big_bytes = 2 * (2 * world * 64 * (BIG_MOE["hidden"] * 2 + BIG_MOE["topk"] * 4)
                          + 64 * BIG_MOE["topk"] * BIG_MOE["hidden"] * 2)
         peers = PeerGroup(dense_bytes + moe_bytes + big_bytes + (64 << 20), device)
+    progress(f"start: {world} rank(s), {args.layers} layers, M={M}, format {args.format}")
     stack = build_stack(fmt, gscale, args.layers, device, rank, world, peers=peers, max_rows=16)
+    progress("stack built")
     gen = torch.Generator(device=device).manual_seed(1234)
     inputs_dev = [torch.randn(M, K, generator=gen, device=device).to(torch.bfloat16) for _, _, K in PROJECTIONS]
     # q and kv read the same activation row (the block's normed hidden state): at M = 1 on one GPU
@@ -285,6 +298,7 @@ def run_gpu(args):
             run_step()
         barrier()
     ms_total = ev0.elapsed_time(ev1)
+    progress("timed region done")
 
     # ---- end to end: host buffers in, host buffers out, copies inside the timed region ----
     def e2e_step():
@@ -323,9 +337,11 @@ def run_gpu(args):
     used_graph = graph is not None
     kgraph = None
 
+    progress("e2e and kernel-only legs done")
     # ---- correctness evidence for the sharded paths, outside every timed region ----
     parity = parity_check(world, rank, device, peers) if world > 1 else None
 
+    progress("parity leg done")
     # ---- the other decode batch sizes of the configuration (same stack, through the linear method) ----
     dense_m = {}
     if not args.no_msweep:
@@ -355,11 +371,41 @@ def run_gpu(args):
                 tot = float(t[1])
             dense_m[str(m_other)] = {"gb_s": round(tot / (ms_m * 1e-3) / 1e9, 1), "ms_per_step": round(ms_m, 3)}
             mg = None
+    progress("other row counts done")
+    # ---- N > 1: the same stack, whole, on rank 0 alone: the one-GPU time each sharded time is set against ----
+    one_gpu = None
+    if world > 1 and not args.no_msweep:
+        dist.barrier()
+        if rank == 0:
+            whole = build_stack(fmt, gscale, args.layers, device, 0, 1)
+            one_gpu = {}
+            for m_ref in sorted({M, 4, 16}):
+                xs = [torch.randn(m_ref, K, generator=gen, device=device).to(torch.bfloat16) for _, _, K in PROJECTIONS]
+
+                def whole_step():
+                    for row in whole:
+                        for lin, x in zip(row, xs):
+                            lin(x)
+
+                runner, wg = graphed(whole_step)
+                for _ in range(3):
+                    runner()
+                one_gpu[str(m_ref)] = round(timed_ms(runner, 5, torch.cuda.synchronize), 3)
+                wg = None
+            whole = None
+            torch.cuda.empty_cache()
+        dist.barrier()
+    progress("one-GPU reference done")
     fmts = bench_formats(args, device) if (world == 1 and not args.no_formats) else None
+    progress("formats leg done")
     moe = None if args.no_moe else bench_moe(args, device, world, rank, peers)
+    progress("routed layer leg done")
     big = None if args.no_moe else bench_big_moe(args, device, world, rank, peers)
+    progress("configuration 4 leg done")
     prefill = bench_prefill(args, device) if (world == 1 and not args.no_prefill) else None
+    progress("prefill leg done")
     nccl = bench_nccl(args, device, world, rank, locals_, inputs_dev) if (world > 1 and not args.no_nccl) else None
+    progress("NCCL comparison leg done")
     status = _native.device_status(local_rank)
 
     times = torch.tensor([ms_total, ms_e2e, ms_kernel, float(bytes_per_step_local)], dtype=torch.float64,
@@ -391,9 +437,11 @@ def run_gpu(args):
     launch_bytes = bytes_per_step_local / n_linear
     launch_ms = ms_kernel / args.steps / n_linear
     achieved = launch_bytes / (launch_ms * 1e-3) / 1e9
-    dominant_kernel = ("gemv_tab_kernel" if tab else "gemv_dot_kernel" if (M == 1 and args.format == "literal")
-                       else "umma_decode_kernel" if (M > 16 and args.format == "literal") else "gemv_kernel")
-    traffic_ratio, traffic_source = TRAFFIC[dominant_kernel]
+    w0 = locals_[0][3]._cb_weight if len(locals_[0]) > 3 else locals_[0][0]._cb_weight
+    on_umma = 16 < kernels.row_batch_max_rows(w0) >= M and (args.format != "literal" or M >= 5)
+    dominant_kernel = ("gemv_tab_kernel" if tab else "umma_decode_kernel" if on_umma
+                       else "gemv_dot_kernel" if (M <= 4 and args.format == "literal") else "gemv_kernel")
+    traffic_ratio, traffic_source = TRAFFIC.get(f"{dominant_kernel}/{args.format}", TRAFFIC[dominant_kernel])
     line = {
         "metric": METRIC,
         "value": round(gbs, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -423,6 +471,11 @@ def run_gpu(args):
         "device_status": status,
         "parity": parity,
         "dense_other_m": dense_m or None,
+        # N > 1: ms per step of the WHOLE stack on rank 0 alone and the sharded stack's speed-up over it
+        "one_gpu": None if one_gpu is None else {
+            "ms_per_step": one_gpu,
+            "speedup": {m: round(t / (ms_total / args.steps if int(m) == M else dense_m[m]["ms_per_step"]), 3)
+                        for m, t in one_gpu.items() if int(m) == M or m in dense_m}},
         "formats": fmts,
         "moe": moe,
         "config4": big,
@@ -684,12 +737,10 @@ def bench_big_moe(args, device, world, rank, peers=None):
     import torch
     from gridbook_b200 import synth
     from gridbook_b200.linear import CBLinear
-    if world not in (1, 8):
-        return None
     f13, _ = get_format("fp8lit")
     f2, g2 = get_format("literal")
     E, topk, hidden, inter = (BIG_MOE[k] for k in ("E", "topk", "hidden", "inter"))
-    shape = dict(BIG_MOE, E=E if world == 8 else E // 8)
+    shape = dict(BIG_MOE, E=E if world > 1 else E // 8)
     layers = _moe_layers(f13, f2, shape, device, world, rank, peers, 2, 64, seed=91)
     gen = torch.Generator(device=device).manual_seed(91 + rank)
     # the shared expert: a dense MLP of the same two formats on every rank
@@ -714,8 +765,8 @@ def bench_big_moe(args, device, world, rank, peers=None):
     tokens = T * world
     return {"workload": f"routed MoE layer, {E} experts top-{topk} + 1 shared, hidden {hidden}, intermediate {inter}, "
                         f"FP8-grid gate_up + NVFP4-grid down, {tokens} tokens"
-                        + ("" if world == 8 else " (one rank's share of the 8-way expert-parallel layer: 32 experts, "
-                                                 "512 routed pairs, shared expert on 64 tokens)"),
+                        + ("" if world > 1 else " (one rank's share of the 8-way expert-parallel layer: 32 experts, "
+                                                "512 routed pairs, shared expert on 64 tokens)"),
             "parallelism": f"expert-parallel x{world}" if world > 1 else "1 GPU (1/8 share)",
             "tok_s": round(tokens / (ms_all * 1e-3), 1), "ms_per_layer": round(ms_all, 4),
             "routed_only_ms_per_layer": round(ms_routed, 4),

@@ -411,12 +411,112 @@ int launch_expand_literal(const gb_weight* w, int64_t row0, int64_t nrows, void*
   GB_LAUNCH_OK("expand_literal_nvfp4_kernel");
   return GB_OK;
 }
+// The fp8 product formats k = 32 (four sub-tables of two values) and k = 16 (two sub-tables of four
+// values) -> the E4M3 value plane, one byte per weight: the sub-table entries are copied through as
+// they are.  Eight lanes per (row, superblock); a lane takes two codewords of each half of the
+// superblock, so that every store instruction of the eight lanes writes 128 contiguous bytes.  The
+// sub-tables sit in shared memory as 32-bit words, eight copies each (copy = lane mod 8: lanes of
+// different copies never share a bank).  Memory-bound: 128 or 64 bytes read and 256 written per
+// 256 weights.
+constexpr int kF8Unroll = 4;
+
+template <bool kK32>
+__global__ void __launch_bounds__(kThreads)
+expand_fp8_fast_kernel(const uint8_t* __restrict__ qw, int64_t row_stride, const uint8_t* __restrict__ codebook,
+                       int64_t nrows, int64_t n_sb, uint4* __restrict__ out) {
+  constexpr int kEntries = kK32 ? 1024 : 512;              // 4 x 256 two-byte or 2 x 256 four-byte entries
+  constexpr int kSb = kK32 ? 128 : 64;
+  __shared__ uint32_t lut[kEntries * 8];
+  for (int e = threadIdx.x; e < kEntries; e += kThreads) {
+    const uint32_t v = kK32 ? (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(codebook) + e)
+                            : __ldg(reinterpret_cast<const uint32_t*>(codebook) + e);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) lut[e * 8 + j] = v;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, sub = lane & 7, which = lane >> 3;
+  const uint32_t* my = lut + sub;
+  const int64_t units = nrows * n_sb;
+  const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
+  for (int64_t u0 = ((int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5)) * (4 * kF8Unroll); u0 < units;
+       u0 += warps * (4 * kF8Unroll)) {
+    uint32_t in[kF8Unroll][kK32 ? 4 : 2];                  // two codewords of the first half, two of the second
+#pragma unroll
+    for (int i = 0; i < kF8Unroll; ++i) {
+      const int64_t u = u0 + 4 * i + which < units ? u0 + 4 * i + which : u0;
+      const int64_t r = u / n_sb, sb = u - r * n_sb;
+      const uint8_t* p = qw + r * row_stride + sb * kSb;
+      if (kK32) {
+        const uint2 a = __ldg(reinterpret_cast<const uint2*>(p) + sub), b = __ldg(reinterpret_cast<const uint2*>(p + 64) + sub);
+        in[i][0] = a.x; in[i][1] = a.y; in[i][2] = b.x; in[i][3] = b.y;
+      } else {
+        in[i][0] = __ldg(reinterpret_cast<const uint32_t*>(p) + sub);
+        in[i][1] = __ldg(reinterpret_cast<const uint32_t*>(p + 32) + sub);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kF8Unroll; ++i) {
+      const int64_t u = u0 + 4 * i + which;
+      if (u >= units) continue;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint4 o;
+        if (kK32) {
+          const uint32_t c0 = in[i][2 * half], c1 = in[i][2 * half + 1];
+          o.x = my[(c0 & 0xffu) * 8] | (my[(256 + ((c0 >> 8) & 0xffu)) * 8] << 16);
+          o.y = my[(512 + ((c0 >> 16) & 0xffu)) * 8] | (my[(768 + (c0 >> 24)) * 8] << 16);
+          o.z = my[(c1 & 0xffu) * 8] | (my[(256 + ((c1 >> 8) & 0xffu)) * 8] << 16);
+          o.w = my[(512 + ((c1 >> 16) & 0xffu)) * 8] | (my[(768 + (c1 >> 24)) * 8] << 16);
+        } else {
+          const uint32_t c = in[i][half];                  // two 16-bit codewords
+          o.x = my[(c & 0xffu) * 8];
+          o.y = my[(256 + ((c >> 8) & 0xffu)) * 8];
+          o.z = my[((c >> 16) & 0xffu) * 8];
+          o.w = my[(256 + (c >> 24)) * 8];
+        }
+        out[u * 16 + half * 8 + sub] = o;
+      }
+    }
+  }
+}
+
+int launch_expand_fp8_fast(const gb_weight* w, int64_t row0, int64_t nrows, void* out, void* stream) {
+  const bool k32 = w->fmt.k_bits == 32;
+  const int64_t n_sb = w->K / 256, units = nrows * n_sb;
+  const int64_t per_cta = (kThreads / 32) * 4 * kF8Unroll;
+  int64_t blocks = (units + per_cta - 1) / per_cta;
+  const int64_t cap = (int64_t)gb_sm_count() * 8;
+  if (cap > 0 && blocks > cap) blocks = cap;
+  gb_count_launch();
+  const uint8_t* base = w->qw + row0 * w->row_stride;
+  if (k32)
+    expand_fp8_fast_kernel<true><<<(unsigned)blocks, kThreads, 0, (cudaStream_t)stream>>>(
+        base, w->row_stride, (const uint8_t*)w->codebook, nrows, n_sb, (uint4*)out);
+  else
+    expand_fp8_fast_kernel<false><<<(unsigned)blocks, kThreads, 0, (cudaStream_t)stream>>>(
+        base, w->row_stride, (const uint8_t*)w->codebook, nrows, n_sb, (uint4*)out);
+  GB_LAUNCH_OK("expand_fp8_fast_kernel");
+  return GB_OK;
+}
 }  // namespace
 
 extern "C" {
 
 int gb_expand_fp8(const gb_weight* w, int64_t row0, int64_t nrows, void* out, void* stream) {
   GB_REQUIRE(w && w->fmt.grid == GB_GRID_FP8, "gb_expand_fp8 wants an fp8-grid weight");
+  const gb_format& f = w->fmt;
+  if (f.mode == GB_MODE_PRODUCT && ((f.k_bits == 32 && f.n_sub == 4 && f.type_size == 128) ||
+                                    (f.k_bits == 16 && f.n_sub == 2 && f.type_size == 64)) &&
+      w->cb_row_offset == nullptr && ((uintptr_t)w->codebook & 3u) == 0 && ((uintptr_t)out & 15u) == 0 &&
+      ((uintptr_t)w->qw & 15u) == 0 && w->row_stride % 16 == 0) {
+    int rc = gb_check_weight(w);
+    if (rc != GB_OK) return rc;
+    GB_REQUIRE(out != nullptr, "null output pointer");
+    GB_REQUIRE(row0 >= 0 && nrows >= 0 && row0 + nrows <= w->rows, "rows [%lld, %lld) outside [0, %lld)",
+               (long long)row0, (long long)(row0 + nrows), (long long)w->rows);
+    if (nrows == 0) return GB_OK;
+    return launch_expand_fp8_fast(w, row0, nrows, out, stream);
+  }
   return launch_expand<kOutFp8>(w, row0, nrows, out, nullptr, 0, stream);
 }
 
@@ -440,7 +540,9 @@ int gb_expand_fp4_nvfp4(const gb_weight* w, int64_t row0, int64_t nrows, void* o
       ((uintptr_t)out_sf & 3u) == 0 && ((uintptr_t)w->qw & 15u) == 0 && w->row_stride % 16 == 0 && kThreads == 256) {
     int rc = gb_check_weight(w);
     if (rc != GB_OK) return rc;
-    GB_REQUIRE(out_packed != nullptr && row0 >= 0 && nrows >= 0 && row0 + nrows <= w->rows, "bad row window");
+    GB_REQUIRE(out_packed != nullptr, "null output pointer");
+    GB_REQUIRE(row0 >= 0 && nrows >= 0 && row0 + nrows <= w->rows, "rows [%lld, %lld) outside [0, %lld)",
+               (long long)row0, (long long)(row0 + nrows), (long long)w->rows);
     if (nrows == 0) return GB_OK;
     return launch_expand_literal(w, row0, nrows, out_packed, out_sf, sf_swizzled == 2, stream);
   }

@@ -1,25 +1,26 @@
 // Decode-batch linear on the tensor cores, without a decoded copy in HBM or in shared memory:
-// y[M, N] = x[M, K] . W^T for 2 <= M <= 128 activation rows.
+// y[M, N] = x[M, K] . W^T for 1 <= M <= 128 activation rows.
 //
 // The WEIGHTS are the M side of the MMA and live in TENSOR MEMORY: a CTA owns 128 weight rows and
 // a K slice.  One warp streams the packed rows into shared memory with tiled TMA loads, one warp
 // streams the matching 64-wide K slabs of the (bucketed) activations with the 128-byte swizzle,
-// eight warps decode.  A decoder thread owns ONE weight row (= its tensor-memory lane): it reads
+// sixteen warps decode.  A decoder thread owns ONE weight row (= its tensor-memory lane): it reads
 // the row's bytes of a superblock with 16-byte loads (rows are an odd number of 16-byte units apart
 // in shared memory, so eight neighbouring rows hit eight bank groups) and per codeword its
 // codebook entries from copies that are replicated so that the lanes of a load phase never share
 // a bank; the decode contract's bf16(value * scale) is one packed bf16 multiply where both factors
 // are exact in bf16 (fp4 grid) and an fp32 multiply + one rounding otherwise (fp8 grid); sixteen
-// decoded bf16 pairs go to the lane's columns with one tcgen05.st.  One thread issues tcgen05.mma
-// (A from tensor memory, M = 128 weight rows, N = activation rows padded to 16, kind::f16); the
-// fp32 accumulators (several, used in turn, when the rows leave room) live in tensor memory too
-// and never leave it during the K loop.  The two decoder warpgroups take superblocks in turn, each
-// with two half-superblock operand buffers (4 x 64 columns), so decoding, the MMAs of the buffer
-// before and the loads overlap.  The decoders read the accumulators out at the end (lane = weight
-// row, column = activation row) and store bf16, or fp32 partial sums per K slice that a small
-// second kernel adds.
+// decoded bf16 pairs go to the lane's columns with one tcgen05.st.  One thread per operand buffer
+// issues tcgen05.mma (A from tensor memory, M = 128 weight rows, N = activation rows padded to 16,
+// kind::f16) into its own fp32 accumulator, which lives in tensor memory too and never leaves it
+// during the K loop.  Four warpgroups of decoders, one per operand buffer (half a superblock of K,
+// 64 columns), take the units in turn, so decoding, the MMAs of the units before and the loads
+// overlap.  The decoders read the accumulators out at the end (lane = weight row, column =
+// activation row), add them and store bf16, or fp32 partial sums per K slice that a small second
+// kernel adds (summing them in the last CTA of a tile to arrive instead was measured: slower from
+// 16 rows on - one CTA's serial L2 reads against a launch that uses the whole GPU).
 //
-// Three packed formats: the literal one (fp4 grid, full k = 8, E4M3 scale bytes: 48-byte
+// Four packed formats: the literal one (fp4 grid, full k = 8, E4M3 scale bytes: 48-byte
 // superblocks), the two-tier product format fp4 k = 16 with its superblocks padded from 73 to 80
 // bytes (so that rows can be fetched by TMA), and the fp8 product format k = 32 (128 bytes).
 #include "gb_common.cuh"

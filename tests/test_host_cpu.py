@@ -457,3 +457,30 @@ def test_engine_methods_refuse_a_tensor_parallel_world(monkeypatch):
     assert C.PrismaQuantConfig(dict(raw)).get_quant_method(Linear(), "m.down_proj") is not None
     monkeypatch.setattr(C, "_engine_tensor_parallel_world_size", lambda: None)       # no engine: stand-alone use
     assert C.PrismaQuantConfig(dict(raw)).get_quant_method(Linear(), "m.down_proj") is not None
+
+
+def test_padded_superblock_layout_keeps_the_bytes_and_the_oracle_reads_it():
+    """Two-tier superblocks moved into 80-byte slots (the resident layout the tensor-core decode kernel
+    fetches by TMA): the format reports the stride as its type_size and the shipped size as its packed
+    size, the padding is zero, and the oracle decodes the padded rows to the same weights."""
+    import numpy as np
+    from gridbook_b200 import codec, formats, synth
+    from oracle import cb_oracle as O, oracle_kwargs
+    fmt = formats.NVFP4_CB_K16
+    pad = fmt.padded(80)
+    assert (fmt.type_size, pad.type_size, pad.packed_type_size, pad.sb_pad) == (73, 80, 73, 7)
+    assert pad.bits_per_weight() == fmt.bits_per_weight() and pad.packed_row_bytes(1024) == 4 * 73
+    assert pad.row_bytes(1024) == 4 * 80 and pad.to_native().type_size == 80
+    with pytest.raises(ValueError):
+        fmt.padded(96)
+    d = synth.make_linear(fmt, 6, 1024, seed=3)
+    q80 = codec.pad_superblocks(torch.from_numpy(d["qw"]), 73, 80)
+    assert q80.shape == (6, 320)
+    blocks = q80.reshape(6, 4, 80)
+    assert torch.equal(blocks[..., :73].reshape(6, -1), torch.from_numpy(d["qw"])) and int(blocks[..., 73:].sum()) == 0
+    off = np.zeros(6, np.int32)
+    w73 = O.reconstruct_weight(d["qw"], d["cb"], off, N=6, K=1024, compose=d["compose"], **oracle_kwargs(fmt))
+    w80 = O.reconstruct_weight(q80.numpy(), d["cb"], off, N=6, K=1024, compose=d["compose"], **oracle_kwargs(pad))
+    assert np.array_equal(w73, w80)
+    with pytest.raises(ValueError):
+        codec.pad_superblocks(torch.zeros(2, 100, dtype=torch.uint8), 73, 80)
