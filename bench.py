@@ -130,7 +130,15 @@ _T0 = time.time()
 def progress(what):
     """One stderr line per leg (rank 0): where a run that is cut off had got to."""
     if int(os.environ.get("RANK", "0")) == 0:
-        print(f"[bench {time.time() - _T0:7.1f}s] {what}", file=sys.stderr, flush=True)
+        status = ""
+        try:
+            from gridbook_b200 import _native
+            import torch
+            if torch.cuda.is_available() and torch.cuda.is_initialized():
+                status = f" (device status {_native.device_status(torch.cuda.current_device())})"
+        except Exception:        # a progress line must never end the run
+            pass
+        print(f"[bench {time.time() - _T0:7.1f}s] {what}{status}", file=sys.stderr, flush=True)
 
 
 def timed_ms(fn, reps, sync):
@@ -258,7 +266,10 @@ def run_gpu(args):
     # warm-up eagerly (also settles allocator and NCCL), then capture one step
     if world > 1:
         dist.barrier()            # the peer exchange waits two seconds for a late rank, no longer
+    progress("first barrier passed")
     last = step()
+    torch.cuda.synchronize()
+    progress("first eager step done")
     n0 = _native.launch_count()
     last = step()
     launches_per_step = _native.launch_count() - n0      # this library's kernels in one step
@@ -276,6 +287,8 @@ def run_gpu(args):
             graph = None
             torch.cuda.synchronize()
 
+    progress("step captured" if graph is not None else "running eagerly")
+
     def run_step():
         if graph is not None:
             graph.replay()
@@ -285,6 +298,7 @@ def run_gpu(args):
     for _ in range(args.warmup):
         run_step()
     barrier()
+    progress("warm-up done")
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(physical_gpu_index(local_rank)) as clocks:
         ev0.record()
@@ -294,7 +308,12 @@ def run_gpu(args):
         barrier()
         # keep the GPU under the same load for a moment, so that the sampler (one row every 50 ms)
         # sees it: the timed region itself lasts a few tens of milliseconds
-        for _ in range(min(2000, max(1, int(300.0 / max(ev0.elapsed_time(ev1) / args.steps, 0.05))))):
+        # (every rank must run the SAME number of steps - a step is a sequence of exchanges - so the
+        # count comes from one number all ranks share, not from each rank's own clock)
+        t_step = torch.tensor([ev0.elapsed_time(ev1) / args.steps], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t_step, op=dist.ReduceOp.MAX)
+        for _ in range(min(2000, max(1, int(300.0 / max(float(t_step[0]), 0.05))))):
             run_step()
         barrier()
     ms_total = ev0.elapsed_time(ev1)
@@ -698,11 +717,12 @@ def bench_moe(args, device, world, rank, peers=None):
     # one GPU also times two larger batches: they take the sorted-rows and the grouped-GEMM tensor-core routes
     for T in ((1, 16, 64, 256, 1024, 4096) if world == 1 else (1, 16, 64, 256)):
         ms_layer, ids = one(T, T + 13 * rank)
+        progress(f"routed layer, {T} tokens per rank")
         entry = {"tok_s": round(world * T / (ms_layer * 1e-3), 1), "ms_per_layer": round(ms_layer, 4)}
         if world == 1:
             # roofline view: packed bytes of the experts this batch touches, each counted once
             touched = int(np.unique(ids[ids >= 0]).size)
-            per_expert = fmt.row_bytes(hidden) * 2 * inter + fmt.row_bytes(inter) * hidden
+            per_expert = fmt.packed_row_bytes(hidden) * 2 * inter + fmt.packed_row_bytes(inter) * hidden
             gbs = touched * per_expert / (ms_layer * 1e-3) / 1e9
             entry.update({"experts_touched": touched, "weight_gb_s": round(gbs, 1),
                           "pct_hbm_peak": round(100.0 * gbs / peaks["hbm_gbs"], 2)})
@@ -717,6 +737,7 @@ def bench_moe(args, device, world, rank, peers=None):
         if Tg % world:
             continue
         ms_layer, _ = one(Tg // world, 1000 + Tg + 13 * rank)
+        progress(f"routed layer, {Tg} tokens in all")
         strong[str(Tg)] = {"tok_s": round(Tg / (ms_layer * 1e-3), 1), "ms_per_layer": round(ms_layer, 4),
                            "tokens_per_rank": Tg // world}
     return {"workload": f"routed MoE layer, {E} experts top-{topk}, hidden {hidden}, intermediate {inter}, "
@@ -742,6 +763,7 @@ def bench_big_moe(args, device, world, rank, peers=None):
     E, topk, hidden, inter = (BIG_MOE[k] for k in ("E", "topk", "hidden", "inter"))
     shape = dict(BIG_MOE, E=E if world > 1 else E // 8)
     layers = _moe_layers(f13, f2, shape, device, world, rank, peers, 2, 64, seed=91)
+    progress("configuration 4: layers built")
     gen = torch.Generator(device=device).manual_seed(91 + rank)
     # the shared expert: a dense MLP of the same two formats on every rank
     sh13 = CBLinear(f13, hidden, [inter, inter], [synth.codebook_tables(f13, 8)], prefix="shared.gate_up")
@@ -761,6 +783,7 @@ def bench_big_moe(args, device, world, rank, peers=None):
     can_graph = world == 1 or peers is not None
     tw_d, ids_d = torch.from_numpy(tw).to(device), torch.from_numpy(ids).to(device)
     ms_routed = _time_layers(layers, x, tw_d, ids_d, device, world, can_graph, flush)
+    progress("configuration 4: routed part timed")
     ms_all = _time_layers(layers, x, tw_d, ids_d, device, world, can_graph, flush, extra=shared)
     tokens = T * world
     return {"workload": f"routed MoE layer, {E} experts top-{topk} + 1 shared, hidden {hidden}, intermediate {inter}, "
@@ -770,7 +793,7 @@ def bench_big_moe(args, device, world, rank, peers=None):
             "parallelism": f"expert-parallel x{world}" if world > 1 else "1 GPU (1/8 share)",
             "tok_s": round(tokens / (ms_all * 1e-3), 1), "ms_per_layer": round(ms_all, 4),
             "routed_only_ms_per_layer": round(ms_routed, 4),
-            "route": str(getattr(layers[0]._local, "_cb_route", ""))}
+            "route": str(getattr(layers[0]._local, "_cb_route", "") or getattr(layers[0], "route", ""))}
 
 
 # ----------------------------------------------------------------------------- prefill leg

@@ -33,9 +33,14 @@ def _c_linear(x, d):
 
 
 @pytest.mark.parametrize("N,K", [(64, 256), (200, 1024), (264, 1280), (1000, 2816), (6144, 5120), (5120, 6144),
-                                 (2048, 5120), (5120, 17408), (34816, 5120), (4096, 4096)])
-def test_one_matrix_against_oracle(dev, N, K):
+                                 (2048, 5120), (5120, 17408), (34816, 5120), (4096, 4096),
+                                 # the shards of the same five projections over four and eight ranks
+                                 (1536, 5120), (512, 5120), (1280, 6144), (8704, 5120), (1280, 17408),
+                                 (768, 5120), (256, 5120), (640, 6144), (4352, 5120), (640, 17408)])
+def test_one_matrix_against_oracle(dev, request, N, K):
     from gridbook_b200 import _native, kernels, synth
+    _native.set_wait_limit_ms(200)           # a wait that cannot end shows as a status, not as minutes
+    request.addfinalizer(lambda: _native.set_wait_limit_ms(0))
     fmt = _literal()
     d = synth.make_linear(fmt, N, K, seed=N + K, global_scale=1.0 / 448.0)
     x = synth.make_activations(1, K, seed=K)
