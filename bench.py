@@ -817,6 +817,8 @@ def bench_prefill(args, device):
         if args.prefill_shape and name != args.prefill_shape:
             continue
         for variant in ("literal", "fp8lit"):
+            if args.prefill_variant and variant != args.prefill_variant:
+                continue
             fmt, gscale = get_format(variant)
             lin = CBLinear(fmt, K, list(parts), [synth.codebook_tables(fmt, 3)], global_scale=gscale)
             ws = None if fmt.is_fp4 else (torch.rand(N, generator=gen, device=device) + 0.5) * 0.02
@@ -1067,6 +1069,8 @@ def main():
     ap.add_argument("--prefill-shape", default=None, choices=[n for n, _, _ in PROJECTIONS],
                     help="prefill leg: this projection only (small profiling captures)")
     ap.add_argument("--prefill-m", type=int, default=0, help="prefill leg: this row count only")
+    ap.add_argument("--prefill-variant", choices=["literal", "fp8lit"], default=None,
+                    help="prefill leg: this grid's variant only (default both)")
     ap.add_argument("--only", default=None, choices=[n for n, _, _ in PROJECTIONS],
                     help="restrict the stack to one projection (small profiling captures)")
     args = ap.parse_args()
