@@ -17,8 +17,15 @@ REF_DIR = os.path.join(HERE, "_ref")
 FILES = (("tests/cb_torch_reference.py", "cb_torch_reference.py"), ("gridbook/codec.py", "codec.py"))
 
 
-def make(reference_root: str = "/root/reference") -> bool:
+def default_reference_root() -> str:
+    """Where the reference checkout is looked for: $GRIDBOOK_REFERENCE, else a folder named
+    `reference` beside this repository."""
+    return os.environ.get("GRIDBOOK_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def make(reference_root: str | None = None) -> bool:
     """Copies the files when `reference_root` holds them; returns whether oracle/_ref is complete."""
+    reference_root = reference_root or default_reference_root()
     if all(os.path.exists(os.path.join(reference_root, src)) for src, _ in FILES):
         os.makedirs(REF_DIR, exist_ok=True)
         for src, dst in FILES:
@@ -43,5 +50,5 @@ def load():
 
 
 if __name__ == "__main__":
-    ok = make(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ok = make(sys.argv[1] if len(sys.argv) > 1 else None)
     print("oracle/_ref", "ready" if ok else "not available (no reference checkout here)")
