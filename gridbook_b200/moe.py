@@ -32,6 +32,10 @@ PREFILL_MIN_PAIRS_PER_EXPERT = 384
 # on 32 experts of hidden 7168, intermediate 2048).
 SORTED_MIN_PAIRS_PER_EXPERT = 4
 SORTED_MIN_PAIRS_OTHER = 16
+# Stacks the sorted-rows kernel does not decode (per-role codebooks, other widths and modes) go from
+# the decode kernel's 16-row passes straight to the decoded stack + grouped GEMM, whose crossover
+# with the decode kernel was measured at ~800 tokens of 128 experts top-8.
+PREFILL_MIN_PAIRS_OTHER = 50
 
 
 def _row_bytes(in_features: int, type_size: int) -> int:
@@ -58,6 +62,7 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         self.pair_kernel_max_pairs = PAIR_KERNEL_MAX_PAIRS
         self.sorted_min_pairs_per_expert = SORTED_MIN_PAIRS_PER_EXPERT
         self.sorted_min_pairs_other = SORTED_MIN_PAIRS_OTHER
+        self.prefill_min_pairs_other = PREFILL_MIN_PAIRS_OTHER
         self.pad_two_tier_superblocks = True   # fp4 k = 16 two-tier stacks: 73-byte superblocks in 80-byte slots
         self.prefill_min_pairs_per_expert = PREFILL_MIN_PAIRS_PER_EXPERT
 
@@ -246,7 +251,11 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
             return torch.empty_like(x)
         x2 = x.reshape(T, -1).to(torch.bfloat16).contiguous()
         ids = topk_ids.to(torch.int32).contiguous()
-        if T * topk >= self.prefill_min_pairs_per_expert * layer._cb_E:
+        sorted_ok = (kernels.moe_gemv_sorted_applies(layer._cb_w13) and kernels.moe_gemv_sorted_applies(layer._cb_w2)
+                     and not (layer._cb_w2.fmt.is_fp4 and layer._cb_inter % 16))
+        prefill_min = (self.prefill_min_pairs_per_expert if sorted_ok
+                       else min(self.prefill_min_pairs_per_expert, self.prefill_min_pairs_other))
+        if T * topk >= prefill_min * layer._cb_E:
             return self._apply_prefill(layer, x2, topk_weights, ids, rule).to(x.dtype).reshape(x.shape)
         pair_kernel = kernels.pair_kernel_applies(layer._cb_w13) and kernels.pair_kernel_applies(layer._cb_w2)
         if T * topk >= (self.sorted_min_pairs_per_expert * layer._cb_E if pair_kernel else self.sorted_min_pairs_other):
