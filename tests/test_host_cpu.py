@@ -484,3 +484,43 @@ def test_padded_superblock_layout_keeps_the_bytes_and_the_oracle_reads_it():
     assert np.array_equal(w73, w80)
     with pytest.raises(ValueError):
         codec.pad_superblocks(torch.zeros(2, 100, dtype=torch.uint8), 73, 80)
+
+
+def _cpu_weight(fmt, rows=256, K=1024, experts=1, offsets=False):
+    """A PackedWeight over CPU tensors: enough for the route predicates, which look at formats,
+    strides and alignment only."""
+    from gridbook_b200.kernels import PackedWeight
+    rb = fmt.row_bytes(K)
+    qw = torch.zeros((experts, rows, rb) if experts > 1 else (rows, rb), dtype=torch.uint8)
+    cb = torch.zeros(4096, dtype=torch.bfloat16 if fmt.is_fp4 else torch.uint8)
+    return PackedWeight(qw, cb, fmt, K, rows, rb, torch.zeros(rows, dtype=torch.int32) if offsets else None, None,
+                        None if fmt.is_fp4 else torch.ones(rows), 1.0, rows * rb if experts > 1 else 0, experts)
+
+
+def test_route_predicates_follow_the_formats_the_kernels_decode():
+    """Which stacks take the sorted-rows tensor-core route and which the per-pair table kernel: the
+    literal fp4 format has both; the two-tier k = 16 format only in 80-byte superblock slots; the fp8
+    product formats k = 32 / k = 16; nothing with per-role codebooks or rows that are not whole
+    128-row tiles."""
+    from gridbook_b200 import formats as F, kernels
+    lit, k16, f32, f16 = F.NVFP4_LITERAL, F.NVFP4_CB_K16, F.FP8_CB_K32, F.FP8_LITERAL
+    assert kernels.moe_gemv_sorted_applies(_cpu_weight(lit, experts=4))
+    assert kernels.pair_kernel_applies(_cpu_weight(lit, experts=4))
+    assert not kernels.moe_gemv_sorted_applies(_cpu_weight(k16, experts=4))            # 73-byte superblocks
+    assert kernels.moe_gemv_sorted_applies(_cpu_weight(k16.padded(80), experts=4))
+    assert not kernels.pair_kernel_applies(_cpu_weight(k16.padded(80), experts=4))
+    assert kernels.moe_gemv_sorted_applies(_cpu_weight(f32, experts=4))
+    assert kernels.moe_gemv_sorted_applies(_cpu_weight(f16, experts=4))
+    assert not kernels.moe_gemv_sorted_applies(_cpu_weight(F.CBFormat("fp8", 30, n_sub=4), experts=4))
+    assert not kernels.moe_gemv_sorted_applies(_cpu_weight(lit, rows=192, experts=4))   # not whole 128-row tiles
+    assert not kernels.moe_gemv_sorted_applies(_cpu_weight(lit, experts=4, offsets=True))
+
+
+def test_routed_method_thresholds_are_instance_attributes_with_the_measured_defaults():
+    from gridbook_b200 import moe
+    assert (moe.SORTED_MIN_PAIRS_PER_EXPERT, moe.SORTED_MIN_PAIRS_OTHER) == (4, 16)
+    assert moe.PREFILL_MIN_PAIRS_PER_EXPERT > moe.PREFILL_MIN_PAIRS_OTHER > moe.SORTED_MIN_PAIRS_PER_EXPERT
+    src = open(moe.__file__).read()
+    for attr in ("pair_kernel_max_pairs", "sorted_min_pairs_per_expert", "sorted_min_pairs_other",
+                 "prefill_min_pairs_per_expert", "prefill_min_pairs_other", "pad_two_tier_superblocks"):
+        assert f"self.{attr} = " in src, attr
