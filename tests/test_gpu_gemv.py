@@ -304,7 +304,11 @@ def test_literal_single_row_table_kernel(dev, N, K):
 
 
 @pytest.mark.parametrize("N,K,M", [(256, 1024, 2), (384, 2048, 16), (1000, 2304, 5), (640, 1536, 100),
-                                   (2048, 5120, 9), (5120, 4352, 128), (300, 1280, 33)])
+                                   (2048, 5120, 9), (5120, 4352, 128), (300, 1280, 33),
+                                   # shards of the benchmark's projections over eight and four ranks: few
+                                   # row tiles, up to seventeen K slices
+                                   (768, 5120, 16), (256, 5120, 16), (640, 6144, 16), (4352, 5120, 16),
+                                   (640, 17408, 16), (1280, 17408, 5)])
 def test_literal_row_batch_tensor_core_decode_kernel(dev, request, N, K, M):
     """2..128 rows of the literal format take the kernel that decodes into shared memory and runs
     tcgen05 MMAs with the weights on the M side: ragged row counts on both sides, a last raw stage
