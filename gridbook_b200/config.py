@@ -211,6 +211,20 @@ class PrismaQuantConfig(QuantizationConfig):
         or from separate `gate_proj` / `up_proj` targets with their own books
         (docs/SPEC.md:480-527); then it carries `_role_refs`, the codebook_ref of each role."""
         self._ensure_resolved()
+        # Per-expert format groups (targets ending in `.format_group_N`: some experts of the stack
+        # in another format) are not served, and must be refused BY NAME: matching on the final
+        # component would skip them in silence and resolve the stack from whatever else matched
+        # (the reference refuses the same crossing, gridbook/config.py:1605-1641).
+        for stored in self.target_scheme:
+            tail = stored.rsplit(".format_group_", 1)
+            if len(tail) == 2 and tail[1].isdigit():
+                base = tail[0]
+                for leaf in ("gate_proj", "up_proj", "gate_up_proj", "down_proj"):
+                    if any(base == f"{w}{prefix}.{leaf}" for w in ("",) + tuple(f"{x}." for x in self._WRAPPERS)) or \
+                            any(f"{w}.{base}" == f"{prefix}.{leaf}" for w in self._WRAPPERS):
+                        raise NativeKernelUnavailableError(
+                            f"[prismaquant] {prefix}: target {stored!r} is a per-expert format group; stacks whose "
+                            "experts differ in format are not served by gridbook_b200")
         fused = self._lookup(f"{prefix}.gate_up_proj")
         gate, up_role = self._lookup(f"{prefix}.gate_proj"), self._lookup(f"{prefix}.up_proj")
         down = self._lookup(f"{prefix}.down_proj")

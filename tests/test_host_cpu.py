@@ -524,3 +524,56 @@ def test_routed_method_thresholds_are_instance_attributes_with_the_measured_defa
     for attr in ("pair_kernel_max_pairs", "sorted_min_pairs_per_expert", "sorted_min_pairs_other",
                  "prefill_min_pairs_per_expert", "prefill_min_pairs_other", "pad_two_tier_superblocks"):
         assert f"self.{attr} = " in src, attr
+
+
+def _routed_cfg(groups, books=None):
+    from gridbook_b200.config import PrismaQuantConfig
+    raw = {"quant_method": "gridbook", "config_groups": {f"g{i}": {"targets": list(t), "scheme": s}
+                                                          for i, (t, s) in enumerate(groups)}}
+    if books is not None:
+        raw["_codebooks"] = books
+    return PrismaQuantConfig(raw)
+
+
+def _k28(*refs):
+    return {"grid": "fp8", "mode": "product", "k": 28, "n_sub": 4, "type_size": 112, "codebook_ref": list(refs)}
+
+
+def test_uniform_routed_stack_is_one_role_however_its_targets_are_spelled():
+    """The cases of the reference's tests/test_routed_per_role_codebooks.py:63-127 on this resolver:
+    one book for the whole stack - written as gate_up_proj + down_proj in one group, or as the three
+    unfused role names - is a uniform stack (one role for gate_up, one for down, the same book); a
+    fused gate_up_proj target speaks for gate AND up while down carries its own book."""
+    pre = "model.layers.1.mlp.experts"
+    leaf = lambda n: f"{pre}.{n}"                                   # noqa: E731
+    refs = [f"cb.routed.K28.sub{i}" for i in range(4)]
+    books = {r: torch.full((128, 2), 3.0) for r in refs}
+    for targets in ([leaf("gate_up_proj"), leaf("down_proj")], [leaf("gate_proj"), leaf("up_proj"), leaf("down_proj")]):
+        cfg = _routed_cfg([(targets, _k28(*refs))], books)
+        up, down = cfg._moe_scheme_for_prefix(pre)
+        assert up["codebook_ref"] == refs and down["codebook_ref"] == refs
+        assert len(cfg.codebooks_for_prefix(f"{pre}.w13", up)) == 1
+        assert len(cfg.codebooks_for_prefix(f"{pre}.w2", down)) == 1
+    w13 = [f"cb.l1.w13.sub{i}" for i in range(4)]
+    dn = [f"cb.l1.down.sub{i}" for i in range(4)]
+    books = {**{r: torch.full((128, 2), 1.0) for r in w13}, **{r: torch.full((128, 2), 2.0) for r in dn}}
+    cfg = _routed_cfg([([leaf("gate_up_proj")], _k28(*w13)), ([leaf("down_proj")], _k28(*dn))], books)
+    up, down = cfg._moe_scheme_for_prefix(pre)
+    r13, r2 = cfg.codebooks_for_prefix(f"{pre}.w13", up), cfg.codebooks_for_prefix(f"{pre}.w2", down)
+    assert len(r13) == 1 and float(r13[0][0][0, 0]) == 1.0 and float(r2[0][0][0, 0]) == 2.0
+
+
+@pytest.mark.parametrize("leaf_name", ["gate_proj", "gate_up_proj", "down_proj"])
+def test_role_crossed_with_a_per_expert_format_group_is_refused_by_name(leaf_name):
+    """tests/test_routed_per_role_codebooks.py:165-182 of the reference: a `...<leaf>.format_group_0`
+    target must not be skipped in silence.  A neighbouring stack's group does not trip the guard."""
+    from gridbook_b200._native import NativeKernelUnavailableError
+    pre = "model.layers.1.mlp.experts"
+    refs = [f"r{i}" for i in range(4)]
+    cfg = _routed_cfg([([f"{pre}.gate_up_proj", f"{pre}.down_proj"], _k28(*refs)),
+                       ([f"{pre}.{leaf_name}.format_group_0"], _k28(*refs))])
+    with pytest.raises(NativeKernelUnavailableError, match="per-expert format group"):
+        cfg._moe_scheme_for_prefix(pre)
+    other = _routed_cfg([([f"{pre}.gate_up_proj", f"{pre}.down_proj"], _k28(*refs)),
+                         ([f"model.layers.2.mlp.experts.{leaf_name}.format_group_0"], _k28(*refs))])
+    assert other._moe_scheme_for_prefix(pre) is not None
