@@ -577,3 +577,18 @@ def test_role_crossed_with_a_per_expert_format_group_is_refused_by_name(leaf_nam
     other = _routed_cfg([([f"{pre}.gate_up_proj", f"{pre}.down_proj"], _k28(*refs)),
                          ([f"model.layers.2.mlp.experts.{leaf_name}.format_group_0"], _k28(*refs))])
     assert other._moe_scheme_for_prefix(pre) is not None
+
+
+def test_codebook_digest_known_answers():
+    """The reference's own known-answer vectors for the table digest (tests/test_codebook_digest.py:94-120):
+    SHA-256 of the fp16 row-major bytes, whatever the dtype and the strides of the tensor handed in."""
+    import hashlib
+    import struct
+    from gridbook_b200.artifact import codebook_sha256
+    table = torch.tensor([0.0, 1.0, -2.0, 0.5], dtype=torch.float32)
+    assert struct.pack("<4e", 0.0, 1.0, -2.0, 0.5).hex() == "0000003c00c00038"
+    assert codebook_sha256(table) == "58e0b63dabbfe62f04be297478992b1c1d301fc4c3c4c1c8abe3f431b322cce5"
+    source = torch.arange(24, dtype=torch.float32).reshape(4, 6).t()        # not contiguous
+    want = hashlib.sha256(struct.pack("<24e", *source.to(torch.float16).contiguous().reshape(-1).tolist())).hexdigest()
+    assert codebook_sha256(source) == want == codebook_sha256(source.to(torch.float64))
+    assert codebook_sha256(torch.empty(0)) == hashlib.sha256(b"").hexdigest()
