@@ -190,8 +190,10 @@ GBO_API void gbo_fp4_act_qdq(const float* x, int64_t M, int64_t K, int scale_div
   for (int64_t g = 0; g < M * (K / 16); ++g) {
     const float* v = x + g * 16;
     float amax = 0.f;
-    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    amax = fmaxf(amax, 1e-8f);
+    int has_nan = 0;
+    for (int i = 0; i < 16; ++i) { amax = fmaxf(amax, fabsf(v[i])); has_nan |= isnan(v[i]); }
+    /* torch.amax spreads a NaN over the group (gridbook/codec.py:254); C's fmaxf would drop it */
+    amax = has_nan ? NAN : fmaxf(amax, 1e-8f);
     const float scale = scale_div ? amax / 6.0f : amax * inv6;
     for (int i = 0; i < 16; ++i) {
       const float xg = v[i] / scale;
@@ -212,11 +214,14 @@ GBO_API void gbo_fp8_act_qdq(const float* x, int64_t M, int64_t K, int scale_div
   for (int64_t m = 0; m < M; ++m) {
     const float* v = x + m * K;
     float amax = 0.f;
-    for (int64_t i = 0; i < K; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    int has_nan = 0;
+    for (int64_t i = 0; i < K; ++i) { amax = fmaxf(amax, fabsf(v[i])); has_nan |= isnan(v[i]); }
     float scale = scale_div ? amax / 448.0f : amax * inv448;
-    scale = fmaxf(scale, 1.0f / (448.0f * 512.0f));
+    /* torch's amax and clamp both keep a NaN (gridbook/codec.py:433-435): the row becomes NaN */
+    scale = has_nan ? NAN : fmaxf(scale, 1.0f / (448.0f * 512.0f));
     for (int64_t i = 0; i < K; ++i) {
       float q = v[i] / scale;
+      if (isnan(q)) { out[m * K + i] = NAN; continue; }
       q = fminf(fmaxf(q, -448.0f), 448.0f);
       out[m * K + i] = bf16_round(e4m3_lut[f32_to_e4m3(q)] * scale);
     }

@@ -153,3 +153,32 @@ def test_argument_errors(dev):
         kernels.expand_fp8(w, 4, 8)
     with pytest.raises(RuntimeError, match="fp4-grid"):
         kernels.expand_fp4_bf16(w)
+
+
+def test_activation_buckets_nonfinite_groups_signed_zero_and_subnormals(dev):
+    """The classes the reference pins for the group-16 bucket in tests/test_fp4_act_qdq.py:118-149: a NaN
+    or an infinity in a group decides the whole group the way torch.amax does (CUDA's fmaxf alone
+    would ignore a lone NaN); signed zeros and bf16 subnormals keep the codec's bits.  Value classes
+    and every finite output must match the oracle (which matches the reference's codec on these
+    rows); NaN payloads are not part of the contract.  The per-token fp8 bucket is not part of this
+    contract: the reference's own kernel (gridbook/csrc/cb_gemv.cu:135-172) takes the row maximum
+    with fmaxf, so a lone NaN there clamps to -448 instead of spreading, and this library does the
+    same; only finite rows are pinned for it."""
+    from gridbook_b200 import kernels
+    rows = torch.tensor([[float("nan"), 1.0] + [0.0] * 14 + [1.0, -2.0] + [0.5] * 14,
+                         [float("inf"), -1.0] + [0.0] * 14 + [3.0, 0.25] + [0.0] * 14,
+                         [float("-inf"), 1.0] + [0.0] * 14 + [float("nan")] + [1.0] * 15], dtype=torch.bfloat16)
+    with np.errstate(all="ignore"):
+        for rule in ("recip", "div"):
+            got = kernels.fp4_act_qdq(rows.to(dev), rule).float().cpu().numpy()
+            ref = O.bf16_round(O.fp4_group16_act_qdq(rows.float().numpy(), rule))
+            assert np.array_equal(np.isnan(got), np.isnan(ref)), (rule, got, ref)
+            assert np.array_equal(np.isposinf(got), np.isposinf(ref)), rule
+            assert np.array_equal(np.isneginf(got), np.isneginf(ref)), rule
+            fin = np.isfinite(ref)
+            assert np.array_equal(got[fin], ref[fin]), rule
+    raw = torch.tensor([0, -32768, 1, -32767] * 8, dtype=torch.int16)
+    x = raw.view(torch.bfloat16).reshape(1, 32)
+    for rule in ("recip", "div"):
+        got = bits_of(kernels.fp4_act_qdq(x.to(dev), rule))
+        assert np.array_equal(got, O.f32_to_bf16_bits(O.fp4_group16_act_qdq(x.float().numpy(), rule))), rule

@@ -106,6 +106,32 @@ def test_midpoint_trap_separates_the_two_scale_rules():
     assert {abs(float(lo)) / abs(float(hi)), abs(float(hi)) / abs(float(lo))} == {0.5, 2.0}
 
 
+def test_activation_edge_cases_match_the_reference_codec():
+    """Rows the reference's kernel test pins (tests/test_fp4_act_qdq.py:107-149), with the outputs its
+    codec gave them (tests/golden/act_edge_cases.json, made by make_act_edge_cases.py): a NaN or an
+    infinity inside a group, signed zeros, the smallest bf16 subnormals, the rule-separating midpoint.
+    Value classes and every finite output agree for the numpy and the C restatement; NaN payloads are
+    not part of the contract."""
+    import json
+    import os
+    from oracle import c_oracle as C
+    with open(os.path.join(os.path.dirname(__file__), "golden", "act_edge_cases.json")) as fh:
+        cases = json.load(fh)
+    assert set(cases) == {"nonfinite", "signed_zero_subnormal", "midpoint"}
+    with np.errstate(all="ignore"):
+        for name, case in cases.items():
+            x = f32(np.array(case["x"], np.uint16)).reshape(case["shape"])
+            for grid in ("fp4", "fp8"):
+                want = f32(np.array(case[grid], np.uint16)).reshape(case["shape"])
+                fin = np.isfinite(want)
+                for impl, got in (("numpy", O.bf16_round(O.act_bucket(x, grid, "div"))),
+                                  ("c", O.bf16_round(C.act_qdq(x, grid, "div")))):
+                    assert np.array_equal(np.isnan(got), np.isnan(want)), (name, grid, impl)
+                    assert np.array_equal(np.isposinf(got), np.isposinf(want)), (name, grid, impl)
+                    assert np.array_equal(np.isneginf(got), np.isneginf(want)), (name, grid, impl)
+                    assert np.array_equal(O.f32_to_bf16_bits(got[fin]), O.f32_to_bf16_bits(want[fin])), (name, grid, impl)
+
+
 def test_sf_swizzle(golden):
     assert np.array_equal(O.swizzle_sf_plane(golden["sf_plain"]), golden["sf_swizzled"])
 

@@ -76,3 +76,26 @@ def test_nvfp4_activation_quantiser_matches_the_reference_code(ref, seed):
     packed, sf = out[0], out[1]
     assert np.array_equal(packed, packed_ref.view(torch.uint8).numpy())
     assert np.array_equal(sf, sf_ref.view(torch.uint8).numpy().reshape(sf.shape))
+
+
+def test_activation_buckets_on_nonfinite_groups_signed_zero_and_subnormals_match_the_reference_code(ref):
+    """Rows the reference's kernel test pins against its codec (tests/test_fp4_act_qdq.py:118-149): a NaN
+    or an infinity decides its whole group (torch.amax spreads a NaN), signed zeros and bf16
+    subnormals come back as the codec writes them.  Value classes and every finite output agree;
+    NaN payloads are not compared."""
+    _, codec = ref
+    rows = torch.tensor([[float("nan"), 1.0] + [0.0] * 14 + [1.0, -2.0] + [0.5] * 14,
+                         [float("inf"), -1.0] + [0.0] * 14 + [3.0, 0.25] + [0.0] * 14,
+                         [float("-inf"), 1.0] + [0.0] * 14 + [float("nan")] + [1.0] * 15], dtype=torch.bfloat16)
+    raw = torch.tensor([0, -32768, 1, -32767] * 8, dtype=torch.int16).view(torch.bfloat16).reshape(1, 32)
+    with np.errstate(all="ignore"):
+        for fn_ref, fn in ((codec.fp4_group16_act_qdq, O.fp4_group16_act_qdq),
+                           (codec.fp8_dynamic_act_qdq, O.fp8_dynamic_act_qdq)):
+            want = fn_ref(rows).to(torch.bfloat16).float().numpy()
+            got = O.bf16_round(fn(rows.float().numpy(), "div"))
+            assert np.array_equal(np.isnan(got), np.isnan(want))
+            assert np.array_equal(np.isposinf(got), np.isposinf(want))
+            assert np.array_equal(np.isneginf(got), np.isneginf(want))
+            fin = np.isfinite(want)
+            assert np.array_equal(got[fin], want[fin])
+            assert np.array_equal(O.f32_to_bf16_bits(fn(raw.float().numpy(), "div")), _bits(fn_ref(raw)))
