@@ -132,6 +132,39 @@ def test_activation_edge_cases_match_the_reference_codec():
                     assert np.array_equal(O.f32_to_bf16_bits(got[fin]), O.f32_to_bf16_bits(want[fin])), (name, grid, impl)
 
 
+def _e2m1_codes(packed, k):
+    return np.stack((packed & 0xF, packed >> 4), axis=-1).reshape(-1, k)
+
+
+def test_nvfp4_activation_quantiser_rounds_e2m1_midpoints_to_even():
+    """Known answer of the reference (tests/test_nvfp4_act_quant_ref.py:17-27,68-77): with a unit
+    scale factor every midpoint between two E2M1 rungs goes to the rung with the even code."""
+    mids = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0]
+    row = np.array([mids + [-v for v in mids] + [6.0, 0.0]], np.float32)
+    packed, sf, recip = O.nvfp4_act_quant(row, 1.0)
+    even = [0, 2, 2, 4, 4, 6, 6]
+    assert _e2m1_codes(packed, 16)[0].tolist() == even + [c | 8 for c in even] + [7, 0]
+    assert sf.tolist() == [[0x38]] and float(recip) == 1.0        # E4M3 byte of 1.0
+
+
+def test_nvfp4_activation_quantiser_scale_factor_underflow_boundary():
+    """Known answer of the reference (tests/test_nvfp4_act_quant_ref.py:29-50,80-91): the smallest E4M3
+    subnormal is 2^-9, so a group whose maximum is at or under 6 * 2^-10 rounds its scale factor to
+    zero (ties to even) and must come out as an all-zero payload, sign bits kept; just above the
+    boundary the scale factor is the code 1."""
+    edge = 6.0 * 2.0 ** -10
+    values = [0.0, 2.0 ** -20, 0.001, 0.003, 0.005, 0.0058, edge, 0.006, 0.008,
+              -(2.0 ** -20), -0.001, -0.003, -0.005, -0.0058, -edge, -0.006]
+    x = O.bf16_round(np.repeat(np.array(values, np.float32), 16).reshape(1, -1))
+    packed, sf, _ = O.nvfp4_act_quant(x, 1.0)
+    codes = _e2m1_codes(packed, x.shape[1])[0].reshape(-1, 16)
+    under = list(range(7)) + list(range(9, 15))
+    assert sf[0, under].tolist() == [0] * len(under)
+    assert sf[0, [7, 8, 15]].tolist() == [1, 1, 1]
+    assert not codes[:7].any()
+    assert np.unique(codes[9:15]).tolist() == [8]                 # a signed numerical zero
+
+
 def test_sf_swizzle(golden):
     assert np.array_equal(O.swizzle_sf_plane(golden["sf_plain"]), golden["sf_swizzled"])
 
