@@ -3,6 +3,9 @@ the two-tier compose table, row padding and grid validation.  Runs once per laye
 model load; nothing here is on the forward path and nothing here is a dense weight."""
 from __future__ import annotations
 
+import os
+import sys
+
 import torch
 
 SUPERBLOCK = 256
@@ -20,44 +23,68 @@ def type_size(k: int, is_fp4: bool, two_tier: bool = False) -> int:
     return 4 * int(k) + ((9 if two_tier else 16) if is_fp4 else 0)
 
 
+def assert_cast_lossless(raw: torch.Tensor, cast: torch.Tensor, what: str, prefix: str) -> None:
+    """Every table value must survive the cast to the representation the kernels stage
+    (gridbook/codec.py:78-107).  Compared in float64, so a float64 sidecar is not rounded before the
+    check.  The error names the layer, the cast, how many values moved and the measured maximum
+    absolute and relative error; PRISMAQUANT_SKIP_CB_CAST_CHECK=1 turns it into a warning on stderr
+    (debugging only), as in the reference."""
+    a = raw.reshape(-1).to(torch.float64)
+    b = cast.reshape(-1).to(torch.float64)
+    sized = a.numel() == b.numel()
+    if sized and torch.equal(a, b):
+        return
+    moved = int((a != b).sum()) if sized else -1
+    err = (a - b).abs() if sized else None
+    worst = float(err.max()) if sized else -1.0
+    rel = float((err / a.abs().clamp_min(1e-12)).max()) if sized else -1.0
+    msg = (f"[prismaquant] {prefix}: the {what} codebook cast is LOSSY: {moved} of {a.numel()} table values "
+           f"do not survive it (max abs {worst:.3e}, max rel {rel:.3e}). Only values already on the target "
+           f"grid cast exactly; a table that is not would make every weight decode against rounded entries. "
+           f"PRISMAQUANT_SKIP_CB_CAST_CHECK=1 overrides this (debugging only).")
+    if os.environ.get("PRISMAQUANT_SKIP_CB_CAST_CHECK") == "1":
+        print("WARNING " + msg, file=sys.stderr, flush=True)
+        return
+    raise ValueError(msg)
+
+
 def validate_codebook_grid(raw: torch.Tensor, grid: str, prefix: str = "codebook") -> None:
-    """Reject tables that are not exactly on their declared grid
-    (gridbook/codec.py:106-143): a lossy cast must be an error, never a rounding."""
+    """Reject tables that are not exactly on their declared grid (gridbook/codec.py:110-143): a format
+    check, not a cast check - 0.53125 survives bf16 but is no E2M1 value."""
     v = raw.reshape(-1).to(torch.float64)
-    if not bool(torch.isfinite(v).all()):
-        raise ValueError(f"[prismaquant] {prefix}: non-finite codebook values; {grid} codebooks "
-                         "must be finite and grid-valued")
+    finite = torch.isfinite(v)
+    if not bool(finite.all()):
+        raise ValueError(f"[prismaquant] {prefix}: {int((~finite).sum())} of {v.numel()} codebook values are "
+                         f"non-finite; {grid} codebooks must be finite and grid-valued")
     if grid == "fp8":
-        ok = v == v.to(torch.float8_e4m3fn).to(torch.float64)
+        ok, name = v == v.to(torch.float8_e4m3fn).to(torch.float64), "E4M3"
     elif grid == "fp4":
         mags = torch.tensor(_E2M1, dtype=torch.float64, device=v.device)
-        ok = (v.abs().unsqueeze(-1) == mags).any(dim=-1)
+        ok, name = (v.abs().unsqueeze(-1) == mags).any(dim=-1), "E2M1"
     else:
         raise ValueError(f"[prismaquant] {prefix}: unknown codebook grid {grid!r}")
     if not bool(ok.all()):
         raise ValueError(f"[prismaquant] {prefix}: {int((~ok).sum())} of {v.numel()} codebook values "
-                         f"are off the grid declared by the {grid} format")
+                         f"are off the {name} grid declared by the {grid} format")
 
 
 def build_flat_codebook(sub_tables: list[torch.Tensor], prefix: str = "codebook",
                         grid: str | None = None) -> torch.Tensor:
     """Concatenate the (2^w, sub_dim) tables row-major into the flat bf16 layout the
     kernels stage (gridbook/codec.py:146-159): entry (idx, j) of table s sits at
-    base_s + idx*sub_dim + j."""
+    base_s + idx*sub_dim + j.  The input is never rounded before the check."""
     raw = torch.cat([t.reshape(-1).to(torch.float64) for t in sub_tables])
     if grid is not None:
         validate_codebook_grid(raw, grid, prefix)
-    flat = raw.to(torch.bfloat16).contiguous()
-    if not torch.equal(flat.to(torch.float64), raw):
-        raise ValueError(f"[prismaquant] {prefix}: the bf16 flat codebook cast is lossy")
+    flat = torch.cat([t.reshape(-1).to(torch.bfloat16) for t in sub_tables]).contiguous()
+    assert_cast_lossless(raw, flat, "bf16 flat", prefix)
     return flat
 
 
 def flat_codebook_fp8(flat: torch.Tensor, prefix: str = "codebook") -> torch.Tensor:
     """Flat E4M3-grid codebook as raw bytes (gridbook/codec.py:162-167)."""
     f8 = flat.to(torch.float8_e4m3fn).contiguous()
-    if not torch.equal(f8.to(torch.float64), flat.to(torch.float64)):
-        raise ValueError(f"[prismaquant] {prefix}: the e4m3 flat codebook cast is lossy")
+    assert_cast_lossless(flat, f8, "e4m3 flat", prefix)
     return f8.view(torch.uint8)
 
 

@@ -80,7 +80,7 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         N, K = qw.shape[0], layer._cb_input_size
         roles = self._role_codebooks()
         grid = self.fmt.grid
-        blocks = [codec.build_flat_codebook([t.to(torch.float32) for t in tabs],
+        blocks = [codec.build_flat_codebook(list(tabs),
                                             prefix=self.prefix, grid=grid) for tabs in roles]
         for b in blocks:
             if b.numel() != self.fmt.codebook_elems():

@@ -141,7 +141,7 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         if role == "w13" and len(roles) not in (1, 2):
             raise NativeKernelUnavailableError(
                 f"{self.prefix}: gate_up takes one shared codebook or one each for gate and up; got {len(roles)}")
-        blocks = [codec.build_flat_codebook([t.to(torch.float32) for t in tabs], prefix=self.prefix, grid=fmt.grid)
+        blocks = [codec.build_flat_codebook(list(tabs), prefix=self.prefix, grid=fmt.grid)
                   for tabs in roles]
         for b in blocks:
             if b.numel() != fmt.codebook_elems():

@@ -147,14 +147,65 @@ def test_scheme_parsing_and_type_size_guard():
 
 def test_codec_rejects_off_grid_codebooks():
     from gridbook_b200 import codec
-    with pytest.raises(ValueError, match="off the grid"):
+    with pytest.raises(ValueError, match="off the E2M1 grid"):
         codec.build_flat_codebook([torch.tensor([[0.53125, 1.0, 2.0, 6.0]])], grid="fp4")
-    with pytest.raises(ValueError, match="off the grid"):
+    with pytest.raises(ValueError, match="off the E4M3 grid"):
         codec.build_flat_codebook([torch.tensor([[0.3, 1.0]])], grid="fp8")
     flat = codec.build_flat_codebook([torch.tensor([[0.5, -6.0, 3.0, 0.0]])], grid="fp4")
     assert flat.dtype is torch.bfloat16 and flat.tolist() == [0.5, -6.0, 3.0, 0.0]
     assert codec.pad_qweight(torch.zeros(3, 73, dtype=torch.uint8)).shape == (3, 89)
     assert codec.build_compose_table()[127 * 16 + 9].item() == 2.25
+
+
+@pytest.mark.parametrize("grid,name", [("fp4", "E2M1 grid"), ("fp8", "E4M3 grid")])
+@pytest.mark.parametrize("value", [0.53125, float("nan"), float("inf")])
+def test_codec_grid_validation_rejects_malformed_tables_at_load(grid, name, value):
+    """Behaviour the reference pins in tests/test_fail_loud.py:224-246: an off-grid, NaN or infinite
+    entry is refused at load with the grid or "non-finite" named; a learned table that sits on the
+    grid is accepted even if it is not the deterministic lattice."""
+    from gridbook_b200 import codec
+    with pytest.raises(ValueError, match=f"{name}|non-finite"):
+        codec.build_flat_codebook([torch.tensor([0.0, -0.5, value], dtype=torch.float32)], "some.layer", grid)
+    ok = codec.build_flat_codebook([torch.tensor([-6.0, -1.5, -0.0, 0.5, 3.0])], "learned", grid)
+    assert ok.dtype is torch.bfloat16
+
+
+def test_codec_cast_check_names_layer_count_and_measured_errors(monkeypatch, capsys):
+    """The lossy-cast error of the reference (tests/test_fail_loud.py:127-222): it names the layer and
+    the cast, counts the entries that moved and prints the measured maximum absolute and relative
+    error; float64 input is not rounded before the check; the environment override turns the error
+    into a warning."""
+    from gridbook_b200 import codec
+    monkeypatch.delenv("PRISMAQUANT_SKIP_CB_CAST_CHECK", raising=False)
+    on_grid = (torch.arange(64, dtype=torch.float32) / 64.0 - 0.5).to(torch.float8_e4m3fn).to(torch.bfloat16)
+    codec.assert_cast_lossless(on_grid, on_grid.to(torch.float8_e4m3fn), "e4m3 flat", "t")
+    assert codec.flat_codebook_fp8(on_grid).dtype is torch.uint8
+
+    flat = on_grid[:8].float().clone()
+    flat[3] = 0.53125                                  # between the E4M3 codes 0.5 and 0.5625
+    cast = flat.to(torch.float8_e4m3fn)
+    with pytest.raises(ValueError) as e:
+        codec.assert_cast_lossless(flat, cast, "e4m3 flat", "model.layers.3.mlp.experts.w13")
+    msg = str(e.value)
+    got = float(cast.float()[3])
+    for part in ("LOSSY", "model.layers.3.mlp.experts.w13", "e4m3 flat", "1 of 8 table values do not survive it",
+                 f"max abs {abs(0.53125 - got):.3e}", f"max rel {abs(0.53125 - got) / 0.53125:.3e}",
+                 "PRISMAQUANT_SKIP_CB_CAST_CHECK=1"):
+        assert part in msg, part
+
+    with pytest.raises(ValueError, match="bf16 flat"):
+        codec.build_flat_codebook([torch.tensor([1.0000001], dtype=torch.float32)], "dense.layer")
+    with pytest.raises(ValueError, match="bf16 flat"):                   # mixed dtypes, one lossy
+        codec.build_flat_codebook([torch.tensor([[1.0000001, 2.0]]), torch.tensor([[0.5]], dtype=torch.bfloat16)])
+    with pytest.raises(ValueError, match="bf16 flat"):
+        codec.build_flat_codebook([torch.tensor([1.0 + 2.0 ** -40], dtype=torch.float64)], "float64.layer")
+    with pytest.raises(ValueError, match="e4m3 flat"):
+        codec.flat_codebook_fp8(torch.tensor([0.53125], dtype=torch.bfloat16), "dense.layer")
+
+    monkeypatch.setenv("PRISMAQUANT_SKIP_CB_CAST_CHECK", "1")
+    codec.assert_cast_lossless(flat, cast, "e4m3 flat", "t")             # must not raise
+    err = capsys.readouterr().err
+    assert "WARNING" in err and "LOSSY" in err
 
 
 def test_plugin_registers_both_names():
