@@ -643,3 +643,69 @@ def test_codebook_digest_known_answers():
     want = hashlib.sha256(struct.pack("<24e", *source.to(torch.float16).contiguous().reshape(-1).tolist())).hexdigest()
     assert codebook_sha256(source) == want == codebook_sha256(source.to(torch.float64))
     assert codebook_sha256(torch.empty(0)) == hashlib.sha256(b"").hexdigest()
+
+
+def test_routed_method_parameter_shapes_and_checkpoint_hook():
+    """The stacked-parameter contract the reference pins in tests/test_moe_stacked.py:77-106 and the
+    instance load hook of gridbook/moe.py:503-546: w13 = [E, 2I, row_bytes(H)], w2 = [E, H, row_bytes(I)],
+    per-(expert, row) fp32 scales on the fp8 grid only; checkpoint tensors named <proj>.cb_qweight /
+    <proj>.weight_scale go straight into the stacked parameters, a shape that breaks the contract is
+    refused by name, everything else reaches the layer's own loader."""
+    from gridbook_b200.moe import PrismaQuantCBMoEMethod, _row_bytes
+    E, hidden, inter, k, ts = 8, 512, 1024, 44, 176
+    scheme = {"grid": "fp8", "mode": "product", "k": k, "n_sub": 4, "type_size": ts, "codebook_ref": ["cb.x"]}
+    method = PrismaQuantCBMoEMethod(None, None, scheme, "model.layers.0.mlp.experts")
+    seen = []
+
+    class Layer(torch.nn.Module):
+        def load_weights(self, weights):
+            for name, _ in weights:
+                seen.append(name)
+                yield name
+
+    layer = Layer()
+    method.create_weights(layer, E, hidden, inter, torch.bfloat16, weight_loader=None)
+    assert layer.w13_cb_qweight.shape == (E, 2 * inter, _row_bytes(hidden, ts)) and layer.w13_cb_qweight.dtype is torch.uint8
+    assert layer.w2_cb_qweight.shape == (E, hidden, _row_bytes(inter, ts))
+    assert layer.w13_weight_scale.shape == (E, 2 * inter) and layer.w13_weight_scale.dtype is torch.float32
+    assert layer.w2_weight_scale.shape == (E, hidden)
+    assert not layer.w13_cb_qweight.requires_grad
+    with pytest.raises(ValueError, match="multiple of 256"):
+        _row_bytes(300, ts)
+
+    w13 = torch.randint(0, 256, tuple(layer.w13_cb_qweight.shape), dtype=torch.uint8)
+    s2 = torch.rand(E, hidden)
+    loaded = list(layer.load_weights([("gate_up_proj.cb_qweight", w13), ("down_proj.weight_scale", s2),
+                                      ("gate.weight", torch.zeros(2))]))
+    assert loaded == ["w13_cb_qweight", "w2_weight_scale", "gate.weight"] and seen == ["gate.weight"]
+    assert torch.equal(layer.w13_cb_qweight.data, w13) and torch.equal(layer.w2_weight_scale.data, s2)
+    with pytest.raises(ValueError, match=r"down_proj\.cb_qweight.*stacked"):
+        list(layer.load_weights([("down_proj.cb_qweight", torch.zeros(E, hidden, 3, dtype=torch.uint8))]))
+
+    fp4 = PrismaQuantCBMoEMethod(None, None, {"grid": "fp4", "mode": "product", "k": 16, "n_sub": 2, "type_size": 73,
+                                              "scale_coding": "two_tier"}, "model.layers.1.mlp.experts")
+    l4 = Layer()
+    fp4.create_weights(l4, 4, 512, 256, torch.bfloat16)
+    assert l4.w13_cb_qweight.shape == (4, 512, 2 * 73) and l4.w2_cb_qweight.shape == (4, 512, 73)
+    assert not hasattr(l4, "w13_weight_scale") and not hasattr(l4, "w2_weight_scale")
+
+
+def test_linear_method_parameter_shapes():
+    """create_weights of the linear method (gridbook/linear.py:233-273): one packed parameter of
+    [sum of the fused shards' rows, row_bytes(K)] bytes, a per-row fp32 scale on the fp8 grid only,
+    in_features a multiple of the superblock."""
+    from gridbook_b200.linear import PrismaQuantCBLinearMethod
+    fp8 = PrismaQuantCBLinearMethod(None, {"grid": "fp8", "mode": "product", "k": 32, "n_sub": 4, "type_size": 128},
+                                    "model.layers.0.self_attn.qkv_proj")
+    layer = torch.nn.Module()
+    fp8.create_weights(layer, 1024, [64, 16, 16], 1024, 96, torch.bfloat16, weight_loader=None)
+    assert layer.cb_qweight.shape == (96, 4 * 128) and layer.cb_qweight.dtype is torch.uint8
+    assert layer.weight_scale.shape == (96,) and layer.weight_scale.dtype is torch.float32
+    assert layer.logical_widths == [64, 16, 16]
+    fp4 = PrismaQuantCBLinearMethod(None, {"grid": "fp4", "mode": "product", "k": 16, "n_sub": 2, "type_size": 73,
+                                           "scale_coding": "two_tier"}, "model.layers.0.mlp.down_proj")
+    l4 = torch.nn.Module()
+    fp4.create_weights(l4, 768, [32], 768, 32, torch.bfloat16)
+    assert l4.cb_qweight.shape == (32, 3 * 73) and not hasattr(l4, "weight_scale")
+    with pytest.raises(ValueError, match="multiple of 256"):
+        fp4.create_weights(torch.nn.Module(), 300, [32], 300, 32, torch.bfloat16)
