@@ -66,7 +66,12 @@ typedef struct gb_weight {
   gb_format fmt;
 } gb_weight;
 
+/* The version a binding compares with GB_ABI_VERSION before its first call: with the binding's
+ * list of required symbols this replaces the strict symbol tuples the reference checks when it
+ * loads a native module (gridbook/cuda_ext.py:344-365,446-451), so a stale library fails at load. */
 GB_API int gb_abi_version(void);
+/* Text of the calling thread's last non-zero status; replaces the message of the RuntimeError a
+ * TORCH_CHECK raises in the reference's bindings (gridbook/csrc/cb_gemv.cu:658-712). */
 GB_API const char* gb_last_error(void);
 
 /* Per-device one-time set-up (function attributes, SM count).  Call at model load,
@@ -74,7 +79,8 @@ GB_API const char* gb_last_error(void);
  * gridbook/csrc/cb_gemv_v2.cu:495-548. */
 GB_API int gb_prepare(int device);
 
-/* Device error word written by kernels whose bounded waits ran out; 0 when healthy. */
+/* Device error word written by kernels whose bounded waits ran out; 0 when healthy.  No counterpart
+ * in the reference, whose kernels do not wait on one another. */
 GB_API int gb_device_status(int device, int* status_out);
 
 /* Clears the device error word (after the cause has been dealt with). */
