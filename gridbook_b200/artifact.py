@@ -99,6 +99,9 @@ class Artifact:
         module.cb_qweight.data = torch.cat(parts, dim=0).to(device)
         if not method.fmt.is_fp4:
             module.weight_scale.data = torch.cat([self.tensor(f"{k}.weight_scale") for k in keys]).to(device)
+        if method.has_static_fp4_activation:     # one calibrated scale per role; the gate wants them identical
+            module.input_global_scale.data = torch.cat(
+                [self.tensor(f"{k}.input_global_scale").reshape(-1).float() for k in keys]).to(device)
         method.process_weights_after_loading(module)
         return module
 
@@ -123,6 +126,10 @@ class Artifact:
             module.w13_weight_scale.data = self.tensor(f"{prefix}.gate_up_proj.weight_scale").to(device)
         if not method.fmt2.is_fp4:
             module.w2_weight_scale.data = self.tensor(f"{prefix}.down_proj.weight_scale").to(device)
+        for which, proj in (("w13", "gate_up_proj"), ("w2", "down_proj")):
+            if method.has_static_fp4_activation[which]:
+                getattr(module, f"{which}_input_global_scale").data = self.tensor(
+                    f"{prefix}.{proj}.input_global_scale").reshape(-1).float().to(device)
         method.process_weights_after_loading(module)
         return module
 

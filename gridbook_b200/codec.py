@@ -88,6 +88,42 @@ def flat_codebook_fp8(flat: torch.Tensor, prefix: str = "codebook") -> torch.Ten
     return f8.view(torch.uint8)
 
 
+NVFP4_ACTIVATION_CONTRACT = "nvfp4_w4a4"    # the one static activation contract an fp4 scheme may declare
+
+
+def static_activation_contract(scheme: dict, prefix: str) -> bool:
+    """Whether a scheme declares the static NVFP4 activation contract; a declaration on the fp8 grid
+    or of an unknown contract is an error (gridbook/config.py:652-668)."""
+    contract = scheme.get("activation_contract")
+    if contract is None:
+        return False
+    if scheme.get("grid") != "fp4":
+        raise ValueError(f"{prefix}: activation_contract is fp4-only")
+    if contract != NVFP4_ACTIVATION_CONTRACT:
+        raise ValueError(f"{prefix}: unsupported activation_contract {contract!r}")
+    return True
+
+
+def loaded_static_activation_scale(values: torch.Tensor, prefix: str) -> float:
+    """Gate after loading for a contracted module's `input_global_scale`
+    (gridbook/nvfp4_activation_contract.py:719-752): a non-empty 1-D fp32 vector, one slot per
+    logical shard, every slot loaded (the parameter starts as NaN) with a finite positive value, and
+    all slots the same fp32 BITS - the activation is quantised before the projection split, so one
+    module has one scale.  Returns that scale."""
+    data = values.detach()
+    if data.dtype != torch.float32 or data.ndim != 1 or data.numel() == 0:
+        raise ValueError(f"{prefix}.input_global_scale parameter must be nonempty 1-D float32, got "
+                         f"dtype={data.dtype}, shape={tuple(data.shape)}")
+    host = data.to("cpu").contiguous()
+    if not bool(torch.isfinite(host).all()) or not bool((host > 0).all()):
+        raise ValueError(f"{prefix}.input_global_scale: every logical shard must load a finite positive scale, "
+                         f"got {host.tolist()}")
+    bits = host.view(torch.int32)
+    if not bool((bits == bits[0]).all()):
+        raise ValueError(f"{prefix}: fused logical shards have non-identical input_global_scale values")
+    return float(host[0])
+
+
 def build_compose_table(sub_table=TWO_TIER_SUB_TABLE) -> torch.Tensor:
     """(4096,) fp32 table ``T[c] * 2^(E-127)`` indexed ``E*16 + c``
     (gridbook/codec.py:170-183, docs/SPEC.md:144-177)."""

@@ -8,7 +8,7 @@ import torch
 from . import _native, codec, kernels
 from ._native import NativeKernelUnavailableError
 from ._vllm_compat import (ChannelQuantScaleParameter, LinearMethodBase, ModelWeightParameter,
-                           register_weight_loader_v2_supported_method)
+                           PerTensorScaleParameter, register_weight_loader_v2_supported_method)
 from .formats import CBFormat
 
 DECODE_MAX_M = 16          # the decode-batch kernels take up to sixteen rows
@@ -33,6 +33,11 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         sc = scheme.get("scale_coding")
         self._sub_table = (sc.get("table") if isinstance(sc, dict) else None) or codec.TWO_TIER_SUB_TABLE
         self.global_scale = float(scheme.get("weight_global_scale", 1.0))
+        # A scheme that declares the static NVFP4 activation contract ships one calibrated
+        # `input_global_scale` per logical shard (gridbook/linear.py:214-218,252-267).  The parameter
+        # is created and checked here so such a checkpoint loads; the prefill route stays the
+        # per-row one (the reference's "rowwise" mode), the static modes have no kernel here.
+        self.has_static_fp4_activation = codec.static_activation_contract(scheme, prefix)
         # fp4 grid, past the decode batches: "nvfp4" = native NVFP4 activations x the native NVFP4
         # view of the layer on the block-scaled tensor cores; "bf16" = the decode contract kept
         # (bucketed bf16 rows x bf16(value * scale)) on the bf16 tensor cores
@@ -54,9 +59,26 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         layer.register_parameter("cb_qweight", ModelWeightParameter(
             data=torch.empty(rows, self.fmt.row_bytes(K), dtype=torch.uint8),
             input_dim=1, output_dim=0, weight_loader=weight_loader))
+        if self.has_static_fp4_activation:
+            # one slot per logical shard; NaN until the checkpoint fills it, so a tensor that never
+            # arrived is seen at the gate after loading instead of becoming an arbitrary scale
+            layer.register_parameter("input_global_scale", PerTensorScaleParameter(
+                data=torch.full((len(output_partition_sizes),), float("nan"), dtype=torch.float32),
+                weight_loader=weight_loader))
         if not self.is_fp4:
             layer.register_parameter("weight_scale", ChannelQuantScaleParameter(
                 data=torch.empty(rows, dtype=torch.float32), output_dim=0, weight_loader=weight_loader))
+
+    def _finalize_static_activation_scale(self, layer) -> None:
+        """Gate after loading for a contracted layer (gridbook/linear.py:348-372): the parameter
+        exists and every logical shard loaded the same finite positive scale.  The value is kept on
+        the layer for a caller that wants it."""
+        if not self.has_static_fp4_activation:
+            return
+        p = getattr(layer, "input_global_scale", None)
+        if p is None:
+            raise ValueError(f"{self.prefix}: contracted FP4-CB layer has no input_global_scale parameter")
+        layer._cb_fp4_input_global_scale_f32 = codec.loaded_static_activation_scale(p.data, self.prefix)
 
     # ------------------------------------------------------------------ post-load prep
     def _role_codebooks(self) -> list[list[torch.Tensor]]:
@@ -70,6 +92,7 @@ class PrismaQuantCBLinearMethod(LinearMethodBase):
         """Build what the kernels keep resident: flat codebook block(s), per-row codebook
         offsets, the compose table, a packed buffer with tail slack, and the layer id.
         Everything that can fail does so here, never at the first forward."""
+        self._finalize_static_activation_scale(layer)
         _native.load(f"{self.prefix}: CB Linear")
         qw = layer.cb_qweight.data
         dev = qw.device

@@ -58,6 +58,12 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         self.fmt13 = CBFormat.from_scheme(self.scheme)
         self.fmt2 = CBFormat.from_scheme(self.scheme_down)
         self.is_fp4 = self.fmt13.is_fp4
+        # Stacks whose scheme declares the static NVFP4 activation contract ship one calibrated scale
+        # per stage (gridbook/moe.py:423-427,492-500): the parameters are created and checked so the
+        # checkpoint loads; the prefill route stays the per-row one.
+        self.has_static_fp4_activation = {
+            "w13": codec.static_activation_contract(self.scheme, f"{prefix}.w13"),
+            "w2": codec.static_activation_contract(self.scheme_down, f"{prefix}.w2")}
         self.k, self.n_sub, self.type_size = self.fmt13.k, self.fmt13.n_sub, self.fmt13.type_size
         self.pair_kernel_max_pairs = PAIR_KERNEL_MAX_PAIRS
         self.sorted_min_pairs_per_expert = SORTED_MIN_PAIRS_PER_EXPERT
@@ -74,11 +80,14 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
         layer._cb_hidden, layer._cb_inter = hidden_size, inter
         attrs = dict(extra_weight_attrs)
 
-        def param(shape, dtype):
-            p = torch.nn.Parameter(torch.empty(*shape, dtype=dtype), requires_grad=False)
+        def param_from(data):
+            p = torch.nn.Parameter(data, requires_grad=False)
             for key, val in attrs.items():
                 setattr(p, key, val)
             return p
+
+        def param(shape, dtype):
+            return param_from(torch.empty(*shape, dtype=dtype))
 
         # w13 = gate_up: out = 2*inter, in = hidden.  w2 = down: out = hidden, in = inter.
         layer.register_parameter("w13_cb_qweight", param(
@@ -89,6 +98,10 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
             layer.register_parameter("w13_weight_scale", param((E, 2 * inter), torch.float32))
         if not self.fmt2.is_fp4:
             layer.register_parameter("w2_weight_scale", param((E, hidden_size), torch.float32))
+        for which in ("w13", "w2"):
+            if self.has_static_fp4_activation[which]:        # NaN until the checkpoint fills it
+                layer.register_parameter(f"{which}_input_global_scale",
+                                         param_from(torch.full((1,), float("nan"), dtype=torch.float32)))
         self._install_load_hook(layer)
 
     def _install_load_hook(self, layer) -> None:
@@ -100,7 +113,9 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
             return
         prefix = self.prefix
         cb_map = {"gate_up_proj.cb_qweight": "w13_cb_qweight", "down_proj.cb_qweight": "w2_cb_qweight",
-                  "gate_up_proj.weight_scale": "w13_weight_scale", "down_proj.weight_scale": "w2_weight_scale"}
+                  "gate_up_proj.weight_scale": "w13_weight_scale", "down_proj.weight_scale": "w2_weight_scale",
+                  "gate_up_proj.input_global_scale": "w13_input_global_scale",
+                  "down_proj.input_global_scale": "w2_input_global_scale"}
 
         def _cb_load_weights(weights):
             deferred = []
@@ -183,8 +198,21 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
             raise NativeKernelUnavailableError(
                 f"{self.prefix}: apply_router_weight_on_input unsupported for CB MoE")
 
+    def _finalize_static_activation_scales(self, layer) -> None:
+        """Gate after loading for contracted stacks (gridbook/moe.py:560-594): each declared stage
+        has its parameter and it was loaded with one finite positive scale."""
+        for which in ("w13", "w2"):
+            if not self.has_static_fp4_activation[which]:
+                continue
+            p = getattr(layer, f"{which}_input_global_scale", None)
+            if p is None:
+                raise ValueError(f"{self.prefix}: contracted FP4-CB MoE has no {which}_input_global_scale parameter")
+            setattr(layer, f"_cb_fp4_input_global_scale_{which}_f32",
+                    codec.loaded_static_activation_scale(p.data, f"{self.prefix}.{which}"))
+
     def process_weights_after_loading(self, layer) -> None:
         self._require_served_contract(layer)
+        self._finalize_static_activation_scales(layer)
         _native.load(f"{self.prefix}: CB routed experts")
         if not layer.w13_cb_qweight.is_cuda:
             raise NativeKernelUnavailableError(

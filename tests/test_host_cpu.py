@@ -709,3 +709,66 @@ def test_linear_method_parameter_shapes():
     assert l4.cb_qweight.shape == (32, 3 * 73) and not hasattr(l4, "weight_scale")
     with pytest.raises(ValueError, match="multiple of 256"):
         fp4.create_weights(torch.nn.Module(), 300, [32], 300, 32, torch.bfloat16)
+
+
+def test_static_activation_contract_parameters_load_and_the_gate_fails_closed():
+    """A scheme that declares the static NVFP4 activation contract ships `input_global_scale`
+    tensors (gridbook/linear.py:214-218,252-267,348-372; gridbook/moe.py:423-427,492-500,560-594):
+    the parameters exist so the checkpoint loads, start as NaN so a tensor that never arrived is
+    seen, and the gate after loading wants one finite positive scale per module, bit-identical
+    across the logical shards.  The declaration is fp4-only and names one known contract."""
+    from gridbook_b200 import codec
+    from gridbook_b200.linear import PrismaQuantCBLinearMethod
+    from gridbook_b200.moe import PrismaQuantCBMoEMethod
+    fp4 = {"grid": "fp4", "mode": "product", "k": 16, "n_sub": 2, "type_size": 73, "scale_coding": "two_tier",
+           "activation_contract": "nvfp4_w4a4"}
+    m = PrismaQuantCBLinearMethod(None, fp4, "model.layers.0.self_attn.qkv_proj")
+    layer = torch.nn.Module()
+    m.create_weights(layer, 512, [32, 16, 16], 512, 64, torch.bfloat16, weight_loader=None)
+    assert layer.input_global_scale.shape == (3,) and layer.input_global_scale.dtype is torch.float32
+    assert bool(torch.isnan(layer.input_global_scale).all())
+    with pytest.raises(ValueError, match="finite positive"):            # nothing was loaded
+        m.process_weights_after_loading(layer)
+    layer.input_global_scale.data.copy_(torch.tensor([0.5, 0.5, 0.25]))
+    with pytest.raises(ValueError, match="non-identical input_global_scale"):
+        m.process_weights_after_loading(layer)
+    layer.input_global_scale.data.fill_(0.5)
+    m._finalize_static_activation_scale(layer)
+    assert layer._cb_fp4_input_global_scale_f32 == 0.5
+    del layer.input_global_scale
+    with pytest.raises(ValueError, match="no input_global_scale parameter"):
+        m._finalize_static_activation_scale(layer)
+    plain = PrismaQuantCBLinearMethod(None, {k: v for k, v in fp4.items() if k != "activation_contract"}, "p")
+    l2 = torch.nn.Module()
+    plain.create_weights(l2, 512, [32], 512, 32, torch.bfloat16)
+    assert not hasattr(l2, "input_global_scale")
+    plain._finalize_static_activation_scale(l2)                          # nothing to check
+
+    with pytest.raises(ValueError, match="fp4-only"):
+        PrismaQuantCBLinearMethod(None, {"grid": "fp8", "mode": "product", "k": 32, "n_sub": 4, "type_size": 128,
+                                         "activation_contract": "nvfp4_w4a4"}, "x")
+    with pytest.raises(ValueError, match="unsupported activation_contract 'other'"):
+        PrismaQuantCBLinearMethod(None, dict(fp4, activation_contract="other"), "x")
+    with pytest.raises(ValueError, match="nonempty 1-D float32"):
+        codec.loaded_static_activation_scale(torch.zeros(2, 2), "x")
+    with pytest.raises(ValueError, match="finite positive"):
+        codec.loaded_static_activation_scale(torch.tensor([-0.0, 0.0]), "x")  # equal values, different bits
+
+    moe = PrismaQuantCBMoEMethod(None, None, fp4, "model.layers.1.mlp.experts")
+
+    class Layer(torch.nn.Module):
+        def load_weights(self, weights):
+            yield from (name for name, _ in weights)
+
+    ml = Layer()
+    moe.create_weights(ml, 4, 512, 256, torch.bfloat16)
+    assert ml.w13_input_global_scale.shape == (1,) and bool(torch.isnan(ml.w2_input_global_scale).all())
+    with pytest.raises(ValueError, match=r"experts\.w13\.input_global_scale.*finite positive"):
+        moe._finalize_static_activation_scales(ml)
+    loaded = list(ml.load_weights([("gate_up_proj.input_global_scale", torch.tensor([2.0])),
+                                   ("down_proj.input_global_scale", torch.tensor([4.0]))]))
+    assert loaded == ["w13_input_global_scale", "w2_input_global_scale"]
+    moe._finalize_static_activation_scales(ml)
+    assert (ml._cb_fp4_input_global_scale_w13_f32, ml._cb_fp4_input_global_scale_w2_f32) == (2.0, 4.0)
+    with pytest.raises(ValueError, match="stacked"):
+        list(ml.load_weights([("down_proj.input_global_scale", torch.tensor(4.0))]))   # a 0-d tensor breaks the contract
