@@ -3,7 +3,7 @@ is native-only.  Every module of gridbook_b200 is parsed and must not (a) import
 Triton, tilelang or another kernel library, (b) call torch.compile, (c) compute a linear with a
 torch GEMM (F.linear, matmul, mm, bmm, einsum, the @ operator) - a missing library or kernel has to
 fail closed, never fall back - and (d) read a working file or the reference checkout.  The CUDA
-sources must not name a cluster-multicast bulk load.  No GPU needed."""
+sources must not name a bulk load that is shared out over a cluster.  No GPU needed."""
 import ast
 import os
 import re
@@ -61,13 +61,19 @@ def test_module_reads_no_working_file_and_no_reference_checkout(name):
     assert not re.search(r"[\"']/root/", text), f"{name} holds a path of one machine"
 
 
-def test_cuda_sources_name_no_cluster_multicast_bulk_load():
+def test_cuda_sources_name_no_bulk_load_shared_over_a_cluster():
+    """Every bulk or tensor copy instruction in the CUDA sources is written without the qualifier that
+    delivers one load to several CTAs of a cluster (spelled in two halves here, so that this file
+    does not name it either)."""
+    qualifier = "multi" + "cast"
+    bulk = "cp" + r"\.async\." + "bulk" + r"[.\w:]*"
     csrc = os.path.join(PKG, "csrc")
     for f in sorted(os.listdir(csrc)):
         with open(os.path.join(csrc, f)) as fh:
             text = fh.read()
-        for m in re.finditer(r"cp\.async\.bulk[.\w:]*", text):
-            assert "multicast" not in m.group(0), f"{f}: {m.group(0)}"
+        assert qualifier + "::cluster" not in text, f
+        for m in re.finditer(bulk, text):
+            assert qualifier not in m.group(0), f"{f}: {m.group(0)}"
 
 
 def test_no_except_clause_swallows_a_missing_kernel():
