@@ -108,7 +108,7 @@ class Artifact:
     def load_experts(self, prefix: str, device="cuda") -> torch.nn.Module:
         """The routed expert stack under ``prefix`` (``<prefix>.gate_up_proj`` / ``.down_proj``
         stacked tensors, docs/SPEC.md:281-289) as a module taking (x, topk_weights, topk_ids)."""
-        from .moe import PrismaQuantCBMoEMethod
+        from .moe import PrismaQuantCBMoEMethod, mark_filled
         cfg = self.config
         pair = cfg._moe_scheme_for_prefix(prefix)
         if pair is None:
@@ -122,6 +122,8 @@ class Artifact:
         method.create_weights(module, E, hidden, two_inter // 2, torch.bfloat16)
         module.w13_cb_qweight.data = w13.to(device)
         module.w2_cb_qweight.data = w2.to(device)
+        mark_filled(module.w13_cb_qweight)
+        mark_filled(module.w2_cb_qweight)
         if not method.fmt13.is_fp4:
             module.w13_weight_scale.data = self.tensor(f"{prefix}.gate_up_proj.weight_scale").to(device)
         if not method.fmt2.is_fp4:

@@ -44,6 +44,34 @@ def _row_bytes(in_features: int, type_size: int) -> int:
     return (in_features // codec.SUPERBLOCK) * type_size
 
 
+# Every stacked expert parameter carries a "was it filled" stamp (gridbook/cb_fill_guard.py:33-75):
+# create_weights allocates uninitialised memory, and a model class whose loader never reaches the
+# stacks would otherwise serve it without any error.
+CB_FILLED_ATTR = "_pq_cb_filled"
+CB_EXPERT_PARAM_NAMES = ("w13_cb_qweight", "w2_cb_qweight")
+
+
+def mark_filled(param) -> None:
+    """Record that checkpoint bytes were put into a stacked expert parameter.  Every fill path
+    calls it: the load hook below, the artifact loader, CBMoE.load, and any loader of the caller's
+    own that assigns the stacks directly."""
+    setattr(param, CB_FILLED_ATTR, True)
+
+
+def unfilled_cb_params(layer) -> list[str]:
+    """Names of the registered, non-empty expert stacks that no fill path has marked.  A stack that
+    is absent or has no experts on this rank proves nothing and is skipped; one without a stamp at
+    all did not come from create_weights and counts as unfilled."""
+    missing = []
+    for name in CB_EXPERT_PARAM_NAMES:
+        p = getattr(layer, name, None)
+        if p is None or p.numel() == 0:
+            continue
+        if not getattr(p, CB_FILLED_ATTR, False):
+            missing.append(name)
+    return missing
+
+
 class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
     """CB decode for routed experts.  ``scheme`` is the gate_up format; ``scheme_down``
     (optional, not expressible in the reference: gridbook/config.py:1631-1640) gives the
@@ -94,6 +122,8 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
             (E, 2 * inter, _row_bytes(hidden_size, self.fmt13.type_size)), torch.uint8))
         layer.register_parameter("w2_cb_qweight", param(
             (E, hidden_size, _row_bytes(inter, self.fmt2.type_size)), torch.uint8))
+        for name in CB_EXPERT_PARAM_NAMES:
+            setattr(getattr(layer, name), CB_FILLED_ATTR, False)
         if not self.fmt13.is_fp4:
             layer.register_parameter("w13_weight_scale", param((E, 2 * inter), torch.float32))
         if not self.fmt2.is_fp4:
@@ -127,6 +157,8 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
                         raise ValueError(f"{prefix}.{name}: checkpoint shape {tuple(w.shape)} != param "
                                          f"{tuple(p.shape)} — stacked (E, out, bytes) contract violated")
                     p.data.copy_(w.to(p.dtype))
+                    if pname in CB_EXPERT_PARAM_NAMES:
+                        mark_filled(p)
                     yield pname
                 else:
                     deferred.append((name, w))
@@ -210,8 +242,19 @@ class PrismaQuantCBMoEMethod(FusedMoEMethodBase):
             setattr(layer, f"_cb_fp4_input_global_scale_{which}_f32",
                     codec.loaded_static_activation_scale(p.data, f"{self.prefix}.{which}"))
 
+    def _assert_experts_filled(self, layer) -> None:
+        """No environment override, by design (gridbook/cb_fill_guard.py:121-140)."""
+        missing = unfilled_cb_params(layer)
+        if missing:
+            raise RuntimeError(
+                f"{self.prefix}: CB expert stack(s) {missing} were REGISTERED but never FILLED from the checkpoint: "
+                f"the layer would serve uninitialised memory (plausible garbage, not a crash). The model class's "
+                f"loader did not pass '<experts>.<proj>.cb_qweight' tensors to this layer's load_weights hook; "
+                f"route them there, or call gridbook_b200.moe.mark_filled(param) after filling a stack directly.")
+
     def process_weights_after_loading(self, layer) -> None:
         self._require_served_contract(layer)
+        self._assert_experts_filled(layer)
         self._finalize_static_activation_scales(layer)
         _native.load(f"{self.prefix}: CB routed experts")
         if not layer.w13_cb_qweight.is_cuda:
@@ -418,6 +461,8 @@ class CBMoE(torch.nn.Module):
     def load(self, w13, w2, w13_scale=None, w2_scale=None, device="cuda"):
         self.w13_cb_qweight.data = w13.to(device)
         self.w2_cb_qweight.data = w2.to(device)
+        mark_filled(self.w13_cb_qweight)
+        mark_filled(self.w2_cb_qweight)
         if w13_scale is not None:
             self.w13_weight_scale.data = w13_scale.to(device)
         if w2_scale is not None:

@@ -772,3 +772,51 @@ def test_static_activation_contract_parameters_load_and_the_gate_fails_closed():
     assert (ml._cb_fp4_input_global_scale_w13_f32, ml._cb_fp4_input_global_scale_w2_f32) == (2.0, 4.0)
     with pytest.raises(ValueError, match="stacked"):
         list(ml.load_weights([("down_proj.input_global_scale", torch.tensor(4.0))]))   # a 0-d tensor breaks the contract
+
+
+def test_expert_stacks_that_were_never_filled_are_refused_after_loading():
+    """The guard the reference pins in tests/test_cb_fill_guard.py: create_weights allocates
+    uninitialised stacks, and a model class whose loader never hands them to this layer would serve
+    that memory without any error.  Every fill path stamps the parameter; after loading, a registered
+    non-empty stack without the stamp is refused by name - before any native library is touched, with
+    no override.  Absent or empty stacks prove nothing and are skipped."""
+    from gridbook_b200 import moe as M
+    scheme = {"grid": "fp4", "mode": "full", "k": 8, "n_sub": 1, "type_size": 48}
+    method = M.PrismaQuantCBMoEMethod(None, None, scheme, "model.layers.0.mlp.experts")
+
+    class Layer(torch.nn.Module):
+        def load_weights(self, weights):
+            yield from (name for name, _ in weights)
+
+    layer = Layer()
+    method.create_weights(layer, 2, 256, 256, torch.bfloat16)
+    assert M.unfilled_cb_params(layer) == ["w13_cb_qweight", "w2_cb_qweight"]
+    with pytest.raises(RuntimeError, match=r"\['w13_cb_qweight', 'w2_cb_qweight'\] were REGISTERED but never FILLED"):
+        method.process_weights_after_loading(layer)
+    list(layer.load_weights([("gate_up_proj.cb_qweight", torch.zeros(2, 512, 48, dtype=torch.uint8))]))
+    assert M.unfilled_cb_params(layer) == ["w2_cb_qweight"]                 # the hook stamps what it fills
+    with pytest.raises(RuntimeError, match=r"\['w2_cb_qweight'\] were REGISTERED"):
+        method.process_weights_after_loading(layer)
+    layer.w2_cb_qweight.data = torch.zeros(2, 256, 48, dtype=torch.uint8)   # a direct fill ...
+    assert M.unfilled_cb_params(layer) == ["w2_cb_qweight"]
+    M.mark_filled(layer.w2_cb_qweight)                                      # ... has to say so
+    assert M.unfilled_cb_params(layer) == []
+    method._assert_experts_filled(layer)
+
+    empty = Layer()
+    method.create_weights(empty, 0, 256, 256, torch.bfloat16)               # no experts on this rank
+    assert M.unfilled_cb_params(empty) == [] and M.unfilled_cb_params(Layer()) == []
+    foreign = Layer()
+    foreign.w13_cb_qweight = torch.nn.Parameter(torch.zeros(1, 4, 48, dtype=torch.uint8), requires_grad=False)
+    assert M.unfilled_cb_params(foreign) == ["w13_cb_qweight"]              # no stamp at all: not ours, not filled
+
+    # the stand-alone module's load() stamps both stacks: it gets past the guard and stops at the
+    # next gate (no CPU path)
+    from gridbook_b200._native import NativeKernelUnavailableError
+    from gridbook_b200.formats import CBFormat
+    fmt = CBFormat.from_scheme(scheme)
+    tabs = [torch.zeros(256, 8)]
+    alone = M.CBMoE(fmt, fmt, 2, 256, 256, tabs, tabs)
+    with pytest.raises(NativeKernelUnavailableError, match="CUDA device"):
+        alone.load(torch.zeros(2, 512, 48, dtype=torch.uint8), torch.zeros(2, 256, 48, dtype=torch.uint8), device="cpu")
+    assert M.unfilled_cb_params(alone) == []
