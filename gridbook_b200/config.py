@@ -19,6 +19,36 @@ DEFAULT_PACKED_MODULES = {
 }
 _MOE_SUFFIXES = (".experts", ".mlp.experts", ".ffn.experts")
 
+try:                                    # the engine's ignore lists are written for this engine
+    import regex as _regex              # (Unicode properties); the stdlib one otherwise
+except ImportError:                     # pragma: no cover - depends on the environment
+    import re as _regex
+
+
+def _canonical_prefix(name: str) -> str:
+    """One namespace for the three spellings a module of the language model arrives in
+    (gridbook/config.py:228-255): the wrapper-class serving form `language_model.model.X`, the
+    older multimodal checkpoint form `model.language_model.X`, a bare `language_model.X`, and the
+    source form `layers.N...` of checkpoints whose keys carry no `model.` at all - all become
+    `model.X`.  Prefix-anchored; `visual.*`, `mtp.*`, `lm_head`, plain `model.layers.*` pass through."""
+    for head, keep in (("language_model.model.", "model."), ("language_model.", "model."),
+                       ("model.language_model.", "model.")):
+        if name.startswith(head):
+            return keep + name[len(head):]
+    if name.startswith("layers."):
+        return "model." + name
+    return name
+
+
+_canonical_target = _canonical_prefix     # stored targets and ignore entries: the same rewrite, once, at parse time
+
+
+def _candidate_bases(name: str) -> list[str]:
+    """The strings `name` may be matched as, most specific first: as given (the engine's mapper can
+    move the stored keys into a namespace of its own after parsing), then canonical."""
+    canonical = _canonical_prefix(name)
+    return [name] if canonical == name else [name, canonical]
+
 
 class PrismaQuantConfig(QuantizationConfig):
     """Holds the raw ``quantization_config`` and resolves it lazily (the sidecar files are
@@ -61,9 +91,15 @@ class PrismaQuantConfig(QuantizationConfig):
         return "gridbook" if method in ("gridbook", "prismaquant") else None
 
     def apply_vllm_mapper(self, hf_to_vllm_mapper) -> None:
+        """The engine's checkpoint-to-module renaming, applied to the stored targets and to the literal
+        ignore entries; patterns (`re:`) are never handed to it (gridbook/config.py:1761)."""
         self._ensure_resolved()
         if hasattr(hf_to_vllm_mapper, "apply_dict"):
             self.target_scheme = hf_to_vllm_mapper.apply_dict(self.target_scheme)
+        if hasattr(hf_to_vllm_mapper, "apply_list"):
+            literal = [ig for ig in self.ignore if not ig.startswith("re:")]
+            mapped = iter(hf_to_vllm_mapper.apply_list(literal))
+            self.ignore = [ig if ig.startswith("re:") else next(mapped) for ig in self.ignore]
 
     # ---- resolution -------------------------------------------------------------------
     def _ensure_resolved(self) -> None:
@@ -84,7 +120,7 @@ class PrismaQuantConfig(QuantizationConfig):
                 # other backends, gridbook/config.py:803-957): remembered so that a lookup can say
                 # so instead of raising a bare KeyError or running them unquantized by accident
                 for target in group.get("targets", []):
-                    self.delegated_targets[target] = gname
+                    self.delegated_targets[_canonical_target(target)] = gname
                 continue
             # v1 / v2 is decided by the group's OWN scale_coding: absent means v1 (E4M3-direct),
             # whatever the artifact's layout_version says (docs/SPEC.md:130-177; the reference's
@@ -92,8 +128,9 @@ class PrismaQuantConfig(QuantizationConfig):
             scheme = dict(raw_scheme)
             scheme.setdefault("_group", gname)
             for target in group.get("targets", []):
-                self.target_scheme[target] = scheme
-        self.ignore = list(full.get("ignore", []))
+                self.target_scheme[_canonical_target(target)] = scheme
+        # literal entries name one module (canonicalised like the targets); `re:` entries are patterns
+        self.ignore = [ig if ig.startswith("re:") else _canonical_target(ig) for ig in full.get("ignore", [])]
         self.codebook_file = full.get("codebook_file", self.raw.get("codebook_file", "cb_codebooks.pqcb"))
         # artifact-external digests of the sidecar's tables (docs/SPEC.md:326-378); None = not declared
         prov = full.get("provenance")
@@ -149,26 +186,56 @@ class PrismaQuantConfig(QuantizationConfig):
     # wrapper prefixes a serving class may put in front of (or strip from) the checkpoint's names
     _WRAPPERS = ("model", "language_model", "language_model.model", "model.language_model", "text_model")
 
-    def _lookup(self, key: str) -> dict | None:
-        if key in self.target_scheme:
-            return self.target_scheme[key]
-        # Only a known wrapper prefix may separate the two names: a second tower whose modules
-        # end in the same tail (vision_tower.layers.0.mlp...) must not pick up this scheme.
-        for stored, scheme in self.target_scheme.items():
-            for wrap in self._WRAPPERS:
-                if key == f"{wrap}.{stored}" or stored == f"{wrap}.{key}":
-                    return scheme
+    def _find(self, table: dict, key: str):
+        """Entry of `table` (stored name -> value) that names the module `key`: the name as given,
+        then its canonical form, then either side behind a known wrapper prefix.  Only a wrapper may
+        separate the two names: a second tower whose modules end in the same tail
+        (vision_tower.layers.0.mlp...) must not pick up this entry."""
+        bases = _candidate_bases(key)
+        for base in bases:
+            if base in table:
+                return table[base]
+        for stored, value in table.items():
+            for base in bases:
+                for wrap in self._WRAPPERS:
+                    if base == f"{wrap}.{stored}" or stored == f"{wrap}.{base}":
+                        return value
         return None
 
+    def _lookup(self, key: str) -> dict | None:
+        return self._find(self.target_scheme, key)
+
     def _delegated_group(self, key: str) -> str | None:
-        table = getattr(self, "delegated_targets", {})
-        if key in table:
-            return table[key]
-        for stored, gname in table.items():
-            for wrap in self._WRAPPERS:
-                if key == f"{wrap}.{stored}" or stored == f"{wrap}.{key}":
-                    return gname
-        return None
+        return self._find(getattr(self, "delegated_targets", {}), key)
+
+    def _name_ignored(self, name: str) -> bool:
+        for base in _candidate_bases(name):
+            for ig in self.ignore:
+                if ig.startswith("re:"):
+                    if _regex.match(ig[3:], base):           # start-anchored, not a full match
+                        return True
+                elif base == ig:
+                    return True
+        return False
+
+    def _is_ignored(self, prefix: str) -> bool:
+        """The `ignore` list with the exact / `re:` reading the engine's own compressed-tensors
+        matcher gives it (the reference pins this in tests/test_target_namespace_compat.py:484-545): a
+        literal entry names one module, nothing under it and nothing that merely starts the same; a
+        pattern is `re.match`ed; a fused module is judged by its checkpoint shards, all of which
+        must agree."""
+        self._ensure_resolved()
+        head, _, leaf = prefix.rpartition(".")
+        roles = self.packed_modules_mapping.get(leaf)
+        if roles:
+            names = [f"{head}.{r}" if head else r for r in roles]
+            flags = [self._name_ignored(n) for n in names]
+            if any(flags) and not all(flags):
+                hit = [n for n, f in zip(names, flags) if f]
+                raise ValueError(f"[prismaquant] {prefix}: the shards of a fused module have different quantization "
+                                 f"schemes: only {hit} of {names} are on the ignore list")
+            return all(flags)
+        return self._name_ignored(prefix)
 
     def _scheme_for_prefix(self, prefix: str) -> dict | None:
         keys = self.shard_target_keys(prefix)
@@ -218,10 +285,8 @@ class PrismaQuantConfig(QuantizationConfig):
         for stored in self.target_scheme:
             tail = stored.rsplit(".format_group_", 1)
             if len(tail) == 2 and tail[1].isdigit():
-                base = tail[0]
                 for leaf in ("gate_proj", "up_proj", "gate_up_proj", "down_proj"):
-                    if any(base == f"{w}{prefix}.{leaf}" for w in ("",) + tuple(f"{x}." for x in self._WRAPPERS)) or \
-                            any(f"{w}.{base}" == f"{prefix}.{leaf}" for w in self._WRAPPERS):
+                    if self._find({tail[0]: True}, f"{prefix}.{leaf}"):
                         raise NativeKernelUnavailableError(
                             f"[prismaquant] {prefix}: target {stored!r} is a per-expert format group; stacks whose "
                             "experts differ in format are not served by gridbook_b200")
@@ -269,7 +334,7 @@ class PrismaQuantConfig(QuantizationConfig):
     def get_quant_method(self, layer, prefix: str):
         self._ensure_resolved()
         self._require_single_gpu_engine()
-        if any(prefix == ig or prefix.startswith(ig + ".") for ig in self.ignore):
+        if self._is_ignored(prefix):
             return _unquantized(layer)
         kind = type(layer).__name__
         if "MoE" in kind or "RoutedExperts" in kind or prefix.endswith(_MOE_SUFFIXES):
