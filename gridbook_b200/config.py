@@ -12,10 +12,25 @@ import torch
 from ._native import NativeKernelUnavailableError
 from ._vllm_compat import HAVE_VLLM, QuantizationConfig
 
-# fused module -> the checkpoint's per-role Linears, in shard order
+# fused module -> the checkpoint's per-role Linears, in shard order.  The engine publishes its own
+# mapping by dispatch time; this table stays underneath it as the fallback (gridbook/config.py:115-132):
+# the gated-delta-net projections, and the attention module that merges `wq_a` with `wkv` through its
+# stacked-parameter table without declaring a packed mapping at all.
 DEFAULT_PACKED_MODULES = {
     "qkv_proj": ["q_proj", "k_proj", "v_proj"],
     "gate_up_proj": ["gate_proj", "up_proj"],
+    "in_proj_qkvz": ["in_proj_qkv", "in_proj_z"],
+    "in_proj_ba": ["in_proj_b", "in_proj_a"],
+    "fused_wqa_wkv": ["wq_a", "wkv"],
+}
+# Other checkpoint spellings of a served leaf (gridbook/config.py:134-158): a different fusion (`w1` /
+# `w3` into the same `gate_up_proj`) or a plain rename (`w2` for `down_proj`).  Consulted only after
+# the primary spelling found nothing; the first spelling with a hit wins whole, never mixed.
+ALTERNATE_SHARD_SPELLINGS = {
+    "gate_up_proj": (["w1", "w3"],),
+    "gate_proj": (["w1"],),
+    "up_proj": (["w3"],),
+    "down_proj": (["w2"],),
 }
 _MOE_SUFFIXES = (".experts", ".mlp.experts", ".ffn.experts")
 
@@ -167,21 +182,34 @@ class PrismaQuantConfig(QuantizationConfig):
         return [books[n] for n in names]
 
     # ---- fused shards (gridbook/config.py:1129-1204) ----------------------------------
+    def _fused_roles(self, leaf: str) -> list[str] | None:
+        live = getattr(self, "packed_modules_mapping", None) or {}
+        return live.get(leaf) or DEFAULT_PACKED_MODULES.get(leaf)
+
     def shard_target_keys(self, prefix: str, unfused_fallback: bool = False) -> list[str]:
+        """Checkpoint names whose rows make up the module `prefix`, in shard order: the roles of a
+        fused module, the module itself, or another spelling of either."""
         self._ensure_resolved()
         head, _, leaf = prefix.rpartition(".")
-        roles = self.packed_modules_mapping.get(leaf)
+        spellings = []
+        roles = self._fused_roles(leaf)
         if roles:
-            keys = [f"{head}.{r}" if head else r for r in roles]
+            spellings.append(list(roles))
+        spellings.append(None)                                  # the module under its own name
+        spellings.extend(list(a) for a in ALTERNATE_SHARD_SPELLINGS.get(leaf, ()))
+        for names in spellings:
+            if names is None:
+                if self._lookup(prefix) is not None:
+                    return [prefix]
+                continue
+            keys = [f"{head}.{r}" if head else r for r in names]
             found = [k for k in keys if self._lookup(k) is not None]
             if found and len(found) != len(keys):
                 raise ValueError(f"[prismaquant] {prefix}: only {found} of {keys} are CB targets; mixed "
                                  "fused modules are not served")
             if found:
                 return keys
-        if self._lookup(prefix) is not None or unfused_fallback:
-            return [prefix]
-        return []
+        return [prefix] if unfused_fallback else []
 
     # wrapper prefixes a serving class may put in front of (or strip from) the checkpoint's names
     _WRAPPERS = ("model", "language_model", "language_model.model", "model.language_model", "text_model")
@@ -226,7 +254,7 @@ class PrismaQuantConfig(QuantizationConfig):
         must agree."""
         self._ensure_resolved()
         head, _, leaf = prefix.rpartition(".")
-        roles = self.packed_modules_mapping.get(leaf)
+        roles = self._fused_roles(leaf)
         if roles:
             names = [f"{head}.{r}" if head else r for r in roles]
             flags = [self._name_ignored(n) for n in names]

@@ -165,3 +165,38 @@ def test_get_quant_method_uses_the_same_resolution(monkeypatch):
                           PrismaQuantCBLinearMethod)
     assert not isinstance(cfg.get_quant_method(Linear(), "language_model.model.layers.5.mlp.gate_up_proj"),
                           PrismaQuantCBLinearMethod)
+
+
+@pytest.mark.parametrize("leaf,members", [("qkv_proj", ("q_proj", "k_proj", "v_proj")), ("gate_up_proj", ("gate_proj", "up_proj")),
+                                          ("in_proj_qkvz", ("in_proj_qkv", "in_proj_z")), ("in_proj_ba", ("in_proj_b", "in_proj_a")),
+                                          ("fused_wqa_wkv", ("wq_a", "wkv"))])
+def test_every_fused_family_is_refused_from_its_checkpoint_roles(leaf, members):
+    """The fused modules the reference knows without the engine's help (gridbook/config.py:117-132),
+    also when the engine's own mapping has replaced the default one."""
+    base = "model.layers.7.mod."
+    cfg = _config({"cb": [base + m for m in members]})
+    for ns in ("", "language_model."):
+        assert cfg._scheme_for_prefix(ns + base + leaf) is not None
+        assert cfg.shard_target_keys(ns + base + leaf) == [ns + base + m for m in members]
+    cfg.packed_modules_mapping = {"something_else": ["a", "b"]}                  # what an engine may publish
+    assert cfg._scheme_for_prefix(base + leaf) is not None
+    cfg.packed_modules_mapping = {leaf: list(reversed(members))}                 # the engine's order wins
+    assert cfg.shard_target_keys(base + leaf) == [base + m for m in reversed(members)]
+
+
+def test_alternate_checkpoint_spellings_are_tried_after_the_primary_one():
+    """`w1` / `w3` fuse into the same gate_up_proj, `w2` is the down projection
+    (gridbook/config.py:134-158): consulted only when the primary spelling finds nothing, and a
+    spelling wins whole."""
+    base = "model.layers.3.mlp.shared_experts."
+    alt = _config({"cb": [base + "w1", base + "w3", base + "w2"]})
+    assert alt.shard_target_keys(base + "gate_up_proj") == [base + "w1", base + "w3"]
+    assert alt.shard_target_keys(base + "down_proj") == [base + "w2"]
+    assert alt.shard_target_keys(base + "gate_proj") == [base + "w1"] and alt.shard_target_keys(base + "up_proj") == [base + "w3"]
+    assert alt._scheme_for_prefix(base + "gate_up_proj") is not None
+    both = _config({"cb": [base + "gate_proj", base + "up_proj", base + "w1", base + "w3"]})
+    assert both.shard_target_keys(base + "gate_up_proj") == [base + "gate_proj", base + "up_proj"]
+    with pytest.raises(ValueError, match="mixed fused modules"):
+        _config({"cb": [base + "w1"]}).shard_target_keys(base + "gate_up_proj")
+    assert _config({"cb": [base + "w9"]}).shard_target_keys(base + "gate_up_proj") == []
+    assert _config({"cb": [base + "w9"]}).shard_target_keys(base + "gate_up_proj", unfused_fallback=True) == [base + "gate_up_proj"]
