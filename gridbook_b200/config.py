@@ -223,12 +223,27 @@ class PrismaQuantConfig(QuantizationConfig):
         for base in bases:
             if base in table:
                 return table[base]
-        for stored, value in table.items():
-            for base in bases:
-                for wrap in self._WRAPPERS:
-                    if base == f"{wrap}.{stored}" or stored == f"{wrap}.{base}":
-                        return value
+        wrapped = self._wrapped_index(table)
+        for base in bases:
+            if base in wrapped:
+                return wrapped[base]
         return None
+
+    def _wrapped_index(self, table: dict) -> dict:
+        """name -> value for every stored name put behind, or freed from, one wrapper prefix; built
+        once per table (a model has thousands of targets and asks once per module)."""
+        cache = self.__dict__.setdefault("_wrapped_cache", [])
+        for seen, size, index in cache:
+            if seen is table and size == len(table):
+                return index
+        index: dict = {}
+        for stored, value in table.items():
+            for wrap in self._WRAPPERS:
+                index.setdefault(f"{wrap}.{stored}", value)
+                if stored.startswith(wrap + "."):
+                    index.setdefault(stored[len(wrap) + 1:], value)
+        cache[:] = [c for c in cache if c[0] is not table][-3:] + [(table, len(table), index)]
+        return index
 
     def _lookup(self, key: str) -> dict | None:
         return self._find(self.target_scheme, key)
